@@ -1,0 +1,114 @@
+"""In-tree build of the native library (``mesh_b200/_lib/libmesh_b200.so``).
+
+Every ``.cu`` / ``.cpp`` under ``mesh_b200/csrc`` is compiled with nvcc for sm_100a only
+(``-gencode arch=compute_100a,code=sm_100a``) and linked into one shared object that
+Python loads through ctypes.  Objects are cached by content hash, so a rebuild after a
+small edit takes seconds.  Run ``python -m mesh_b200._build`` or call :func:`build`.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import json
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+LIBDIR = ROOT / "_lib"
+OBJDIR = ROOT.parent / "build" / "obj"
+LIBNAME = "libmesh_b200.so"
+
+NVCC_FLAGS = [
+    "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+    "-Xcompiler", "-fPIC,-fvisibility=default", "--expt-relaxed-constexpr", "-DNDEBUG",
+]
+
+
+def nvcc_path() -> str | None:
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    return cand if os.path.exists(cand) else None
+
+
+def sources() -> list[Path]:
+    out = sorted(p for p in CSRC.rglob("*.cu")) + sorted(p for p in CSRC.rglob("*.cpp"))
+    return [p for p in out if "/standalone/" not in str(p)]
+
+
+def _headers_digest() -> str:
+    h = hashlib.sha256()
+    for p in sorted(list(CSRC.rglob("*.cuh")) + list(CSRC.rglob("*.h"))):
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _compile_one(nvcc: str, src: Path, hdr: str, verbose: bool) -> Path:
+    h = hashlib.sha256(src.read_bytes())
+    h.update(hdr.encode())
+    obj = OBJDIR / f"{src.stem}-{h.hexdigest()[:16]}.o"
+    if obj.exists():
+        return obj
+    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    if src.suffix == ".cpp":
+        cmd.insert(1, "-x"); cmd.insert(2, "cu")
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+    if verbose and r.stderr.strip():
+        print(r.stderr, file=sys.stderr)
+    return obj
+
+
+def lib_path() -> Path:
+    return LIBDIR / LIBNAME
+
+
+def is_current() -> bool:
+    meta = LIBDIR / "build.json"
+    if not (lib_path().exists() and meta.exists()):
+        return False
+    try:
+        return json.loads(meta.read_text()).get("digest") == _tree_digest()
+    except Exception:
+        return False
+
+
+def _tree_digest() -> str:
+    h = hashlib.sha256(_headers_digest().encode())
+    for s in sources():
+        h.update(str(s.relative_to(CSRC)).encode())
+        h.update(s.read_bytes())
+    return h.hexdigest()
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every source for sm_100a and link the shared library.  Returns its path."""
+    if not force and is_current():
+        return lib_path()
+    nvcc = nvcc_path()
+    if nvcc is None:
+        raise RuntimeError("nvcc not found: cannot build mesh_b200's native library")
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    hdr = _headers_digest()
+    srcs = sources()
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+        objs = list(ex.map(lambda s: _compile_one(nvcc, s, hdr, verbose), srcs))
+    tmp = LIBDIR / (LIBNAME + ".tmp")
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(tmp),
+           *map(str, objs), "-lpthread", "-ldl", "-lrt"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, lib_path())
+    (LIBDIR / "build.json").write_text(json.dumps({"digest": _tree_digest(), "sources": [str(s.relative_to(CSRC)) for s in srcs]}))
+    return lib_path()
+
+
+if __name__ == "__main__":
+    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(p)

@@ -1,0 +1,76 @@
+"""ctypes access to ``libmesh_b200.so``.
+
+The library is built in-tree by :mod:`mesh_b200._build`.  On a machine with a GPU a missing
+or unloadable library is an error (ops never fall back silently to eager PyTorch); on a
+machine without one, CPU-only parts of the package work without it.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_int, c_longlong, c_uint32, c_void_p
+
+_lock = threading.Lock()
+_lib = None
+
+MAX_RANKS = 8
+
+
+class GemmArgs(ctypes.Structure):
+    """Mirror of ``MeshGemmArgs`` (csrc/gemm/gemm_api.h)."""
+    _fields_ = [
+        ("A", c_void_p), ("B", c_void_p), ("D", c_void_p), ("D2", c_void_p), ("aux", c_void_p),
+        ("M", c_int), ("N", c_int), ("K", c_int),
+        ("lda", c_longlong), ("ldb", c_longlong), ("ldd", c_longlong), ("ldd2", c_longlong), ("ld_aux", c_longlong),
+        ("a_rows", c_int), ("b_rows", c_int),
+        ("d_cols", c_int), ("d2_cols", c_int),
+        ("a_mn", c_int), ("b_mn", c_int),
+        ("epi", c_int), ("act", c_int),
+        ("b_up_rows", c_int), ("d_up_cols", c_int),
+        ("status", c_void_p),
+        ("a_ready", c_void_p), ("a_ready_value", c_uint32), ("a_ready_rows", c_int), ("m_rotate", c_int),
+        ("ag_src", c_void_p), ("ag_dst", c_void_p * MAX_RANKS), ("ag_flags", c_void_p * MAX_RANKS),
+        ("ag_rows_per_rank", c_int), ("ag_ld", c_longlong),
+        ("rank", c_int), ("world", c_int),
+        ("rs_recv", c_void_p * MAX_RANKS), ("rs_count", c_void_p * MAX_RANKS),
+        ("rs_expect", c_uint32), ("rs_out", c_void_p), ("rs_rows_per_rank", c_int),
+        ("num_ctas", c_int),
+    ]
+
+
+def available() -> bool:
+    from . import _build
+    return _build.lib_path().exists()
+
+
+def lib() -> ctypes.CDLL:
+    """Load (building first if sources changed and nvcc is present) and return the library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        from . import _build
+        path = _build.lib_path()
+        if not path.exists() or (not _build.is_current() and _build.nvcc_path() is not None):
+            try:
+                path = _build.build()
+            except Exception as e:  # keep a stale but loadable library usable
+                if not path.exists():
+                    raise RuntimeError(f"mesh_b200 native library is missing and could not be built: {e}") from e
+        L = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
+        L.mesh_last_error.restype = ctypes.c_char_p
+        L.mesh_gemm_bf16.argtypes = [ctypes.POINTER(GemmArgs), c_void_p]
+        L.mesh_gemm_bf16.restype = c_int
+        _lib = L
+        return L
+
+
+def last_error() -> str:
+    return lib().mesh_last_error().decode()
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed (code {rc}): {last_error()}")

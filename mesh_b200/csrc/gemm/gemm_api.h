@@ -1,0 +1,53 @@
+// C ABI of the GEMM library (loaded through ctypes; no torch headers involved).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MESH_MAX_RANKS 8
+
+// All leading dimensions are in elements (bf16).  Pointers are device pointers; peer
+// pointers (ag_dst, ag_flags, rs_recv, rs_count) come from the symmetric heap.
+typedef struct MeshGemmArgs {
+  const void* A;
+  const void* B;
+  void* D;
+  void* D2;
+  const void* aux;
+  int M, N, K;
+  long long lda, ldb, ldd, ldd2, ld_aux;
+  int a_rows, b_rows;          // rows of the stored A / B matrices (TMA bounds)
+  int d_cols, d2_cols;         // columns of the stored D / D2 matrices (TMA bounds)
+  int a_mn, b_mn;              // 1: operand is stored [K, rows] (MN-major)
+  int epi, act;
+  int b_up_rows, d_up_cols;
+  void* status;
+  // all-gather -> GEMM
+  const void* a_ready;
+  uint32_t a_ready_value;
+  int a_ready_rows;
+  int m_rotate;
+  const void* ag_src;
+  void* ag_dst[MESH_MAX_RANKS];
+  void* ag_flags[MESH_MAX_RANKS];
+  int ag_rows_per_rank;
+  long long ag_ld;
+  int rank, world;
+  // GEMM -> reduce-scatter
+  void* rs_recv[MESH_MAX_RANKS];
+  void* rs_count[MESH_MAX_RANKS];
+  uint32_t rs_expect;
+  void* rs_out;
+  int rs_rows_per_rank;
+  int num_ctas;                // 0: one per SM
+} MeshGemmArgs;
+
+// Returns 0 or a negative error (bad shape/alignment) or a positive cudaError_t.
+int mesh_gemm_bf16(const MeshGemmArgs* args, void* stream);
+const char* mesh_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif

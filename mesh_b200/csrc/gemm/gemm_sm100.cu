@@ -1,0 +1,170 @@
+// Host side of the tcgen05 GEMM: argument checks, TMA descriptor encoding, launch.
+#include "gemm_sm100.cuh"
+#include "gemm_api.h"
+#include "../runtime/host_common.h"
+
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstring>
+
+namespace mesh {
+namespace gemm {
+
+// 2-D map over a row-major bf16 matrix [rows, cols] with leading dimension ld (elements).
+static bool make_map_2d(CUtensorMap* tm, const void* base, uint64_t cols, uint64_t rows, uint64_t ld,
+                        uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swz) {
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, swz);
+}
+
+// 3-D map that makes a row-major [k_rows, mn_cols] matrix look like [mn_cols/64][k_rows][64], so
+// that one box {64, 64, groups} lands in shared memory as `groups` consecutive 8 KiB
+// [64 k-rows][128 B] slabs — the MN-major canonical layout tcgen05 expects.
+static bool make_map_mn(CUtensorMap* tm, const void* base, uint64_t mn_cols, uint64_t k_rows, uint64_t ld,
+                        uint32_t groups) {
+  cuuint64_t dims[3] = {64, k_rows, mn_cols / 64};
+  cuuint64_t strides[2] = {ld * 2, 128};
+  cuuint32_t box[3] = {64, 64, groups};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+template <int A_MN, int B_MN, int EPI, bool AG>
+static int launch(const Params& p, int ctas, cudaStream_t stream) {
+  auto kern = gemm_kernel<A_MN, B_MN, EPI, AG>;
+  static bool configured = false;   // per instantiation
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return set_error((int)e, "cudaFuncSetAttribute(gemm smem): %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int threads = NUM_THREADS + (AG ? 32 * COMM_WARPS : 0);
+  kern<<<ctas, threads, SMEM_BYTES, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error((int)e, "gemm launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace gemm
+}  // namespace mesh
+
+using namespace mesh;
+using namespace mesh::gemm;
+
+extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return set_error(-1, "gemm: empty problem");
+  if (a->K % 8 || a->N % 8 || a->lda % 8 || a->ldb % 8)
+    return set_error(-2, "gemm: K, N and leading dimensions must be multiples of 8 (16-byte TMA rule)");
+  if ((uintptr_t)a->A % 16 || (uintptr_t)a->B % 16) return set_error(-2, "gemm: operands must be 16-byte aligned");
+  if (a->a_mn && (a->M % 64)) return set_error(-3, "gemm: MN-major A needs M %% 64 == 0");
+  if (a->b_mn && (a->N % 64)) return set_error(-3, "gemm: MN-major B needs N %% 64 == 0");
+  if ((a->epi == EPI_GLU_FWD || a->epi == EPI_GLU_BWD) && (a->N % 32))
+    return set_error(-3, "gemm: GLU epilogues need N %% 32 == 0");
+  if (a->epi == EPI_GLU_FWD && a->b_mn) return set_error(-3, "gemm: GLU forward needs K-major weights");
+  if (a->world > MESH_MAX_RANKS) return set_error(-4, "gemm: world > %d", MESH_MAX_RANKS);
+
+  Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.m_tiles = (a->M + BM - 1) / BM;
+  const int tile_n = (a->epi == EPI_GLU_FWD) ? BN / 2 : BN;
+  p.n_tiles = (a->N + tile_n - 1) / tile_n;
+  p.k_blocks = (a->K + BK - 1) / BK;
+  p.act = a->act;
+  p.b_up_rows = a->b_up_rows;
+  p.d_up_cols = a->d_up_cols;
+  p.has_d2 = a->D2 != nullptr;
+  p.aux = (const __nv_bfloat16*)a->aux;
+  p.ld_aux = a->ld_aux;
+  p.status = (Status*)a->status;
+  p.a_ready = (const uint32_t*)a->a_ready;
+  p.a_ready_value = a->a_ready_value;
+  p.a_ready_rows = a->a_ready_rows > 0 ? a->a_ready_rows : BM;
+  p.m_rotate = a->m_rotate;
+  p.rank = a->rank; p.world = a->world > 0 ? a->world : 1;
+  const bool ag = a->ag_src != nullptr;
+  if (ag) {
+    if (a->ag_rows_per_rank % p.a_ready_rows || a->ag_ld % 8)
+      return set_error(-5, "gemm: all-gather rows per rank must be a multiple of the flag granularity");
+    p.ag_src = (const __nv_bfloat16*)a->ag_src;
+    for (int r = 0; r < p.world; ++r) {
+      p.ag_dst[r] = (__nv_bfloat16*)a->ag_dst[r];
+      p.ag_flags[r] = (uint32_t*)a->ag_flags[r];
+    }
+    p.ag_rows_per_rank = a->ag_rows_per_rank;
+    p.ag_ld = a->ag_ld;
+  }
+  if (a->epi == EPI_SCATTER) {
+    if (a->rs_rows_per_rank % BM) return set_error(-5, "gemm: reduce-scatter rows per rank must be a multiple of 128");
+    for (int r = 0; r < p.world; ++r) {
+      p.rs_recv[r] = (__nv_bfloat16*)a->rs_recv[r];
+      p.rs_count[r] = (uint32_t*)a->rs_count[r];
+    }
+    p.rs_expect = a->rs_expect;
+    p.rs_out = (__nv_bfloat16*)a->rs_out;
+    p.rs_rows_per_rank = a->rs_rows_per_rank;
+  }
+
+  // ---- tensor maps
+  bool ok = true;
+  if (a->a_mn) ok = ok && make_map_mn(&p.tmA, a->A, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->lda, BM / 64);
+  else         ok = ok && make_map_2d(&p.tmA, a->A, (uint64_t)a->K, (uint64_t)(a->a_rows ? a->a_rows : a->M),
+                                      (uint64_t)a->lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  const uint64_t b_rows = (uint64_t)(a->b_rows ? a->b_rows : a->N);
+  if (a->b_mn) ok = ok && make_map_mn(&p.tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->ldb, BN / 64);
+  else         ok = ok && make_map_2d(&p.tmB, a->B, (uint64_t)a->K, b_rows, (uint64_t)a->ldb, BK,
+                                      a->epi == EPI_GLU_FWD ? BN / 2 : BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (a->epi != EPI_SCATTER) {
+    if (a->ldd % 8 || (uintptr_t)a->D % 16) return set_error(-2, "gemm: D must be 16-byte aligned with ld %% 8 == 0");
+    const uint64_t d_cols = (uint64_t)(a->d_cols ? a->d_cols : a->N);
+    ok = ok && make_map_2d(&p.tmD, a->D, d_cols, (uint64_t)a->M, (uint64_t)a->ldd, EPI_BOX_COLS, 32,
+                           CU_TENSOR_MAP_SWIZZLE_64B);
+    if (a->D2) {
+      const uint64_t d2_cols = (uint64_t)(a->d2_cols ? a->d2_cols : 2 * a->N);
+      ok = ok && make_map_2d(&p.tmD2, a->D2, d2_cols, (uint64_t)a->M, (uint64_t)a->ldd2, EPI_BOX_COLS, 32,
+                             CU_TENSOR_MAP_SWIZZLE_64B);
+    }
+  }
+  if (!ok) return last_error_code();
+
+  int ctas = a->num_ctas > 0 ? a->num_ctas : sm_count();
+  const int tiles = p.m_tiles * p.n_tiles;
+  if (!ag && a->epi != EPI_SCATTER && ctas > tiles) ctas = tiles;
+
+#define MESH_LAUNCH(AM, BMJ, E, G) return launch<AM, BMJ, E, G>(p, ctas, stream)
+  switch (a->epi) {
+    case EPI_STORE:
+      if (ag) {
+        if (!a->a_mn && !a->b_mn) MESH_LAUNCH(0, 0, EPI_STORE, true);
+        return set_error(-6, "gemm: all-gather fusion is built for K-major operands only");
+      }
+      if (!a->a_mn && !a->b_mn) MESH_LAUNCH(0, 0, EPI_STORE, false);
+      if (!a->a_mn && a->b_mn) MESH_LAUNCH(0, 1, EPI_STORE, false);
+      if (a->a_mn && !a->b_mn) MESH_LAUNCH(1, 0, EPI_STORE, false);
+      MESH_LAUNCH(1, 1, EPI_STORE, false);
+    case EPI_GLU_FWD:
+      if (a->a_mn) return set_error(-6, "gemm: GLU forward needs K-major activations");
+      if (ag) MESH_LAUNCH(0, 0, EPI_GLU_FWD, true);
+      MESH_LAUNCH(0, 0, EPI_GLU_FWD, false);
+    case EPI_GLU_BWD:
+      if (a->a_mn) return set_error(-6, "gemm: GLU backward needs K-major dY");
+      if (ag) {
+        if (a->b_mn) MESH_LAUNCH(0, 1, EPI_GLU_BWD, true);
+        MESH_LAUNCH(0, 0, EPI_GLU_BWD, true);
+      }
+      if (a->b_mn) MESH_LAUNCH(0, 1, EPI_GLU_BWD, false);
+      MESH_LAUNCH(0, 0, EPI_GLU_BWD, false);
+    case EPI_SCATTER:
+      if (a->a_mn) return set_error(-6, "gemm: reduce-scatter fusion needs K-major A");
+      if (a->b_mn) MESH_LAUNCH(0, 1, EPI_SCATTER, false);
+      MESH_LAUNCH(0, 0, EPI_SCATTER, false);
+    default:
+      return set_error(-7, "gemm: unknown epilogue %d", a->epi);
+  }
+#undef MESH_LAUNCH
+}

@@ -1,0 +1,542 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a:  D[M,N] = A[M,K] * B[N,K]^T.
+//
+//   warp 0      TMA producer   (cp.async.bulk.tensor into a 4-stage shared-memory ring)
+//   warp 1      MMA issuer     (tcgen05.mma, 128x256x16, accumulators in TMEM, 2 buffers)
+//   warps 2..5  epilogue       (tcgen05.ld -> registers -> fused math -> swizzled smem -> TMA store,
+//                               or direct stores to a peer GPU + arrival flags)
+//
+// Either operand may be K-major (row-major [rows, K]) or MN-major (row-major [K, rows]),
+// which covers forward, dgrad and wgrad of a linear layer without any transposed copy.
+// Fusions that live in this kernel:
+//   * SwiGLU / GeGLU forward  (gate and up weights are two row ranges of one B matrix and
+//     land in the two halves of one accumulator; the epilogue writes act(g)*u and,
+//     optionally, g and u for the backward pass),
+//   * SwiGLU / GeGLU backward (the epilogue of dA = dY*Wd reads g,u and writes dg,du),
+//   * all-gather -> GEMM      (the producer waits on per-row-block arrival flags; tiles
+//     are visited starting from this rank's own rows; spare warps push this rank's rows
+//     into every peer's gathered buffer),
+//   * GEMM -> reduce-scatter  (the epilogue stores each tile to the rank that owns its
+//     rows and raises that rank's arrival counter; a tail phase sums the arrived
+//     partials).
+// This covers the computations K1-K3 of the reference's operation table
+// (compiler/mesh_compiler/operations.py:1191-1272 contraction, :544-588 pointwise) and
+// its partial-sum reduction (compiler/mesh_compiler/placement.py:812-834).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include "../device/ptx.cuh"
+
+namespace mesh {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int EPI_WARPS = 4;
+constexpr int EPI_BOX_COLS = 32;             // bf16 columns per TMA store box (64 B rows)
+constexpr int EPI_BOX_BYTES = 32 * EPI_BOX_COLS * 2;   // 2 KiB
+constexpr int EPI_BUFS = 4;                  // staging boxes per epilogue warp
+constexpr int STAGING_BYTES = EPI_WARPS * EPI_BUFS * EPI_BOX_BYTES;   // 32 KiB
+constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int COMM_WARPS = 4;                // extra warps of the all-gather variant
+constexpr int AG_SPLIT = 8;                  // parts per 128-row block pushed by the comm warps
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+enum Epilogue : int {
+  EPI_STORE = 0,        // D = acc
+  EPI_GLU_FWD = 1,      // D = act(g) * u  (+ optional D2 = [g | u])
+  EPI_GLU_BWD = 2,      // D = [dg | du] from acc = dAct and aux = [g | u]
+  EPI_SCATTER = 3,      // partial tile -> owner rank's receive slot (+ arrival counter)
+};
+enum Activation : int { ACT_SILU = 0, ACT_GELU_TANH = 1 };
+
+constexpr int MAX_RANKS = 8;
+
+struct Params {
+  CUtensorMap tmA, tmB, tmD, tmD2;
+  int M, N, K;
+  int m_tiles, n_tiles, k_blocks;
+  int act;
+  int b_up_rows;            // GLU_FWD: row offset of the "up" weights inside B
+  int d_up_cols;            // GLU_FWD (D2) / GLU_BWD (D and aux): column offset of the "up" half
+  int has_d2;
+  const __nv_bfloat16* aux; // GLU_BWD: [g | u], row-major
+  long long ld_aux;
+  Status* status;
+  // ---- all-gather -> GEMM -------------------------------------------------------------
+  const uint32_t* a_ready;  // one counter per `a_ready_rows` rows of A; tile waits for >= a_ready_value
+  uint32_t a_ready_value;
+  int a_ready_rows;
+  int m_rotate;             // first m-tile visited (own shard first)
+  // push side (run by the comm warps): this rank's rows `ag_src` [ag_rows_per_rank, ag_ld] are
+  // stored into every rank's gathered buffer `ag_dst[d]` at row rank*ag_rows_per_rank, and the
+  // destination's arrival counter `ag_flags[d][block]` is raised once per part.
+  const __nv_bfloat16* ag_src;
+  __nv_bfloat16* ag_dst[MAX_RANKS];
+  uint32_t* ag_flags[MAX_RANKS];
+  int ag_rows_per_rank;
+  long long ag_ld;          // elements per row
+  int rank, world;
+  // ---- GEMM -> reduce-scatter -----------------------------------------------------------
+  __nv_bfloat16* rs_recv[MAX_RANKS];   // rs_recv[o]: rank o's receive buffer [world][rows_per_rank][N]
+  uint32_t* rs_count[MAX_RANKS];       // rs_count[o]: rank o's arrival counters, one per (m-tile of o, n-tile)
+  uint32_t rs_expect;                  // counter value that means "all world partials of this tile arrived"
+  __nv_bfloat16* rs_out;               // this rank's reduced output [rows_per_rank][N]
+  int rs_rows_per_rank;
+};
+
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float act_fwd(float g, int act) {
+  if (act == ACT_SILU) {
+    return g / (1.f + __expf(-g));
+  } else {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    float t = tanhf(k0 * (g + k1 * g * g * g));
+    return 0.5f * g * (1.f + t);
+  }
+}
+// returns act(g) and writes d act / d g
+__device__ __forceinline__ float act_fwd_bwd(float g, int act, float& dact) {
+  if (act == ACT_SILU) {
+    float s = 1.f / (1.f + __expf(-g));
+    dact = s * (1.f + g * (1.f - s));
+    return g * s;
+  } else {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    float inner = k0 * (g + k1 * g * g * g);
+    float t = tanhf(inner);
+    dact = 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
+    return 0.5f * g * (1.f + t);
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack_bf16(uint32_t w) {
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&w);
+  return __bfloat1622float2(v);
+}
+
+// Write 32 fp32 values (one row, 32 columns) as bf16 into a [32 rows][64 B] staging box laid
+// out with the 64-byte TMA swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3).
+__device__ __forceinline__ void stage_row(uint32_t box_smem, int row, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t w0 = pack_bf16(v[8 * j + 0], v[8 * j + 1]);
+    uint32_t w1 = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+    uint32_t w2 = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
+    uint32_t w3 = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+    uint32_t addr = box_smem + row * 64 + ((j ^ ((row >> 1) & 3)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                 : "memory");
+  }
+}
+
+struct TileCoord {
+  int m_idx, n_idx;
+};
+
+// Tiles are walked in groups of 8 m-tiles so that the CTAs running at the same time share
+// A and B tiles in L2.  `m_rotate` shifts the m order (all-gather: own rows first).
+__device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, int n_tiles, int m_rotate) {
+  constexpr int GROUP_M = 8;
+  int per_group = GROUP_M * n_tiles;
+  int group = tile / per_group;
+  int first_m = group * GROUP_M;
+  int group_m = min(GROUP_M, m_tiles - first_m);
+  int in_group = tile - group * per_group;
+  TileCoord c;
+  c.m_idx = first_m + in_group % group_m;
+  c.n_idx = in_group / group_m;
+  c.m_idx += m_rotate;
+  if (c.m_idx >= m_tiles) c.m_idx -= m_tiles;
+  return c;
+}
+
+template <int A_MN, int B_MN, int EPI, bool AG>
+__global__ void __launch_bounds__(NUM_THREADS + (AG ? 32 * COMM_WARPS : 0), 1)
+gemm_kernel(const __grid_constant__ Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sA0 = smem_base;
+  const uint32_t sB0 = smem_base + STAGES * A_STAGE_BYTES;
+  const uint32_t sStage0 = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t bars = sStage0 + STAGING_BYTES;
+  // barrier map (8 B each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then words
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * STAGE_BYTES + STAGING_BYTES + 8 * (2 * STAGES + 4));
+  volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), EPI_WARPS);
+    }
+    *abort_smem = 0;
+    fence_mbar_init();
+    prefetch_tmap(&p.tmA);
+    prefetch_tmap(&p.tmB);
+    if (EPI != EPI_SCATTER) prefetch_tmap(&p.tmD);
+  }
+  if (warp == 0) {
+    tmem_alloc<1>(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    // ===================================================================== TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        TileCoord tc = tile_coord(tile, p.m_tiles, p.n_tiles, p.m_rotate);
+        const int m0 = tc.m_idx * BM;
+        const int n0 = tc.n_idx * (EPI == EPI_GLU_FWD ? BN / 2 : BN);
+        if (p.a_ready != nullptr) {
+          // rows of A that arrive from other GPUs: wait for their arrival counter
+          ok = wait_flag_ge(p.a_ready + m0 / p.a_ready_rows, p.a_ready_value, p.status, SITE_LOCAL_FLAG);
+          if (!ok) { *abort_smem = 1; break; }
+          fence_proxy_async_all();   // data was written through the generic proxy, TMA reads it
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, p.status, SITE_SMEM_EMPTY);
+          if (!ok) break;
+          const uint32_t fb = full_bar(stage);
+          mbar_expect_tx(fb, STAGE_BYTES);
+          const uint32_t sA = sA0 + stage * A_STAGE_BYTES;
+          const uint32_t sB = sB0 + stage * B_STAGE_BYTES;
+          if (A_MN) tma_load_3d(sA, &p.tmA, fb, 0, kb * BK, m0 / 64);
+          else      tma_load_2d(sA, &p.tmA, fb, kb * BK, m0);
+          if (EPI == EPI_GLU_FWD) {
+            tma_load_2d(sB, &p.tmB, fb, kb * BK, n0);
+            tma_load_2d(sB + B_STAGE_BYTES / 2, &p.tmB, fb, kb * BK, p.b_up_rows + n0);
+          } else if (B_MN) {
+            tma_load_3d(sB, &p.tmB, fb, 0, kb * BK, n0 / 64);
+          } else {
+            tma_load_2d(sB, &p.tmB, fb, kb * BK, n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================================================================== MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int t = 0;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
+        const int acc = t & 1;
+        const uint32_t acc_phase = (t >> 1) & 1;
+        ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_smem, p.status, SITE_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          ok = mbar_wait(full_bar(stage), phase, abort_smem, p.status, SITE_SMEM_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sA = sA0 + stage * A_STAGE_BYTES;
+          const uint32_t sB = sB0 + stage * B_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 16 k-elements = 32 B inside the 128 B swizzle row; 8-row groups 1 KiB apart.
+            // MN-major: 16 k-rows = 2 KiB; 64-element MN groups one TMA box (64 rows * 128 B) apart.
+            const uint64_t da = A_MN ? umma_smem_desc(sA + k * 2048, 8192, 1024)
+                                     : umma_smem_desc(sA + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc(sB + k * 2048, 8192, 1024)
+                                     : umma_smem_desc(sB + k * 32, 16, 1024);
+            umma_f16<1>(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));   // stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(tfull_bar(acc));
+      }
+    }
+  } else if (warp < 2 + EPI_WARPS) {
+    // ===================================================================== epilogue
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    const uint32_t my_staging = sStage0 + (warp - 2) * EPI_BUFS * EPI_BOX_BYTES;
+    int buf = 0;
+    bool ok = true;
+    int t = 0;
+    // Claim a staging box: at most EPI_BUFS-1 earlier stores may still be reading smem.
+    auto claim_box = [&]() -> uint32_t {
+      if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
+      __syncwarp();
+      uint32_t b = my_staging + buf * EPI_BOX_BYTES;
+      buf = (buf + 1) & (EPI_BUFS - 1);
+      return b;
+    };
+    auto emit_box = [&](const CUtensorMap* tm, uint32_t box, int col, int row) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(tm, box, col, row);
+        tma_store_commit();
+      }
+    };
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
+      TileCoord tc = tile_coord(tile, p.m_tiles, p.n_tiles, p.m_rotate);
+      const int m0 = tc.m_idx * BM;
+      const int acc = t & 1;
+      const uint32_t acc_phase = (t >> 1) & 1;
+      ok = mbar_wait(tfull_bar(acc), acc_phase, abort_smem, p.status, SITE_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      const int grow = m0 + row_in_tile;
+
+      if constexpr (EPI == EPI_STORE) {
+        const int n0 = tc.n_idx * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (n0 + c * 32 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          uint32_t box = claim_box();
+          stage_row(box, lane, v);
+          emit_box(&p.tmD, box, n0 + c * 32, m0 + q * 32);
+        }
+      } else if constexpr (EPI == EPI_GLU_FWD) {
+        const int n0 = tc.n_idx * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          if (n0 + c * 32 >= p.N) break;
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(taddr + c * 32, rg);
+          tmem_ld_32x32(taddr + BN / 2 + c * 32, ru);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            v[i] = act_fwd(__uint_as_float(rg[i]), p.act) * __uint_as_float(ru[i]);
+          uint32_t box = claim_box();
+          stage_row(box, lane, v);
+          emit_box(&p.tmD, box, n0 + c * 32, m0 + q * 32);
+          if (p.has_d2) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rg[i]);
+            box = claim_box();
+            stage_row(box, lane, v);
+            emit_box(&p.tmD2, box, n0 + c * 32, m0 + q * 32);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ru[i]);
+            box = claim_box();
+            stage_row(box, lane, v);
+            emit_box(&p.tmD2, box, p.d_up_cols + n0 + c * 32, m0 + q * 32);
+          }
+        }
+      } else if constexpr (EPI == EPI_GLU_BWD) {
+        const int n0 = tc.n_idx * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = n0 + c * 32;
+          if (col >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          // g and u of this row/column range, 64 B each (rows past M read nothing)
+          uint4 gq[4], uq[4];
+          const bool in_rows = grow < p.M;
+          const __nv_bfloat16* gptr = p.aux + (long long)grow * p.ld_aux + col;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const bool in = in_rows && (col + 8 * j < p.N);
+            gq[j] = in ? __ldg(reinterpret_cast<const uint4*>(gptr) + j) : make_uint4(0, 0, 0, 0);
+            uq[j] = in ? __ldg(reinterpret_cast<const uint4*>(gptr + p.d_up_cols) + j) : make_uint4(0, 0, 0, 0);
+          }
+          tmem_ld_wait();
+          float dg[32], du[32];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t gw[4] = {gq[j].x, gq[j].y, gq[j].z, gq[j].w};
+            const uint32_t uw[4] = {uq[j].x, uq[j].y, uq[j].z, uq[j].w};
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              float2 g2 = unpack_bf16(gw[h]);
+              float2 u2 = unpack_bf16(uw[h]);
+              const int i = 8 * j + 2 * h;
+              float da0 = __uint_as_float(r[i]), da1 = __uint_as_float(r[i + 1]);
+              float d0, d1;
+              float a0 = act_fwd_bwd(g2.x, p.act, d0);
+              float a1 = act_fwd_bwd(g2.y, p.act, d1);
+              dg[i] = da0 * u2.x * d0;
+              dg[i + 1] = da1 * u2.y * d1;
+              du[i] = da0 * a0;
+              du[i + 1] = da1 * a1;
+            }
+          }
+          uint32_t box = claim_box();
+          stage_row(box, lane, dg);
+          emit_box(&p.tmD, box, col, m0 + q * 32);
+          box = claim_box();
+          stage_row(box, lane, du);
+          emit_box(&p.tmD, box, p.d_up_cols + col, m0 + q * 32);
+        }
+      } else {  // EPI_SCATTER: partial tile goes to the rank that owns these rows
+        const int n0 = tc.n_idx * BN;
+        const int owner = m0 / p.rs_rows_per_rank;
+        const int local_row = grow - owner * p.rs_rows_per_rank;
+        __nv_bfloat16* dst = p.rs_recv[owner] +
+            ((long long)p.rank * p.rs_rows_per_rank + local_row) * (long long)p.N + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (n0 + c * 32 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (grow < p.M) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              w.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              w.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              w.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              if (n0 + c * 32 + 8 * j < p.N) *(reinterpret_cast<uint4*>(dst + c * 32) + j) = w;
+            }
+          }
+        }
+        // publish: every lane's stores, then one arrival per warp on the owner's counter
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int owner_m_tile = (m0 - owner * p.rs_rows_per_rank) / BM;
+          red_release_sys_add(p.rs_count[owner] + owner_m_tile * p.n_tiles + tc.n_idx, 1u);
+        }
+      }
+      // accumulator fully read: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  } else if (AG) {
+    // ===================================================================== all-gather push
+    // The comm warps of all CTAs together store this rank's rows into every rank's gathered
+    // buffer (own copy first, then the rank before this one, and so on, because each
+    // consumer walks its tiles starting from its own rows and continuing with the next
+    // rank's), 128-row blocks split in AG_SPLIT parts, and raise the destination's counter.
+    const int cw = warp - (2 + EPI_WARPS);
+    const int tid = cw * 32 + lane;
+    constexpr int NT = COMM_WARPS * 32;
+    const int blocks_per_rank = p.ag_rows_per_rank / p.a_ready_rows;
+    const long long vec_per_block = (p.ag_ld / 8) * p.a_ready_rows;   // 16-byte vectors
+    const long long per_part = (vec_per_block + AG_SPLIT - 1) / AG_SPLIT;
+    const int units = blocks_per_rank * p.world * AG_SPLIT;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      const int part = unit % AG_SPLIT;
+      const int blk = (unit / AG_SPLIT) % blocks_per_rank;
+      const int step = unit / (AG_SPLIT * blocks_per_rank);           // 0 .. world-1
+      const int dest = (p.rank - step + p.world) % p.world;
+      const long long row0 = (long long)blk * p.a_ready_rows;
+      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src + row0 * p.ag_ld);
+      uint4* dst = reinterpret_cast<uint4*>(
+          p.ag_dst[dest] + ((long long)p.rank * p.ag_rows_per_rank + row0) * p.ag_ld);
+      const long long beg = part * per_part;
+      const long long end = min(vec_per_block, beg + per_part);
+      long long i = beg + tid;
+      for (; i + 3 * NT < end; i += 4 * NT) {
+        uint4 v0 = __ldg(src + i), v1 = __ldg(src + i + NT), v2 = __ldg(src + i + 2 * NT),
+              v3 = __ldg(src + i + 3 * NT);
+        dst[i] = v0; dst[i + NT] = v1; dst[i + 2 * NT] = v2; dst[i + 3 * NT] = v3;
+      }
+      for (; i < end; i += NT) dst[i] = __ldg(src + i);
+      __threadfence_system();
+      // named barrier among the comm warps only (id 1), then one arrival for this part
+      asm volatile("bar.sync 1, %0;" ::"n"(COMM_WARPS * 32) : "memory");
+      if (tid == 0)
+        red_release_sys_add(p.ag_flags[dest] + p.rank * blocks_per_rank + blk, 1u);
+    }
+  }
+
+  // ------------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+
+  if constexpr (EPI == EPI_SCATTER) {
+    // =================================================================== reduce tail
+    // Sum the `world` partial copies of every (m-tile, n-tile) of this rank's rows once
+    // its arrival counter shows that all of them landed.
+    const int my_m_tiles = (p.rs_rows_per_rank + BM - 1) / BM;
+    const int items = my_m_tiles * p.n_tiles;
+    __shared__ int item_ok;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      const int mt = item / p.n_tiles, nt = item % p.n_tiles;
+      if (threadIdx.x == 0) {
+        item_ok = wait_flag_ge(p.rs_count[p.rank] + item, p.rs_expect, p.status, SITE_PEER_FLAG) ? 1 : 0;
+      }
+      __syncthreads();
+      const bool good = item_ok != 0;
+      __syncthreads();
+      if (!good) break;
+      const int rows = min(BM, p.rs_rows_per_rank - mt * BM);
+      const int cols = min(BN, p.N - nt * BN);
+      const int vec_per_row = cols / 8;
+      for (int idx = threadIdx.x; idx < rows * vec_per_row; idx += blockDim.x) {
+        const int r = idx / vec_per_row, v = idx % vec_per_row;
+        const long long off = (long long)(mt * BM + r) * p.N + nt * BN + v * 8;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < p.world; ++s) {
+          const uint4 w = __ldcg(reinterpret_cast<const uint4*>(
+              p.rs_recv[p.rank] + (long long)s * p.rs_rows_per_rank * p.N + off));
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            float2 f = unpack_bf16(ww[h]);
+            acc[2 * h] += f.x;
+            acc[2 * h + 1] += f.y;
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16(acc[0], acc[1]);
+        o.y = pack_bf16(acc[2], acc[3]);
+        o.z = pack_bf16(acc[4], acc[5]);
+        o.w = pack_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(p.rs_out + off) = o;
+      }
+    }
+  }
+}
+
+}  // namespace gemm
+}  // namespace mesh

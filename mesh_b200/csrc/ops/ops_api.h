@@ -1,0 +1,32 @@
+// C ABI of the single-GPU ops (norms, rotary embedding, router, quantised matmul, attention).
+#pragma once
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// y = x * rsqrt(mean(x^2) + eps) * (w + w_offset); if `residual` != NULL, first x += residual (written
+// back to `residual_out` when given).  rstd[rows] (fp32) is written when non-NULL.
+int mesh_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* residual_out,
+                     float* rstd, int rows, int cols, float eps, float w_offset, void* stream);
+// dx from dy, x, w, rstd; dw_partial[blocks][cols] fp32 scratch is reduced into dw (fp32) by a second
+// kernel.  `blocks` rows of scratch are used (<= 1024).
+int mesh_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
+                     float* dw_partial, int blocks, int rows, int cols, float w_offset, void* stream);
+int mesh_rmsnorm_bwd_blocks(int rows);
+
+// Rotate-half rotary embedding, in place, on x[tokens, heads, head_dim] (row stride `ld` elements
+// per token).  cos/sin are fp32 [max_pos, head_dim/2]; positions int32[tokens].  inverse=1 applies
+// the transpose rotation (backward pass).
+int mesh_rope(void* x, const int* positions, const float* cos_t, const float* sin_t, int tokens, int heads,
+              int head_dim, long long ld, int inverse, void* stream);
+
+// softmax over experts then top-k (k <= 8, experts <= 256).  bias (fp32[experts], may be NULL) is added
+// to the logits before the softmax.  weights fp32[tokens,k] (renormalised over the k when renorm),
+// indices int32[tokens,k]; ties go to the lower expert index.
+int mesh_router_topk(const void* logits, int logits_is_fp32, const float* bias, float* weights, int* indices,
+                     int tokens, int experts, int k, int renorm, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

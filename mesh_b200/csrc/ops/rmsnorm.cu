@@ -1,0 +1,211 @@
+// RMSNorm forward (+ fused residual add) and backward for bf16 activations, fp32 math.
+// One CTA per row, 16-byte vector accesses, the row kept in registers between the reduction
+// and the scaling pass so that x is read from HBM once.
+// Reference semantics: the `rms` entry of NORMS, compiler/mesh_compiler/operations.py:6671-6682.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include "ops_api.h"
+#include "../runtime/host_common.h"
+
+namespace mesh {
+namespace {
+
+constexpr int NORM_THREADS = 256;
+constexpr int MAX_VEC_PER_THREAD = 8;   // 8 vectors * 8 elements * 256 threads = 16384 columns
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? sh[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (l == 0) sh[0] = t;
+  }
+  __syncthreads();
+  t = sh[0];
+  __syncthreads();
+  return t;
+}
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 q;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return q;
+}
+
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int rows, int cols,
+                   float eps, float w_offset) {
+  __shared__ float sh[32];
+  const int nvec = cols >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
+    const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * cols) : nullptr;
+    float v[MAX_VEC_PER_THREAD][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        unpack8(xr[c], v[i]);
+        if (rr) {
+          float r8[8];
+          unpack8(rr[c], r8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] += r8[j];
+          if (res_out) {
+            // the sum is rounded to bf16 once and that rounded value is what gets normalised
+            uint4 q = pack8(v[i]);
+            reinterpret_cast<uint4*>(res_out + (size_t)row * cols)[c] = q;
+            unpack8(q, v[i]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      }
+    }
+    ss = block_sum(ss, sh);
+    const float rstd = rsqrtf(ss / (float)cols + eps);
+    if (rstd_out && threadIdx.x == 0) rstd_out[row] = rstd;
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * cols);
+#pragma unroll
+    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        float w8[8], o[8];
+        unpack8(reinterpret_cast<const uint4*>(w)[c], w8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * (w8[j] + w_offset);
+        yr[c] = pack8(o);
+      }
+    }
+  }
+}
+
+// Each CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; writes dx per row and keeps a
+// per-thread running sum of dy*x*rstd for its columns, stored to dw_partial[blockIdx.x][cols].
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int cols,
+                   float w_offset) {
+  __shared__ float sh[32];
+  const int nvec = cols >> 3;
+  float dwacc[MAX_VEC_PER_THREAD][8];
+#pragma unroll
+  for (int i = 0; i < MAX_VEC_PER_THREAD; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * cols);
+    const float r = rstd[row];
+    float xv[MAX_VEC_PER_THREAD][8], gv[MAX_VEC_PER_THREAD][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        float w8[8];
+        unpack8(xr[c], xv[i]);
+        unpack8(gr[c], gv[i]);
+        unpack8(reinterpret_cast<const uint4*>(w)[c], w8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dwacc[i][j] += gv[i][j] * xv[i][j] * r;
+          gv[i][j] *= (w8[j] + w_offset);          // gv now holds w*dy
+          dot += gv[i][j] * xv[i][j];
+        }
+      }
+    }
+    dot = block_sum(dot, sh);
+    const float coef = dot * r * r * r / (float)cols;
+    uint4* dr = reinterpret_cast<uint4*>(dx + (size_t)row * cols);
+#pragma unroll
+    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = gv[i][j] * r - xv[i][j] * coef;
+        dr[c] = pack8(o);
+      }
+    }
+  }
+  if (dw_partial) {
+    float* out = dw_partial + (size_t)blockIdx.x * cols;
+#pragma unroll
+    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) out[c * 8 + j] = dwacc[i][j];
+      }
+    }
+  }
+}
+
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int blocks,
+                                         int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int b = 0; b < blocks; ++b) s += partial[(size_t)b * cols + c];
+  dw[c] = s;
+}
+
+}  // namespace
+}  // namespace mesh
+
+using namespace mesh;
+
+extern "C" int mesh_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* residual_out,
+                                float* rstd, int rows, int cols, float eps, float w_offset, void* stream) {
+  if (rows <= 0) return 0;
+  if (cols % 8 || cols > NORM_THREADS * MAX_VEC_PER_THREAD * 8)
+    return set_error(-2, "rmsnorm: cols must be a multiple of 8 and <= %d", NORM_THREADS * MAX_VEC_PER_THREAD * 8);
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  rmsnorm_fwd_kernel<<<grid, NORM_THREADS, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+      (__nv_bfloat16*)residual_out, rstd, rows, cols, eps, w_offset);
+  MESH_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int mesh_rmsnorm_bwd_blocks(int rows) { return rows < 296 ? rows : 296; }
+
+extern "C" int mesh_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
+                                float* dw_partial, int blocks, int rows, int cols, float w_offset, void* stream) {
+  if (rows <= 0) return 0;
+  if (cols % 8 || cols > NORM_THREADS * MAX_VEC_PER_THREAD * 8)
+    return set_error(-2, "rmsnorm: cols must be a multiple of 8 and <= %d", NORM_THREADS * MAX_VEC_PER_THREAD * 8);
+  if (blocks <= 0 || blocks > 1024) return set_error(-2, "rmsnorm_bwd: blocks out of range");
+  rmsnorm_bwd_kernel<<<blocks, NORM_THREADS, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx,
+      dw_partial, rows, cols, w_offset);
+  MESH_CUDA_OK(cudaGetLastError());
+  if (dw && dw_partial) {
+    rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, (cudaStream_t)stream>>>(dw_partial, dw, blocks, cols);
+    MESH_CUDA_OK(cudaGetLastError());
+  }
+  return 0;
+}

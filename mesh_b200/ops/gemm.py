@@ -1,0 +1,191 @@
+"""bf16 GEMMs on the 5th-generation tensor cores (tcgen05 + TMEM, TMA-fed) and their fused forms.
+
+All matrices are row-major ``torch.bfloat16`` CUDA tensors.  ``gemm(a, b)`` computes
+``a @ b.T`` like ``torch.nn.functional.linear``; the ``*_mn`` flags say that an operand is stored
+transposed (``[K, rows]``), which lets dgrad and wgrad reuse the same kernel with no transposed
+copies.  The GLU helpers fuse the SwiGLU / GeGLU pointwise math into the GEMM epilogues.
+
+Reference semantics: contraction ``compiler/mesh_compiler/operations.py:1191-1272``; SwiGLU FFN of
+``examples/parallel.py:44-51``; GeGLU-tanh of ``examples/engines.py:44``.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native
+from ..utils.status import status_block
+
+EPI_STORE, EPI_GLU_FWD, EPI_GLU_BWD, EPI_SCATTER = 0, 1, 2, 3
+ACT = {"silu": 0, "swiglu": 0, "gelu_tanh": 1, "geglu": 1}
+
+
+def _check2d(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.bfloat16 or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name}: expected a 2-D row-major bf16 CUDA tensor, got {t.dtype} {tuple(t.shape)} {t.stride()}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _launch(args: _native.GemmArgs) -> None:
+    rc = _native.lib().mesh_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_stream()))
+    _native.check(rc, "mesh_gemm_bf16")
+
+
+def _base_args(a: torch.Tensor, b: torch.Tensor, a_mn: bool, b_mn: bool) -> tuple[_native.GemmArgs, int, int, int]:
+    _check2d(a, "a")
+    _check2d(b, "b")
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"contraction sizes differ: {K} vs {Kb}")
+    g = _native.GemmArgs()
+    g.A, g.B = a.data_ptr(), b.data_ptr()
+    g.M, g.N, g.K = M, N, K
+    g.lda, g.ldb = a.stride(0), b.stride(0)
+    g.a_mn, g.b_mn = int(a_mn), int(b_mn)
+    g.a_rows = 0 if a_mn else a.shape[0]
+    g.b_rows = 0 if b_mn else b.shape[0]
+    g.status = status_block(a.device).data_ptr()
+    g.world = 1
+    return g, M, N, K
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, num_ctas: int = 0) -> torch.Tensor:
+    """``out[M,N] = A[M,K] @ B[N,K]^T`` with fp32 accumulation.
+
+    ``a_mn``: ``a`` is stored ``[K, M]``;  ``b_mn``: ``b`` is stored ``[K, N]``.
+    """
+    g, M, N, K = _base_args(a, b, a_mn, b_mn)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    _check2d(out, "out")
+    g.D, g.ldd, g.d_cols = out.data_ptr(), out.stride(0), out.shape[1]
+    g.epi = EPI_STORE
+    g.num_ctas = num_ctas
+    _launch(g)
+    return out
+
+
+def glu_fwd(x: torch.Tensor, w_gate_up: torch.Tensor, *, act: str = "silu", save_gu: bool = True,
+            out: torch.Tensor | None = None, gu: torch.Tensor | None = None):
+    """``act(x @ Wg^T) * (x @ Wu^T)`` where ``w_gate_up = [Wg; Wu]`` is ``[2F, K]``.
+
+    Returns ``(h[M,F], gu[M,2F] or None)``; ``gu = [g | u]`` is what the backward pass needs.
+    """
+    _check2d(x, "x")
+    _check2d(w_gate_up, "w_gate_up")
+    F2, K = w_gate_up.shape
+    F = F2 // 2
+    M = x.shape[0]
+    g = _native.GemmArgs()
+    g.A, g.B = x.data_ptr(), w_gate_up.data_ptr()
+    g.M, g.N, g.K = M, F, K
+    g.lda, g.ldb = x.stride(0), w_gate_up.stride(0)
+    g.a_rows, g.b_rows = M, F2
+    g.b_up_rows = F
+    g.epi, g.act = EPI_GLU_FWD, ACT[act]
+    if out is None:
+        out = torch.empty((M, F), dtype=torch.bfloat16, device=x.device)
+    g.D, g.ldd, g.d_cols = out.data_ptr(), out.stride(0), F
+    if save_gu:
+        if gu is None:
+            gu = torch.empty((M, F2), dtype=torch.bfloat16, device=x.device)
+        g.D2, g.ldd2, g.d2_cols, g.d_up_cols = gu.data_ptr(), gu.stride(0), F2, F
+    else:
+        gu = None
+    g.status = status_block(x.device).data_ptr()
+    g.world = 1
+    _launch(g)
+    return out, gu
+
+
+def glu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor, *, act: str = "silu",
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """Backward of the GLU through the down projection in one kernel.
+
+    ``dH = dy @ w_down`` (``w_down`` is ``[D, F]``, used MN-major) and the epilogue turns it into
+    ``[dg | du]`` (``[M, 2F]``) using the saved ``gu = [g | u]``.
+    """
+    _check2d(dy, "dy")
+    _check2d(w_down, "w_down")
+    _check2d(gu, "gu")
+    M, D = dy.shape
+    D2, F = w_down.shape
+    if D2 != D or gu.shape != (M, 2 * F):
+        raise ValueError("glu_bwd: shape mismatch")
+    g = _native.GemmArgs()
+    g.A, g.B = dy.data_ptr(), w_down.data_ptr()
+    g.M, g.N, g.K = M, F, D
+    g.lda, g.ldb = dy.stride(0), w_down.stride(0)
+    g.a_rows = M
+    g.b_mn = 1
+    g.epi, g.act = EPI_GLU_BWD, ACT[act]
+    g.aux, g.ld_aux = gu.data_ptr(), gu.stride(0)
+    g.d_up_cols = F
+    if out is None:
+        out = torch.empty((M, 2 * F), dtype=torch.bfloat16, device=dy.device)
+    g.D, g.ldd, g.d_cols = out.data_ptr(), out.stride(0), 2 * F
+    g.status = status_block(dy.device).data_ptr()
+    g.world = 1
+    _launch(g)
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """``y = x @ w^T`` with dgrad/wgrad on the same tcgen05 kernel (no transposes materialised)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w)
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).reshape(x.shape)          # [M,N] x [N,K] stored [K=N, cols=K]
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True)               # dy^T x : [N, K]
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return _Linear.apply(x, w)
+
+
+class _GluFFN(torch.autograd.Function):
+    """Whole gated FFN ``(act(x Wg^T) * (x Wu^T)) Wd^T`` in 2 forward and 4 backward kernels."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate_up, w_down, act):
+        x2 = x.reshape(-1, x.shape[-1])
+        h, gu = glu_fwd(x2, w_gate_up, act=act, save_gu=True)
+        y = gemm(h, w_down)
+        ctx.save_for_backward(x2, w_gate_up, w_down, h, gu)
+        ctx.act = act
+        ctx.xshape = x.shape
+        return y.reshape(*x.shape[:-1], w_down.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_gate_up, w_down, h, gu = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dgu = glu_bwd(dy2, w_down, gu, act=ctx.act)                 # [M, 2F]
+        dw_down = gemm(dy2, h, a_mn=True, b_mn=True)                # [D, F]
+        dx = gemm(dgu, w_gate_up, b_mn=True).reshape(ctx.xshape)    # [M, D]
+        dw_gate_up = gemm(dgu, x2, a_mn=True, b_mn=True)            # [2F, D]
+        return dx, dw_gate_up, dw_down, None
+
+
+def glu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    return _GluFFN.apply(x, w_gate_up, w_down, act)

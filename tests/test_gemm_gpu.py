@@ -1,0 +1,97 @@
+"""tcgen05 GEMM and its fused epilogues against a plain PyTorch fp32 statement of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * scale).to(torch.bfloat16)
+
+
+def _close(got, want, tol=2e-2):
+    got = got.float()
+    want = want.float()
+    err = (got - want).abs().max().item()
+    ref = want.abs().max().item() + 1e-6
+    assert err / ref < tol, f"max err {err} vs max ref {ref}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 512), (200, 264, 328), (4096, 1024, 1024)])
+def test_gemm_kmajor(M, N, K):
+    from mesh_b200.ops.gemm import gemm
+    from mesh_b200.utils.status import check_status
+    a, b = _rand((M, K), seed=1), _rand((N, K), seed=2)
+    out = gemm(a, b)
+    check_status()
+    _close(out, a.float() @ b.float().T)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 320), (448, 832, 1000)])
+def test_gemm_mn_major(a_mn, b_mn, M, N, K):
+    from mesh_b200.ops.gemm import gemm
+    from mesh_b200.utils.status import check_status
+    a = _rand((K, M) if a_mn else (M, K), seed=3)
+    b = _rand((K, N) if b_mn else (N, K), seed=4)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    check_status()
+    af = a.float().T if a_mn else a.float()
+    bf = b.float().T if b_mn else b.float()
+    _close(out, af @ bf.T)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+@pytest.mark.parametrize("M,F,K", [(128, 128, 64), (256, 384, 256), (300, 608, 512)])
+def test_glu_fwd(act, M, F, K):
+    from mesh_b200.ops.gemm import glu_fwd
+    from mesh_b200.utils.status import check_status
+    x, w = _rand((M, K), seed=5), _rand((2 * F, K), 0.05, seed=6)
+    h, gu = glu_fwd(x, w, act=act)
+    check_status()
+    g = x.float() @ w[:F].float().T
+    u = x.float() @ w[F:].float().T
+    a = torch.nn.functional.silu(g) if act == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
+    _close(gu[:, :F], g)
+    _close(gu[:, F:], u)
+    _close(h, a * u)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+@pytest.mark.parametrize("M,F,D", [(128, 256, 64), (256, 512, 256), (300, 576, 384)])
+def test_glu_bwd(act, M, F, D):
+    from mesh_b200.ops.gemm import glu_bwd
+    from mesh_b200.utils.status import check_status
+    dy, wd, gu = _rand((M, D), seed=7), _rand((D, F), 0.05, seed=8), _rand((M, 2 * F), seed=9)
+    out = glu_bwd(dy, wd, gu, act=act)
+    check_status()
+    g = gu[:, :F].float().requires_grad_(True)
+    u = gu[:, F:].float().requires_grad_(True)
+    a = torch.nn.functional.silu(g) if act == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
+    dh = dy.float() @ wd.float()
+    (a * u).backward(dh)
+    _close(out[:, :F], g.grad)
+    _close(out[:, F:], u.grad)
+
+
+def test_glu_ffn_autograd():
+    from mesh_b200.ops.gemm import glu_ffn
+    from mesh_b200.utils.status import check_status
+    M, D, F = 512, 256, 640
+    x = _rand((M, D), seed=10).requires_grad_(True)
+    wgu = _rand((2 * F, D), 0.05, seed=11).requires_grad_(True)
+    wd = _rand((D, F), 0.05, seed=12).requires_grad_(True)
+    y = glu_ffn(x, wgu, wd)
+    dy = _rand((M, D), seed=13)
+    y.backward(dy)
+    check_status()
+    xr, wgur, wdr = (t.detach().float().requires_grad_(True) for t in (x, wgu, wd))
+    g = xr @ wgur[:F].T
+    u = xr @ wgur[F:].T
+    yr = (torch.nn.functional.silu(g) * u) @ wdr.T
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad, 3e-2)
+    _close(wgu.grad, wgur.grad, 3e-2)
+    _close(wd.grad, wdr.grad, 3e-2)

@@ -1,0 +1,58 @@
+"""RMSNorm, RoPE and router top-k kernels against fp32 PyTorch statements."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 2048), (7, 1536), (300, 4096), (64, 8192)])
+def test_rmsnorm_fwd(rows, cols):
+    from mesh_b200.ops.norm import rmsnorm_fwd, rmsnorm_ref
+    x = torch.randn(rows, cols, device="cuda").bfloat16()
+    w = (torch.randn(cols, device="cuda") * 0.1 + 1).bfloat16()
+    y, _, _ = rmsnorm_fwd(x, w, 1e-6)
+    torch.testing.assert_close(y.float(), rmsnorm_ref(x, w).float(), atol=2e-2, rtol=2e-2)
+    r = torch.randn(rows, cols, device="cuda").bfloat16()
+    y2, res, _ = rmsnorm_fwd(x, w, 1e-6, residual=r, weight_offset=1.0)
+    s = (x.float() + r.float()).bfloat16()
+    torch.testing.assert_close(res.float(), s.float(), atol=1e-2, rtol=1e-2)
+    torch.testing.assert_close(y2.float(), rmsnorm_ref(s, w, weight_offset=1.0).float(), atol=3e-2, rtol=3e-2)
+
+
+def test_rmsnorm_bwd():
+    from mesh_b200.ops.norm import rmsnorm
+    x = torch.randn(500, 2048, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(2048, device="cuda") * 0.1 + 1).bfloat16().requires_grad_(True)
+    dy = torch.randn(500, 2048, device="cuda").bfloat16()
+    rmsnorm(x, w).backward(dy)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    yr.backward(dy.float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, atol=0.5, rtol=3e-2)
+
+
+@pytest.mark.parametrize("heads,hd", [(8, 256), (16, 128), (2, 64)])
+def test_rope(heads, hd):
+    from mesh_b200.ops.rope import rope_, rope_ref, rope_tables
+    T = 77
+    cos, sin = rope_tables(1024, hd, theta=1e6)
+    pos = torch.randint(0, 1024, (T,), device="cuda", dtype=torch.int32)
+    x = torch.randn(T, heads, hd, device="cuda").bfloat16()
+    want = rope_ref(x, pos, cos, sin)
+    got = rope_(x.clone(), pos, cos, sin)
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    back = rope_(got.clone(), pos, cos, sin, inverse=True)
+    torch.testing.assert_close(back.float(), x.float(), atol=4e-2, rtol=4e-2)
+
+
+@pytest.mark.parametrize("E,k", [(64, 6), (8, 2), (256, 8), (40, 3)])
+def test_router_topk(E, k):
+    from mesh_b200.ops.router import router_topk, router_topk_ref
+    T = 1000
+    logits = torch.randn(T, E, device="cuda")
+    bias = torch.randn(E, device="cuda")
+    w, i = router_topk(logits, k, bias)
+    wr, ir = router_topk_ref(logits, k, bias)
+    assert torch.equal(i, ir)
+    torch.testing.assert_close(w, wr, atol=1e-5, rtol=1e-4)
