@@ -1,0 +1,193 @@
+"""Sequence-parallel tensor-parallel gated FFN on fused compute+collective kernels.
+
+Megatron-style split (reference placement ``megatron()``, examples/parallel.py:77-89): gate/up
+weights column-parallel, down weight row-parallel, activations sharded along the token
+dimension between layers.  The reference's compiler would emit an all-gather before the column
+GEMM and a reduce(-scatter) after the row GEMM (compiler/mesh_compiler/placement.py:250-340,
+:812-834); here each pair is ONE kernel:
+
+  forward   1. push x shard to every rank's gathered buffer  +  [g|u] = X Wgu^T, h = act(g)*u
+            2. partial y = h Wd^T, tiles stored to the owner rank  +  owner sums the partials
+  backward  3. push dy shard  +  dH = dY Wd with the GLU backward in the epilogue -> [dg|du]
+            4. dWd  = dY^T h
+            5. partial dx = [dg|du] Wgu, scattered + reduced like (2)
+            6. dWgu = [dg|du]^T X
+
+Buffers that peers write into are double-buffered by use parity; their arrival counters only ever
+increase, so no barrier or reset is needed between steps (same idea as the reference's
+``copies`` buffers and monotonic words, rdma/mesh-flow.c:7-15).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native
+from ..ops import gemm as G
+from ..runtime.heap import SymmetricHeap
+from ..utils.status import status_block
+
+BM, BN = 128, 256
+AG_SPLIT = 8
+EPI_WARPS = 4
+
+
+class _Gathered:
+    """A double-buffered all-gather landing zone [M, D] with per-128-row arrival counters."""
+
+    def __init__(self, heap: SymmetricHeap, M: int, D: int):
+        self.buf = [heap.alloc((M, D), torch.bfloat16) for _ in range(2)]
+        self.flags = [heap.alloc_signals(M // BM) for _ in range(2)]
+        self.uses = [0, 0]
+        self.turn = 0
+
+    def next(self):
+        par = self.turn & 1
+        self.turn += 1
+        self.uses[par] += 1
+        return self.buf[par], self.flags[par], AG_SPLIT * self.uses[par]
+
+
+class _Scattered:
+    """A double-buffered reduce-scatter landing zone [world, M/world, N] with per-tile counters."""
+
+    def __init__(self, heap: SymmetricHeap, world: int, rows: int, N: int):
+        self.world = world
+        self.buf = [heap.alloc((world, rows, N), torch.bfloat16) for _ in range(2)]
+        self.count = [heap.alloc_signals((rows // BM) * ((N + BN - 1) // BN)) for _ in range(2)]
+        self.uses = [0, 0]
+        self.turn = 0
+
+    def next(self):
+        par = self.turn & 1
+        self.turn += 1
+        self.uses[par] += 1
+        return self.buf[par], self.count[par], self.world * EPI_WARPS * self.uses[par]
+
+
+class FusedTPFFN:
+    """Holds the symmetric workspaces of one (M, D, F) FFN shape and runs its six fused kernels.
+
+    ``w_gate_up``: this rank's ``[2*F/world, D]`` (gate rows, then up rows); ``w_down``: ``[D, F/world]``.
+    """
+
+    def __init__(self, heap: SymmetricHeap, tokens: int, d_model: int, d_ff: int, act: str = "silu"):
+        self.heap = heap
+        self.rank, self.world = heap.rank, heap.world
+        self.M, self.D, self.F = tokens, d_model, d_ff
+        self.act = act
+        P = self.world
+        if tokens % (P * BM):
+            raise ValueError(f"tokens ({tokens}) must be a multiple of world*128")
+        if d_ff % P or (d_ff // P) % 64 or d_model % 64:
+            raise ValueError("d_ff/world and d_model must be multiples of 64")
+        self.rows = tokens // P
+        self.Fl = d_ff // P
+        self.x_full = _Gathered(heap, tokens, d_model)
+        self.dy_full = _Gathered(heap, tokens, d_model)
+        self.y_recv = _Scattered(heap, P, self.rows, d_model)
+        self.dx_recv = _Scattered(heap, P, self.rows, d_model)
+        self._saved = None
+
+    # ---------------------------------------------------------------- kernels
+    def _args(self, dev) -> _native.GemmArgs:
+        g = _native.GemmArgs()
+        g.status = status_block(dev).data_ptr()
+        g.rank, g.world = self.rank, self.world
+        return g
+
+    def _gather_args(self, g, zone: _Gathered, src: torch.Tensor):
+        buf, flags, expect = zone.next()
+        g.A, g.lda, g.a_rows = buf.ptr(), self.D, self.M
+        g.a_ready, g.a_ready_value, g.a_ready_rows = flags.ptr(), expect, BM
+        g.m_rotate = self.rank * (self.rows // BM)
+        g.ag_src, g.ag_rows_per_rank, g.ag_ld = src.data_ptr(), self.rows, self.D
+        for r in range(self.world):
+            g.ag_dst[r] = buf.ptr(r)
+            g.ag_flags[r] = flags.ptr(r)
+        return buf
+
+    def _scatter_args(self, g, zone: _Scattered, out: torch.Tensor):
+        buf, count, expect = zone.next()
+        g.epi = G.EPI_SCATTER
+        for r in range(self.world):
+            g.rs_recv[r] = buf.ptr(r)
+            g.rs_count[r] = count.ptr(r)
+        g.rs_expect, g.rs_out, g.rs_rows_per_rank = expect, out.data_ptr(), self.rows
+        g.m_rotate = ((self.rank + 1) % self.world) * (self.rows // BM)   # own rows last
+
+    def forward(self, x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, save: bool = True):
+        """x: this rank's ``[M/world, D]`` token shard -> y shard ``[M/world, D]``."""
+        dev = x.device
+        M, D, Fl = self.M, self.D, self.Fl
+        h = torch.empty((M, Fl), dtype=torch.bfloat16, device=dev)
+        gu = torch.empty((M, 2 * Fl), dtype=torch.bfloat16, device=dev) if save else None
+        # (1) all-gather(x) -> GLU GEMM
+        g = self._args(dev)
+        xbuf = self._gather_args(g, self.x_full, x)
+        g.B, g.ldb, g.b_rows, g.b_up_rows = w_gate_up.data_ptr(), w_gate_up.stride(0), 2 * Fl, Fl
+        g.M, g.N, g.K = M, Fl, D
+        g.epi, g.act = G.EPI_GLU_FWD, G.ACT[self.act]
+        g.D, g.ldd, g.d_cols = h.data_ptr(), Fl, Fl
+        if save:
+            g.D2, g.ldd2, g.d2_cols, g.d_up_cols = gu.data_ptr(), 2 * Fl, 2 * Fl, Fl
+        G._launch(g)
+        # (2) down GEMM -> reduce-scatter
+        y = torch.empty((self.rows, D), dtype=torch.bfloat16, device=dev)
+        g = self._args(dev)
+        g.A, g.lda, g.a_rows = h.data_ptr(), Fl, M
+        g.B, g.ldb, g.b_rows = w_down.data_ptr(), w_down.stride(0), D
+        g.M, g.N, g.K = M, D, Fl
+        self._scatter_args(g, self.y_recv, y)
+        G._launch(g)
+        if save:
+            self._saved = (xbuf, h, gu, w_gate_up, w_down)
+        return y
+
+    def backward(self, dy: torch.Tensor):
+        """dy: ``[M/world, D]`` -> ``(dx shard, dW_gate_up, dW_down)``."""
+        xbuf, h, gu, w_gate_up, w_down = self._saved
+        dev = dy.device
+        M, D, Fl = self.M, self.D, self.Fl
+        dy = dy.contiguous()
+        # (3) all-gather(dy) -> dH GEMM with GLU backward epilogue
+        dgu = torch.empty((M, 2 * Fl), dtype=torch.bfloat16, device=dev)
+        g = self._args(dev)
+        dybuf = self._gather_args(g, self.dy_full, dy)
+        g.B, g.ldb, g.b_mn = w_down.data_ptr(), w_down.stride(0), 1
+        g.M, g.N, g.K = M, Fl, D
+        g.epi, g.act = G.EPI_GLU_BWD, G.ACT[self.act]
+        g.aux, g.ld_aux, g.d_up_cols = gu.data_ptr(), 2 * Fl, Fl
+        g.D, g.ldd, g.d_cols = dgu.data_ptr(), 2 * Fl, 2 * Fl
+        G._launch(g)
+        # (4) dWd = dY^T h   (dY is complete in this rank's gathered buffer once (3) has finished)
+        dw_down = G.gemm(dybuf.local, h, a_mn=True, b_mn=True)
+        # (5) dx partial = [dg|du] Wgu -> reduce-scatter
+        dx = torch.empty((self.rows, D), dtype=torch.bfloat16, device=dev)
+        g = self._args(dev)
+        g.A, g.lda, g.a_rows = dgu.data_ptr(), 2 * Fl, M
+        g.B, g.ldb, g.b_mn = w_gate_up.data_ptr(), w_gate_up.stride(0), 1
+        g.M, g.N, g.K = M, D, 2 * Fl
+        self._scatter_args(g, self.dx_recv, dx)
+        G._launch(g)
+        # (6) dWgu = [dg|du]^T X
+        dw_gate_up = G.gemm(dgu, xbuf.local, a_mn=True, b_mn=True)
+        return dx, dw_gate_up, dw_down
+
+
+class _FusedTPFFNFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_gate_up, w_down, op: FusedTPFFN):
+        ctx.op = op
+        return op.forward(x, w_gate_up, w_down, save=True)
+
+    @staticmethod
+    def backward(ctx, dy):
+        dx, dwgu, dwd = ctx.op.backward(dy)
+        return dx, dwgu, dwd, None
+
+
+def fused_tp_ffn(x, w_gate_up, w_down, op: FusedTPFFN):
+    """Autograd entry point; ``op`` owns the symmetric workspaces."""
+    return _FusedTPFFNFn.apply(x, w_gate_up, w_down, op)

@@ -1,0 +1,58 @@
+"""Spawn helpers: run ``fn(rank, world, rendezvous, *args)`` in ``world`` child processes.
+
+Used by the multi-GPU tests and examples; the CPU tests use the same helper with gloo ranks, which
+is this package's "fake cluster" (the reference has none and only runs on its live pair).
+"""
+from __future__ import annotations
+
+import os
+import socket
+import traceback
+from datetime import timedelta
+
+
+def free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _child(rank: int, world: int, port: int, fn, args, use_cuda: bool, init_pg: str | None):
+    import torch
+    import torch.distributed as dist
+    from ..runtime.rendezvous import Rendezvous
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    if use_cuda:
+        torch.cuda.set_device(rank)
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=120),
+                          wait_for_workers=False)
+    if init_pg:
+        dist.init_process_group(init_pg, store=dist.PrefixStore("pg", store), rank=rank, world_size=world,
+                                timeout=timedelta(seconds=120))
+    rdv = Rendezvous(dist.PrefixStore("rdv", store), rank, world, timeout_s=120.0)
+    try:
+        fn(rank, world, rdv, *args)
+        rdv.barrier("spawn-exit")
+    except BaseException:
+        traceback.print_exc()
+        raise
+    finally:
+        if init_pg and dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def spawn_ranks(fn, world: int, *args, use_cuda: bool = False, init_pg: str | None = None, timeout: float = 600.0):
+    """Run ``fn`` on ``world`` ranks and raise if any child fails.  ``fn`` must be importable."""
+    import torch.multiprocessing as mp
+    port = free_port()
+    ctx = mp.start_processes(_child, args=(world, port, fn, args, use_cuda, init_pg), nprocs=world, join=False,
+                             start_method="spawn")
+    import time
+    deadline = time.monotonic() + timeout
+    while not ctx.join(timeout=1.0):
+        if time.monotonic() > deadline:
+            for p in ctx.processes:
+                if p.is_alive():
+                    p.terminate()
+            raise TimeoutError(f"spawn_ranks: children did not finish within {timeout}s")
