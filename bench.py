@@ -1,0 +1,256 @@
+#!/usr/bin/env python
+"""Headline benchmark: tensor-parallel SwiGLU FFN period (forward + backward), bf16,
+x[4096 tokens, d_model 4096], d_ff 14336, sequence-parallel, at TP = number of GPUs; plus the
+E2B-class decode tokens/s as a secondary record.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
+
+``--impl mesh`` (default) runs this package's fused kernels; ``--impl baseline`` runs the stock
+NCCL + cuBLAS restatement in ``baseline/``; ``--impl reference`` reports why the reference itself
+cannot run on this hardware.  Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+TOKENS, D_MODEL, D_FF = 4096, 4096, 14336
+REFERENCE_UNAVAILABLE = ("reference is not installable: /root/reference has no setup.py/pyproject.toml (pip: 'Neither "
+                         "setup.py nor pyproject.toml found'), and its code needs macOS Metal/CoreML, Apple RDMA verbs "
+                         "and external metal-microbench libraries")
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="mesh", choices=["mesh", "baseline", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the secondary E2B-class decode record")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import mesh_b200
+    from mesh_b200 import _native
+    from mesh_b200.distributed import init, shutdown
+
+    ctx = init(backend="nccl")
+    rank, world, dev = ctx.rank, ctx.world, ctx.device
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    rows = TOKENS // world
+    Fl = D_FF // world
+
+    # ---- synthetic data of the named shape, random-init weights (same seed on every rank)
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    x_host = torch.randn(TOKENS, D_MODEL, generator=g).bfloat16()[rank * rows:(rank + 1) * rows].contiguous().pin_memory()
+    dy = torch.randn(TOKENS, D_MODEL, generator=g).bfloat16()[rank * rows:(rank + 1) * rows].to(dev)
+    x_dev = x_host.to(dev).requires_grad_(True)
+
+    if args.impl == "mesh":
+        from mesh_b200.parallel.layers import TPGatedFFN
+        layer = TPGatedFFN(D_MODEL, D_FF, ctx, act="silu", sequence_parallel=True, seed=7)
+        params = list(layer.parameters())
+
+        def step(x):
+            return layer(x)
+    else:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__))))
+        from baseline.tp_ffn import tp_ffn
+        gw = torch.Generator(device="cpu").manual_seed(7)
+        sl = slice(rank * Fl, (rank + 1) * Fl)
+        wg = torch.empty(D_FF, D_MODEL).normal_(0, 0.02, generator=gw)[sl].to(dev, torch.bfloat16).requires_grad_(True)
+        wu = torch.empty(D_FF, D_MODEL).normal_(0, 0.02, generator=gw)[sl].to(dev, torch.bfloat16).requires_grad_(True)
+        wd = torch.empty(D_MODEL, D_FF).normal_(0, 0.02, generator=gw)[:, sl].contiguous().to(dev, torch.bfloat16).requires_grad_(True)
+        params = [wg, wu, wd]
+        grp = ctx.group if world > 1 else None
+
+        def step(x):
+            return tp_ffn(x, wg, wu, wd, grp)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
+
+    def zero_grads():
+        for p in params:
+            p.grad = None
+        x_dev.grad = None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run_device_step():
+        y = step(x_dev)
+        y.backward(dy)
+
+    def run_e2e_step():
+        x = x_host.to(dev, non_blocking=True).requires_grad_(True)        # H2D from pinned memory, every step
+        y = step(x)
+        loss = (y.float() * dy.float()).sum()
+        loss.backward()
+        return float(loss.item())                                         # D2H read of the step's result
+
+    # ---- device-timed region: K steps, L2 flushed (untimed) between them
+    for _ in range(args.warmup):
+        zero_grads(); run_device_step()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(dev.index))
+    sampler.start()
+    launches0 = _native.launch_count
+    evs = []
+    barrier()
+    t_wall0 = time.perf_counter()
+    for _ in range(args.steps):
+        zero_grads()
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); run_device_step(); e1.record()
+        evs.append((e0, e1))
+    barrier()
+    t_wall1 = time.perf_counter()
+    launches = _native.launch_count - launches0
+    dev_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+
+    # ---- end-to-end through the public API: H2D of the step's input + D2H of its result, every step
+    for _ in range(args.warmup):
+        zero_grads(); run_e2e_step()
+    barrier()
+    e2e_evs = []
+    for _ in range(args.steps):
+        zero_grads()
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); loss_val = run_e2e_step(); e1.record()
+        e2e_evs.append((e0, e1))
+    barrier()
+    e2e_ms = sum(a.elapsed_time(b) for a, b in e2e_evs) / args.steps
+    clocks = sampler.stop()
+
+    # ---- max over ranks
+    t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(t[0]), float(t[1])
+
+    if args.impl == "mesh":
+        from mesh_b200.utils.status import check_status
+        check_status()
+
+    decode = None
+    if not args.no_decode and args.impl == "mesh":
+        try:
+            from mesh_b200.models.e2b import bench_decode
+            decode = bench_decode(ctx)
+        except ImportError:
+            decode = None
+        except Exception as e:  # the FFN record must survive a decode failure
+            decode = {"error": f"{type(e).__name__}: {e}"[:300]}
+
+    if rank == 0:
+        flops = 3 * (2 * TOKENS * D_MODEL * 2 * D_FF + 2 * TOKENS * D_FF * D_MODEL)
+        from mesh_b200.config import capacity
+        peak = capacity().get("bf16_tflops_sustained", 1382.0)
+        line = {
+            "metric": "tp_ffn_period_us", "value": round(dev_ms * 1e3, 2), "unit": "us per layer (fwd+bwd)",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms, 5),
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (N(0,1) activations, N(0,0.02) random-init weights)", "impl": args.impl,
+            "config": {"model": "sequence-parallel SwiGLU FFN, x[4096,4096], d_ff 14336", "global_batch": TOKENS,
+                       "seq_len": TOKENS, "parallelism": f"tp{world}+sp", "l2": "256 MiB flush write between steps (untimed)",
+                       "timing": "CUDA events per step, summed over K steps, max over ranks"},
+            "tflops_per_gpu": round(flops / world / (dev_ms * 1e-3) / 1e12, 1),
+            "frac_of_measured_sustained_bf16_peak": round(flops / world / (dev_ms * 1e-3) / 1e12 / peak, 3),
+            "wall_ms_per_step_incl_flush": round((t_wall1 - t_wall0) * 1e3 / args.steps, 4),
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_ms * 1e3, 2), "unit": "us per layer (fwd+bwd) incl. H2D input + D2H loss",
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches if args.impl == "mesh" else 0,
+        }
+        if decode is not None:
+            line["decode"] = decode
+        print(json.dumps(line), flush=True)
+    shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

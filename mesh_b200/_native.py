@@ -12,6 +12,12 @@ from ctypes import c_int, c_longlong, c_uint32, c_void_p
 
 _lock = threading.Lock()
 _lib = None
+launch_count = 0   # kernels of this library launched by this process (bench accounting)
+
+
+def count_launch(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
 
 MAX_RANKS = 8
 

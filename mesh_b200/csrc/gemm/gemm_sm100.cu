@@ -98,13 +98,22 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
     }
     p.ag_rows_per_rank = a->ag_rows_per_rank;
     p.ag_ld = a->ag_ld;
+    if ((uintptr_t)a->ag_src % 16) return set_error(-2, "gemm: all-gather source must be 16-byte aligned");
+    if (!make_map_2d(&p.tmA2, a->ag_src, (uint64_t)a->K, (uint64_t)a->ag_rows_per_rank, (uint64_t)a->ag_ld, BK, BM,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return last_error_code();
   }
   if (a->epi == EPI_SCATTER) {
     if (a->rs_rows_per_rank % BM) return set_error(-5, "gemm: reduce-scatter rows per rank must be a multiple of 128");
+    // every rank's receive buffer viewed as a [rows, 64] matrix: one box = one contiguous 4 KiB run
+    const uint64_t n_tiles_rs = (uint64_t)((a->N + BN - 1) / BN);
+    const uint64_t view_rows = (uint64_t)p.world * (a->rs_rows_per_rank / BM) * n_tiles_rs * (BN / 64) * BM;
     for (int r = 0; r < p.world; ++r) {
-      p.rs_recv[r] = (__nv_bfloat16*)a->rs_recv[r];
       p.rs_count[r] = (uint32_t*)a->rs_count[r];
+      if (!make_map_2d(&p.tmRS[r], a->rs_recv[r], 64, view_rows, 64, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+        return last_error_code();
     }
+    p.rs_recv = (const __nv_bfloat16*)a->rs_recv[p.rank];
     p.rs_expect = a->rs_expect;
     p.rs_out = (__nv_bfloat16*)a->rs_out;
     p.rs_rows_per_rank = a->rs_rows_per_rank;

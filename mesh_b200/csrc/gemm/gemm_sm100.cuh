@@ -61,6 +61,8 @@ constexpr int MAX_RANKS = 8;
 
 struct Params {
   CUtensorMap tmA, tmB, tmD, tmD2;
+  CUtensorMap tmA2;                    // all-gather: this rank's own rows, read straight from the source
+  CUtensorMap tmRS[MAX_RANKS];         // reduce-scatter: rank o's receive buffer as a [.., 64]-column matrix
   int M, N, K;
   int m_tiles, n_tiles, k_blocks;
   int act;
@@ -85,7 +87,9 @@ struct Params {
   long long ag_ld;          // elements per row
   int rank, world;
   // ---- GEMM -> reduce-scatter -----------------------------------------------------------
-  __nv_bfloat16* rs_recv[MAX_RANKS];   // rs_recv[o]: rank o's receive buffer [world][rows_per_rank][N]
+  // rs_recv: this rank's receive buffer, tile-contiguous: [src rank][m-tile][n-tile][4 column
+  // chunks][128 rows][64 columns]; a (chunk, 32-row quarter) is one contiguous 4 KiB TMA store box.
+  const __nv_bfloat16* rs_recv;
   uint32_t* rs_count[MAX_RANKS];       // rs_count[o]: rank o's arrival counters, one per (m-tile of o, n-tile)
   uint32_t rs_expect;                  // counter value that means "all world partials of this tile arrived"
   __nv_bfloat16* rs_out;               // this rank's reduced output [rows_per_rank][N]
@@ -136,6 +140,21 @@ __device__ __forceinline__ void stage_row(uint32_t box_smem, int row, const floa
     uint32_t w2 = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
     uint32_t w3 = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
     uint32_t addr = box_smem + row * 64 + ((j ^ ((row >> 1) & 3)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                 : "memory");
+  }
+}
+
+// Same for one half (32 columns) of a [32 rows][128 B] box with the 128-byte swizzle:
+// 16-byte chunk j of row r sits at chunk j ^ (r & 7).  `half` selects columns [0,32) or [32,64).
+__device__ __forceinline__ void stage_row128(uint32_t box_smem, int row, int half, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t w0 = pack_bf16(v[8 * j + 0], v[8 * j + 1]);
+    uint32_t w1 = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+    uint32_t w2 = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
+    uint32_t w3 = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+    uint32_t addr = box_smem + row * 128 + (((half * 4 + j) ^ (row & 7)) << 4);
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
                  : "memory");
   }
@@ -218,8 +237,11 @@ gemm_kernel(const __grid_constant__ Params p) {
         TileCoord tc = tile_coord(tile, p.m_tiles, p.n_tiles, p.m_rotate);
         const int m0 = tc.m_idx * BM;
         const int n0 = tc.n_idx * (EPI == EPI_GLU_FWD ? BN / 2 : BN);
-        if (p.a_ready != nullptr) {
-          // rows of A that arrive from other GPUs: wait for their arrival counter
+        // all-gather: this rank's own rows are read straight from the source shard (no wait);
+        // rows that arrive from other GPUs wait for their arrival counter.
+        const int own_lo = AG ? p.rank * p.ag_rows_per_rank : 0;
+        const bool own = AG && m0 >= own_lo && m0 < own_lo + p.ag_rows_per_rank;
+        if (p.a_ready != nullptr && !own) {
           ok = wait_flag_ge(p.a_ready + m0 / p.a_ready_rows, p.a_ready_value, p.status, SITE_LOCAL_FLAG);
           if (!ok) { *abort_smem = 1; break; }
           fence_proxy_async_all();   // data was written through the generic proxy, TMA reads it
@@ -232,6 +254,7 @@ gemm_kernel(const __grid_constant__ Params p) {
           const uint32_t sA = sA0 + stage * A_STAGE_BYTES;
           const uint32_t sB = sB0 + stage * B_STAGE_BYTES;
           if (A_MN) tma_load_3d(sA, &p.tmA, fb, 0, kb * BK, m0 / 64);
+          else if (own) tma_load_2d(sA, &p.tmA2, fb, kb * BK, m0 - own_lo);
           else      tma_load_2d(sA, &p.tmA, fb, kb * BK, m0);
           if (EPI == EPI_GLU_FWD) {
             tma_load_2d(sB, &p.tmB, fb, kb * BK, n0);
@@ -362,29 +385,55 @@ gemm_kernel(const __grid_constant__ Params p) {
           }
         }
       } else if constexpr (EPI == EPI_GLU_BWD) {
+        // g,u are fetched with coalesced loads (4 lanes per 64-byte row segment), one chunk
+        // ahead, transposed through the staging boxes, and the same boxes then carry dg,du out.
         const int n0 = tc.n_idx * BN;
+        const int lrow = lane >> 2, lchunk = lane & 3;        // loader role: row (of 8), 16-byte chunk
+        const int n_chunks = min(BN / 32, (p.N - n0 + 31) / 32);
+        uint4 gq[4], uq[4];
+        auto fetch = [&](int c) {
+          const int col = n0 + c * 32 + lchunk * 8;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = m0 + q * 32 + lrow + 8 * i;
+            const bool in = (r < p.M) && (col < p.N);
+            const __nv_bfloat16* ptr = p.aux + (long long)r * p.ld_aux + col;
+            gq[i] = in ? __ldg(reinterpret_cast<const uint4*>(ptr)) : make_uint4(0, 0, 0, 0);
+            uq[i] = in ? __ldg(reinterpret_cast<const uint4*>(ptr + p.d_up_cols)) : make_uint4(0, 0, 0, 0);
+          }
+        };
+        fetch(0);
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < n_chunks; ++c) {
           const int col = n0 + c * 32;
-          if (col >= p.N) break;
           uint32_t r[32];
           tmem_ld_32x32(taddr + c * 32, r);
-          // g and u of this row/column range, 64 B each (rows past M read nothing)
-          uint4 gq[4], uq[4];
-          const bool in_rows = grow < p.M;
-          const __nv_bfloat16* gptr = p.aux + (long long)grow * p.ld_aux + col;
+          // boxes of this chunk: set (c & 1); the stores issued two chunks ago must have left them
+          if (lane == 0) tma_store_wait_read<2>();
+          __syncwarp();
+          const uint32_t gbox = my_staging + ((c & 1) * 2) * EPI_BOX_BYTES;
+          const uint32_t ubox = gbox + EPI_BOX_BYTES;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const bool in = in_rows && (col + 8 * j < p.N);
-            gq[j] = in ? __ldg(reinterpret_cast<const uint4*>(gptr) + j) : make_uint4(0, 0, 0, 0);
-            uq[j] = in ? __ldg(reinterpret_cast<const uint4*>(gptr + p.d_up_cols) + j) : make_uint4(0, 0, 0, 0);
+          for (int i = 0; i < 4; ++i) {
+            const int rr = lrow + 8 * i;
+            const uint32_t off = rr * 64 + ((lchunk ^ ((rr >> 1) & 3)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(gbox + off), "r"(gq[i].x), "r"(gq[i].y),
+                         "r"(gq[i].z), "r"(gq[i].w) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ubox + off), "r"(uq[i].x), "r"(uq[i].y),
+                         "r"(uq[i].z), "r"(uq[i].w) : "memory");
           }
-          tmem_ld_wait();
+          if (c + 1 < n_chunks) fetch(c + 1);
+          __syncwarp();
           float dg[32], du[32];
+          tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t gw[4] = {gq[j].x, gq[j].y, gq[j].z, gq[j].w};
-            const uint32_t uw[4] = {uq[j].x, uq[j].y, uq[j].z, uq[j].w};
+            const uint32_t off = lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+            uint32_t gw[4], uw[4];
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(gw[0]), "=r"(gw[1]), "=r"(gw[2]), "=r"(gw[3])
+                         : "r"(gbox + off) : "memory");
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(uw[0]), "=r"(uw[1]), "=r"(uw[2]), "=r"(uw[3])
+                         : "r"(ubox + off) : "memory");
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
               float2 g2 = unpack_bf16(gw[h]);
@@ -400,44 +449,53 @@ gemm_kernel(const __grid_constant__ Params p) {
               du[i + 1] = da1 * a1;
             }
           }
-          uint32_t box = claim_box();
-          stage_row(box, lane, dg);
-          emit_box(&p.tmD, box, col, m0 + q * 32);
-          box = claim_box();
-          stage_row(box, lane, du);
-          emit_box(&p.tmD, box, p.d_up_cols + col, m0 + q * 32);
-        }
-      } else {  // EPI_SCATTER: partial tile goes to the rank that owns these rows
-        const int n0 = tc.n_idx * BN;
-        const int owner = m0 / p.rs_rows_per_rank;
-        const int local_row = grow - owner * p.rs_rows_per_rank;
-        __nv_bfloat16* dst = p.rs_recv[owner] +
-            ((long long)p.rank * p.rs_rows_per_rank + local_row) * (long long)p.N + n0;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          if (n0 + c * 32 >= p.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          if (grow < p.M) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 w;
-              w.x = pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-              w.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-              w.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-              w.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-              if (n0 + c * 32 + 8 * j < p.N) *(reinterpret_cast<uint4*>(dst + c * 32) + j) = w;
-            }
+          __syncwarp();                       // every lane has read its g,u row before it is overwritten
+          stage_row(gbox, lane, dg);
+          stage_row(ubox, lane, du);
+          emit_box(&p.tmD, gbox, col, m0 + q * 32);
+          if (lane == 0) {
+            tma_store_2d(&p.tmD, ubox, p.d_up_cols + col, m0 + q * 32);
+            tma_store_commit();
           }
         }
-        // publish: every lane's stores, then one arrival per warp on the owner's counter
-        __threadfence_system();
-        __syncwarp();
+      } else {  // EPI_SCATTER: partial tile goes to the rank that owns these rows
+        const int owner = m0 / p.rs_rows_per_rank;
+        const int owner_m_tile = (m0 - owner * p.rs_rows_per_rank) / BM;
+        const int m_tiles_local = p.rs_rows_per_rank / BM;
+        // row of the [.., 64]-column view where this warp's first box of the tile starts
+        const int row_base = (((p.rank * m_tiles_local + owner_m_tile) * p.n_tiles + tc.n_idx) * (BN / 64)) * BM + q * 32;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          if (tc.n_idx * BN + c * 64 >= p.N) break;
+          if (lane == 0) tma_store_wait_read<1>();     // two 4 KiB boxes per warp, used alternately
+          __syncwarp();
+          const uint32_t box = my_staging + (c & 1) * 2 * EPI_BOX_BYTES;
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c * 64 + hlf * 32, r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            stage_row128(box, lane, hlf, v);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&p.tmRS[owner], box, 0, row_base + c * BM);
+            tma_store_commit();
+          }
+        }
+        // publish: wait until this warp's bulk stores are complete, order them before the flag at
+        // system scope, then one arrival per warp on the owner's counter for this tile
         if (lane == 0) {
-          const int owner_m_tile = (m0 - owner * p.rs_rows_per_rank) / BM;
+          tma_store_wait_all<0>();
+          fence_proxy_async_all();
+          __threadfence_system();
           red_release_sys_add(p.rs_count[owner] + owner_m_tile * p.n_tiles + tc.n_idx, 1u);
         }
+        __syncwarp();
       }
       // accumulator fully read: hand it back to the MMA warp
       tc_fence_before();
@@ -471,10 +529,12 @@ gemm_kernel(const __grid_constant__ Params p) {
       const long long beg = part * per_part;
       const long long end = min(vec_per_block, beg + per_part);
       long long i = beg + tid;
-      for (; i + 3 * NT < end; i += 4 * NT) {
-        uint4 v0 = __ldg(src + i), v1 = __ldg(src + i + NT), v2 = __ldg(src + i + 2 * NT),
-              v3 = __ldg(src + i + 3 * NT);
-        dst[i] = v0; dst[i + NT] = v1; dst[i + 2 * NT] = v2; dst[i + 3 * NT] = v3;
+      for (; i + 7 * NT < end; i += 8 * NT) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldg(src + i + u * NT);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[i + u * NT] = v[u];
       }
       for (; i < end; i += NT) dst[i] = __ldg(src + i);
       __threadfence_system();
@@ -509,22 +569,33 @@ gemm_kernel(const __grid_constant__ Params p) {
       const bool good = item_ok != 0;
       __syncthreads();
       if (!good) break;
-      const int rows = min(BM, p.rs_rows_per_rank - mt * BM);
       const int cols = min(BN, p.N - nt * BN);
-      const int vec_per_row = cols / 8;
-      for (int idx = threadIdx.x; idx < rows * vec_per_row; idx += blockDim.x) {
-        const int r = idx / vec_per_row, v = idx % vec_per_row;
-        const long long off = (long long)(mt * BM + r) * p.N + nt * BN + v * 8;
+      const int m_tiles_local = p.rs_rows_per_rank / BM;
+      constexpr int TILE_ELEMS = BM * BN;
+      // one 16-byte vector per thread and step: (chunk c, row r, vector v) with v fastest
+      for (int idx = threadIdx.x; idx < (BN / 64) * BM * 8; idx += blockDim.x) {
+        const int v = idx & 7, r = (idx >> 3) & (BM - 1), c = idx >> 10;
+        if (c * 64 + v * 8 >= cols) continue;
+        const long long in_tile = (long long)c * (BM * 64) + r * 64 + v * 8;
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int s = 0; s < p.world; ++s) {
-          const uint4 w = __ldcg(reinterpret_cast<const uint4*>(
-              p.rs_recv[p.rank] + (long long)s * p.rs_rows_per_rank * p.N + off));
-          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        uint4 w[MAX_RANKS];
 #pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            float2 f = unpack_bf16(ww[h]);
-            acc[2 * h] += f.x;
-            acc[2 * h + 1] += f.y;
+        for (int s = 0; s < MAX_RANKS; ++s) {       // all sources in flight, then a fixed-order sum
+          if (s < p.world) {
+            const long long tile = ((long long)s * m_tiles_local + mt) * p.n_tiles + nt;
+            w[s] = __ldcg(reinterpret_cast<const uint4*>(p.rs_recv + tile * TILE_ELEMS + in_tile));
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < MAX_RANKS; ++s) {
+          if (s < p.world) {
+            const uint32_t ww[4] = {w[s].x, w[s].y, w[s].z, w[s].w};
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              float2 f = unpack_bf16(ww[h]);
+              acc[2 * h] += f.x;
+              acc[2 * h + 1] += f.y;
+            }
           }
         }
         uint4 o;
@@ -532,7 +603,7 @@ gemm_kernel(const __grid_constant__ Params p) {
         o.y = pack_bf16(acc[2], acc[3]);
         o.z = pack_bf16(acc[4], acc[5]);
         o.w = pack_bf16(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(p.rs_out + off) = o;
+        *reinterpret_cast<uint4*>(p.rs_out + (long long)(mt * BM + r) * p.N + nt * BN + c * 64 + v * 8) = o;
       }
     }
   }

@@ -33,6 +33,7 @@ def _stream() -> int:
 def _launch(args: _native.GemmArgs) -> None:
     rc = _native.lib().mesh_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_stream()))
     _native.check(rc, "mesh_gemm_bf16")
+    _native.count_launch()
 
 
 def _base_args(a: torch.Tensor, b: torch.Tensor, a_mn: bool, b_mn: bool) -> tuple[_native.GemmArgs, int, int, int]:

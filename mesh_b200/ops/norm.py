@@ -36,6 +36,7 @@ def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: t
     rc = L.mesh_rmsnorm_fwd(_p(x), _p(residual), _p(w), _p(y), _p(res_out), _p(rstd), c_int(rows), c_int(cols),
                             c_float(eps), c_float(weight_offset), _s())
     _native.check(rc, "mesh_rmsnorm_fwd")
+    _native.count_launch(1)
     return y, res_out, rstd
 
 
@@ -50,6 +51,7 @@ def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.
     rc = L.mesh_rmsnorm_bwd(_p(dy.contiguous()), _p(x), _p(w), _p(rstd), _p(dx), _p(dw), _p(partial), c_int(blocks),
                             c_int(rows), c_int(cols), c_float(weight_offset), _s())
     _native.check(rc, "mesh_rmsnorm_bwd")
+    _native.count_launch(2)
     return dx, dw
 
 

@@ -30,6 +30,7 @@ def rope_(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torc
                                  c_longlong(x.stride(0)), c_int(int(inverse)),
                                  c_void_p(torch.cuda.current_stream().cuda_stream))
     _native.check(rc, "mesh_rope")
+    _native.count_launch(1)
     return x
 
 

@@ -23,6 +23,7 @@ def router_topk(logits: torch.Tensor, k: int, bias: torch.Tensor | None = None, 
                                         c_void_p(idx.data_ptr()), c_int(T), c_int(E), c_int(k), c_int(int(renorm)),
                                         c_void_p(torch.cuda.current_stream().cuda_stream))
     _native.check(rc, "mesh_router_topk")
+    _native.count_launch(1)
     return w, idx
 
 

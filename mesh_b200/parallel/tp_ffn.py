@@ -54,7 +54,8 @@ class _Scattered:
 
     def __init__(self, heap: SymmetricHeap, world: int, rows: int, N: int):
         self.world = world
-        self.buf = [heap.alloc((world, rows, N), torch.bfloat16) for _ in range(2)]
+        # tile-contiguous: [src rank][m-tile][n-tile][128*256]
+        self.buf = [heap.alloc((world, rows // BM, (N + BN - 1) // BN, BM * BN), torch.bfloat16) for _ in range(2)]
         self.count = [heap.alloc_signals((rows // BM) * ((N + BN - 1) // BN)) for _ in range(2)]
         self.uses = [0, 0]
         self.turn = 0
