@@ -40,7 +40,7 @@ class GemmArgs(ctypes.Structure):
         ("rank", c_int), ("world", c_int),
         ("rs_recv", c_void_p * MAX_RANKS), ("rs_count", c_void_p * MAX_RANKS),
         ("rs_expect", c_uint32), ("rs_out", c_void_p), ("rs_rows_per_rank", c_int),
-        ("num_ctas", c_int),
+        ("num_ctas", c_int), ("tile_n", c_int), ("pair", c_int),
     ]
 
 

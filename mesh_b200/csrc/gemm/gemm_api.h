@@ -42,10 +42,14 @@ typedef struct MeshGemmArgs {
   void* rs_out;
   int rs_rows_per_rank;
   int num_ctas;                // 0: one per SM
+  int tile_n;                  // 0: choose; 128 or 256: width of the output tile
+  int pair;                    // 0: cta_group::2 pairs when possible; -1: single-CTA tiles
 } MeshGemmArgs;
 
 // Returns 0 or a negative error (bad shape/alignment) or a positive cudaError_t.
 int mesh_gemm_bf16(const MeshGemmArgs* args, void* stream);
+// Tile width the launcher picks for an M x N problem on `ctas` CTAs (0: one per SM).
+int mesh_gemm_choose_tile_n(int M, int N, int ctas);
 const char* mesh_last_error(void);
 
 #ifdef __cplusplus

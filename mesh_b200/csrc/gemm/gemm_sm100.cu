@@ -33,9 +33,9 @@ static bool make_map_mn(CUtensorMap* tm, const void* base, uint64_t mn_cols, uin
                       CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int A_MN, int B_MN, int EPI, bool AG>
+template <int A_MN, int B_MN, int EPI, bool AG, int BNV, bool PAIR>
 static int launch(const Params& p, int ctas, cudaStream_t stream) {
-  auto kern = gemm_kernel<A_MN, B_MN, EPI, AG>;
+  auto kern = gemm_kernel<A_MN, B_MN, EPI, AG, BNV, PAIR>;
   static bool configured = false;   // per instantiation
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -43,8 +43,21 @@ static int launch(const Params& p, int ctas, cudaStream_t stream) {
     configured = true;
   }
   const int threads = NUM_THREADS + (AG ? 32 * COMM_WARPS : 0);
-  kern<<<ctas, threads, SMEM_BYTES, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_error((int)e, "gemm launch: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -54,6 +67,19 @@ static int launch(const Params& p, int ctas, cudaStream_t stream) {
 
 using namespace mesh;
 using namespace mesh::gemm;
+
+extern "C" int mesh_gemm_choose_tile_n(int M, int N, int ctas) {
+  if (ctas <= 0) ctas = sm_count();
+  const long m_tiles = (M + BM - 1) / BM;
+  auto eff = [&](int bn) {
+    const long tiles = m_tiles * ((N + bn - 1) / bn);
+    const long waves = (tiles + ctas - 1) / ctas;
+    return (double)tiles / (double)(waves * ctas) * ((double)N / (double)(((N + bn - 1) / bn) * bn));
+  };
+  // a 128-wide tile re-reads A twice as often and runs nearer the shared-memory limit: it has to
+  // win by a clear margin before it is chosen
+  return eff(128) * 0.80 > eff(256) ? 128 : 256;
+}
 
 extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   cudaStream_t stream = (cudaStream_t)stream_v;
@@ -72,8 +98,19 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   memset(&p, 0, sizeof(p));
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.m_tiles = (a->M + BM - 1) / BM;
-  const int tile_n = (a->epi == EPI_GLU_FWD) ? BN / 2 : BN;
+  int ctas = a->num_ctas > 0 ? a->num_ctas : sm_count();
+  // Tile width: 256 by default; 128 when that fills the last wave of CTAs much better.
+  int bn = a->tile_n;
+  if (a->epi == EPI_GLU_FWD) bn = 256;
+  if (bn != 128 && bn != 256) bn = mesh_gemm_choose_tile_n(a->M, a->N, ctas);
+  const int tile_n = (a->epi == EPI_GLU_FWD) ? BN / 2 : bn;
   p.n_tiles = (a->N + tile_n - 1) / tile_n;
+  // cta_group::2 pairs (256-row tiles) unless switched off or the problem has a single m-tile
+  const bool pair = a->pair >= 0 && p.m_tiles >= 2 && ctas >= 2;
+  const int cta_per_unit = pair ? 2 : 1;
+  if (pair) ctas &= ~1;
+  p.m_units = (p.m_tiles + cta_per_unit - 1) / cta_per_unit;
+  const int bn_cta = bn / cta_per_unit;
   p.k_blocks = (a->K + BK - 1) / BK;
   p.act = a->act;
   p.b_up_rows = a->b_up_rows;
@@ -85,7 +122,7 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   p.a_ready = (const uint32_t*)a->a_ready;
   p.a_ready_value = a->a_ready_value;
   p.a_ready_rows = a->a_ready_rows > 0 ? a->a_ready_rows : BM;
-  p.m_rotate = a->m_rotate;
+  p.m_rotate = a->m_rotate;   // converted to scheduling units below
   p.rank = a->rank; p.world = a->world > 0 ? a->world : 1;
   const bool ag = a->ag_src != nullptr;
   if (ag) {
@@ -106,8 +143,8 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   if (a->epi == EPI_SCATTER) {
     if (a->rs_rows_per_rank % BM) return set_error(-5, "gemm: reduce-scatter rows per rank must be a multiple of 128");
     // every rank's receive buffer viewed as a [rows, 64] matrix: one box = one contiguous 4 KiB run
-    const uint64_t n_tiles_rs = (uint64_t)((a->N + BN - 1) / BN);
-    const uint64_t view_rows = (uint64_t)p.world * (a->rs_rows_per_rank / BM) * n_tiles_rs * (BN / 64) * BM;
+    const uint64_t n_tiles_rs = (uint64_t)p.n_tiles;
+    const uint64_t view_rows = (uint64_t)p.world * (a->rs_rows_per_rank / BM) * n_tiles_rs * (bn / 64) * BM;
     for (int r = 0; r < p.world; ++r) {
       p.rs_count[r] = (uint32_t*)a->rs_count[r];
       if (!make_map_2d(&p.tmRS[r], a->rs_recv[r], 64, view_rows, 64, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -125,9 +162,9 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   else         ok = ok && make_map_2d(&p.tmA, a->A, (uint64_t)a->K, (uint64_t)(a->a_rows ? a->a_rows : a->M),
                                       (uint64_t)a->lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
   const uint64_t b_rows = (uint64_t)(a->b_rows ? a->b_rows : a->N);
-  if (a->b_mn) ok = ok && make_map_mn(&p.tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->ldb, BN / 64);
+  if (a->b_mn) ok = ok && make_map_mn(&p.tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->ldb, bn_cta / 64);
   else         ok = ok && make_map_2d(&p.tmB, a->B, (uint64_t)a->K, b_rows, (uint64_t)a->ldb, BK,
-                                      a->epi == EPI_GLU_FWD ? BN / 2 : BN, CU_TENSOR_MAP_SWIZZLE_128B);
+                                      a->epi == EPI_GLU_FWD ? BN / 2 : bn_cta, CU_TENSOR_MAP_SWIZZLE_128B);
   if (a->epi != EPI_SCATTER) {
     if (a->ldd % 8 || (uintptr_t)a->D % 16) return set_error(-2, "gemm: D must be 16-byte aligned with ld %% 8 == 0");
     const uint64_t d_cols = (uint64_t)(a->d_cols ? a->d_cols : a->N);
@@ -141,11 +178,22 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   }
   if (!ok) return last_error_code();
 
-  int ctas = a->num_ctas > 0 ? a->num_ctas : sm_count();
-  const int tiles = p.m_tiles * p.n_tiles;
+  const int tiles = p.m_units * p.n_tiles * cta_per_unit;
   if (!ag && a->epi != EPI_SCATTER && ctas > tiles) ctas = tiles;
+  if (pair) {
+    if (p.m_rotate % 2) p.m_rotate = 0; else p.m_rotate /= 2;   // rotation is only an ordering hint
+  }
 
-#define MESH_LAUNCH(AM, BMJ, E, G) return launch<AM, BMJ, E, G>(p, ctas, stream)
+#define MESH_LAUNCH(AM, BMJ, E, G)                                          \
+  do {                                                                      \
+    constexpr int E128 = ((E) == EPI_GLU_FWD ? EPI_STORE : (E));            \
+    if (bn == 128 && (E) != EPI_GLU_FWD) {                                  \
+      if (pair) return launch<AM, BMJ, E128, G, 128, true>(p, ctas, stream); \
+      return launch<AM, BMJ, E128, G, 128, false>(p, ctas, stream);         \
+    }                                                                       \
+    if (pair) return launch<AM, BMJ, E, G, 256, true>(p, ctas, stream);     \
+    return launch<AM, BMJ, E, G, 256, false>(p, ctas, stream);              \
+  } while (0)
   switch (a->epi) {
     case EPI_STORE:
       if (ag) {

@@ -65,6 +65,7 @@ struct Params {
   CUtensorMap tmRS[MAX_RANKS];         // reduce-scatter: rank o's receive buffer as a [.., 64]-column matrix
   int M, N, K;
   int m_tiles, n_tiles, k_blocks;
+  int m_units;              // m-tiles (single CTA) or pairs of m-tiles (cta_group::2) the scheduler walks
   int act;
   int b_up_rows;            // GLU_FWD: row offset of the "up" weights inside B
   int d_up_cols;            // GLU_FWD (D2) / GLU_BWD (D and aux): column offset of the "up" half
@@ -97,25 +98,37 @@ struct Params {
 };
 
 // ------------------------------------------------------------------------------------------
+// Hardware approximations (ex2/rcp/tanh .approx, ~2^-11 relative error) are ample for values
+// that are rounded to bf16 right after, and keep the epilogue well under the MMA time per tile.
+__device__ __forceinline__ float fast_sigmoid(float g) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  return r;
+}
+__device__ __forceinline__ float fast_tanh(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
+}
 __device__ __forceinline__ float act_fwd(float g, int act) {
   if (act == ACT_SILU) {
-    return g / (1.f + __expf(-g));
+    return g * fast_sigmoid(g);
   } else {
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-    float t = tanhf(k0 * (g + k1 * g * g * g));
+    float t = fast_tanh(k0 * (g + k1 * g * g * g));
     return 0.5f * g * (1.f + t);
   }
 }
 // returns act(g) and writes d act / d g
 __device__ __forceinline__ float act_fwd_bwd(float g, int act, float& dact) {
   if (act == ACT_SILU) {
-    float s = 1.f / (1.f + __expf(-g));
+    float s = fast_sigmoid(g);
     dact = s * (1.f + g * (1.f - s));
     return g * s;
   } else {
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-    float inner = k0 * (g + k1 * g * g * g);
-    float t = tanhf(inner);
+    float t = fast_tanh(k0 * (g + k1 * g * g * g));
     dact = 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
     return 0.5f * g * (1.f + t);
   }
@@ -181,9 +194,22 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, int n_til
   return c;
 }
 
-template <int A_MN, int B_MN, int EPI, bool AG>
+// PAIR: two CTAs of a cluster work on one 256-row tile with tcgen05 cta_group::2.  Each CTA loads
+// its own 128 rows of A and its own half of the B tile (plain TMA loads, no multicast); the
+// leader CTA issues the MMAs for both, so every SM pulls a third less from L2 per FLOP.
+template <int A_MN, int B_MN, int EPI, bool AG, int BN_T, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS + (AG ? 32 * COMM_WARPS : 0), 1)
 gemm_kernel(const __grid_constant__ Params p) {
+  // tile width is a template parameter: 256 or 128; a CTA stages BN (single) or BN/2 (pair) rows of B
+  constexpr int BN = BN_T;
+  constexpr int CTAS = PAIR ? 2 : 1;
+  constexpr int BN_CTA = BN / CTAS;
+  constexpr int B_STAGE_BYTES = BN_CTA * BK * 2;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  constexpr int STAGES = (STAGE_BYTES == 48 * 1024) ? 4 : (STAGE_BYTES == 32 * 1024 ? 6 : 8);
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  static_assert(STAGES * STAGE_BYTES == gemm::STAGES * gemm::STAGE_BYTES, "every variant uses the same shared memory");
+  static_assert(EPI != EPI_GLU_FWD || BN == 256, "GLU forward keeps gate and up halves in one 256-wide accumulator");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA0 = smem_base;
@@ -201,7 +227,8 @@ gemm_kernel(const __grid_constant__ Params p) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int total_tiles = p.m_units * p.n_tiles;   // a unit is one m-tile, or a pair of them
+  const int tile_first = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -210,7 +237,7 @@ gemm_kernel(const __grid_constant__ Params p) {
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), EPI_WARPS);
+      mbar_init(tempty_bar(a), EPI_WARPS * CTAS);
     }
     *abort_smem = 0;
     fence_mbar_init();
@@ -219,11 +246,12 @@ gemm_kernel(const __grid_constant__ Params p) {
     if (EPI != EPI_SCATTER) prefetch_tmap(&p.tmD);
   }
   if (warp == 0) {
-    tmem_alloc<1>(smem_u32(tmem_slot), TMEM_COLS);
-    tmem_relinquish<1>();
+    tmem_alloc<CTAS>(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish<CTAS>();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
@@ -233,9 +261,9 @@ gemm_kernel(const __grid_constant__ Params p) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        TileCoord tc = tile_coord(tile, p.m_tiles, p.n_tiles, p.m_rotate);
-        const int m0 = tc.m_idx * BM;
+      for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
+        TileCoord tc = tile_coord(tile, p.m_units, p.n_tiles, p.m_rotate);
+        const int m0 = (tc.m_idx * CTAS + (int)cta_rank) * BM;
         const int n0 = tc.n_idx * (EPI == EPI_GLU_FWD ? BN / 2 : BN);
         // all-gather: this rank's own rows are read straight from the source shard (no wait);
         // rows that arrive from other GPUs wait for their arrival counter.
@@ -249,20 +277,37 @@ gemm_kernel(const __grid_constant__ Params p) {
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, p.status, SITE_SMEM_EMPTY);
           if (!ok) break;
-          const uint32_t fb = full_bar(stage);
-          mbar_expect_tx(fb, STAGE_BYTES);
           const uint32_t sA = sA0 + stage * A_STAGE_BYTES;
           const uint32_t sB = sB0 + stage * B_STAGE_BYTES;
-          if (A_MN) tma_load_3d(sA, &p.tmA, fb, 0, kb * BK, m0 / 64);
-          else if (own) tma_load_2d(sA, &p.tmA2, fb, kb * BK, m0 - own_lo);
-          else      tma_load_2d(sA, &p.tmA, fb, kb * BK, m0);
-          if (EPI == EPI_GLU_FWD) {
-            tma_load_2d(sB, &p.tmB, fb, kb * BK, n0);
-            tma_load_2d(sB + B_STAGE_BYTES / 2, &p.tmB, fb, kb * BK, p.b_up_rows + n0);
-          } else if (B_MN) {
-            tma_load_3d(sB, &p.tmB, fb, 0, kb * BK, n0 / 64);
+          if constexpr (!PAIR) {
+            const uint32_t fb = full_bar(stage);
+            mbar_expect_tx(fb, STAGE_BYTES);
+            if (A_MN) tma_load_3d(sA, &p.tmA, fb, 0, kb * BK, m0 / 64);
+            else if (own) tma_load_2d(sA, &p.tmA2, fb, kb * BK, m0 - own_lo);
+            else      tma_load_2d(sA, &p.tmA, fb, kb * BK, m0);
+            if (EPI == EPI_GLU_FWD) {
+              tma_load_2d(sB, &p.tmB, fb, kb * BK, n0);
+              tma_load_2d(sB + B_STAGE_BYTES / 2, &p.tmB, fb, kb * BK, p.b_up_rows + n0);
+            } else if (B_MN) {
+              tma_load_3d(sB, &p.tmB, fb, 0, kb * BK, n0 / 64);
+            } else {
+              tma_load_2d(sB, &p.tmB, fb, kb * BK, n0);
+            }
           } else {
-            tma_load_2d(sB, &p.tmB, fb, kb * BK, n0);
+            // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
+            if (cta_rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+            const uint32_t fb = mapa_u32(full_bar(stage), 0);
+            if (A_MN) tma_load_3d_pair(sA, &p.tmA, fb, 0, kb * BK, m0 / 64);
+            else if (own) tma_load_2d_pair(sA, &p.tmA2, fb, kb * BK, m0 - own_lo);
+            else      tma_load_2d_pair(sA, &p.tmA, fb, kb * BK, m0);
+            if (EPI == EPI_GLU_FWD) {
+              // leader stages the gate rows, its peer the up rows: accumulator columns [0,128) | [128,256)
+              tma_load_2d_pair(sB, &p.tmB, fb, kb * BK, (cta_rank ? p.b_up_rows : 0) + n0);
+            } else if (B_MN) {
+              tma_load_3d_pair(sB, &p.tmB, fb, 0, kb * BK, (n0 + (int)cta_rank * BN_CTA) / 64);
+            } else {
+              tma_load_2d_pair(sB, &p.tmB, fb, kb * BK, n0 + (int)cta_rank * BN_CTA);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -270,13 +315,13 @@ gemm_kernel(const __grid_constant__ Params p) {
     }
   } else if (warp == 1) {
     // ===================================================================== MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM * CTAS, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int t = 0;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
+      for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step, ++t) {
         const int acc = t & 1;
         const uint32_t acc_phase = (t >> 1) & 1;
         ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_smem, p.status, SITE_TMEM_EMPTY);
@@ -297,12 +342,17 @@ gemm_kernel(const __grid_constant__ Params p) {
                                      : umma_smem_desc(sA + k * 32, 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(sB + k * 2048, 8192, 1024)
                                      : umma_smem_desc(sB + k * 32, 16, 1024);
-            umma_f16<1>(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16<CTAS>(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(empty_bar(stage));   // stage is free once these MMAs have read it
+          // stage is free (in both CTAs of a pair) once these MMAs have read it
+          if constexpr (PAIR) umma_commit_pair(empty_bar(stage), 3);
+          else umma_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(tfull_bar(acc));
+        if (ok) {
+          if constexpr (PAIR) umma_commit_pair(tfull_bar(acc), 3);
+          else umma_commit(tfull_bar(acc));
+        }
       }
     }
   } else if (warp < 2 + EPI_WARPS) {
@@ -329,9 +379,9 @@ gemm_kernel(const __grid_constant__ Params p) {
         tma_store_commit();
       }
     };
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
-      TileCoord tc = tile_coord(tile, p.m_tiles, p.n_tiles, p.m_rotate);
-      const int m0 = tc.m_idx * BM;
+    for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step, ++t) {
+      TileCoord tc = tile_coord(tile, p.m_units, p.n_tiles, p.m_rotate);
+      const int m0 = (tc.m_idx * CTAS + (int)cta_rank) * BM;
       const int acc = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
       ok = mbar_wait(tfull_bar(acc), acc_phase, abort_smem, p.status, SITE_TMEM_FULL);
@@ -500,7 +550,10 @@ gemm_kernel(const __grid_constant__ Params p) {
       // accumulator fully read: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (PAIR && cta_rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
+        else mbar_arrive(tempty_bar(acc));
+      }
     }
     if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
@@ -548,9 +601,10 @@ gemm_kernel(const __grid_constant__ Params p) {
   // ------------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // neither CTA frees TMEM or exits while its peer still uses the pair
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc<1>(tmem_base, TMEM_COLS);
+    tmem_dealloc<CTAS>(tmem_base, TMEM_COLS);
   }
 
   if constexpr (EPI == EPI_SCATTER) {

@@ -56,7 +56,7 @@ def _base_args(a: torch.Tensor, b: torch.Tensor, a_mn: bool, b_mn: bool) -> tupl
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
-         out: torch.Tensor | None = None, num_ctas: int = 0) -> torch.Tensor:
+         out: torch.Tensor | None = None, num_ctas: int = 0, tile_n: int = 0, pair: int = 0) -> torch.Tensor:
     """``out[M,N] = A[M,K] @ B[N,K]^T`` with fp32 accumulation.
 
     ``a_mn``: ``a`` is stored ``[K, M]``;  ``b_mn``: ``b`` is stored ``[K, N]``.
@@ -67,7 +67,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     _check2d(out, "out")
     g.D, g.ldd, g.d_cols = out.data_ptr(), out.stride(0), out.shape[1]
     g.epi = EPI_STORE
-    g.num_ctas = num_ctas
+    g.num_ctas, g.tile_n, g.pair = num_ctas, tile_n, pair
     _launch(g)
     return out
 

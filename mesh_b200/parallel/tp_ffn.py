@@ -54,9 +54,12 @@ class _Scattered:
 
     def __init__(self, heap: SymmetricHeap, world: int, rows: int, N: int):
         self.world = world
-        # tile-contiguous: [src rank][m-tile][n-tile][128*256]
-        self.buf = [heap.alloc((world, rows // BM, (N + BN - 1) // BN, BM * BN), torch.bfloat16) for _ in range(2)]
-        self.count = [heap.alloc_signals((rows // BM) * ((N + BN - 1) // BN)) for _ in range(2)]
+        # tile width the launcher would pick for the whole [world*rows, N] product
+        self.tile_n = _native.lib().mesh_gemm_choose_tile_n(world * rows, N, 0)
+        bn = self.tile_n
+        # tile-contiguous: [src rank][m-tile][n-tile][128*bn]
+        self.buf = [heap.alloc((world, rows // BM, (N + bn - 1) // bn, BM * bn), torch.bfloat16) for _ in range(2)]
+        self.count = [heap.alloc_signals((rows // BM) * ((N + bn - 1) // bn)) for _ in range(2)]
         self.uses = [0, 0]
         self.turn = 0
 
@@ -112,6 +115,7 @@ class FusedTPFFN:
     def _scatter_args(self, g, zone: _Scattered, out: torch.Tensor):
         buf, count, expect = zone.next()
         g.epi = G.EPI_SCATTER
+        g.tile_n = zone.tile_n
         for r in range(self.world):
             g.rs_recv[r] = buf.ptr(r)
             g.rs_count[r] = count.ptr(r)

@@ -1,0 +1,70 @@
+"""Small single-GPU workloads for profiler captures (one op per invocation, a few launches).
+
+    python -m mesh_b200.tools.prof_ops gemm --m 4096 --n 4096 --k 4096 --iters 3
+    python -m mesh_b200.tools.prof_ops glu_fwd | glu_bwd | rmsnorm | rope | router
+
+Sizes are chosen larger than L2 (126 MB) in total footprint where DRAM figures matter but a few
+hundred MB at most, so a full-metric capture of one or two launches ends by itself in about a minute.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op")
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    from mesh_b200.ops import gemm as G
+    from mesh_b200.utils.status import check_status
+    dev = "cuda"
+    torch.manual_seed(0)
+    if a.op == "gemm":
+        x = torch.randn(a.m, a.k, device=dev).bfloat16()
+        w = torch.randn(a.n, a.k, device=dev).bfloat16()
+        for _ in range(a.iters):
+            G.gemm(x, w)
+    elif a.op == "glu_fwd":
+        x = torch.randn(a.m, a.k, device=dev).bfloat16()
+        w = (torch.randn(2 * a.n, a.k, device=dev) * 0.02).bfloat16()
+        for _ in range(a.iters):
+            G.glu_fwd(x, w)
+    elif a.op == "glu_bwd":
+        dy = torch.randn(a.m, a.k, device=dev).bfloat16()
+        wd = (torch.randn(a.k, a.n, device=dev) * 0.02).bfloat16()
+        gu = torch.randn(a.m, 2 * a.n, device=dev).bfloat16()
+        for _ in range(a.iters):
+            G.glu_bwd(dy, wd, gu)
+    elif a.op == "rmsnorm":
+        from mesh_b200.ops.norm import rmsnorm_fwd
+        x = torch.randn(a.m * 8, a.n, device=dev).bfloat16()
+        w = torch.ones(a.n, device=dev).bfloat16()
+        for _ in range(a.iters):
+            rmsnorm_fwd(x, w)
+    elif a.op == "rope":
+        from mesh_b200.ops.rope import rope_, rope_tables
+        cos, sin = rope_tables(4096, 256, 1e6)
+        x = torch.randn(a.m * 8, 8, 256, device=dev).bfloat16()
+        pos = torch.randint(0, 4096, (a.m * 8,), device=dev, dtype=torch.int32)
+        for _ in range(a.iters):
+            rope_(x, pos, cos, sin)
+    elif a.op == "router":
+        from mesh_b200.ops.router import router_topk
+        logits = torch.randn(a.m * 64, 64, device=dev)
+        for _ in range(a.iters):
+            router_topk(logits, 6)
+    else:
+        raise SystemExit(f"unknown op {a.op}")
+    check_status()
+    torch.cuda.synchronize()
+    print("ok")
+
+
+if __name__ == "__main__":
+    main()
