@@ -75,6 +75,10 @@ def init(backend: str | None = None, device: str | torch.device | None = None, t
     return _ctx
 
 
+def current_or_none() -> "MeshContext | None":
+    return _ctx
+
+
 def context() -> MeshContext:
     if _ctx is None:
         return init()
