@@ -1,0 +1,365 @@
+// Skinny (batch <= 8) linear layers for token-by-token decoding: y[b, n] = sum_k x[b, k] W[n, k].
+//
+// Decoding is bound by the bytes of W, so the kernel is organised around streaming W once at full
+// HBM rate: a CTA owns 16 rows of W (two groups of 8), its 8 warps split K, each lane pulls 16-byte
+// pieces of two rows straight from global memory into mma.sync A fragments (the k order inside a
+// 32-wide block is permuted identically for W and x, which a dot product does not notice), the
+// batch is the 8-wide N side of m16n8k16, and partial sums meet in shared memory.  Around that
+// core sit the fusions that remove the launches between the layers of a decoder block:
+//   prologue   RMSNorm of x (recomputed by every CTA: duplicated cheap compute is free,
+//              design/collective-goals.md:27-29)
+//   weights    bf16, or 4-bit codes with one fp16 scale per 64 k (dequantised in registers with a
+//              mask, subtract and multiply per pair; reference: `mesh::fragment` coded weights,
+//              rdma/mesh_code.py:9-16, compiler/mesh_compiler/operations.py:6996-7040)
+//   epilogue   store | GLU (gate and up rows in one CTA) | QKV + RoPE + KV-cache append |
+//              one-shot all-reduce across GPUs + residual add (row-parallel projections of a
+//              tensor-parallel block: 8-byte {value, sequence} words stored into every peer and
+//              polled locally, so one NVLink crossing per reduction, K2 of the reference's table).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include "decode_api.h"
+#include "../device/ptx.cuh"
+#include "../runtime/host_common.h"
+
+namespace mesh {
+namespace decode {
+
+constexpr int THREADS = 256;
+constexpr int WARPS = 8;
+constexpr int NB = 8;                 // batch columns of the MMA
+constexpr int XPAD = 64;              // bytes of padding per x row in shared memory (bank spread)
+
+struct LinArgs {
+  const __nv_bfloat16* x; long long ldx; int B, K;
+  const __nv_bfloat16* norm_w; float eps, norm_off;   // prologue RMSNorm (norm_w == nullptr: none)
+  const void* w; const __half* scales;                // weights [N, K] bf16, or packed 4-bit [N, K/2] + scales [N, K/64]
+  int n_groups;                                       // 16-row groups this launch covers
+  int mode, act;
+  int up_off;                                         // GLU: row offset of the up weights; QKV: unused
+  void* out; long long ldo; int out_f32;              // STORE/GLU output [B, N]
+  // QKV + RoPE + cache append
+  int q_heads, kv_heads, head_dim;                    // local heads; rows = (q_heads + 2 kv_heads) * head_dim
+  const int* pos; const float* cos_t; const float* sin_t;
+  __nv_bfloat16* q_out;                               // [B, q_heads * head_dim]
+  __nv_bfloat16* k_cache; __nv_bfloat16* v_cache;     // [B, kv_heads, max_seq, head_dim]
+  int max_seq;
+  // all-reduce + residual
+  int rank, world;
+  uint2* ar_recv[MESH_DEC_MAX_RANKS];                 // ar_recv[d]: rank d's slots [world][N * 8]
+  const uint32_t* step_ptr; uint32_t calls_per_step, call_index;   // sequence number = step * calls + index + 1
+  const __nv_bfloat16* residual; long long ldr;       // [B, N]
+  Status* status;
+};
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 8 packed 4-bit codes (nibble order 0,4,1,5,2,6,3,7 = k 0..7) -> four bf16x2 words (c - 8) * s
+__device__ __forceinline__ void dequant8(uint32_t p, __nv_bfloat162 s2, __nv_bfloat162 bias2, uint32_t (&o)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t t = ((p >> (4 * i)) & 0x000F000Fu) | 0x43004300u;          // bf16(128 + code) in both halves
+    // (128 + c) - 136 is exact in bf16; folding the 136*s into an fma addend would round it first
+    __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&t), bias2), s2);
+    o[i] = *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+__device__ __forceinline__ float dec_act(float g, int act) {
+  if (act == 0) {
+    return g / (1.f + __expf(-g));
+  } else {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    return 0.5f * g * (1.f + tanhf(k0 * (g + k1 * g * g * g)));
+  }
+}
+
+// first row of the two 8-row groups a CTA works on
+__device__ __forceinline__ void group_rows(const LinArgs& a, int g, int& rA, int& rB) {
+  if (a.mode == MESH_DEC_GLU) {
+    rA = g * 8;
+    rB = a.up_off + g * 8;
+  } else if (a.mode == MESH_DEC_QKV) {
+    const int per_head = a.head_dim / 16;               // groups per head: rows i..i+8 and i+hd/2..
+    const int h = g / per_head, j = g % per_head;
+    rA = h * a.head_dim + j * 8;
+    rB = rA + a.head_dim / 2;
+  } else {
+    rA = g * 16;
+    rB = rA + 8;
+  }
+}
+
+template <int W4>
+__global__ void __launch_bounds__(THREADS) decode_linear_kernel(const LinArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int K = a.K;
+  const int xstride = K * 2 + XPAD;                               // bytes per x row
+  uint8_t* xs = smem;                                             // [NB][xstride]
+  float* red = reinterpret_cast<float*>(smem + NB * xstride);     // [WARPS][16][NB]
+  float* fin = red + WARPS * 16 * NB;                             // [16][NB]
+  __shared__ float rstd_s[NB];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g8 = lane >> 2, t4 = lane & 3;
+
+  // ---- prologue: x (zero rows past the batch) -> shared memory, optionally RMS-normalised
+  {
+    const int nvec = K >> 3;
+    for (int b = warp; b < NB; b += WARPS) {
+      float ss = 0.f;
+      for (int v = lane; v < nvec; v += 32) {
+        uint4 q = make_uint4(0, 0, 0, 0);
+        if (b < a.B) q = *reinterpret_cast<const uint4*>(a.x + (long long)b * a.ldx + v * 8);
+        *reinterpret_cast<uint4*>(xs + b * xstride + v * 16) = q;
+        if (a.norm_w) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(h[i]);
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+      }
+      if (a.norm_w) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) rstd_s[b] = rsqrtf(ss / (float)K + a.eps);
+      }
+    }
+    __syncthreads();
+    if (a.norm_w) {
+      for (int idx = threadIdx.x; idx < NB * nvec; idx += THREADS) {
+        const int b = idx / nvec, v = idx % nvec;
+        if (b >= a.B) continue;
+        uint4* p = reinterpret_cast<uint4*>(xs + b * xstride + v * 16);
+        uint4 q = *p;
+        const uint4 wq = *reinterpret_cast<const uint4*>(a.norm_w + v * 8);
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+        const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wq);
+        const float r = rstd_s[b];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __bfloat1622float2(h[i]);
+          float2 w = __bfloat1622float2(wh[i]);
+          h[i] = __floats2bfloat162_rn(f.x * r * (w.x + a.norm_off), f.y * r * (w.y + a.norm_off));
+        }
+        *p = q;
+      }
+      __syncthreads();
+    }
+  }
+
+  const int kslice = K / WARPS;                         // multiple of 32
+  const int k_lo = warp * kslice;
+  const uint8_t* xrow = xs + g8 * xstride;
+
+  for (int grp = blockIdx.x; grp < a.n_groups; grp += gridDim.x) {
+    int rA, rB;
+    group_rows(a, grp, rA, rB);
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    if constexpr (!W4) {
+      const __nv_bfloat16* wA = reinterpret_cast<const __nv_bfloat16*>(a.w) + (long long)(rA + g8) * K + k_lo + t4 * 8;
+      const __nv_bfloat16* wB = reinterpret_cast<const __nv_bfloat16*>(a.w) + (long long)(rB + g8) * K + k_lo + t4 * 8;
+      const uint8_t* xp = xrow + (k_lo + t4 * 8) * 2;
+      int kb = 0;
+      for (; kb + 128 <= kslice; kb += 128) {           // 4 blocks of 32 k in flight: 8 x 16 B per lane
+        uint4 va[4], vb[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          va[u] = __ldcs(reinterpret_cast<const uint4*>(wA + kb + 32 * u));
+          vb[u] = __ldcs(reinterpret_cast<const uint4*>(wB + kb + 32 * u));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xp + (kb + 32 * u) * 2);
+          mma_bf16(c, va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
+          mma_bf16(c, va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
+        }
+      }
+      for (; kb < kslice; kb += 32) {
+        const uint4 va = __ldcs(reinterpret_cast<const uint4*>(wA + kb));
+        const uint4 vb = __ldcs(reinterpret_cast<const uint4*>(wB + kb));
+        const uint4 xv = *reinterpret_cast<const uint4*>(xp + kb * 2);
+        mma_bf16(c, va.x, vb.x, va.y, vb.y, xv.x, xv.y);
+        mma_bf16(c, va.z, vb.z, va.w, vb.w, xv.z, xv.w);
+      }
+    } else {
+      // 4-bit: a lane's 8 k values are one 32-bit word; one fp16 scale per 64 k per row
+      const uint32_t* wA = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.w) + (long long)(rA + g8) * (K / 2)) + (k_lo >> 3) + t4;
+      const uint32_t* wB = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.w) + (long long)(rB + g8) * (K / 2)) + (k_lo >> 3) + t4;
+      const __half* sA = a.scales + (long long)(rA + g8) * (K / 64) + (k_lo >> 6);
+      const __half* sB = a.scales + (long long)(rB + g8) * (K / 64) + (k_lo >> 6);
+      const uint8_t* xp = xrow + (k_lo + t4 * 8) * 2;
+      for (int kb = 0; kb < kslice; kb += 64) {          // kslice is a multiple of 64 for the 4-bit path
+        const uint32_t pa0 = __ldcs(wA + (kb >> 3)), pa1 = __ldcs(wA + (kb >> 3) + 4);
+        const uint32_t pb0 = __ldcs(wB + (kb >> 3)), pb1 = __ldcs(wB + (kb >> 3) + 4);
+        const float fa = __half2float(sA[kb >> 6]), fb = __half2float(sB[kb >> 6]);
+        const __nv_bfloat162 sa2 = __floats2bfloat162_rn(fa, fa), sb2 = __floats2bfloat162_rn(fb, fb);
+        const __nv_bfloat162 ba2 = __floats2bfloat162_rn(136.f, 136.f);
+        const __nv_bfloat162 bb2 = ba2;
+        uint32_t wa[4], wb[4];
+        dequant8(pa0, sa2, ba2, wa);
+        dequant8(pb0, sb2, bb2, wb);
+        uint4 xv = *reinterpret_cast<const uint4*>(xp + kb * 2);
+        mma_bf16(c, wa[0], wb[0], wa[1], wb[1], xv.x, xv.y);
+        mma_bf16(c, wa[2], wb[2], wa[3], wb[3], xv.z, xv.w);
+        dequant8(pa1, sa2, ba2, wa);
+        dequant8(pb1, sb2, bb2, wb);
+        xv = *reinterpret_cast<const uint4*>(xp + (kb + 32) * 2);
+        mma_bf16(c, wa[0], wb[0], wa[1], wb[1], xv.x, xv.y);
+        mma_bf16(c, wa[2], wb[2], wa[3], wb[3], xv.z, xv.w);
+      }
+    }
+    // ---- K-split reduction through shared memory: c0,c1 = (row g8, batch 2t,2t+1); c2,c3 = row g8+8
+    float* my = red + warp * 16 * NB;
+    my[g8 * NB + 2 * t4] = c[0];
+    my[g8 * NB + 2 * t4 + 1] = c[1];
+    my[(g8 + 8) * NB + 2 * t4] = c[2];
+    my[(g8 + 8) * NB + 2 * t4 + 1] = c[3];
+    __syncthreads();
+    if (threadIdx.x < 16 * NB) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) s += red[w * 16 * NB + threadIdx.x];
+      fin[threadIdx.x] = s;
+    }
+    __syncthreads();
+    // ---- epilogue: thread e = (row r of 16, batch n)
+    if (threadIdx.x < 16 * NB) {
+      const int r = threadIdx.x / NB, n = threadIdx.x % NB;
+      const float val = fin[threadIdx.x];
+      const int row = (r < 8) ? rA + r : rB + (r - 8);
+      if (a.mode == MESH_DEC_STORE) {
+        if (n < a.B) {
+          float val = fin[threadIdx.x];
+          if (a.residual) val += __bfloat162float(a.residual[(long long)n * a.ldr + row]);
+          if (a.out_f32) reinterpret_cast<float*>(a.out)[(long long)n * a.ldo + row] = val;
+          else reinterpret_cast<__nv_bfloat16*>(a.out)[(long long)n * a.ldo + row] = __float2bfloat16_rn(val);
+        }
+      } else if (a.mode == MESH_DEC_GLU) {
+        if (r < 8 && n < a.B) {
+          const float u = fin[(r + 8) * NB + n];
+          reinterpret_cast<__nv_bfloat16*>(a.out)[(long long)n * a.ldo + row] = __float2bfloat16_rn(dec_act(val, a.act) * u);
+        }
+      } else if (a.mode == MESH_DEC_QKV) {
+        if (r < 8 && n < a.B) {
+          const int hd = a.head_dim, half = hd / 2;
+          const int h = row / hd, i = row % hd;            // i < half
+          const float lo = val, hi = fin[(r + 8) * NB + n];
+          const int p = a.pos[n];
+          float o_lo = lo, o_hi = hi;
+          if (h < a.q_heads + a.kv_heads) {                  // q and k heads are rotated
+            const float cs = a.cos_t[(long long)p * half + i], sn = a.sin_t[(long long)p * half + i];
+            o_lo = lo * cs - hi * sn;
+            o_hi = hi * cs + lo * sn;
+          }
+          __nv_bfloat16* dst;
+          if (h < a.q_heads) {
+            dst = a.q_out + (long long)n * a.q_heads * hd + h * hd;
+          } else if (h < a.q_heads + a.kv_heads) {
+            dst = a.k_cache + (((long long)n * a.kv_heads + (h - a.q_heads)) * a.max_seq + p) * hd;
+          } else {
+            dst = a.v_cache + (((long long)n * a.kv_heads + (h - a.q_heads - a.kv_heads)) * a.max_seq + p) * hd;
+          }
+          dst[i] = __float2bfloat16_rn(o_lo);
+          dst[i + half] = __float2bfloat16_rn(o_hi);
+        }
+      } else {   // MESH_DEC_ALLREDUCE: one-shot sum over ranks of this row group, plus the residual
+        if (n < a.B) {
+          // the two halves of the slot array alternate call by call, so a fast peer's next
+          // reduction never lands on words a slow rank has not read yet
+          const uint32_t ar_seq = (a.step_ptr ? *a.step_ptr : 0u) * a.calls_per_step + a.call_index + 1u;
+          const long long per_src = (long long)a.n_groups * 16 * NB;
+          const long long slot = (long long)(ar_seq & 1u) * a.world * per_src + (long long)row * NB + n;
+          const uint2 word = make_uint2(__float_as_uint(val), ar_seq);
+          for (int d = 0; d < a.world; ++d) {
+            uint2* p = a.ar_recv[d] + (long long)a.rank * per_src + slot;
+            asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(word.x), "r"(word.y) : "memory");
+          }
+          float sum = 0.f;
+          bool ok = true;
+          for (int s = 0; s < a.world && ok; ++s) {
+            const uint2* p = a.ar_recv[a.rank] + (long long)s * per_src + slot;
+            uint2 w;
+            unsigned long long t0 = 0;
+            uint32_t it = 0;
+            while (true) {
+              asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
+              if (w.y == ar_seq) break;
+              if (((++it) & 0x3ffu) == 0) {
+                if (t0 == 0) t0 = globaltimer_ns();
+                else if (globaltimer_ns() - t0 > MESH_WAIT_LIMIT_NS || status_aborted(a.status)) {
+                  status_record(a.status, MESH_TIMEOUT, SITE_PEER_FLAG, ar_seq, w.y, (unsigned long long)p);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+            sum += __uint_as_float(w.x);
+          }
+          if (ok) {
+            if (a.residual) sum += __bfloat162float(a.residual[(long long)n * a.ldr + row]);
+            reinterpret_cast<__nv_bfloat16*>(a.out)[(long long)n * a.ldo + row] = __float2bfloat16_rn(sum);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace decode
+}  // namespace mesh
+
+using namespace mesh;
+using namespace mesh::decode;
+
+extern "C" int mesh_decode_linear(const MeshDecodeLinear* d, void* stream) {
+  if (d->B < 1 || d->B > NB) return set_error(-2, "decode_linear: batch must be 1..8");
+  if (d->K % 256) return set_error(-2, "decode_linear: K must be a multiple of 256");
+  if (d->w4 && d->K % 512) return set_error(-2, "decode_linear: 4-bit weights need K %% 512 == 0");
+  if (d->N % 16) return set_error(-2, "decode_linear: N must be a multiple of 16");
+  if (d->world > MESH_DEC_MAX_RANKS) return set_error(-4, "decode_linear: world too large");
+  LinArgs a;
+  memset(&a, 0, sizeof(a));
+  a.x = (const __nv_bfloat16*)d->x; a.ldx = d->ldx; a.B = d->B; a.K = d->K;
+  a.norm_w = (const __nv_bfloat16*)d->norm_w; a.eps = d->eps; a.norm_off = d->norm_off;
+  a.w = d->w; a.scales = (const __half*)d->scales;
+  a.n_groups = d->N / 16;
+  a.mode = d->mode; a.act = d->act; a.up_off = d->up_off;
+  a.out = d->out; a.ldo = d->ldo; a.out_f32 = d->out_f32;
+  a.q_heads = d->q_heads; a.kv_heads = d->kv_heads; a.head_dim = d->head_dim;
+  a.pos = d->pos; a.cos_t = d->cos_t; a.sin_t = d->sin_t;
+  a.q_out = (__nv_bfloat16*)d->q_out; a.k_cache = (__nv_bfloat16*)d->k_cache; a.v_cache = (__nv_bfloat16*)d->v_cache;
+  a.max_seq = d->max_seq;
+  a.rank = d->rank; a.world = d->world > 0 ? d->world : 1;
+  for (int r = 0; r < a.world; ++r) a.ar_recv[r] = (uint2*)d->ar_recv[r];
+  a.step_ptr = d->step_ptr; a.calls_per_step = d->calls_per_step; a.call_index = d->call_index;
+  a.residual = (const __nv_bfloat16*)d->residual; a.ldr = d->ldr;
+  a.status = (Status*)d->status;
+  if (d->mode == MESH_DEC_QKV) {
+    if (d->head_dim % 16 || (d->q_heads + 2 * d->kv_heads) * d->head_dim != d->N)
+      return set_error(-2, "decode_linear: qkv rows must equal (q_heads + 2 kv_heads) * head_dim");
+  }
+  if (d->mode == MESH_DEC_GLU) a.n_groups = d->N / 8;   // N = gate rows; every group pairs 8 gate + 8 up rows
+  const size_t smem = (size_t)NB * (d->K * 2 + XPAD) + (size_t)(WARPS + 1) * 16 * NB * sizeof(float);
+  if (smem > 220 * 1024) return set_error(-2, "decode_linear: K too large for shared memory");
+  auto kern = d->w4 ? decode_linear_kernel<1> : decode_linear_kernel<0>;
+  static bool configured[2] = {false, false};
+  if (!configured[d->w4 ? 1 : 0]) {
+    MESH_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    configured[d->w4 ? 1 : 0] = true;
+  }
+  int grid = a.n_groups;
+  const int cap = sm_count() * (smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4));
+  if (grid > cap) grid = cap;
+  kern<<<grid, THREADS, smem, (cudaStream_t)stream>>>(a);
+  MESH_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -35,6 +35,14 @@ class MeshContext:
         return self._heap
 
     @property
+    def comm(self):
+        """This context's Communicator (collective kernels over the heap), created on first use."""
+        if getattr(self, "_comm", None) is None:
+            from .comm import Communicator
+            self._comm = Communicator(self.heap)
+        return self._comm
+
+    @property
     def is_cuda(self) -> bool:
         return self.device.type == "cuda"
 

@@ -88,6 +88,8 @@ class ProcessGroupMesh(dist.ProcessGroup):
             ctx = current_or_none()
             if ctx is not None and ctx.world == self._world and ctx.rank == self._rank and ctx.is_cuda:
                 self._heap = ctx.heap
+                self._comm = ctx.comm
+                return self._comm
             else:
                 rdv = Rendezvous(dist.PrefixStore("mesh-heap", self._store), self._rank, self._world,
                                  timeout_s=self._timeout.total_seconds())

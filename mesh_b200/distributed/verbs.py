@@ -16,21 +16,13 @@ from .context import current_or_none
 
 _RED = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN, "prod": dist.ReduceOp.PRODUCT,
         "avg": dist.ReduceOp.AVG}
-_comm = None
-
 
 def _communicator(t: torch.Tensor):
     """The mesh Communicator for CUDA tensors of a process that called ``mesh_b200.distributed.init``."""
-    global _comm
     ctx = current_or_none()
-    if ctx is None or not t.is_cuda or ctx.world == 1 and False:
+    if ctx is None or not t.is_cuda or not ctx.is_cuda:
         return None
-    if not ctx.is_cuda:
-        return None
-    if _comm is None or _comm.heap is not ctx.heap:
-        from .comm import Communicator
-        _comm = Communicator(ctx.heap)
-    return _comm
+    return ctx.comm
 
 
 def world_size(group=None) -> int:
