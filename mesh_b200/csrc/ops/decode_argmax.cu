@@ -6,6 +6,7 @@
 #include "decode_api.h"
 #include "../device/ptx.cuh"
 #include "../runtime/host_common.h"
+#include <cstring>
 
 namespace mesh {
 namespace {
@@ -17,6 +18,8 @@ decode_argmax_kernel(const float* __restrict__ logits, long long ldl, int vocab_
                      int* __restrict__ tokens_out, int* __restrict__ pos, int rank, int world,
                      uint2* const* __restrict__ xchg_unused, uint2* x0, uint2* x1, uint2* x2, uint2* x3, uint2* x4,
                      uint2* x5, uint2* x6, uint2* x7, uint32_t* step, Status* st) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int b = blockIdx.x;
   const uint32_t seq = (step ? *step : 0u) + 1u;
   const float* row = logits + (long long)b * ldl;
@@ -110,9 +113,18 @@ extern "C" int mesh_decode_argmax(const float* logits, long long ldl, int B, int
   if (world < 1 || world > 8) return set_error(-4, "decode_argmax: world out of range");
   uint2* x[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   for (int r = 0; r < world && xchg; ++r) x[r] = (uint2*)xchg[r];
-  decode_argmax_kernel<<<B, AM_THREADS, 0, (cudaStream_t)stream>>>(logits, ldl, vocab_local, vocab_offset, tokens_out, pos,
-                                                                  rank, world, nullptr, x[0], x[1], x[2], x[3], x[4],
-                                                                  x[5], x[6], x[7], step, (Status*)status);
-  MESH_CUDA_OK(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)B);
+  cfg.blockDim = dim3(AM_THREADS);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  uint2* const* none = nullptr;
+  MESH_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_argmax_kernel, logits, ldl, vocab_local, vocab_offset, tokens_out, pos, rank,
+                                  world, none, x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], step, (Status*)status));
   return 0;
 }

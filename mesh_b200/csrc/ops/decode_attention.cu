@@ -10,6 +10,7 @@
 #include <math_constants.h>
 #include "decode_api.h"
 #include "../runtime/host_common.h"
+#include <cstring>
 
 namespace mesh {
 namespace {
@@ -28,6 +29,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         __nv_bfloat16* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
                         int q_heads, int kv_heads, int max_seq, int window, float scale, int splits, int T) {
   constexpr int PER = HD / 32;                       // dims per lane
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // q and the newest cache row come from the previous kernel
   // b indexes (sequence, query token); the cache belongs to the sequence
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int seq_idx = b / T;
@@ -140,24 +143,37 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int g = 0; g < group; ++g) {
-    const float* pg = scratch + (((long long)b * q_heads + kvh * group + g) * splits) * (HD + 2);
+  // weights of every (head, split) first — 64 independent loads at most — then the value sums
+  // run over independent loads too (no load -> branch -> load chains through L2)
+  __shared__ float w_s[MAX_GROUP][64];
+  __shared__ float inv_s[MAX_GROUP];
+  const float* pbase = scratch + (((long long)b * q_heads + kvh * group) * splits) * (HD + 2);
+  for (int idx = threadIdx.x; idx < group * splits; idx += ATT_THREADS) {
+    const int g = idx / splits, s = idx % splits;
+    w_s[g][s] = __ldcg(pbase + ((long long)g * splits + s) * (HD + 2) + HD);          // m of the split
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < group) {
+    const int g = threadIdx.x;
     float mm = -CUDART_INF_F;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, __ldcg(pg + (long long)s * (HD + 2) + HD));
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, w_s[g][s]);
     float ll = 0.f;
     for (int s = 0; s < splits; ++s) {
-      const float ms = __ldcg(pg + (long long)s * (HD + 2) + HD);
-      if (ms != -CUDART_INF_F) ll += __ldcg(pg + (long long)s * (HD + 2) + HD + 1) * __expf(ms - mm);
+      const float ms = w_s[g][s];
+      const float wgt = (ms == -CUDART_INF_F) ? 0.f : __expf(ms - mm);
+      ll += wgt * __ldcg(pbase + ((long long)g * splits + s) * (HD + 2) + HD + 1);
+      w_s[g][s] = wgt;
     }
-    const float inv = ll > 0.f ? 1.f / ll : 0.f;
-    for (int d = threadIdx.x; d < HD; d += ATT_THREADS) {
-      float a = 0.f;
-      for (int s = 0; s < splits; ++s) {
-        const float ms = __ldcg(pg + (long long)s * (HD + 2) + HD);
-        if (ms != -CUDART_INF_F) a += __ldcg(pg + (long long)s * (HD + 2) + d) * __expf(ms - mm);
-      }
-      out[((long long)b * q_heads + kvh * group + g) * HD + d] = __float2bfloat16_rn(a * inv);
-    }
+    inv_s[g] = ll > 0.f ? 1.f / ll : 0.f;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < group * HD; idx += ATT_THREADS) {
+    const int g = idx / HD, d = idx % HD;
+    const float* pg = pbase + (long long)g * splits * (HD + 2) + d;
+    float a = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) a += __ldcg(pg + (long long)s * (HD + 2)) * w_s[g][s];
+    out[((long long)b * q_heads + kvh * group + g) * HD + d] = __float2bfloat16_rn(a * inv_s[g]);
   }
 }
 
@@ -178,14 +194,25 @@ extern "C" int mesh_decode_attention(const void* q, const void* k_cache, const v
   if (tokens_per_seq < 1) tokens_per_seq = 1;
   dim3 grid(splits, kv_heads, B * tokens_per_seq);
   const size_t smem = (size_t)ATT_WARPS * (q_heads / kv_heads) * head_dim * sizeof(float);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.blockDim = dim3(ATT_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
 #define LAUNCH(HD)                                                                                          \
   if (smem > 48 * 1024) {                                                                                   \
     static bool cfg = false;                                                                                \
     if (!cfg) { MESH_CUDA_OK(cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)); cfg = true; } \
   }                                                                                                         \
-  decode_attention_kernel<HD><<<grid, ATT_THREADS, smem, (cudaStream_t)stream>>>(                          \
+  cfg.gridDim = grid;                                                                                       \
+  MESH_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_attention_kernel<HD>,                                        \
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, pos,         \
-      (__nv_bfloat16*)out, scratch, counters, q_heads, kv_heads, max_seq, window, scale, splits, tokens_per_seq)
+      (__nv_bfloat16*)out, scratch, counters, q_heads, kv_heads, max_seq, window, scale, splits, tokens_per_seq))
   if (head_dim == 256) { LAUNCH(256); }
   else if (head_dim == 128) { LAUNCH(128); }
   else if (head_dim == 64) { LAUNCH(64); }

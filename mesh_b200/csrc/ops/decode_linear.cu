@@ -21,6 +21,7 @@
 #include "decode_api.h"
 #include "../device/ptx.cuh"
 #include "../runtime/host_common.h"
+#include <cstring>
 
 namespace mesh {
 namespace decode {
@@ -96,7 +97,79 @@ __device__ __forceinline__ void group_rows(const LinArgs& a, int g, int& rA, int
   }
 }
 
-template <int W4>
+// One pipeline step = one chunk of CH k-values of one 16-row group for this warp's K slice.
+// bf16: CH = 32*U (U 16-byte loads per row); 4-bit: CH = 64*U (U pairs of 32-bit words per row).
+template <int W4, int U>
+struct Chunk {
+  uint4 a[W4 ? (U + 1) / 2 : U];      // bf16: U x 16 B of row A;  4-bit: U x {word0, word1} packed two per uint4
+  uint4 b[W4 ? (U + 1) / 2 : U];
+  float sa[W4 ? U : 1], sb[W4 ? U : 1];
+};
+
+template <int W4, int U>
+__device__ __forceinline__ void load_chunk(const LinArgs& a, int grp, int kb, int k_lo, int g8, int t4, Chunk<W4, U>& c) {
+  int rA, rB;
+  group_rows(a, grp, rA, rB);
+  const int K = a.K;
+  if constexpr (!W4) {
+    const __nv_bfloat16* wA = reinterpret_cast<const __nv_bfloat16*>(a.w) + (long long)(rA + g8) * K + k_lo + kb + t4 * 8;
+    const __nv_bfloat16* wB = reinterpret_cast<const __nv_bfloat16*>(a.w) + (long long)(rB + g8) * K + k_lo + kb + t4 * 8;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      c.a[u] = __ldcs(reinterpret_cast<const uint4*>(wA + 32 * u));
+      c.b[u] = __ldcs(reinterpret_cast<const uint4*>(wB + 32 * u));
+    }
+  } else {
+    const uint32_t* wA = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.w) + (long long)(rA + g8) * (K / 2)) + ((k_lo + kb) >> 3) + t4;
+    const uint32_t* wB = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.w) + (long long)(rB + g8) * (K / 2)) + ((k_lo + kb) >> 3) + t4;
+    const __half* sA = a.scales + (long long)(rA + g8) * (K / 64) + ((k_lo + kb) >> 6);
+    const __half* sB = a.scales + (long long)(rB + g8) * (K / 64) + ((k_lo + kb) >> 6);
+    uint32_t* pa = reinterpret_cast<uint32_t*>(c.a);
+    uint32_t* pb = reinterpret_cast<uint32_t*>(c.b);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      pa[2 * u] = __ldcs(wA + 8 * u);
+      pa[2 * u + 1] = __ldcs(wA + 8 * u + 4);
+      pb[2 * u] = __ldcs(wB + 8 * u);
+      pb[2 * u + 1] = __ldcs(wB + 8 * u + 4);
+      c.sa[u] = __half2float(sA[u]);
+      c.sb[u] = __half2float(sB[u]);
+    }
+  }
+}
+
+template <int W4, int U>
+__device__ __forceinline__ void mma_chunk(const Chunk<W4, U>& c, const uint8_t* xp, float (&acc)[4]) {
+  if constexpr (!W4) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(xp + 64 * u);
+      mma_bf16(acc, c.a[u].x, c.b[u].x, c.a[u].y, c.b[u].y, xv.x, xv.y);
+      mma_bf16(acc, c.a[u].z, c.b[u].z, c.a[u].w, c.b[u].w, xv.z, xv.w);
+    }
+  } else {
+    const uint32_t* pa = reinterpret_cast<const uint32_t*>(c.a);
+    const uint32_t* pb = reinterpret_cast<const uint32_t*>(c.b);
+    const __nv_bfloat162 off = __floats2bfloat162_rn(136.f, 136.f);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const __nv_bfloat162 sa2 = __floats2bfloat162_rn(c.sa[u], c.sa[u]), sb2 = __floats2bfloat162_rn(c.sb[u], c.sb[u]);
+      uint32_t wa[4], wb[4];
+      dequant8(pa[2 * u], sa2, off, wa);
+      dequant8(pb[2 * u], sb2, off, wb);
+      uint4 xv = *reinterpret_cast<const uint4*>(xp + 128 * u);
+      mma_bf16(acc, wa[0], wb[0], wa[1], wb[1], xv.x, xv.y);
+      mma_bf16(acc, wa[2], wb[2], wa[3], wb[3], xv.z, xv.w);
+      dequant8(pa[2 * u + 1], sa2, off, wa);
+      dequant8(pb[2 * u + 1], sb2, off, wb);
+      xv = *reinterpret_cast<const uint4*>(xp + 128 * u + 64);
+      mma_bf16(acc, wa[0], wb[0], wa[1], wb[1], xv.x, xv.y);
+      mma_bf16(acc, wa[2], wb[2], wa[3], wb[3], xv.z, xv.w);
+    }
+  }
+}
+
+template <int W4, int U>
 __global__ void __launch_bounds__(THREADS) decode_linear_kernel(const LinArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int K = a.K;
@@ -107,6 +180,19 @@ __global__ void __launch_bounds__(THREADS) decode_linear_kernel(const LinArgs a)
   __shared__ float rstd_s[NB];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g8 = lane >> 2, t4 = lane & 3;
+  constexpr int CH = (W4 ? 64 : 32) * U;
+  const int kslice = K / WARPS;
+  const int k_lo = warp * kslice;
+  const int chunks = kslice / CH;
+  const int my_groups = (a.n_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int steps = my_groups * chunks;
+
+  // Let the next kernel of the stream start its own weight prefetch now; the weights of this
+  // kernel do not depend on the previous one, so the first chunk is requested before waiting for it.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  Chunk<W4, U> c0, c1;
+  if (steps > 0) load_chunk<W4, U>(a, blockIdx.x, 0, k_lo, g8, t4, c0);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // ---- prologue: x (zero rows past the batch) -> shared memory, optionally RMS-normalised
   {
@@ -155,67 +241,24 @@ __global__ void __launch_bounds__(THREADS) decode_linear_kernel(const LinArgs a)
     }
   }
 
-  const int kslice = K / WARPS;                         // multiple of 32
-  const int k_lo = warp * kslice;
-  const uint8_t* xrow = xs + g8 * xstride;
+  const uint8_t* xbase = xs + g8 * xstride + (k_lo + t4 * 8) * 2;
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
 
-  for (int grp = blockIdx.x; grp < a.n_groups; grp += gridDim.x) {
+  // Two register sets alternate: while one chunk feeds the tensor cores the next one is in flight,
+  // across group boundaries too, so the stream of weight loads never drains.
+  for (int step = 0; step < steps; ++step) {
+    const int gi = step / chunks, ci = step - gi * chunks;
+    const int grp = blockIdx.x + gi * gridDim.x;
+    if (step + 1 < steps) {
+      const int gn = (step + 1) / chunks, cn = (step + 1) - gn * chunks;
+      if (step & 1) load_chunk<W4, U>(a, blockIdx.x + gn * gridDim.x, cn * CH, k_lo, g8, t4, c0);
+      else          load_chunk<W4, U>(a, blockIdx.x + gn * gridDim.x, cn * CH, k_lo, g8, t4, c1);
+    }
+    if (step & 1) mma_chunk<W4, U>(c1, xbase + ci * CH * 2, c);
+    else          mma_chunk<W4, U>(c0, xbase + ci * CH * 2, c);
+    if (ci != chunks - 1) continue;
     int rA, rB;
     group_rows(a, grp, rA, rB);
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
-    if constexpr (!W4) {
-      const __nv_bfloat16* wA = reinterpret_cast<const __nv_bfloat16*>(a.w) + (long long)(rA + g8) * K + k_lo + t4 * 8;
-      const __nv_bfloat16* wB = reinterpret_cast<const __nv_bfloat16*>(a.w) + (long long)(rB + g8) * K + k_lo + t4 * 8;
-      const uint8_t* xp = xrow + (k_lo + t4 * 8) * 2;
-      int kb = 0;
-      for (; kb + 128 <= kslice; kb += 128) {           // 4 blocks of 32 k in flight: 8 x 16 B per lane
-        uint4 va[4], vb[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          va[u] = __ldcs(reinterpret_cast<const uint4*>(wA + kb + 32 * u));
-          vb[u] = __ldcs(reinterpret_cast<const uint4*>(wB + kb + 32 * u));
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const uint4 xv = *reinterpret_cast<const uint4*>(xp + (kb + 32 * u) * 2);
-          mma_bf16(c, va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
-          mma_bf16(c, va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
-        }
-      }
-      for (; kb < kslice; kb += 32) {
-        const uint4 va = __ldcs(reinterpret_cast<const uint4*>(wA + kb));
-        const uint4 vb = __ldcs(reinterpret_cast<const uint4*>(wB + kb));
-        const uint4 xv = *reinterpret_cast<const uint4*>(xp + kb * 2);
-        mma_bf16(c, va.x, vb.x, va.y, vb.y, xv.x, xv.y);
-        mma_bf16(c, va.z, vb.z, va.w, vb.w, xv.z, xv.w);
-      }
-    } else {
-      // 4-bit: a lane's 8 k values are one 32-bit word; one fp16 scale per 64 k per row
-      const uint32_t* wA = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.w) + (long long)(rA + g8) * (K / 2)) + (k_lo >> 3) + t4;
-      const uint32_t* wB = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.w) + (long long)(rB + g8) * (K / 2)) + (k_lo >> 3) + t4;
-      const __half* sA = a.scales + (long long)(rA + g8) * (K / 64) + (k_lo >> 6);
-      const __half* sB = a.scales + (long long)(rB + g8) * (K / 64) + (k_lo >> 6);
-      const uint8_t* xp = xrow + (k_lo + t4 * 8) * 2;
-      for (int kb = 0; kb < kslice; kb += 64) {          // kslice is a multiple of 64 for the 4-bit path
-        const uint32_t pa0 = __ldcs(wA + (kb >> 3)), pa1 = __ldcs(wA + (kb >> 3) + 4);
-        const uint32_t pb0 = __ldcs(wB + (kb >> 3)), pb1 = __ldcs(wB + (kb >> 3) + 4);
-        const float fa = __half2float(sA[kb >> 6]), fb = __half2float(sB[kb >> 6]);
-        const __nv_bfloat162 sa2 = __floats2bfloat162_rn(fa, fa), sb2 = __floats2bfloat162_rn(fb, fb);
-        const __nv_bfloat162 ba2 = __floats2bfloat162_rn(136.f, 136.f);
-        const __nv_bfloat162 bb2 = ba2;
-        uint32_t wa[4], wb[4];
-        dequant8(pa0, sa2, ba2, wa);
-        dequant8(pb0, sb2, bb2, wb);
-        uint4 xv = *reinterpret_cast<const uint4*>(xp + kb * 2);
-        mma_bf16(c, wa[0], wb[0], wa[1], wb[1], xv.x, xv.y);
-        mma_bf16(c, wa[2], wb[2], wa[3], wb[3], xv.z, xv.w);
-        dequant8(pa1, sa2, ba2, wa);
-        dequant8(pb1, sb2, bb2, wb);
-        xv = *reinterpret_cast<const uint4*>(xp + (kb + 32) * 2);
-        mma_bf16(c, wa[0], wb[0], wa[1], wb[1], xv.x, xv.y);
-        mma_bf16(c, wa[2], wb[2], wa[3], wb[3], xv.z, xv.w);
-      }
-    }
     // ---- K-split reduction through shared memory: c0,c1 = (row g8, batch 2t,2t+1); c2,c3 = row g8+8
     float* my = red + warp * 16 * NB;
     my[g8 * NB + 2 * t4] = c[0];
@@ -311,6 +354,7 @@ __global__ void __launch_bounds__(THREADS) decode_linear_kernel(const LinArgs a)
       }
     }
     __syncthreads();
+    c[0] = c[1] = c[2] = c[3] = 0.f;
   }
 }
 
@@ -350,16 +394,35 @@ extern "C" int mesh_decode_linear(const MeshDecodeLinear* d, void* stream) {
   if (d->mode == MESH_DEC_GLU) a.n_groups = d->N / 8;   // N = gate rows; every group pairs 8 gate + 8 up rows
   const size_t smem = (size_t)NB * (d->K * 2 + XPAD) + (size_t)(WARPS + 1) * 16 * NB * sizeof(float);
   if (smem > 220 * 1024) return set_error(-2, "decode_linear: K too large for shared memory");
-  auto kern = d->w4 ? decode_linear_kernel<1> : decode_linear_kernel<0>;
-  static bool configured[2] = {false, false};
-  if (!configured[d->w4 ? 1 : 0]) {
+  const int kslice = d->K / WARPS;
+  // chunk width: 128 k per step when the slice allows it (4 x 16 B per row in flight, twice), else one block
+  const bool wide = d->w4 ? (kslice % 128 == 0) : (kslice % 128 == 0);
+  void (*kern)(const LinArgs) = nullptr;
+  int slot = 0;
+  if (d->w4) { kern = wide ? decode_linear_kernel<1, 2> : decode_linear_kernel<1, 1>; slot = wide ? 0 : 1; }
+  else       { kern = wide ? decode_linear_kernel<0, 4> : decode_linear_kernel<0, 1>; slot = wide ? 2 : 3; }
+  static bool configured[4] = {false, false, false, false};
+  if (!configured[slot]) {
     MESH_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    configured[d->w4 ? 1 : 0] = true;
+    configured[slot] = true;
   }
   int grid = a.n_groups;
-  const int cap = sm_count() * (smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4));
+  // at most two CTAs per SM: fewer, longer-lived CTAs amortise the x prologue and keep the weight
+  // pipeline full across group boundaries
+  const int cap = sm_count() * (smem > 100 * 1024 ? 1 : 2);
   if (grid > cap) grid = cap;
-  kern<<<grid, THREADS, smem, (cudaStream_t)stream>>>(a);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MESH_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, a));
   MESH_CUDA_OK(cudaGetLastError());
   return 0;
 }

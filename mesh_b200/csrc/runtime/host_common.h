@@ -17,6 +17,8 @@ bool encode_tiled(CUtensorMap* tm, CUtensorMapDataType dtype, int rank, const vo
                   const cuuint32_t* elem_strides, CUtensorMapSwizzle swizzle);
 
 int sm_count();
+// Programmatic dependent launch between consecutive kernels of a stream (MESH_PDL=0 switches it off).
+bool pdl_enabled();
 
 #define MESH_CUDA_OK(expr)                                                              \
   do {                                                                                  \

@@ -59,6 +59,20 @@ def main() -> None:
         logits = torch.randn(a.m * 64, 64, device=dev)
         for _ in range(a.iters):
             router_topk(logits, 6)
+    elif a.op == "e2b_decode":
+        # solo E2B-class decoder: short prefill, then `iters` eager decode steps (152 launches each)
+        import torch.distributed as dist
+        from mesh_b200.distributed.context import MeshContext
+        from mesh_b200.models.e2b import E2BConfig, E2BDecoder
+        from mesh_b200.runtime.rendezvous import Rendezvous
+        ctx = MeshContext(0, 1, torch.device("cuda", 0), Rendezvous(dist.HashStore(), 0, 1), None)
+        m = E2BDecoder(E2BConfig(), ctx, a.m if a.m <= 8 else 1, "w4" if a.n == 4 else "bf16")
+        prompt = torch.randint(0, 262144, (m.B, 64), dtype=torch.int32, device=dev)
+        m.prefill(prompt)
+        m.pos.fill_(600)
+        torch.cuda.synchronize()
+        for _ in range(a.iters):
+            m._decode_step()
     else:
         raise SystemExit(f"unknown op {a.op}")
     check_status()
