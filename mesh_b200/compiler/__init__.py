@@ -1,0 +1,5 @@
+"""GSPMD-style sharding compiler: capture -> place -> schedule -> Program (+ archive, shares)."""
+from .driver import compile_module, compile_program, compiled  # noqa: F401
+from .ir import TrainingResult, send, recv  # noqa: F401
+from .placement import counts  # noqa: F401
+from .runtime import Program  # noqa: F401

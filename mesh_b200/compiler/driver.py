@@ -1,0 +1,49 @@
+"""Pipeline driver: capture -> place -> schedule -> ``Scheduled`` (compiler/mesh_compiler/driver.py:22-120).
+
+    scheduled = compile_module(module, args, processors, placement, loss=0)
+    result = Program(scheduled)(*args)
+
+``processors``: ``{name: (machine, device)}`` in rank order (``device`` = ``"cuda:i"`` or ``"cpu"``);
+``placement``: the callable contract of :mod:`mesh_b200.compiler.placement`; ``mesh``: optional grid shape
+for N-D placements.  Compilation is host-only and deterministic: every rank derives the same plan from
+the same inputs, so nothing needs to be exchanged.
+"""
+from __future__ import annotations
+
+from . import export as _export
+from .ir import Scheduled
+from .placement import place
+from .schedule import schedule, unit_cost
+
+
+def compile_captured(exported, processors, placement, cost=unit_cost, mesh=None) -> Scheduled:
+    plan = place(exported, processors, placement, mesh)
+    sig, structure = schedule(plan, cost)
+    stated = {}
+    for node in exported.graph_module.graph.nodes:
+        if node.op == "placeholder":
+            stated[node.name] = repr(plan.input_specs.get(node.name))
+    names = list(processors)
+    return Scheduled(exported, plan, dict(processors), stated, sig, structure, output_processor=names[0], cost=None)
+
+
+def compile_module(module, args, processors, placement, cost=unit_cost, planning=None, machine=None, mesh=None,
+                   kwargs=None, **export_options) -> Scheduled:
+    """Ahead-of-time compile of one module call.  ``loss=<flat output index>`` compiles forward+backward."""
+    exported = _export.export(module, args, kwargs, **export_options)
+    return compile_captured(exported, processors, placement, cost, mesh)
+
+
+def compile_program(program, args, functions, processors, placement, cost=unit_cost, planning=None, machine=None,
+                    mesh=None, **export_options) -> Scheduled:
+    """A program whose ``forward`` only calls the named ``functions`` (compiled once, called many times)."""
+    exported, calls = _export.calls(program, args, functions, **export_options)
+    sch = compile_captured(exported, processors, placement, cost, mesh)
+    sch.structure["function_calls"] = calls
+    return sch
+
+
+def compiled(scheduled: Scheduled) -> Scheduled:
+    """Attach (recompute) the synchronisation signature (driver.py:118 of the reference)."""
+    scheduled.signature, scheduled.structure = schedule(scheduled.plan)
+    return scheduled

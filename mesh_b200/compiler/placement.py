@@ -1,0 +1,698 @@
+"""GSPMD-style sharding propagation and collective insertion.
+
+The caller states placements with a callable ``placement(node) -> None | str | (dimension, processors, units)``
+called for every node (compiler/mesh_compiler/placement.py:837-864):
+
+* ``str``: the value lives whole on that processor;
+* ``(dimension, processors, units)``: sharded along ``dimension`` over ``processors``; ``units`` is ``None``
+  (``torch.chunk`` sizes), a tuple of ratios (unequal shards, nearest integers with least-error +-1 repair and
+  optional bounds), a tuple of P+1 edges, or ``"striped"`` (processor j holds elements j, j+P, ...);
+* tuples for ``dimension`` / nested tuples for ``processors``: one entry per axis of an N-D mesh.
+
+Unstated nodes inherit through per-op rules; a contraction over a sharded dimension leaves a *partial*
+value that is reduced where a replicated or sharded value is needed (all-reduce / reduce-scatter);
+mismatches are resharded: sharded->replicated = all-gather (kind ``broadcast``), dim a -> dim b =
+all-to-all (``alltoall``), partial -> * = ``reduce``, owner -> owner = ``permute``
+(placement.py:250-340, :812-834).  A rule miss is never an error: the inputs are gathered and the op
+runs replicated (placement.py:656-657).  Replicated constants (masks, aranges) are *sliced locally*
+when they meet a sharded value, so a causal mask follows a striped or unequal sequence split with no
+special case.
+"""
+from __future__ import annotations
+
+import math
+import operator
+from typing import Any, Callable
+
+import torch
+
+from .ir import JOIN, PAGES, Mesh, O, P, Plan, R, Ref, S, Spec, Step, Transfer
+
+aten = torch.ops.aten
+
+
+# ----------------------------------------------------------------------------- shard sizes
+def counts(n: int, units=None, parts: int = 1, lower=None, upper=None) -> list[int]:
+    """Sizes of ``parts`` shards of ``n`` elements (reference: placement.py:65-87).
+
+    ``units is None``: ``torch.chunk`` sizes (``ceil(n / parts)``, trailing shards may be empty);
+    ``"striped"``: shard j gets ``ceil((n - j) / parts)``; ``parts`` ratios: nearest integers, then +-1 on the
+    shard whose size moves closest to its exact share until the sizes sum to ``n`` (within bounds);
+    ``parts + 1`` values: explicit edges.
+    """
+    if units is None:
+        step = -(-n // parts)
+        return [max(0, min(step, n - j * step)) for j in range(parts)]
+    if isinstance(units, str):
+        if units != "striped":
+            raise ValueError(f"unknown units {units!r}")
+        return [max(0, -(-(n - j) // parts)) for j in range(parts)]
+    units = list(units)
+    if len(units) == parts + 1:
+        return [int(units[j + 1] - units[j]) for j in range(parts)]
+    if len(units) != parts:
+        raise ValueError(f"{len(units)} units for {parts} processors")
+    total = float(sum(units))
+    exact = [n * u / total for u in units]
+    lo = [0] * parts if lower is None else list(lower)
+    hi = [n] * parts if upper is None else list(upper)
+    sizes = [int(min(max(round(e), l), h)) for e, l, h in zip(exact, lo, hi)]
+    while sum(sizes) != n:
+        step = 1 if sum(sizes) < n else -1
+        best, best_err = None, None
+        for j in range(parts):
+            new = sizes[j] + step
+            if new < lo[j] or new > hi[j]:
+                continue
+            err = abs(new - exact[j])
+            if best is None or err < best_err:
+                best, best_err = j, err
+        if best is None:
+            raise ValueError("bounds make the shard sizes infeasible")
+        sizes[best] += step
+    return sizes
+
+
+def striped_place(j: int, r: int, c: list[int]) -> int:
+    """Global index of the j-th element held by rank r under striping with per-rank counts ``c``
+    (compiler/mesh_compiler/operations.py:59-62); equal counts reduce to ``P*j + r``."""
+    cr = c[r]
+    return j + sum(((2 * j + 1) * co + cr - (1 if o > r else 0)) // (2 * cr) for o, co in enumerate(c) if o != r)
+
+
+def local_indices(spec: Spec, coord: int, n: int) -> slice | list[int]:
+    """Which elements of a dimension of size ``n`` the processor at ``coord`` holds."""
+    if spec.striped:
+        if len(set(spec.counts)) == 1 or all(cnt in (spec.counts[0], spec.counts[0] - 1) for cnt in spec.counts):
+            return slice(coord, n, len(spec.counts))
+        return [striped_place(j, coord, list(spec.counts)) for j in range(spec.counts[coord])]
+    start = sum(spec.counts[:coord])
+    return slice(start, start + spec.counts[coord])
+
+
+# ----------------------------------------------------------------------------- op classes
+POINTWISE = {
+    aten.add.Tensor, aten.sub.Tensor, aten.mul.Tensor, aten.div.Tensor, aten.pow.Tensor_Scalar, aten.pow.Tensor_Tensor,
+    aten.rsqrt.default, aten.sqrt.default, aten.sigmoid.default, aten.silu.default, aten.gelu.default, aten.tanh.default,
+    aten.exp.default, aten.log.default, aten.neg.default, aten.abs.default, aten.reciprocal.default, aten.relu.default,
+    aten.where.self, aten.eq.Scalar, aten.eq.Tensor, aten.ne.Scalar, aten.le.Scalar, aten.lt.Scalar, aten.ge.Scalar,
+    aten.gt.Scalar, aten.le.Tensor, aten.lt.Tensor, aten.ge.Tensor, aten.gt.Tensor, aten.logical_and.default,
+    aten.logical_or.default, aten.logical_not.default, aten.maximum.default, aten.minimum.default, aten._to_copy.default,
+    aten.clone.default, aten.alias.default, aten.mul.Scalar, aten.div.Scalar, aten.add.Scalar, aten.sub.Scalar,
+    aten.erf.default, aten.masked_fill.Scalar, aten.masked_fill.Tensor, aten.sigmoid_backward.default,
+    aten.tanh_backward.default, aten.silu_backward.default, aten.gelu_backward.default, aten.threshold_backward.default,
+    aten.clamp.default, aten.clamp_min.default, aten.clamp_max.default, aten.rsub.Scalar, aten.cos.default,
+    aten.sin.default, aten.bitwise_and.Tensor, aten.bitwise_or.Tensor, aten.bitwise_not.default, aten.fill.Scalar,
+    aten.zeros_like.default, aten.ones_like.default, aten.full_like.default, aten.detach.default, aten.square.default,
+    aten.exp2.default, aten.log2.default, aten.softplus.default, aten.hardtanh.default, aten.leaky_relu.default,
+    aten.native_dropout_backward.default, aten.sign.default, aten.floor.default, aten.ceil.default, aten.round.default,
+    aten.remainder.Scalar, aten.fmod.Scalar, aten.isnan.default, aten.isinf.default, aten.nan_to_num.default,
+    aten.lift_fresh_copy.default, aten.contiguous.default if hasattr(aten, "contiguous") else aten.clone.default,
+}
+# ops that stay "partial" when exactly the listed argument positions are partial and the rest replicated/scalars
+LINEAR_IN = {
+    aten.add.Tensor: "all", aten.sub.Tensor: "all", aten.neg.default: "all", aten.clone.default: "all",
+    aten.alias.default: "all", aten._to_copy.default: "all", aten.detach.default: "all",
+    aten.mul.Tensor: "one", aten.div.Tensor: "first", aten.mul.Scalar: "all", aten.div.Scalar: "all",
+}
+CREATION = {aten.full.default, aten.zeros.default, aten.ones.default, aten.arange.start_step, aten.arange.default,
+            aten.arange.start, aten.scalar_tensor.default, aten.empty.memory_format, aten.new_zeros.default,
+            aten.new_ones.default, aten.new_full.default, aten.new_empty.default, aten.tril_indices.default,
+            aten.eye.default, aten.linspace.default}
+REDUCTIONS = {aten.sum.dim_IntList: "sum", aten.sum.default: "sum", aten.mean.dim: "mean", aten.mean.default: "mean",
+              aten.amax.default: "max", aten.amin.default: "min", aten.any.dim: "max", aten.any.default: "max",
+              aten.all.dim: "min", aten.all.default: "min", aten.max.default: "max", aten.min.default: "min"}
+SOFTMAX_LIKE = {aten._softmax.default: 1, aten._log_softmax.default: 1, aten._softmax_backward_data.default: 2,
+                aten._log_softmax_backward_data.default: 2, aten.cumsum.default: 1, aten.argmax.default: 1,
+                aten.topk.default: 2, aten.sort.default: 1, aten.logsumexp.default: 1}
+
+
+def _shape(node) -> tuple:
+    v = node.meta.get("val")
+    return tuple(v.shape) if isinstance(v, torch.Tensor) else ()
+
+
+def _is_tensor_node(a) -> bool:
+    return isinstance(a, torch.fx.Node) and isinstance(a.meta.get("val"), torch.Tensor)
+
+
+class Propagator:
+    """Walks the exported graph once; emits the SPMD plan."""
+
+    def __init__(self, gm: torch.fx.GraphModule, mesh: Mesh, stated: dict, outputs_stated: dict | None = None):
+        self.gm, self.mesh = gm, mesh
+        self.na = len(mesh.shape)
+        self.stated = stated                       # node name -> tuple[Spec] per axis
+        self.spec: dict[str, tuple] = {}           # value name -> tuple[Spec]
+        self.shape: dict[str, tuple] = {}
+        self.dtype: dict[str, torch.dtype] = {}
+        self.steps: list[Step] = []
+        self.transfers: list[Transfer] = []
+        self.tmp = 0
+        self.channel = 0
+        self.renamed: dict[str, str] = {}         # node name -> value that carries it after a stated reshard
+
+    # ---- helpers
+    def fresh(self, base: str) -> str:
+        self.tmp += 1
+        return f"{base}__r{self.tmp}"
+
+    def all_r(self) -> tuple:
+        return tuple(R for _ in range(self.na))
+
+    def emit_collective(self, verb: str, kind: str, axis: int, src: str, spec_from: Spec, spec_to: Spec, consumer=JOIN) -> str:
+        out = self.fresh(src)
+        self.channel += 1
+        shp = self.shape[src]
+        nbytes = int(math.prod(shp)) * (torch.empty((), dtype=self.dtype[src]).element_size() if src in self.dtype else 4)
+        dim = spec_from.dim if spec_from.kind == "S" else spec_to.dim
+        cnt = spec_from.counts if spec_from.kind == "S" else spec_to.counts
+        self.transfers.append(Transfer(self.channel, kind, verb, axis, src, dim, tuple(cnt), consumer, nbytes))
+        self.steps.append(Step("collective", out, verb, (Ref(src),), {},
+                               {"axis": axis, "from": spec_from, "to": spec_to, "channel": self.channel, "kind": kind,
+                                "full_shape": shp}))
+        self.shape[out] = shp
+        if src in self.dtype:
+            self.dtype[out] = self.dtype[src]
+        return out
+
+    def reshard(self, name: str, want: tuple) -> str:
+        """Bring value ``name`` to placement ``want`` (per axis); returns the (possibly new) value name."""
+        have = self.spec[name]
+        cur = name
+        for ax in range(self.na):
+            h, w = have[ax], want[ax]
+            if h == w:
+                continue
+            new_specs = list(self.spec[cur])
+            if h.kind == "P":
+                if w.kind == "S":
+                    cur2 = self.emit_collective("reduce_scatter", "reduce", ax, cur, h, w)
+                elif w.kind == "O":
+                    cur2 = self.emit_collective("reduce", "reduce", ax, cur, h, w)
+                else:
+                    cur2 = self.emit_collective("all_reduce", "reduce", ax, cur, h, R)
+                    if w.kind == "P":
+                        raise AssertionError("replicated -> partial is never requested")
+            elif h.kind == "S":
+                if w.kind == "R":
+                    cur2 = self.emit_collective("all_gather", "broadcast", ax, cur, h, w, consumer=PAGES)
+                elif w.kind == "S":
+                    if h.dim == w.dim:      # same dim, other cuts: gather + slice (rare)
+                        mid = self.emit_collective("all_gather", "broadcast", ax, cur, h, R)
+                        self.spec[mid] = tuple(R if i == ax else s for i, s in enumerate(self.spec[cur]))
+                        cur2 = self.emit_slice(mid, ax, w)
+                    else:
+                        cur2 = self.emit_collective("all_to_all", "alltoall", ax, cur, h, w)
+                elif w.kind == "O":
+                    cur2 = self.emit_collective("gather", "broadcast", ax, cur, h, w)
+                else:
+                    raise AssertionError(f"sharded -> {w}")
+            elif h.kind == "R":
+                if w.kind == "S":
+                    cur2 = self.emit_slice(cur, ax, w)
+                elif w.kind == "O":
+                    cur2 = cur                      # every processor has it; the owner simply uses its copy
+                    new_specs[ax] = w
+                    cur2 = self.alias(cur, tuple(new_specs))
+                    have = self.spec[cur2]
+                    cur = cur2
+                    continue
+                else:
+                    raise AssertionError(f"replicated -> {w}")
+            else:  # owner
+                if w.kind == "R":
+                    cur2 = self.emit_collective("broadcast", "broadcast", ax, cur, h, w)
+                elif w.kind == "O":
+                    cur2 = self.emit_collective("send_recv", "permute", ax, cur, h, w)
+                elif w.kind == "S":
+                    cur2 = self.emit_collective("scatter", "broadcast", ax, cur, h, w)
+                else:
+                    raise AssertionError(f"owner -> {w}")
+            new_specs[ax] = w
+            self.spec[cur2] = tuple(new_specs)
+            cur = cur2
+        return cur
+
+    def alias(self, src: str, specs: tuple) -> str:
+        out = self.fresh(src)
+        self.steps.append(Step("alias", out, None, (Ref(src),)))
+        self.shape[out] = self.shape[src]
+        if src in self.dtype:
+            self.dtype[out] = self.dtype[src]
+        self.spec[out] = specs
+        return out
+
+    def emit_slice(self, src: str, axis: int, w: Spec) -> str:
+        out = self.fresh(src)
+        self.steps.append(Step("slice", out, None, (Ref(src),), {}, {"axis": axis, "to": w}))
+        self.shape[out] = self.shape[src]
+        if src in self.dtype:
+            self.dtype[out] = self.dtype[src]
+        specs = list(self.spec[src])
+        specs[axis] = w
+        self.spec[out] = tuple(specs)
+        return out
+
+    # ---- per-axis rules.  Each returns (wanted specs of tensor args, out spec) for ONE axis.
+    def rule_pointwise(self, node, targs, specs, ax):
+        out_shape = _shape(node)
+        nd = len(out_shape)
+        shard = None
+        owner = None
+        for a, s in zip(targs, specs):
+            if s.kind == "S":
+                ash = self.shape[a]
+                d_out = s.dim + (nd - len(ash))
+                if shard is None and 0 <= d_out < nd and ash[s.dim] == out_shape[d_out]:
+                    shard = (d_out, s)
+            elif s.kind == "O" and owner is None:
+                owner = s
+        partial = [s.kind == "P" for s in specs]
+        if shard is None and any(partial):
+            lin = LINEAR_IN.get(node.target)
+            others_ok = all(s.kind in ("R", "P") for s in specs)
+            keep = False
+            if lin == "all" and all(partial) and others_ok:
+                keep = True
+            elif lin == "all" and len(specs) == 1:
+                keep = True
+            elif lin == "one" and sum(partial) == 1 and others_ok:
+                keep = True
+            elif lin == "first" and partial[0] and sum(partial) == 1 and others_ok:
+                keep = True
+            if keep:
+                return list(specs), specs[partial.index(True)]
+            return [R if s.kind == "P" else s for s in specs], (owner or R) if not any(s.kind == "S" for s in specs) else R
+        if shard is not None:
+            d_out, s0 = shard
+            want = []
+            for a in targs:
+                ash = self.shape[a]
+                d_in = d_out - (nd - len(ash))
+                if d_in < 0 or ash[d_in] == 1 and out_shape[d_out] != 1:
+                    want.append(R)                             # broadcast along the sharded dim
+                else:
+                    want.append(Spec("S", d_in, s0.counts, s0.striped))
+            return want, Spec("S", d_out, s0.counts, s0.striped)
+        if owner is not None:
+            return [owner if s.kind != "R" else R for s in specs], owner
+        return [R for _ in specs], R
+
+    def rule_mm(self, node, targs, specs, ax, batch: int):
+        """mm (batch=0) / bmm (batch=1): A[.., m, k] x B[.., k, n]."""
+        a, b = specs
+        m_dim, k_a = batch, batch + 1
+        k_b, n_dim = batch, batch + 1
+        sa = a.dim if a.kind == "S" else None
+        sb = b.dim if b.kind == "S" else None
+        if batch and sa == 0 and (sb == 0 or b.kind == "R"):
+            return [a, Spec("S", 0, a.counts, a.striped)], Spec("S", 0, a.counts, a.striped)
+        if batch and sb == 0 and a.kind == "R":
+            return [Spec("S", 0, b.counts, b.striped), b], Spec("S", 0, b.counts, b.striped)
+        if sa == k_a and (sb == k_b or b.kind == "R"):           # contraction sharded -> partial sums
+            return [a, Spec("S", k_b, a.counts, a.striped)], P()
+        if sb == k_b and a.kind == "R":
+            return [Spec("S", k_a, b.counts, b.striped), b], P()
+        if sa == m_dim and b.kind in ("R",):
+            return [a, R], Spec("S", m_dim, a.counts, a.striped)
+        if sb == n_dim and a.kind == "R":
+            return [R, b], Spec("S", n_dim, b.counts, b.striped)
+        if sa == m_dim and sb == n_dim:                          # same axis on both: gather the weight-like operand
+            return [a, R], Spec("S", m_dim, a.counts, a.striped)
+        if sa == m_dim and b.kind == "P":
+            return [a, R], Spec("S", m_dim, a.counts, a.striped)
+        if a.kind == "P" and b.kind == "R":
+            return [a, b], a
+        if a.kind == "R" and b.kind == "P":
+            return [a, b], b
+        if a.kind == "O" or b.kind == "O":
+            o = a if a.kind == "O" else b
+            return [o if a.kind != "R" else R, o if b.kind != "R" else R], o
+        return [R, R], R
+
+    def rule_view(self, node, targs, specs, ax):
+        s = specs[0]
+        if s.kind != "S":
+            return [s], s
+        ish, osh = self.shape[targs[0]], _shape(node)
+        if s.striped:
+            return [R], R
+        pre = int(math.prod(ish[:s.dim]))
+        acc = 1
+        for d_out, sz in enumerate(osh):
+            if acc == pre and sz != 1 or (acc == pre and d_out == len(osh) - 1):
+                n_in = ish[s.dim]
+                if sz % n_in == 0:                     # the sharded dim becomes the outer factor of a merged dim
+                    f = sz // n_in
+                    return [s], Spec("S", d_out, tuple(c * f for c in s.counts))
+                if n_in % sz == 0:                     # the sharded dim is split; shards must hold whole inner blocks
+                    inner = n_in // sz
+                    if all(c % inner == 0 for c in s.counts):
+                        return [s], Spec("S", d_out, tuple(c // inner for c in s.counts))
+                break
+            acc *= sz
+            if acc > pre:
+                break
+        return [R], R
+
+    # ---- the walk
+    def run(self, inputs_order: list[str]) -> Plan:
+        input_specs, outputs, output_specs = {}, [], {}
+        for node in self.gm.graph.nodes:
+            if node.op == "placeholder":
+                self.shape[node.name] = _shape(node)
+                v = node.meta.get("val")
+                if isinstance(v, torch.Tensor):
+                    self.dtype[node.name] = v.dtype
+                sp = self.stated.get(node.name) or self.all_r()
+                self.spec[node.name] = sp
+                input_specs[node.name] = sp
+            elif node.op == "get_attr":
+                self.shape[node.name] = _shape(node)
+                self.spec[node.name] = self.all_r()
+                self.steps.append(Step("const", node.name, node.target))
+            elif node.op == "call_function":
+                self.call(node)
+            elif node.op == "output":
+                flat = node.args[0] if isinstance(node.args[0], (tuple, list)) else (node.args[0],)
+                for i, o in enumerate(flat):
+                    if isinstance(o, torch.fx.Node):
+                        want = self.stated.get(("output", i)) or self.all_r()
+                        # partial and owner values are completed; sharded values stay sharded only if stated
+                        name = self.reshard(self.renamed.get(o.name, o.name), want)
+                        outputs.append(name)
+                        output_specs[name] = want
+                    else:
+                        outputs.append(("const", o))
+        return Plan(self.mesh, self.steps, inputs_order, input_specs, outputs, output_specs, self.transfers,
+                    dict(self.shape), dict(self.dtype))
+
+    def call(self, node):
+        tgt = node.target
+        flat_args = list(node.args)
+        tnames = [self.renamed.get(a.name, a.name) for a in flat_args if _is_tensor_node(a)]
+        if tgt is operator.getitem:
+            src = self.renamed.get(node.args[0].name, node.args[0].name)
+            self.steps.append(Step("call", node.name, tgt, (Ref(src), node.args[1])))
+            self.shape[node.name] = _shape(node)
+            sp = self.spec.get((src, node.args[1])) or self.spec.get(src) or self.all_r()
+            self.spec[node.name] = sp
+            v = node.meta.get("val")
+            if isinstance(v, torch.Tensor):
+                self.dtype[node.name] = v.dtype
+            return
+        val = node.meta.get("val")
+        self.shape[node.name] = _shape(node)
+        if isinstance(val, torch.Tensor):
+            self.dtype[node.name] = val.dtype
+        # list-of-tensor args (cat, stack, index_put): handled by the fallback below unless all equal
+        list_args = [a for a in flat_args if isinstance(a, (list, tuple)) and any(_is_tensor_node(x) for x in a)]
+        out_specs = []
+        wants: dict[str, list] = {n: [] for n in tnames}
+        meta: dict[str, Any] = {}
+        handled = not list_args and isinstance(val, torch.Tensor)
+        if tgt in CREATION or (not tnames and not list_args):
+            self.spec[node.name] = self.all_r()
+            self.steps.append(Step("call", node.name, tgt, self.ref_args(node.args), self.ref_kwargs(node.kwargs)))
+            return
+        if handled:
+            for ax in range(self.na):
+                specs = [self.spec[n][ax] for n in tnames]
+                res = self.axis_rule(node, tnames, specs, ax, meta)
+                if res is None:
+                    handled = False
+                    break
+                w, o = res
+                for n, s in zip(tnames, w):
+                    wants[n].append(s)
+                out_specs.append(o)
+        if handled:
+            # two axes must not shard the same tensor dimension of the output
+            dims = [s.dim for s in out_specs if s.kind == "S"]
+            if len(dims) != len(set(dims)):
+                handled = False
+        if not handled:
+            self.fallback(node, tnames, list_args)
+            return
+        new_names = {}
+        orig = [a.name for a in flat_args if _is_tensor_node(a)]
+        for o, n in zip(orig, tnames):
+            new_names[o] = self.reshard(n, tuple(wants[n]))
+        self.spec[node.name] = tuple(out_specs)
+        args = self.ref_args(node.args, new_names)
+        kwargs = self.ref_kwargs(node.kwargs, new_names)
+        meta["out_specs"] = tuple(out_specs)
+        meta["full_shape"] = _shape(node)
+        self.steps.append(Step("call", node.name, tgt, args, kwargs, meta))
+        want = self.stated.get(node.name)
+        if want is not None and want != tuple(out_specs):
+            self.renamed[node.name] = self.reshard(node.name, want)      # a stated placement is a constraint
+
+    def axis_rule(self, node, tnames, specs, ax, meta):
+        tgt = node.target
+        if tgt in POINTWISE:
+            return self.rule_pointwise(node, tnames, specs, ax)
+        if tgt in (aten.mm.default, aten.bmm.default):
+            return self.rule_mm(node, tnames, specs, ax, 0 if tgt is aten.mm.default else 1)
+        if tgt is aten.addmm.default:                                   # bias + a @ b
+            w, o = self.rule_mm(node, tnames[1:], specs[1:], ax, 0)
+            if o.kind == "S" and o.dim == 1:
+                bias = Spec("S", len(self.shape[tnames[0]]) - 1, o.counts, o.striped)
+            elif o.kind == "P":
+                return [R, R, R], R                                      # keep it simple: bias with partial sums
+            else:
+                bias = R
+            return [bias] + w, o
+        if tgt in (aten.view.default, aten._unsafe_view.default, aten.reshape.default):
+            res = self.rule_view(node, tnames, specs, ax)
+            meta.setdefault("localize", ("shape", 1))
+            return res
+        if tgt is aten.expand.default:
+            s = specs[0]
+            ish, osh = self.shape[tnames[0]], _shape(node)
+            off = len(osh) - len(ish)
+            meta.setdefault("localize", ("shape", 1))
+            if s.kind == "S":
+                return [s], Spec("S", s.dim + off, s.counts, s.striped)
+            return [s], s
+        if tgt in (aten.permute.default,):
+            s = specs[0]
+            if s.kind == "S":
+                perm = [p % len(node.args[1]) for p in node.args[1]]
+                return [s], Spec("S", perm.index(s.dim), s.counts, s.striped)
+            return [s], s
+        if tgt in (aten.transpose.int, aten.t.default):
+            s = specs[0]
+            nd = len(self.shape[tnames[0]])
+            d0, d1 = (0, 1) if tgt is aten.t.default else (node.args[1] % nd, node.args[2] % nd)
+            if s.kind == "S":
+                nd_ = {d0: d1, d1: d0}.get(s.dim, s.dim)
+                return [s], Spec("S", nd_, s.counts, s.striped)
+            return [s], s
+        if tgt is aten.unsqueeze.default:
+            s = specs[0]
+            nd = len(self.shape[tnames[0]]) + 1
+            d = node.args[1] % nd
+            if s.kind == "S":
+                return [s], Spec("S", s.dim + (1 if d <= s.dim else 0), s.counts, s.striped)
+            return [s], s
+        if tgt in (aten.squeeze.dim, aten.squeeze.dims):
+            s = specs[0]
+            nd = len(self.shape[tnames[0]])
+            ds = node.args[1] if isinstance(node.args[1], (list, tuple)) else [node.args[1]]
+            ds = sorted(d % nd for d in ds if self.shape[tnames[0]][d % nd] == 1)
+            if s.kind == "S":
+                if s.dim in ds:
+                    return [R], R
+                return [s], Spec("S", s.dim - sum(1 for d in ds if d < s.dim), s.counts, s.striped)
+            return [s], s
+        if tgt in REDUCTIONS:
+            return self.rule_reduce(node, tnames, specs, ax, meta)
+        if tgt in SOFTMAX_LIKE:
+            pos = SOFTMAX_LIKE[tgt]
+            nd = len(_shape(node)) or len(self.shape[tnames[0]])
+            dim = node.args[pos] if len(node.args) > pos else -1
+            dim = dim % max(nd, 1)
+            shard = next((s for s in specs if s.kind == "S"), None)
+            if isinstance(node.meta.get("val"), (tuple, list)):
+                return None
+            if shard is not None and shard.dim != dim:
+                return [Spec("S", shard.dim, shard.counts, shard.striped) for _ in specs], shard
+            return [R for _ in specs], R
+        if tgt is aten.embedding.default:
+            w, idx = specs
+            if idx.kind == "S" and w.kind == "R":
+                return [R, idx], Spec("S", idx.dim, idx.counts, idx.striped)
+            if w.kind == "S" and w.dim == 0 and idx.kind == "R" and not w.striped:
+                meta["vocab_parallel"] = (ax, w.counts)
+                return [w, R], P()
+            if w.kind == "S" and w.dim == 1 and idx.kind == "R":
+                return [w, R], Spec("S", len(_shape(node)) - 1, w.counts, w.striped)
+            return [R, R], R
+        if tgt is aten.embedding_dense_backward.default:
+            g, idx = specs
+            if g.kind == "S" and idx.kind == "S" and g.dim == idx.dim:
+                return [g, idx], P()
+            if g.kind == "S" and g.dim == len(self.shape[tnames[0]]) - 1 and idx.kind == "R":
+                return [g, R], Spec("S", 1, g.counts, g.striped)
+            return [R, R], R
+        if tgt in (aten.slice.Tensor, aten.select.int, aten.narrow.default, aten.slice_backward.default,
+                   aten.select_backward.default):
+            s = specs[0]
+            if tgt in (aten.slice_backward.default, aten.select_backward.default):
+                dim = node.args[2]
+                nd = len(node.args[1])
+            else:
+                dim = node.args[1] if len(node.args) > 1 else 0
+                nd = len(self.shape[tnames[0]])
+            dim = dim % nd
+            if s.kind == "S" and s.dim != dim:
+                out_dim = s.dim - (1 if tgt is aten.select.int and dim < s.dim else 0)
+                if tgt in (aten.slice_backward.default, aten.select_backward.default):
+                    meta.setdefault("localize", ("shape", 1))
+                    out_dim = s.dim + (1 if tgt is aten.select_backward.default and dim <= s.dim else 0)
+                return [s], Spec("S", out_dim, s.counts, s.striped)
+            if s.kind == "S":
+                return [R], R
+            return [s], s
+        if tgt in (aten.native_layer_norm.default,):
+            return None
+        return None
+
+    def rule_reduce(self, node, tnames, specs, ax, meta):
+        s = specs[0]
+        tgt = node.target
+        kind = REDUCTIONS[tgt]
+        ish = self.shape[tnames[0]]
+        nd = len(ish)
+        if tgt in (aten.sum.default, aten.mean.default, aten.any.default, aten.all.default, aten.max.default, aten.min.default):
+            dims, keep = list(range(nd)), False
+        else:
+            d = node.args[1] if len(node.args) > 1 else None
+            dims = list(range(nd)) if d is None or d == [] else [x % nd for x in (d if isinstance(d, (list, tuple)) else [d])]
+            keep = bool(node.args[2]) if len(node.args) > 2 else False
+        if s.kind == "S":
+            if s.dim in dims:
+                if kind == "mean":
+                    total = int(math.prod(ish[d] for d in dims))
+                    meta["mean_as_sum"] = total
+                    return [s], P("sum")
+                return [s], P(kind)
+            nd_ = s.dim if keep else s.dim - sum(1 for d in dims if d < s.dim)
+            return [s], Spec("S", nd_, s.counts, s.striped)
+        if s.kind == "P":
+            if kind == "sum" or (kind == "mean"):
+                return [s], s
+            return [R], R
+        return [s], s
+
+    def fallback(self, node, tnames, list_args):
+        """Rule miss: gather every tensor input and run the op replicated."""
+        new_names = {}
+        for a in node.args:
+            if _is_tensor_node(a):
+                new_names[a.name] = self.reshard(self.renamed.get(a.name, a.name), self.all_r())
+        for la in list_args:
+            for x in la:
+                if _is_tensor_node(x):
+                    new_names[x.name] = self.reshard(self.renamed.get(x.name, x.name), self.all_r())
+        for v in node.kwargs.values():
+            if _is_tensor_node(v):
+                new_names[v.name] = self.reshard(self.renamed.get(v.name, v.name), self.all_r())
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
+                               self.ref_kwargs(node.kwargs, new_names), {"fallback": True}))
+        self.spec[node.name] = self.all_r()
+
+    def ref_args(self, args, rename=None):
+        rename = rename or {}
+
+        def conv(a):
+            if isinstance(a, torch.fx.Node):
+                return Ref(rename.get(a.name, self.renamed.get(a.name, a.name)))
+            if isinstance(a, (list, tuple)):
+                return type(a)(conv(x) for x in a)
+            return a
+        return tuple(conv(a) for a in args)
+
+    def ref_kwargs(self, kwargs, rename=None):
+        rename = rename or {}
+        return {k: (Ref(rename.get(v.name, self.renamed.get(v.name, v.name))) if isinstance(v, torch.fx.Node) else v) for k, v in kwargs.items()}
+
+
+# ----------------------------------------------------------------------------- the public stage
+def normalise(stated, node, mesh: Mesh, names_to_axis) -> tuple | None:
+    """Turn what the placement callable returned for ``node`` into per-axis Specs."""
+    if stated is None:
+        return None
+    na = len(mesh.shape)
+    if isinstance(stated, str):
+        rank = mesh.names.index(stated)
+        co = mesh.coords(rank)
+        return tuple(O(co[a]) for a in range(na))
+    dim, procs, units = stated
+    shape = _shape(node)
+    if isinstance(dim, (tuple, list)):
+        dims = list(dim)
+        units_l = list(units) if isinstance(units, (tuple, list)) and len(units) == len(dims) and not all(
+            isinstance(u, (int, float)) for u in units) else [units] * len(dims)
+        specs = [R] * na
+        for a, (d, u) in enumerate(zip(dims, units_l)):
+            if d is None:
+                continue
+            d = d % len(shape)
+            c = counts(shape[d], u, mesh.shape[a])
+            specs[a] = Spec("S", d, tuple(c), u == "striped")
+        return tuple(specs)
+    procs = tuple(procs)
+    axis = names_to_axis(procs)
+    d = dim % len(shape)
+    c = counts(shape[d], units, len(procs))
+    specs = [R] * na
+    specs[axis] = Spec("S", d, tuple(c), units == "striped")
+    return tuple(specs)
+
+
+def place(exported, processors: dict, placement: Callable, mesh_shape: tuple | None = None) -> Plan:
+    """Propagate the stated placements through the exported graph and insert collectives."""
+    names = tuple(processors)
+    mesh = Mesh(names, tuple(mesh_shape) if mesh_shape else (len(names),))
+    if math.prod(mesh.shape) != len(names):
+        raise ValueError("mesh shape does not match the number of processors")
+
+    def names_to_axis(procs: tuple) -> int:
+        ranks = tuple(names.index(p) for p in procs)
+        for a in range(len(mesh.shape)):
+            if any(ranks == mesh.axis_group(r, a) for r in ranks):
+                return a
+        if len(ranks) == len(names):
+            return 0
+        raise ValueError(f"processors {procs} are not a line of the mesh")
+
+    stated = {}
+    gm = exported.graph_module
+    out_node = None
+    for node in gm.graph.nodes:
+        if node.op == "output":
+            out_node = node
+            continue
+        if node.op in ("placeholder", "call_function", "get_attr") and node.target is not operator.getitem:
+            if not isinstance(node.meta.get("val"), torch.Tensor):
+                continue
+            sp = normalise(placement(node), node, mesh, names_to_axis)
+            if sp is not None:
+                stated[node.name] = sp
+    # gradients land where their parameter lives (sharded parameters get reduce-scattered gradients)
+    if out_node is not None:
+        flat = out_node.args[0] if isinstance(out_node.args[0], (tuple, list)) else (out_node.args[0],)
+        by_target = {qual: ph for ph, (qual, _) in exported.state.items()}
+        for i, (kind, target) in enumerate(exported.outputs):
+            if kind == "grad_param" and target in by_target and by_target[target] in stated:
+                stated[("output", i)] = stated[by_target[target]]
+            elif kind == "grad_input" and target in stated:
+                stated[("output", i)] = stated[target]
+    order = [n.name for n in gm.graph.nodes if n.op == "placeholder"]
+    prop = Propagator(gm, mesh, stated)
+    plan = prop.run(order)
+    # stated placements on intermediate nodes are constraints: applied by resharding right after the node
+    return plan

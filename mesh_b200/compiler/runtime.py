@@ -1,0 +1,409 @@
+"""Running a scheduled program: ``Program(scheduled)(*args)``.
+
+Two executors share one step interpreter:
+
+* **distributed** — this process is one processor (one process per GPU); collectives go through the
+  explicit verbs (the ``mesh`` backend's kernels on CUDA, gloo on CPU);
+* **threads** — every processor runs as a thread of this process with in-process queues, which is the
+  reference's eager send/recv semantics (compiler/mesh_compiler/ir.py:20-36) and serves as bring-up
+  executor and oracle.
+
+Arguments are bound by the captured signature; parameters and buffers are the caller's live tensors,
+re-read on every call (compiler/mesh_compiler/runtime.py:42-44); buffer and input mutations are stored
+in place into the caller's storage (runtime.py:53-58).  Every processor is handed the full tensors and
+reads only the slices its placement names (placement.py:173-180).
+"""
+from __future__ import annotations
+
+import math
+import operator
+import threading
+from typing import Any
+
+import torch
+import torch.distributed as dist
+from torch.utils import _pytree as pytree
+
+from .ir import Mesh, Plan, Ref, Scheduled, Spec, Step, TrainingResult
+from .placement import local_indices
+
+aten = torch.ops.aten
+
+
+# ----------------------------------------------------------------------------- collectives back ends
+class ThreadWorld:
+    """Shared state of the threads that interpret one program."""
+
+    def __init__(self, n: int):
+        self.n = n
+        self.lock = threading.Lock()
+        self.slots: dict[Any, dict] = {}
+        self.barriers: dict[Any, threading.Barrier] = {}
+        self.timeout = 120.0
+
+    def exchange(self, key, group: tuple, rank: int, value):
+        """All ranks of ``group`` deposit ``value``; returns the list in group order."""
+        with self.lock:
+            slot = self.slots.setdefault((key, group), {})
+            bar = self.barriers.setdefault((key, group), threading.Barrier(len(group)))
+        slot[rank] = value
+        bar.wait(self.timeout)
+        out = [slot[r] for r in group]
+        bar.wait(self.timeout)
+        if rank == group[0]:
+            with self.lock:
+                self.slots.pop((key, group), None)
+                self.barriers.pop((key, group), None)
+        return out
+
+
+class ThreadCollectives:
+    def __init__(self, world: ThreadWorld, mesh: Mesh, rank: int):
+        self.world, self.mesh, self.rank = world, mesh, rank
+        self.seq = 0
+
+    def gather_all(self, t, axis):
+        self.seq += 1
+        g = self.mesh.axis_group(self.rank, axis)
+        return self.world.exchange(self.seq, g, self.rank, t), g
+
+
+class DistCollectives:
+    """torch.distributed groups per mesh axis; a 1-D mesh uses the default group / mesh verbs."""
+
+    _groups: dict = {}
+
+    def __init__(self, mesh: Mesh, rank: int):
+        self.mesh, self.rank = mesh, rank
+        self.seq = 0
+        if len(mesh.shape) > 1:
+            for a in range(len(mesh.shape)):
+                seen = set()
+                for r in range(mesh.size):
+                    g = mesh.axis_group(r, a)
+                    if g in seen:
+                        continue
+                    seen.add(g)
+                    if (mesh.shape, g) not in DistCollectives._groups:
+                        DistCollectives._groups[(mesh.shape, g)] = dist.new_group(list(g))
+
+    def group(self, axis):
+        g = self.mesh.axis_group(self.rank, axis)
+        if len(self.mesh.shape) == 1:
+            return None, g
+        return DistCollectives._groups[(self.mesh.shape, g)], g
+
+    def gather_all(self, t, axis):
+        """Generic fallback used by the uncommon verbs: all-gather of arbitrary (same-dtype) tensors."""
+        grp, g = self.group(axis)
+        shapes = [None] * len(g)
+        dist.all_gather_object(shapes, (tuple(t.shape), t.dtype), group=grp)
+        outs = [torch.empty(s, dtype=d, device=t.device) for s, d in shapes]
+        dist.all_gather(outs, t.contiguous(), group=grp)
+        return outs, g
+
+
+# ----------------------------------------------------------------------------- step interpreter
+class Executor:
+    def __init__(self, plan: Plan, rank: int, coll, device: torch.device):
+        self.plan, self.rank, self.coll, self.device = plan, rank, coll, device
+        self.mesh = plan.mesh
+        self.coords = self.mesh.coords(rank)
+        self.dist = isinstance(coll, DistCollectives)
+
+    # ---- shards of full tensors
+    def shard(self, full: torch.Tensor, specs: tuple) -> torch.Tensor | None:
+        t = full
+        for ax, s in enumerate(specs):
+            if s.kind == "S":
+                idx = local_indices(s, self.coords[ax], t.shape[s.dim])
+                t = self._index(t, s.dim, idx)
+            elif s.kind == "O" and s.owner != self.coords[ax]:
+                return None
+        return t
+
+    @staticmethod
+    def _index(t, dim, idx):
+        if isinstance(idx, slice):
+            if idx.step in (None, 1):
+                return t.narrow(dim, idx.start, max(0, idx.stop - idx.start))
+            sl = [slice(None)] * t.dim()
+            sl[dim] = idx
+            return t[tuple(sl)]
+        return t.index_select(dim, torch.tensor(idx, device=t.device, dtype=torch.long))
+
+    # ---- collectives
+    def collective(self, step: Step, t):
+        m = step.meta
+        ax, frm, to, verb = m["axis"], m["from"], m["to"], step.target
+        P = self.mesh.shape[ax]
+        me = self.coords[ax]
+        if P == 1:
+            return t
+        if self.dist:
+            return self._collective_dist(verb, ax, frm, to, t, m)
+        parts, g = self.coll.gather_all(t, ax)
+        if verb == "all_reduce" or verb == "reduce":
+            out = self._reduce(parts, frm.op)
+            if verb == "reduce" and to.owner != me:
+                return None
+            return out
+        if verb == "reduce_scatter":
+            out = self._reduce(parts, frm.op)
+            return self._index(out, to.dim, local_indices(to, me, out.shape[to.dim])).contiguous()
+        if verb == "all_gather" or verb == "gather":
+            if verb == "gather" and to.owner != me:
+                return None
+            return self._assemble(parts, frm, m["full_shape"])
+        if verb == "all_to_all":
+            full = self._assemble(parts, frm, m["full_shape"])
+            return self._index(full, to.dim, local_indices(to, me, full.shape[to.dim])).contiguous()
+        if verb == "broadcast":
+            return parts[frm.owner]
+        if verb == "scatter":
+            full = parts[frm.owner]
+            return self._index(full, to.dim, local_indices(to, me, full.shape[to.dim])).contiguous()
+        if verb == "send_recv":
+            return parts[frm.owner] if to.owner == me else None
+        raise NotImplementedError(verb)
+
+    @staticmethod
+    def _reduce(parts, op):
+        out = parts[0].clone()
+        for p in parts[1:]:
+            if op == "max":
+                out = torch.maximum(out, p)
+            elif op == "min":
+                out = torch.minimum(out, p)
+            else:
+                out = out + p
+        return out
+
+    def _assemble(self, parts, spec: Spec, full_shape):
+        if not spec.striped:
+            return torch.cat(parts, dim=spec.dim)
+        n = sum(p.shape[spec.dim] for p in parts)
+        shape = list(parts[0].shape)
+        shape[spec.dim] = n
+        out = torch.empty(shape, dtype=parts[0].dtype, device=parts[0].device)
+        for r, p in enumerate(parts):
+            idx = local_indices(spec, r, n)
+            sl = [slice(None)] * out.dim()
+            sl[spec.dim] = idx if isinstance(idx, slice) else torch.tensor(idx, device=out.device)
+            out[tuple(sl)] = p
+        return out
+
+    def _collective_dist(self, verb, ax, frm, to, t, m):
+        from ..distributed import verbs
+        grp, g = self.coll.group(ax)
+        me = self.coords[ax]
+        if verb == "all_reduce":
+            out = t.clone()
+            return verbs.all_reduce(out, frm.op, group=grp)
+        if verb == "reduce_scatter" and not to.striped:
+            return verbs.reduce_scatter(t, to.dim, frm.op, list(to.counts), group=grp)
+        if verb == "all_gather" and not frm.striped:
+            return verbs.all_gather(t, frm.dim, list(frm.counts), group=grp)
+        if verb == "all_to_all" and not frm.striped and not to.striped:
+            # cut along the new dim, exchange, join along the old dim
+            pieces = [p.contiguous() for p in t.split(list(to.counts), dim=to.dim)]
+            moved = [p.movedim(frm.dim, 0).contiguous() for p in pieces]
+            # per-destination blocks have different sizes along the new dim, so exchange them as a list
+            recv = [torch.empty((frm.counts[r],) + tuple(moved[me].shape[1:]), dtype=t.dtype, device=t.device) for r in range(len(g))]
+            dist.all_to_all(recv, moved, group=grp)
+            out = torch.cat(recv, dim=0).movedim(0, frm.dim)
+            return out.contiguous()
+        if verb == "broadcast":
+            src = g[frm.owner]
+            buf = t if t is not None else torch.empty(m["full_shape"], dtype=self.plan.dtypes.get(m.get("value", ""), torch.float32), device=self.device)
+            dist.broadcast(buf, src=src, group=grp)
+            return buf
+        # uncommon verbs (striped gathers, owner moves): generic gather of the parts
+        stand_in = t if t is not None else torch.empty(0, device=self.device)
+        parts, _ = self.coll.gather_all(stand_in, ax)
+        if verb == "reduce":
+            out = self._reduce(parts, frm.op)
+            return out if to.owner == me else None
+        if verb == "reduce_scatter":
+            out = self._reduce(parts, frm.op)
+            return self._index(out, to.dim, local_indices(to, me, out.shape[to.dim])).contiguous()
+        if verb in ("all_gather", "gather"):
+            if verb == "gather" and to.owner != me:
+                return None
+            return self._assemble(parts, frm, m["full_shape"])
+        if verb == "all_to_all":
+            full = self._assemble(parts, frm, m["full_shape"])
+            return self._index(full, to.dim, local_indices(to, me, full.shape[to.dim])).contiguous()
+        if verb == "scatter":
+            full = parts[frm.owner]
+            return self._index(full, to.dim, local_indices(to, me, full.shape[to.dim])).contiguous()
+        if verb == "send_recv":
+            return parts[frm.owner] if to.owner == me else None
+        raise NotImplementedError(verb)
+
+    # ---- one program execution
+    def run(self, inputs: dict, consts) -> list:
+        env: dict[str, Any] = {}
+        for name, full in inputs.items():
+            env[name] = self.shard(full, self.plan.input_specs[name]) if isinstance(full, torch.Tensor) else full
+
+        def val(a):
+            if isinstance(a, Ref):
+                return env[a.name]
+            if isinstance(a, (list, tuple)):
+                return type(a)(val(x) for x in a)
+            return a
+
+        for st in self.plan.steps:
+            if st.op == "const":
+                env[st.out] = consts(st.target)
+            elif st.op == "alias":
+                env[st.out] = env[st.args[0].name]
+            elif st.op == "slice":
+                src = env[st.args[0].name]
+                s, ax = st.meta["to"], st.meta["axis"]
+                env[st.out] = None if src is None else self._index(src, s.dim, local_indices(s, self.coords[ax], src.shape[s.dim]))
+            elif st.op == "collective":
+                env[st.out] = self.collective(st, env[st.args[0].name])
+            else:
+                env[st.out] = self.call(st, val)
+        out = []
+        for o in self.plan.outputs:
+            out.append(o[1] if isinstance(o, tuple) else env[o])
+        return out
+
+    def call(self, st: Step, val):
+        args = list(val(a) for a in st.args)
+        kwargs = {k: val(v) for k, v in st.kwargs.items()}
+        if any(a is None for a, r in zip(args, st.args) if isinstance(r, Ref)):
+            return None                                   # an operand lives on another processor
+        if "device" in kwargs and kwargs["device"] is not None:
+            kwargs["device"] = self.device
+        tgt = st.target
+        m = st.meta
+        loc = m.get("localize")
+        if loc is not None and "out_specs" in m:
+            i = loc[1]
+            shape = list(args[i])
+            full = m["full_shape"]
+            for ax, s in enumerate(m["out_specs"]):
+                if s.kind == "S" and len(shape) == len(full):
+                    shape[s.dim] = s.counts[self.coords[ax]]
+            if -1 in shape and len(shape) == len(full):
+                pass
+            args[i] = shape
+        if "mean_as_sum" in m:
+            a = list(args)
+            t = a[0]
+            rest = a[1:]
+            r = aten.sum.dim_IntList(t, rest[0] if rest else None, *(rest[1:2] if len(rest) > 1 else []))
+            if tgt is aten.mean.default:
+                r = t.sum()
+            return r / m["mean_as_sum"]
+        if "vocab_parallel" in m:
+            ax, cnts = m["vocab_parallel"]
+            start = sum(cnts[:self.coords[ax]])
+            w, idx = args[0], args[1]
+            local = idx - start
+            ok = (local >= 0) & (local < w.shape[0])
+            e = aten.embedding.default(w, local.clamp(0, max(w.shape[0] - 1, 0)), *args[2:])
+            return e * ok.unsqueeze(-1).to(e.dtype)
+        return tgt(*args, **kwargs)
+
+
+# ----------------------------------------------------------------------------- Program
+class Arguments:
+    """Binds call arguments to placeholders by the captured signature (runtime.py:18-50 of the reference)."""
+
+    def __init__(self, scheduled: Scheduled):
+        self.exported = scheduled.exported
+        self.plan = scheduled.plan
+
+    def prepare(self, args, kwargs) -> dict:
+        ex = self.exported
+        flat, spec = pytree.tree_flatten((tuple(args), dict(kwargs)))
+        if spec != ex.in_spec:
+            flat = list(ex.in_spec.flatten_up_to((tuple(args), dict(kwargs))))
+        if len(flat) != len(ex.user_inputs):
+            raise TypeError(f"expected {len(ex.user_inputs)} input leaves, got {len(flat)}")
+        bound = {name: (t.detach() if isinstance(t, torch.Tensor) else t) for name, (_, t) in ex.state.items()}
+        bound.update(dict(zip(ex.user_inputs, flat)))
+        return bound
+
+
+class Program(Arguments):
+    """``Program(scheduled)(*args, **kwargs)`` -> outputs pytree | ``TrainingResult`` | ``None`` on non-owner ranks."""
+
+    def __init__(self, scheduled: Scheduled, entry: str | None = None, device=None, threads: bool | None = None):
+        super().__init__(scheduled)
+        self.scheduled = scheduled
+        self.mesh = scheduled.plan.mesh
+        distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size() == self.mesh.size
+        self.threads = (not distributed) if threads is None else threads
+        if not self.threads:
+            self.rank = dist.get_rank()
+            dev = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() and
+                             dist.get_backend() != "gloo" else torch.device("cpu"))
+            self.device = torch.device(dev)
+            self.exec = Executor(self.plan, self.rank, DistCollectives(self.mesh, self.rank), self.device)
+        else:
+            self.device = torch.device(device or "cpu")
+        self.entry = entry
+        self.last_structure = None
+
+    def _consts(self, target):
+        gm = self.exported.graph_module
+        obj = gm
+        for part in str(target).split("."):
+            obj = getattr(obj, part)
+        return obj.to(self.device) if isinstance(obj, torch.Tensor) else obj
+
+    def __call__(self, *args, **kwargs):
+        bound = self.prepare(args, kwargs)
+        bound = {k: (v.to(self.device) if isinstance(v, torch.Tensor) and v.device != self.device else v) for k, v in bound.items()}
+        if not self.threads:
+            flat = self.exec.run(bound, self._consts)
+            return self._result(flat, self.exec, bound)
+        world = ThreadWorld(self.mesh.size)
+        results: list = [None] * self.mesh.size
+        errors: list = []
+
+        def work(r):
+            try:
+                ex = Executor(self.plan, r, ThreadCollectives(world, self.mesh, r), self.device)
+                results[r] = (ex, ex.run(bound, self._consts))
+            except BaseException as e:  # surfaced to the caller below
+                errors.append(e)
+                for b in list(world.barriers.values()):
+                    b.abort()
+
+        ts = [threading.Thread(target=work, args=(r,), daemon=True) for r in range(self.mesh.size)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        if errors:
+            raise errors[0]
+        self.per_rank = results
+        owner = 0 if self.entry is None else self.mesh.names.index(self.entry)
+        ex, flat = results[owner]
+        return self._result(flat, ex, bound, results)
+
+    def _result(self, flat, ex, bound, all_results=None):
+        exp = self.exported
+        # in-place stores of buffer / input mutations
+        for i, ph in exp.mutations.items():
+            if flat[i] is not None and isinstance(bound.get(ph), torch.Tensor):
+                target = exp.state[ph][1] if ph in exp.state else bound[ph]
+                with torch.no_grad():
+                    target.copy_(flat[i].to(target.device))
+        returned = [(k, v) for (k, _), v in zip(exp.outputs, flat)]
+        if exp.training:
+            outs = [v for k, v in returned if k in ("user", "loss")]
+            grads_p = {t: v for (k, t), v in zip(exp.outputs, flat) if k == "grad_param"}
+            grads_i = {t: v for (k, t), v in zip(exp.outputs, flat) if k == "grad_input"}
+            try:
+                outs_tree = pytree.tree_unflatten(outs, exp.out_spec)
+            except Exception:
+                outs_tree = outs[0] if len(outs) == 1 else tuple(outs)
+            return TrainingResult(outs_tree, grads_p, grads_i)
+        outs = [v for k, v in returned if k in ("user", "loss")]
+        return pytree.tree_unflatten(outs, exp.out_spec)
