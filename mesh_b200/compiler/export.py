@@ -74,7 +74,7 @@ def read(ep, training: bool = False) -> Exported:
         for v in (val if isinstance(val, (tuple, list)) else [val]):
             if isinstance(v, torch.Tensor) and any(not isinstance(s, int) for s in v.shape):
                 raise ValueError(f"symbolic dimension in {node.name}: shapes must be static")
-    return Exported(gm, state, kinds, users, outputs, ep.call_spec.in_spec, ep.call_spec.out_spec, mutations, training)
+    return Exported(gm, state, kinds, users, outputs, ep.call_spec.in_spec, ep.call_spec.out_spec, mutations, training, ep)
 
 
 def calls(program: torch.nn.Module, args: tuple, functions, **options) -> tuple[Exported, dict]:

@@ -195,6 +195,7 @@ class Exported:
     out_spec: Any
     mutations: dict                  # output index -> placeholder name written in place
     training: bool = False
+    program: Any = None              # the torch.export.ExportedProgram (what archives store)
 
 
 class TrainingResult(NamedTuple):

@@ -308,6 +308,8 @@ class Executor:
             ok = (local >= 0) & (local < w.shape[0])
             e = aten.embedding.default(w, local.clamp(0, max(w.shape[0] - 1, 0)), *args[2:])
             return e * ok.unsqueeze(-1).to(e.dtype)
+        if tgt in (aten.view.default, aten._unsafe_view.default):
+            return args[0].reshape(args[1])        # shards and gathered values are not always dense
         return tgt(*args, **kwargs)
 
 
