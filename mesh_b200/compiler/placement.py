@@ -444,6 +444,9 @@ class Propagator:
         kwargs = self.ref_kwargs(node.kwargs, new_names)
         meta["out_specs"] = tuple(out_specs)
         meta["full_shape"] = _shape(node)
+        stack = node.meta.get("nn_module_stack")
+        if stack:
+            meta["module"] = list(stack.values())[-1][0]          # submodule path the op was traced from
         self.steps.append(Step("call", node.name, tgt, args, kwargs, meta))
         want = self.stated.get(node.name)
         if want is not None and want != tuple(out_specs):
