@@ -1,0 +1,154 @@
+"""Persistent plans: plan once, start many.
+
+The reference plans a program once (``mesh_plan``) and starts it many times (``mesh_transfers_start``):
+executions are software-pipelined over ``copies`` buffers — execution *t* uses copy *t mod copies* — a plan
+carries the membership view it was built for and is refused with ``ESTALE`` once the view has moved, and
+host code can publish / wait on plan words with a no-progress bound (rdma/mesh-call.h:95-106,
+rdma/mesh-dataflow.c:287-317, rdma/mesh-collective.c:17-90, :390).  Here a plan is a workspace layout
+(lifetime-coloured by the native planner, repeated per copy) plus a CUDA graph per copy; ``start`` is a
+graph launch.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import time
+from ctypes import c_char_p, c_double, c_int, c_int64, c_uint64
+
+import torch
+
+from .. import _native
+from ..config import capacity
+from .rendezvous import ECANCELED, ETIMEDOUT, MeshStale
+
+ALGOS = ["one_shot", "two_shot", "nvls", "copy_engine"]
+
+
+def choose_allreduce(nbytes: int, world: int, nvls: bool = False, alpha_us: float = 2.5) -> tuple[str, float]:
+    """Closed-form alpha + n*beta choice (no LP is needed for routing on a uniform fabric)."""
+    L = _native.lib()
+    est = c_double(0)
+    a = L.mesh_plan_choose_allreduce(c_uint64(nbytes), c_int(world), c_double(alpha_us),
+                                     c_double(capacity()["nvlink_gbs_per_dir"]), c_int(int(nvls)), ctypes.byref(est))
+    return ALGOS[a], est.value
+
+
+def layout(buffers: list[tuple[int, int, int]], copies: int = 1, align: int = 256) -> tuple[list[list[int]], int]:
+    """``buffers``: ``(first step, last step, bytes)``.  Returns ``(offsets[copy][buffer], bytes per copy)``."""
+    n = len(buffers)
+    out = (c_int64 * max(1, n * copies))()
+    L = _native.lib()
+    L.mesh_plan_layout.restype = c_int64
+    one = L.mesh_plan_layout(c_int(n), (c_int * max(n, 1))(*[b[0] for b in buffers]), (c_int * max(n, 1))(*[b[1] for b in buffers]),
+                             (c_int64 * max(n, 1))(*[b[2] for b in buffers]), c_int64(align), c_int(copies), out)
+    return [[out[c * n + i] for i in range(n)] for c in range(copies)], int(one)
+
+
+class Plan:
+    """A captured step with ``copies`` workspaces; ``start()`` launches execution ``t`` on copy ``t % copies``."""
+
+    def __init__(self, rdv=None, copies: int = 2, horizon: int | None = None):
+        self.rdv = rdv
+        self.epoch = rdv.epoch if rdv is not None else 0
+        self.copies = copies
+        self.horizon = horizon or copies
+        self.graphs: list = [None] * copies
+        self.executions = 0
+        self.completions: list = []
+        self.retired = False
+
+    def capture(self, copy: int, fn) -> None:
+        """Record ``fn()`` (which must only enqueue work on the current stream) as the body of ``copy``."""
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            fn()                                  # warm-up outside capture
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        self.graphs[copy] = g
+
+    def start(self, executions: int = 1) -> int:
+        """Enqueue ``executions`` runs.  Raises ``MeshStale`` when the membership view moved since planning;
+        waits (bounded) when more than ``horizon`` executions would be in flight."""
+        if self.retired:
+            raise RuntimeError("plan was retired")
+        if self.rdv is not None:
+            self.rdv.check_epoch(self.epoch)
+        for _ in range(executions):
+            copy = self.executions % self.copies
+            if len(self.completions) >= self.horizon:
+                ev = self.completions.pop(0)
+                ev.synchronize()
+            if self.graphs[copy] is None:
+                raise RuntimeError(f"copy {copy} was never captured")
+            self.graphs[copy].replay()
+            ev = torch.cuda.Event()
+            ev.record()
+            self.completions.append(ev)
+            self.executions += 1
+        return self.executions
+
+    def ended(self, execution: int) -> bool:
+        done = self.executions - len([e for e in self.completions if not e.query()])
+        return execution < done
+
+    def retire(self) -> None:
+        for ev in self.completions:
+            ev.synchronize()
+        self.completions.clear()
+        self.graphs = [None] * self.copies
+        self.retired = True
+
+
+class HostWord:
+    """A pinned host word that kernels and the host both see: publish / arrived / wait with a no-progress bound
+    (``mesh_host_publish`` / ``mesh_host_arrived`` / ``mesh_host_wait``, rdma/mesh-collective.c:17-90)."""
+
+    def __init__(self):
+        self.t = torch.zeros(2, dtype=torch.int64).pin_memory() if torch.cuda.is_available() else torch.zeros(2, dtype=torch.int64)
+
+    def publish(self, value: int) -> None:
+        if value > int(self.t[0]):                      # monotonic: never written to an earlier value
+            self.t[0] = value
+
+    def cancel(self) -> None:
+        self.t[1] = 1
+
+    def arrived(self, value: int) -> bool:
+        return int(self.t[0]) >= value
+
+    def wait(self, value: int, timeout_s: float = 5.0) -> int:
+        """0 when reached, ``ECANCELED`` when cancelled, ``ETIMEDOUT`` after ``timeout_s`` without progress."""
+        last, t_last = int(self.t[0]), time.monotonic()
+        while True:
+            cur = int(self.t[0])
+            if cur >= value:
+                return 0
+            if int(self.t[1]):
+                return ECANCELED
+            if cur != last:
+                last, t_last = cur, time.monotonic()
+            elif time.monotonic() - t_last > timeout_s:
+                return ETIMEDOUT
+            time.sleep(0.0005)
+
+
+def save(path: str, epoch: int, words: list[int]) -> None:
+    arr = (c_uint64 * max(1, len(words)))(*words)
+    rc = _native.lib().mesh_plan_save(c_char_p(str(path).encode()), c_uint64(epoch), arr, c_uint64(len(words)))
+    if rc != 0:
+        raise OSError(f"mesh_plan_save({path}) failed: {rc}")
+
+
+def load(path: str, cap: int = 1 << 20) -> tuple[int, list[int]]:
+    arr = (c_uint64 * cap)()
+    ep = c_uint64(0)
+    L = _native.lib()
+    L.mesh_plan_load.restype = c_int64
+    n = L.mesh_plan_load(c_char_p(str(path).encode()), ctypes.byref(ep), arr, c_uint64(cap))
+    if n < 0:
+        raise OSError({-1: "cannot open", -2: "bad header", -3: "checksum mismatch", -4: "too large"}.get(n, str(n)) + f": {path}")
+    return int(ep.value), list(arr[:n])

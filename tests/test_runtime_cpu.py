@@ -1,0 +1,93 @@
+"""Host runtime pieces that need no GPU: planner layout / chooser / archives, stats block + meshctl, host words,
+epoch staleness, the engine-bridge shaped C ABI."""
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch.distributed as dist
+
+from mesh_b200.runtime import plan, service
+from mesh_b200.runtime.rendezvous import ECANCELED, ETIMEDOUT, MeshStale, Rendezvous
+
+
+def test_planner_layout_chooser_archive(tmp_path):
+    offs, one = plan.layout([(0, 3, 1000), (4, 6, 1000), (2, 5, 500)], copies=2, align=256)
+    assert offs[0][0] == offs[0][1]                     # disjoint lifetimes share memory
+    assert offs[1][0] == offs[0][0] + one               # second copy is the first shifted by one copy
+    assert one < 1024 + 1024 + 512
+    small, _ = plan.choose_allreduce(4096, 8)
+    big, _ = plan.choose_allreduce(256 << 20, 8)
+    assert small == "one_shot" and big == "two_shot"
+    assert plan.choose_allreduce(256 << 20, 8, nvls=True)[0] == "nvls"
+    words = [1, 2, 3, 2 ** 63]
+    plan.save(tmp_path / "p.plan", 7, words)
+    assert plan.load(tmp_path / "p.plan") == (7, words)
+    raw = bytearray((tmp_path / "p.plan").read_bytes())
+    raw[-1] ^= 1
+    (tmp_path / "bad.plan").write_bytes(raw)
+    with pytest.raises(OSError, match="checksum"):
+        plan.load(tmp_path / "bad.plan")
+
+
+def test_stats_block_and_meshctl():
+    group = f"t{os.getpid()}"
+    assert service.start(group, 0, 1, heartbeat_s=0.05) is False
+    try:
+        service.count("launches", 5)
+        service.count("bytes", 1000, peer=3)
+        service.channel(3, "CONNECTED")
+        time.sleep(0.12)
+        s = service.read(group, 0)
+        assert s["alive"] and s["launches"] == 5 and s["bytes_to_peer"][3] == 1000 and s["channels"][3] == "CONNECTED"
+        out = subprocess.run([sys.executable, "-m", "mesh_b200.tools.meshctl", "status", "--group", group, "--world", "1", "--ready"],
+                             capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        assert out.returncode == 0 and json.loads(out.stdout)["ranks"][0]["pid"] == os.getpid()
+        service.deadline(0.05)                            # the service thread raises abort once the deadline passes
+        time.sleep(0.2)
+        assert service.aborted()
+    finally:
+        service.stop(unlink=True)
+    assert service.read(group, 0) is None
+
+
+def test_host_word_and_epoch():
+    w = plan.HostWord()
+    w.publish(3)
+    w.publish(2)                                          # never moves backwards
+    assert w.arrived(3) and not w.arrived(4)
+    assert w.wait(3, 0.1) == 0 and w.wait(4, 0.05) == ETIMEDOUT
+    w.cancel()
+    assert w.wait(4, 0.05) == ECANCELED
+    rdv = Rendezvous(dist.HashStore(), 0, 1)
+    p = plan.Plan(rdv, copies=2)
+    rdv.advance_epoch()
+    with pytest.raises(MeshStale):
+        p.start()
+
+
+def test_engine_bridge_abi():
+    from mesh_b200 import _native
+    L = _native.lib()
+    L.mesh_open.restype = ctypes.c_void_p
+    L.mesh_publish.restype = ctypes.c_uint64
+    L.mesh_ipc_inbox.restype = ctypes.POINTER(ctypes.c_float)
+    L.mesh_ipc_outbox.restype = ctypes.POINTER(ctypes.c_float)
+    h = ctypes.c_void_p(L.mesh_open(ctypes.c_uint64(8)))
+    src = (ctypes.c_float * 4)(1, 2, 3, 4)
+    assert L.mesh_gather(h, src, ctypes.c_uint64(2), ctypes.c_uint64(4)) == 0
+    t = L.mesh_publish(h)
+    assert L.mesh_poll(h, ctypes.c_uint64(t)) == 0          # non-blocking: not consumed yet
+    inbox, outbox = L.mesh_ipc_inbox(h), L.mesh_ipc_outbox(h)
+    for i in range(8):
+        outbox[i] = inbox[i] * 2
+    L.mesh_ipc_complete(h)
+    assert L.mesh_poll(h, ctypes.c_uint64(t)) == 1
+    dst = (ctypes.c_float * 4)()
+    L.mesh_scatter(h, dst, ctypes.c_uint64(2), ctypes.c_uint64(4))
+    assert list(dst) == [2, 4, 6, 8]
+    assert L.mesh_gather(h, src, ctypes.c_uint64(6), ctypes.c_uint64(4)) == -1
+    L.mesh_close(h)
