@@ -29,7 +29,7 @@ class GemmArgs(ctypes.Structure):
         ("M", c_int), ("N", c_int), ("K", c_int),
         ("lda", c_longlong), ("ldb", c_longlong), ("ldd", c_longlong), ("ldd2", c_longlong), ("ld_aux", c_longlong),
         ("a_rows", c_int), ("b_rows", c_int),
-        ("d_cols", c_int), ("d2_cols", c_int),
+        ("d_cols", c_int), ("d2_cols", c_int), ("d_rows", c_int),
         ("a_mn", c_int), ("b_mn", c_int),
         ("epi", c_int), ("act", c_int),
         ("b_up_rows", c_int), ("d_up_cols", c_int),
@@ -41,6 +41,7 @@ class GemmArgs(ctypes.Structure):
         ("rs_recv", c_void_p * MAX_RANKS), ("rs_count", c_void_p * MAX_RANKS),
         ("rs_expect", c_uint32), ("rs_out", c_void_p), ("rs_rows_per_rank", c_int),
         ("num_ctas", c_int), ("tile_n", c_int), ("pair", c_int),
+        ("tiles", c_void_p), ("n_tiles_dev", c_void_p), ("max_tiles", c_int),
     ]
 
 

@@ -10,6 +10,10 @@ extern "C" {
 
 // All leading dimensions are in elements (bf16).  Pointers are device pointers; peer
 // pointers (ag_dst, ag_flags, rs_recv, rs_count) come from the symmetric heap.
+// One tile of a descriptor-driven GEMM (same layout as mesh::gemm::TileDesc).  In pair mode a descriptor
+// covers 256 output rows: the second CTA of the pair adds 128 to a_mn0 and d_row0.
+typedef struct MeshTileDesc { int a_mn0, k0, k_blocks, b_mn0, b_k0, d_row0, d_col0, pad; } MeshTileDesc;
+
 typedef struct MeshGemmArgs {
   const void* A;
   const void* B;
@@ -20,6 +24,7 @@ typedef struct MeshGemmArgs {
   long long lda, ldb, ldd, ldd2, ld_aux;
   int a_rows, b_rows;          // rows of the stored A / B matrices (TMA bounds)
   int d_cols, d2_cols;         // columns of the stored D / D2 matrices (TMA bounds)
+  int d_rows;                  // rows of the stored D (0: M); grouped launches write a taller stacked matrix
   int a_mn, b_mn;              // 1: operand is stored [K, rows] (MN-major)
   int epi, act;
   int b_up_rows, d_up_cols;
@@ -44,6 +49,10 @@ typedef struct MeshGemmArgs {
   int num_ctas;                // 0: one per SM
   int tile_n;                  // 0: choose; 128 or 256: width of the output tile
   int pair;                    // 0: cta_group::2 pairs when possible; -1: single-CTA tiles
+  // descriptor-driven mode (grouped / ragged GEMMs): device list of MeshTileDesc and its device length
+  const void* tiles;
+  const void* n_tiles_dev;
+  int max_tiles;               // upper bound of *n_tiles_dev (grid sizing only)
 } MeshGemmArgs;
 
 // Returns 0 or a negative error (bad shape/alignment) or a positive cudaError_t.

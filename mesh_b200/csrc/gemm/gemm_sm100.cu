@@ -106,7 +106,7 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   const int tile_n = (a->epi == EPI_GLU_FWD) ? BN / 2 : bn;
   p.n_tiles = (a->N + tile_n - 1) / tile_n;
   // cta_group::2 pairs (256-row tiles) unless switched off or the problem has a single m-tile
-  const bool pair = a->pair >= 0 && p.m_tiles >= 2 && ctas >= 2;
+  const bool pair = a->pair >= 0 && p.m_tiles >= 2 && ctas >= 2 && (a->tiles == nullptr || a->pair > 0);
   const int cta_per_unit = pair ? 2 : 1;
   if (pair) ctas &= ~1;
   p.m_units = (p.m_tiles + cta_per_unit - 1) / cta_per_unit;
@@ -119,6 +119,8 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   p.aux = (const __nv_bfloat16*)a->aux;
   p.ld_aux = a->ld_aux;
   p.status = (Status*)a->status;
+  p.tiles = (const TileDesc*)a->tiles;
+  p.n_tiles_dev = (const int*)a->n_tiles_dev;
   p.a_ready = (const uint32_t*)a->a_ready;
   p.a_ready_value = a->a_ready_value;
   p.a_ready_rows = a->a_ready_rows > 0 ? a->a_ready_rows : BM;
@@ -158,28 +160,31 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
 
   // ---- tensor maps
   bool ok = true;
-  if (a->a_mn) ok = ok && make_map_mn(&p.tmA, a->A, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->lda, BM / 64);
+  if (a->a_mn) ok = ok && make_map_mn(&p.tmA, a->A, (uint64_t)a->M, (uint64_t)(a->a_rows ? a->a_rows : a->K), (uint64_t)a->lda, BM / 64);
   else         ok = ok && make_map_2d(&p.tmA, a->A, (uint64_t)a->K, (uint64_t)(a->a_rows ? a->a_rows : a->M),
                                       (uint64_t)a->lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
   const uint64_t b_rows = (uint64_t)(a->b_rows ? a->b_rows : a->N);
-  if (a->b_mn) ok = ok && make_map_mn(&p.tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->ldb, bn_cta / 64);
+  // MN-major B: b_rows (when given) is the number of stored K rows (stacked per-expert weights are taller than K)
+  if (a->b_mn) ok = ok && make_map_mn(&p.tmB, a->B, (uint64_t)a->N, (uint64_t)(a->b_rows ? a->b_rows : a->K), (uint64_t)a->ldb, bn_cta / 64);
   else         ok = ok && make_map_2d(&p.tmB, a->B, (uint64_t)a->K, b_rows, (uint64_t)a->ldb, BK,
                                       a->epi == EPI_GLU_FWD ? BN / 2 : bn_cta, CU_TENSOR_MAP_SWIZZLE_128B);
   if (a->epi != EPI_SCATTER) {
     if (a->ldd % 8 || (uintptr_t)a->D % 16) return set_error(-2, "gemm: D must be 16-byte aligned with ld %% 8 == 0");
     const uint64_t d_cols = (uint64_t)(a->d_cols ? a->d_cols : a->N);
-    ok = ok && make_map_2d(&p.tmD, a->D, d_cols, (uint64_t)a->M, (uint64_t)a->ldd, EPI_BOX_COLS, 32,
+    const uint64_t d_rows = (uint64_t)(a->d_rows ? a->d_rows : a->M);
+    ok = ok && make_map_2d(&p.tmD, a->D, d_cols, d_rows, (uint64_t)a->ldd, EPI_BOX_COLS, 32,
                            CU_TENSOR_MAP_SWIZZLE_64B);
     if (a->D2) {
       const uint64_t d2_cols = (uint64_t)(a->d2_cols ? a->d2_cols : 2 * a->N);
-      ok = ok && make_map_2d(&p.tmD2, a->D2, d2_cols, (uint64_t)a->M, (uint64_t)a->ldd2, EPI_BOX_COLS, 32,
+      ok = ok && make_map_2d(&p.tmD2, a->D2, d2_cols, d_rows, (uint64_t)a->ldd2, EPI_BOX_COLS, 32,
                              CU_TENSOR_MAP_SWIZZLE_64B);
     }
   }
   if (!ok) return last_error_code();
 
   const int tiles = p.m_units * p.n_tiles * cta_per_unit;
-  if (!ag && a->epi != EPI_SCATTER && ctas > tiles) ctas = tiles;
+  if (!ag && a->epi != EPI_SCATTER && a->tiles == nullptr && ctas > tiles) ctas = tiles;
+  if (a->tiles != nullptr && a->max_tiles > 0 && ctas > a->max_tiles * cta_per_unit) ctas = a->max_tiles * cta_per_unit;
   if (pair) {
     if (p.m_rotate % 2) p.m_rotate = 0; else p.m_rotate /= 2;   // rotation is only an ordering hint
   }

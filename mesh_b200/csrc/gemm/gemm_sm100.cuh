@@ -59,8 +59,24 @@ enum Activation : int { ACT_SILU = 0, ACT_GELU_TANH = 1 };
 
 constexpr int MAX_RANKS = 8;
 
+// Descriptor-driven (grouped / ragged) mode: the persistent kernel walks a device-resident list of tiles
+// instead of a dense grid, so problems whose sizes are only known on the GPU (tokens per expert after a
+// dispatch) run without a host round trip.  Coordinates are in elements of the stored matrices.
+struct TileDesc {
+  int a_mn0;      // first row (K-major A) or column (MN-major A) of this tile in A
+  int k0;         // first K coordinate (both operands)
+  int k_blocks;   // number of 64-wide K blocks
+  int b_mn0;      // first row (K-major B) or column (MN-major B) in B, expert offset included
+  int b_k0;       // extra K offset of B (MN-major stacked weights: expert * rows)
+  int d_row0;     // first output row
+  int d_col0;     // first output column
+  int pad;
+};
+
 struct Params {
   CUtensorMap tmA, tmB, tmD, tmD2;
+  const TileDesc* tiles;    // nullptr: dense grid
+  const int* n_tiles_dev;   // number of valid descriptors (device word)
   CUtensorMap tmA2;                    // all-gather: this rank's own rows, read straight from the source
   CUtensorMap tmRS[MAX_RANKS];         // reduce-scatter: rank o's receive buffer as a [.., 64]-column matrix
   int M, N, K;
@@ -197,6 +213,33 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, int n_til
 // PAIR: two CTAs of a cluster work on one 256-row tile with tcgen05 cta_group::2.  Each CTA loads
 // its own 128 rows of A and its own half of the B tile (plain TMA loads, no multicast); the
 // leader CTA issues the MMAs for both, so every SM pulls a third less from L2 per FLOP.
+struct Work {
+  int m0, ka0, kb0, k_blocks, bn0, d_row0, d_col0;
+};
+// Resolve tile number `tile` for the CTA with rank `cta_rank` in its pair.
+__device__ __forceinline__ Work get_work(const Params& p, int tile, int cta_rank, int ctas, int tile_n) {
+  Work w;
+  if (p.tiles != nullptr) {
+    const TileDesc d = p.tiles[tile];
+    w.m0 = d.a_mn0 + cta_rank * BM;
+    w.ka0 = d.k0;
+    w.kb0 = d.k0 + d.b_k0;
+    w.k_blocks = d.k_blocks;
+    w.bn0 = d.b_mn0;
+    w.d_row0 = d.d_row0 + cta_rank * BM;
+    w.d_col0 = d.d_col0;
+  } else {
+    TileCoord tc = tile_coord(tile, p.m_units, p.n_tiles, p.m_rotate);
+    w.m0 = (tc.m_idx * ctas + cta_rank) * BM;
+    w.ka0 = w.kb0 = 0;
+    w.k_blocks = p.k_blocks;
+    w.bn0 = tc.n_idx * tile_n;
+    w.d_row0 = w.m0;
+    w.d_col0 = w.bn0;
+  }
+  return w;
+}
+
 template <int A_MN, int B_MN, int EPI, bool AG, int BN_T, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS + (AG ? 32 * COMM_WARPS : 0), 1)
 gemm_kernel(const __grid_constant__ Params p) {
@@ -227,7 +270,9 @@ gemm_kernel(const __grid_constant__ Params p) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_tiles = p.m_units * p.n_tiles;   // a unit is one m-tile, or a pair of them
+  // a unit is one m-tile, or a pair of them; in descriptor mode the count lives on the device
+  const int total_tiles = p.tiles != nullptr ? *p.n_tiles_dev : p.m_units * p.n_tiles;
+  constexpr int TILE_N = (EPI == EPI_GLU_FWD) ? BN / 2 : BN;
   const int tile_first = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
 
   if (threadIdx.x == 0) {
@@ -262,9 +307,8 @@ gemm_kernel(const __grid_constant__ Params p) {
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
-        TileCoord tc = tile_coord(tile, p.m_units, p.n_tiles, p.m_rotate);
-        const int m0 = (tc.m_idx * CTAS + (int)cta_rank) * BM;
-        const int n0 = tc.n_idx * (EPI == EPI_GLU_FWD ? BN / 2 : BN);
+        const Work wk = get_work(p, tile, (int)cta_rank, CTAS, TILE_N);
+        const int m0 = wk.m0, n0 = wk.bn0;
         // all-gather: this rank's own rows are read straight from the source shard (no wait);
         // rows that arrive from other GPUs wait for their arrival counter.
         const int own_lo = AG ? p.rank * p.ag_rows_per_rank : 0;
@@ -274,7 +318,8 @@ gemm_kernel(const __grid_constant__ Params p) {
           if (!ok) { *abort_smem = 1; break; }
           fence_proxy_async_all();   // data was written through the generic proxy, TMA reads it
         }
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = 0; kb < wk.k_blocks; ++kb) {
+          const int ka = wk.ka0 + kb * BK, kbb = wk.kb0 + kb * BK;      // K coordinates in A and in B
           ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, p.status, SITE_SMEM_EMPTY);
           if (!ok) break;
           const uint32_t sA = sA0 + stage * A_STAGE_BYTES;
@@ -282,31 +327,31 @@ gemm_kernel(const __grid_constant__ Params p) {
           if constexpr (!PAIR) {
             const uint32_t fb = full_bar(stage);
             mbar_expect_tx(fb, STAGE_BYTES);
-            if (A_MN) tma_load_3d(sA, &p.tmA, fb, 0, kb * BK, m0 / 64);
-            else if (own) tma_load_2d(sA, &p.tmA2, fb, kb * BK, m0 - own_lo);
-            else      tma_load_2d(sA, &p.tmA, fb, kb * BK, m0);
+            if (A_MN) tma_load_3d(sA, &p.tmA, fb, 0, ka, m0 / 64);
+            else if (own) tma_load_2d(sA, &p.tmA2, fb, ka, m0 - own_lo);
+            else      tma_load_2d(sA, &p.tmA, fb, ka, m0);
             if (EPI == EPI_GLU_FWD) {
-              tma_load_2d(sB, &p.tmB, fb, kb * BK, n0);
-              tma_load_2d(sB + B_STAGE_BYTES / 2, &p.tmB, fb, kb * BK, p.b_up_rows + n0);
+              tma_load_2d(sB, &p.tmB, fb, kbb, n0);
+              tma_load_2d(sB + B_STAGE_BYTES / 2, &p.tmB, fb, kbb, p.b_up_rows + n0);
             } else if (B_MN) {
-              tma_load_3d(sB, &p.tmB, fb, 0, kb * BK, n0 / 64);
+              tma_load_3d(sB, &p.tmB, fb, 0, kbb, n0 / 64);
             } else {
-              tma_load_2d(sB, &p.tmB, fb, kb * BK, n0);
+              tma_load_2d(sB, &p.tmB, fb, kbb, n0);
             }
           } else {
             // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
             if (cta_rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
             const uint32_t fb = mapa_u32(full_bar(stage), 0);
-            if (A_MN) tma_load_3d_pair(sA, &p.tmA, fb, 0, kb * BK, m0 / 64);
-            else if (own) tma_load_2d_pair(sA, &p.tmA2, fb, kb * BK, m0 - own_lo);
-            else      tma_load_2d_pair(sA, &p.tmA, fb, kb * BK, m0);
+            if (A_MN) tma_load_3d_pair(sA, &p.tmA, fb, 0, ka, m0 / 64);
+            else if (own) tma_load_2d_pair(sA, &p.tmA2, fb, ka, m0 - own_lo);
+            else      tma_load_2d_pair(sA, &p.tmA, fb, ka, m0);
             if (EPI == EPI_GLU_FWD) {
               // leader stages the gate rows, its peer the up rows: accumulator columns [0,128) | [128,256)
-              tma_load_2d_pair(sB, &p.tmB, fb, kb * BK, (cta_rank ? p.b_up_rows : 0) + n0);
+              tma_load_2d_pair(sB, &p.tmB, fb, kbb, (cta_rank ? p.b_up_rows : 0) + n0);
             } else if (B_MN) {
-              tma_load_3d_pair(sB, &p.tmB, fb, 0, kb * BK, (n0 + (int)cta_rank * BN_CTA) / 64);
+              tma_load_3d_pair(sB, &p.tmB, fb, 0, kbb, (n0 + (int)cta_rank * BN_CTA) / 64);
             } else {
-              tma_load_2d_pair(sB, &p.tmB, fb, kb * BK, n0 + (int)cta_rank * BN_CTA);
+              tma_load_2d_pair(sB, &p.tmB, fb, kbb, n0 + (int)cta_rank * BN_CTA);
             }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -328,7 +373,8 @@ gemm_kernel(const __grid_constant__ Params p) {
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int tile_k_blocks = p.tiles != nullptr ? p.tiles[tile].k_blocks : p.k_blocks;
+        for (int kb = 0; kb < tile_k_blocks; ++kb) {
           ok = mbar_wait(full_bar(stage), phase, abort_smem, p.status, SITE_SMEM_FULL);
           if (!ok) break;
           tc_fence_after();
@@ -380,8 +426,8 @@ gemm_kernel(const __grid_constant__ Params p) {
       }
     };
     for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step, ++t) {
-      TileCoord tc = tile_coord(tile, p.m_units, p.n_tiles, p.m_rotate);
-      const int m0 = (tc.m_idx * CTAS + (int)cta_rank) * BM;
+      const Work wk = get_work(p, tile, (int)cta_rank, CTAS, TILE_N);
+      const int m0 = wk.d_row0;
       const int acc = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
       ok = mbar_wait(tfull_bar(acc), acc_phase, abort_smem, p.status, SITE_TMEM_FULL);
@@ -391,7 +437,7 @@ gemm_kernel(const __grid_constant__ Params p) {
       const int grow = m0 + row_in_tile;
 
       if constexpr (EPI == EPI_STORE) {
-        const int n0 = tc.n_idx * BN;
+        const int n0 = wk.d_col0;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           if (n0 + c * 32 >= p.N) break;
@@ -406,7 +452,7 @@ gemm_kernel(const __grid_constant__ Params p) {
           emit_box(&p.tmD, box, n0 + c * 32, m0 + q * 32);
         }
       } else if constexpr (EPI == EPI_GLU_FWD) {
-        const int n0 = tc.n_idx * (BN / 2);
+        const int n0 = wk.d_col0;
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           if (n0 + c * 32 >= p.N) break;
@@ -437,7 +483,7 @@ gemm_kernel(const __grid_constant__ Params p) {
       } else if constexpr (EPI == EPI_GLU_BWD) {
         // g,u are fetched with coalesced loads (4 lanes per 64-byte row segment), one chunk
         // ahead, transposed through the staging boxes, and the same boxes then carry dg,du out.
-        const int n0 = tc.n_idx * BN;
+        const int n0 = wk.d_col0;
         const int lrow = lane >> 2, lchunk = lane & 3;        // loader role: row (of 8), 16-byte chunk
         const int n_chunks = min(BN / 32, (p.N - n0 + 31) / 32);
         uint4 gq[4], uq[4];
@@ -513,10 +559,11 @@ gemm_kernel(const __grid_constant__ Params p) {
         const int owner_m_tile = (m0 - owner * p.rs_rows_per_rank) / BM;
         const int m_tiles_local = p.rs_rows_per_rank / BM;
         // row of the [.., 64]-column view where this warp's first box of the tile starts
-        const int row_base = (((p.rank * m_tiles_local + owner_m_tile) * p.n_tiles + tc.n_idx) * (BN / 64)) * BM + q * 32;
+        const int n_idx = wk.d_col0 / BN;
+        const int row_base = (((p.rank * m_tiles_local + owner_m_tile) * p.n_tiles + n_idx) * (BN / 64)) * BM + q * 32;
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
-          if (tc.n_idx * BN + c * 64 >= p.N) break;
+          if (n_idx * BN + c * 64 >= p.N) break;
           if (lane == 0) tma_store_wait_read<1>();     // two 4 KiB boxes per warp, used alternately
           __syncwarp();
           const uint32_t box = my_staging + (c & 1) * 2 * EPI_BOX_BYTES;
@@ -543,7 +590,7 @@ gemm_kernel(const __grid_constant__ Params p) {
           tma_store_wait_all<0>();
           fence_proxy_async_all();
           __threadfence_system();
-          red_release_sys_add(p.rs_count[owner] + owner_m_tile * p.n_tiles + tc.n_idx, 1u);
+          red_release_sys_add(p.rs_count[owner] + owner_m_tile * p.n_tiles + n_idx, 1u);
         }
         __syncwarp();
       }
