@@ -431,6 +431,7 @@ gemm_kernel(const __grid_constant__ Params p) {
       const int acc = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
       ok = mbar_wait(tfull_bar(acc), acc_phase, abort_smem, p.status, SITE_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);      // tcgen05.ld below is warp-collective
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;

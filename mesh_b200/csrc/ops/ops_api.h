@@ -27,6 +27,21 @@ int mesh_rope(void* x, const int* positions, const float* cos_t, const float* si
 int mesh_router_topk(const void* logits, int logits_is_fp32, const float* bias, float* weights, int* indices,
                      int tokens, int experts, int k, int renorm, void* stream);
 
+// Flash attention forward (tcgen05).  q/k/v are 2-D row-major views: row = batch * T + token, head h of q at
+// columns [q_col0 + h*head_dim, ...) of a matrix with `q_cols` columns and leading dimension ldq (same for k, v with
+// KV heads).  Logical positions for the masks: q_pos = q_off + i*q_stride, k_pos = k_off + j*k_stride.
+typedef struct MeshFlashArgs {
+  const void* q; const void* k; const void* v; void* out; float* lse;
+  long long ldq, ldk, ldv, ldo;
+  int q_cols, k_cols, v_cols, q_col0, k_col0, v_col0;
+  int B, H, Hkv, Tq, Tk, head_dim;
+  int causal, window;
+  int q_off, q_stride, k_off, k_stride;
+  float scale;
+  void* status;
+} MeshFlashArgs;
+int mesh_flash_attention_fwd(const MeshFlashArgs* a, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -177,8 +177,7 @@ class E2BDecoder:
         comm = self.ctx.comm if self.world > 1 else None
         x = self.emb[prompt.reshape(-1).long()]                                       # [B*T, d]
         positions = torch.arange(T, dtype=torch.int32, device=self.dev).repeat(B)
-        pos0 = torch.zeros(B, dtype=torch.int32, device=self.dev)
-        att = D.DecodeAttention(B, self.qh, self.kvh, hd, splits=2, tokens_per_seq=T, device=self.dev)
+        from ..ops.attention import flash_attention
         att_out = torch.empty((B * T, self.qh * hd), dtype=torch.bfloat16, device=self.dev)
         for l, L in enumerate(self.layers):
             h, _, _ = rmsnorm_fwd(x, L["n1"], c.eps)
@@ -190,8 +189,9 @@ class E2BDecoder:
             vv = qkv[:, (self.qh + self.kvh) * hd:].view(B * T, self.kvh, hd)
             L["kc"][:, :, :T].copy_(kv.view(B, T, self.kvh, hd).transpose(1, 2))
             L["vc"][:, :, :T].copy_(vv.view(B, T, self.kvh, hd).transpose(1, 2))
-            q = qv.contiguous().view(B, T, self.qh, hd)
-            att(q, L["kc"], L["vc"], pos0, att_out, window=c.window if c.is_local(l) else 0)
+            # prefill attention straight from the fused qkv matrix (tcgen05 flash attention; no copies of q, k, v)
+            flash_attention(qv.view(B, T, self.qh, hd), kv.view(B, T, self.kvh, hd), vv.view(B, T, self.kvh, hd), causal=True,
+                            window=c.window if c.is_local(l) else 0, out=att_out.view(B, T, self.qh, hd))
             o = gemm(att_out, L["wo"])
             if comm is not None:
                 comm.all_reduce(o)

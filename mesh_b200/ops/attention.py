@@ -1,0 +1,123 @@
+"""Attention on the hand-written kernels: flash forward (tcgen05), partial-result merging, ring attention.
+
+Reference semantics: blockwise online-softmax attention with ring rotation over context-parallel ranks, striped
+logical positions, GQA (compiler/mesh_compiler/operations.py:7081-7166; placement ``units="striped"``,
+placement.py:57-69).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .. import _native
+from ..utils.status import status_block
+
+
+class _Flash(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p), ("lse", c_void_p),
+                ("ldq", c_longlong), ("ldk", c_longlong), ("ldv", c_longlong), ("ldo", c_longlong),
+                ("q_cols", c_int), ("k_cols", c_int), ("v_cols", c_int), ("q_col0", c_int), ("k_col0", c_int), ("v_col0", c_int),
+                ("B", c_int), ("H", c_int), ("Hkv", c_int), ("Tq", c_int), ("Tk", c_int), ("head_dim", c_int),
+                ("causal", c_int), ("window", c_int), ("q_off", c_int), ("q_stride", c_int), ("k_off", c_int),
+                ("k_stride", c_int), ("scale", c_float), ("status", c_void_p)]
+
+
+def _view2d(t: torch.Tensor):
+    """``t [B, T, H, hd]`` (possibly a column slice of a wider fused matrix) -> (base ptr of the row-major parent, ld, col0)."""
+    B, T, H, hd = t.shape
+    assert t.stride(3) == 1 and t.stride(2) == hd and (B == 1 or t.stride(0) == T * t.stride(1)), \
+        "need [B, T, H, hd] with dense heads and batch entries back to back"
+    return t.data_ptr(), t.stride(1), H * hd
+
+
+def flash_attention(q, k, v, *, causal=True, window=0, scale=None, q_off=0, q_stride=1, k_off=0, k_stride=1,
+                    need_lse=False, out=None):
+    """``q [B, Tq, H, hd]``, ``k, v [B, Tk, Hkv, hd]`` bf16 -> ``out [B, Tq, H, hd]`` (and ``lse [B, H, Tq]``)."""
+    B, Tq, H, hd = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    scale = hd ** -0.5 if scale is None else scale
+    if out is None:
+        out = torch.empty((B, Tq, H, hd), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device) if need_lse else None
+    a = _Flash()
+    a.q, a.ldq, a.q_cols = _view2d(q)
+    a.k, a.ldk, a.k_cols = _view2d(k)
+    a.v, a.ldv, a.v_cols = _view2d(v)
+    a.out, a.ldo = out.data_ptr(), out.stride(1)
+    a.lse = 0 if lse is None else lse.data_ptr()
+    a.B, a.H, a.Hkv, a.Tq, a.Tk, a.head_dim = B, H, Hkv, Tq, Tk, hd
+    a.causal, a.window = int(causal), int(window)
+    a.q_off, a.q_stride, a.k_off, a.k_stride = q_off, q_stride, k_off, k_stride
+    a.scale = scale
+    a.status = status_block(q.device).data_ptr()
+    rc = _native.lib().mesh_flash_attention_fwd(ctypes.byref(a), c_void_p(torch.cuda.current_stream().cuda_stream))
+    _native.check(rc, "mesh_flash_attention_fwd")
+    _native.count_launch()
+    return (out, lse) if need_lse else out
+
+
+def merge_partials(o1, lse1, o2, lse2):
+    """Merge two attention results over disjoint key sets: ``o [B, T, H, hd]``, ``lse [B, H, T]``."""
+    m = torch.maximum(lse1, lse2)
+    m_safe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    w1, w2 = torch.exp(lse1 - m_safe), torch.exp(lse2 - m_safe)
+    tot = w1 + w2
+    inv = torch.where(tot > 0, 1.0 / tot, torch.zeros_like(tot))
+    a1 = (w1 * inv).transpose(1, 2).unsqueeze(-1)
+    a2 = (w2 * inv).transpose(1, 2).unsqueeze(-1)
+    o = (o1.float() * a1 + o2.float() * a2).to(o1.dtype)
+    return o, m_safe + torch.log(torch.where(tot > 0, tot, torch.ones_like(tot))) + torch.where(tot > 0, 0.0, float("-inf"))
+
+
+def ring_attention(q, k, v, comm, *, causal=True, striped=False, scale=None):
+    """Context-parallel attention: every rank holds a sequence shard of q, k, v (contiguous blocks, or striped
+    tokens ``r, r+P, ...``); the KV shards travel around the ring while each rank attends its queries to the chunk
+    it currently holds, starting with its own (the reference rotates the key loop to start at the rank's own block,
+    operations.py:7089-7094), and partial results are merged by their log-sum-exp.  Chunks that the causal mask
+    hides completely are skipped."""
+    P, r = comm.world, comm.rank
+    B, T, H, hd = q.shape
+    kv = torch.stack([k, v]).contiguous()
+    o, lse = None, None
+    for step in range(P):
+        src = (r - step) % P                                  # whose KV chunk we hold at this step
+        if striped:
+            q_off, q_stride, k_off, k_stride = r, P, src, P
+        else:
+            q_off, q_stride, k_off, k_stride = r * T, 1, src * T, 1
+        visible = (not causal) or striped or src <= r
+        nxt = None
+        if step + 1 < P:                                      # pass the chunk on while we compute
+            nxt = torch.empty_like(kv)
+            comm.permute(nxt, kv, [(j, (j + 1) % P) for j in range(P)])
+        if visible:
+            oi, li = flash_attention(q, kv[0], kv[1], causal=causal, scale=scale, q_off=q_off, q_stride=q_stride,
+                                     k_off=k_off, k_stride=k_stride, need_lse=True)
+            o, lse = (oi, li) if o is None else merge_partials(o, lse, oi, li)
+        if nxt is not None:
+            kv = nxt
+    return o, lse
+
+
+def attention_ref(q, k, v, causal=True, window=0, scale=None, q_off=0, q_stride=1, k_off=0, k_stride=1):
+    """fp32 PyTorch statement (oracle)."""
+    B, Tq, H, hd = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    scale = hd ** -0.5 if scale is None else scale
+    kf = k.float().repeat_interleave(H // Hkv, 2)
+    vf = v.float().repeat_interleave(H // Hkv, 2)
+    s = torch.einsum("bthd,bshd->bhts", q.float(), kf) * scale
+    qp = q_off + torch.arange(Tq, device=q.device) * q_stride
+    kp = k_off + torch.arange(Tk, device=q.device) * k_stride
+    mask = torch.zeros(Tq, Tk, dtype=torch.bool, device=q.device)
+    if causal:
+        mask |= kp[None, :] > qp[:, None]
+    if window > 0:
+        mask |= kp[None, :] <= qp[:, None] - window
+    s = s.masked_fill(mask[None, None], float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    p = torch.softmax(s, -1)
+    p = torch.where(torch.isnan(p), torch.zeros_like(p), p)
+    return torch.einsum("bhts,bshd->bthd", p, vf), lse

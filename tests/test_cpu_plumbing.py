@@ -76,3 +76,23 @@ def _ffn_rank(rank, world, rdv):
 
 def test_tp2_swiglu_ffn_matches_single_device():
     spawn_ranks(_ffn_rank, 2, init_pg="gloo")
+
+
+def _dp_rank(rank, world, rdv):
+    from mesh_b200.parallel.dp import DataParallel
+    torch.manual_seed(0)
+    m = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+    ref = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+    ref.load_state_dict(m.state_dict())
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(8 * world, 16, generator=g)
+    dp = DataParallel(m, world, rank, bucket_bytes=1024)
+    m(x[rank * 8:(rank + 1) * 8]).pow(2).mean().backward()
+    dp.finish()
+    ref(x).pow(2).mean().backward()                       # the full batch on one device
+    for a, b in zip(m.parameters(), ref.parameters()):
+        assert torch.allclose(a.grad, b.grad, atol=1e-6)
+
+
+def test_data_parallel_overlapped_reduce_scatter_matches_full_batch():
+    spawn_ranks(_dp_rank, 2, init_pg="gloo")
