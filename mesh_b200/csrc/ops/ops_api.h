@@ -42,6 +42,18 @@ typedef struct MeshFlashArgs {
 } MeshFlashArgs;
 int mesh_flash_attention_fwd(const MeshFlashArgs* a, void* stream);
 
+// Backward of the same attention: `fwd` describes q, k, v, the masks and `lse` exactly as in the forward call.
+// `dq` is a zero-initialised fp32 accumulator [B*Tq, ld_dq]; dk/dv are bf16 outputs [B*Tk, ld_dkv], unless the
+// fp32 accumulators dk_acc/dv_acc are given, which are added to instead (a KV chunk visited by several ranks).
+typedef struct MeshFlashBwdArgs {
+  MeshFlashArgs fwd;
+  const void* dout; const float* delta;
+  long long ld_do; int do_cols, do_col0;
+  float* dq; void* dk; void* dv; float* dk_acc; float* dv_acc;
+  long long ld_dq, ld_dkv;
+} MeshFlashBwdArgs;
+int mesh_flash_attention_bwd(const MeshFlashBwdArgs* a, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

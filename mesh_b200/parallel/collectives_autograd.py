@@ -10,20 +10,60 @@ import torch
 import torch.distributed as dist
 
 
+def _comm_of(group, t):
+    """``group`` may be a torch.distributed group or an axis context (``parallel/topology.py``); CUDA tensors of an
+    axis that has a symmetric heap go through this package's collective kernels."""
+    if hasattr(group, "ranks") and hasattr(group, "world"):
+        if t.is_cuda and group._heap is not None:
+            return group.comm, None
+        return None, group.group
+    return None, group
+
+
+def _world(group) -> int:
+    if hasattr(group, "ranks") and hasattr(group, "world"):
+        return group.world
+    return dist.get_world_size(group)
+
+
+def _ag(out, x, group):
+    comm, g = _comm_of(group, x)
+    if comm is not None:
+        comm.all_gather(out, x)
+    else:
+        dist.all_gather_into_tensor(out, x, group=g)
+
+
+def _rs(out, x, group):
+    comm, g = _comm_of(group, x)
+    if comm is not None:
+        comm.reduce_scatter(out, x)
+    else:
+        dist.reduce_scatter_tensor(out, x, group=g)
+
+
+def _ar(x, group):
+    comm, g = _comm_of(group, x)
+    if comm is not None:
+        comm.all_reduce(x)
+    else:
+        dist.all_reduce(x, group=g)
+
+
 class _AllGather(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         ctx.group = group
-        w = dist.get_world_size(group)
+        w = _world(group)
         out = torch.empty((x.shape[0] * w, *x.shape[1:]), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        _ag(out, x.contiguous(), group)
         return out
 
     @staticmethod
     def backward(ctx, g):
-        w = dist.get_world_size(ctx.group)
+        w = _world(ctx.group)
         out = torch.empty((g.shape[0] // w, *g.shape[1:]), dtype=g.dtype, device=g.device)
-        dist.reduce_scatter_tensor(out, g.contiguous(), group=ctx.group)
+        _rs(out, g.contiguous(), ctx.group)
         return out, None
 
 
@@ -31,16 +71,16 @@ class _ReduceScatter(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         ctx.group = group
-        w = dist.get_world_size(group)
+        w = _world(group)
         out = torch.empty((x.shape[0] // w, *x.shape[1:]), dtype=x.dtype, device=x.device)
-        dist.reduce_scatter_tensor(out, x.contiguous(), group=group)
+        _rs(out, x.contiguous(), group)
         return out
 
     @staticmethod
     def backward(ctx, g):
-        w = dist.get_world_size(ctx.group)
+        w = _world(ctx.group)
         out = torch.empty((g.shape[0] * w, *g.shape[1:]), dtype=g.dtype, device=g.device)
-        dist.all_gather_into_tensor(out, g.contiguous(), group=ctx.group)
+        _ag(out, g.contiguous(), ctx.group)
         return out, None
 
 
@@ -48,7 +88,7 @@ class _AllReduce(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         y = x.clone()
-        dist.all_reduce(y, group=group)
+        _ar(y, group)
         return y
 
     @staticmethod
@@ -67,7 +107,7 @@ class _CopyToTP(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         g = g.clone()
-        dist.all_reduce(g, group=ctx.group)
+        _ar(g, ctx.group)
         return g, None
 
 

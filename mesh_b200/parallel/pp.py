@@ -1,0 +1,140 @@
+"""Pipeline parallelism: one-forward-one-backward schedule over point-to-point sends (NCCL on GPUs, gloo on CPU).
+
+The reference pipelines by placing layers on different processors, whose crossing edges become send/recv
+(examples/engines.py:91-96), and by keeping several executions of a plan in flight (``copies`` / ``horizon``,
+rdma/mesh-flow.c:7-12); it names no training schedule.  This module adds the usual one: stage ``s`` of ``P`` runs
+``P - s - 1`` warm-up forwards, then alternates one forward with one backward, then drains the backwards, so at most
+``P - s`` microbatches of activations are alive on a stage.  A send toward a neighbour and the receive of the
+opposite direction from the same neighbour are issued as one batch, which is what keeps two stages that both want
+to send first from waiting on each other.
+"""
+from __future__ import annotations
+
+from typing import Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+class _Wire:
+    """Batched point-to-point along the pipeline axis."""
+
+    def __init__(self, axis):
+        self.axis = axis
+        self.prev = None if axis.first else axis.peer(-1)
+        self.next = None if axis.last else axis.peer(+1)
+        self.sent_bytes = 0
+
+    def exchange(self, send_prev=None, send_next=None, recv_prev=None, recv_next=None):
+        ops = []
+        g = self.axis.group
+        for t, peer, fn in ((send_prev, self.prev, dist.isend), (recv_prev, self.prev, dist.irecv),
+                            (send_next, self.next, dist.isend), (recv_next, self.next, dist.irecv)):
+            if t is not None and peer is not None:
+                ops.append(dist.P2POp(fn, t, peer, group=g))
+                if fn is dist.isend:
+                    self.sent_bytes += t.numel() * t.element_size()
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+
+
+def run_1f1b(stage: Callable[[torch.Tensor], torch.Tensor], axis, microbatches: Sequence, *,
+             act_shape: Sequence[int], act_dtype: torch.dtype, loss_fn: Callable | None = None,
+             targets: Sequence | None = None, grad_scale: float | None = None):
+    """Run one training step of a pipeline stage.
+
+    ``stage(x)`` maps the activations received from the previous stage (on the first stage: the microbatch itself)
+    to the activations for the next one.  On the last stage ``loss_fn(y, target)`` turns them into a scalar; its
+    gradient is scaled by ``grad_scale`` (default ``1 / len(microbatches)``), so parameter gradients come out as the
+    mean over microbatches.  ``microbatches`` must have the same length on every stage (only the first stage reads
+    the entries).  Returns the list of microbatch losses on the last stage (``[]`` elsewhere) and statistics.
+    """
+    M = len(microbatches)
+    P, s = axis.world, axis.rank
+    wire = _Wire(axis)
+    scale = 1.0 / M if grad_scale is None else grad_scale
+    dev = axis.device
+    warm = min(P - s - 1, M)
+    rem = M - warm
+    alive: list[tuple] = []            # (input, output) of forwards whose backward has not run
+    losses: list[torch.Tensor] = []
+    peak_alive = 0
+
+    def new_act():
+        return torch.empty(tuple(act_shape), dtype=act_dtype, device=dev)
+
+    def forward(i: int, x_in):
+        nonlocal peak_alive
+        if axis.first:
+            x = microbatches[i]
+        else:
+            x = x_in.requires_grad_(True)
+        y = stage(x)
+        if axis.last:
+            if loss_fn is None:
+                raise ValueError("the last stage needs loss_fn")
+            loss = loss_fn(y, None if targets is None else targets[i])
+            losses.append(loss.detach())
+            y = loss
+        alive.append((x, y))
+        peak_alive = max(peak_alive, len(alive))
+        return y
+
+    def backward(gy):
+        x, y = alive.pop(0)
+        if axis.last:
+            (y * scale).backward()
+        else:
+            torch.autograd.backward(y, gy)
+        if axis.first:
+            return None
+        g = x.grad
+        x.grad = None
+        return g
+
+    # ---- warm-up forwards
+    for i in range(warm):
+        x_in = None
+        if not axis.first:
+            x_in = new_act()
+            wire.exchange(recv_prev=x_in)
+        y = forward(i, x_in)
+        wire.exchange(send_next=None if axis.last else y.detach())
+    # ---- steady state
+    x_in = None
+    if rem > 0 and not axis.first:
+        x_in = new_act()
+        wire.exchange(recv_prev=x_in)
+    for i in range(rem):
+        y = forward(warm + i, x_in)
+        gy = None
+        if not axis.last:
+            gy = new_act()
+            wire.exchange(send_next=y.detach(), recv_next=gy)
+        gx = backward(gy)
+        if i + 1 < rem:
+            x_in = None if axis.first else new_act()
+            wire.exchange(send_prev=gx, recv_prev=x_in)
+        else:
+            wire.exchange(send_prev=gx)
+    # ---- drain
+    for _ in range(warm):
+        gy = None
+        if not axis.last:
+            gy = new_act()
+            wire.exchange(recv_next=gy)
+        gx = backward(gy)
+        wire.exchange(send_prev=gx)
+    return losses, {"peak_alive": peak_alive, "sent_bytes": wire.sent_bytes, "microbatches": M}
+
+
+def split_layers(n_layers: int, stages: int) -> list[range]:
+    """Contiguous layer ranges per stage, earlier stages taking the remainder."""
+    base, extra = divmod(n_layers, stages)
+    out, lo = [], 0
+    for s in range(stages):
+        n = base + (1 if s < extra else 0)
+        out.append(range(lo, lo + n))
+        lo += n
+    return out

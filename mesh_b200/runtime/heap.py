@@ -59,6 +59,53 @@ class SymmBuffer:
         return [self.heap.peer_ptrs[r] + self.offset for r in range(self.heap.world)]
 
 
+class HeapGroup:
+    """A subset of a heap's ranks seen as a heap of its own: ``rank`` and ``world`` are positions within the
+    group, and buffers resolve peer pointers through the group's member list, so a communicator, a fused layer or a
+    model built on it talks to the members only (a tensor-, context- or expert-parallel axis of a larger job; the
+    reference's submeshes, mesh/api.py:40-120).
+
+    Allocation moves the parent's bump pointer.  The heap stays symmetric as long as every rank of the job makes the
+    same sequence of allocations, each through its own group of an axis (groups of one axis have equal sizes)."""
+
+    def __init__(self, heap: "SymmetricHeap", ranks):
+        ranks = [int(r) for r in ranks]
+        if heap.rank not in ranks:
+            raise ValueError(f"rank {heap.rank} is not a member of group {ranks}")
+        if len(set(ranks)) != len(ranks) or any(not 0 <= r < heap.world for r in ranks):
+            raise ValueError(f"bad group {ranks} for a heap of {heap.world} ranks")
+        self.parent, self.ranks = heap, ranks
+        self.rank, self.world = ranks.index(heap.rank), len(ranks)
+        self.device = heap.device
+        self.peer_ptrs = [heap.peer_ptrs[r] for r in ranks]
+        self.mc_ptr = 0                      # the multicast mapping spans all ranks of the parent
+
+    def _wrap(self, b: "SymmBuffer") -> "SymmBuffer":
+        return SymmBuffer(self, b.offset, b.nbytes, b.shape, b.dtype)
+
+    def alloc(self, shape, dtype=torch.bfloat16, align: int = 1024) -> "SymmBuffer":
+        return self._wrap(self.parent.alloc(shape, dtype, align))
+
+    def alloc_signals(self, count: int) -> "SymmBuffer":
+        return self._wrap(self.parent.alloc_signals(count))
+
+    def view(self, offset: int, shape, dtype) -> torch.Tensor:
+        return self.parent.view(offset, shape, dtype)
+
+    def mark(self):
+        return self.parent.mark()
+
+    def release(self, mark) -> None:
+        self.parent.release(mark)
+
+    def group(self, ranks) -> "HeapGroup":
+        """Sub-group given by positions within this group."""
+        return HeapGroup(self.parent, [self.ranks[r] for r in ranks])
+
+    def close(self) -> None:               # the parent owns the memory
+        pass
+
+
 class SymmetricHeap:
     def __init__(self, rdv: Rendezvous, nbytes: int, device: int, *, signal_bytes: int = 1 << 20,
                  multicast: bool = False, mode: str = "auto"):
@@ -201,6 +248,10 @@ class SymmetricHeap:
             n *= s
         nbytes = n * torch.empty((), dtype=dtype).element_size()
         return self._bytes[offset:offset + nbytes].view(dtype).view(*shape)
+
+    def group(self, ranks) -> HeapGroup:
+        """The ranks ``ranks`` (which must include this one) as a heap of their own."""
+        return HeapGroup(self, ranks)
 
     def mark(self) -> tuple[int, int]:
         return self._bump, self._sig_bump

@@ -71,3 +71,67 @@ def test_ring_attention_two_ranks(striped):
         pytest.skip("needs 2 GPUs")
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_ring_rank, 2, striped, use_cuda=True)
+
+
+def _ref_grads(q, k, v, dout, causal, window):
+    from mesh_b200.ops.attention import attention_ref
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    o, _ = attention_ref(qf, kf, vf, causal, window)
+    o.backward(dout.float())
+    return qf.grad, kf.grad, vf.grad
+
+
+@pytest.mark.parametrize("hd,H,Hkv", [(128, 4, 4), (128, 4, 2), (64, 2, 1)])
+@pytest.mark.parametrize("T,causal,window", [(256, True, 0), (384, True, 100), (200, False, 0)])
+def test_flash_backward(hd, H, Hkv, T, causal, window):
+    from mesh_b200.ops.attention import attention
+    from mesh_b200.utils.status import check_status
+    torch.manual_seed(1)
+    B = 2
+    q = torch.randn(B, T, H, hd, device="cuda").bfloat16().requires_grad_(True)
+    k = torch.randn(B, T, Hkv, hd, device="cuda").bfloat16().requires_grad_(True)
+    v = torch.randn(B, T, Hkv, hd, device="cuda").bfloat16().requires_grad_(True)
+    dout = torch.randn(B, T, H, hd, device="cuda").bfloat16()
+    out = attention(q, k, v, causal=causal, window=window)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    check_status()
+    dq, dk, dv = _ref_grads(q.detach(), k.detach(), v.detach(), dout, causal, window)
+    _close(q.grad, dq, 3e-2)
+    _close(k.grad, dk, 3e-2)
+    _close(v.grad, dv, 3e-2)
+
+
+def _ring_bwd_rank(rank, world, rdv, striped):
+    from mesh_b200.config import MeshConfig, set_config
+    from mesh_b200.distributed.context import MeshContext
+    from mesh_b200.ops.attention import ring_attention_autograd
+    from mesh_b200.utils.status import check_status
+    torch.cuda.set_device(rank)
+    set_config(MeshConfig.from_env(heap_bytes=512 << 20))
+    ctx = MeshContext(rank, world, torch.device("cuda", rank), rdv, None)
+    B, T, H, Hkv, hd = 1, 256 * world, 4, 2, 128
+    g = torch.Generator(device="cpu").manual_seed(0)
+    q = torch.randn(B, T, H, hd, generator=g).bfloat16().cuda()
+    k, v = (torch.randn(B, T, Hkv, hd, generator=g).bfloat16().cuda() for _ in range(2))
+    dout = torch.randn(B, T, H, hd, generator=g).bfloat16().cuda()
+    sl = slice(rank, T, world) if striped else slice(rank * (T // world), (rank + 1) * (T // world))
+    ql, kl, vl = (t[:, sl].contiguous().requires_grad_(True) for t in (q, k, v))
+    o = ring_attention_autograd(ql, kl, vl, ctx.comm, causal=True, striped=striped)
+    o.backward(dout[:, sl].contiguous())
+    torch.cuda.synchronize()
+    check_status()
+    dq, dk, dv = _ref_grads(q, k, v, dout, True, 0)
+    _close(ql.grad, dq[:, sl], 3e-2)
+    _close(kl.grad, dk[:, sl], 3e-2)
+    _close(vl.grad, dv[:, sl], 3e-2)
+    rdv.barrier("ring-bwd-done")
+    ctx.heap.close()
+
+
+@pytest.mark.parametrize("striped", [False, True])
+def test_ring_attention_backward_two_ranks(striped):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_ring_bwd_rank, 2, striped, use_cuda=True)
