@@ -53,18 +53,24 @@ int mesh_coll_reduce(const MeshCommArgs* c, const void* in, void* out, uint64_t 
                      void* stream);
 int mesh_coll_barrier(const MeshCommArgs* c, void* stream);
 
-// Point-to-point: the sender stores into the receiver's slot and raises `ready`; the receiver copies
-// out and raises `ack` on the sender.  `seq` is the per-(src,dst) message number, starting at 1.
-typedef struct MeshP2PArgs {
-  int rank, peer;
-  void* slot;               // send: the receiver's slot for this rank (peer pointer); recv: own slot for `peer`
-  uint32_t* ready;          // send: receiver's ready word (peer pointer); recv: own ready word
-  uint32_t* ack;            // send: own ack word; recv: sender's ack word (peer pointer)
-  uint32_t seq;
+// Pipelined exchange: this rank's sends (the same `in` to each listed peer) and its receive, in one launch.  A
+// channel is a (source, destination) pair with a ring of `depth` pieces of `piece` bytes in the source's memory;
+// `ready_base` / `ack_base` are the channel's counter totals before this message (nb arrivals per piece).
+typedef struct MeshXferChan {
+  void* slot;               // the ring: local for a send, on the peer for the receive
+  uint32_t* ready;          // counter at the receiver
+  uint32_t* ack;            // counter at the sender
+  uint32_t ready_base, ack_base;
+} MeshXferChan;
+typedef struct MeshXferArgs {
+  int n_send, has_recv, nb, depth;
+  MeshXferChan send[MESH_COLL_MAX_RANKS];
+  MeshXferChan recv;
+  const void* in; void* out;
+  uint64_t send_bytes, recv_bytes, piece;
   void* status;
-} MeshP2PArgs;
-int mesh_p2p_send(const MeshP2PArgs* a, const void* in, uint64_t bytes, void* stream);
-int mesh_p2p_recv(const MeshP2PArgs* a, void* out, uint64_t bytes, void* stream);
+} MeshXferArgs;
+int mesh_p2p_exchange(const MeshXferArgs* a, void* stream);
 
 // Test hook for the bounded-wait path: waits on a word nobody writes, with a short limit, and
 // returns normally after recording TIMEOUT in the status block.

@@ -10,7 +10,9 @@ namespace mesh {
 namespace coll {
 
 constexpr int THREADS = 512;
-constexpr int MAX_BLOCKS = 64;
+// One block per SM at most: every block waits for every block of every rank, so all of a launch's blocks must be
+// resident at once.
+constexpr int MAX_BLOCKS = 148;
 constexpr int R = MESH_COLL_MAX_RANKS;
 
 struct Comm {
@@ -40,11 +42,15 @@ __device__ void copy_bytes(uint8_t* __restrict__ dst, const uint8_t* __restrict_
     uint4* d = reinterpret_cast<uint4*>(dst);
     const uint64_t step = gsize();
     uint64_t i = gtid();
-    for (; i + 3 * step < nv; i += 4 * step) {
-      uint4 v0 = s[i], v1 = s[i + step], v2 = s[i + 2 * step], v3 = s[i + 3 * step];
-      d[i] = v0; d[i + step] = v1; d[i + 2 * step] = v2; d[i + 3 * step] = v3;
+    for (; i < nv; i += 4 * step) {        // all of a round's loads are issued before its first store
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i + u * step < nv) v[u] = s[i + u * step];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i + u * step < nv) d[i + u * step] = v[u];
     }
-    for (; i < nv; i += step) d[i] = s[i];
     for (uint64_t j = (nv << 4) + gtid(); j < n; j += step) dst[j] = src[j];
   } else {
     for (uint64_t j = gtid(); j < n; j += gsize()) dst[j] = src[j];
@@ -52,9 +58,10 @@ __device__ void copy_bytes(uint8_t* __restrict__ dst, const uint8_t* __restrict_
 }
 
 // All of this block's earlier stores are made visible system-wide, then one arrival on every
-// rank's counter for (step, this rank).
+// rank's counter for (step, this rank).  The barrier orders every thread's stores before the signalling threads,
+// whose system-scope release is cumulative over them: one fence per signalling thread instead of one per thread
+// of the block (a system-scope fence costs microseconds).
 __device__ __forceinline__ void signal_all(const Comm& c, int step) {
-  __threadfence_system();
   __syncthreads();
   if ((int)threadIdx.x < c.world)
     red_release_sys_add(c.arrived[threadIdx.x] + step * c.world + c.rank, 1u);
@@ -95,6 +102,74 @@ template <typename A> __device__ __forceinline__ A combine(A x, A y, int op) {
   }
 }
 
+// One 16-byte vector of the result from the `nw` vectors w[0..nw) (fixed order 0..nw-1).
+template <typename T, int NW>
+__device__ __forceinline__ uint4 reduce_vec(const uint4 (&w)[NW], int nw, int op, float avg) {
+  using A = typename Acc<T>::type;
+  constexpr int V = 16 / sizeof(T);
+  A acc[V];
+  const T* e0 = reinterpret_cast<const T*>(&w[0]);
+#pragma unroll
+  for (int k = 0; k < V; ++k) acc[k] = to_acc<T>(e0[k]);
+#pragma unroll
+  for (int r = 1; r < NW; ++r) {
+    if (r < nw) {
+      const T* e = reinterpret_cast<const T*>(&w[r]);
+#pragma unroll
+      for (int k = 0; k < V; ++k) acc[k] = combine<A>(acc[k], to_acc<T>(e[k]), op);
+    }
+  }
+  uint4 o;
+  T* eo = reinterpret_cast<T*>(&o);
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    if (op == MESH_AVG) acc[k] = (A)((float)acc[k] * avg);
+    eo[k] = from_acc<T>(acc[k]);
+  }
+  return o;
+}
+
+// Vector part of the pull reduction with the number of ranks W known at compile time and U vectors per thread in
+// flight from every rank (the loads cross NVLink: bytes in flight set the rate).
+template <typename T, int W, int U>
+__device__ void reduce_pull_vec(const Comm& c, uint64_t src_byte_off, T* __restrict__ out, uint64_t nv, int op) {
+  const float avg = 1.0f / (float)c.world;
+  const uint4* src[W];
+#pragma unroll
+  for (int r = 0; r < W; ++r) src[r] = reinterpret_cast<const uint4*>(c.staging[r < c.world ? r : 0] + src_byte_off);
+  const uint64_t step = gsize();
+  uint64_t i = gtid();
+  for (; i + (U - 1) * step < nv; i += U * step) {
+    uint4 w[U][W];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int r = 0; r < W; ++r)
+        if (r < c.world) w[u][r] = __ldcg(src[r] + i + u * step);
+#pragma unroll
+    for (int u = 0; u < U; ++u) reinterpret_cast<uint4*>(out)[i + u * step] = reduce_vec<T, W>(w[u], c.world, op, avg);
+  }
+  for (; i < nv; i += step) {
+    uint4 w[W];
+#pragma unroll
+    for (int r = 0; r < W; ++r)
+      if (r < c.world) w[r] = __ldcg(src[r] + i);
+    reinterpret_cast<uint4*>(out)[i] = reduce_vec<T, W>(w, c.world, op, avg);
+  }
+}
+
+template <typename T> __device__ __forceinline__ T ld_elem(const uint8_t* base, uint64_t i) {
+  return __ldcg(reinterpret_cast<const T*>(base) + i);
+}
+template <> __device__ __forceinline__ __nv_bfloat16 ld_elem<__nv_bfloat16>(const uint8_t* base, uint64_t i) {
+  unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(base) + i);
+  return *reinterpret_cast<__nv_bfloat16*>(&raw);
+}
+template <> __device__ __forceinline__ __half ld_elem<__half>(const uint8_t* base, uint64_t i) {
+  unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(base) + i);
+  return *reinterpret_cast<__half*>(&raw);
+}
+
 // out[i] = reduce over ranks (fixed order 0..world-1) of src_r[i], for i in [0, n): the sources
 // are `world` buffers at the same offset of each rank's staging.
 template <typename T>
@@ -102,100 +177,21 @@ __device__ void reduce_pull(const Comm& c, uint64_t src_byte_off, T* __restrict_
   using A = typename Acc<T>::type;
   constexpr int V = 16 / sizeof(T);
   const bool vec = (((uintptr_t)out) & 15) == 0 && (src_byte_off & 15) == 0;
-  const float avg = 1.0f / (float)c.world;
   uint64_t done = 0;
   if (vec) {
     const uint64_t nv = n / V;
-    for (uint64_t i = gtid(); i < nv; i += gsize()) {
-      uint4 w[R];
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-        if (r < c.world) w[r] = __ldcg(reinterpret_cast<const uint4*>(c.staging[r] + src_byte_off) + i);
-      A acc[V];
-      const T* e0 = reinterpret_cast<const T*>(&w[0]);
-#pragma unroll
-      for (int k = 0; k < V; ++k) acc[k] = to_acc<T>(e0[k]);
-#pragma unroll
-      for (int r = 1; r < R; ++r) {
-        if (r < c.world) {
-          const T* e = reinterpret_cast<const T*>(&w[r]);
-#pragma unroll
-          for (int k = 0; k < V; ++k) acc[k] = combine<A>(acc[k], to_acc<T>(e[k]), op);
-        }
-      }
-      uint4 o;
-      T* eo = reinterpret_cast<T*>(&o);
-#pragma unroll
-      for (int k = 0; k < V; ++k) {
-        if (op == MESH_AVG) acc[k] = (A)((float)acc[k] * avg);
-        eo[k] = from_acc<T>(acc[k]);
-      }
-      reinterpret_cast<uint4*>(out)[i] = o;
-    }
+    if (c.world <= 2) reduce_pull_vec<T, 2, 4>(c, src_byte_off, out, nv, op);
+    else if (c.world <= 4) reduce_pull_vec<T, 4, 2>(c, src_byte_off, out, nv, op);
+    else reduce_pull_vec<T, R, 1>(c, src_byte_off, out, nv, op);
     done = nv * V;
   }
+  const float avg = 1.0f / (float)c.world;
   for (uint64_t i = done + gtid(); i < n; i += gsize()) {
-    A acc = to_acc<T>(reinterpret_cast<const volatile T*>(c.staging[0] + src_byte_off)[i]);
-    for (int r = 1; r < c.world; ++r)
-      acc = combine<A>(acc, to_acc<T>(reinterpret_cast<const volatile T*>(c.staging[r] + src_byte_off)[i]), op);
+    A acc = to_acc<T>(ld_elem<T>(c.staging[0] + src_byte_off, i));
+    for (int r = 1; r < c.world; ++r) acc = combine<A>(acc, to_acc<T>(ld_elem<T>(c.staging[r] + src_byte_off, i)), op);
     if (op == MESH_AVG) acc = (A)((float)acc * avg);
     out[i] = from_acc<T>(acc);
   }
-}
-// volatile reads of bf16/half need plain types
-template <> __device__ void reduce_pull<__nv_bfloat16>(const Comm& c, uint64_t off, __nv_bfloat16* __restrict__ out,
-                                                      uint64_t n, int op);
-template <> __device__ void reduce_pull<__half>(const Comm& c, uint64_t off, __half* __restrict__ out, uint64_t n, int op);
-
-template <typename T16, typename Cvt>
-__device__ void reduce_pull16(const Comm& c, uint64_t src_byte_off, T16* __restrict__ out, uint64_t n, int op, Cvt) {
-  const bool vec = (((uintptr_t)out) & 15) == 0 && (src_byte_off & 15) == 0;
-  const float avg = 1.0f / (float)c.world;
-  uint64_t done = 0;
-  if (vec) {
-    const uint64_t nv = n / 8;
-    for (uint64_t i = gtid(); i < nv; i += gsize()) {
-      uint4 w[R];
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-        if (r < c.world) w[r] = __ldcg(reinterpret_cast<const uint4*>(c.staging[r] + src_byte_off) + i);
-      float acc[8];
-      const T16* e0 = reinterpret_cast<const T16*>(&w[0]);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] = to_acc<T16>(e0[k]);
-#pragma unroll
-      for (int r = 1; r < R; ++r) {
-        if (r < c.world) {
-          const T16* e = reinterpret_cast<const T16*>(&w[r]);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) acc[k] = combine<float>(acc[k], to_acc<T16>(e[k]), op);
-        }
-      }
-      uint4 o;
-      T16* eo = reinterpret_cast<T16*>(&o);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) eo[k] = from_acc<T16>(op == MESH_AVG ? acc[k] * avg : acc[k]);
-      reinterpret_cast<uint4*>(out)[i] = o;
-    }
-    done = nv * 8;
-  }
-  for (uint64_t i = done + gtid(); i < n; i += gsize()) {
-    const unsigned short* p0 = reinterpret_cast<const unsigned short*>(c.staging[0] + src_byte_off);
-    unsigned short raw = __ldcg(p0 + i);
-    float acc = to_acc<T16>(*reinterpret_cast<T16*>(&raw));
-    for (int r = 1; r < c.world; ++r) {
-      raw = __ldcg(reinterpret_cast<const unsigned short*>(c.staging[r] + src_byte_off) + i);
-      acc = combine<float>(acc, to_acc<T16>(*reinterpret_cast<T16*>(&raw)), op);
-    }
-    out[i] = from_acc<T16>(op == MESH_AVG ? acc * avg : acc);
-  }
-}
-template <> __device__ void reduce_pull<__nv_bfloat16>(const Comm& c, uint64_t off, __nv_bfloat16* __restrict__ out,
-                                                      uint64_t n, int op) {
-  reduce_pull16<__nv_bfloat16>(c, off, out, n, op, 0);
-}
-template <> __device__ void reduce_pull<__half>(const Comm& c, uint64_t off, __half* __restrict__ out, uint64_t n, int op) {
-  reduce_pull16<__half>(c, off, out, n, op, 0);
 }
 
 constexpr uint64_t HDR = MESH_COLL_HEADER_BYTES;
@@ -287,28 +283,87 @@ __global__ void __launch_bounds__(THREADS) barrier_kernel(Comm c) {
   wait_ranks(c, 0, c.expect_a, (1u << c.world) - 1u);
 }
 
-__global__ void __launch_bounds__(THREADS) p2p_send_kernel(uint8_t* slot, uint32_t* ready, const uint32_t* ack, uint32_t seq,
-                                                         const uint8_t* in, uint64_t bytes, Status* st) {
-  __shared__ int ok_s;
-  if (threadIdx.x == 0) ok_s = wait_flag_ge(ack, seq - 1, st, SITE_PEER_FLAG) ? 1 : 0;   // slot is free again
-  __syncthreads();
-  if (!ok_s) return;
-  copy_bytes(slot, in, bytes);
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) red_release_sys_add(ready, 1u);     // one arrival per block; receiver expects seq*blocks
+// Block-scope byte copy (the calling block copies all n bytes), eight 16-byte loads in flight per thread: the
+// source may be a peer's memory, where the latency is a few microseconds.
+__device__ void copy_bytes_block(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, uint64_t n) {
+  if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+    const uint64_t nv = n >> 4, step = blockDim.x;
+    const uint4* s = reinterpret_cast<const uint4*>(src);
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    uint64_t i = threadIdx.x;
+    for (; i < nv; i += 8 * step) {        // all of a round's loads are issued before its first store
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (i + u * step < nv) v[u] = __ldcg(s + i + u * step);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (i + u * step < nv) d[i + u * step] = v[u];
+    }
+    for (uint64_t j = (nv << 4) + threadIdx.x; j < n; j += step) dst[j] = src[j];
+  } else {
+    for (uint64_t j = threadIdx.x; j < n; j += blockDim.x) dst[j] = src[j];
+  }
 }
 
-__global__ void __launch_bounds__(THREADS) p2p_recv_kernel(const uint8_t* slot, const uint32_t* ready, uint32_t* ack,
-                                                         uint32_t expect_ready, uint8_t* out, uint64_t bytes, Status* st) {
+// Pipelined point-to-point exchange: one launch plays this rank's sending and receiving roles of a message (or of a
+// collective permute) at once.  A message travels in pieces through a ring of `depth` slots in the SENDER's memory:
+// the sender stages a piece locally and raises `ready` at the receiver; the receiver pulls the piece over NVLink
+// straight into its destination and raises `ack` at the sender, which frees the slot.  Pulling keeps the expensive
+// step (a system-scope fence behind stores that crossed the link) off the path: the only stores that cross are the
+// counters.  `nb` blocks per role each move 1/nb of every piece.  Counters are monotonic: `ready` counts
+// sender-block arrivals, `ack` receiver-block arrivals; the `*_base` values are the totals of all earlier messages
+// on the channel, known to both ends from the call sequence.
+struct XferChan {
+  uint8_t* slot; uint32_t* ready; uint32_t* ack; uint32_t ready_base, ack_base;
+};
+struct Xfer {
+  int n_send, has_recv, nb, depth;
+  XferChan send[R];
+  XferChan recv;
+  const uint8_t* in; uint8_t* out;
+  uint64_t send_bytes, recv_bytes, piece;
+  Status* st;
+};
+
+__global__ void __launch_bounds__(THREADS) exchange_kernel(const __grid_constant__ Xfer x) {
   __shared__ int ok_s;
-  if (threadIdx.x == 0) ok_s = wait_flag_ge(ready, expect_ready, st, SITE_PEER_FLAG) ? 1 : 0;
-  __syncthreads();
-  if (!ok_s) return;
-  copy_bytes(out, slot, bytes);
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) red_release_sys_add(ack, 1u);
+  const int role = blockIdx.x / x.nb, b = blockIdx.x % x.nb;
+  const bool sender = role < x.n_send;
+  const XferChan& ch = sender ? x.send[role] : x.recv;
+  const uint64_t bytes = sender ? x.send_bytes : x.recv_bytes;
+  const uint64_t pieces = (bytes + x.piece - 1) / x.piece;
+  if (sender) {
+    // every earlier message on this channel has been pulled, so the whole ring is free
+    if (threadIdx.x == 0) ok_s = wait_flag_ge(ch.ack, ch.ack_base, x.st, SITE_PEER_FLAG) ? 1 : 0;
+    __syncthreads();
+    if (!ok_s) return;
+  }
+  for (uint64_t i = 0; i < pieces; ++i) {
+    const uint64_t lo = i * x.piece, len = min(x.piece, bytes - lo);
+    const uint64_t part = ((len + x.nb - 1) / x.nb + 15) & ~(uint64_t)15;
+    const uint64_t p0 = min(len, (uint64_t)b * part), p1 = min(len, p0 + part);
+    uint8_t* slot = ch.slot + (i % x.depth) * x.piece;
+    if (sender) {
+      if (i >= (uint64_t)x.depth) {
+        if (threadIdx.x == 0)
+          ok_s = wait_flag_ge(ch.ack, ch.ack_base + (uint32_t)(i - x.depth + 1) * x.nb, x.st, SITE_PEER_FLAG) ? 1 : 0;
+        __syncthreads();
+        if (!ok_s) return;
+      }
+      copy_bytes_block(slot + p0, x.in + lo + p0, p1 - p0);
+      __syncthreads();                    // then thread 0's release covers the whole block's stores
+      if (threadIdx.x == 0) red_release_sys_add(ch.ready, 1u);
+    } else {
+      if (threadIdx.x == 0)
+        ok_s = wait_flag_ge(ch.ready, ch.ready_base + (uint32_t)(i + 1) * x.nb, x.st, SITE_PEER_FLAG) ? 1 : 0;
+      __syncthreads();
+      if (!ok_s) return;
+      copy_bytes_block(x.out + lo + p0, slot + p0, p1 - p0);
+      __syncthreads();                    // every thread's loads have returned (their values were stored)
+      if (threadIdx.x == 0) red_release_sys_add(ch.ack, 1u);
+    }
+  }
 }
 
 __global__ void wait_flag_test_kernel(const uint32_t* flag, uint32_t expect, unsigned long long limit_ns, Status* st) {
@@ -485,19 +540,20 @@ extern "C" int mesh_coll_barrier(const MeshCommArgs* a, void* stream) {
   return 0;
 }
 
-// p2p messages use a fixed grid so that `ready` advances by the same amount per message on both ends
-static const int P2P_BLOCKS = 16;
-extern "C" int mesh_p2p_send(const MeshP2PArgs* a, const void* in, uint64_t bytes, void* stream) {
-  p2p_send_kernel<<<P2P_BLOCKS, THREADS, 0, (cudaStream_t)stream>>>((uint8_t*)a->slot, a->ready, a->ack,
-                                                                   (a->seq - 1) * P2P_BLOCKS + 1, (const uint8_t*)in, bytes,
-                                                                   (Status*)a->status);
-  MESH_CUDA_OK(cudaGetLastError());
-  return 0;
-}
-extern "C" int mesh_p2p_recv(const MeshP2PArgs* a, void* out, uint64_t bytes, void* stream) {
-  p2p_recv_kernel<<<P2P_BLOCKS, THREADS, 0, (cudaStream_t)stream>>>((const uint8_t*)a->slot, a->ready, a->ack,
-                                                                   a->seq * P2P_BLOCKS, (uint8_t*)out, bytes,
-                                                                   (Status*)a->status);
+extern "C" int mesh_p2p_exchange(const MeshXferArgs* a, void* stream) {
+  if (a->n_send < 0 || a->n_send > R || a->nb < 1 || a->nb > 64 || a->depth < 1 || a->piece == 0 || (a->piece & 15))
+    return set_error(-4, "p2p_exchange: bad arguments");
+  Xfer x;
+  x.n_send = a->n_send; x.has_recv = a->has_recv; x.nb = a->nb; x.depth = a->depth;
+  for (int i = 0; i < a->n_send; ++i)
+    x.send[i] = XferChan{(uint8_t*)a->send[i].slot, a->send[i].ready, a->send[i].ack, a->send[i].ready_base, a->send[i].ack_base};
+  x.recv = XferChan{(uint8_t*)a->recv.slot, a->recv.ready, a->recv.ack, a->recv.ready_base, a->recv.ack_base};
+  x.in = (const uint8_t*)a->in; x.out = (uint8_t*)a->out;
+  x.send_bytes = a->send_bytes; x.recv_bytes = a->recv_bytes; x.piece = a->piece;
+  x.st = (Status*)a->status;
+  const int roles = a->n_send + (a->has_recv ? 1 : 0);
+  if (roles == 0) return 0;
+  exchange_kernel<<<roles * a->nb, THREADS, 0, (cudaStream_t)stream>>>(x);
   MESH_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -239,8 +239,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchArgs a)
       }
     }
   }
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();                      // the signalling threads' system-scope release covers the block's stores
   if ((int)threadIdx.x < a.world) red_release_sys_add(a.arrived[threadIdx.x], 1u);
 }
 

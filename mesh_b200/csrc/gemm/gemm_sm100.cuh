@@ -590,7 +590,6 @@ gemm_kernel(const __grid_constant__ Params p) {
         if (lane == 0) {
           tma_store_wait_all<0>();
           fence_proxy_async_all();
-          __threadfence_system();
           red_release_sys_add(p.rs_count[owner] + owner_m_tile * p.n_tiles + n_idx, 1u);
         }
         __syncwarp();
@@ -638,8 +637,8 @@ gemm_kernel(const __grid_constant__ Params p) {
         for (int u = 0; u < 8; ++u) dst[i + u * NT] = v[u];
       }
       for (; i < end; i += NT) dst[i] = __ldg(src + i);
-      __threadfence_system();
-      // named barrier among the comm warps only (id 1), then one arrival for this part
+      // named barrier among the comm warps only (id 1), then one arrival for this part: the release below is
+      // cumulative over the stores the barrier ordered before it, so one system-scope fence serves the group
       asm volatile("bar.sync 1, %0;" ::"n"(COMM_WARPS * 32) : "memory");
       if (tid == 0)
         red_release_sys_add(p.ag_flags[dest] + p.rank * blocks_per_rank + blk, 1u);

@@ -50,6 +50,9 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return q;
 }
 
+// VPT = 16-byte vectors per thread (a row has up to VPT * 256 of them): sized to the row so that the registers
+// holding the row stay few and several CTAs per SM keep enough loads in flight to fill HBM.
+template <int VPT>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
@@ -60,10 +63,10 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
     const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * cols) : nullptr;
-    float v[MAX_VEC_PER_THREAD][8];
+    float v[VPT][8];
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nvec) {
         unpack8(xr[c], v[i]);
@@ -88,7 +91,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     if (rstd_out && threadIdx.x == 0) rstd_out[row] = rstd;
     uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * cols);
 #pragma unroll
-    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nvec) {
         float w8[8], o[8];
@@ -103,6 +106,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 
 // Each CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; writes dx per row and keeps a
 // per-thread running sum of dy*x*rstd for its columns, stored to dw_partial[blockIdx.x][cols].
+template <int VPT>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -110,19 +114,19 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
                    float w_offset) {
   __shared__ float sh[32];
   const int nvec = cols >> 3;
-  float dwacc[MAX_VEC_PER_THREAD][8];
+  float dwacc[VPT][8];
 #pragma unroll
-  for (int i = 0; i < MAX_VEC_PER_THREAD; ++i)
+  for (int i = 0; i < VPT; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * cols);
     const float r = rstd[row];
-    float xv[MAX_VEC_PER_THREAD][8], gv[MAX_VEC_PER_THREAD][8];
+    float xv[VPT][8], gv[VPT][8];
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nvec) {
         float w8[8];
@@ -141,7 +145,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     const float coef = dot * r * r * r / (float)cols;
     uint4* dr = reinterpret_cast<uint4*>(dx + (size_t)row * cols);
 #pragma unroll
-    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nvec) {
         float o[8];
@@ -154,7 +158,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   if (dw_partial) {
     float* out = dw_partial + (size_t)blockIdx.x * cols;
 #pragma unroll
-    for (int i = 0; i < MAX_VEC_PER_THREAD; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nvec) {
 #pragma unroll
@@ -183,15 +187,22 @@ extern "C" int mesh_rmsnorm_fwd(const void* x, const void* residual, const void*
   if (rows <= 0) return 0;
   if (cols % 8 || cols > NORM_THREADS * MAX_VEC_PER_THREAD * 8)
     return set_error(-2, "rmsnorm: cols must be a multiple of 8 and <= %d", NORM_THREADS * MAX_VEC_PER_THREAD * 8);
-  const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  rmsnorm_fwd_kernel<<<grid, NORM_THREADS, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-      (__nv_bfloat16*)residual_out, rstd, rows, cols, eps, w_offset);
+  const int grid = rows < 148 * 16 ? rows : 148 * 16;
+  const int nvec = cols / 8;
+#define FWD(V)                                                                                                     \
+  rmsnorm_fwd_kernel<V><<<grid, NORM_THREADS, 0, (cudaStream_t)stream>>>(                                           \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,          \
+      (__nv_bfloat16*)residual_out, rstd, rows, cols, eps, w_offset)
+  if (nvec <= NORM_THREADS) FWD(1);
+  else if (nvec <= 2 * NORM_THREADS) FWD(2);
+  else if (nvec <= 4 * NORM_THREADS) FWD(4);
+  else FWD(8);
+#undef FWD
   MESH_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
-extern "C" int mesh_rmsnorm_bwd_blocks(int rows) { return rows < 296 ? rows : 296; }
+extern "C" int mesh_rmsnorm_bwd_blocks(int rows) { return rows < 592 ? rows : 592; }
 
 extern "C" int mesh_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
                                 float* dw_partial, int blocks, int rows, int cols, float w_offset, void* stream) {
@@ -199,9 +210,16 @@ extern "C" int mesh_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
   if (cols % 8 || cols > NORM_THREADS * MAX_VEC_PER_THREAD * 8)
     return set_error(-2, "rmsnorm: cols must be a multiple of 8 and <= %d", NORM_THREADS * MAX_VEC_PER_THREAD * 8);
   if (blocks <= 0 || blocks > 1024) return set_error(-2, "rmsnorm_bwd: blocks out of range");
-  rmsnorm_bwd_kernel<<<blocks, NORM_THREADS, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx,
-      dw_partial, rows, cols, w_offset);
+  const int nvec = cols / 8;
+#define BWD(V)                                                                                                     \
+  rmsnorm_bwd_kernel<V><<<blocks, NORM_THREADS, 0, (cudaStream_t)stream>>>(                                         \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx,         \
+      dw_partial, rows, cols, w_offset)
+  if (nvec <= NORM_THREADS) BWD(1);
+  else if (nvec <= 2 * NORM_THREADS) BWD(2);
+  else if (nvec <= 4 * NORM_THREADS) BWD(4);
+  else BWD(8);
+#undef BWD
   MESH_CUDA_OK(cudaGetLastError());
   if (dw && dw_partial) {
     rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, (cudaStream_t)stream>>>(dw_partial, dw, blocks, cols);

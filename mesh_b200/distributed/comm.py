@@ -39,9 +39,17 @@ class _CommArgs(ctypes.Structure):
                 ("status", c_void_p), ("nblocks", c_int)]
 
 
-class _P2PArgs(ctypes.Structure):
-    _fields_ = [("rank", c_int), ("peer", c_int), ("slot", c_void_p), ("ready", c_void_p), ("ack", c_void_p),
-                ("seq", c_uint32), ("status", c_void_p)]
+class _XferChan(ctypes.Structure):
+    _fields_ = [("slot", c_void_p), ("ready", c_void_p), ("ack", c_void_p), ("ready_base", c_uint32), ("ack_base", c_uint32)]
+
+
+class _XferArgs(ctypes.Structure):
+    _fields_ = [("n_send", c_int), ("has_recv", c_int), ("nb", c_int), ("depth", c_int), ("send", _XferChan * MAX_RANKS),
+                ("recv", _XferChan), ("inp", c_void_p), ("out", c_void_p), ("send_bytes", c_uint64), ("recv_bytes", c_uint64),
+                ("piece", c_uint64), ("status", c_void_p)]
+
+
+P2P_DEPTH = 4
 
 
 def _op_code(op) -> int:
@@ -59,7 +67,7 @@ def _stream() -> c_void_p:
 
 
 class Communicator:
-    def __init__(self, heap: SymmetricHeap, staging_bytes: int = 64 << 20, p2p_slot_bytes: int = 4 << 20):
+    def __init__(self, heap: SymmetricHeap, staging_bytes: int = 64 << 20, p2p_slot_bytes: int = 32 << 20):
         self.heap = heap
         self.rank, self.world = heap.rank, heap.world
         if self.world > MAX_RANKS:
@@ -69,12 +77,12 @@ class Communicator:
         self._arrived = [heap.alloc_signals(2 * self.world) for _ in range(2)]
         self._expect = [[0, 0], [0, 0]]
         self._turn = 0
-        self.p2p_slot_bytes = p2p_slot_bytes
-        self._slots = heap.alloc((self.world, p2p_slot_bytes), torch.uint8)   # slot[src] on the receiver
+        self.p2p_slot_bytes = p2p_slot_bytes // (P2P_DEPTH * 16) * (P2P_DEPTH * 16)
+        self._slots = heap.alloc((self.world, self.p2p_slot_bytes), torch.uint8)   # ring[dst] on the sender
         self._ready = heap.alloc_signals(self.world)                          # ready[src] on the receiver
         self._ack = heap.alloc_signals(self.world)                            # ack[dst] on the sender
-        self._send_seq = [0] * self.world
-        self._recv_seq = [0] * self.world
+        self._sent = [0] * self.world          # block arrivals raised so far on the channel to each destination
+        self._rcvd = [0] * self.world          # ... and on the channel from each source
         self.L = _native.lib()
         self.max_blocks = self.L.mesh_coll_max_blocks()
         self.one_shot_max = config().one_shot_max_bytes
@@ -82,7 +90,8 @@ class Communicator:
 
     # ------------------------------------------------------------------ plumbing
     def _blocks(self, nbytes: int) -> int:
-        return max(1, min(self.max_blocks, (nbytes + (128 << 10) - 1) // (128 << 10)))
+        # one 16-byte vector per thread (512 threads) until every SM has a block
+        return max(1, min(self.max_blocks, (nbytes + (8 << 10) - 1) // (8 << 10)))
 
     def _args(self, nblocks: int, two_step: bool = False) -> _CommArgs:
         par = self._turn & 1
@@ -297,67 +306,72 @@ class Communicator:
         _native.count_launch()
 
     # ------------------------------------------------------------------ point to point
+    def _p2p_blocks(self, nbytes: int) -> int:
+        return max(1, min(48, nbytes // (64 << 10)))
+
+    def _exchange(self, inp, dsts: list[int], out, src: int | None) -> None:
+        """One launch: ``inp`` goes to every rank of ``dsts`` and ``out`` is filled from ``src``.  Both ends of a
+        channel derive the piece count and the block count from the message size, so their counters agree."""
+        piece = self.p2p_slot_bytes // P2P_DEPTH
+        a = _XferArgs()
+        a.depth, a.piece = P2P_DEPTH, piece
+        a.status = status_block(self.heap.device).data_ptr()
+        sb = inp.numel() * inp.element_size() if inp is not None else 0
+        rb = out.numel() * out.element_size() if out is not None else 0
+        nbytes = max(sb if dsts else 0, rb if src is not None else 0)
+        nb = self._p2p_blocks(nbytes)
+        if dsts and src is not None and sb != rb:
+            raise ValueError("exchange: this rank's send and receive sizes differ; use send and recv")
+        a.nb = nb
+        a.n_send = len(dsts)
+        for i, d in enumerate(dsts):
+            ch = a.send[i]
+            ch.slot = self._slots.ptr(self.rank) + d * self.p2p_slot_bytes
+            ch.ready = self._ready.ptr(d) + 4 * self.rank
+            ch.ack = self._ack.ptr(self.rank) + 4 * d
+            ch.ready_base = ch.ack_base = self._sent[d] & 0xFFFFFFFF
+            self._sent[d] += -(-sb // piece) * nb
+        a.has_recv = int(src is not None)
+        if src is not None:
+            ch = a.recv
+            ch.slot = self._slots.ptr(src) + self.rank * self.p2p_slot_bytes
+            ch.ready = self._ready.ptr(self.rank) + 4 * src
+            ch.ack = self._ack.ptr(src) + 4 * self.rank
+            ch.ready_base = ch.ack_base = self._rcvd[src] & 0xFFFFFFFF
+            self._rcvd[src] += -(-rb // piece) * nb
+        a.inp = inp.data_ptr() if (inp is not None and sb) else 0
+        a.out = out.data_ptr() if (out is not None and rb) else 0
+        a.send_bytes, a.recv_bytes = sb, rb
+        if a.n_send == 0 and not a.has_recv:
+            return
+        _native.check(self.L.mesh_p2p_exchange(ctypes.byref(a), _stream()), "mesh_p2p_exchange")
+        _native.count_launch()
+
     def send(self, t: torch.Tensor, dst: int) -> None:
-        """Store ``t`` into rank ``dst``'s slot for this rank (messages larger than a slot go in pieces)."""
+        """Stage ``t`` piece by piece in this rank's ring for ``dst``, from which the receiver pulls it.  Finishes (on
+        the stream) once the last piece is staged: a message no larger than the ring does not wait for the receiver."""
         self._check(t, "tensor")
-        flat = t.view(-1).view(torch.uint8)
-        pos, n = 0, flat.numel()
-        while True:
-            cnt = min(n - pos, self.p2p_slot_bytes)
-            self._send_seq[dst] += 1
-            a = _P2PArgs()
-            a.rank, a.peer = self.rank, dst
-            a.slot = self._slots.ptr(dst) + self.rank * self.p2p_slot_bytes
-            a.ready = self._ready.ptr(dst) + 4 * self.rank
-            a.ack = self._ack.ptr(self.rank) + 4 * dst
-            a.seq = self._send_seq[dst]
-            a.status = status_block(self.heap.device).data_ptr()
-            rc = self.L.mesh_p2p_send(ctypes.byref(a), c_void_p(flat[pos:].data_ptr() if cnt else 0), c_uint64(cnt), _stream())
-            _native.check(rc, "mesh_p2p_send")
-            _native.count_launch()
-            pos += cnt
-            if pos >= n:
-                break
+        self._exchange(t.view(-1).view(torch.uint8), [dst], None, None)
 
     def recv(self, t: torch.Tensor, src: int) -> torch.Tensor:
         self._check(t, "tensor")
-        flat = t.view(-1).view(torch.uint8)
-        pos, n = 0, flat.numel()
-        while True:
-            cnt = min(n - pos, self.p2p_slot_bytes)
-            self._recv_seq[src] += 1
-            a = _P2PArgs()
-            a.rank, a.peer = self.rank, src
-            a.slot = self._slots.ptr(self.rank) + src * self.p2p_slot_bytes
-            a.ready = self._ready.ptr(self.rank) + 4 * src
-            a.ack = self._ack.ptr(src) + 4 * self.rank
-            a.seq = self._recv_seq[src]
-            a.status = status_block(self.heap.device).data_ptr()
-            rc = self.L.mesh_p2p_recv(ctypes.byref(a), c_void_p(flat[pos:].data_ptr() if cnt else 0), c_uint64(cnt), _stream())
-            _native.check(rc, "mesh_p2p_recv")
-            _native.count_launch()
-            pos += cnt
-            if pos >= n:
-                break
+        self._exchange(None, [], t.view(-1).view(torch.uint8), src)
         return t
 
     def permute(self, out: torch.Tensor, inp: torch.Tensor, pairs: list[tuple[int, int]]):
         """collective-permute: for every ``(src, dst)`` pair, ``out`` on dst = ``inp`` on src
-        (rdma/mesh_compile.py:1597-1613)."""
-        # piece by piece, so that a ring of large messages never has a send waiting for a slot whose
-        # receive sits behind that peer's own later send
-        fin, fout = inp.view(-1).view(torch.uint8), out.view(-1).view(torch.uint8)
-        n = max(fin.numel(), fout.numel())
-        pos = 0
-        while True:
-            hi = min(n, pos + self.p2p_slot_bytes)
-            for s, d in pairs:
-                if s == self.rank:
-                    self.send(fin[pos:hi], d)
-            for s, d in pairs:
-                if d == self.rank:
-                    self.recv(fout[pos:hi], s)
-            pos = hi
-            if pos >= n:
-                break
+        (rdma/mesh_compile.py:1597-1613).  Sending and receiving run in the same launch, so a ring of messages of
+        any size cannot have every rank waiting to send."""
+        dsts = [d for s_, d in pairs if s_ == self.rank]
+        srcs = [s_ for s_, d in pairs if d == self.rank]
+        if len(srcs) > 1:
+            raise ValueError("permute: a rank receives from at most one source")
+        fin = inp.view(-1).view(torch.uint8) if dsts else None
+        fout = out.view(-1).view(torch.uint8) if srcs else None
+        if fin is not None and fout is not None and fin.numel() != fout.numel():
+            # unequal sizes: the receive must not share a launch geometry with the sends
+            self._exchange(fin, dsts, None, None)
+            self._exchange(None, [], fout, srcs[0])
+            return out
+        self._exchange(fin, dsts, fout, srcs[0] if srcs else None)
         return out

@@ -102,7 +102,7 @@ class AxisContext:
         used: every rank must touch the same axes' communicators in the same order."""
         if self._comm is None:
             from ..distributed.comm import Communicator
-            self._comm = Communicator(self.heap, staging_bytes=16 << 20, p2p_slot_bytes=2 << 20)
+            self._comm = Communicator(self.heap, staging_bytes=32 << 20, p2p_slot_bytes=16 << 20)
         return self._comm
 
     def peer(self, offset: int) -> int:

@@ -21,6 +21,11 @@ def _child(rank: int, world: int, port: int, fn, args, use_cuda: bool, init_pg: 
     import torch
     import torch.distributed as dist
     from ..runtime.rendezvous import Rendezvous
+    watchdog = float(os.environ.get("MESH_SPAWN_WATCHDOG_S", "0") or 0)
+    if watchdog > 0:
+        # a rank that is still running after this long prints where it is (all threads) and carries on
+        import faulthandler
+        faulthandler.dump_traceback_later(watchdog, exit=False)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
     if use_cuda:
@@ -34,6 +39,13 @@ def _child(rank: int, world: int, port: int, fn, args, use_cuda: bool, init_pg: 
     try:
         fn(rank, world, rdv, *args)
         rdv.barrier("spawn-exit")
+        # Rank 0's process hosts the store.  It may leave the barrier first, and a store that goes away while another
+        # rank is still reading the barrier's keys looks to that rank like a peer that never arrived: so the host
+        # stays until every other rank has said that it is through.
+        if rank != 0:
+            store.set(f"spawn-bye/{rank}", b"1")
+        elif world > 1:
+            store.wait([f"spawn-bye/{r}" for r in range(1, world)], timedelta(seconds=120))
     except BaseException:
         traceback.print_exc()
         raise
