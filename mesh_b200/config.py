@@ -32,7 +32,7 @@ class MeshConfig:
     wait_ns: int = 5_000_000_000        # host-side "no progress" bound, like MESH_PLATFORM_NS (5 s)
     device_wait_ns: int = 2_000_000_000 # device-side bounded waits
     deadline_s: float = 0.0             # whole-run deadline, 0 = none (MESH_DEADLINE)
-    heap_bytes: int = 1 << 30           # symmetric heap size per GPU (MESH_HEAP_BYTES)
+    heap_bytes: int = 4 << 30           # symmetric heap size per GPU (MESH_HEAP_BYTES)
     signal_bytes: int = 1 << 20         # signal pad size per GPU
     one_shot_max_bytes: int = 512 << 10 # all-reduce: one-shot below, two-shot above
     nvls: bool = True                   # use NVLS multimem paths when the heap has a multicast mapping

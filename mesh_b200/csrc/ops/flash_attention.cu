@@ -1,11 +1,16 @@
 // Flash attention forward on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
 //
-// One CTA owns 128 query rows of one head.  Warp 4 is the copy/MMA warp: it streams K and V blocks
+// One CTA owns 128 query rows of one head.  Warp 8 is the copy/MMA warp: it streams K and V blocks
 // through a 2-stage shared-memory ring and issues  S = Q K^T  and  O += P V  as tcgen05.mma with the
-// accumulators in tensor memory (S double-buffered, O resident for the whole KV sweep).  Warps 0-3 are
-// the softmax warps: thread r owns query row r — tcgen05.ld hands it its whole row of S, so row max and
-// row sum need no shuffles — it writes P (bf16) into shared memory in the swizzled K-major layout the
-// second MMA reads, and rescales its row of O in tensor memory when the running max moves.
+// accumulators in tensor memory (S double-buffered, O resident for the whole KV sweep).  Warps 0-7 are
+// the softmax warps, two per scheduler so that one hides the other's latencies: threads r and r + 128 share
+// query row r, each taking half of the key columns of a block — tcgen05.ld hands a thread its part of the row, so
+// the row max costs one exchange through shared memory and the row sum none until the end.  A thread reads its
+// scores once and keeps them in registers (the S buffer is handed back to the MMA warp at once), writes P (bf16)
+// into shared memory in the swizzled K-major layout the second MMA reads, and rescales its half of the row of O
+// in tensor memory only when the running max has moved by more than 2^8 (P stays within bf16/fp32 range; the
+// final division by the row sum makes the result independent of the reference point).  Blocks that no mask
+// touches take a path without position arithmetic.
 // V is consumed MN-major straight from its row-major [kv, head_dim] tile: no transposes anywhere.
 //
 // Semantics (compiler/mesh_compiler/operations.py:7081-7166): blockwise online softmax with (m, s, acc)
@@ -26,7 +31,8 @@ namespace mesh {
 namespace fa {
 
 constexpr int BQ = 128;
-constexpr int THREADS = 160;          // 4 softmax warps + 1 copy/MMA warp
+constexpr int SM_THREADS = 256;       // 8 softmax warps
+constexpr int THREADS = 288;          // + 1 copy/MMA warp
 
 struct Params {
   CUtensorMap tmQ, tmK, tmV;          // 2-D maps over [rows, cols] views; boxes {64, 128} / {64, BKV}
@@ -40,6 +46,12 @@ struct Params {
   Status* status;
 };
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int HD>
 struct Cfg {
   static constexpr int BKV = HD <= 128 ? 128 : 64;
@@ -47,7 +59,7 @@ struct Cfg {
   static constexpr int Q_BYTES = BQ * HD * 2;
   static constexpr int KV_BYTES = BKV * HD * 2;
   static constexpr int P_BYTES = BQ * BKV * 2;
-  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256 + 2 * 2 * 128 * 4;
   static constexpr int S_COLS = BKV;                    // per S buffer
   static constexpr int O_COL0 = 256;                    // S0 at 0, S1 at 128, O from 256
 };
@@ -69,6 +81,7 @@ __global__ void __launch_bounds__(THREADS, 1) flash_fwd_kernel(const __grid_cons
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::Q_BYTES + 4 * C::KV_BYTES + C::P_BYTES + 8 * 12);
   volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xchg = reinterpret_cast<float*>(tmem_slot + 4);      // [2 parities][2 halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -98,14 +111,14 @@ __global__ void __launch_bounds__(THREADS, 1) flash_fwd_kernel(const __grid_cons
       mbar_init(bar(KV_FULL + s), 1);
       mbar_init(bar(KV_EMPTY + s), 1);
       mbar_init(bar(S_FULL + s), 1);
-      mbar_init(bar(S_EMPTY + s), 128);
+      mbar_init(bar(S_EMPTY + s), SM_THREADS);
     }
-    mbar_init(bar(P_FULL), 128);
+    mbar_init(bar(P_FULL), SM_THREADS);
     mbar_init(bar(O_DONE), 1);
     *abort_smem = 0;
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc<1>(smem_u32(tmem_slot), 512);
     tmem_relinquish<1>();
   }
@@ -114,7 +127,7 @@ __global__ void __launch_bounds__(THREADS, 1) flash_fwd_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0 && n_blocks > 0) {
       // ------------------------------------------------------------------ copy + MMA issue
       const int q_row = b * p.Tq + q0;
@@ -185,100 +198,119 @@ __global__ void __launch_bounds__(THREADS, 1) flash_fwd_kernel(const __grid_cons
       }
     }
   } else {
-    // -------------------------------------------------------------------- softmax warps: thread = query row
-    const int row = threadIdx.x;                      // 0..127 == TMEM lane
+    // -------------------------------------------------------------------- softmax warps
+    constexpr int HALF = BKV / 2;                     // key columns of a block per thread
+    constexpr int NCH = HALF / 32;                    // 32-column TMEM loads per thread and block
+    const int row = threadIdx.x & 127;                // == TMEM lane
+    const int half = threadIdx.x >> 7;                // which half of the key columns (and of the O columns)
     const int qi = q0 + row;
     const int qpos = p.q_off + qi * p.q_stride;
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-    float m = -CUDART_INF_F, l = 0.f;
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const float thr = 8.f / p.scale_log2;             // the reference point moves when the max grew by > 2^8
+    float m_ref = -CUDART_INF_F, l = 0.f;             // reference point (identical in both threads of a row), own sum
     bool ok = true;
-    for (int it = 0; ok && it < n_blocks; ++it) {
+    // Every softmax warp runs all n_blocks iterations and meets the others at the named barrier in each, also after
+    // a wait has run out (ok == false, warp-uniform): it then skips the work, so the barrier counts stay equal.
+    for (int it = 0; it < n_blocks; ++it) {
       const int s = it & 1;
-      ok = mbar_wait(bar(S_FULL + s), (it >> 1) & 1, abort_smem, p.status, SITE_TMEM_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
+      if (ok) {
+        ok = mbar_wait(bar(S_FULL + s), (it >> 1) & 1, abort_smem, p.status, SITE_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+      }
       const int kbase = (j_lo + it) * BKV;
-      // pass 1: row maximum of the masked scores
+      // does any mask or the end of the keys cut into this block (for some row of the tile)?
+      const int kpos_lo = p.k_off + kbase * p.k_stride, kpos_hi = p.k_off + (kbase + BKV - 1) * p.k_stride;
+      const bool masked = (kbase + BKV > p.Tk) || (p.causal && kpos_hi > qpos_lo) ||
+                          (p.window > 0 && kpos_lo <= qpos_hi - p.window);
+      // this thread's scores, read once
+      uint32_t r[NCH][32];
       float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(lane_addr + s * 128 + c * 32, r);
-        tmem_ld_wait();
+      if (ok) {
+        tc_fence_after();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kj = kbase + c * 32 + i;
-          const int kpos = p.k_off + kj * p.k_stride;
-          const bool vis = kj < p.Tk && (!p.causal || kpos <= qpos) && (p.window <= 0 || kpos > qpos - p.window);
-          if (vis) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int c = 0; c < NCH; ++c) tmem_ld_32x32(lane_addr + s * 128 + half * HALF + c * 32, r[c]);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(bar(S_EMPTY + s));                // the MMA warp may overwrite this S buffer
+        if (masked) {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int kj = kbase + half * HALF + c * 32 + i;
+              const int kpos = p.k_off + kj * p.k_stride;
+              const bool vis = kj < p.Tk && (!p.causal || kpos <= qpos) && (p.window <= 0 || kpos > qpos - p.window);
+              if (!vis) r[c][i] = 0xff800000u;        // -inf: exp2 gives an exact zero
+              mx = fmaxf(mx, __uint_as_float(r[c][i]));
+            }
+        } else {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+              mx = fmaxf(mx, fmaxf(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1])));
         }
       }
-      const float m_new = fmaxf(m, mx);
-      const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
-      const float alpha = (m == -CUDART_INF_F) ? 0.f : exp2f((m - m_use) * p.scale_log2);
+      // row max = max of the two halves
+      float* xm = xchg + (it & 1) * 256;
+      xm[half * 128 + row] = mx;
+      asm volatile("bar.sync 1, %0;" ::"n"(SM_THREADS) : "memory");
+      mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
+      if (!ok) continue;
+      float alpha = 1.f;
+      if (mx > m_ref + thr) {                         // also the first block with a visible key (m_ref = -inf)
+        alpha = ex2_approx((m_ref - mx) * p.scale_log2);          // ex2(-inf) = 0
+        m_ref = mx;
+      }
+      const float neg_ms = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref * p.scale_log2;
       // P of the previous block must have been consumed before it is overwritten, and O must be final
       if (it > 0) {
         ok = mbar_wait(bar(O_DONE), (it - 1) & 1, abort_smem, p.status, SITE_TMEM_EMPTY);
         ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+        if (!ok) continue;
         tc_fence_after();
       }
-      // pass 2: p = exp2((s - m) * scale), row sum, bf16 P into swizzled shared memory
       float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(lane_addr + s * 128 + c * 32, r);
-        tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float pv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int kj = kbase + c * 32 + i + u;
-            const int kpos = p.k_off + kj * p.k_stride;
-            const bool vis = kj < p.Tk && (!p.causal || kpos <= qpos) && (p.window <= 0 || kpos > qpos - p.window);
-            pv[u] = vis ? exp2f((__uint_as_float(r[i + u]) - m_use) * p.scale_log2) : 0.f;
-          }
-          __nv_bfloat162 hb = __floats2bfloat162_rn(pv[0], pv[1]);
-          // the sum uses the rounded values the tensor core will see
-          float2 back = __bfloat1622float2(hb);
-          sum += back.x + back.y;
+          const float p0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), p.scale_log2, neg_ms));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), p.scale_log2, neg_ms));
+          sum += p0 + p1;
+          __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
           w[i / 2] = *reinterpret_cast<uint32_t*>(&hb);
         }
-        // 32 columns = 64 bytes = 4 chunks of 16 B inside the 128-byte swizzled row of chunk (c / 2)
-        const uint32_t row_base = sP + (c / 2) * (BQ * 128) + row * 128;
+        // 32 columns = 64 bytes = 4 pieces of 16 B inside the 128-byte swizzled row of their 64-column chunk
+        const int col = half * HALF + c * 32;
+        const uint32_t row_base = sP + (col / 64) * (BQ * 128) + row * 128;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const uint32_t chunk = ((c & 1) * 4 + j) ^ (row & 7);
+          const uint32_t chunk = (((col % 64) / 32) * 4 + j) ^ (row & 7);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (chunk << 4)), "r"(w[4 * j]),
                        "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3]) : "memory");
         }
       }
-      // S buffer read out: the MMA warp may overwrite it with a later block
-      tc_fence_before();
-      mbar_arrive(bar(S_EMPTY + s));
       l = l * alpha + sum;
-      m = m_new;
-      // rescale this row of O (skipped for the first block: the first PV MMA overwrites O)
-      // tcgen05.ld / .st are warp-collective: the decision to rescale must be the same for all 32 rows of a warp
+      // rescale this thread's half of the row of O (never for the first block: the first PV MMA overwrites O).
+      // tcgen05.ld / .st are warp-collective: the decision must be the same for all 32 rows of a warp
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(lane_addr + C::O_COL0 + c * 32, r);
+        for (int c = 0; c < HD / 64; ++c) {
+          uint32_t o[32];
+          const uint32_t addr = lane_addr + C::O_COL0 + half * (HD / 2) + c * 32;
+          tmem_ld_32x32(addr, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
           asm volatile(
               "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
               "%15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-              ::"r"(lane_addr + C::O_COL0 + c * 32), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]),
-                "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
-                "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+              ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]),
+                "r"(o[6]), "r"(o[7]), "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]),
+                "r"(o[15]), "r"(o[16]), "r"(o[17]), "r"(o[18]), "r"(o[19]), "r"(o[20]), "r"(o[21]), "r"(o[22]), "r"(o[23]),
+                "r"(o[24]), "r"(o[25]), "r"(o[26]), "r"(o[27]), "r"(o[28]), "r"(o[29]), "r"(o[30]), "r"(o[31])
               : "memory");
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -294,37 +326,42 @@ __global__ void __launch_bounds__(THREADS, 1) flash_fwd_kernel(const __grid_cons
       tc_fence_after();
     }
     ok = __all_sync(0xffffffffu, ok);      // the TMEM loads below are warp-collective: every lane takes part,
+    // the row sum is the sum of the two halves' sums (both are relative to the same reference point)
+    float* xl = xchg + (n_blocks & 1) * 256;
+    xl[half * 128 + row] = l;
+    asm volatile("bar.sync 1, %0;" ::"n"(SM_THREADS) : "memory");
+    l += xl[(half ^ 1) * 128 + row];
     if (ok) {                              // only the global stores are predicated on the row being real
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.out + ((long long)b * p.Tq + qi) * p.ldo + h * HD;
+      __nv_bfloat16* dst = p.out + ((long long)b * p.Tq + qi) * p.ldo + h * HD + half * (HD / 2);
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t r[32];
+      for (int c = 0; c < HD / 64; ++c) {
+        uint32_t o[32];
         if (n_blocks > 0) {
-          tmem_ld_32x32(lane_addr + C::O_COL0 + c * 32, r);
+          tmem_ld_32x32(lane_addr + C::O_COL0 + half * (HD / 2) + c * 32, o);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0;
+          for (int i = 0; i < 32; ++i) o[i] = 0;
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          uint4 o;
-          __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&o);
+          uint4 q4;
+          __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&q4);
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            hb[i] = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * i]) * inv, __uint_as_float(r[8 * j + 2 * i + 1]) * inv);
-          if (qi < p.Tq) *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = o;
+            hb[i] = __floats2bfloat162_rn(__uint_as_float(o[8 * j + 2 * i]) * inv, __uint_as_float(o[8 * j + 2 * i + 1]) * inv);
+          if (qi < p.Tq) *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = q4;
         }
       }
-      if (p.lse && qi < p.Tq)
+      if (p.lse && qi < p.Tq && half == 0)
         p.lse[((long long)b * p.H + h) * p.Tq + qi] =
-            l > 0.f ? (m * p.scale_log2 + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
+            l > 0.f ? (m_ref * p.scale_log2 + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc<1>(tmem, 512);
   }

@@ -25,7 +25,8 @@ namespace mesh {
 namespace fab {
 
 constexpr int BQ = 128, BKV = 128;
-constexpr int THREADS = 160;
+constexpr int SM_THREADS = 256;       // 8 softmax warps: threads r and r + 128 share row r, half of the columns each
+constexpr int THREADS = 288;          // + 1 copy/MMA warp
 
 struct Params {
   CUtensorMap tmQ, tmK, tmV, tmdO;           // boxes {64, 128}
@@ -40,6 +41,12 @@ struct Params {
   float scale, scale_log2;
   Status* status;
 };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
   tmem_ld_32x32(addr, r);
@@ -103,13 +110,13 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
     mbar_init(bar(KV_FULL), 1);
     mbar_init(bar(Q_FULL), 1);
     mbar_init(bar(SDP_FULL), 1);
-    mbar_init(bar(PDS_FULL), 128);
+    mbar_init(bar(PDS_FULL), SM_THREADS);
     mbar_init(bar(MMA2_DONE), 1);
-    mbar_init(bar(DQ_READ), 128);
+    mbar_init(bar(DQ_READ), SM_THREADS);
     *abort_smem = 0;
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc<1>(smem_u32(tmem_slot), 512);
     tmem_relinquish<1>();
   }
@@ -118,7 +125,7 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0 && n_iter > 0) {
       const int k_row = b * p.Tk + k0;
       mbar_expect_tx(bar(KV_FULL), 2 * TILE);
@@ -183,8 +190,9 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
       }
     }
   } else {
-    const int row = threadIdx.x;
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const int row = threadIdx.x & 127;                // == TMEM lane; query row in the loop, key row at the end
+    const int half = threadIdx.x >> 7;                // which 64 key columns of S / dP, which half of the dQ/dK/dV columns
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
     for (int it = 0; ok && it < n_iter; ++it) {
       const int g = it / n_q, i = i_lo + it % n_q;
@@ -192,20 +200,25 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
       const int qi = i * BQ + row;
       const int qpos = p.q_off + qi * p.q_stride;
       const bool qreal = qi < p.Tq;
-      const float L = qreal ? p.lse[((long long)b * p.H + h) * p.Tq + qi] : 0.f;
+      const float L = qreal ? p.lse[((long long)b * p.H + h) * p.Tq + qi] : -CUDART_INF_F;
       const float dl = qreal ? p.delta[((long long)b * p.H + h) * p.Tq + qi] : 0.f;
-      const float L2 = L * 1.4426950408889634f;
+      // rows with no visible key at all (L = -inf) and rows past the end get P = 0 through an infinite offset
+      const float negL2 = (L == -CUDART_INF_F) ? -CUDART_INF_F : -L * 1.4426950408889634f;
+      // does a mask or the end of the keys / queries cut into this (query block, key block) pair?
+      const int qpos_lo = p.q_off + i * BQ * p.q_stride, qpos_hi = p.q_off + (i * BQ + BQ - 1) * p.q_stride;
+      const bool masked = (k0 + BKV > p.Tk) || (p.causal && kpos_hi > qpos_lo) ||
+                          (p.window > 0 && kpos_lo <= qpos_hi - p.window);
       ok = mbar_wait(bar(SDP_FULL), it & 1, abort_smem, p.status, SITE_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      // P and dS may be overwritten once the previous iteration's second group has consumed them: it has, because
-      // SDP_FULL of this iteration was issued after MMA2_DONE of the previous one was waited for by the MMA warp
+      // P and dS may be overwritten: SDP_FULL of this iteration was issued after the MMA warp had waited for the
+      // previous iteration's second group of products, which read them
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t rs[32], rp[32];
-        tmem_ld_32x32(lane_addr + C_S + c * 32, rs);
-        tmem_ld_32x32(lane_addr + C_DP + c * 32, rp);
+        tmem_ld_32x32(lane_addr + C_S + half * 64 + c * 32, rs);
+        tmem_ld_32x32(lane_addr + C_DP + half * 64 + c * 32, rp);
         tmem_ld_wait();
         uint32_t wp[16], wd[16];
 #pragma unroll
@@ -213,11 +226,13 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
           float pv[2], dv[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int kj = k0 + c * 32 + e + u;
-            const int kpos = p.k_off + kj * p.k_stride;
-            const bool vis = qreal && kj < p.Tk && (!p.causal || kpos <= qpos) && (p.window <= 0 || kpos > qpos - p.window) &&
-                             L != -CUDART_INF_F;
-            const float pr = vis ? exp2f(__uint_as_float(rs[e + u]) * p.scale_log2 - L2) : 0.f;
+            float pr = ex2_approx(fmaf(__uint_as_float(rs[e + u]), p.scale_log2, negL2));
+            if (masked) {
+              const int kj = k0 + half * 64 + c * 32 + e + u;
+              const int kpos = p.k_off + kj * p.k_stride;
+              const bool vis = kj < p.Tk && (!p.causal || kpos <= qpos) && (p.window <= 0 || kpos > qpos - p.window);
+              pr = vis ? pr : 0.f;
+            }
             pv[u] = pr;
             dv[u] = pr * (__uint_as_float(rp[e + u]) - dl) * p.scale;
           }
@@ -226,22 +241,22 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
           wp[e / 2] = *reinterpret_cast<uint32_t*>(&hp);
           wd[e / 2] = *reinterpret_cast<uint32_t*>(&hd2);
         }
-        store_row32(sP, row, c, wp);
-        store_row32(sdS, row, c, wd);
+        store_row32(sP, row, half * 2 + c, wp);
+        store_row32(sdS, row, half * 2 + c, wd);
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(bar(PDS_FULL));
-      // dQ tile of this (query block, key block): add into the float accumulator
+      // dQ tile of this (query block, key block): add this thread's half of the row into the float accumulator
       ok = mbar_wait(bar(MMA2_DONE), it & 1, abort_smem, p.status, SITE_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float* dq = p.dq + ((long long)b * p.Tq + qi) * p.ld_dq + h * HD;
+      float* dq = p.dq + ((long long)b * p.Tq + qi) * p.ld_dq + h * HD + half * (HD / 2);
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < HD / 64; ++c) {
         uint32_t r[32];
-        tmem_ld32(lane_addr + C_S + c * 32, r);
+        tmem_ld32(lane_addr + C_S + half * (HD / 2) + c * 32, r);
         if (qreal) {
 #pragma unroll
           for (int e = 0; e < 32; e += 4)
@@ -252,16 +267,16 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
       tc_fence_before();
       mbar_arrive(bar(DQ_READ));
     }
-    // ---- dK, dV of this key block (thread = key row)
+    // ---- dK, dV of this key block (thread = key row, half of the head dimension)
     ok = __all_sync(0xffffffffu, ok);
     if (ok && n_iter > 0) {
       const int kj = k0 + row;
-      const long long off = ((long long)b * p.Tk + kj) * p.ld_dkv + hk * HD;
+      const long long off = ((long long)b * p.Tk + kj) * p.ld_dkv + hk * HD + half * (HD / 2);
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
-        const int col0 = which ? C_DK : C_DV;
+        const int col0 = (which ? C_DK : C_DV) + half * (HD / 2);
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < HD / 64; ++c) {
           uint32_t r[32];
           tmem_ld32(lane_addr + col0 + c * 32, r);
           if (kj >= p.Tk) continue;
@@ -288,7 +303,7 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
           }
         }
       }
-    } else if (n_iter == 0 && !p.dk_acc) {
+    } else if (n_iter == 0 && !p.dk_acc && half == 0) {
       // nothing sees this key block: its gradients are zero
       const int kj = k0 + row;
       if (kj < p.Tk) {
@@ -302,7 +317,7 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc<1>(tmem, 512);
   }

@@ -46,9 +46,22 @@ bool encode_tiled(CUtensorMap* tm, CUtensorMapDataType dtype, int rank, const vo
     set_error(-100, "cuTensorMapEncodeTiled is not available from this driver");
     return false;
   }
+  // The encoder is a driver call and wants a context current on the calling thread.  A thread that has only ever
+  // had its device selected (an autograd worker whose device is the default one, for instance) has none bound until
+  // its first runtime call that needs one: make that call here, once per thread.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   CUresult r = fn(tm, dtype, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes, box, elem_strides,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {          // the context changed under this thread: bind again and retry once
+    cudaFree(nullptr);
+    r = fn(tm, dtype, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes, box, elem_strides,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) {
     set_error(-101, "cuTensorMapEncodeTiled failed: CUresult %d (rank %d, dims %llu x %llu, box %u x %u)", (int)r, rank,
               (unsigned long long)dims[0], (unsigned long long)dims[1], box[0], box[1]);

@@ -87,6 +87,8 @@ class E2BDecoder:
                      wqkv=wqkv, wo=wo, wgu=wgu, wd=wd)
             if quant == "w4":
                 for k in ("wqkv", "wo", "wgu", "wd"):
+                    if L[k].shape[1] % 512:                   # the 4-bit kernel walks K in steps of 512: a shard this
+                        continue                              # narrow (wo at TP=8) stays bf16
                     codes, scales = D.quantize_w4(L[k])
                     L[k + "_q"], L[k + "_s"] = codes, scales
                     L[k] = D.dequantize_w4(codes, scales)     # prefill GEMMs use the dequantised values (same numbers)
@@ -130,7 +132,7 @@ class E2BDecoder:
 
     # ------------------------------------------------------------------ pieces
     def _w(self, L, name):
-        if self.quant == "w4":
+        if self.quant == "w4" and (name + "_q") in L:
             return L[name + "_q"], L[name + "_s"]
         return L[name], None
 
@@ -252,7 +254,13 @@ def bench_decode(ctx, steps: int = 256, prompt_len: int = 512, configs=(("bf16",
         _ = ctx.comm                      # allocated before the mark below, so it outlives the per-run release
     for quant, B in configs:
         mark = ctx.heap.mark() if ctx.world > 1 else None
-        m = E2BDecoder(cfg, ctx, B, quant)
+        try:
+            m = E2BDecoder(cfg, ctx, B, quant)
+        except Exception as e:      # a configuration that cannot be built is reported, the others still run
+            res["runs"].append({"weights": quant, "batch": B, "error": f"{type(e).__name__}: {e}"[:200]})
+            if mark is not None:
+                ctx.heap.release(mark)
+            continue
         g = torch.Generator(device="cpu").manual_seed(11)
         prompt = torch.randint(0, cfg.vocab, (B, prompt_len), generator=g, dtype=torch.int32).to(ctx.device)
         m.prefill(prompt)

@@ -2,6 +2,8 @@
 
     python -m mesh_b200.tools.prof_ops gemm --m 4096 --n 4096 --k 4096 --iters 3
     python -m mesh_b200.tools.prof_ops glu_fwd | glu_bwd | rmsnorm | rope | router
+    python -m mesh_b200.tools.prof_ops flash_fwd | flash_bwd --m <seq> --n <heads> --k <head_dim> [--time]
+    python -m mesh_b200.tools.prof_ops decode_linear --m <batch> --n <out rows> --k <in cols> [--time]
 
 Sizes are chosen larger than L2 (126 MB) in total footprint where DRAM figures matter but a few
 hundred MB at most, so a full-metric capture of one or two launches ends by itself in about a minute.
@@ -13,6 +15,22 @@ import argparse
 import torch
 
 
+def _time(run, flops, what, bytes_moved=0, iters=20):
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    extra = f" {flops / ms / 1e9:.1f} TFLOP/s" if flops else ""
+    extra += f" {bytes_moved / ms / 1e6:.1f} GB/s" if bytes_moved else ""
+    print(f"{what}: {ms * 1e3:.1f} us{extra}")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("op")
@@ -20,6 +38,7 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--time", action="store_true", help="also print a CUDA-event timing of the op (not under a profiler)")
     a = ap.parse_args()
     from mesh_b200.ops import gemm as G
     from mesh_b200.utils.status import check_status
@@ -59,6 +78,42 @@ def main() -> None:
         logits = torch.randn(a.m * 64, 64, device=dev)
         for _ in range(a.iters):
             router_topk(logits, 6)
+    elif a.op in ("flash_fwd", "flash_bwd"):
+        from mesh_b200.ops.attention import flash_attention, flash_attention_backward
+        T, H, hd = a.m, a.n if a.n <= 64 else 8, a.k if a.k <= 256 else 128
+        B = 4
+        q, k, v = (torch.randn(B, T, H, hd, device=dev).bfloat16() for _ in range(3))
+        out, lse = flash_attention(q, k, v, causal=True, need_lse=True)
+        dout = torch.randn_like(out)
+        delta = (dout.float() * out.float()).sum(-1).transpose(1, 2).contiguous()
+        if a.op == "flash_fwd":
+            run = lambda: flash_attention(q, k, v, causal=True, need_lse=True)
+            flops = 4 * B * H * T * T * hd / 2
+        else:
+            dq = torch.zeros(B, T, H, hd, device=dev)
+            run = lambda: flash_attention_backward(q, k, v, out, lse, dout, causal=True, delta=delta, dq=dq)
+            flops = 10 * B * H * T * T * hd / 2
+        for _ in range(a.iters):
+            run()
+        if a.time:
+            _time(run, flops, f"{a.op} B{B} T{T} H{H} hd{hd} causal")
+    elif a.op == "decode_linear":
+        from mesh_b200.ops import decode as D
+        # several weight matrices in turn, so that the weights come from HBM and not from L2
+        n_w = max(2, (256 << 20) // (a.n * a.k * 2))
+        ws = [(torch.randn(a.n, a.k, device=dev) * 0.02).bfloat16() for _ in range(n_w)]
+        B = a.m if a.m <= 8 else 1
+        x = torch.randn(B, a.k, device=dev).bfloat16()
+        out = torch.empty(B, a.n, device=dev, dtype=torch.bfloat16)
+        state = {"i": 0}
+
+        def run():
+            D.decode_linear(x, ws[state["i"] % n_w], out=out)
+            state["i"] += 1
+        for _ in range(a.iters):
+            run()
+        if a.time:
+            _time(run, 0, f"decode_linear B{B} {a.n}x{a.k} bf16", bytes_moved=a.n * a.k * 2)
     elif a.op == "e2b_decode":
         # solo E2B-class decoder: short prefill, then `iters` eager decode steps (152 launches each)
         import torch.distributed as dist
