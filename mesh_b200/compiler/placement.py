@@ -412,6 +412,8 @@ class Propagator:
         wants: dict[str, list] = {n: [] for n in tnames}
         meta: dict[str, Any] = {}
         handled = not list_args and isinstance(val, torch.Tensor)
+        if tgt is aten.convolution.default and self.halo_convolution(node, tnames):
+            return
         if tgt in CREATION or (not tnames and not list_args):
             self.spec[node.name] = self.all_r()
             self.steps.append(Step("call", node.name, tgt, self.ref_args(node.args), self.ref_kwargs(node.kwargs)))
@@ -589,6 +591,53 @@ class Propagator:
                 return [s], s
             return [R], R
         return [s], s
+
+    def halo_convolution(self, node, tnames) -> bool:
+        """A convolution whose input is cut along one spatial dimension: every processor fetches the rows of its
+        neighbours that its windows reach (a neighbour exchange, the reference's halos, placement.py:388-485) and
+        convolves its own extended block with no padding along that dimension; the output keeps the input's cut.
+        Handled when the windows are 'same'-sized along the cut dimension (stride 1, 2 * padding = dilation *
+        (kernel - 1)), the cut is contiguous and the weights are replicated; anything else falls back to gathering."""
+        x, w = tnames[0], tnames[1]
+        args = list(node.args)
+        stride, padding, dilation, transposed, groups = args[3], list(args[4]), args[5], args[6], args[8]
+        if transposed or any(self.spec[n][a].kind != "R" for n in tnames[1:] for a in range(self.na)):
+            return False
+        cut = [(a, sp) for a, sp in enumerate(self.spec[x]) if sp.kind != "R"]
+        if len(cut) != 1 or cut[0][1].kind != "S" or cut[0][1].striped or cut[0][1].dim < 2:
+            return False
+        ax, sp = cut[0]
+        i = sp.dim - 2
+        k = self.shape[w][sp.dim]
+        reach = dilation[i] * (k - 1)
+        if stride[i] != 1 or 2 * padding[i] != reach or min(sp.counts) < max(padding[i], reach - padding[i]):
+            return False
+        left, right = padding[i], reach - padding[i]
+        src = x
+        if reach:
+            src = self.fresh(x)
+            self.channel += 1
+            esz = torch.empty((), dtype=self.dtype[x]).element_size() if x in self.dtype else 4
+            edge = int(math.prod(self.shape[x])) // max(1, self.shape[x][sp.dim]) * (left + right) * esz
+            self.transfers.append(Transfer(self.channel, "permute", "halo", ax, x, sp.dim, tuple(sp.counts), JOIN, edge))
+            self.steps.append(Step("collective", src, "halo", (Ref(x),), {},
+                                   {"axis": ax, "from": sp, "to": sp, "channel": self.channel, "kind": "permute",
+                                    "full_shape": self.shape[x], "left": left, "right": right}))
+            self.shape[src] = self.shape[x]
+            if x in self.dtype:
+                self.dtype[src] = self.dtype[x]
+            self.spec[src] = self.spec[x]
+        padding[i] = 0
+        new_args = list(self.ref_args(node.args, {node.args[0].name: src}))
+        new_args[4] = padding
+        out_spec = tuple(Spec("S", sp.dim, sp.counts) if a == ax else R for a in range(self.na))
+        self.spec[node.name] = out_spec
+        self.steps.append(Step("call", node.name, node.target, tuple(new_args), self.ref_kwargs(node.kwargs),
+                               {"out_specs": out_spec, "full_shape": _shape(node), "halo": (left, right)}))
+        want = self.stated.get(node.name)
+        if want is not None and want != out_spec:
+            self.renamed[node.name] = self.reshard(node.name, want)
+        return True
 
     def fallback(self, node, tnames, list_args):
         """Rule miss: gather every tensor input and run the op replicated."""

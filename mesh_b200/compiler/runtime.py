@@ -138,8 +138,10 @@ class Executor:
         ax, frm, to, verb = m["axis"], m["from"], m["to"], step.target
         P = self.mesh.shape[ax]
         me = self.coords[ax]
-        if P == 1:
+        if P == 1 and verb != "halo":
             return t
+        if verb == "halo":
+            return self._halo(t, ax, frm.dim, m["left"], m["right"], me, P)
         if self.dist:
             return self._collective_dist(verb, ax, frm, to, t, m)
         parts, g = self.coll.gather_all(t, ax)
@@ -166,6 +168,39 @@ class Executor:
         if verb == "send_recv":
             return parts[frm.owner] if to.owner == me else None
         raise NotImplementedError(verb)
+
+    def _halo(self, t, ax, dim, left, right, me, P):
+        """Extend this processor's block by ``left`` rows of the previous processor's end and ``right`` rows of the
+        next one's start (zeros beyond the ends of the whole tensor)."""
+        def edge(src, lo, n):
+            return src.narrow(dim, lo, n)
+        zl = torch.zeros_like(edge(t, 0, left)) if left else None
+        zr = torch.zeros_like(edge(t, 0, right)) if right else None
+        if P == 1:
+            got_l, got_r = zl, zr
+        elif self.dist:
+            grp, g = self.coll.group(ax)
+            got_l, got_r = zl, zr
+            ops = []
+            if right and me > 0:                                 # my first rows are the previous processor's right halo
+                ops.append(dist.P2POp(dist.isend, edge(t, 0, right).contiguous(), g[me - 1], group=grp))
+            if left and me < P - 1:
+                ops.append(dist.P2POp(dist.isend, edge(t, t.shape[dim] - left, left).contiguous(), g[me + 1], group=grp))
+            if left and me > 0:
+                got_l = torch.empty_like(zl)
+                ops.append(dist.P2POp(dist.irecv, got_l, g[me - 1], group=grp))
+            if right and me < P - 1:
+                got_r = torch.empty_like(zr)
+                ops.append(dist.P2POp(dist.irecv, got_r, g[me + 1], group=grp))
+            if ops:
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+        else:
+            parts, _ = self.coll.gather_all(t, ax)
+            got_l = edge(parts[me - 1], parts[me - 1].shape[dim] - left, left) if (left and me > 0) else zl
+            got_r = edge(parts[me + 1], 0, right) if (right and me < P - 1) else zr
+        pieces = [p for p in (got_l, t, got_r) if p is not None]
+        return torch.cat(pieces, dim=dim) if len(pieces) > 1 else t
 
     @staticmethod
     def _reduce(parts, op):

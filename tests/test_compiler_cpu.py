@@ -152,3 +152,28 @@ def _dist_rank(rank, world, rdv):
 def test_program_distributed_gloo():
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_dist_rank, 2, init_pg="gloo")
+
+
+@pytest.mark.parametrize("n,dim", [(2, 2), (4, 3)])
+def test_convolution_with_halo_exchange(n, dim):
+    """A 'same' convolution over an input cut along a spatial dimension: neighbours exchange edge rows."""
+    torch.manual_seed(7)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c1 = torch.nn.Conv2d(3, 8, 3, padding=1)
+            self.c2 = torch.nn.Conv2d(8, 4, 5, padding=4, dilation=2)
+
+        def forward(self, x):
+            return self.c2(torch.relu(self.c1(x)))
+
+    m = Net().eval()
+    x = torch.randn(2, 3, 16, 16)
+    procs = _procs(n)
+    names = tuple(procs)
+    sch = compile_module(m, (x,), procs, lambda node: (dim, names, None) if node.op == "placeholder" and node.name == "x" else None)
+    verbs = sch.structure["by_verb"]
+    assert verbs.get("halo", 0) == 2 and verbs.get("all_gather", 0) == 1, verbs      # two exchanges, one gather of the result
+    out = Program(sch)(x)
+    assert torch.allclose(out, m(x), atol=1e-5)
