@@ -1,0 +1,119 @@
+"""Lowering pass: pairs of (collective, matmul) in a plan become single fused steps.
+
+The placement stage emits the textbook schedule of a tensor-parallel layer over sequence-sharded activations
+(compiler/mesh_compiler/placement.py:250-340, :812-834 in the reference): an all-gather of the activations, then the
+column-parallel matmul; the row-parallel matmul, then a reduce-scatter of its partial sums.  On the B200 each pair is
+one kernel (``mesh_b200/parallel/fused_linear.py``: the transfer runs tile by tile under the tensor-core work), so this
+pass rewrites
+
+    X_full = all_gather(X_shard); [view]; Y = mm(X_full, W_t)          ->   Y = fused ag_mm(X_shard, W_t)
+    P = mm(H, W_t); [view]; Y_shard = reduce_scatter(P)                ->   Y_shard = fused mm_rs(H, W_t)
+
+when the sharded dimension is the leading one of the flattened operand (rows of rank r are consecutive), the cut is
+equal and contiguous, and the intermediate values have no other consumer.  A fused step carries everything the
+unfused pair carried, so an executor without the kernels (CPU ranks, odd shapes) runs the pair as before; the report
+says how many pairs were found, which is also what the structure tests check.
+"""
+from __future__ import annotations
+
+import copy
+import math
+
+import torch
+
+from .ir import Plan, Ref, Step
+
+aten = torch.ops.aten
+_VIEWS = (aten.view.default, aten._unsafe_view.default, aten.reshape.default)
+
+
+def _uses(plan: Plan) -> dict[str, list[int]]:
+    uses: dict[str, list[int]] = {}
+
+    def walk(obj, i):
+        if isinstance(obj, Ref):
+            uses.setdefault(obj.name, []).append(i)
+        elif isinstance(obj, (tuple, list)):
+            for o in obj:
+                walk(o, i)
+        elif isinstance(obj, dict):
+            for o in obj.values():
+                walk(o, i)
+    for i, st in enumerate(plan.steps):
+        walk(st.args, i)
+        walk(st.kwargs, i)
+    for o in plan.outputs:
+        if isinstance(o, str):
+            uses.setdefault(o, []).append(len(plan.steps))
+    return uses
+
+
+def _leading(shape, dim) -> bool:
+    """Is ``dim`` the leading dimension of the flattened tensor (everything before it has size 1)?"""
+    return all(s == 1 for s in shape[:dim])
+
+
+def fuse_plan(plan: Plan) -> tuple[Plan, dict]:
+    """Returns a rewritten copy of ``plan`` and a report ``{"ag_mm": n, "mm_rs": n}``."""
+    plan = copy.copy(plan)
+    steps = list(plan.steps)
+    uses = _uses(plan)
+    producer = {st.out: i for i, st in enumerate(steps)}
+    drop: set[int] = set()
+    replace: dict[int, Step] = {}
+    report = {"ag_mm": 0, "mm_rs": 0}
+
+    def single_use(name) -> int | None:
+        u = uses.get(name, [])
+        return u[0] if len(u) == 1 else None
+
+    for i, st in enumerate(steps):
+        # ---- all_gather -> (view) -> mm
+        if st.op == "collective" and st.target == "all_gather" and i not in drop:
+            frm = st.meta["from"]
+            if frm.striped or len(set(frm.counts)) != 1 or not _leading(st.meta["full_shape"], frm.dim):
+                continue
+            j = single_use(st.out)
+            chain = [i]
+            cur = st.out
+            while j is not None and j < len(steps) and steps[j].op == "call" and steps[j].target in _VIEWS:
+                chain.append(j)
+                cur = steps[j].out
+                j = single_use(cur)
+            if j is None or j >= len(steps):
+                continue
+            mm = steps[j]
+            if mm.op != "call" or mm.target is not aten.mm.default or not isinstance(mm.args[0], Ref) or mm.args[0].name != cur:
+                continue
+            rows = int(math.prod(st.meta["full_shape"][: frm.dim + 1]))
+            k = int(math.prod(st.meta["full_shape"][frm.dim + 1:]))
+            meta = dict(mm.meta)
+            meta.update({"fused": "ag_mm", "axis": st.meta["axis"], "from": frm, "to": st.meta["to"], "rows": rows, "k": k,
+                         "gather_shape": st.meta["full_shape"], "channel": st.meta.get("channel"), "kind": st.meta.get("kind")})
+            replace[j] = Step("fused", mm.out, "ag_mm", (st.args[0], mm.args[1]), {}, meta)
+            drop.update(chain)
+            report["ag_mm"] += 1
+        # ---- mm -> (view) -> reduce_scatter
+        if st.op == "call" and st.target is aten.mm.default and i not in drop and i not in replace:
+            j = single_use(st.out)
+            chain = []
+            cur = st.out
+            while j is not None and j < len(steps) and steps[j].op == "call" and steps[j].target in _VIEWS:
+                chain.append(j)
+                cur = steps[j].out
+                j = single_use(cur)
+            if j is None or j >= len(steps):
+                continue
+            rs = steps[j]
+            if rs.op != "collective" or rs.target != "reduce_scatter" or rs.args[0].name != cur:
+                continue
+            to = rs.meta["to"]
+            if to.striped or len(set(to.counts)) != 1 or not _leading(rs.meta["full_shape"], to.dim) or rs.meta["from"].op != "sum":
+                continue
+            meta = dict(rs.meta)
+            meta.update({"fused": "mm_rs", "out_shape": rs.meta["full_shape"]})
+            replace[j] = Step("fused", rs.out, "mm_rs", (st.args[0], st.args[1]), {}, meta)
+            drop.update([i] + chain)
+            report["mm_rs"] += 1
+    plan.steps = [replace.get(i, st) for i, st in enumerate(steps) if i not in drop]
+    return plan, report

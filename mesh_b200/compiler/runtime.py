@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import math
 import operator
+import os
 import threading
 from typing import Any
 
@@ -300,12 +301,59 @@ class Executor:
                 env[st.out] = None if src is None else self._index(src, s.dim, local_indices(s, self.coords[ax], src.shape[s.dim]))
             elif st.op == "collective":
                 env[st.out] = self.collective(st, env[st.args[0].name])
+            elif st.op == "fused":
+                env[st.out] = self.fused(st, env[st.args[0].name], env[st.args[1].name])
             else:
                 env[st.out] = self.call(st, val)
         out = []
         for o in self.plan.outputs:
             out.append(o[1] if isinstance(o, tuple) else env[o])
         return out
+
+    # ---- fused (collective, matmul) pairs, see compiler/fuse.py
+    def _fused_kernels(self, kind: str, a, w_t, rows_total: int):
+        """The fused-kernel object for this shape, or None when the pair has to run unfused (CPU ranks, dtypes other
+        than bf16, shapes the kernels do not tile, no symmetric heap in this process)."""
+        if not (self.dist and a.is_cuda and a.dtype == torch.bfloat16 and w_t.dtype == torch.bfloat16):
+            return None
+        w = w_t.t()
+        P = self.mesh.size
+        if len(self.mesh.shape) != 1 or not w.is_contiguous() or rows_total % (P * 128) or w.shape[0] % 64 or w.shape[1] % 64:
+            return None
+        from ..distributed.context import current_or_none
+        ctx = current_or_none()
+        if ctx is None or ctx.world != P:
+            return None
+        cache = self.__dict__.setdefault("_fused_cache", {})
+        key = (kind, rows_total, tuple(w.shape))
+        if key not in cache:
+            from ..parallel.fused_linear import FusedColumnLinear, FusedRowLinear
+            cache[key] = (FusedColumnLinear(ctx.heap, rows_total, w.shape[1], w.shape[0]) if kind == "ag_mm"
+                          else FusedRowLinear(ctx.heap, rows_total, w.shape[1], w.shape[0]))
+        return cache[key]
+
+    def fused(self, st: Step, a, w_t):
+        m = st.meta
+        if a is None or w_t is None:
+            return None
+        if st.target == "ag_mm":
+            op = self._fused_kernels("ag_mm", a, w_t, m["rows"])
+            if op is not None:
+                y, _ = op.forward(a.reshape(-1, m["k"]).contiguous(), w_t.t())
+                return y
+            gathered = self.collective(Step("collective", st.out, "all_gather", (), {}, {**m, "full_shape": m["gather_shape"]}), a)
+            return aten.mm.default(gathered.reshape(m["rows"], m["k"]), w_t)
+        if st.target == "mm_rs":
+            shape = list(m["out_shape"])
+            op = self._fused_kernels("mm_rs", a, w_t, a.shape[0])
+            if op is not None:
+                y = op.forward(a.contiguous(), w_t.t())
+                to = m["to"]
+                shape[to.dim] = to.counts[self.coords[m["axis"]]]
+                return y.reshape(shape)
+            partial = aten.mm.default(a, w_t).reshape(shape)
+            return self.collective(Step("collective", st.out, "reduce_scatter", (), {}, m), partial)
+        raise NotImplementedError(st.target)
 
     def call(self, st: Step, val):
         args = list(val(a) for a in st.args)
@@ -374,6 +422,10 @@ class Program(Arguments):
     def __init__(self, scheduled: Scheduled, entry: str | None = None, device=None, threads: bool | None = None):
         super().__init__(scheduled)
         self.scheduled = scheduled
+        self.fusion = {"ag_mm": 0, "mm_rs": 0}
+        if os.environ.get("MESH_FUSE", "1") != "0":
+            from .fuse import fuse_plan
+            self.plan, self.fusion = fuse_plan(self.plan)
         self.mesh = scheduled.plan.mesh
         distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size() == self.mesh.size
         self.threads = (not distributed) if threads is None else threads

@@ -203,7 +203,8 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
     case EPI_STORE:
       if (ag) {
         if (!a->a_mn && !a->b_mn) MESH_LAUNCH(0, 0, EPI_STORE, true);
-        return set_error(-6, "gemm: all-gather fusion is built for K-major operands only");
+        if (!a->a_mn && a->b_mn) MESH_LAUNCH(0, 1, EPI_STORE, true);
+        return set_error(-6, "gemm: all-gather fusion needs K-major activations");
       }
       if (!a->a_mn && !a->b_mn) MESH_LAUNCH(0, 0, EPI_STORE, false);
       if (!a->a_mn && a->b_mn) MESH_LAUNCH(0, 1, EPI_STORE, false);

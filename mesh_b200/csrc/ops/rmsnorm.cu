@@ -51,54 +51,80 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // VPT = 16-byte vectors per thread (a row has up to VPT * 256 of them): sized to the row so that the registers
-// holding the row stay few and several CTAs per SM keep enough loads in flight to fill HBM.
-template <int VPT>
+// holding the row stay few and several CTAs per SM keep enough loads in flight to fill HBM.  RPP rows are processed
+// per pass (their loads are all issued before the first reduction), which doubles the bytes in flight for narrow rows.
+template <int VPT, int RPP>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int rows, int cols,
                    float eps, float w_offset) {
-  __shared__ float sh[32];
+  __shared__ float sh[RPP][32];
   const int nvec = cols >> 3;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
-    const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * cols) : nullptr;
-    float v[VPT][8];
-    float ss = 0.f;
+  for (int row0 = blockIdx.x * RPP; row0 < rows; row0 += gridDim.x * RPP) {
+    float v[RPP][VPT][8];
+    float ss[RPP];
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
-      if (c < nvec) {
-        unpack8(xr[c], v[i]);
-        if (rr) {
-          float r8[8];
-          unpack8(rr[c], r8);
+    for (int q = 0; q < RPP; ++q) {
+      const int row = row0 + q;
+      ss[q] = 0.f;
+      if (row < rows) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
+        const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * cols) : nullptr;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[i][j] += r8[j];
-          if (res_out) {
-            // the sum is rounded to bf16 once and that rounded value is what gets normalised
-            uint4 q = pack8(v[i]);
-            reinterpret_cast<uint4*>(res_out + (size_t)row * cols)[c] = q;
-            unpack8(q, v[i]);
+        for (int i = 0; i < VPT; ++i) {
+          const int c = threadIdx.x + i * NORM_THREADS;
+          if (c < nvec) {
+            unpack8(xr[c], v[q][i]);
+            if (rr) {
+              float r8[8];
+              unpack8(rr[c], r8);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[q][i][j] += r8[j];
+              if (res_out) {
+                // the sum is rounded to bf16 once and that rounded value is what gets normalised
+                uint4 qv = pack8(v[q][i]);
+                reinterpret_cast<uint4*>(res_out + (size_t)row * cols)[c] = qv;
+                unpack8(qv, v[q][i]);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss[q] += v[q][i][j] * v[q][i][j];
           }
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
       }
     }
-    ss = block_sum(ss, sh);
-    const float rstd = rsqrtf(ss / (float)cols + eps);
-    if (rstd_out && threadIdx.x == 0) rstd_out[row] = rstd;
-    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * cols);
+    // RPP block reductions share the barriers
+    const int wi = threadIdx.x >> 5, l = threadIdx.x & 31;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
-      if (c < nvec) {
-        float w8[8], o[8];
-        unpack8(reinterpret_cast<const uint4*>(w)[c], w8);
+    for (int q = 0; q < RPP; ++q) {
+      ss[q] = warp_sum(ss[q]);
+      if (l == 0) sh[q][wi] = ss[q];
+    }
+    __syncthreads();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * (w8[j] + w_offset);
-        yr[c] = pack8(o);
+    for (int q = 0; q < RPP; ++q) {
+      float t = (l < (NORM_THREADS >> 5)) ? sh[q][l] : 0.f;
+      ss[q] = warp_sum(t);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < RPP; ++q) {
+      const int row = row0 + q;
+      if (row >= rows) continue;
+      const float rstd = rsqrtf(ss[q] / (float)cols + eps);
+      if (rstd_out && threadIdx.x == 0) rstd_out[row] = rstd;
+      uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * cols);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * NORM_THREADS;
+        if (c < nvec) {
+          float w8[8], o[8];
+          unpack8(reinterpret_cast<const uint4*>(w)[c], w8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = v[q][i][j] * rstd * (w8[j] + w_offset);
+          yr[c] = pack8(o);
+        }
       }
     }
   }
@@ -187,16 +213,20 @@ extern "C" int mesh_rmsnorm_fwd(const void* x, const void* residual, const void*
   if (rows <= 0) return 0;
   if (cols % 8 || cols > NORM_THREADS * MAX_VEC_PER_THREAD * 8)
     return set_error(-2, "rmsnorm: cols must be a multiple of 8 and <= %d", NORM_THREADS * MAX_VEC_PER_THREAD * 8);
-  const int grid = rows < 148 * 16 ? rows : 148 * 16;
   const int nvec = cols / 8;
-#define FWD(V)                                                                                                     \
-  rmsnorm_fwd_kernel<V><<<grid, NORM_THREADS, 0, (cudaStream_t)stream>>>(                                           \
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,          \
-      (__nv_bfloat16*)residual_out, rstd, rows, cols, eps, w_offset)
-  if (nvec <= NORM_THREADS) FWD(1);
-  else if (nvec <= 2 * NORM_THREADS) FWD(2);
-  else if (nvec <= 4 * NORM_THREADS) FWD(4);
-  else FWD(8);
+#define FWD(V, R)                                                                                                  \
+  do {                                                                                                             \
+    const int passes = (rows + (R) - 1) / (R);                                                                     \
+    const int grid = passes < 148 * 16 ? passes : 148 * 16;                                                        \
+    rmsnorm_fwd_kernel<V, R><<<grid, NORM_THREADS, 0, (cudaStream_t)stream>>>(                                      \
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,        \
+        (__nv_bfloat16*)residual_out, rstd, rows, cols, eps, w_offset);                                            \
+  } while (0)
+  const bool many = rows >= 148 * 8;        // enough rows that pairing them does not idle SMs
+  if (nvec <= NORM_THREADS) { if (many) FWD(1, 2); else FWD(1, 1); }
+  else if (nvec <= 2 * NORM_THREADS) { if (many) FWD(2, 2); else FWD(2, 1); }
+  else if (nvec <= 4 * NORM_THREADS) FWD(4, 1);
+  else FWD(8, 1);
 #undef FWD
   MESH_CUDA_OK(cudaGetLastError());
   return 0;

@@ -96,9 +96,10 @@ class _GatherKV(torch.autograd.Function):
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg: HybridConfig, par: ParallelContext, layer: int, dtype, device):
+    def __init__(self, cfg: HybridConfig, par: ParallelContext, layer: int, dtype, device, in_flight: int = 1):
         super().__init__()
-        self.cfg, self.par = cfg, par
+        self.cfg, self.par, self.in_flight = cfg, par, in_flight
+        self._fused = {}
         tp = par.tp
         assert cfg.n_heads % tp.world == 0 and cfg.n_kv_heads % tp.world == 0, "heads must divide over tp"
         self.Hq, self.Hkv, self.hd = cfg.n_heads // tp.world, cfg.n_kv_heads // tp.world, cfg.head_dim
@@ -120,13 +121,33 @@ class Attention(nn.Module):
             self._rope = rope_tables(self.cfg.seq_len, self.hd, self.cfg.rope_theta, device=device)
         return self._rope
 
+    def _fused_ops(self, tokens: int):
+        """The fused projection kernels for ``tokens`` rows over the tensor axis (None when the shape does not fit)."""
+        if tokens not in self._fused:
+            tp = self.par.tp
+            nq = (self.Hq + 2 * self.Hkv) * self.hd
+            ok = tokens % (tp.world * 128) == 0 and nq % 64 == 0 and (self.Hq * self.hd) % 64 == 0 and self.cfg.d_model % 64 == 0
+            if ok:
+                from ..parallel.fused_linear import FusedColumnLinear, FusedRowLinear
+                self._fused[tokens] = (FusedColumnLinear(tp.heap, tokens, self.cfg.d_model, nq, in_flight=self.in_flight),
+                                       FusedRowLinear(tp.heap, tokens, self.Hq * self.hd, self.cfg.d_model))
+            else:
+                self._fused[tokens] = None
+        return self._fused[tokens]
+
     def forward(self, x, B: int, pos: torch.Tensor):
         """``x [B*Tc/tp, D]`` (this rank's tokens) -> same shape.  ``pos [Tc]``: logical positions of the cp shard."""
         cfg, par = self.cfg, self.par
         tp, cp = par.tp, par.cp
-        xg = all_gather_seq(x, tp) if tp.world > 1 else x
-        Tc = xg.shape[0] // B
-        qkv = _linear(xg, self.w_qkv).view(B, Tc, self.Hq + 2 * self.Hkv, self.hd)
+        fused = self._fused_ops(x.shape[0] * tp.world) if (tp.world > 1 and _fast(x)) else None
+        if fused is not None:
+            from ..parallel.fused_linear import column_linear
+            qkv = column_linear(x, self.w_qkv, fused[0])          # all-gather fused into the QKV GEMM
+        else:
+            xg = all_gather_seq(x, tp) if tp.world > 1 else x
+            qkv = _linear(xg, self.w_qkv)
+        Tc = qkv.shape[0] // B
+        qkv = qkv.view(B, Tc, self.Hq + 2 * self.Hkv, self.hd)
         q, k, v = qkv[:, :, : self.Hq], qkv[:, :, self.Hq: self.Hq + self.Hkv], qkv[:, :, self.Hq + self.Hkv:]
         if _fast(x):
             from ..ops.attention import attention, ring_attention_autograd
@@ -152,19 +173,22 @@ class Attention(nn.Module):
             s = torch.einsum("bthd,bshd->bhts", q, kf) * self.hd ** -0.5
             s = s.masked_fill((kpos[None, :] > pos[:, None])[None, None], float("-inf"))
             o = torch.einsum("bhts,bshd->bthd", torch.softmax(s.float(), -1).to(q.dtype), vf)
+        if fused is not None:
+            from ..parallel.fused_linear import row_linear
+            return row_linear(o.reshape(B * Tc, self.Hq * self.hd), self.w_o, fused[1])   # GEMM -> reduce-scatter
         y = _linear(o.reshape(B * Tc, self.Hq * self.hd), self.w_o)
         return reduce_scatter_seq(y, tp) if tp.world > 1 else y
 
 
 class Block(nn.Module):
-    def __init__(self, cfg: HybridConfig, par: ParallelContext, layer: int, dtype, device):
+    def __init__(self, cfg: HybridConfig, par: ParallelContext, layer: int, dtype, device, in_flight: int = 1):
         super().__init__()
         self.cfg = cfg
         self.norm1 = nn.Parameter(torch.ones(cfg.d_model, dtype=dtype, device=device))
         self.norm2 = nn.Parameter(torch.ones(cfg.d_model, dtype=dtype, device=device))
-        self.attn = Attention(cfg, par, layer, dtype, device)
+        self.attn = Attention(cfg, par, layer, dtype, device, in_flight)
         self.ffn = TPGatedFFN(cfg.d_model, cfg.d_ff, par.tp, cfg.act, sequence_parallel=True, dtype=dtype, device=device,
-                              init_std=cfg.init_std, seed=2000 + layer)
+                              init_std=cfg.init_std, seed=2000 + layer, in_flight=in_flight)
 
     def forward(self, x, B, pos):
         x = x + self.attn(_norm(x, self.norm1, self.cfg.eps), B, pos)
@@ -181,12 +205,13 @@ def shard_positions(cfg: HybridConfig, cp_world: int, cp_rank: int, device) -> t
 class HybridStage(nn.Module):
     """The layers of one pipeline stage (plus the embedding on the first and the head on the last)."""
 
-    def __init__(self, cfg: HybridConfig, par: ParallelContext, dtype=torch.bfloat16, device=None):
+    def __init__(self, cfg: HybridConfig, par: ParallelContext, dtype=torch.bfloat16, device=None, in_flight: int = 1):
         super().__init__()
         self.cfg, self.par = cfg, par
         device = device or par.device
         self.layers_range = split_layers(cfg.n_layers, par.pp.world)[par.pp.rank]
-        self.blocks = nn.ModuleList(Block(cfg, par, i, dtype, device) for i in self.layers_range)
+        # in_flight: forward passes of this stage that can run before their backward passes (pipeline warm-up)
+        self.blocks = nn.ModuleList(Block(cfg, par, i, dtype, device, in_flight) for i in self.layers_range)
         g = torch.Generator(device="cpu").manual_seed(7)
         emb = torch.empty(cfg.vocab, cfg.d_model).normal_(0, cfg.init_std, generator=g)
         head = torch.empty(cfg.vocab, cfg.d_model).normal_(0, cfg.init_std, generator=g)
@@ -230,7 +255,7 @@ class HybridTrainer:
                  dtype=torch.bfloat16):
         from ..parallel.optim import ShardedAdamW
         self.cfg, self.par, self.mb, self.M = cfg, par, micro_batch, n_micro
-        self.stage = HybridStage(cfg, par, dtype=dtype)
+        self.stage = HybridStage(cfg, par, dtype=dtype, in_flight=max(1, min(n_micro, par.pp.world - par.pp.rank)))
         self.dtype = dtype
         self.params = [p for p in self.stage.parameters()]
         dp = par.dp

@@ -64,10 +64,10 @@ class _FusedBase:
 class FusedColumnLinear(_FusedBase):
     """``w``: this rank's ``[N_local, D]`` rows of the weight."""
 
-    def __init__(self, heap, tokens: int, d_in: int, n_local: int):
+    def __init__(self, heap, tokens: int, d_in: int, n_local: int, in_flight: int = 1):
         super().__init__(heap, tokens, d_in, n_local)
         self.D, self.N = d_in, n_local
-        self.x_full = _Gathered(heap, tokens, d_in)
+        self.x_full = _Gathered(heap, tokens, d_in, copies=in_flight + 1)   # X is read again by the backward pass
         self.dx_recv = _Scattered(heap, self.world, self.rows, d_in)
 
     def forward(self, x: torch.Tensor, w: torch.Tensor):

@@ -33,7 +33,7 @@ class TPGatedFFN(nn.Module):
 
     def __init__(self, d_model: int, d_ff: int, ctx: MeshContext | None = None, act: str = "silu",
                  sequence_parallel: bool = True, dtype=torch.bfloat16, device=None, init_std: float = 0.02,
-                 seed: int = 0):
+                 seed: int = 0, in_flight: int = 1):
         super().__init__()
         self.ctx = ctx or context()
         P, r = self.ctx.world, self.ctx.rank
@@ -53,11 +53,12 @@ class TPGatedFFN(nn.Module):
         self.w_down = nn.Parameter(wd.contiguous().to(device=device, dtype=dtype))
         self._fused = None
         self._fused_tokens = None
+        self.in_flight = in_flight          # forward passes that may run before their backward passes (pipeline microbatches)
 
     def _fused_op(self, tokens_total: int):
         if self._fused is None or self._fused_tokens != tokens_total:
             from .tp_ffn import FusedTPFFN
-            self._fused = FusedTPFFN(self.ctx.heap, tokens_total, self.d_model, self.d_ff, self.act)
+            self._fused = FusedTPFFN(self.ctx.heap, tokens_total, self.d_model, self.d_ff, self.act, in_flight=self.in_flight)
             self._fused_tokens = tokens_total
         return self._fused
 

@@ -34,16 +34,22 @@ EPI_WARPS = 4
 
 
 class _Gathered:
-    """A double-buffered all-gather landing zone [M, D] with per-128-row arrival counters."""
+    """An all-gather landing zone [M, D] with per-128-row arrival counters, ``copies`` buffers used in turn.
 
-    def __init__(self, heap: SymmetricHeap, M: int, D: int):
-        self.buf = [heap.alloc((M, D), torch.bfloat16) for _ in range(2)]
-        self.flags = [heap.alloc_signals(M // BM) for _ in range(2)]
-        self.uses = [0, 0]
+    Two copies are enough for the exchange itself (a rank can be at most one use ahead of a peer).  The gathered
+    tensor is also what the weight-gradient GEMM of the backward pass reads, so a caller that runs several forward
+    passes before the matching backward passes (pipeline microbatches) asks for as many copies as passes in flight."""
+
+    def __init__(self, heap: SymmetricHeap, M: int, D: int, copies: int = 2):
+        copies = max(2, copies)
+        self.copies = copies
+        self.buf = [heap.alloc((M, D), torch.bfloat16) for _ in range(copies)]
+        self.flags = [heap.alloc_signals(M // BM) for _ in range(copies)]
+        self.uses = [0] * copies
         self.turn = 0
 
     def next(self):
-        par = self.turn & 1
+        par = self.turn % self.copies
         self.turn += 1
         self.uses[par] += 1
         return self.buf[par], self.flags[par], AG_SPLIT * self.uses[par]
@@ -76,7 +82,7 @@ class FusedTPFFN:
     ``w_gate_up``: this rank's ``[2*F/world, D]`` (gate rows, then up rows); ``w_down``: ``[D, F/world]``.
     """
 
-    def __init__(self, heap: SymmetricHeap, tokens: int, d_model: int, d_ff: int, act: str = "silu"):
+    def __init__(self, heap: SymmetricHeap, tokens: int, d_model: int, d_ff: int, act: str = "silu", in_flight: int = 1):
         self.heap = heap
         self.rank, self.world = heap.rank, heap.world
         self.M, self.D, self.F = tokens, d_model, d_ff
@@ -88,7 +94,7 @@ class FusedTPFFN:
             raise ValueError("d_ff/world and d_model must be multiples of 64")
         self.rows = tokens // P
         self.Fl = d_ff // P
-        self.x_full = _Gathered(heap, tokens, d_model)
+        self.x_full = _Gathered(heap, tokens, d_model, copies=in_flight + 1)
         self.dy_full = _Gathered(heap, tokens, d_model)
         self.y_recv = _Scattered(heap, P, self.rows, d_model)
         self.dx_recv = _Scattered(heap, P, self.rows, d_model)

@@ -177,3 +177,31 @@ def test_convolution_with_halo_exchange(n, dim):
     assert verbs.get("halo", 0) == 2 and verbs.get("all_gather", 0) == 1, verbs      # two exchanges, one gather of the result
     out = Program(sch)(x)
     assert torch.allclose(out, m(x), atol=1e-5)
+
+
+def test_collective_matmul_pairs_are_fused_and_results_unchanged(monkeypatch):
+    """Sequence-parallel Megatron block: the all-gather -> mm and mm -> reduce-scatter pairs become fused steps
+    (run unfused on CPU ranks), and the program computes what it computed before the rewrite."""
+    torch.manual_seed(8)
+    m = Decoder(dim=64, heads=4, ffn=128, layers=2)
+    x = torch.randn(1, 16, 64)
+    procs = _procs(2)
+    names = tuple(procs)
+    tp = megatron(procs)
+
+    def placement(node):
+        if node.op == "placeholder" and node.name == "x":
+            return (1, names, None)
+        return tp(node)
+    sch = compile_module(m, (x,), procs, placement, loss=0)
+    prog = Program(sch)
+    assert prog.fusion["ag_mm"] >= 4 and prog.fusion["mm_rs"] >= 2, prog.fusion
+    assert any(st.op == "fused" for st in prog.plan.steps)
+    res = prog(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads, tol=5e-5)
+    monkeypatch.setenv("MESH_FUSE", "0")
+    plain = Program(sch)
+    assert plain.fusion == {"ag_mm": 0, "mm_rs": 0}
+    res2 = plain(x)
+    assert abs(float(res2.outputs) - float(res.outputs)) < 1e-6
