@@ -21,6 +21,8 @@ def main():
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--micro", type=int, default=8)
     a = ap.parse_args()
+    from mesh_b200.config import MeshConfig, set_config
+    set_config(MeshConfig.from_env(heap_bytes=16 << 30))      # gathered activations of every layer live in the heap
     ctx = init()
     from mesh_b200 import _native
     from mesh_b200.models.hybrid import HybridConfig, HybridTrainer

@@ -20,7 +20,7 @@ import torch
 from .. import _native
 from ..ops import gemm as G
 from ..utils.status import status_block
-from .tp_ffn import BM, _Gathered, _Scattered
+from .tp_ffn import BM, _Gathered, _Scattered, shared_zone
 
 
 class _FusedBase:
@@ -68,7 +68,7 @@ class FusedColumnLinear(_FusedBase):
         super().__init__(heap, tokens, d_in, n_local)
         self.D, self.N = d_in, n_local
         self.x_full = _Gathered(heap, tokens, d_in, copies=in_flight + 1)   # X is read again by the backward pass
-        self.dx_recv = _Scattered(heap, self.world, self.rows, d_in)
+        self.dx_recv = shared_zone(heap, _Scattered, self.world, self.rows, d_in)
 
     def forward(self, x: torch.Tensor, w: torch.Tensor):
         dev = x.device
@@ -102,8 +102,8 @@ class FusedRowLinear(_FusedBase):
     def __init__(self, heap, tokens: int, k_local: int, d_out: int):
         super().__init__(heap, tokens, k_local, d_out)
         self.K, self.D = k_local, d_out
-        self.y_recv = _Scattered(heap, self.world, self.rows, d_out)
-        self.dy_full = _Gathered(heap, tokens, d_out)
+        self.y_recv = shared_zone(heap, _Scattered, self.world, self.rows, d_out)
+        self.dy_full = shared_zone(heap, _Gathered, tokens, d_out)
 
     def forward(self, h: torch.Tensor, w: torch.Tensor):
         dev = h.device

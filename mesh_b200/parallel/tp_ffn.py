@@ -76,6 +76,18 @@ class _Scattered:
         return self.buf[par], self.count[par], self.world * EPI_WARPS * self.uses[par]
 
 
+def shared_zone(heap, cls, *shape):
+    """Landing zones that hold data only while one kernel pair runs (reduce-scatter partials, gathered gradients) are
+    shared by every layer of the same shape on a heap: layers run one after the other, and the zones' counters are
+    monotonic, so consecutive users simply continue the sequence.  (The gathered activations are not shared: the
+    backward pass reads them again.)"""
+    zones = heap.__dict__.setdefault("_zones", {})
+    key = (cls.__name__, *shape)
+    if key not in zones:
+        zones[key] = cls(heap, *shape)
+    return zones[key]
+
+
 class FusedTPFFN:
     """Holds the symmetric workspaces of one (M, D, F) FFN shape and runs its six fused kernels.
 
@@ -95,9 +107,9 @@ class FusedTPFFN:
         self.rows = tokens // P
         self.Fl = d_ff // P
         self.x_full = _Gathered(heap, tokens, d_model, copies=in_flight + 1)
-        self.dy_full = _Gathered(heap, tokens, d_model)
-        self.y_recv = _Scattered(heap, P, self.rows, d_model)
-        self.dx_recv = _Scattered(heap, P, self.rows, d_model)
+        self.dy_full = shared_zone(heap, _Gathered, tokens, d_model)
+        self.y_recv = shared_zone(heap, _Scattered, P, self.rows, d_model)
+        self.dx_recv = self.y_recv          # forward and backward never overlap within a rank's stream
         self._saved = None
 
     # ---------------------------------------------------------------- kernels
