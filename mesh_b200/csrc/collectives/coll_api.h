@@ -39,6 +39,9 @@ int mesh_coll_max_blocks(void);
 // bytes: payload of this rank.  All functions return 0 / negative argument error / positive cudaError_t.
 int mesh_coll_allreduce(const MeshCommArgs* c, const void* in, void* out, uint64_t count, int dtype, int op,
                         int two_shot, void* stream);
+// The same sum through the NVSwitch (multimem.ld_reduce / multimem.st on the heap's multicast mapping).
+int mesh_coll_allreduce_mc(const MeshCommArgs* c, void* mc_staging, const void* in, void* out, uint64_t count, int dtype,
+                           void* stream);
 int mesh_coll_allgather(const MeshCommArgs* c, const void* in, void* out, uint64_t bytes_per_rank, void* stream);
 // v-variant: rank r contributes counts[r] bytes placed at displs[r] in the output.
 int mesh_coll_allgatherv(const MeshCommArgs* c, const void* in, void* out, const uint64_t* counts,

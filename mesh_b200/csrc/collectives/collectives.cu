@@ -370,6 +370,69 @@ __global__ void wait_flag_test_kernel(const uint32_t* flag, uint32_t expect, uns
   if (threadIdx.x == 0 && blockIdx.x == 0) wait_flag_ge(flag, expect, st, SITE_HOST_FLAG, limit_ns);
 }
 
+// ------------------------------------------------------------------------------ in-switch all-reduce (NVLS)
+// With a multicast mapping of the heap, one `multimem.ld_reduce` returns the sum over every rank's copy of an address
+// (the switch adds) and one `multimem.st` writes a value into every rank's copy.  Two-shot form: this rank reduces its
+// slice through the multicast address of the staging buffers' first half and broadcasts the result into their
+// second half; after the second round of signals every rank copies the complete result out of its own memory.
+// Sum only; bf16 / f16 accumulate in fp32 inside the switch.
+template <typename T> struct McOps;
+template <> struct McOps<float> {
+  static __device__ __forceinline__ uint4 ld(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct McOps<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct McOps<__half> {
+  static __device__ __forceinline__ uint4 ld(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS) allreduce_mc_kernel(Comm c, uint8_t* mc_staging, const T* in, T* out, uint64_t count) {
+  const uint32_t all = (1u << c.world) - 1u;
+  constexpr uint64_t V = 16 / sizeof(T);
+  const uint64_t padded = (count + V - 1) / V * V;
+  copy_bytes(c.staging[c.rank] + HDR, reinterpret_cast<const uint8_t*>(in), count * sizeof(T));
+  // the tail of the last vector must not hold stale data: it is summed by the switch like everything else
+  for (uint64_t i = count + gtid(); i < padded; i += gsize()) reinterpret_cast<T*>(c.staging[c.rank] + HDR)[i] = T(0);
+  signal_all(c, 0);
+  if (!wait_ranks(c, 0, c.expect_a, all)) return;
+  const uint64_t nv = padded / V;
+  const uint64_t per = (nv + c.world - 1) / c.world;
+  const uint64_t lo = min(nv, (uint64_t)c.rank * per), hi = min(nv, lo + per);
+  const uint64_t half = (c.staging_bytes / 2) & ~(uint64_t)15;
+  uint4* src = reinterpret_cast<uint4*>(mc_staging + HDR);
+  uint4* dst = reinterpret_cast<uint4*>(mc_staging + HDR + half);
+  for (uint64_t i = lo + gtid(); i < hi; i += gsize()) McOps<T>::st(dst + i, McOps<T>::ld(src + i));
+  signal_all(c, 1);
+  if (!wait_ranks(c, 1, c.expect_b, all)) return;
+  copy_bytes(reinterpret_cast<uint8_t*>(out), c.staging[c.rank] + HDR + half, count * sizeof(T));
+}
+
 // ------------------------------------------------------------------------------ host side
 static int make_comm(const MeshCommArgs* a, Comm* c) {
   if (a->world < 1 || a->world > R) return set_error(-4, "collective: world %d out of range", a->world);
@@ -452,6 +515,26 @@ extern "C" int mesh_coll_allreduce(const MeshCommArgs* a, const void* in, void* 
 #define CALL(T) launch_allreduce<T>(c, grid, in, out, count, op, two_shot, (cudaStream_t)stream)
   MESH_DISPATCH_DTYPE(dtype, CALL)
 #undef CALL
+}
+
+// In-switch variant: `mc_staging` is the multicast address of this call's staging buffer.  Sum of f32 / bf16 / f16 only.
+extern "C" int mesh_coll_allreduce_mc(const MeshCommArgs* a, void* mc_staging, const void* in, void* out, uint64_t count,
+                                      int dtype, void* stream) {
+  Comm c;
+  if (int rc = make_comm(a, &c)) return rc;
+  if (mc_staging == nullptr) return set_error(-11, "allreduce_mc: the heap has no multicast mapping");
+  const uint64_t bytes = (count * esize(dtype) + 15) & ~15ull;
+  if (bytes > (a->staging_bytes / 2 & ~15ull)) return set_error(-10, "allreduce_mc: message exceeds half the staging buffer");
+  const int grid = grid_of(a);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case MESH_F32: allreduce_mc_kernel<float><<<grid, THREADS, 0, s>>>(c, (uint8_t*)mc_staging, (const float*)in, (float*)out, count); break;
+    case MESH_BF16: allreduce_mc_kernel<__nv_bfloat16><<<grid, THREADS, 0, s>>>(c, (uint8_t*)mc_staging, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, count); break;
+    case MESH_F16: allreduce_mc_kernel<__half><<<grid, THREADS, 0, s>>>(c, (uint8_t*)mc_staging, (const __half*)in, (__half*)out, count); break;
+    default: return set_error(-9, "allreduce_mc: sums of f32, bf16 and f16 only");
+  }
+  MESH_CUDA_OK(cudaGetLastError());
+  return 0;
 }
 
 extern "C" int mesh_coll_allgatherv(const MeshCommArgs* a, const void* in, void* out, const uint64_t* counts,

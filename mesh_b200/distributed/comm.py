@@ -86,6 +86,7 @@ class Communicator:
         self.L = _native.lib()
         self.max_blocks = self.L.mesh_coll_max_blocks()
         self.one_shot_max = config().one_shot_max_bytes
+        self.use_nvls = bool(config().nvls and getattr(heap, "mc_ptr", 0))
         self.calls = 0
 
     # ------------------------------------------------------------------ plumbing
@@ -139,6 +140,16 @@ class Communicator:
             nbytes = cnt * es
             two = nbytes > self.one_shot_max and self.world > 1
             nb = self._blocks(nbytes)
+            mc = self._staging[self._turn & 1].mc_ptr if (self.use_nvls and two and opc == SUM and dt in (F32, BF16, F16)) else 0
+            if mc:
+                # in-switch reduction: the heap has a multicast mapping (MESH_NVLS=1)
+                a = self._args(nb, two_step=True)
+                rc = self.L.mesh_coll_allreduce_mc(ctypes.byref(a), c_void_p(mc), c_void_p(flat_in[pos:].data_ptr()),
+                                                   c_void_p(flat_out[pos:].data_ptr()), c_uint64(cnt), c_int(dt), _stream())
+                _native.check(rc, "mesh_coll_allreduce_mc")
+                _native.count_launch()
+                pos += cnt
+                continue
             a = self._args(nb, two_step=two)
             rc = self.L.mesh_coll_allreduce(ctypes.byref(a), c_void_p(flat_in[pos:].data_ptr() if n else 0),
                                             c_void_p(flat_out[pos:].data_ptr() if n else 0), c_uint64(cnt), c_int(dt),
