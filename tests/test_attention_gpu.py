@@ -70,7 +70,7 @@ def test_ring_attention_two_ranks(striped):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_ring_rank, 2, striped, use_cuda=True)
+    spawn_ranks(_ring_rank, 2, striped, use_cuda=True, timeout=300.0)
 
 
 def _ref_grads(q, k, v, dout, causal, window):
@@ -134,4 +134,4 @@ def test_ring_attention_backward_two_ranks(striped):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_ring_bwd_rank, 2, striped, use_cuda=True)
+    spawn_ranks(_ring_bwd_rank, 2, striped, use_cuda=True, timeout=300.0)

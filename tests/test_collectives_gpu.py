@@ -94,7 +94,7 @@ def _run(rank, world, rdv):
 
 def test_collectives_world1():
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_run, 1, use_cuda=True)
+    spawn_ranks(_run, 1, use_cuda=True, timeout=300.0)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -102,7 +102,7 @@ def test_collectives_multi(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_run, world, use_cuda=True)
+    spawn_ranks(_run, world, use_cuda=True, timeout=300.0)
 
 
 def test_bounded_wait_reports_timeout():

@@ -132,4 +132,4 @@ def test_e2b_tensor_parallel(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_tp_rank, world, use_cuda=True)
+    spawn_ranks(_tp_rank, world, use_cuda=True, timeout=300.0)

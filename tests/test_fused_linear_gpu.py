@@ -52,4 +52,4 @@ def test_fused_column_and_row_linear(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_rank, world, use_cuda=True)
+    spawn_ranks(_rank, world, use_cuda=True, timeout=300.0)

@@ -45,4 +45,4 @@ def test_hybrid_training_step(dims):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_rank, world, dims, use_cuda=True, init_pg="nccl" if world > 1 else None)
+    spawn_ranks(_rank, world, dims, use_cuda=True, timeout=300.0, init_pg="nccl" if world > 1 else None)

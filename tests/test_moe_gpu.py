@@ -65,4 +65,4 @@ def test_moe_expert_parallel(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_run, world, 256, 256, 128, 8 * world // 2 if world > 2 else 8, 2, 2, use_cuda=True)
+    spawn_ranks(_run, world, 256, 256, 128, 8 * world // 2 if world > 2 else 8, 2, 2, use_cuda=True, timeout=300.0)

@@ -69,4 +69,4 @@ def test_fused_tp_ffn_multi(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_run_rank, world, 128 * world * 2, 256, 64 * world * 2, 3, use_cuda=True)
+    spawn_ranks(_run_rank, world, 128 * world * 2, 256, 64 * world * 2, 3, use_cuda=True, timeout=300.0)
