@@ -111,6 +111,9 @@ class Executor:
         self.mesh = plan.mesh
         self.coords = self.mesh.coords(rank)
         self.dist = isinstance(coll, DistCollectives)
+        # with MESH_SYNC_TRACE=1 every collective that actually runs is logged, to be compared with the compiled
+        # synchronisation signature (compiler/syncmon.py)
+        self.trace = [] if os.environ.get("MESH_SYNC_TRACE", "0") == "1" else None
 
     # ---- shards of full tensors
     def shard(self, full: torch.Tensor, specs: tuple) -> torch.Tensor | None:
@@ -139,6 +142,8 @@ class Executor:
         ax, frm, to, verb = m["axis"], m["from"], m["to"], step.target
         P = self.mesh.shape[ax]
         me = self.coords[ax]
+        if self.trace is not None and "channel" in m:
+            self.trace.append((verb, m.get("kind"), ax, m["channel"]))
         if P == 1 and verb != "halo":
             return t
         if verb == "halo":
@@ -339,6 +344,8 @@ class Executor:
         if st.target == "ag_mm":
             op = self._fused_kernels("ag_mm", a, w_t, m["rows"])
             if op is not None:
+                if self.trace is not None:
+                    self.trace.append(("all_gather", m.get("kind"), m["axis"], m["channel"]))
                 y, _ = op.forward(a.reshape(-1, m["k"]).contiguous(), w_t.t())
                 return y
             gathered = self.collective(Step("collective", st.out, "all_gather", (), {}, {**m, "full_shape": m["gather_shape"]}), a)
@@ -347,6 +354,8 @@ class Executor:
             shape = list(m["out_shape"])
             op = self._fused_kernels("mm_rs", a, w_t, a.shape[0])
             if op is not None:
+                if self.trace is not None:
+                    self.trace.append(("reduce_scatter", m.get("kind"), m["axis"], m["channel"]))
                 y = op.forward(a.contiguous(), w_t.t())
                 to = m["to"]
                 shape[to.dim] = to.counts[self.coords[m["axis"]]]

@@ -77,3 +77,38 @@ def test_simulate_reports_wrong_expectation():
     progs = {0: [Launch("k", pre=[(1, "c", 1)], waits=[("c", 2)])], 1: [Launch("k", pre=[(0, "c", 1)], waits=[("c", 1)])]}
     stuck = simulate(progs)
     assert len(stuck) == 1 and "rank 0" in stuck[0] and "c >= 2 (is 1)" in stuck[0]
+
+
+def test_sync_monitor_matches_the_signature_and_names_divergence(monkeypatch):
+    from mesh_b200.compiler import Program, compile_module, syncmon
+    from mesh_b200.compiler.runtime import Executor, ThreadCollectives, ThreadWorld
+    from mesh_b200.models.llama import Decoder, megatron
+    monkeypatch.setenv("MESH_SYNC_TRACE", "1")
+    torch.manual_seed(0)
+    m = Decoder(dim=32, heads=2, ffn=64, layers=1)
+    x = torch.randn(1, 8, 32)
+    procs = {"a": (0, "cpu"), "b": (0, "cpu")}
+    names = tuple(procs)
+    tp = megatron(procs)
+    sch = compile_module(m, (x,), procs, lambda n: (1, names, None) if n.op == "placeholder" and n.name == "x" else tp(n))
+    prog = Program(sch)                       # fused steps included: they log the collective they stand for
+    # run rank by rank in threads, keeping the executors to read their traces
+    import threading
+    bound = prog.prepare((x,), {})
+    world = ThreadWorld(2)
+    exes = [Executor(prog.plan, r, ThreadCollectives(world, prog.mesh, r), torch.device("cpu")) for r in range(2)]
+    ts = [threading.Thread(target=lambda e=e: e.run(bound, prog._consts)) for e in exes]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    for e in exes:
+        rep = syncmon.compare(sch, e.trace, prog.plan)
+        assert rep["ok"] and rep["count_observed"] == rep["count_expected"] > 0, rep
+    # without the fusion pass the executed order is the scheduled one and the digest is the compiled signature's
+    assert syncmon.digest(sch, syncmon.expected(sch.plan)) == sch.signature.digest
+    # a skipped collective and a swapped pair are named
+    t = list(exes[0].trace)
+    rep = syncmon.compare(sch, t[:3] + t[4:], prog.plan)
+    assert not rep["ok"] and rep["first_divergence"]["index"] == 3 and len(rep["missing"]) == 1
+    t[1], t[2] = t[2], t[1]
+    rep = syncmon.compare(sch, t, prog.plan)
+    assert not rep["ok"] and rep["first_divergence"]["index"] == 1 and rep["missing"] == []
