@@ -154,3 +154,108 @@ class CodedLinear(torch.nn.Module):
             from .decode import decode_linear
             return decode_linear(x2.contiguous(), self.codes, scales=self.scales).reshape(*lead, self.out_features)
         return torch.nn.functional.linear(x2, self.dense().to(x2.dtype)).reshape(*lead, self.out_features)
+
+
+# ------------------------------------------------------------------------------------------------ coded matrices
+def hadamard_transform(x: torch.Tensor) -> torch.Tensor:
+    """Unnormalised fast Walsh-Hadamard transform along the last dimension (a power of two)."""
+    n = x.shape[-1]
+    if n & (n - 1):
+        raise ValueError("the Hadamard transform needs a power-of-two width")
+    y, step = x, 1
+    while step < n:
+        pair = y.reshape(*y.shape[:-1], -1, 2 * step)
+        a, b = pair[..., :step], pair[..., step:]
+        y = torch.cat((a + b, a - b), -1).reshape(x.shape)
+        step *= 2
+    return y
+
+
+class CodedMatrix(torch.nn.Module):
+    """A ``fragment``-coded weight matrix with the input transform it was coded under.
+
+    Quantisation error shrinks when the inputs are decorrelated first, so a coded matrix may come with (one of) a
+    column order, a dense rotation of the input, or a sign flip followed by a Hadamard transform; ``forward`` applies
+    the transform and multiplies by the decoded weights.  ``select`` restricts the matrix to some output rows /
+    input columns (tensor-parallel shards).  The fields are those of the reference's ``Matrix``
+    (rdma/mesh_code.py:19-64): ``codes, tiles, bands, row_scale, col_scale`` plus optional ``row_order``,
+    ``col_order``, ``rotation`` + ``rotation_scale``, ``signs``."""
+
+    def __init__(self, fields: dict, rows=None, columns=None):
+        super().__init__()
+        self.names = tuple(fields)
+        for k, v in fields.items():
+            self.register_buffer(k, v)
+        R, C = fields["tiles"].shape[0] * 32, fields["tiles"].shape[1] * 32
+        row_order = fields.get("row_order", torch.arange(R)).long()
+        col_order = fields.get("col_order", torch.arange(C)).long()
+        rows = torch.arange(R) if rows is None else torch.as_tensor(rows).long()
+        columns = torch.arange(C) if columns is None else torch.as_tensor(columns).long()
+        # stored row i holds logical row row_order[i]: find where the wanted logical rows are stored
+        self.register_buffer("stored_rows", torch.argsort(row_order)[rows])
+        self.register_buffer("input_ids", columns)
+        mixes = "rotation" in fields or "signs" in fields
+        stored_cols = torch.argsort(col_order)[columns]
+        # a transform that mixes the inputs produces all stored columns; otherwise only the selected ones are read
+        self.register_buffer("stored_cols", torch.arange(C) if mixes else stored_cols)
+        self.shape = (rows.numel(), columns.numel())
+        self.width = C
+
+    def select(self, rows=None, columns=None) -> "CodedMatrix":
+        return CodedMatrix({k: getattr(self, k) for k in self.names}, rows, columns)
+
+    def transform(self, x: torch.Tensor) -> torch.Tensor:
+        if hasattr(self, "rotation"):
+            basis = self.rotation.index_select(1, self.input_ids).float() * self.rotation_scale[:, None].float()
+            return torch.nn.functional.linear(x, basis.to(x.dtype))
+        if hasattr(self, "signs"):
+            full = x.new_zeros((*x.shape[:-1], self.width)).index_copy(-1, self.input_ids, x)
+            mixed = hadamard_transform(full * self.signs.to(x.dtype)) / self.width ** 0.5
+            return mixed.index_select(-1, self.col_order.long()) if hasattr(self, "col_order") else mixed
+        return x
+
+    def weight(self, dtype=torch.float32) -> torch.Tensor:
+        return fragment(self.codes, self.tiles, self.bands, self.row_scale, self.col_scale, self.stored_rows,
+                        self.stored_cols, dtype)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return torch.nn.functional.linear(self.transform(x), self.weight(x.dtype))
+
+
+class CodedFFN(torch.nn.Module):
+    """GeGLU FFN over three coded matrices, restricted to ``count`` hidden units from ``first`` (a tensor-parallel
+    share); gate and up share one input transform when they were coded under the same one
+    (rdma/mesh_code.py:68-82)."""
+
+    def __init__(self, gate: CodedMatrix, up: CodedMatrix, down: CodedMatrix, first: int = 0, count: int | None = None):
+        super().__init__()
+        hidden = torch.arange(first, first + (count if count is not None else gate.shape[0] - first))
+        self.gate, self.up, self.down = gate.select(rows=hidden), up.select(rows=hidden), down.select(columns=hidden)
+        names = ("col_order", "rotation", "rotation_scale", "signs")
+        self.shared = all(hasattr(gate, n) == hasattr(up, n) and (not hasattr(gate, n) or torch.equal(getattr(gate, n), getattr(up, n)))
+                          for n in names)
+
+    def forward(self, x):
+        t = self.gate.transform(x)
+        g = torch.nn.functional.linear(t, self.gate.weight(x.dtype))
+        u = torch.nn.functional.linear(t if self.shared else self.up.transform(x), self.up.weight(x.dtype))
+        return self.down(torch.nn.functional.gelu(g, approximate="tanh") * u)
+
+
+def save_matrices(path, matrices: dict, metadata: dict | None = None) -> None:
+    """``{name: fields}`` -> one safetensors file with tensors ``name.field``."""
+    from safetensors.torch import save_file
+    flat = {f"{n}.{k}": v.contiguous() for n, fields in matrices.items() for k, v in fields.items()}
+    save_file(flat, str(path), metadata=metadata or {})
+
+
+def load_matrices(path) -> dict:
+    """The coded matrices of a safetensors file written by :func:`save_matrices` (or by the reference's tooling:
+    tensors ``name.codes``, ``name.tiles``, ...; rdma/mesh_code.py:85-101)."""
+    from safetensors.torch import load_file
+    tensors = load_file(str(path), device="cpu")
+    out = {}
+    for name in sorted(k[:-6] for k in tensors if k.endswith(".codes")):
+        fields = {k[len(name) + 1:]: v for k, v in tensors.items() if k.startswith(name + ".")}
+        out[name] = CodedMatrix(fields)
+    return out

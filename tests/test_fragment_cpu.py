@@ -68,3 +68,39 @@ def test_fragment_exports():
     assert any("fragment" in str(n.target) for n in ep.graph.nodes)
     x = torch.randn(3, 32)
     assert torch.allclose(ep.module()(x), M()(x))
+
+
+def test_coded_matrix_transforms_selection_and_file_round_trip(tmp_path):
+    from mesh_b200.ops.fragment import CodedFFN, CodedMatrix, hadamard_transform, load_matrices, save_matrices
+    torch.manual_seed(3)
+    R, C = 64, 64
+    w = torch.randn(R, C) / 8
+    x = torch.randn(5, C)
+    # plain
+    plain = CodedMatrix(encode_fragment(w, 8))
+    assert (plain(x) - x @ w.T).abs().max() < 0.05
+    # sign flip + Hadamard: code W H^-1 so that (H s x) W'^T = x W^T
+    signs = torch.where(torch.rand(C) < 0.5, -1.0, 1.0)
+    Hm = hadamard_transform(torch.eye(C)) / C ** 0.5                 # orthonormal, symmetric
+    w_rot = (w * signs[None, :]) @ Hm.T                              # W diag(s) H^T
+    f = encode_fragment(w_rot, 8)
+    f["signs"] = signs
+    mixed = CodedMatrix(f)
+    assert (mixed(x) - x @ w.T).abs().max() < 0.05
+    # a dense rotation
+    q, _ = torch.linalg.qr(torch.randn(C, C))
+    f = encode_fragment(w @ q.T, 8)
+    f["rotation"], f["rotation_scale"] = q, torch.ones(C)
+    rot = CodedMatrix(f)
+    assert (rot(x) - x @ w.T).abs().max() < 0.05
+    # row / column selection = the same slice of the dense product
+    sub = plain.select(rows=torch.arange(32, 64), columns=torch.arange(0, 32))
+    assert (sub(x[:, :32]) - x[:, :32] @ w[32:, :32].T).abs().max() < 0.05
+    # FFN share and file round trip
+    wg, wu, wd = torch.randn(64, 64) / 8, torch.randn(64, 64) / 8, torch.randn(64, 64) / 8
+    mats = {"gate": encode_fragment(wg, 8), "up": encode_fragment(wu, 8), "down": encode_fragment(wd, 8)}
+    save_matrices(tmp_path / "ffn.safetensors", mats)
+    loaded = load_matrices(tmp_path / "ffn.safetensors")
+    ffn = CodedFFN(loaded["gate"], loaded["up"], loaded["down"], first=32, count=32)
+    ref = (torch.nn.functional.gelu(x @ wg[32:].T, approximate="tanh") * (x @ wu[32:].T)) @ wd[:, 32:].T
+    assert ffn.shared and (ffn(x) - ref).abs().max() < 0.1
