@@ -23,7 +23,7 @@ import threading
 import time
 
 TOKENS, D_MODEL, D_FF = 4096, 4096, 14336
-REFERENCE_UNAVAILABLE = ("reference is not installable: /root/reference has no setup.py/pyproject.toml (pip: 'Neither "
+REFERENCE_UNAVAILABLE = ("reference is not installable: its source tree has no setup.py/pyproject.toml (pip: 'Neither "
                          "setup.py nor pyproject.toml found'), and its code needs macOS Metal/CoreML, Apple RDMA verbs "
                          "and external metal-microbench libraries")
 

@@ -1,7 +1,7 @@
 """Sharded checkpoint: one safetensors file per rank plus a JSON index, re-shardable on load.
 
-The reference archives compiled programs, not model state, and every rank builds the whole module (SURVEY
-of compiler/mesh_compiler/archive.py:24-83, placement.py:173-180).  This format adds true sharded state:
+The reference archives compiled programs, not model state, and every rank builds the whole module
+(compiler/mesh_compiler/archive.py:24-83, placement.py:173-180).  This format adds true sharded state:
 ``index.json`` records for every tensor the compiler's triple ``(dimension, counts, world)`` — the same
 ``counts`` / displacement semantics as ``placement.counts`` (compiler/mesh_compiler/placement.py:65-108) — so
 a checkpoint written at one world size loads at another, each rank reading only the slices it needs.
