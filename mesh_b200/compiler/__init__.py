@@ -3,3 +3,6 @@ from .driver import compile_module, compile_program, compiled  # noqa: F401
 from .ir import TrainingResult, send, recv  # noqa: F401
 from .placement import counts  # noqa: F401
 from .runtime import Program  # noqa: F401
+from .lower import lower  # noqa: F401,E402
+from .fuse import fuse_plan  # noqa: F401,E402
+from . import syncmon, check  # noqa: F401,E402
