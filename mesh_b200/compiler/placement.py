@@ -414,6 +414,10 @@ class Propagator:
         handled = not list_args and isinstance(val, torch.Tensor)
         if tgt is aten.convolution.default and self.halo_convolution(node, tnames):
             return
+        if tgt is aten._assert_tensor_metadata.default:
+            return                                       # a trace-time check of dtype/shape: nothing to run, no reason to gather
+        if tgt is aten.index_put.default and self.accumulating_index_put(node):
+            return
         if tgt in CREATION or (not tnames and not list_args):
             self.spec[node.name] = self.all_r()
             self.steps.append(Step("call", node.name, tgt, self.ref_args(node.args), self.ref_kwargs(node.kwargs)))
@@ -525,6 +529,16 @@ class Propagator:
             if shard is not None and shard.dim != dim:
                 return [Spec("S", shard.dim, shard.counts, shard.striped) for _ in specs], shard
             return [R for _ in specs], R
+        if tgt in (aten.gather.default, aten.scatter_add.default, aten.scatter.src):
+            # every tensor operand cut along the same dimension, which is not the indexed one: rows are independent
+            nd = len(self.shape[tnames[0]])
+            dim = node.args[1] % max(nd, 1)
+            shard = next((s for s in specs if s.kind == "S"), None)
+            same_rank = all(len(self.shape[n]) == nd for n in tnames)
+            if shard is not None and shard.dim != dim and same_rank and all(
+                    self.shape[n][shard.dim] == self.shape[tnames[0]][shard.dim] for n in tnames):
+                return [Spec("S", shard.dim, shard.counts, shard.striped) for _ in specs], Spec("S", shard.dim, shard.counts, shard.striped)
+            return [R for _ in specs], R
         if tgt is aten.embedding.default:
             w, idx = specs
             if idx.kind == "S" and w.kind == "R":
@@ -591,6 +605,49 @@ class Propagator:
                 return [s], s
             return [R], R
         return [s], s
+
+    def accumulating_index_put(self, node) -> bool:
+        """``zeros.index_put(indices, values, accumulate=True)`` with the indices and values cut along the same leading
+        dimension (the backward of an embedding or of a gather over sharded tokens): every processor accumulates its
+        own rows into a zero buffer; the results are partial sums."""
+        base, indices, values = node.args[0], node.args[1], node.args[2]
+        accumulate = node.args[3] if len(node.args) > 3 else node.kwargs.get("accumulate", False)
+        if not accumulate or not _is_tensor_node(base) or not _is_tensor_node(values):
+            return False
+        zero_makers = (aten.zeros.default, aten.new_zeros.default, aten.zeros_like.default, aten.full.default, aten.full_like.default)
+        if base.op != "call_function" or base.target not in zero_makers:
+            return False
+        if base.target in (aten.full.default, aten.full_like.default) and base.args[1] != 0:
+            return False
+        idx_nodes = [i for i in indices if i is not None]
+        if not idx_nodes or not all(_is_tensor_node(i) for i in idx_nodes):
+            return False
+        vname = self.renamed.get(values.name, values.name)
+        cut = [(a, sp) for a, sp in enumerate(self.spec[vname]) if sp.kind != "R"]
+        if len(cut) != 1 or cut[0][1].kind != "S":
+            return False
+        ax, sp = cut[0]
+        new_names = {}
+        for i in idx_nodes:          # the indices follow the values' cut: it must be a dimension the index tensors span
+            iname = self.renamed.get(i.name, i.name)
+            ish = self.shape[iname]
+            if sp.dim >= len(ish) or tuple(ish) != tuple(self.shape[vname][: len(ish)]):
+                return False
+        for i in idx_nodes:
+            iname = self.renamed.get(i.name, i.name)
+            want = tuple(Spec("S", sp.dim, sp.counts, sp.striped) if a == ax else R for a in range(self.na))
+            new_names[i.name] = self.reshard(iname, want)
+        bname = self.renamed.get(base.name, base.name)
+        new_names[base.name] = self.reshard(bname, self.all_r())
+        out_spec = tuple(P() if a == ax else R for a in range(self.na))
+        self.shape[node.name] = _shape(node)
+        v = node.meta.get("val")
+        if isinstance(v, torch.Tensor):
+            self.dtype[node.name] = v.dtype
+        self.spec[node.name] = out_spec
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
+                               self.ref_kwargs(node.kwargs, new_names), {"out_specs": out_spec, "full_shape": _shape(node)}))
+        return True
 
     def halo_convolution(self, node, tnames) -> bool:
         """A convolution whose input is cut along one spatial dimension: every processor fetches the rows of its
