@@ -11,7 +11,7 @@
 //                                                              a dense simplex here)
 //   * cycle mean of a weighted graph (throughput bound of a software-pipelined plan, :2370)
 //   * signature check: every member of a group issues the same ordered list of synchronising operations
-// Tree packing, concurrent flow and relay routing have no counterpart: every peer is one hop away.
+// Critical path, list scheduling, chain cover, minimum arborescence and concurrent flow live in routing.cpp.
 // Deterministic by construction (integer or IEEE arithmetic in a fixed order), so every rank
 // derives the same result from the same input.
 #include <algorithm>

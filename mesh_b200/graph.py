@@ -100,3 +100,70 @@ def signature_check(sequences: list[list[int]]) -> int:
     """-1 when every member issues the same ordered operations, else the first differing position."""
     flat = [x for s in sequences for x in s]
     return _native.lib().mesh_graph_signature_check(c_int(len(sequences)), _ia([len(s) for s in sequences]), _la(flat or [0]))
+
+
+# ------------------------------------------------------------------------------------------------ scheduling, routing
+def longest_path(n: int, edges: list[tuple[int, int]], cost: list[float]) -> list[float]:
+    """``tail[v]``: ``cost[v]`` plus the heaviest path after ``v``; ``max(tail)`` is the critical path."""
+    out = (c_double * max(n, 1))()
+    rc = _native.lib().mesh_graph_longest_path(c_int(n), c_int(len(edges)), _ia([e[0] for e in edges]), _ia([e[1] for e in edges]),
+                                               _da(cost), out)
+    if rc != 0:
+        raise ValueError("graph has a cycle")
+    return list(out)[:n]
+
+
+def list_schedule(n: int, edges: list[tuple[int, int]], cost: list[float], procs: int):
+    """Critical-path list scheduling on ``procs`` identical processors -> ``(start, processor, makespan)``."""
+    start, proc, span = (c_double * max(n, 1))(), (c_int * max(n, 1))(), c_double(0)
+    rc = _native.lib().mesh_graph_list_schedule(c_int(n), c_int(len(edges)), _ia([e[0] for e in edges]), _ia([e[1] for e in edges]),
+                                                _da(cost), c_int(procs), start, proc, ctypes.byref(span))
+    if rc != 0:
+        raise ValueError("graph has a cycle" if rc == -1 else "need at least one processor")
+    return list(start)[:n], list(proc)[:n], span.value
+
+
+def chains(n: int, edges: list[tuple[int, int]]) -> tuple[list[int], int]:
+    """Minimum chain cover of a DAG (Dilworth): ``(chain id per node, number of chains)``."""
+    out = (c_int * max(n, 1))()
+    k = _native.lib().mesh_graph_chains(c_int(n), c_int(len(edges)), _ia([e[0] for e in edges]), _ia([e[1] for e in edges]), out)
+    if k < 0:
+        raise ValueError("graph has a cycle")
+    return list(out)[:n], k
+
+
+def arborescence(n: int, edges: list[tuple[int, int, float]], root: int) -> tuple[list[int], float]:
+    """Cheapest broadcast tree from ``root`` (Chu-Liu / Edmonds): ``(index of the edge entering each node, weight)``."""
+    pe, total = (c_int * max(n, 1))(), c_double(0)
+    rc = _native.lib().mesh_graph_arborescence(c_int(n), c_int(len(edges)), _ia([e[0] for e in edges]), _ia([e[1] for e in edges]),
+                                               _da([e[2] for e in edges]), c_int(root), pe, ctypes.byref(total))
+    if rc != 0:
+        raise ValueError("some node cannot be reached from the root")
+    return list(pe)[:n], total.value
+
+
+def concurrent_flow(n: int, edges: list[tuple[int, int, float]], commodities: list[tuple[int, int, float]], eps: float = 0.05):
+    """Largest fraction of every demand that fits at once (Garg-Koenemann) -> ``(lambda, flow[commodity][edge])``."""
+    m, k = len(edges), len(commodities)
+    flow = (c_double * max(1, m * k))()
+    f = _native.lib().mesh_graph_concurrent_flow
+    f.restype = c_double
+    lam = f(c_int(n), c_int(m), _ia([e[0] for e in edges]), _ia([e[1] for e in edges]), _da([e[2] for e in edges]), c_int(k),
+            _ia([c[0] for c in commodities]), _ia([c[1] for c in commodities]), _da([c[2] for c in commodities]), c_double(eps), flow)
+    if lam < 0:
+        raise ValueError("a commodity has no path")
+    return lam, [list(flow[c * m:(c + 1) * m]) for c in range(k)]
+
+
+def dot(n: int, edges: list[tuple[int, int]], labels: list[str] | None = None, groups: list[int] | None = None) -> str:
+    """Graphviz text of a graph; ``groups[v]`` colours nodes by processor / chain."""
+    palette = ["#1f77b4", "#ff7f0e", "#2ca02c", "#d62728", "#9467bd", "#8c564b", "#e377c2", "#7f7f7f"]
+    lines = ["digraph mesh {", "  rankdir=LR;"]
+    for v in range(n):
+        attr = [f'label="{labels[v] if labels else v}"']
+        if groups is not None:
+            attr.append(f'style=filled fillcolor="{palette[groups[v] % len(palette)]}"')
+        lines.append(f"  n{v} [{' '.join(attr)}];")
+    lines += [f"  n{a} -> n{b};" for a, b in edges]
+    lines.append("}")
+    return "\n".join(lines) + "\n"

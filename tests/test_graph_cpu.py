@@ -103,3 +103,39 @@ def test_cycle_mean_and_signature():
     assert graph.signature_check([[1, 2, 3], [1, 2, 3]]) == -1
     assert graph.signature_check([[1, 2, 3], [1, 9, 3]]) == 1
     assert graph.signature_check([[1, 2], [1, 2, 3]]) == 2
+
+
+def test_longest_path_list_schedule_and_chains():
+    from mesh_b200 import graph as G
+    # diamond with a tail: 0 -> {1, 2} -> 3 -> 4
+    edges = [(0, 1), (0, 2), (1, 3), (2, 3), (3, 4)]
+    cost = [1.0, 5.0, 2.0, 1.0, 1.0]
+    tail = G.longest_path(5, edges, cost)
+    assert tail[0] == 8.0 and tail[2] == 4.0 and max(tail) == 8.0
+    start, proc, span = G.list_schedule(5, edges, cost, procs=2)
+    assert span == 8.0 and start[1] == 1.0 and start[2] == 1.0 and proc[1] != proc[2] and start[3] == 6.0
+    _, _, span1 = G.list_schedule(5, edges, cost, procs=1)
+    assert span1 == sum(cost)
+    ids, k = G.chains(5, edges)
+    assert k == 2 and ids[1] != ids[2]                     # the only antichain of size 2 is {1, 2}
+    # an antichain of 4 independent nodes needs 4 chains
+    assert G.chains(4, [])[1] == 4
+    txt = G.dot(5, edges, groups=ids)
+    assert txt.startswith("digraph") and "n0 -> n1" in txt
+
+
+def test_arborescence_and_concurrent_flow():
+    from mesh_b200 import graph as G
+    # classic Edmonds example with a cycle 1 -> 2 -> 3 -> 1 that must be broken
+    edges = [(0, 1, 10.0), (0, 2, 12.0), (0, 3, 9.0), (1, 2, 2.0), (2, 3, 3.0), (3, 1, 1.0)]
+    pe, total = G.arborescence(4, edges, 0)
+    assert pe[0] == -1 and abs(total - 12.0) < 1e-9          # 0->3 (9), 3->1 (1), 1->2 (2)
+    assert {edges[e][:2] for e in pe[1:]} == {(0, 3), (3, 1), (1, 2)}
+    # two commodities sharing one link of capacity 10: each wants 10 -> half of each fits
+    fedges = [(0, 2, 100.0), (1, 2, 100.0), (2, 3, 10.0), (3, 4, 100.0), (3, 5, 100.0)]
+    lam, flow = G.concurrent_flow(6, fedges, [(0, 4, 10.0), (1, 5, 10.0)], eps=0.05)
+    assert 0.42 < lam <= 0.5 + 1e-9
+    assert abs(flow[0][2] - lam * 10) < 1e-6 and flow[0][2] + flow[1][2] <= 10 + 1e-6
+    # a parallel path doubles it
+    lam2, _ = G.concurrent_flow(6, fedges + [(2, 3, 10.0)], [(0, 4, 10.0), (1, 5, 10.0)], eps=0.05)
+    assert lam2 > 0.85
