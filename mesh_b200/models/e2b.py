@@ -252,6 +252,8 @@ def bench_decode(ctx, steps: int = 256, prompt_len: int = 512, configs=(("bf16",
            "prompt": prompt_len, "decode_steps": steps, "tp": ctx.world, "runs": []}
     if ctx.world > 1:
         _ = ctx.comm                      # allocated before the mark below, so it outlives the per-run release
+    from ..runtime.monitor import ErrorMonitor
+    from ..utils.status import check_status, clear_abort
     for quant, B in configs:
         mark = ctx.heap.mark() if ctx.world > 1 else None
         try:
@@ -272,16 +274,38 @@ def bench_decode(ctx, steps: int = 256, prompt_len: int = 512, configs=(("bf16",
             # step counters must agree across ranks: they do (every rank ran the same two steps)
             dist.barrier()
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        m.decode(steps, record=False)
-        e1.record()
-        torch.cuda.synchronize()
+        # If a rank falls out of step, every later kernel of the replayed graph would sit out its full wait limit.
+        # A monitor (started after the capture: a second thread may not touch the device while a stream is being
+        # captured) spreads the abort flag after the first failure, so the rest of the run drains at once.
+        monitor = ErrorMonitor(ctx.device, interval_ms=10)
+        try:
+            import time as _time
+            t_dead = _time.perf_counter() + 1.0
+            while monitor.report()["polls"] < 1 and _time.perf_counter() < t_dead:
+                _time.sleep(0.002)                   # its set-up (pinned buffer, stream) is over before the timed region
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            m.decode(steps, record=False)
+            e1.record()
+            torch.cuda.synchronize()
+        finally:
+            monitor.stop()
         ms = e0.elapsed_time(e1)
         t = torch.tensor([ms], device=ctx.device, dtype=torch.float64)
         if ctx.world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
+        # a run in which any rank timed out or was cancelled is not reported as a number; every rank learns of it,
+        # so that all of them leave the loop together
+        from ..utils.status import decode, status_block
+        torch.cuda.synchronize()
+        bad = torch.tensor([int(decode(status_block(ctx.device))["code"] != "OK")], device=ctx.device)
+        if ctx.world > 1:
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad):
+            clear_abort(ctx.device)
+            check_status(ctx.device)
+            raise RuntimeError("decode: another rank reported a device-side failure")
         res["runs"].append({"weights": quant, "batch": B, "ms_per_token": round(ms / steps, 4),
                             "tokens_per_s": round(B * steps / (ms * 1e-3), 1)})
         del m
