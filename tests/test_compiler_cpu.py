@@ -205,3 +205,28 @@ def test_collective_matmul_pairs_are_fused_and_results_unchanged(monkeypatch):
     assert plain.fusion == {"ag_mm": 0, "mm_rs": 0}
     res2 = plain(x)
     assert abs(float(res2.outputs) - float(res.outputs)) < 1e-6
+
+
+def test_plan_cache_hits_and_key_sensitivity(tmp_path):
+    import time
+    from mesh_b200.compiler.cache import cache_key, compile_cached
+    torch.manual_seed(9)
+    m = Decoder(dim=32, heads=2, ffn=64, layers=1).eval()
+    x = torch.randn(2, 4, 32)
+    procs = _procs(2)
+    t0 = time.perf_counter()
+    sch, hit = compile_cached(m, (x,), procs, megatron(procs), tmp_path)
+    t_miss = time.perf_counter() - t0
+    assert not hit
+    t0 = time.perf_counter()
+    sch2, hit2 = compile_cached(m, (x,), procs, megatron(procs), tmp_path)
+    t_hit = time.perf_counter() - t0
+    assert hit2 and t_hit < t_miss
+    assert torch.allclose(Program(sch2)(x), m(x), atol=1e-5)
+    k0 = cache_key(m, (x,), procs, megatron(procs))
+    assert k0 == cache_key(m, (x,), procs, megatron(procs))
+    assert k0 != cache_key(m, (torch.randn(2, 8, 32),), procs, megatron(procs))             # other shapes
+    assert k0 != cache_key(m, (x,), _procs(4), megatron(_procs(4)))                           # other processors
+    assert k0 != cache_key(m, (x,), procs, megatron(procs, units=(3, 1)))                     # other shares
+    assert k0 != cache_key(m, (x,), procs, megatron(procs), loss=0)                           # other options
+    assert k0 != cache_key(Decoder(dim=32, heads=2, ffn=96, layers=1), (x,), procs, megatron(procs))
