@@ -19,6 +19,7 @@ import math
 import operator
 import os
 import threading
+import time
 from typing import Any
 
 import torch
@@ -114,6 +115,9 @@ class Executor:
         # with MESH_SYNC_TRACE=1 every collective that actually runs is logged, to be compared with the compiled
         # synchronisation signature (compiler/syncmon.py)
         self.trace = [] if os.environ.get("MESH_SYNC_TRACE", "0") == "1" else None
+        # with MESH_OBSERVE=1 every step is timed (device-synchronised on CUDA): what the share solver calls observed
+        # costs, and what a person reads to see where a processor's time goes (compiler/observe.py)
+        self.times = [] if os.environ.get("MESH_OBSERVE", "0") == "1" else None
 
     # ---- shards of full tensors
     def shard(self, full: torch.Tensor, specs: tuple) -> torch.Tensor | None:
@@ -295,7 +299,11 @@ class Executor:
                 return type(a)(val(x) for x in a)
             return a
 
-        for st in self.plan.steps:
+        for index, st in enumerate(self.plan.steps):
+            if self.times is not None:
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize(self.device)
+                t0 = time.perf_counter()
             if st.op == "const":
                 env[st.out] = consts(st.target)
             elif st.op == "alias":
@@ -310,6 +318,10 @@ class Executor:
                 env[st.out] = self.fused(st, env[st.args[0].name], env[st.args[1].name])
             else:
                 env[st.out] = self.call(st, val)
+            if self.times is not None:
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize(self.device)
+                self.times.append((index, time.perf_counter() - t0))
         out = []
         for o in self.plan.outputs:
             out.append(o[1] if isinstance(o, tuple) else env[o])

@@ -230,3 +230,22 @@ def test_plan_cache_hits_and_key_sensitivity(tmp_path):
     assert k0 != cache_key(m, (x,), procs, megatron(procs, units=(3, 1)))                     # other shares
     assert k0 != cache_key(m, (x,), procs, megatron(procs), loss=0)                           # other options
     assert k0 != cache_key(Decoder(dim=32, heads=2, ffn=96, layers=1), (x,), procs, megatron(procs))
+
+
+def test_observed_step_times():
+    from mesh_b200.compiler.observe import observe, stage_costs
+    torch.manual_seed(10)
+    m = Decoder(dim=64, heads=4, ffn=256, layers=2).eval()
+    x = torch.randn(2, 16, 64)
+    procs = _procs(2)
+    prog = Program(compile_module(m, (x,), procs, megatron(procs)))
+    rep = observe(prog, x, repeats=2)
+    assert len(rep["steps"]) == len(prog.plan.steps) and rep["total"] > 0
+    assert any(k.startswith("blocks.1") for k in rep["by_module"]) and rep["by_kind"].get("collective", 0) > 0
+    stages = stage_costs(rep, prog.plan)
+    n_coll = sum(1 for st in prog.plan.steps if st.op in ("collective", "fused"))
+    assert len(stages) in (n_coll, n_coll + 1)
+    assert abs(sum(s["compute_s"] + s["collective_s"] for s in stages) - rep["total"]) < 1e-9
+    # observation is off again afterwards
+    prog(x)
+    assert prog.per_rank[0][0].times is None
