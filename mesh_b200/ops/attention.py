@@ -243,3 +243,72 @@ def attention_ref(q, k, v, causal=True, window=0, scale=None, q_off=0, q_stride=
     p = torch.softmax(s, -1)
     p = torch.where(torch.isnan(p), torch.zeros_like(p), p)
     return torch.einsum("bhts,bshd->bthd", p, vf), lse
+
+
+# ------------------------------------------------------------------------------------------- head-exchange (Ulysses)
+def _a2a(x: torch.Tensor, axis) -> torch.Tensor:
+    """All-to-all over dim 0 of ``x [P, ...]``: block ``j`` goes to member ``j``; returns ``[P, ...]`` with block ``j``
+    received from member ``j``.  ``axis``: an axis context (own kernels on CUDA with a heap) or a torch group."""
+    import torch.distributed as dist
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    comm = getattr(axis, "comm", None) if (x.is_cuda and getattr(axis, "_heap", None) is not None) else None
+    if comm is not None:
+        comm.all_to_all(out.view(x.shape[0], -1), x.view(x.shape[0], -1))
+    else:
+        dist.all_to_all_single(out, x, group=getattr(axis, "group", axis))
+    return out
+
+
+class _SeqToHeads(torch.autograd.Function):
+    """``[B, T/P, H, hd]`` (sequence cut) -> ``[B, T, H/P, hd]`` (heads cut); the backward is the inverse exchange."""
+
+    @staticmethod
+    def forward(ctx, x, axis, P):
+        ctx.axis, ctx.P = axis, P
+        B, Tl, H, hd = x.shape
+        send = x.view(B, Tl, P, H // P, hd).permute(2, 0, 1, 3, 4)            # [P(dst), B, Tl, H/P, hd]
+        got = _a2a(send, axis)                                                  # [P(src = sequence block), B, Tl, H/P, hd]
+        return got.permute(1, 0, 2, 3, 4).reshape(B, P * Tl, H // P, hd)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _HeadsToSeq.apply(g, ctx.axis, ctx.P), None, None
+
+
+class _HeadsToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, axis, P):
+        ctx.axis, ctx.P = axis, P
+        B, T, Hl, hd = x.shape
+        send = x.view(B, P, T // P, Hl, hd).permute(1, 0, 2, 3, 4)             # [P(dst = owner of the block), B, Tl, Hl, hd]
+        got = _a2a(send, axis)                                                  # [P(src = head group), B, Tl, Hl, hd]
+        return got.permute(1, 2, 0, 3, 4).reshape(B, T // P, P * Hl, hd)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _SeqToHeads.apply(g, ctx.axis, ctx.P), None, None
+
+
+def ulysses_attention(q, k, v, axis, *, causal=True, window=0, scale=None, local_attention=None):
+    """Context-parallel attention by exchanging heads for sequence: every member holds a contiguous ``T / P`` slice
+    of the tokens for all heads; one all-to-all gives it all tokens of ``H / P`` heads, attention runs locally on whole
+    sequences, and a second all-to-all restores the sequence cut.  Needs ``H`` (and the KV heads) divisible by ``P``;
+    costs two all-to-alls of the activations instead of ``P - 1`` KV rotations, which wins when there are enough heads.
+    The reference reaches this form through its generic all-to-all reshard (compiler/mesh_compiler/placement.py:270).
+    Differentiable.  ``local_attention(q, k, v)`` defaults to the flash kernels on CUDA bf16 and to the fp32
+    statement elsewhere."""
+    P = axis.world
+    if P == 1:
+        qh, kh, vh = q, k, v
+    else:
+        if q.shape[2] % P or k.shape[2] % P:
+            raise ValueError("head-exchange attention needs the query and KV heads divisible by the group size")
+        qh, kh, vh = (_SeqToHeads.apply(t, axis, P) for t in (q, k, v))
+    if local_attention is None:
+        if qh.is_cuda and qh.dtype == torch.bfloat16:
+            local_attention = lambda a, b, c: attention(a, b, c, causal=causal, window=window, scale=scale)
+        else:
+            local_attention = lambda a, b, c: attention_ref(a, b, c, causal, window, scale)[0].to(a.dtype)
+    oh = local_attention(qh, kh, vh)
+    return oh if P == 1 else _HeadsToSeq.apply(oh, axis, P)

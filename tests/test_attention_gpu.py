@@ -135,3 +135,42 @@ def test_ring_attention_backward_two_ranks(striped):
         pytest.skip("needs 2 GPUs")
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_ring_bwd_rank, 2, striped, use_cuda=True, timeout=300.0)
+
+
+def _ulysses_rank(rank, world, rdv):
+    from mesh_b200.config import MeshConfig, set_config
+    from mesh_b200.distributed.context import MeshContext
+    from mesh_b200.ops.attention import ulysses_attention
+    from mesh_b200.parallel.topology import AxisContext
+    from mesh_b200.utils.status import check_status
+    torch.cuda.set_device(rank)
+    set_config(MeshConfig.from_env(heap_bytes=512 << 20))
+    ctx = MeshContext(rank, world, torch.device("cuda", rank), rdv, None)
+    axis = AxisContext("cp", rank, list(range(world)), ctx.device, None, ctx.heap)
+    B, T, H, Hkv, hd = 1, 256 * world, 4, 2, 128
+    g = torch.Generator(device="cpu").manual_seed(0)
+    q = torch.randn(B, T, H, hd, generator=g).bfloat16().cuda()
+    k, v = (torch.randn(B, T, Hkv, hd, generator=g).bfloat16().cuda() for _ in range(2))
+    dout = torch.randn(B, T, H, hd, generator=g).bfloat16().cuda()
+    sl = slice(rank * (T // world), (rank + 1) * (T // world))
+    ql, kl, vl = (t[:, sl].contiguous().requires_grad_(True) for t in (q, k, v))
+    o = ulysses_attention(ql, kl, vl, axis, causal=True)
+    o.backward(dout[:, sl].contiguous())
+    torch.cuda.synchronize()
+    check_status()
+    dq, dk, dv = _ref_grads(q, k, v, dout, True, 0)
+    from mesh_b200.ops.attention import attention_ref
+    ref, _ = attention_ref(q, k, v, True)
+    _close(o, ref[:, sl])
+    _close(ql.grad, dq[:, sl], 3e-2)
+    _close(kl.grad, dk[:, sl], 3e-2)
+    _close(vl.grad, dv[:, sl], 3e-2)
+    rdv.barrier("ulysses-done")
+    ctx.heap.close()
+
+
+def test_head_exchange_attention_two_ranks():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_ulysses_rank, 2, use_cuda=True, timeout=300.0)

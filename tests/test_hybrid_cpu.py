@@ -113,3 +113,29 @@ def _hybrid_rank(rank, world, rdv, dims_text, striped):
                                           ("tp2cp2pp2", True)])
 def test_hybrid_step_matches_single_process(dims, striped):
     spawn_ranks(_hybrid_rank, ParallelDims.parse(dims).world, dims, striped, init_pg="gloo")
+
+
+def _ulysses_rank(rank, world, rdv):
+    from mesh_b200.ops.attention import attention_ref, ulysses_attention
+    from mesh_b200.parallel.topology import AxisContext
+    axis = AxisContext("cp", rank, list(range(world)), torch.device("cpu"), dist.group.WORLD)
+    g = torch.Generator().manual_seed(4)
+    B, T, H, Hkv, hd = 2, 8 * world, 2 * world, world, 8
+    q = torch.randn(B, T, H, hd, generator=g)
+    k, v = torch.randn(B, T, Hkv, hd, generator=g), torch.randn(B, T, Hkv, hd, generator=g)
+    dout = torch.randn(B, T, H, hd, generator=g)
+    sl = slice(rank * (T // world), (rank + 1) * (T // world))
+    ql, kl, vl = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+    o = ulysses_attention(ql, kl, vl, axis, causal=True)
+    o.backward(dout[:, sl])
+    qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ref, _ = attention_ref(qf, kf, vf, True)
+    ref.backward(dout)
+    assert torch.allclose(o, ref[:, sl], atol=1e-5)
+    for got, want in ((ql.grad, qf.grad), (kl.grad, kf.grad), (vl.grad, vf.grad)):
+        assert torch.allclose(got, want[:, sl], atol=1e-5)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_head_exchange_attention_matches_full_attention(world):
+    spawn_ranks(_ulysses_rank, world, init_pg="gloo")
