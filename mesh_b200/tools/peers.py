@@ -21,7 +21,7 @@ def discover(n_gpus: int | None = None, can_access=None, capacity: dict | None =
         from ..config import capacity as cap_fn
         capacity = cap_fn()
     matrix = [[a == b or bool(can_access(a, b)) for b in range(n_gpus)] for a in range(n_gpus)]
-    return {"gpus": n_gpus, "peer_access": matrix, "p2p_gbs_per_direction": capacity.get("nvlink_p2p_gbs", 770.0),
+    return {"gpus": n_gpus, "peer_access": matrix, "p2p_gbs_per_direction": capacity.get("nvlink_p2p_gbs", capacity.get("nvlink_gbs_per_dir", 770.0)),
             "all_connected": all(all(r) for r in matrix)}
 
 

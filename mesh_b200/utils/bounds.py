@@ -137,7 +137,7 @@ def b200_node(n_gpus: int = 8, cap: dict | None = None) -> tuple[Topology, dict[
     if cap is None:
         from ..config import capacity
         cap = capacity()
-    p2p = cap.get("nvlink_p2p_gbs", 770.0) * 1e9 * 8
+    p2p = cap.get("nvlink_p2p_gbs", cap.get("nvlink_gbs_per_dir", 770.0)) * 1e9 * 8
     lat = cap.get("nvlink_latency_us", 2.0) * 1e-6
     topo = Topology(set(range(n_gpus)))
     for a in range(n_gpus):
