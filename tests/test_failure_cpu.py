@@ -77,7 +77,11 @@ def test_supervisor_restarts_once_and_resumes(tmp_path):
         start = json.load(open(ck))["step"] if os.path.exists(ck) else 0
         for step in range(start, 6):
             if rank == 1 and restart == 0 and step == 3:
-                sys.exit(7)                       # the injected failure: a rank exits on the host
+                # the injected failure: a rank exits on the host, once the checkpoint of step 3 is on disk
+                t_end = time.time() + 10
+                while time.time() < t_end and not (os.path.exists(ck) and json.load(open(ck))["step"] >= 3):
+                    time.sleep(0.01)
+                sys.exit(7)
             time.sleep(0.05)
             if rank == 0:
                 json.dump({{"step": step + 1}}, open(ck + ".tmp", "w")); os.replace(ck + ".tmp", ck)
