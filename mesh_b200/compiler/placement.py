@@ -418,6 +418,8 @@ class Propagator:
             return                                       # a trace-time check of dtype/shape: nothing to run, no reason to gather
         if tgt is aten.index_put.default and self.accumulating_index_put(node):
             return
+        if tgt in (aten.cat.default, aten.stack.default) and self.joined(node):
+            return
         if tgt in CREATION or (not tnames and not list_args):
             self.spec[node.name] = self.all_r()
             self.steps.append(Step("call", node.name, tgt, self.ref_args(node.args), self.ref_kwargs(node.kwargs)))
@@ -605,6 +607,49 @@ class Propagator:
                 return [s], s
             return [R], R
         return [s], s
+
+    def joined(self, node) -> bool:
+        """``cat`` / ``stack`` of tensors that all carry the same cut along a dimension other than the joined one:
+        every processor joins its own pieces and the result keeps the cut (for ``stack``, dimensions at or after the
+        new one move up by one)."""
+        parts = list(node.args[0])
+        if not parts or not all(_is_tensor_node(p) for p in parts):
+            return False
+        names = [self.renamed.get(p.name, p.name) for p in parts]
+        nd = len(self.shape[names[0]])
+        dim = (node.args[1] if len(node.args) > 1 else node.kwargs.get("dim", 0))
+        stack = node.target is aten.stack.default
+        dim = dim % (nd + 1 if stack else max(nd, 1))
+        first = self.spec[names[0]]
+        out_spec = []
+        for a, sp in enumerate(first):
+            if sp.kind == "R":
+                if any(self.spec[n][a].kind != "R" for n in names):
+                    return False
+                out_spec.append(R)
+                continue
+            if sp.kind != "S" or (not stack and sp.dim == dim):
+                return False
+            for n in names:
+                o = self.spec[n][a]
+                if o.kind != "S" or o.dim != sp.dim or o.counts != sp.counts or o.striped != sp.striped or len(self.shape[n]) != nd:
+                    return False
+            d = sp.dim + 1 if (stack and sp.dim >= dim) else sp.dim
+            out_spec.append(Spec("S", d, sp.counts, sp.striped))
+        if all(s.kind == "R" for s in out_spec):
+            return False                                   # nothing to keep: the generic path handles it
+        out_spec = tuple(out_spec)
+        self.shape[node.name] = _shape(node)
+        v = node.meta.get("val")
+        if isinstance(v, torch.Tensor):
+            self.dtype[node.name] = v.dtype
+        self.spec[node.name] = out_spec
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args), self.ref_kwargs(node.kwargs),
+                               {"out_specs": out_spec, "full_shape": _shape(node)}))
+        want = self.stated.get(node.name)
+        if want is not None and want != out_spec:
+            self.renamed[node.name] = self.reshard(node.name, want)
+        return True
 
     def accumulating_index_put(self, node) -> bool:
         """``zeros.index_put(indices, values, accumulate=True)`` with the indices and values cut along the same leading
