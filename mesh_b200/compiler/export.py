@@ -29,6 +29,12 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
         ep = torch.export.export(module, tuple(args), kwargs or {}, strict=strict)
+        if decompositions is None and loss is None:
+            # inference keeps attention as one operation (the placement has a rule for heads cut over processors and
+            # the executor can hand it to a fused kernel); the joint forward+backward export needs it decomposed
+            decompositions = torch.export.default_decompositions()
+            for op in (torch.ops.aten.scaled_dot_product_attention.default,):
+                decompositions.pop(op, None)
         ep = ep.run_decompositions(decompositions) if decompositions is not None else ep.run_decompositions()
         if loss is not None:
             from torch.export.experimental import _export_forward_backward

@@ -541,6 +541,20 @@ class Propagator:
                     self.shape[n][shard.dim] == self.shape[tnames[0]][shard.dim] for n in tnames):
                 return [Spec("S", shard.dim, shard.counts, shard.striped) for _ in specs], Spec("S", shard.dim, shard.counts, shard.striped)
             return [R for _ in specs], R
+        if tgt is aten.scaled_dot_product_attention.default:
+            # q, k, v [batch, heads, tokens, head_dim]: heads (or the batch) cut the same way on all three -> local
+            if len(tnames) != 3:
+                return None                                   # a mask tensor: leave it to the generic path
+            q = specs[0]
+            same_heads = self.shape[tnames[0]][1] == self.shape[tnames[1]][1] == self.shape[tnames[2]][1]
+            if q.kind == "S" and q.dim in (0, 1) and not q.striped and (q.dim == 0 or same_heads):
+                want = Spec("S", q.dim, q.counts)
+                return [want, want, want], want
+            kv = next((s for s in specs[1:] if s.kind == "S" and s.dim in (0, 1) and not s.striped), None)
+            if q.kind == "R" and kv is not None and (kv.dim == 0 or same_heads):
+                want = Spec("S", kv.dim, kv.counts)
+                return [want, want, want], want
+            return [R, R, R], R
         if tgt is aten.embedding.default:
             w, idx = specs
             if idx.kind == "S" and w.kind == "R":

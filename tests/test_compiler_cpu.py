@@ -249,3 +249,40 @@ def test_observed_step_times():
     # observation is off again afterwards
     prog(x)
     assert prog.per_rank[0][0].times is None
+
+
+def test_attention_stays_whole_when_heads_are_cut():
+    """Inference graphs keep attention as one operation; with the heads cut over processors it needs no transfer."""
+    class Attn(torch.nn.Module):
+        def __init__(self, dim, heads):
+            super().__init__()
+            self.heads = heads
+            self.wq, self.wk, self.wv, self.wo = (torch.nn.Linear(dim, dim, bias=False) for _ in range(4))
+
+        def forward(self, x):
+            B, T, D = x.shape
+            split = lambda t: t.view(B, T, self.heads, D // self.heads).transpose(1, 2)
+            o = torch.nn.functional.scaled_dot_product_attention(split(self.wq(x)), split(self.wk(x)), split(self.wv(x)),
+                                                                 is_causal=True)
+            return self.wo(o.transpose(1, 2).reshape(B, T, D))
+
+    torch.manual_seed(11)
+    m = Attn(32, 4).eval()
+    x = torch.randn(2, 8, 32)
+    procs = _procs(2)
+
+    names = tuple(procs)
+
+    def placement(node):
+        if node.op != "placeholder":
+            return None
+        if any(k in node.name for k in ("wq", "wk", "wv")):
+            return (0, names, None)                                   # rows = heads
+        if "wo" in node.name:
+            return (1, names, None)
+        return None
+    sch = compile_module(m, (x,), procs, placement)
+    targets = [str(st.target) for st in sch.plan.steps if st.op == "call"]
+    assert any("scaled_dot_product_attention" in t for t in targets)
+    assert [st.target for st in sch.plan.steps if st.op == "collective"] == ["all_reduce"]
+    assert torch.allclose(Program(sch)(x), m(x), atol=1e-5)

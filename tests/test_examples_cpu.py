@@ -18,7 +18,7 @@ def _load(name):
         sys.path.remove(EX)
 
 
-@pytest.mark.parametrize("name,kinds", [("parallel", {"reduce"}), ("pl", {"reduce", "broadcast"}), ("cp", {"broadcast"}),
+@pytest.mark.parametrize("name,kinds", [("parallel", {"reduce"}), ("pl", {"reduce"}), ("cp", {"broadcast"}),
                                         ("ep", {"alltoall"}), ("engines", {"permute"}), ("crossing", {"reduce"})])
 def test_compiled_examples(name, kinds):
     rep = _load(name).main(["--small", "--nodes", "2"])
