@@ -127,6 +127,54 @@ SOFTMAX_LIKE = {aten._softmax.default: 1, aten._log_softmax.default: 1, aten._so
                 aten.topk.default: 2, aten.sort.default: 1, aten.logsumexp.default: 1}
 
 
+def _trailing(core: int, outs: int, operands=None):
+    """Operators over the last ``core`` dimensions of every (listed) tensor operand; the leading ones are a batch."""
+    def describe(node, shapes):
+        nd = len(shapes[0])
+        flags = [True] * len(shapes) if operands is None else [i in operands for i in range(len(shapes))]
+        if any(f and len(sh) != nd for f, sh in zip(flags, shapes)):
+            return None                                     # a broadcast batch or a vector right-hand side
+        return {"batched": flags, "protect": set(range(nd - core, nd)), "outs": ["S"] * outs}
+    return describe
+
+
+def _along(position: int, outs: int, default=-1):
+    """Operators that work along one dimension (argument ``position``) of their first operand."""
+    def describe(node, shapes):
+        nd = len(shapes[0])
+        dim = node.args[position] if len(node.args) > position else node.kwargs.get("dim", default)
+        return {"batched": [True] + [False] * (len(shapes) - 1), "protect": {dim % max(nd, 1)}, "outs": ["S"] * outs}
+    return describe
+
+
+def _layer_norm(node, shapes):
+    core = len(node.args[1])
+    nd = len(shapes[0])
+    return {"batched": [True] + [False] * (len(shapes) - 1), "protect": set(range(nd - core, nd)), "outs": ["S", "S", "S"]}
+
+
+def _layer_norm_backward(node, shapes):
+    # (grad_out, input, normalized_shape, mean, rstd, weight, bias, mask) -> (dx, dweight, dbias): rows are
+    # independent for dx; the weight and bias gradients are sums over the rows
+    core = len(node.args[2])
+    nd = len(shapes[0])
+    return {"batched": [True, True, True, True] + [False] * (len(shapes) - 4), "protect": set(range(nd - core, nd)),
+            "outs": ["S", "P", "P"]}
+
+
+# operators whose leading (or all but one) dimensions are independent problems: a cut there stays where it is
+BATCHED = {
+    aten.linalg_cholesky_ex.default: _trailing(2, 2), aten.linalg_qr.default: _trailing(2, 2),
+    aten._linalg_solve_ex.default: _trailing(2, 4), aten.linalg_solve_triangular.default: _trailing(2, 1),
+    aten.cholesky_solve.default: _trailing(2, 1), aten.triu.default: _trailing(2, 1), aten.tril.default: _trailing(2, 1),
+    aten._linalg_det.default: _trailing(2, 3), aten._linalg_slogdet.default: _trailing(2, 4),
+    aten.linalg_inv_ex.default: _trailing(2, 2), aten.linalg_lu_factor_ex.default: _trailing(2, 3),
+    aten.sort.default: _along(1, 2), aten.sort.stable: _along(2, 2), aten.topk.default: _along(2, 2),
+    aten.cummax.default: _along(1, 2), aten.cummin.default: _along(1, 2),
+    aten.native_layer_norm.default: _layer_norm, aten.native_layer_norm_backward.default: _layer_norm_backward,
+}
+
+
 def _shape(node) -> tuple:
     v = node.meta.get("val")
     return tuple(v.shape) if isinstance(v, torch.Tensor) else ()
@@ -420,6 +468,8 @@ class Propagator:
             return
         if tgt in (aten.cat.default, aten.stack.default) and self.joined(node):
             return
+        if tgt in BATCHED and self.batched(node, tnames):
+            return
         if tgt in CREATION or (not tnames and not list_args):
             self.spec[node.name] = self.all_r()
             self.steps.append(Step("call", node.name, tgt, self.ref_args(node.args), self.ref_kwargs(node.kwargs)))
@@ -492,6 +542,22 @@ class Propagator:
             if s.kind == "S":
                 perm = [p % len(node.args[1]) for p in node.args[1]]
                 return [s], Spec("S", perm.index(s.dim), s.counts, s.striped)
+            return [s], s
+        if tgt is aten.flip.default:
+            s = specs[0]
+            nd = len(self.shape[tnames[0]])
+            if s.kind == "S" and s.dim in {d % nd for d in node.args[1]}:
+                return [R], R                                            # reversing along the cut moves rows between processors
+            return [s], s
+        if tgt is aten.diagonal.default:
+            s = specs[0]
+            nd = len(self.shape[tnames[0]])
+            d1 = (node.args[2] if len(node.args) > 2 else node.kwargs.get("dim1", 0)) % nd
+            d2 = (node.args[3] if len(node.args) > 3 else node.kwargs.get("dim2", 1)) % nd
+            if s.kind == "S":
+                if s.dim in (d1, d2):
+                    return [R], R
+                return [s], Spec("S", s.dim - sum(1 for d in (d1, d2) if d < s.dim), s.counts, s.striped)
             return [s], s
         if tgt in (aten.transpose.int, aten.t.default):
             s = specs[0]
@@ -623,9 +689,9 @@ class Propagator:
         return [s], s
 
     def joined(self, node) -> bool:
-        """``cat`` / ``stack`` of tensors that all carry the same cut along a dimension other than the joined one:
-        every processor joins its own pieces and the result keeps the cut (for ``stack``, dimensions at or after the
-        new one move up by one)."""
+        """``cat`` / ``stack`` of tensors that carry the same cut along a dimension other than the joined one (whole
+        copies among them give up all but their own rows): every processor joins its own pieces and the result keeps
+        the cut (for ``stack``, dimensions at or after the new one move up by one)."""
         parts = list(node.args[0])
         if not parts or not all(_is_tensor_node(p) for p in parts):
             return False
@@ -634,34 +700,105 @@ class Propagator:
         dim = (node.args[1] if len(node.args) > 1 else node.kwargs.get("dim", 0))
         stack = node.target is aten.stack.default
         dim = dim % (nd + 1 if stack else max(nd, 1))
-        first = self.spec[names[0]]
-        out_spec = []
-        for a, sp in enumerate(first):
-            if sp.kind == "R":
-                if any(self.spec[n][a].kind != "R" for n in names):
-                    return False
-                out_spec.append(R)
-                continue
-            if sp.kind != "S" or (not stack and sp.dim == dim):
+        out_spec, wants = [], {n: [] for n in names}
+        for a in range(self.na):
+            here = [self.spec[n][a] for n in names]
+            if any(o.kind not in ("R", "S") for o in here):
                 return False
-            for n in names:
-                o = self.spec[n][a]
-                if o.kind != "S" or o.dim != sp.dim or o.counts != sp.counts or o.striped != sp.striped or len(self.shape[n]) != nd:
+            sp = next((o for o in here if o.kind == "S"), None)
+            if sp is None:
+                out_spec.append(R)
+                for n in names:
+                    wants[n].append(R)
+                continue
+            if not stack and sp.dim == dim:
+                return False
+            extent = self.shape[next(n for n, o in zip(names, here) if o.kind == "S")][sp.dim]
+            for n, o in zip(names, here):
+                if len(self.shape[n]) != nd or self.shape[n][sp.dim] != extent:
                     return False
+                if o.kind == "S" and (o.dim != sp.dim or o.counts != sp.counts or o.striped != sp.striped):
+                    return False
+                wants[n].append(Spec("S", sp.dim, sp.counts, sp.striped))      # a whole copy gives up all but its own rows
             d = sp.dim + 1 if (stack and sp.dim >= dim) else sp.dim
             out_spec.append(Spec("S", d, sp.counts, sp.striped))
         if all(s.kind == "R" for s in out_spec):
             return False                                   # nothing to keep: the generic path handles it
         out_spec = tuple(out_spec)
+        new_names = {}
+        for part, n in zip(parts, names):
+            new_names[part.name] = self.reshard(n, tuple(wants[n]))
         self.shape[node.name] = _shape(node)
         v = node.meta.get("val")
         if isinstance(v, torch.Tensor):
             self.dtype[node.name] = v.dtype
         self.spec[node.name] = out_spec
-        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args), self.ref_kwargs(node.kwargs),
-                               {"out_specs": out_spec, "full_shape": _shape(node)}))
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
+                               self.ref_kwargs(node.kwargs, new_names), {"out_specs": out_spec, "full_shape": _shape(node)}))
         want = self.stated.get(node.name)
         if want is not None and want != out_spec:
+            self.renamed[node.name] = self.reshard(node.name, want)
+        return True
+
+    def batched(self, node, tnames) -> bool:
+        """An operator of ``BATCHED`` whose operands are cut along a batch dimension (one it does not work along):
+        every processor runs it on its own problems; outputs keep the cut (or are partial sums where the operator sums
+        over the batch).  Handles operators with several outputs, which the per-axis rules do not."""
+        shapes = [self.shape[n] for n in tnames]
+        info = BATCHED[node.target](node, shapes)
+        if info is None:
+            return False
+        flags, protect, outs = info["batched"], info["protect"], info["outs"]
+        wants = {n: [] for n in tnames}
+        out_specs = [[] for _ in outs]
+        found = False
+        for ax in range(self.na):
+            specs = [self.spec[n][ax] for n in tnames]
+            if any(s.kind not in ("R", "S") for s in specs):
+                return False
+            cut = next((s for s, f in zip(specs, flags) if f and s.kind == "S"), None)
+            if cut is None:
+                if any(s.kind != "R" for s in specs):
+                    return False                            # an unbatched operand is cut: the generic path gathers it
+                for n in tnames:
+                    wants[n].append(R)
+                for o in out_specs:
+                    o.append(R)
+                continue
+            lead = shapes[flags.index(True)][: cut.dim + 1]
+            if cut.dim in protect or any(f and tuple(sh[: cut.dim + 1]) != tuple(lead) for f, sh in zip(flags, shapes)):
+                return False
+            found = True
+            same = Spec("S", cut.dim, cut.counts, cut.striped)
+            for n, f in zip(tnames, flags):
+                wants[n].append(same if f else R)
+            for o, kind in zip(out_specs, outs):
+                o.append(same if kind == "S" else P())
+        if not found:
+            return False
+        dims = [s.dim for s in out_specs[0] if s.kind == "S"]
+        if len(dims) != len(set(dims)):
+            return False
+        new_names = {}
+        orig = [a.name for a in node.args if _is_tensor_node(a)]
+        for o, n in zip(orig, tnames):
+            new_names[o] = self.reshard(n, tuple(wants[n]))
+        val = node.meta.get("val")
+        several = isinstance(val, (tuple, list))
+        if several:
+            for i, sp in enumerate(out_specs[: len(val)]):
+                self.spec[(node.name, i)] = tuple(sp)
+            self.spec[node.name] = self.all_r()
+        else:
+            self.spec[node.name] = tuple(out_specs[0])
+        meta = {"out_specs": tuple(out_specs[0]), "full_shape": _shape(node)}
+        stack = node.meta.get("nn_module_stack")
+        if stack:
+            meta["module"] = list(stack.values())[-1][0]
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
+                               self.ref_kwargs(node.kwargs, new_names), meta))
+        want = self.stated.get(node.name)
+        if not several and want is not None and want != self.spec[node.name]:
             self.renamed[node.name] = self.reshard(node.name, want)
         return True
 

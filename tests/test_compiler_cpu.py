@@ -286,3 +286,25 @@ def test_attention_stays_whole_when_heads_are_cut():
     assert any("scaled_dot_product_attention" in t for t in targets)
     assert [st.target for st in sch.plan.steps if st.op == "collective"] == ["all_reduce"]
     assert torch.allclose(Program(sch)(x), m(x), atol=1e-5)
+
+
+def test_batched_operators_with_several_outputs_keep_a_batch_cut():
+    """Layer norm (forward and backward) and sort over a batch cut: no gathers, weight gradients are partial sums."""
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln, self.fc = torch.nn.LayerNorm(16), torch.nn.Linear(16, 8)
+
+        def forward(self, x):
+            values, _ = torch.sort(self.fc(self.ln(x)), dim=-1)
+            return (values * values).mean()
+
+    torch.manual_seed(12)
+    m, x = Net(), torch.randn(4, 6, 16)
+    procs = _procs(2)
+    sch = compile_module(m, (x,), procs, data_parallel(procs), loss=0)
+    assert not [st for st in sch.plan.steps if st.meta.get("fallback")]
+    assert {st.target for st in sch.plan.steps if st.op == "collective"} == {"all_reduce"}
+    res = Program(sch)(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
