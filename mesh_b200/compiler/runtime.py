@@ -60,14 +60,17 @@ class ThreadWorld:
 
 
 class ThreadCollectives:
-    def __init__(self, world: ThreadWorld, mesh: Mesh, rank: int):
-        self.world, self.mesh, self.rank = world, mesh, rank
+    def __init__(self, world: ThreadWorld, mesh: Mesh, rank: int, device: torch.device | None = None):
+        self.world, self.mesh, self.rank, self.device = world, mesh, rank, device
         self.seq = 0
 
     def gather_all(self, t, axis):
         self.seq += 1
         g = self.mesh.axis_group(self.rank, axis)
-        return self.world.exchange(self.seq, g, self.rank, t), g
+        parts = self.world.exchange(self.seq, g, self.rank, t)
+        if self.device is not None:               # processors on different devices: what arrives is copied to this one
+            parts = [v.to(self.device) if isinstance(v, torch.Tensor) and v.device != self.device else v for v in parts]
+        return parts, g
 
 
 class DistCollectives:
@@ -286,11 +289,14 @@ class Executor:
             return parts[frm.owner] if to.owner == me else None
         raise NotImplementedError(verb)
 
+    def _here(self, t):
+        return t.to(self.device) if isinstance(t, torch.Tensor) and t.device != self.device else t
+
     # ---- one program execution
     def run(self, inputs: dict, consts) -> list:
         env: dict[str, Any] = {}
         for name, full in inputs.items():
-            env[name] = self.shard(full, self.plan.input_specs[name]) if isinstance(full, torch.Tensor) else full
+            env[name] = self._here(self.shard(full, self.plan.input_specs[name])) if isinstance(full, torch.Tensor) else full
 
         def val(a):
             if isinstance(a, Ref):
@@ -305,7 +311,7 @@ class Executor:
                     torch.cuda.synchronize(self.device)
                 t0 = time.perf_counter()
             if st.op == "const":
-                env[st.out] = consts(st.target)
+                env[st.out] = self._here(consts(st.target))
             elif st.op == "alias":
                 env[st.out] = env[st.args[0].name]
             elif st.op == "slice":
@@ -444,6 +450,7 @@ class Program(Arguments):
         super().__init__(scheduled)
         self.scheduled = scheduled
         self.fusion = {"ag_mm": 0, "mm_rs": 0}
+        self.devices = None
         if os.environ.get("MESH_FUSE", "1") != "0":
             from .fuse import fuse_plan
             self.plan, self.fusion = fuse_plan(self.plan)
@@ -456,6 +463,12 @@ class Program(Arguments):
                              dist.get_backend() != "gloo" else torch.device("cpu"))
             self.device = torch.device(dev)
             self.exec = Executor(self.plan, self.rank, DistCollectives(self.mesh, self.rank), self.device)
+        elif device == "processors":
+            # every processor on the device its description names (the reference's on_devices stage); values that
+            # cross are copied where they arrive
+            from .devices import on_devices
+            self.devices = on_devices(scheduled.processors)
+            self.device = self.devices[0 if entry is None else self.mesh.names.index(entry)]
         else:
             self.device = torch.device(device or "cpu")
         self.entry = entry
@@ -466,11 +479,12 @@ class Program(Arguments):
         obj = gm
         for part in str(target).split("."):
             obj = getattr(obj, part)
-        return obj.to(self.device) if isinstance(obj, torch.Tensor) else obj
+        return obj.to(self.device) if isinstance(obj, torch.Tensor) and not self.devices else obj
 
     def __call__(self, *args, **kwargs):
         bound = self.prepare(args, kwargs)
-        bound = {k: (v.to(self.device) if isinstance(v, torch.Tensor) and v.device != self.device else v) for k, v in bound.items()}
+        if not self.devices:
+            bound = {k: (v.to(self.device) if isinstance(v, torch.Tensor) and v.device != self.device else v) for k, v in bound.items()}
         if not self.threads:
             flat = self.exec.run(bound, self._consts)
             return self._result(flat, self.exec, bound)
@@ -480,7 +494,8 @@ class Program(Arguments):
 
         def work(r):
             try:
-                ex = Executor(self.plan, r, ThreadCollectives(world, self.mesh, r), self.device)
+                dev = self.devices[r] if self.devices else self.device
+                ex = Executor(self.plan, r, ThreadCollectives(world, self.mesh, r, dev if self.devices else None), dev)
                 results[r] = (ex, ex.run(bound, self._consts))
             except BaseException as e:  # surfaced to the caller below
                 errors.append(e)
