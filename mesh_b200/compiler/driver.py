@@ -40,6 +40,8 @@ def compile_program(program, args, functions, processors, placement, cost=unit_c
     exported, calls = _export.calls(program, args, functions, **export_options)
     sch = compile_captured(exported, processors, placement, cost, mesh)
     sch.structure["function_calls"] = calls
+    from .calls import analyse
+    sch.structure["call_analysis"] = analyse(exported, functions).summary()
     return sch
 
 
