@@ -162,6 +162,12 @@ def _layer_norm_backward(node, shapes):
             "outs": ["S", "P", "P"]}
 
 
+# random draws: the executor makes them with a counter-based generator keyed by (seed, execution, draw site, logical
+# element), so that a value is the same however it is cut and identical on every processor that holds a copy
+DRAWS = {aten.native_dropout.default: "dropout", aten.rand_like.default: "uniform", aten.randn_like.default: "normal",
+         aten.rand.default: "uniform", aten.randn.default: "normal"}
+
+
 # operators whose leading (or all but one) dimensions are independent problems: a cut there stays where it is
 BATCHED = {
     aten.linalg_cholesky_ex.default: _trailing(2, 2), aten.linalg_qr.default: _trailing(2, 2),
@@ -198,6 +204,7 @@ class Propagator:
         self.transfers: list[Transfer] = []
         self.tmp = 0
         self.channel = 0
+        self.sites = 0                             # random draws so far: each gets its own stream of the generator
         self.renamed: dict[str, str] = {}         # node name -> value that carries it after a stated reshard
 
     # ---- helpers
@@ -470,6 +477,8 @@ class Propagator:
             return
         if tgt in BATCHED and self.batched(node, tnames):
             return
+        if tgt in DRAWS:
+            return self.drawn(node, tnames)
         if tgt in CREATION or (not tnames and not list_args):
             self.spec[node.name] = self.all_r()
             self.steps.append(Step("call", node.name, tgt, self.ref_args(node.args), self.ref_kwargs(node.kwargs)))
@@ -801,6 +810,33 @@ class Propagator:
         if not several and want is not None and want != self.spec[node.name]:
             self.renamed[node.name] = self.reshard(node.name, want)
         return True
+
+    def drawn(self, node, tnames) -> None:
+        """A random draw (dropout mask, ``rand`` / ``randn`` and their ``_like`` forms).  It takes the next draw-site
+        number (the reference numbers draw sites the same way, compiler/mesh_compiler/export.py:412-507) and the
+        placement of its operand: each processor draws exactly the elements it holds."""
+        kind = DRAWS[node.target]
+        site, self.sites = self.sites, self.sites + 1
+        new_names = {}
+        if tnames:
+            src = tnames[0]
+            want = tuple(s if s.kind in ("R", "S") else R for s in self.spec[src])      # partial sums are summed first
+            new_names[node.args[0].name] = self.reshard(src, want)
+            out_spec = tuple(Spec(s.kind, s.dim, s.counts, s.striped) if s.kind == "S" else R for s in want)
+        else:
+            out_spec = self.all_r()
+        val = node.meta.get("val")
+        first = val[0] if isinstance(val, (tuple, list)) else val
+        full = tuple(first.shape)
+        if isinstance(val, (tuple, list)):
+            for i in range(len(val)):
+                self.spec[(node.name, i)] = out_spec
+        else:
+            self.dtype[node.name] = first.dtype
+        self.spec[node.name] = out_spec
+        self.shape[node.name] = _shape(node)
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names), self.ref_kwargs(node.kwargs, new_names),
+                               {"draw": kind, "site": site, "out_specs": out_spec, "full_shape": full, "dtype": first.dtype}))
 
     def accumulating_index_put(self, node) -> bool:
         """``zeros.index_put(indices, values, accumulate=True)`` with the indices and values cut along the same leading

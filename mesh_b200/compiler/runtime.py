@@ -121,6 +121,7 @@ class Executor:
         # with MESH_OBSERVE=1 every step is timed (device-synchronised on CUDA): what the share solver calls observed
         # costs, and what a person reads to see where a processor's time goes (compiler/observe.py)
         self.times = [] if os.environ.get("MESH_OBSERVE", "0") == "1" else None
+        self.seed, self.execution = int(os.environ.get("MESH_SEED", "0")), 0        # random draws: see draw()
 
     # ---- shards of full tensors
     def shard(self, full: torch.Tensor, specs: tuple) -> torch.Tensor | None:
@@ -382,6 +383,33 @@ class Executor:
             return self.collective(Step("collective", st.out, "reduce_scatter", (), {}, m), partial)
         raise NotImplementedError(st.target)
 
+    def draw(self, m: dict, args):
+        """Random numbers for the elements this processor holds, as a function of their positions in the whole tensor
+        (Philox4x32-10 keyed by seed, execution and draw site; ``mesh_b200/ops/philox.py``)."""
+        from ..ops import philox
+        full = m["full_shape"]
+        slices = [None] * len(full)
+        for ax, s in enumerate(m["out_specs"]):
+            if s.kind == "S":
+                slices[s.dim] = local_indices(s, self.coords[ax], full[s.dim])
+        e = philox.logical_index(full, slices, self.device)
+        words = philox.philox4x32((e & philox.MASK, (e >> 32) & philox.MASK, torch.full_like(e, m["site"] & philox.MASK),
+                                   torch.full_like(e, self.execution & philox.MASK)),
+                                  (self.seed & philox.MASK, (self.seed >> 32) & philox.MASK))
+        u = (words[0] >> 8).to(torch.float32) * (1.0 / (1 << 24))                      # [0, 1)
+        dtype = m.get("dtype", torch.float32)
+        if m["draw"] == "uniform":
+            return u.to(dtype)
+        if m["draw"] == "normal":                                                       # Box-Muller from two words
+            v = (words[1] >> 8).to(torch.float32) * (1.0 / (1 << 24))
+            return (torch.sqrt(-2.0 * torch.log1p(-u)) * torch.cos(2 * math.pi * v)).to(dtype)
+        x, p = args[0], float(args[1])
+        train = args[2] if len(args) > 2 else True
+        if train is False or p <= 0:
+            return x, torch.ones_like(x, dtype=torch.bool)
+        keep = u >= p
+        return torch.where(keep, x / (1 - p), torch.zeros((), dtype=x.dtype, device=x.device)), keep
+
     def call(self, st: Step, val):
         args = list(val(a) for a in st.args)
         kwargs = {k: val(v) for k, v in st.kwargs.items()}
@@ -391,6 +419,8 @@ class Executor:
             kwargs["device"] = self.device
         tgt = st.target
         m = st.meta
+        if "draw" in m:
+            return self.draw(m, args)
         loc = m.get("localize")
         if loc is not None and "out_specs" in m:
             i = loc[1]
@@ -451,6 +481,9 @@ class Program(Arguments):
         self.scheduled = scheduled
         self.fusion = {"ag_mm": 0, "mm_rs": 0}
         self.devices = None
+        # random draws are a function of (seed, execution, draw site, element): every processor must use the same seed;
+        # the execution number advances with every call, so that successive steps draw fresh numbers
+        self.seed, self.execution = int(os.environ.get("MESH_SEED", "0")), 0
         if os.environ.get("MESH_FUSE", "1") != "0":
             from .fuse import fuse_plan
             self.plan, self.fusion = fuse_plan(self.plan)
@@ -485,7 +518,9 @@ class Program(Arguments):
         bound = self.prepare(args, kwargs)
         if not self.devices:
             bound = {k: (v.to(self.device) if isinstance(v, torch.Tensor) and v.device != self.device else v) for k, v in bound.items()}
+        execution, self.execution = self.execution, self.execution + 1
         if not self.threads:
+            self.exec.seed, self.exec.execution = self.seed, execution
             flat = self.exec.run(bound, self._consts)
             return self._result(flat, self.exec, bound)
         world = ThreadWorld(self.mesh.size)
@@ -496,6 +531,7 @@ class Program(Arguments):
             try:
                 dev = self.devices[r] if self.devices else self.device
                 ex = Executor(self.plan, r, ThreadCollectives(world, self.mesh, r, dev if self.devices else None), dev)
+                ex.seed, ex.execution = self.seed, execution
                 results[r] = (ex, ex.run(bound, self._consts))
             except BaseException as e:  # surfaced to the caller below
                 errors.append(e)
