@@ -36,10 +36,81 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
             for op in (torch.ops.aten.scaled_dot_product_attention.default,):
                 decompositions.pop(op, None)
         ep = ep.run_decompositions(decompositions) if decompositions is not None else ep.run_decompositions()
+        expand_loops(ep.graph_module)
         if loss is not None:
             from torch.export.experimental import _export_forward_backward
             ep = _export_forward_backward(ep, joint_loss_index=loss)
     return read(ep, training=loss is not None)
+
+
+def _inline(graph, body: torch.fx.GraphModule, operands: list, before: torch.fx.Node) -> list:
+    """Copy ``body``'s nodes in front of ``before`` with its placeholders bound to ``operands``; returns its outputs."""
+    holders = [n for n in body.graph.nodes if n.op == "placeholder"]
+    if len(holders) != len(operands):
+        raise ValueError(f"loop body takes {len(holders)} values, {len(operands)} given")
+    env = dict(zip(holders, operands))
+    with graph.inserting_before(before):
+        out = graph.graph_copy(body.graph, env)
+    return list(out) if isinstance(out, (tuple, list)) else [out]
+
+
+def _made(graph, before, target, args, val):
+    with graph.inserting_before(before):
+        node = graph.call_function(target, args)
+    node.meta["val"] = val
+    return node
+
+
+def expand_loops(gm: torch.fx.GraphModule) -> int:
+    """Unroll the ``map`` and ``scan`` higher-order operators of a captured graph (the reference expands them the same
+    way at capture, compiler/mesh_compiler/export.py:112-130): iteration ``i`` of the body is copied into the graph
+    with ``x[i]`` as its element, the per-iteration results are stacked, and a scan's carry flows from copy to copy.
+    After this every node is a plain operator, which is what the placement stage has rules for.  Returns how many
+    operators were expanded (nested ones count)."""
+    import operator
+    hop = torch.ops.higher_order
+    done = 0
+    while True:
+        node = next((n for n in gm.graph.nodes if n.op == "call_function" and n.target in (hop.map_impl, hop.scan)), None)
+        if node is None:
+            break
+        graph = gm.graph
+        body = getattr(gm, node.args[0].target)
+        if node.target is hop.map_impl:
+            carried, xs, extra = [], list(node.args[1]), list(node.args[2])
+        else:
+            carried, xs, extra = list(node.args[1]), list(node.args[2]), list(node.args[3]) if len(node.args) > 3 else []
+        steps = xs[0].meta["val"].shape[0]
+        order = range(steps - 1, -1, -1) if node.kwargs.get("reverse", False) else range(steps)
+        rows: list[list] = []
+        for i in order:
+            elems = [_made(graph, node, torch.ops.aten.select.int, (x, 0, i), torch.ops.aten.select.int(x.meta["val"], 0, i)) for x in xs]
+            out = _inline(graph, body, carried + elems + extra, node)
+            carried, ys = out[: len(carried)], out[len(carried):]
+            rows.append(ys)
+        if node.kwargs.get("reverse", False):
+            rows.reverse()
+        stacked = []
+        for j in range(len(rows[0]) if rows else 0):
+            parts = [r[j] for r in rows]
+            stacked.append(_made(graph, node, torch.ops.aten.stack.default, (parts, 0),
+                                 torch.ops.aten.stack.default([p.meta["val"] for p in parts], 0)))
+        results = carried + stacked
+        for user in list(node.users):
+            if user.op == "call_function" and user.target is operator.getitem:
+                user.replace_all_uses_with(results[user.args[1]])
+                graph.erase_node(user)
+            else:
+                raise NotImplementedError(f"{node.name} is used whole by {user.name}")
+        holder = node.args[0]
+        graph.erase_node(node)
+        if not holder.users:
+            graph.erase_node(holder)
+        done += 1
+    if done:
+        gm.graph.lint()
+        gm.recompile()
+    return done
 
 
 def read(ep, training: bool = False) -> Exported:
