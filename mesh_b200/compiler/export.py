@@ -36,7 +36,12 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
             for op in (torch.ops.aten.scaled_dot_product_attention.default,):
                 decompositions.pop(op, None)
         ep = ep.run_decompositions(decompositions) if decompositions is not None else ep.run_decompositions()
-        expand_loops(ep.graph_module)
+        if expand_loops(ep.graph_module):
+            # results that were items of a loop operator are other nodes now: the signature names them
+            out_node = next(n for n in ep.graph_module.graph.nodes if n.op == "output")
+            for spec, node in zip(ep.graph_signature.output_specs, out_node.args[0]):
+                if isinstance(node, torch.fx.Node) and hasattr(spec.arg, "name"):
+                    spec.arg.name = node.name
         if loss is not None:
             from torch.export.experimental import _export_forward_backward
             ep = _export_forward_backward(ep, joint_loss_index=loss)

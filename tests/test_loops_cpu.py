@@ -74,3 +74,16 @@ def test_unrolled_loops_over_a_batch_cut_inference_and_training():
     loss.backward()
     assert abs(float(res.outputs) - float(loss)) < 1e-6
     assert torch.allclose(res.parameters["m.w"], w.grad, atol=1e-6)
+
+
+def test_archive_round_trip_of_a_program_with_unrolled_loops(tmp_path):
+    from mesh_b200.compiler import archive
+    torch.manual_seed(2)
+    xs, h0 = torch.randn(5, 6, 4), torch.randn(6, 4)
+    procs = {"p0": (0, "cpu"), "p1": (0, "cpu")}
+    sch = compile_module(Recurrent(), (xs, h0), procs, _placement(tuple(procs)))
+    archive.save(tmp_path / "a", sch)
+    back = archive.load(tmp_path / "a")
+    assert back.signature.digest == sch.signature.digest
+    a, b = Program(sch)(xs, h0), Program(back)(xs, h0)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
