@@ -20,7 +20,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--micro", type=int, default=8)
+    ap.add_argument("--impl", choices=["mesh", "stock"], default="mesh",
+                    help="stock: the same model and grid from PyTorch's own modules and torch.distributed (baseline/hybrid_stock.py)")
     a = ap.parse_args()
+    if a.impl == "stock":
+        return stock(a)
     from mesh_b200.config import MeshConfig, set_config
     set_config(MeshConfig.from_env(heap_bytes=16 << 30))      # gathered activations of every layer live in the heap
     ctx = init()
@@ -77,6 +81,62 @@ def main():
                                "inputs": "pinned host token ids copied every step"}})
     from mesh_b200.distributed import shutdown
     shutdown()
+
+
+def stock(a):
+    """The stock arm: same configuration, same clock, none of this package's kernels, layers or collectives."""
+    import os
+
+    import torch.distributed as dist
+    sys_path_root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    import sys
+    sys.path.insert(0, sys_path_root)
+    from baseline.hybrid_stock import Grid, StockConfig, StockTrainer
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    grid = Grid(a.grid if world > 1 else "", rank, world)
+    if a.small:
+        cfg = StockConfig(vocab=8192, d_model=1024, n_layers=4, n_heads=8, n_kv_heads=8, head_dim=128, d_ff=4096, seq_len=2048)
+    else:
+        cfg = StockConfig(vocab=50304, d_model=2048, n_layers=24, n_heads=16, n_kv_heads=16, head_dim=128, d_ff=8192, seq_len=8192)
+    M = a.micro
+    tr = StockTrainer(cfg, grid, dev, torch.bfloat16, micro_batch=1, n_micro=M, lr=1e-4)
+    g = torch.Generator(device="cpu").manual_seed(3 + grid.coord["dp"])
+    tokens = torch.randint(0, cfg.vocab, (M, cfg.seq_len), generator=g).pin_memory()
+    targets = torch.randint(0, cfg.vocab, (M, cfg.seq_len), generator=g).pin_memory()
+
+    def step():
+        return tr.step(tokens.to(dev, non_blocking=True), targets.to(dev, non_blocking=True))
+
+    for _ in range(max(1, a.warmup)):
+        loss = step()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = step()
+    e1.record()
+    last = float(loss)
+    barrier(world)
+    t = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    tok = M * cfg.seq_len * grid.size["dp"]
+    emit(rank, {"metric": "hybrid_train_tokens_per_s", "impl": "stock", "value": round(tok / (ms * 1e-3), 1), "unit": "tokens/s",
+                "n_gpus": world, "ms_per_step": round(ms, 3), "steps": a.steps, "loss": round(last, 4),
+                "config": {"grid": a.grid if world > 1 else "solo", "layers": cfg.n_layers, "d_model": cfg.d_model,
+                           "heads": cfg.n_heads, "d_ff": cfg.d_ff, "vocab": cfg.vocab, "seq_len": cfg.seq_len, "microbatches": M,
+                           "attention": "scaled_dot_product_attention; keys and values all-gathered over cp, contiguous tokens",
+                           "pipeline": "all forward, then all backward", "optimizer": "torch.optim.AdamW fused, bf16 parameters",
+                           "inputs": "pinned host token ids copied every step"}})
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
