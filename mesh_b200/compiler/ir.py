@@ -21,6 +21,11 @@ from typing import Any, NamedTuple
 
 import torch
 
+def pack(*items) -> tuple:
+    """Step target: the values of several steps as one tuple (an operator's results put back together)."""
+    return tuple(items)
+
+
 JOIN, PAGES = "join", "pages"       # consumers of a transfer: wait for all of it / take pieces as they land
 
 # ----------------------------------------------------------------------------- eager send / recv

@@ -134,7 +134,7 @@ def _line(st: Step) -> str:
         return f"{st.out} = local_slice({_fmt(st.args[0])}, axis={st.meta['axis']}, to={st.meta['to']!r})"
     if st.op == "collective":
         m = st.meta
-        extra = f", left={m['left']}, right={m['right']}" if st.target == "halo" else ""
+        extra = f", left={m['left']}, right={m['right']}" if st.target in ("halo", "halo_back") else ""
         return f"{st.out} = {st.target}({_fmt(st.args[0])}, axis={m['axis']}, channel={m.get('channel')}{extra})   # {m['from']!r} -> {m['to']!r}"
     if st.op == "fused":
         return f"{st.out} = fused_{st.target}({', '.join(_fmt(a) for a in st.args)}, axis={st.meta['axis']}, channel={st.meta.get('channel')})"

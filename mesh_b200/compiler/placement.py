@@ -26,7 +26,7 @@ from typing import Any, Callable
 
 import torch
 
-from .ir import JOIN, PAGES, Mesh, O, P, Plan, R, Ref, S, Spec, Step, Transfer
+from .ir import JOIN, PAGES, Mesh, O, P, Plan, R, Ref, S, Spec, Step, Transfer, pack
 
 aten = torch.ops.aten
 
@@ -162,10 +162,31 @@ def _layer_norm_backward(node, shapes):
             "outs": ["S", "P", "P"]}
 
 
+# pooling: (position of the kernel / stride / padding / dilation arguments, tensor operands that have the input's
+# extent, tensor operands that have the output's extent, number of outputs)
+POOLS = {
+    aten.avg_pool2d.default: {"kernel": 1, "stride": 2, "padding": 3, "dilation": None, "inputs": (0,), "outputs": (), "outs": 1, "backward": False},
+    aten.max_pool2d_with_indices.default: {"kernel": 1, "stride": 2, "padding": 3, "dilation": 4, "inputs": (0,), "outputs": (), "outs": 2, "backward": False},
+    aten.avg_pool2d_backward.default: {"kernel": 2, "stride": 3, "padding": 4, "dilation": None, "inputs": (1,), "outputs": (0,), "outs": 1, "backward": True},
+    aten.max_pool2d_with_indices_backward.default: {"kernel": 2, "stride": 3, "padding": 4, "dilation": 5, "inputs": (1,), "outputs": (0, 2), "outs": 1, "backward": True},
+}
+
+
 # random draws: the executor makes them with a counter-based generator keyed by (seed, execution, draw site, logical
 # element), so that a value is the same however it is cut and identical on every processor that holds a copy
 DRAWS = {aten.native_dropout.default: "dropout", aten.rand_like.default: "uniform", aten.randn_like.default: "normal",
          aten.rand.default: "uniform", aten.randn.default: "normal"}
+
+
+def _convolution(node, shapes):
+    # (input, weight, bias?): samples are independent; a cut anywhere else is the halo rule's business
+    return {"batched": [True] + [False] * (len(shapes) - 1), "protect": set(range(1, len(shapes[0]))), "outs": ["S"]}
+
+
+def _convolution_backward(node, shapes):
+    # (grad_output, input, weight, ...) -> (grad_input, grad_weight, grad_bias): the last two sum over the samples
+    return {"batched": [True, True] + [False] * (len(shapes) - 2), "protect": set(range(1, len(shapes[0]))),
+            "outs": ["S", "P", "P"]}
 
 
 # operators whose leading (or all but one) dimensions are independent problems: a cut there stays where it is
@@ -177,6 +198,7 @@ BATCHED = {
     aten.linalg_inv_ex.default: _trailing(2, 2), aten.linalg_lu_factor_ex.default: _trailing(2, 3),
     aten.sort.default: _along(1, 2), aten.sort.stable: _along(2, 2), aten.topk.default: _along(2, 2),
     aten.cummax.default: _along(1, 2), aten.cummin.default: _along(1, 2),
+    aten.convolution.default: _convolution, aten.convolution_backward.default: _convolution_backward,
     aten.native_layer_norm.default: _layer_norm, aten.native_layer_norm_backward.default: _layer_norm_backward,
 }
 
@@ -204,6 +226,7 @@ class Propagator:
         self.transfers: list[Transfer] = []
         self.tmp = 0
         self.channel = 0
+        self.extended: dict = {}                  # (value, left, right) -> its halo-extended copy (forward -> backward)
         self.sites = 0                             # random draws so far: each gets its own stream of the generator
         self.renamed: dict[str, str] = {}         # node name -> value that carries it after a stated reshard
 
@@ -469,11 +492,15 @@ class Propagator:
         handled = not list_args and isinstance(val, torch.Tensor)
         if tgt is aten.convolution.default and self.halo_convolution(node, tnames):
             return
+        if tgt is aten.convolution_backward.default and self.halo_convolution_backward(node, tnames):
+            return
         if tgt is aten._assert_tensor_metadata.default:
             return                                       # a trace-time check of dtype/shape: nothing to run, no reason to gather
         if tgt is aten.index_put.default and self.accumulating_index_put(node):
             return
         if tgt in (aten.cat.default, aten.stack.default) and self.joined(node):
+            return
+        if tgt in POOLS and self.pooled(node, tnames):
             return
         if tgt in BATCHED and self.batched(node, tnames):
             return
@@ -749,6 +776,75 @@ class Propagator:
             self.renamed[node.name] = self.reshard(node.name, want)
         return True
 
+    def pooled(self, node, tnames) -> bool:
+        """2-D pooling (and its backward) over an input cut along a spatial dimension where no window straddles a cut:
+        stride = kernel, no padding or dilation there, every processor's extent a multiple of the kernel.  Each
+        processor pools its own block; the output is cut at the same places, divided by the kernel.  (The indices of a
+        max pooling are positions within the local block, which is what its backward, run on the same block, expects.)
+        Cuts along the batch or channel dimensions need nothing: they are handled as a batch."""
+        info = POOLS[node.target]
+        args = list(node.args)
+
+        def arg(key, default):
+            pos = info[key]
+            v = args[pos] if pos is not None and len(args) > pos else default
+            return list(v) if isinstance(v, (list, tuple)) else [v, v]
+        kernel = arg("kernel", None)
+        stride = arg("stride", []) or kernel
+        padding, dilation = arg("padding", 0), arg("dilation", 1)
+        kernel, stride, padding, dilation = (v * 2 if len(v) == 1 else v for v in (kernel, stride, padding, dilation))
+        x = tnames[list(info["inputs"])[0]] if not info["backward"] else tnames[1]
+        nd = len(self.shape[x])
+        ins = [tnames[i] for i in info["inputs"]]
+        outs = [tnames[i] for i in info["outputs"]]
+        wants = {n: [] for n in tnames}
+        spec_in, spec_out = [], []
+        found = False
+        for ax in range(self.na):
+            sp = self.spec[x][ax]
+            if sp.kind == "R":
+                others = [self.spec[n][ax] for n in tnames if n != x]
+                if any(o.kind != "R" for o in others):
+                    return False
+                for n in tnames:
+                    wants[n].append(R)
+                spec_in.append(R)
+                spec_out.append(R)
+                continue
+            if sp.kind != "S" or sp.striped:
+                return False
+            if sp.dim < nd - 2:                                        # batch or channel: nothing to check
+                small = sp
+            else:
+                i = sp.dim - (nd - 2)
+                if stride[i] != kernel[i] or padding[i] or dilation[i] != 1 or any(c % kernel[i] for c in sp.counts):
+                    return False
+                small = Spec("S", sp.dim, tuple(c // kernel[i] for c in sp.counts))
+            found = True
+            for n in ins:
+                wants[n].append(sp)
+            for n in outs:
+                wants[n].append(small)
+            spec_in.append(sp)
+            spec_out.append(small)
+        if not found:
+            return False
+        new_names = {}
+        orig = [a.name for a in node.args if _is_tensor_node(a)]
+        for o, n in zip(orig, tnames):
+            new_names[o] = self.reshard(n, tuple(wants[n]))
+        result = tuple(spec_in if info["backward"] else spec_out)
+        val = node.meta.get("val")
+        if isinstance(val, (tuple, list)):
+            for i in range(len(val)):
+                self.spec[(node.name, i)] = result
+            self.spec[node.name] = self.all_r()
+        else:
+            self.spec[node.name] = result
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
+                               self.ref_kwargs(node.kwargs, new_names), {"out_specs": result, "full_shape": _shape(node)}))
+        return True
+
     def batched(self, node, tnames) -> bool:
         """An operator of ``BATCHED`` whose operands are cut along a batch dimension (one it does not work along):
         every processor runs it on its own problems; outputs keep the cut (or are partial sums where the operator sums
@@ -903,8 +999,11 @@ class Propagator:
             return False
         left, right = padding[i], reach - padding[i]
         src = x
-        if reach:
+        if reach and (x, left, right) in self.extended:
+            src = self.extended[(x, left, right)]
+        elif reach:
             src = self.fresh(x)
+            self.extended[(x, left, right)] = src
             self.channel += 1
             esz = torch.empty((), dtype=self.dtype[x]).element_size() if x in self.dtype else 4
             edge = int(math.prod(self.shape[x])) // max(1, self.shape[x][sp.dim]) * (left + right) * esz
@@ -926,6 +1025,79 @@ class Propagator:
         want = self.stated.get(node.name)
         if want is not None and want != out_spec:
             self.renamed[node.name] = self.reshard(node.name, want)
+        return True
+
+    def _halo_step(self, x: str, ax: int, sp: Spec, left: int, right: int, verb: str = "halo") -> str:
+        """Emit the neighbour exchange of ``x``'s edge rows (or, for ``halo_back``, its adjoint); returns the new value."""
+        out = self.fresh(x)
+        self.channel += 1
+        esz = torch.empty((), dtype=self.dtype[x]).element_size() if x in self.dtype else 4
+        full = self.shape[x]
+        edge = int(math.prod(full)) // max(1, full[sp.dim]) * (left + right) * esz
+        self.transfers.append(Transfer(self.channel, "permute", verb, ax, x, sp.dim, tuple(sp.counts), JOIN, edge))
+        self.steps.append(Step("collective", out, verb, (Ref(x),), {},
+                               {"axis": ax, "from": sp, "to": sp, "channel": self.channel, "kind": "permute",
+                                "full_shape": full, "left": left, "right": right}))
+        self.shape[out] = full
+        if x in self.dtype:
+            self.dtype[out] = self.dtype[x]
+        self.spec[out] = self.spec[x]
+        return out
+
+    def halo_convolution_backward(self, node, tnames) -> bool:
+        """The backward of :meth:`halo_convolution`.  Every processor differentiates the convolution of its own extended
+        block: the weight and bias gradients are partial sums; the gradient with respect to the extended block has
+        rows that belong to the neighbours, which the adjoint of the halo exchange sends back and adds."""
+        args = list(node.args)
+        g, x, w = tnames[0], tnames[1], tnames[2]
+        stride, padding, dilation, transposed, groups, mask = args[4], list(args[5]), args[6], args[7], args[9], list(args[10])
+        if transposed or any(self.spec[w][a].kind != "R" for a in range(self.na)):
+            return False
+        cut = [(a, sp) for a, sp in enumerate(self.spec[x]) if sp.kind != "R"]
+        if len(cut) != 1 or cut[0][1].kind != "S" or cut[0][1].striped or cut[0][1].dim < 2:
+            return False
+        ax, sp = cut[0]
+        i = sp.dim - 2
+        k = self.shape[w][sp.dim]
+        reach = dilation[i] * (k - 1)
+        if stride[i] != 1 or 2 * padding[i] != reach or min(sp.counts) < max(padding[i], reach - padding[i]):
+            return False
+        if self.shape[g][sp.dim] != self.shape[x][sp.dim]:
+            return False
+        left, right = padding[i], reach - padding[i]
+        same = tuple(Spec("S", sp.dim, sp.counts) if a == ax else R for a in range(self.na))
+        g_local = self.reshard(g, same)
+        x_ext = x
+        if reach:
+            x_ext = self.extended.get((x, left, right)) or self._halo_step(x, ax, sp, left, right)
+            self.extended[(x, left, right)] = x_ext
+        padding[i] = 0
+        new_args = list(self.ref_args(node.args, {node.args[0].name: g_local, node.args[1].name: x_ext}))
+        new_args[5] = padding
+        raw = self.fresh(node.name)
+        self.steps.append(Step("call", raw, node.target, tuple(new_args), self.ref_kwargs(node.kwargs),
+                               {"halo": (left, right), "full_shape": ()}))
+        partial = tuple(P() if a == ax else R for a in range(self.na))
+        items = []
+        for j in range(3):
+            if not mask[j]:
+                items.append(None)
+                continue
+            item = self.fresh(f"{node.name}_{j}")
+            self.steps.append(Step("call", item, operator.getitem, (Ref(raw), j)))
+            val = node.meta["val"][j]
+            self.shape[item], self.dtype[item] = tuple(val.shape), val.dtype
+            self.spec[item] = same if j == 0 else partial
+            if j == 0 and reach:
+                self.shape[item] = self.shape[x]
+                if x in self.dtype:
+                    self.dtype[item] = self.dtype[x]
+                item = self._halo_step(item, ax, sp, left, right, "halo_back")
+            items.append(item)
+            self.spec[(node.name, j)] = same if j == 0 else partial
+        self.spec[node.name] = self.all_r()
+        self.shape[node.name] = ()
+        self.steps.append(Step("call", node.name, pack, tuple(Ref(it) if it is not None else None for it in items)))
         return True
 
     def fallback(self, node, tnames, list_args):

@@ -152,10 +152,12 @@ class Executor:
         me = self.coords[ax]
         if self.trace is not None and "channel" in m:
             self.trace.append((verb, m.get("kind"), ax, m["channel"]))
-        if P == 1 and verb != "halo":
+        if P == 1 and verb not in ("halo", "halo_back"):
             return t
         if verb == "halo":
             return self._halo(t, ax, frm.dim, m["left"], m["right"], me, P)
+        if verb == "halo_back":
+            return self._halo_back(t, ax, frm.dim, m["left"], m["right"], me, P)
         if self.dist:
             return self._collective_dist(verb, ax, frm, to, t, m)
         parts, g = self.coll.gather_all(t, ax)
@@ -215,6 +217,44 @@ class Executor:
             got_r = edge(parts[me + 1], 0, right) if (right and me < P - 1) else zr
         pieces = [p for p in (got_l, t, got_r) if p is not None]
         return torch.cat(pieces, dim=dim) if len(pieces) > 1 else t
+
+    def _halo_back(self, t, ax, dim, left, right, me, P):
+        """The adjoint of :meth:`_halo`: ``t`` is a gradient over this processor's extended block.  Its first ``left``
+        rows belong to the previous processor's last rows and its last ``right`` rows to the next processor's first
+        rows; they are sent there and added, and what the neighbours hold for this block's edges is added here."""
+        rows = t.shape[dim] - left - right
+        core = t.narrow(dim, left, rows).clone()
+        mine_l = t.narrow(dim, 0, left) if left else None                   # for the previous processor
+        mine_r = t.narrow(dim, left + rows, right) if right else None       # for the next processor
+        got_prev = got_next = None
+        if P > 1 and self.dist:
+            grp, g = self.coll.group(ax)
+            ops = []
+            if left and me > 0:
+                ops.append(dist.P2POp(dist.isend, mine_l.contiguous(), g[me - 1], group=grp))
+            if right and me < P - 1:
+                ops.append(dist.P2POp(dist.isend, mine_r.contiguous(), g[me + 1], group=grp))
+            if right and me > 0:                                 # the previous processor's right halo covers my first rows
+                got_prev = torch.empty_like(core.narrow(dim, 0, right))
+                ops.append(dist.P2POp(dist.irecv, got_prev, g[me - 1], group=grp))
+            if left and me < P - 1:
+                got_next = torch.empty_like(core.narrow(dim, rows - left, left))
+                ops.append(dist.P2POp(dist.irecv, got_next, g[me + 1], group=grp))
+            if ops:
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+        elif P > 1:
+            parts, _ = self.coll.gather_all(t, ax)
+            if right and me > 0:
+                prev = parts[me - 1]
+                got_prev = prev.narrow(dim, prev.shape[dim] - right, right)
+            if left and me < P - 1:
+                got_next = parts[me + 1].narrow(dim, 0, left)
+        if got_prev is not None:
+            core.narrow(dim, 0, right).add_(got_prev)
+        if got_next is not None:
+            core.narrow(dim, rows - left, left).add_(got_next)
+        return core
 
     @staticmethod
     def _reduce(parts, op):

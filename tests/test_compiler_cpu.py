@@ -308,3 +308,53 @@ def test_batched_operators_with_several_outputs_keep_a_batch_cut():
     res = Program(sch)(x)
     loss, grads = _eager(m, x)
     _check(res, loss, grads)
+
+
+class _ConvNet(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.c1, self.c2 = torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.Conv2d(8, 8, 5, padding=2)
+        self.fc = torch.nn.Linear(8 * 4 * 4, 5)
+
+    def forward(self, x):
+        h = torch.nn.functional.max_pool2d(torch.relu(self.c1(x)), 2)
+        h = torch.nn.functional.avg_pool2d(torch.relu(self.c2(h)), 2)
+        return self.fc(h.flatten(1)).pow(2).mean()
+
+
+@pytest.mark.parametrize("n,dim", [(2, 2), (2, 3), (2, 0)])
+def test_convolution_network_trains_under_a_spatial_or_batch_cut(n, dim):
+    """Convolution forward and backward with halo exchange (and its adjoint), pooling whose windows do not straddle a
+    cut, and the plain batch cut: no operator gathers its input, gradients match eager."""
+    torch.manual_seed(13)
+    m, x = _ConvNet(), torch.randn(2, 3, 16, 16)
+    procs = _procs(n)
+    names = tuple(procs)
+    sch = compile_module(m, (x,), procs, lambda nd: (dim, names, None) if nd.op == "placeholder" and nd.name == "x" else None, loss=0)
+    assert not [st.target for st in sch.plan.steps if st.meta.get("fallback")]
+    verbs = sch.structure["by_verb"]
+    if dim == 0:
+        assert set(verbs) == {"all_reduce"}
+    else:
+        assert verbs["halo"] == 2 and verbs["halo_back"] == 1              # the first layer's input needs no gradient
+    res = Program(sch)(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
+
+
+def _conv_rank(rank, world, rdv):
+    torch.manual_seed(14)
+    m, x = _ConvNet(), torch.randn(2, 3, 16, 16)
+    procs = _procs(world)
+    names = tuple(procs)
+    sch = compile_module(m, (x,), procs, lambda nd: (2, names, None) if nd.op == "placeholder" and nd.name == "x" else None, loss=0)
+    res = Program(sch)(x)                      # one process per processor: halos go point to point
+    loss, grads = _eager(m, x)
+    assert abs(float(res.outputs) - float(loss)) < 1e-5
+    for k in ("c1.weight", "c2.weight", "fc.bias"):
+        assert torch.allclose(res.parameters[k], grads[k], atol=1e-5), k
+
+
+def test_halo_exchange_and_its_adjoint_between_processes():
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_conv_rank, 2, init_pg="gloo")
