@@ -178,6 +178,11 @@ DRAWS = {aten.native_dropout.default: "dropout", aten.rand_like.default: "unifor
          aten.rand.default: "uniform", aten.randn.default: "normal"}
 
 
+def _batch_norm_inference(node, shapes):
+    # (input, weight, bias, running_mean, running_var, momentum, eps) -> (output, empty, empty): per-channel arithmetic
+    return {"batched": [True] + [False] * (len(shapes) - 1), "protect": {1}, "outs": ["S", "R", "R"]}
+
+
 def _convolution(node, shapes):
     # (input, weight, bias?): samples are independent; a cut anywhere else is the halo rule's business
     return {"batched": [True] + [False] * (len(shapes) - 1), "protect": set(range(1, len(shapes[0]))), "outs": ["S"]}
@@ -198,6 +203,7 @@ BATCHED = {
     aten.linalg_inv_ex.default: _trailing(2, 2), aten.linalg_lu_factor_ex.default: _trailing(2, 3),
     aten.sort.default: _along(1, 2), aten.sort.stable: _along(2, 2), aten.topk.default: _along(2, 2),
     aten.cummax.default: _along(1, 2), aten.cummin.default: _along(1, 2),
+    aten._native_batch_norm_legit_no_training.default: _batch_norm_inference,
     aten.convolution.default: _convolution, aten.convolution_backward.default: _convolution_backward,
     aten.native_layer_norm.default: _layer_norm, aten.native_layer_norm_backward.default: _layer_norm_backward,
 }
@@ -878,7 +884,7 @@ class Propagator:
             for n, f in zip(tnames, flags):
                 wants[n].append(same if f else R)
             for o, kind in zip(out_specs, outs):
-                o.append(same if kind == "S" else P())
+                o.append(same if kind == "S" else R if kind == "R" else P())
         if not found:
             return False
         dims = [s.dim for s in out_specs[0] if s.kind == "S"]

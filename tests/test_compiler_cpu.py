@@ -358,3 +358,25 @@ def _conv_rank(rank, world, rdv):
 def test_halo_exchange_and_its_adjoint_between_processes():
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_conv_rank, 2, init_pg="gloo")
+
+
+@pytest.mark.parametrize("dim", [0, 2])
+def test_inference_batch_norm_keeps_batch_and_spatial_cuts(dim):
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c, self.bn = torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.BatchNorm2d(8)
+
+        def forward(self, x):
+            return torch.relu(self.bn(self.c(x)))
+
+    torch.manual_seed(15)
+    m = Net().eval()
+    m.bn.running_mean.normal_()
+    m.bn.running_var.uniform_(0.5, 2.0)
+    x = torch.randn(4, 3, 8, 8)
+    procs = _procs(2)
+    names = tuple(procs)
+    sch = compile_module(m, (x,), procs, lambda nd: (dim, names, None) if nd.op == "placeholder" and nd.name == "x" else None)
+    assert sch.structure["fallbacks"] == 0 and sch.structure["by_verb"].get("all_gather") == 1      # only the result
+    assert torch.allclose(Program(sch)(x), m(x), atol=1e-6)
