@@ -87,3 +87,18 @@ def test_hourly_runner_records_result_failure_and_timeout(tmp_path):
     assert bad["status"] == "exit 3" and "boom" in bad["tail"]
     slow = hourly.run_one({"name": "slow", "cmd": [py, "-c", "import time; time.sleep(60)"], "deadline_s": 1}, cwd=tmp_path)
     assert slow["status"] == "timeout" and slow["seconds"] < 20
+
+
+def test_micro_workloads_run_small_and_variants_agree():
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "micro.py")
+    spec = importlib.util.spec_from_file_location("micro_workloads", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    recs = mod.main(["all", "--small", "--device", "cpu", "--steps", "1"])
+    names = {r["workload"] for r in recs}
+    assert names == set(mod.WORKLOADS)
+    assert all(r["ms"] > 0 for r in recs)
+    assert all(r["orthogonality_error"] < 1e-3 for r in recs if r["workload"] == "orth")
+    assert all(r.get("difference", 0) < 1e-4 for r in recs if r["workload"] in ("pairwise", "moe_dispatch"))
