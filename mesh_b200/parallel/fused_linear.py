@@ -169,3 +169,51 @@ def column_linear(x, w, op: FusedColumnLinear):
 def row_linear(h, w, op: FusedRowLinear):
     """``h [tokens, K_local]`` -> this rank's ``[tokens/world, D]`` rows of the summed product."""
     return _RowFn.apply(h, w, op)
+
+
+class FusedRowLinearAllReduce(_FusedBase):
+    """``y = all_reduce(h W^T)`` for layers whose activations are not cut over the tokens (plain Megatron tensor
+    parallelism, the row-parallel half: examples/parallel.py:84-89 of the reference, whose compiler emits a reduce
+    there, compiler/mesh_compiler/placement.py:812-834).
+
+    A two-shot all-reduce whose first shot is the GEMM's own epilogue: the tiles are scattered to the owners of their
+    token rows and summed there (:class:`FusedRowLinear`), then the summed rows are all-gathered with the
+    communicator's kernel, so the partial products never make a round trip through HBM before they cross NVLink.
+    Backward: ``dy`` is whole on every rank, so ``dh = dy W`` and ``dW = dy^T h`` are local products."""
+
+    def __init__(self, heap, comm, tokens: int, k_local: int, d_out: int):
+        super().__init__(heap, tokens, k_local, d_out)
+        self.row = FusedRowLinear(heap, tokens, k_local, d_out)
+        self.comm, self.D = comm, d_out
+
+    def forward(self, h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        mine = self.row.forward(h, w)                                     # [tokens / world, D]: summed over the ranks
+        full = torch.empty((self.M, self.D), dtype=mine.dtype, device=mine.device)
+        self.comm.all_gather(full, mine)
+        return full
+
+    def backward(self, dy: torch.Tensor, h: torch.Tensor, w: torch.Tensor):
+        dy = dy.contiguous()
+        dh = G.gemm(dy, w, b_mn=True)                                     # [tokens, K_local] = dy W, W [D, K] read as [K = D, N = K_local]
+        dw = G.gemm(dy, h, a_mn=True, b_mn=True)                          # [D, K_local] = dy^T h
+        return dh, dw
+
+
+class _RowARFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, w, op: FusedRowLinearAllReduce):
+        h = h.contiguous()
+        ctx.op = op
+        ctx.save_for_backward(h, w)
+        return op.forward(h, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        h, w = ctx.saved_tensors
+        dh, dw = ctx.op.backward(dy, h, w)
+        return dh, dw, None
+
+
+def row_linear_all_reduce(h, w, op: FusedRowLinearAllReduce):
+    """``h [tokens, K_local]`` -> ``[tokens, D]``, the product summed over the ranks, whole on every rank."""
+    return _RowARFn.apply(h, w, op)

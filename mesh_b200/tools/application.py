@@ -28,7 +28,7 @@ from pathlib import Path
 from ..utils.disk import room
 
 MANIFEST = "MANIFEST.json"
-SKIP_DIRS = {".git", "__pycache__", "gpurun_out", "_work", ".pytest_cache"}
+SKIP_DIRS = {".git", "__pycache__", ".pytest_cache"}
 
 
 def _sha(path: Path) -> str:

@@ -53,3 +53,47 @@ def test_fused_column_and_row_linear(world):
         pytest.skip(f"needs {world} GPUs")
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_rank, world, use_cuda=True, timeout=300.0)
+
+
+def _rank_all_reduce(rank, world, rdv):
+    from mesh_b200.config import MeshConfig, set_config
+    from mesh_b200.distributed.comm import Communicator
+    from mesh_b200.distributed.context import MeshContext
+    from mesh_b200.parallel.fused_linear import FusedRowLinearAllReduce, row_linear_all_reduce
+    from mesh_b200.utils.status import check_status
+    torch.cuda.set_device(rank)
+    set_config(MeshConfig.from_env(heap_bytes=1 << 30))
+    ctx = MeshContext(rank, world, torch.device("cuda", rank), rdv, None)
+    comm = Communicator(ctx.heap, staging_bytes=32 << 20, p2p_slot_bytes=8 << 20)
+    M, D, N = 256 * world, 512, 768
+    g = torch.Generator().manual_seed(4)
+    h = torch.randn(M, N, generator=g).bfloat16()
+    w = (torch.randn(D, N, generator=g) * 0.05).bfloat16()
+    dy = torch.randn(M, D, generator=g).bfloat16()
+    Nl = N // world
+    op = FusedRowLinearAllReduce(ctx.heap, comm, M, Nl, D)
+    for step in range(2):
+        hl = h[:, rank * Nl:(rank + 1) * Nl].contiguous().cuda().requires_grad_(True)
+        wl = w[:, rank * Nl:(rank + 1) * Nl].contiguous().cuda().requires_grad_(True)
+        y = row_linear_all_reduce(hl, wl, op)                     # [M, D], whole on every rank
+        y.backward(dy.cuda())
+        torch.cuda.synchronize()
+        check_status()
+        hf, wf = h.float().requires_grad_(True), w.float().requires_grad_(True)
+        yf = hf @ wf.T
+        yf.backward(dy.float())
+
+        def close(a, b, tol=3e-2):
+            assert (a.float().cpu() - b).abs().max() <= tol * b.abs().max() + 1e-3
+        close(y, yf.detach())
+        close(hl.grad, hf.grad[:, rank * Nl:(rank + 1) * Nl])
+        close(wl.grad, wf.grad[:, rank * Nl:(rank + 1) * Nl])
+    rdv.barrier("fused-ar-done")
+    ctx.heap.close()
+
+
+def test_fused_row_linear_all_reduce():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_rank_all_reduce, 2, use_cuda=True, timeout=300.0)
