@@ -108,7 +108,8 @@ class HostWord:
     (``mesh_host_publish`` / ``mesh_host_arrived`` / ``mesh_host_wait``, rdma/mesh-collective.c:17-90)."""
 
     def __init__(self):
-        self.t = torch.zeros(2, dtype=torch.int64).pin_memory() if torch.cuda.is_available() else torch.zeros(2, dtype=torch.int64)
+        # [0] what has been supplied (arrivals), [1] cancellation, [2] what has been sent (the sender may reuse its buffer)
+        self.t = torch.zeros(3, dtype=torch.int64).pin_memory() if torch.cuda.is_available() else torch.zeros(3, dtype=torch.int64)
 
     def publish(self, value: int) -> None:
         if value > int(self.t[0]):                      # monotonic: never written to an earlier value
@@ -119,6 +120,14 @@ class HostWord:
 
     def arrived(self, value: int) -> bool:
         return int(self.t[0]) >= value
+
+    def mark_sent(self, value: int) -> None:
+        if value > int(self.t[2]):
+            self.t[2] = value
+
+    def sent(self, value: int) -> bool:
+        """Has everything up to ``value`` left this rank (``mesh_host_sent``): its source buffers may be rewritten."""
+        return int(self.t[2]) >= value
 
     def wait(self, value: int, timeout_s: float = 5.0) -> int:
         """0 when reached, ``ECANCELED`` when cancelled, ``ETIMEDOUT`` after ``timeout_s`` without progress."""

@@ -59,6 +59,10 @@ def test_host_word_and_epoch():
     w.publish(3)
     w.publish(2)                                          # never moves backwards
     assert w.arrived(3) and not w.arrived(4)
+    assert not w.sent(1)
+    w.mark_sent(2)
+    w.mark_sent(1)
+    assert w.sent(2) and not w.sent(3)
     assert w.wait(3, 0.1) == 0 and w.wait(4, 0.05) == ETIMEDOUT
     w.cancel()
     assert w.wait(4, 0.05) == ECANCELED
