@@ -983,6 +983,21 @@ class Propagator:
                                self.ref_kwargs(node.kwargs, new_names), {"out_specs": out_spec, "full_shape": _shape(node)}))
         return True
 
+    def _spatial_cut(self, x: str):
+        """``((axis, spec), {axis: batch spec})`` when ``x`` is cut along exactly one spatial dimension (contiguous) and,
+        on other grid axes, at most along the batch dimension; ``(None, None)`` otherwise."""
+        cut, batch = None, {}
+        for a, sp in enumerate(self.spec[x]):
+            if sp.kind == "R":
+                continue
+            if sp.kind == "S" and sp.dim == 0:
+                batch[a] = sp
+            elif sp.kind == "S" and sp.dim >= 2 and not sp.striped and cut is None:
+                cut = (a, sp)
+            else:
+                return None, None
+        return (cut, batch) if cut is not None else (None, None)
+
     def halo_convolution(self, node, tnames) -> bool:
         """A convolution whose input is cut along one spatial dimension: every processor fetches the rows of its
         neighbours that its windows reach (a neighbour exchange, the reference's halos, placement.py:388-485) and
@@ -994,10 +1009,10 @@ class Propagator:
         stride, padding, dilation, transposed, groups = args[3], list(args[4]), args[5], args[6], args[8]
         if transposed or any(self.spec[n][a].kind != "R" for n in tnames[1:] for a in range(self.na)):
             return False
-        cut = [(a, sp) for a, sp in enumerate(self.spec[x]) if sp.kind != "R"]
-        if len(cut) != 1 or cut[0][1].kind != "S" or cut[0][1].striped or cut[0][1].dim < 2:
+        cut, batch = self._spatial_cut(x)
+        if cut is None:
             return False
-        ax, sp = cut[0]
+        ax, sp = cut
         i = sp.dim - 2
         k = self.shape[w][sp.dim]
         reach = dilation[i] * (k - 1)
@@ -1024,7 +1039,7 @@ class Propagator:
         padding[i] = 0
         new_args = list(self.ref_args(node.args, {node.args[0].name: src}))
         new_args[4] = padding
-        out_spec = tuple(Spec("S", sp.dim, sp.counts) if a == ax else R for a in range(self.na))
+        out_spec = tuple(Spec("S", sp.dim, sp.counts) if a == ax else batch.get(a, R) for a in range(self.na))
         self.spec[node.name] = out_spec
         self.steps.append(Step("call", node.name, node.target, tuple(new_args), self.ref_kwargs(node.kwargs),
                                {"out_specs": out_spec, "full_shape": _shape(node), "halo": (left, right)}))
@@ -1059,10 +1074,10 @@ class Propagator:
         stride, padding, dilation, transposed, groups, mask = args[4], list(args[5]), args[6], args[7], args[9], list(args[10])
         if transposed or any(self.spec[w][a].kind != "R" for a in range(self.na)):
             return False
-        cut = [(a, sp) for a, sp in enumerate(self.spec[x]) if sp.kind != "R"]
-        if len(cut) != 1 or cut[0][1].kind != "S" or cut[0][1].striped or cut[0][1].dim < 2:
+        cut, batch = self._spatial_cut(x)
+        if cut is None:
             return False
-        ax, sp = cut[0]
+        ax, sp = cut
         i = sp.dim - 2
         k = self.shape[w][sp.dim]
         reach = dilation[i] * (k - 1)
@@ -1071,7 +1086,7 @@ class Propagator:
         if self.shape[g][sp.dim] != self.shape[x][sp.dim]:
             return False
         left, right = padding[i], reach - padding[i]
-        same = tuple(Spec("S", sp.dim, sp.counts) if a == ax else R for a in range(self.na))
+        same = tuple(Spec("S", sp.dim, sp.counts) if a == ax else batch.get(a, R) for a in range(self.na))
         g_local = self.reshard(g, same)
         x_ext = x
         if reach:
@@ -1083,7 +1098,7 @@ class Propagator:
         raw = self.fresh(node.name)
         self.steps.append(Step("call", raw, node.target, tuple(new_args), self.ref_kwargs(node.kwargs),
                                {"halo": (left, right), "full_shape": ()}))
-        partial = tuple(P() if a == ax else R for a in range(self.na))
+        partial = tuple(P() if (a == ax or a in batch) else R for a in range(self.na))     # sums over rows and samples
         items = []
         for j in range(3):
             if not mask[j]:

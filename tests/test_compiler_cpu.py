@@ -380,3 +380,28 @@ def test_inference_batch_norm_keeps_batch_and_spatial_cuts(dim):
     sch = compile_module(m, (x,), procs, lambda nd: (dim, names, None) if nd.op == "placeholder" and nd.name == "x" else None)
     assert sch.structure["fallbacks"] == 0 and sch.structure["by_verb"].get("all_gather") == 1      # only the result
     assert torch.allclose(Program(sch)(x), m(x), atol=1e-6)
+
+
+def test_convolution_network_on_a_grid_batch_by_height():
+    """A 2 x 2 grid: the batch over one axis, the image height over the other; halos travel along the second axis only."""
+    torch.manual_seed(16)
+    m, x = _ConvNet(), torch.randn(4, 3, 16, 16)
+    procs = _procs(4)
+    sch = compile_module(m, (x,), procs, lambda nd: ((0, 2), None, (None, None)) if nd.op == "placeholder" and nd.name == "x" else None,
+                         loss=0, mesh=(2, 2))
+    assert sch.structure["fallbacks"] == 0
+    assert sch.structure["by_verb"]["halo"] == 2 and sch.structure["by_verb"]["halo_back"] == 1
+    res = Program(sch)(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
+
+
+def test_random_draws_do_not_depend_on_a_grid_cut():
+    class Draws(torch.nn.Module):
+        def forward(self, x):
+            return torch.nn.functional.dropout(x, 0.5, training=True) + torch.rand_like(x)
+
+    x = torch.ones(4, 8)
+    grid = Program(compile_module(Draws(), (x,), _procs(4), lambda nd: ((0, 1), None, (None, None)) if nd.name == "x" else None, mesh=(2, 2)))(x)
+    whole = Program(compile_module(Draws(), (x,), _procs(1), lambda nd: None))(x)
+    assert torch.equal(grid, whole)
