@@ -222,12 +222,38 @@ def _pinv_rule(a, *, atol=None, rtol=None, hermitian=False):
     return pinv(a)
 
 
-def table(max_squarings: int = 16, base: dict | None = None, keep_attention: bool = True) -> dict:
+def var_mean(x: torch.Tensor, dim=None, *, correction=None, keepdim: bool = False):
+    """Variance and mean through sums only, so that a reduction over a cut dimension becomes partial sums and one
+    all-reduce (the two-pass form: the mean first, then the mean of squared differences)."""
+    dims = list(range(x.ndim)) if dim is None else [d % x.ndim for d in ([dim] if isinstance(dim, int) else dim)]
+    count = math.prod(x.shape[d] for d in dims)
+    c = 1 if correction is None else correction
+    mean = x.mean(dims, keepdim=True)
+    diff = x - mean
+    var = (diff * diff).sum(dims, keepdim=keepdim) / max(count - c, 0)
+    return var, (mean if keepdim else mean.squeeze(dims))
+
+
+def norms(base: dict | None = None) -> dict:
+    """Training-mode batch norm (forward and backward) as means, sums and pointwise arithmetic.  Under a batch cut the
+    statistics are then those of the whole batch - what the single-process module computes - at the price of two small
+    all-reduces, instead of the operator gathering its input."""
+    out = dict(base if base is not None else torch.export.default_decompositions())
+    out.update(torch._decomp.get_decompositions([aten._native_batch_norm_legit_functional, aten._native_batch_norm_legit,
+                                                 aten.native_batch_norm, aten.native_batch_norm_backward]))
+    out[aten.var_mean.correction] = var_mean
+    return out
+
+
+def table(max_squarings: int = 16, base: dict | None = None, keep_attention: bool = True, batch_norm: bool = False) -> dict:
     """The capture stage's decomposition table with the formulations of this module added.
 
     ``base``: the table to extend (default: ``torch.export.default_decompositions()``); ``keep_attention`` leaves
-    ``scaled_dot_product_attention`` whole, as the capture stage does for inference graphs."""
+    ``scaled_dot_product_attention`` whole, as the capture stage does for inference graphs (pass ``False`` for a joint
+    forward+backward capture); ``batch_norm`` adds :func:`norms`."""
     out = dict(base if base is not None else torch.export.default_decompositions())
+    if batch_norm:
+        out = norms(out)
     if keep_attention:
         out.pop(aten.scaled_dot_product_attention.default, None)
     out[aten.linalg_matrix_exp.default] = lambda a: matrix_exp(a, max_squarings)

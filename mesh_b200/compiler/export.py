@@ -43,9 +43,40 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
                 if isinstance(node, torch.fx.Node) and hasattr(spec.arg, "name"):
                     spec.arg.name = node.name
         if loss is not None:
+            _detach_mutations(ep)
             from torch.export.experimental import _export_forward_backward
-            ep = _export_forward_backward(ep, joint_loss_index=loss)
+            # ``loss`` counts the module's own outputs; new values of mutated buffers come before them in the graph
+            users = [i for i, spec in enumerate(ep.graph_signature.output_specs) if spec.kind == OutputKind.USER_OUTPUT]
+            ep = _export_forward_backward(ep, joint_loss_index=users[loss])
     return read(ep, training=loss is not None)
+
+
+def _detach_mutations(ep) -> int:
+    """New values of mutated buffers and inputs (running statistics of a batch norm, step counters) are results of the
+    forward pass that nothing differentiates: cut them off the autograd graph, as eager mode does when it updates them
+    under ``no_grad``.  Without this the joint export refuses any forward output that requires a gradient."""
+    gm = ep.graph_module
+    out_node = next(n for n in gm.graph.nodes if n.op == "output")
+    outs = list(out_node.args[0])
+    changed = 0
+    for i, spec in enumerate(ep.graph_signature.output_specs):
+        if spec.kind not in (OutputKind.BUFFER_MUTATION, OutputKind.USER_INPUT_MUTATION):
+            continue
+        node = outs[i]
+        val = node.meta.get("val") if isinstance(node, torch.fx.Node) else None
+        if not isinstance(val, torch.Tensor) or not val.dtype.is_floating_point:
+            continue
+        with gm.graph.inserting_before(out_node):
+            cut = gm.graph.call_function(torch.ops.aten.detach.default, (node,))
+        cut.meta["val"] = val.detach()
+        outs[i] = cut
+        if hasattr(spec.arg, "name"):
+            spec.arg.name = cut.name
+        changed += 1
+    if changed:
+        out_node.args = (tuple(outs),)
+        gm.recompile()
+    return changed
 
 
 def _inline(graph, body: torch.fx.GraphModule, operands: list, before: torch.fx.Node) -> list:

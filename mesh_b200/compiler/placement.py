@@ -147,6 +147,18 @@ def _along(position: int, outs: int, default=-1):
     return describe
 
 
+def _split(position: int, removes: bool = False):
+    """Operators that cut their operand into a list of pieces along one dimension (``removes``: and drop it)."""
+    def describe(node, shapes):
+        nd = len(shapes[0])
+        dim = (node.args[position] if len(node.args) > position else node.kwargs.get("dim", 0)) % max(nd, 1)
+        info = {"batched": [True], "protect": {dim}, "outs": ["S"] * len(node.meta["val"])}
+        if removes:
+            info["out_dim"] = lambda d: d - (1 if d > dim else 0)
+        return info
+    return describe
+
+
 def _layer_norm(node, shapes):
     core = len(node.args[1])
     nd = len(shapes[0])
@@ -203,6 +215,7 @@ BATCHED = {
     aten.linalg_inv_ex.default: _trailing(2, 2), aten.linalg_lu_factor_ex.default: _trailing(2, 3),
     aten.sort.default: _along(1, 2), aten.sort.stable: _along(2, 2), aten.topk.default: _along(2, 2),
     aten.cummax.default: _along(1, 2), aten.cummin.default: _along(1, 2),
+    aten.split_with_sizes.default: _split(2), aten.split.Tensor: _split(2), aten.unbind.int: _split(1, removes=True),
     aten._native_batch_norm_legit_no_training.default: _batch_norm_inference,
     aten.convolution.default: _convolution, aten.convolution_backward.default: _convolution_backward,
     aten.native_layer_norm.default: _layer_norm, aten.native_layer_norm_backward.default: _layer_norm_backward,
@@ -356,6 +369,13 @@ class Propagator:
         if shard is None and any(partial):
             lin = LINEAR_IN.get(node.target)
             others_ok = all(s.kind in ("R", "P") for s in specs)
+            if node.target in (aten.add.Tensor, aten.sub.Tensor) and any(isinstance(a, (int, float, bool)) for a in node.args[:2]):
+                lin = None                                    # partial + constant: every processor would add the constant
+            if node.target is aten.div.Tensor and not isinstance(node.args[0], torch.fx.Node):
+                lin = None                                    # constant / partial is not linear in the partial
+            if node.target not in (aten.clone.default, aten.alias.default, aten._to_copy.default, aten.detach.default) and any(
+                    s.kind == "P" and s.op != "sum" for s in specs):
+                lin = None                                    # only sums pass through arithmetic; a pending max or min does not
             keep = False
             if lin == "all" and all(partial) and others_ok:
                 keep = True
@@ -649,6 +669,20 @@ class Propagator:
                     self.shape[n][shard.dim] == self.shape[tnames[0]][shard.dim] for n in tnames):
                 return [Spec("S", shard.dim, shard.counts, shard.striped) for _ in specs], Spec("S", shard.dim, shard.counts, shard.striped)
             return [R for _ in specs], R
+        if tgt in (aten.slice_scatter.default, aten.select_scatter.default):
+            # (whole, piece, dim, ...): a cut along any other dimension carries through both operands
+            nd = len(self.shape[tnames[0]])
+            dim = (node.args[2] if len(node.args) > 2 else node.kwargs.get("dim", 0)) % nd
+            drop = tgt is aten.select_scatter.default
+            whole, piece = specs
+            if whole.kind == "S" and whole.dim != dim and not whole.striped:
+                d = whole.dim - (1 if drop and whole.dim > dim else 0)
+                return [whole, Spec("S", d, whole.counts)], Spec("S", whole.dim, whole.counts)
+            if whole.kind == "R" and piece.kind == "S" and not piece.striped:
+                d = piece.dim + (1 if drop and piece.dim >= dim else 0)
+                if d != dim:
+                    return [Spec("S", d, piece.counts), piece], Spec("S", d, piece.counts)
+            return [R, R], R
         if tgt is aten.scaled_dot_product_attention.default:
             # q, k, v [batch, heads, tokens, head_dim]: heads (or the batch) cut the same way on all three -> local
             if len(tnames) != 3:
@@ -881,10 +915,11 @@ class Propagator:
                 return False
             found = True
             same = Spec("S", cut.dim, cut.counts, cut.striped)
+            moved = Spec("S", info["out_dim"](cut.dim), cut.counts, cut.striped) if "out_dim" in info else same
             for n, f in zip(tnames, flags):
                 wants[n].append(same if f else R)
             for o, kind in zip(out_specs, outs):
-                o.append(same if kind == "S" else R if kind == "R" else P())
+                o.append(moved if kind == "S" else R if kind == "R" else P())
         if not found:
             return False
         dims = [s.dim for s in out_specs[0] if s.kind == "S"]

@@ -405,3 +405,41 @@ def test_random_draws_do_not_depend_on_a_grid_cut():
     grid = Program(compile_module(Draws(), (x,), _procs(4), lambda nd: ((0, 1), None, (None, None)) if nd.name == "x" else None, mesh=(2, 2)))(x)
     whole = Program(compile_module(Draws(), (x,), _procs(1), lambda nd: None))(x)
     assert torch.equal(grid, whole)
+
+
+def test_recurrent_network_under_a_batch_cut():
+    """An LSTM unrolls into splits, pointwise gates and joins: every piece keeps the batch cut, gradients are summed."""
+    class Rnn(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.r, self.h = torch.nn.LSTM(8, 16, batch_first=True), torch.nn.Linear(16, 1)
+
+        def forward(self, x):
+            return self.h(self.r(x)[0]).pow(2).mean()
+
+    torch.manual_seed(17)
+    m, x = Rnn(), torch.randn(4, 5, 8)
+    procs = _procs(2)
+    sch = compile_module(m, (x,), procs, data_parallel(procs), loss=0)
+    assert sch.structure["fallbacks"] == 0 and set(sch.structure["by_verb"]) == {"all_reduce"}
+    res = Program(sch)(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
+
+
+def test_constants_meet_partial_sums_only_after_the_reduction():
+    """``sum over a cut dimension`` leaves partial sums; adding a constant, or dividing a constant by them, must wait
+    for the reduction (each processor would otherwise apply the constant to its own partial)."""
+    class Net(torch.nn.Module):
+        def forward(self, x):
+            s = x.sum(0)
+            return s + 1.0, 2.0 - s, 3.0 / (s * s + 1.0), (s * 2.0) / 4.0, x.amax(0) * -1.0
+
+    torch.manual_seed(18)
+    x = torch.randn(6, 5)
+    for n in (2, 3):
+        procs = _procs(n)
+        names = tuple(procs)
+        out = Program(compile_module(Net(), (x,), procs, lambda nd: (0, names, None) if nd.name == "x" else None))(x)
+        for got, ref in zip(out, Net()(x)):
+            assert torch.allclose(got, ref, atol=1e-6)

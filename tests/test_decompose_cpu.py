@@ -66,3 +66,32 @@ def test_capture_expands_the_operators_and_a_batch_cut_stays_local():
     out = Program(sch)(x)
     for got, ref in zip(out, m(x)):
         assert (got - ref).abs().max() < 2e-4 * max(1.0, float(ref.abs().max()))
+
+
+def test_training_batch_norm_under_a_batch_cut_uses_whole_batch_statistics():
+    import copy
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c, self.bn = torch.nn.Conv2d(4, 4, 3, padding=1), torch.nn.BatchNorm2d(4)
+
+        def forward(self, x):
+            return (x + torch.relu(self.bn(self.c(x)))).pow(2).mean()
+
+    torch.manual_seed(2)
+    m, x = Net(), torch.randn(4, 4, 8, 8)
+    ref = copy.deepcopy(m)
+    procs = {"p0": (0, "cpu"), "p1": (0, "cpu")}
+    sch = compile_module(m, (x,), procs, data_parallel(procs), loss=0, decompositions=decompose.norms())
+    assert sch.structure["fallbacks"] == 0 and "all_gather" not in sch.structure["by_verb"]
+    res = Program(sch)(x)
+    loss = ref(x)
+    loss.backward()
+    assert abs(float(res.outputs) - float(loss)) < 1e-6
+    for k, p in ref.named_parameters():
+        assert torch.allclose(res.parameters[k], p.grad, atol=1e-5), k
+    # the running statistics were stored into the module's own buffers, once
+    assert torch.allclose(m.bn.running_mean, ref.bn.running_mean, atol=1e-6)
+    assert torch.allclose(m.bn.running_var, ref.bn.running_var, atol=1e-6)
+    assert int(m.bn.num_batches_tracked) == int(ref.bn.num_batches_tracked) == 1
