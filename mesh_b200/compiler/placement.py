@@ -648,9 +648,24 @@ class Propagator:
             return [s], s
         if tgt in REDUCTIONS:
             return self.rule_reduce(node, tnames, specs, ax, meta)
+        if tgt in (aten.argmax.default, aten.argmin.default, aten.logsumexp.default):
+            # reductions with no partial form: local when the cut is along a dimension that stays
+            s = specs[0]
+            nd = len(self.shape[tnames[0]])
+            dims = node.args[1] if len(node.args) > 1 else None
+            keep = bool(node.args[2]) if len(node.args) > 2 else False
+            if dims is None:
+                return [R], R
+            dims = sorted(d % nd for d in (dims if isinstance(dims, (list, tuple)) else [dims]))
+            if s.kind != "S":
+                return ([s], s) if s.kind == "R" else ([R], R)
+            if s.dim in dims:
+                return [R], R
+            out_dim = s.dim if keep else s.dim - sum(1 for d in dims if d < s.dim)
+            return [s], Spec("S", out_dim, s.counts, s.striped)
         if tgt in SOFTMAX_LIKE:
             pos = SOFTMAX_LIKE[tgt]
-            nd = len(_shape(node)) or len(self.shape[tnames[0]])
+            nd = len(self.shape[tnames[0]])
             dim = node.args[pos] if len(node.args) > pos else -1
             dim = dim % max(nd, 1)
             shard = next((s for s in specs if s.kind == "S"), None)

@@ -1,0 +1,125 @@
+"""Many small operator graphs under several cuts: whatever the rules decide, results equal the unsharded module."""
+import pytest
+import torch
+
+from mesh_b200.compiler import Program, compile_module
+
+F = torch.nn.functional
+CASES = {
+ "softmax_cut_dim": lambda x: torch.softmax(x, 0),
+ "logsumexp": lambda x: torch.logsumexp(x, 0) + torch.logsumexp(x, 1).sum(),
+ "max_vals": lambda x: x.max(0).values + x.min(1).values.sum(),
+ "argmax": lambda x: x.argmax(0).float() + x.argmax(1).float().sum(),
+ "cumsum": lambda x: x.cumsum(0) + x.cumsum(1),
+ "var": lambda x: x.var(0) + x.std(1).sum(),
+ "norm": lambda x: x.norm(dim=0) + x.norm(),
+ "mean_mul": lambda x: x.mean(0) * x.mean(1).sum() + x.mean(),
+ "prod": lambda x: (x * 0.1 + 1).prod(0),
+ "matmul_t": lambda x: x.T @ x + (x @ x.T).sum(),
+ "where": lambda x: torch.where(x > 0, x, x * 0.1).sum(0) + 1,
+ "clamp_sum": lambda x: x.clamp(min=0).sum(0).sqrt() + 1e-3,
+ "amax_neg": lambda x: -x.amax(0) + (x.amax(0) + 1) * 2,
+ "sort": lambda x: x.sort(0).values + x.sort(1).values,
+ "topk": lambda x: x.topk(2, 0).values.sum(0) + x.topk(2, 1).values.sum(1).sum(),
+ "flip_roll": lambda x: x.flip(0) + x.roll(1, 0) + x.flip(1),
+ "pad": lambda x: F.pad(x, (1, 1, 2, 0)).sum(0),
+ "index": lambda x: x[torch.tensor([0, 2, 1])].sum(0) + x[:, torch.tensor([1, 0])].sum(),
+ "expand_bcast": lambda x: (x[:, None, :] * x[None, :, :]).sum((0, 2)),
+ "layer_norm": lambda x: F.layer_norm(x, (x.shape[1],)) + F.layer_norm(x.T, (x.shape[0],)).T,
+ "einsum": lambda x: torch.einsum("ij,kj->ik", x, x).sum(1) + torch.einsum("ij,ik->jk", x, x).sum(),
+ "div_const": lambda x: 1.0 / (x.sum(0).abs() + 1) + (x.sum(0) / 3),
+ "any_all": lambda x: (x > 0).any(0).float() + (x > -5).all(0).float(),
+ "mse": lambda x: F.mse_loss(x, x.flip(0)) + F.l1_loss(x, torch.zeros_like(x)),
+ "tril": lambda x: torch.tril(x @ x.T).sum(0),
+ "gather": lambda x: x.gather(1, x.argsort(1)) .sum(0) + x.gather(0, x.argsort(0)).sum(),
+ "repeat": lambda x: x.repeat(2, 1).sum(0) + x.repeat_interleave(2, 0).sum(0),
+ "stack_cat": lambda x: torch.stack([x, x * 2]).sum((0, 1)) + torch.cat([x, x], 0).sum(0) + torch.cat([x, x], 1).sum(),
+ "count": lambda x: (x > 0).sum(0).float() / x.shape[0] + (x > 0).float().mean(),
+}
+
+CUTS = [(2, 0, None), (2, 1, None), (3, 0, "striped"), (2, 0, (2, 1))]
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_operator_graph_matches_eager_under_every_cut(name):
+    fn = CASES[name]
+
+    class Net(torch.nn.Module):
+        def forward(self, x):
+            return fn(x)
+
+    torch.manual_seed(0)
+    x = torch.randn(6, 4)
+    ref = fn(x)
+    for n, dim, units in CUTS:
+        procs = {f"p{i}": (0, "cpu") for i in range(n)}
+        names = tuple(procs)
+        sch = compile_module(Net(), (x,), procs, lambda nd: (dim, names, units) if nd.name == "x" else None)
+        out = Program(sch)(x)
+        assert out.shape == ref.shape, (n, dim, units)
+        assert torch.allclose(out.float(), ref.float(), atol=1e-4), (n, dim, units, sch.structure["fallbacks"])
+
+
+# ---- training graphs: fn(x [6, 4], w [4, 5], v [5]) -> loss; the data and / or the weight are cut
+TRAINING = {
+ "linear_relu": lambda x, w, v: (torch.relu(x @ w) * v).sum(),
+ "softmax_ce": lambda x, w, v: F.cross_entropy((x @ w) * v, torch.arange(6) % 5),
+ "mean_var": lambda x, w, v: ((x @ w).var(0) * v).sum() + (x @ w).mean(),
+ "norm_rows": lambda x, w, v: F.normalize(x @ w, dim=1).mul(v).sum(),
+ "norm_cols": lambda x, w, v: F.normalize(x @ w, dim=0).mul(v).sum(),
+ "max_pool_rows": lambda x, w, v: (x @ w).max(0).values.dot(v),
+ "logsumexp0": lambda x, w, v: torch.logsumexp(x @ w, 0).dot(v),
+ "layernorm": lambda x, w, v: F.layer_norm(x @ w, (5,), v, v * 0.5).pow(2).mean(),
+ "gelu_dropout0": lambda x, w, v: F.dropout(F.gelu(x @ w), 0.0).sum() + v.sum(),
+ "bilinear": lambda x, w, v: ((x @ w) * (x @ w).flip(0)).sum() * v.mean(),
+ "tanh_chain": lambda x, w, v: torch.tanh(torch.tanh(x @ w) @ w.T @ w).mean() + (v * v).sum(),
+ "cumsum_rows": lambda x, w, v: (x @ w).cumsum(0).mul(v).mean(),
+ "weight_norm": lambda x, w, v: (x @ (w / w.norm(dim=0, keepdim=True))).pow(2).sum() + v.norm(),
+ "embedding": lambda x, w, v: F.embedding(torch.arange(6) % 4, w).mul(v).sum() + (x * 0).sum(),
+ "mse_target": lambda x, w, v: F.mse_loss(x @ w, torch.ones(6, 5)) + F.smooth_l1_loss((x @ w) * v, torch.zeros(6, 5)),
+ "outer": lambda x, w, v: torch.einsum("bi,bj->ij", x, x @ w).mul(w).sum() + v.sum(),
+ "where_mask": lambda x, w, v: torch.where((x @ w) > 0, x @ w, 0.1 * (x @ w)).mul(v).mean(),
+ "sort_vals": lambda x, w, v: (x @ w).sort(0).values[-2:].mul(v).sum(),
+ "exp_sum_div": lambda x, w, v: ((x @ w).exp() / ((x @ w).exp().sum(0) + 1.0)).mul(v).sum(),
+}
+
+TRAINING_CUTS = [(2, (0, None), None), (3, (0, "striped"), None), (2, None, (1, None)), (2, (0, None), (1, None)), (2, (1, None), (0, None))]
+
+
+@pytest.mark.parametrize("name", sorted(TRAINING))
+def test_training_graph_loss_and_gradients_match_eager_under_every_cut(name):
+    fn = TRAINING[name]
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            g = torch.Generator().manual_seed(1)
+            self.w = torch.nn.Parameter(torch.randn(4, 5, generator=g))
+            self.v = torch.nn.Parameter(torch.randn(5, generator=g))
+
+        def forward(self, x):
+            return fn(x, self.w, self.v)
+
+    torch.manual_seed(0)
+    x = torch.randn(6, 4)
+    ref = Net()
+    loss = ref(x)
+    loss.backward()
+    for n, xcut, wcut in TRAINING_CUTS:
+        procs = {f"p{i}": (0, "cpu") for i in range(n)}
+        names = tuple(procs)
+
+        def placement(nd):
+            if nd.op != "placeholder":
+                return None
+            if nd.name == "x" and xcut:
+                return (xcut[0], names, xcut[1])
+            if nd.name == "p_w" and wcut:
+                return (wcut[0], names, wcut[1])
+            return None
+        res = Program(compile_module(Net(), (x,), procs, placement, loss=0), threads=True)(x)
+        assert abs(float(res.outputs) - float(loss)) < 1e-4, (n, xcut, wcut)
+        gw = res.parameters["w"]
+        want = ref.w.grad if gw.shape == ref.w.grad.shape else ref.w.grad.narrow(wcut[0], 0, gw.shape[wcut[0]])   # processor 0's shard
+        assert torch.allclose(gw, want, atol=1e-4), (n, xcut, wcut)
+        assert torch.allclose(res.parameters["v"], ref.v.grad, atol=1e-4), (n, xcut, wcut)
