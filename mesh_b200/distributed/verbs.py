@@ -56,8 +56,16 @@ def all_gather(t: torch.Tensor, dim: int = 0, counts: list[int] | None = None, g
     elif len(set(counts)) == 1:
         dist.all_gather_into_tensor(out, tt, group=group)
     else:
-        parts = list(out.split(counts, 0))
-        dist.all_gather(parts, tt, group=group)
+        # library back ends want equal blocks: pad every block to the largest, gather, keep each rank's own rows
+        top = max(counts)
+        padded = tt.new_zeros((top, *tt.shape[1:]))
+        padded[: tt.shape[0]] = tt
+        blocks = tt.new_empty((W * top, *tt.shape[1:]))
+        dist.all_gather_into_tensor(blocks, padded, group=group)
+        at = 0
+        for r, n in enumerate(counts):
+            out[at:at + n] = blocks[r * top:r * top + n]
+            at += n
     return out.movedim(0, dim)
 
 
@@ -78,7 +86,19 @@ def reduce_scatter(t: torch.Tensor, dim: int = 0, op: str = "sum", counts: list[
     elif len(set(counts)) == 1:
         dist.reduce_scatter_tensor(out, tt, _RED[op], group=group)
     else:
-        dist.reduce_scatter(out, [p.contiguous() for p in tt.split(counts, 0)], _RED[op], group=group)
+        # unequal segments: pad each to the largest with the reduction's identity, reduce-scatter equal blocks, trim
+        top = max(counts)
+        fill = 0 if op == "sum" else (float("-inf") if op == "max" else float("inf"))
+        if not tt.dtype.is_floating_point and op != "sum":
+            fill = torch.iinfo(tt.dtype).min if op == "max" else torch.iinfo(tt.dtype).max
+        blocks = tt.new_full((W * top, *tt.shape[1:]), fill)
+        at = 0
+        for r, n in enumerate(counts):
+            blocks[r * top:r * top + n] = tt[at:at + n]
+            at += n
+        mine = tt.new_empty((top, *tt.shape[1:]))
+        dist.reduce_scatter_tensor(mine, blocks, _RED[op], group=group)
+        out.copy_(mine[: counts[rank]])
     return out.movedim(0, dim)
 
 

@@ -123,3 +123,52 @@ def test_training_graph_loss_and_gradients_match_eager_under_every_cut(name):
         want = ref.w.grad if gw.shape == ref.w.grad.shape else ref.w.grad.narrow(wcut[0], 0, gw.shape[wcut[0]])   # processor 0's shard
         assert torch.allclose(gw, want, atol=1e-4), (n, xcut, wcut)
         assert torch.allclose(res.parameters["v"], ref.v.grad, atol=1e-4), (n, xcut, wcut)
+
+
+def _dist_rank(rank, world, rdv):
+    """One process per processor (gloo): unequal cuts, which need per-rank counts in every collective."""
+    torch.manual_seed(0)
+    x = torch.randn(6, 4)
+    procs = {f"p{i}": (0, "cpu") for i in range(world)}
+    names = tuple(procs)
+    for name, fn in CASES.items():
+        class Net(torch.nn.Module):
+            def forward(self, x):
+                return fn(x)
+        out = Program(compile_module(Net(), (x,), procs, lambda nd: (0, names, (2, 1)) if nd.name == "x" else None))(x)
+        if out is not None:
+            assert torch.allclose(out.float(), fn(x).float(), atol=1e-4), name
+    for name in ("linear_relu", "layernorm", "sort_vals", "exp_sum_div", "outer"):
+        fn = TRAINING[name]
+
+        class Train(torch.nn.Module):
+            def __init__(self):
+                super().__init__()
+                g = torch.Generator().manual_seed(1)
+                self.w = torch.nn.Parameter(torch.randn(4, 5, generator=g))
+                self.v = torch.nn.Parameter(torch.randn(5, generator=g))
+
+            def forward(self, x):
+                return fn(x, self.w, self.v)
+        ref = Train()
+        loss = ref(x)
+        loss.backward()
+        for xcut, wcut in (((0, None), (1, None)), (None, (1, None))):           # the weight's 5 columns: 3 + 2
+
+            def placement(nd):
+                if nd.op != "placeholder":
+                    return None
+                if nd.name == "x" and xcut:
+                    return (xcut[0], names, xcut[1])
+                return (wcut[0], names, wcut[1]) if nd.name == "p_w" else None
+            res = Program(compile_module(Train(), (x,), procs, placement, loss=0))(x)
+            assert abs(float(res.outputs) - float(loss)) < 1e-4, name
+            gw = res.parameters["w"]
+            start = 0 if rank == 0 else 3
+            assert torch.allclose(gw, ref.w.grad[:, start:start + gw.shape[1]], atol=1e-4), name
+            assert torch.allclose(res.parameters["v"], ref.v.grad, atol=1e-4), name
+
+
+def test_one_process_per_processor_with_unequal_cuts():
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_dist_rank, 2, init_pg="gloo", timeout=900)
