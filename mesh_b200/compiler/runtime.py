@@ -590,6 +590,13 @@ class Program(Arguments):
 
     def _result(self, flat, ex, bound, all_results=None):
         exp = self.exported
+        if all_results is not None:
+            # the threaded interpreter sees every processor: a value that lives on another processor (a gradient of a
+            # layer placed there) is taken from its owner instead of being reported as absent
+            flat = list(flat)
+            for i, v in enumerate(flat):
+                if v is None:
+                    flat[i] = next((r[1][i] for r in all_results if r is not None and r[1][i] is not None), None)
         # in-place stores of buffer / input mutations
         for i, ph in exp.mutations.items():
             if flat[i] is not None and isinstance(bound.get(ph), torch.Tensor):

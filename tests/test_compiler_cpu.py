@@ -443,3 +443,33 @@ def test_constants_meet_partial_sums_only_after_the_reduction():
         out = Program(compile_module(Net(), (x,), procs, lambda nd: (0, names, None) if nd.name == "x" else None))(x)
         for got, ref in zip(out, Net()(x)):
             assert torch.allclose(got, ref, atol=1e-6)
+
+
+def test_layers_on_different_processors_forward_and_backward():
+    """A processor name per layer (a pipeline by placement): activations and their gradients go point to point, every
+    gradient is reported from the processor that owns its layer."""
+    class MLP(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b, self.c = torch.nn.Linear(8, 16), torch.nn.Linear(16, 16), torch.nn.Linear(16, 4)
+
+        def forward(self, x):
+            return self.c(torch.relu(self.b(torch.relu(self.a(x))))).pow(2).mean()
+
+    def placement(node):
+        if node.op == "placeholder":
+            if node.name == "x" or "p_a_" in node.name or "p_b_" in node.name:
+                return "p0"
+            return "p1" if "p_c_" in node.name else None
+        quals = [q for _, (q, _) in (node.meta.get("nn_module_stack") or {}).items()]
+        return "p1" if "c" in quals else "p0" if ("a" in quals or "b" in quals) else None
+
+    torch.manual_seed(19)
+    m, x = MLP(), torch.randn(6, 8)
+    sch = compile_module(m, (x,), _procs(2), placement, loss=0)
+    assert sch.structure["fallbacks"] == 0 and sch.structure["by_verb"]["send_recv"] >= 2
+    assert "all_reduce" not in sch.structure["by_verb"] and "all_gather" not in sch.structure["by_verb"]
+    res = Program(sch)(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
+    assert set(res.parameters) == set(grads) and all(g is not None for g in res.parameters.values())
