@@ -545,7 +545,8 @@ class Propagator:
                     break
                 w, o = res
                 for n, s in zip(tnames, w):
-                    wants[n].append(s)
+                    if len(wants[n]) <= ax:                  # an operand used twice (x * x) states its want once
+                        wants[n].append(s)
                 out_specs.append(o)
         if handled:
             # two axes must not shard the same tensor dimension of the output
@@ -800,7 +801,8 @@ class Propagator:
             if sp is None:
                 out_spec.append(R)
                 for n in names:
-                    wants[n].append(R)
+                    if len(wants[n]) <= a:
+                        wants[n].append(R)
                 continue
             if not stack and sp.dim == dim:
                 return False
@@ -810,7 +812,8 @@ class Propagator:
                     return False
                 if o.kind == "S" and (o.dim != sp.dim or o.counts != sp.counts or o.striped != sp.striped):
                     return False
-                wants[n].append(Spec("S", sp.dim, sp.counts, sp.striped))      # a whole copy gives up all but its own rows
+                if len(wants[n]) <= a:
+                    wants[n].append(Spec("S", sp.dim, sp.counts, sp.striped))      # a whole copy gives up all but its own rows
             d = sp.dim + 1 if (stack and sp.dim >= dim) else sp.dim
             out_spec.append(Spec("S", d, sp.counts, sp.striped))
         if all(s.kind == "R" for s in out_spec):
@@ -862,7 +865,8 @@ class Propagator:
                 if any(o.kind != "R" for o in others):
                     return False
                 for n in tnames:
-                    wants[n].append(R)
+                    if len(wants[n]) <= ax:
+                        wants[n].append(R)
                 spec_in.append(R)
                 spec_out.append(R)
                 continue
@@ -877,9 +881,11 @@ class Propagator:
                 small = Spec("S", sp.dim, tuple(c // kernel[i] for c in sp.counts))
             found = True
             for n in ins:
-                wants[n].append(sp)
+                if len(wants[n]) <= ax:
+                    wants[n].append(sp)
             for n in outs:
-                wants[n].append(small)
+                if len(wants[n]) <= ax:
+                    wants[n].append(small)
             spec_in.append(sp)
             spec_out.append(small)
         if not found:
@@ -921,7 +927,8 @@ class Propagator:
                 if any(s.kind != "R" for s in specs):
                     return False                            # an unbatched operand is cut: the generic path gathers it
                 for n in tnames:
-                    wants[n].append(R)
+                    if len(wants[n]) <= ax:
+                        wants[n].append(R)
                 for o in out_specs:
                     o.append(R)
                 continue
@@ -932,7 +939,8 @@ class Propagator:
             same = Spec("S", cut.dim, cut.counts, cut.striped)
             moved = Spec("S", info["out_dim"](cut.dim), cut.counts, cut.striped) if "out_dim" in info else same
             for n, f in zip(tnames, flags):
-                wants[n].append(same if f else R)
+                if len(wants[n]) <= ax:
+                    wants[n].append(same if f else R)
             for o, kind in zip(out_specs, outs):
                 o.append(moved if kind == "S" else R if kind == "R" else P())
         if not found:

@@ -172,3 +172,45 @@ def _dist_rank(rank, world, rdv):
 def test_one_process_per_processor_with_unequal_cuts():
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_dist_rank, 2, init_pg="gloo", timeout=900)
+
+
+GRIDS = [((0, None), (None, 1)), ((None, 0), (1, None)), ((0, 1), (None, None))]      # (cut of x, cut of w) per grid axis
+
+
+@pytest.mark.parametrize("name", sorted(TRAINING))
+def test_training_graph_on_a_two_by_two_grid(name):
+    fn = TRAINING[name]
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            g = torch.Generator().manual_seed(1)
+            self.w = torch.nn.Parameter(torch.randn(4, 5, generator=g))
+            self.v = torch.nn.Parameter(torch.randn(5, generator=g))
+
+        def forward(self, x):
+            return fn(x, self.w, self.v)
+
+    torch.manual_seed(0)
+    x = torch.randn(6, 4)
+    ref = Net()
+    loss = ref(x)
+    loss.backward()
+    procs = {f"p{i}": (0, "cpu") for i in range(4)}
+    for xd, wd in GRIDS:
+        def placement(nd):
+            if nd.op != "placeholder":
+                return None
+            if nd.name == "x" and any(d is not None for d in xd):
+                return (xd, None, (None, None))
+            if nd.name == "p_w" and any(d is not None for d in wd):
+                return (wd, None, (None, None))
+            return None
+        res = Program(compile_module(Net(), (x,), procs, placement, loss=0, mesh=(2, 2)), threads=True)(x)
+        assert abs(float(res.outputs) - float(loss)) < 1e-4, (xd, wd)
+        assert torch.allclose(res.parameters["v"], ref.v.grad, atol=1e-4), (xd, wd)
+        gw, want = res.parameters["w"], ref.w.grad
+        for d in range(2):                                       # processor 0 holds the first block of a cut weight
+            if gw.shape[d] != want.shape[d]:
+                want = want.narrow(d, 0, gw.shape[d])
+        assert torch.allclose(gw, want, atol=1e-4), (xd, wd)
