@@ -214,3 +214,49 @@ def test_training_graph_on_a_two_by_two_grid(name):
             if gw.shape[d] != want.shape[d]:
                 want = want.narrow(d, 0, gw.shape[d])
         assert torch.allclose(gw, want, atol=1e-4), (xd, wd)
+
+
+# ---- views and batched products of a [4, 6, 8] tensor
+VIEWS = {
+ "merge01": lambda x: x.reshape(24, 8).sum(0),
+ "merge12": lambda x: x.reshape(4, 48).sum(1),
+ "split2": lambda x: x.reshape(4, 6, 2, 4).sum((1, 3)),
+ "split0": lambda x: x.reshape(2, 2, 6, 8).sum((0, 2)),
+ "split1": lambda x: x.reshape(4, 3, 2, 8).sum((2,)),
+ "flatten_all": lambda x: x.reshape(-1).cumsum(0)[-1:],
+ "transpose_merge": lambda x: x.transpose(0, 1).reshape(6, 32).sum(1),
+ "permute_merge": lambda x: x.permute(2, 0, 1).reshape(8, 24) @ torch.ones(24, 3),
+ "heads": lambda x: x.reshape(4, 6, 2, 4).transpose(1, 2).reshape(8, 6, 4).sum((1, 2)),
+ "bmm": lambda x: torch.bmm(x, x.transpose(1, 2)).sum((1, 2)),
+ "bmm_merge": lambda x: torch.bmm(x, x.transpose(1, 2)).reshape(24, 6).sum(1),
+ "unsqueeze_expand": lambda x: x.unsqueeze(1).expand(4, 3, 6, 8).reshape(12, 48).sum(1),
+ "squeeze": lambda x: x[:, :1].squeeze(1) + x.sum(1),
+ "select": lambda x: x[:, 2] + x[1].sum(0) + x[..., 3].sum(),
+ "narrow": lambda x: x[:, 1:4].sum(1) + x[1:3].sum((0, 1)) ,
+ "chunk": lambda x: sum(c.sum(1) for c in x.chunk(3, 1)) + sum(c.sum() for c in x.chunk(2, 0)),
+ "unfold_like": lambda x: x.reshape(4, 2, 3, 8)[:, :, 1:].reshape(4, 4, 8).sum(1),
+ "movedim": lambda x: x.movedim(0, 2).contiguous().view(48, 4).sum(0),
+ "linear3d": lambda x: torch.nn.functional.linear(x, torch.ones(5, 8)).sum(1),
+ "mean_dims": lambda x: x.mean((0, 2)) + x.mean(1).sum(),
+ "softmax3d": lambda x: torch.softmax(x, 1).sum(2).sum(1) + torch.softmax(x, 2).sum(1).sum(1) + torch.softmax(x, 0).sum((1, 2)),
+}
+
+VIEW_CUTS = [(2, 0, None), (2, 2, None), (3, 1, "striped"), (2, 1, (1, 2))]
+
+
+@pytest.mark.parametrize("name", sorted(VIEWS))
+def test_views_of_a_cut_tensor_match_eager(name):
+    fn = VIEWS[name]
+
+    class Net(torch.nn.Module):
+        def forward(self, x):
+            return fn(x)
+
+    torch.manual_seed(0)
+    x = torch.randn(4, 6, 8)
+    ref = fn(x)
+    for n, dim, units in VIEW_CUTS:
+        procs = {f"p{i}": (0, "cpu") for i in range(n)}
+        names = tuple(procs)
+        out = Program(compile_module(Net(), (x,), procs, lambda nd: (dim, names, units) if nd.name == "x" else None))(x)
+        assert out.shape == ref.shape and torch.allclose(out, ref, atol=1e-4), (n, dim, units)
