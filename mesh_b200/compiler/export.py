@@ -43,24 +43,25 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
                 if isinstance(node, torch.fx.Node) and hasattr(spec.arg, "name"):
                     spec.arg.name = node.name
         if loss is not None:
-            _detach_mutations(ep)
             from torch.export.experimental import _export_forward_backward
             # ``loss`` counts the module's own outputs; new values of mutated buffers come before them in the graph
             users = [i for i, spec in enumerate(ep.graph_signature.output_specs) if spec.kind == OutputKind.USER_OUTPUT]
+            _detach_mutations(ep, keep=users[loss])
             ep = _export_forward_backward(ep, joint_loss_index=users[loss])
     return read(ep, training=loss is not None)
 
 
-def _detach_mutations(ep) -> int:
-    """New values of mutated buffers and inputs (running statistics of a batch norm, step counters) are results of the
-    forward pass that nothing differentiates: cut them off the autograd graph, as eager mode does when it updates them
-    under ``no_grad``.  Without this the joint export refuses any forward output that requires a gradient."""
+def _detach_mutations(ep, keep: int | None = None) -> int:
+    """New values of mutated buffers and inputs (running statistics of a batch norm, step counters) and outputs other
+    than the loss (output ``keep``) are results of the forward pass that nothing differentiates: cut them off the
+    autograd graph, as eager mode does when it updates buffers under ``no_grad``.  Without this the joint export
+    refuses any forward output that requires a gradient."""
     gm = ep.graph_module
     out_node = next(n for n in gm.graph.nodes if n.op == "output")
     outs = list(out_node.args[0])
     changed = 0
     for i, spec in enumerate(ep.graph_signature.output_specs):
-        if spec.kind not in (OutputKind.BUFFER_MUTATION, OutputKind.USER_INPUT_MUTATION):
+        if i == keep or spec.kind not in (OutputKind.BUFFER_MUTATION, OutputKind.USER_INPUT_MUTATION, OutputKind.USER_OUTPUT):
             continue
         node = outs[i]
         val = node.meta.get("val") if isinstance(node, torch.fx.Node) else None
