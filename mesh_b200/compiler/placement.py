@@ -708,6 +708,10 @@ class Propagator:
             if q.kind == "S" and q.dim in (0, 1) and not q.striped and (q.dim == 0 or same_heads):
                 want = Spec("S", q.dim, q.counts)
                 return [want, want, want], want
+            causal = node.kwargs.get("is_causal", node.args[5] if len(node.args) > 5 else False)
+            if q.kind == "S" and q.dim == 2 and not causal and all(s.kind in ("R", "S") for s in specs[1:]):
+                # queries are independent of each other: keep them cut, hold all keys and values
+                return [Spec("S", 2, q.counts, q.striped), R, R], Spec("S", 2, q.counts, q.striped)
             kv = next((s for s in specs[1:] if s.kind == "S" and s.dim in (0, 1) and not s.striped), None)
             if q.kind == "R" and kv is not None and (kv.dim == 0 or same_heads):
                 want = Spec("S", kv.dim, kv.counts)

@@ -260,3 +260,24 @@ def test_views_of_a_cut_tensor_match_eager(name):
         names = tuple(procs)
         out = Program(compile_module(Net(), (x,), procs, lambda nd: (dim, names, units) if nd.name == "x" else None))(x)
         assert out.shape == ref.shape and torch.allclose(out, ref, atol=1e-4), (n, dim, units)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_whole_attention_under_every_cut(causal):
+    """Inference graphs keep attention as one operator: heads or batch cut -> local; queries cut along the sequence ->
+    local when not causal; anything else gathers.  Every combination equals the unsharded result."""
+    class Attn(torch.nn.Module):
+        def forward(self, q, k, v):
+            return F.scaled_dot_product_attention(q, k, v, is_causal=causal)
+
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(2, 4, 6, 8) for _ in range(3))
+    ref = Attn()(q, k, v)
+    for n, dim, units in ((2, 0, None), (2, 1, None), (2, 2, None), (3, 2, "striped"), (2, 3, None)):
+        procs = {f"p{i}": (0, "cpu") for i in range(n)}
+        names = tuple(procs)
+        for which in (("q", "k", "v"), ("q",), ("k", "v")):
+            sch = compile_module(Attn(), (q, k, v), procs, lambda nd: (dim, names, units) if nd.name in which else None)
+            assert torch.allclose(Program(sch)(q, k, v), ref, atol=1e-5), (n, dim, units, which)
+            if dim in (0, 1) and which == ("q", "k", "v"):
+                assert sch.structure["by_verb"] == {"all_gather": 1}          # only the result is brought together
