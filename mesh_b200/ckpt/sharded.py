@@ -113,9 +113,17 @@ def load_sharded(directory, step: int | None, rank: int, world: int, new_layout:
             out[name] = shard_of(0)[name].to(device)
             continue
         total = sum(old_counts)
+        dtype = getattr(torch, str(meta.get("dtype", "torch.float32")).split(".")[-1])
         if new_layout and name in new_layout:
             ndim, ncounts = new_layout[name]
-            assert ndim == dim, "resharding along another dimension goes through a full gather"
+            if ndim != dim:
+                # another dimension (or none: replicated): put the old shards together, then take the new slice
+                whole = torch.cat([shard_of(r)[name] for r in range(old_world) if old_counts[r]], dim=dim)
+                if ndim is None:
+                    out[name] = whole.to(device)
+                else:
+                    out[name] = whole.narrow(ndim, sum(ncounts[:rank]), ncounts[rank]).contiguous().to(device)
+                continue
         else:
             ncounts = chunk_counts(total, None, world)
         lo = sum(ncounts[:rank])
@@ -132,5 +140,5 @@ def load_sharded(directory, step: int | None, rank: int, world: int, new_layout:
         else:
             shape = list(meta["shape"])
             shape[dim] = 0
-            out[name] = torch.empty(shape, device=device)
+            out[name] = torch.empty(shape, dtype=dtype, device=device)
     return out, index.get("extra", {})

@@ -44,3 +44,32 @@ def test_sharded_adamw_matches_torch():
     opt2 = ShardedAdamW([torch.nn.Parameter(p.detach().clone())], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
     opt2.load_state_dict(sd)
     assert opt2.step_no == 5 and torch.equal(opt2.state[0]["m"], opt.state[0]["m"])
+
+
+def test_reshard_round_trips_over_random_layouts(tmp_path):
+    """Any old world and cut to any new world and cut (same dimension, another dimension, or replicated), with unequal
+    shares and shards of size zero, gives back the same bytes and dtypes."""
+    import random
+    from mesh_b200.ckpt.sharded import load_sharded, save_sharded
+    from mesh_b200.compiler.placement import counts
+    random.seed(0)
+    torch.manual_seed(0)
+    for trial in range(25):
+        shape = [random.randint(1, 7) for _ in range(random.randint(1, 3))]
+        full = torch.randn(*shape).to(random.choice([torch.float32, torch.bfloat16]))
+        ids = torch.arange(shape[0] * 2).reshape(shape[0], 2)
+        ow, nw = random.randint(1, 5), random.randint(1, 5)
+        dim = random.randrange(len(shape))
+        oc = counts(shape[dim], random.choice([None, [random.randint(1, 4) for _ in range(ow)]]), ow)
+        ic = counts(shape[0], None, ow)
+        d = tmp_path / f"t{trial}"
+        for r in range(ow):
+            local = {"a": full.narrow(dim, sum(oc[:r]), oc[r]), "i": ids.narrow(0, sum(ic[:r]), ic[r]), "r": full.flatten()[:1]}
+            save_sharded(d, 1, local, {"a": (dim, oc), "i": (0, ic), "r": (None, None)}, r, ow)
+        ndim = random.choice([dim, dim, random.randrange(len(shape)), None])
+        nc = counts(shape[ndim], random.choice([None, [random.randint(1, 4) for _ in range(nw)]]), nw) if ndim is not None else None
+        parts = [load_sharded(d, None, r, nw, {"a": (ndim, nc)})[0] for r in range(nw)]
+        got = torch.cat([p["a"] for p in parts], ndim) if ndim is not None else parts[-1]["a"]
+        assert got.dtype == full.dtype and torch.equal(got, full), (shape, ow, nw, dim, ndim, oc, nc)
+        assert torch.equal(torch.cat([p["i"] for p in parts], 0), ids) and parts[0]["i"].dtype == torch.int64
+        assert all(torch.equal(p["r"], full.flatten()[:1]) for p in parts)
