@@ -48,7 +48,10 @@ def save_sharded(directory, step: int, local: dict, layout: dict, rank: int, wor
         dim, _ = layout[name]
         if dim is None and rank != 0:
             continue
-        tensors[name] = t.detach().contiguous().cpu()
+        t = t.detach().contiguous().cpu()
+        if t.untyped_storage().nbytes() != t.numel() * t.element_size():
+            t = t.clone()                      # a view into a larger storage: the file format wants tensors of their own
+        tensors[name] = t
     tmp = d / f"rank{rank}.safetensors.tmp"
     save_file(tensors, str(tmp))
     os.replace(tmp, d / f"rank{rank}.safetensors")
