@@ -43,14 +43,15 @@ def save_sharded(directory, step: int, local: dict, layout: dict, rank: int, wor
             j.write(json.dumps({"event": "begin", "step": step, "world": world}) + "\n")
             j.flush()
             os.fsync(j.fileno())
-    tensors = {}
+    tensors, seen = {}, set()
     for name, t in local.items():
         dim, _ = layout[name]
         if dim is None and rank != 0:
             continue
         t = t.detach().contiguous().cpu()
-        if t.untyped_storage().nbytes() != t.numel() * t.element_size():
-            t = t.clone()                      # a view into a larger storage: the file format wants tensors of their own
+        if t.untyped_storage().nbytes() != t.numel() * t.element_size() or t.untyped_storage().data_ptr() in seen:
+            t = t.clone()                      # a view, or a second name for the same bytes: the file format wants tensors of their own
+        seen.add(t.untyped_storage().data_ptr())
         tensors[name] = t
     tmp = d / f"rank{rank}.safetensors.tmp"
     save_file(tensors, str(tmp))
