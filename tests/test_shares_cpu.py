@@ -103,3 +103,69 @@ def test_coupled_share_solve_matches_a_reference_lp_solver():
             if ref.status == 0: bad += 1; print("we failed", trial, e, ref.fun)
 
     assert bad == 0
+
+
+def test_allocator_helpers_against_brute_force():
+    """Ragged-row separators and equal-finish shares are optimal on small random instances; capacity repair keeps the
+    total and respects every cap."""
+    import itertools
+    import random
+    from fractions import Fraction
+    from mesh_b200.runtime.allocate import equal_finish, separators, shift
+    random.seed(0)
+    bad = 0
+    # separators vs brute force
+    for t in range(100):
+        rows = random.randint(1, 9); P = random.randint(1, 4)
+        lens = [random.randint(0, 9) for _ in range(rows)]
+        offsets = [0]
+        for l in lens: offsets.append(offsets[-1] + l)
+        speeds = [random.randint(1, 4) for _ in range(P)]
+        try:
+            cuts = separators(offsets, speeds)
+        except Exception as e:
+            bad += 1; print("sep fail", offsets, speeds, type(e).__name__, e); continue
+        ok = cuts[0] == 0 and cuts[-1] == rows and all(a <= b for a, b in zip(cuts, cuts[1:])) and len(cuts) == P + 1
+        if not ok: bad += 1; print("sep invalid", offsets, speeds, cuts); continue
+        mine = max(Fraction(offsets[cuts[j + 1]] - offsets[cuts[j]], speeds[j]) for j in range(P))
+        best = None
+        for c in itertools.combinations_with_replacement(range(rows + 1), P - 1):
+            cc = [0, *c, rows]
+            v = max(Fraction(offsets[cc[j + 1]] - offsets[cc[j]], speeds[j]) for j in range(P))
+            best = v if best is None else min(best, v)
+        if mine != best: bad += 1; print("sep subopt", offsets, speeds, cuts, mine, best)
+    # equal_finish: sums, bounds, grain; near-optimal vs brute force on small totals
+    for t in range(100):
+        n = random.randint(1, 4); grain = random.choice([1, 2, 4])
+        low = [grain * random.randint(0, 2) for _ in range(n)]
+        high = [l + grain * random.randint(1, 6) for l in low]
+        lo_t, hi_t = sum(low), sum(high)
+        total = grain * random.randint(lo_t // grain, hi_t // grain)
+        a = [random.random() for _ in range(n)]; b = [random.random() + 0.05 for _ in range(n)]
+        try:
+            ints, real, T = equal_finish(total, grain, low, high, a, b)
+        except Exception as e:
+            bad += 1; print("ef fail", total, grain, low, high, type(e).__name__, e); continue
+        if sum(ints) != total or any(x % grain for x in ints) or any(x < l or x > h for x, l, h in zip(ints, low, high)):
+            bad += 1; print("ef invalid", total, grain, low, high, ints); continue
+        mine = max(a[i] + b[i] * ints[i] for i in range(n))
+        best = None
+        for c in itertools.product(*[range(low[i], high[i] + 1, grain) for i in range(n)]):
+            if sum(c) == total:
+                v = max(a[i] + b[i] * c[i] for i in range(n)); best = v if best is None else min(best, v)
+        if mine > best + 1e-9: bad += 1; print("ef subopt", total, grain, low, high, a, b, ints, mine, best)
+    # shift: capacity repaired, total kept
+    for t in range(100):
+        n = random.randint(1, 5)
+        upper = [random.randint(1, 10) for _ in range(n)]
+        shares = [random.randint(0, 12) for _ in range(n)]
+        load = [lambda x, k=random.random(): k * x for _ in range(n)]
+        if sum(shares) > sum(upper):
+            try:
+                shift(shares, upper, load); bad += 1; print("shift should fail")
+            except ValueError: pass
+            continue
+        out = shift(shares, upper, load)
+        if sum(out) != sum(shares) or any(o > u for o, u in zip(out, upper)) or any(o < 0 for o in out): bad += 1; print("shift", shares, upper, out)
+
+    assert bad == 0
