@@ -23,6 +23,24 @@ _OUT_KINDS = {OutputKind.USER_OUTPUT: "user", OutputKind.LOSS_OUTPUT: "loss",
               OutputKind.BUFFER_MUTATION: "mutation", OutputKind.USER_INPUT_MUTATION: "mutation"}
 
 
+_TABLE = None
+
+
+def _default_table() -> dict:
+    """The default decomposition table, built once per process (building it walks every registered operator)."""
+    global _TABLE
+    if _TABLE is None:
+        _TABLE = dict(torch.export.default_decompositions())
+    return dict(_TABLE)
+
+
+def _inference_table() -> dict:
+    """The default table without attention, which inference graphs keep whole."""
+    table = _default_table()
+    table.pop(torch.ops.aten.scaled_dot_product_attention.default, None)
+    return table
+
+
 def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, loss: int | None = None,
            strict: bool = True, decompositions=None) -> Exported:
     """Export ``module(*args, **kwargs)``; with ``loss`` (index of the loss among flat outputs) the joint graph."""
@@ -32,10 +50,8 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
         if decompositions is None and loss is None:
             # inference keeps attention as one operation (the placement has a rule for heads cut over processors and
             # the executor can hand it to a fused kernel); the joint forward+backward export needs it decomposed
-            decompositions = torch.export.default_decompositions()
-            for op in (torch.ops.aten.scaled_dot_product_attention.default,):
-                decompositions.pop(op, None)
-        ep = ep.run_decompositions(decompositions) if decompositions is not None else ep.run_decompositions()
+            decompositions = _inference_table()
+        ep = ep.run_decompositions(decompositions if decompositions is not None else _default_table())
         if expand_loops(ep.graph_module):
             # results that were items of a loop operator are other nodes now: the signature names them
             out_node = next(n for n in ep.graph_module.graph.nodes if n.op == "output")
