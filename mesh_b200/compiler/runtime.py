@@ -470,7 +470,8 @@ class Executor:
                 if s.kind == "S" and len(shape) == len(full):
                     shape[s.dim] = s.counts[self.coords[ax]]
             if -1 in shape and len(shape) == len(full):
-                pass
+                # an inferred extent is ambiguous for an empty shard: state it (a cut dimension was set just above)
+                shape = [full[k] if v == -1 else v for k, v in enumerate(shape)]
             args[i] = shape
         if "mean_as_sum" in m:
             a = list(args)

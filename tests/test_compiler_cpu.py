@@ -473,3 +473,18 @@ def test_layers_on_different_processors_forward_and_backward():
     loss, grads = _eager(m, x)
     _check(res, loss, grads)
     assert set(res.parameters) == set(grads) and all(g is not None for g in res.parameters.values())
+
+
+@pytest.mark.parametrize("n", [3, 4])
+def test_more_processors_than_samples_leaves_empty_shards(n):
+    """A batch of 2 over 3 or 4 processors: the trailing shards are empty (the sizes of ``torch.chunk``), every operator,
+    view and collective still runs, and the gradients are those of the whole batch."""
+    torch.manual_seed(20)
+    m = Decoder(dim=48, heads=4, ffn=96, layers=1)
+    x = torch.randn(2, 6, 48)
+    procs = _procs(n)
+    sch = compile_module(m, (x,), procs, data_parallel(procs), loss=0)
+    assert counts(2, None, n)[-1] == 0
+    res = Program(sch)(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
