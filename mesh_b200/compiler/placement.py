@@ -195,6 +195,19 @@ def _batch_norm_inference(node, shapes):
     return {"batched": [True] + [False] * (len(shapes) - 1), "protect": {1}, "outs": ["S", "R", "R"]}
 
 
+def _group_norm(node, shapes):
+    # (input, weight, bias, N, C, HxW, groups, eps) -> (output, mean, rstd): every sample is normalised on its own;
+    # the batch size is an argument, which the executor replaces by the number of samples it holds
+    return {"batched": [True] + [False] * (len(shapes) - 1), "protect": set(range(1, len(shapes[0]))), "outs": ["S", "S", "S"],
+            "batch_arg": 3}
+
+
+def _group_norm_backward(node, shapes):
+    # (grad_output, input, mean, rstd, weight, N, C, HxW, groups, mask) -> (grad_input, grad_weight, grad_bias)
+    return {"batched": [True, True, True, True] + [False] * (len(shapes) - 4), "protect": set(range(1, len(shapes[0]))),
+            "outs": ["S", "P", "P"], "batch_arg": 5}
+
+
 def _convolution(node, shapes):
     # (input, weight, bias?): samples are independent; a cut anywhere else is the halo rule's business
     return {"batched": [True] + [False] * (len(shapes) - 1), "protect": set(range(1, len(shapes[0]))), "outs": ["S"]}
@@ -217,6 +230,7 @@ BATCHED = {
     aten.cummax.default: _along(1, 2), aten.cummin.default: _along(1, 2),
     aten.split_with_sizes.default: _split(2), aten.split.Tensor: _split(2), aten.unbind.int: _split(1, removes=True),
     aten._native_batch_norm_legit_no_training.default: _batch_norm_inference,
+    aten.native_group_norm.default: _group_norm, aten.native_group_norm_backward.default: _group_norm_backward,
     aten.convolution.default: _convolution, aten.convolution_backward.default: _convolution_backward,
     aten.native_layer_norm.default: _layer_norm, aten.native_layer_norm_backward.default: _layer_norm_backward,
 }
@@ -965,6 +979,8 @@ class Propagator:
         else:
             self.spec[node.name] = tuple(out_specs[0])
         meta = {"out_specs": tuple(out_specs[0]), "full_shape": _shape(node)}
+        if "batch_arg" in info:
+            meta["batch_arg"] = info["batch_arg"]
         stack = node.meta.get("nn_module_stack")
         if stack:
             meta["module"] = list(stack.values())[-1][0]

@@ -461,6 +461,8 @@ class Executor:
         m = st.meta
         if "draw" in m:
             return self.draw(m, args)
+        if "batch_arg" in m:
+            args[m["batch_arg"]] = args[0].shape[0]        # the operator takes the batch size as a number: this shard's
         loc = m.get("localize")
         if loc is not None and "out_specs" in m:
             i = loc[1]

@@ -488,3 +488,23 @@ def test_more_processors_than_samples_leaves_empty_shards(n):
     res = Program(sch)(x)
     loss, grads = _eager(m, x)
     _check(res, loss, grads)
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_group_norm_under_a_batch_cut_takes_the_local_batch_size(n):
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c, self.gn = torch.nn.Conv2d(4, 8, 3, padding=1), torch.nn.GroupNorm(2, 8)
+
+        def forward(self, x):
+            return torch.relu(self.gn(self.c(x))).pow(2).mean()
+
+    torch.manual_seed(21)
+    m, x = Net(), torch.randn(6, 4, 8, 8)                                # 6 samples over 4 processors: 2, 2, 2, 0
+    procs = _procs(n)
+    sch = compile_module(m, (x,), procs, data_parallel(procs), loss=0)
+    assert sch.structure["fallbacks"] == 0 and set(sch.structure["by_verb"]) == {"all_reduce"}
+    res = Program(sch)(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
