@@ -723,8 +723,12 @@ class Propagator:
                 want = Spec("S", q.dim, q.counts)
                 return [want, want, want], want
             causal = node.kwargs.get("is_causal", node.args[5] if len(node.args) > 5 else False)
-            if q.kind == "S" and q.dim == 2 and not causal and all(s.kind in ("R", "S") for s in specs[1:]):
-                # queries are independent of each other: keep them cut, hold all keys and values
+            if q.kind == "S" and q.dim == 2 and all(s.kind in ("R", "S") for s in specs[1:]) and (
+                    not causal or self.shape[tnames[0]][2] == self.shape[tnames[1]][2]):
+                # queries are independent of each other: keep them cut, hold all keys and values; a causal mask is then
+                # stated by the executor for the rows this processor holds (their positions in the whole sequence)
+                if causal:
+                    meta["causal_rows"] = ax
                 return [Spec("S", 2, q.counts, q.striped), R, R], Spec("S", 2, q.counts, q.striped)
             kv = next((s for s in specs[1:] if s.kind == "S" and s.dim in (0, 1) and not s.striped), None)
             if q.kind == "R" and kv is not None and (kv.dim == 0 or same_heads):

@@ -461,6 +461,22 @@ class Executor:
         m = st.meta
         if "draw" in m:
             return self.draw(m, args)
+        if "causal_rows" in m:
+            # whole attention over this processor's query rows: row i of the whole sequence sees keys 0..i
+            ax = m["causal_rows"]
+            spec = m["out_specs"][ax]
+            q, k = args[0], args[1]
+            rows = local_indices(spec, self.coords[ax], m["full_shape"][2])
+            pos = torch.arange(m["full_shape"][2], device=q.device)[rows] if isinstance(rows, slice) else torch.tensor(rows, device=q.device)
+            mask = pos[:, None] >= torch.arange(k.shape[2], device=q.device)[None, :]
+            kw = {key: v for key, v in kwargs.items() if key not in ("is_causal", "attn_mask")}
+            extra = list(args[3:])
+            if len(extra) > 2:
+                extra[2] = False                              # positional is_causal
+            if extra:
+                extra[0] = mask
+                return tgt(q, k, args[2], *extra, **kw)
+            return tgt(q, k, args[2], attn_mask=mask, is_causal=False, **kw)
         if "batch_arg" in m:
             args[m["batch_arg"]] = args[0].shape[0]        # the operator takes the batch size as a number: this shard's
         loc = m.get("localize")

@@ -281,3 +281,6 @@ def test_whole_attention_under_every_cut(causal):
             assert torch.allclose(Program(sch)(q, k, v), ref, atol=1e-5), (n, dim, units, which)
             if dim in (0, 1) and which == ("q", "k", "v"):
                 assert sch.structure["by_verb"] == {"all_gather": 1}          # only the result is brought together
+            if dim == 2 and which == ("q", "k", "v"):
+                # queries stay cut (with their rows of the causal mask); keys, values and the result are gathered
+                assert sch.structure["fallbacks"] == 0 and sch.structure["by_verb"] == {"all_gather": 3}
