@@ -52,8 +52,9 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
             # the executor can hand it to a fused kernel); the joint forward+backward export needs it decomposed
             decompositions = _inference_table()
         ep = ep.run_decompositions(decompositions if decompositions is not None else _default_table())
-        if expand_loops(ep.graph_module):
-            # results that were items of a loop operator are other nodes now: the signature names them
+        if expand_loops(ep.graph_module) + merge_repeats(ep.graph_module):
+            # results that were items of a loop operator, or repeats of another node, are other nodes now: the
+            # signature names them
             out_node = next(n for n in ep.graph_module.graph.nodes if n.op == "output")
             for spec, node in zip(ep.graph_signature.output_specs, out_node.args[0]):
                 if isinstance(node, torch.fx.Node) and hasattr(spec.arg, "name"):
@@ -112,6 +113,52 @@ def _made(graph, before, target, args, val):
         node = graph.call_function(target, args)
     node.meta["val"] = val
     return node
+
+
+def merge_repeats(gm: torch.fx.GraphModule) -> int:
+    """Nodes that apply the same operator to the same operands are one node (the three views of one normalised
+    activation that feed the query, key and value projections, for instance): what is cut, gathered or reduced once for
+    one of them then serves all.  The captured graph is functional, so equal operator and operands mean equal values;
+    random draws are left alone.  Returns how many nodes were merged."""
+    import operator
+
+    def key_of(a):
+        if isinstance(a, torch.fx.Node):
+            return ("node", a.name)
+        if isinstance(a, (list, tuple)):
+            return (type(a).__name__, tuple(key_of(x) for x in a))
+        if isinstance(a, dict):
+            return ("dict", tuple(sorted((k, key_of(v)) for k, v in a.items())))
+        if isinstance(a, (torch.dtype, torch.device, torch.layout, torch.memory_format)):
+            return ("torch", str(a))
+        return (type(a).__name__, a)
+    seen: dict = {}
+    outputs = {a for n in gm.graph.nodes if n.op == "output" for a in n.all_input_nodes}
+    merged = 0
+    for node in list(gm.graph.nodes):
+        if node.op != "call_function":
+            continue
+        name = str(node.target)
+        if any(w in name for w in ("rand", "dropout", "bernoulli", "normal", "multinomial", "higher_order")) or "_scatter" in name and False:
+            continue
+        if node.target is not operator.getitem and not isinstance(node.meta.get("val"), torch.Tensor):
+            continue                                          # operators with several results keep their own node
+        try:
+            key = (name, key_of(node.args), key_of(node.kwargs))
+            hash(key)
+        except TypeError:
+            continue
+        first = seen.get(key)
+        if first is None:
+            seen[key] = node
+        elif node not in outputs:                            # a result the caller reads keeps its node
+            node.replace_all_uses_with(first)
+            gm.graph.erase_node(node)
+            merged += 1
+    if merged:
+        gm.graph.lint()
+        gm.recompile()
+    return merged
 
 
 def expand_loops(gm: torch.fx.GraphModule) -> int:

@@ -80,6 +80,16 @@ def fuse_plan(plan: Plan) -> tuple[Plan, dict]:
                 chain.append(j)
                 cur = steps[j].out
                 j = single_use(cur)
+            keep = None
+            if j is None:
+                # several readers (the query, key and value projections share one gather): the first product is fused
+                # and hands the gathered rows on to the others, provided every reader is a product with them on the left
+                readers = sorted(set(uses.get(cur, [])))
+                if readers and readers[-1] < len(steps) and all(
+                        steps[r].op == "call" and steps[r].target is aten.mm.default and isinstance(steps[r].args[0], Ref)
+                        and steps[r].args[0].name == cur and not (isinstance(steps[r].args[1], Ref) and steps[r].args[1].name == cur)
+                        for r in readers):
+                    j, keep = readers[0], cur
             if j is None or j >= len(steps):
                 continue
             mm = steps[j]
@@ -90,6 +100,8 @@ def fuse_plan(plan: Plan) -> tuple[Plan, dict]:
             meta = dict(mm.meta)
             meta.update({"fused": "ag_mm", "axis": st.meta["axis"], "from": frm, "to": st.meta["to"], "rows": rows, "k": k,
                          "gather_shape": st.meta["full_shape"], "channel": st.meta.get("channel"), "kind": st.meta.get("kind")})
+            if keep is not None:
+                meta["keep"] = keep                          # the executor binds the gathered rows [rows, k] to this name
             replace[j] = Step("fused", mm.out, "ag_mm", (st.args[0], mm.args[1]), {}, meta)
             drop.update(chain)
             report["ag_mm"] += 1

@@ -108,7 +108,7 @@ def _run_with_env(ex: Executor, inputs: dict, consts, env) -> list:
         elif st.op == "collective":
             env[st.out] = ex.collective(st, env[st.args[0].name])
         elif st.op == "fused":
-            env[st.out] = ex.fused(st, env[st.args[0].name], env[st.args[1].name])
+            env[st.out] = ex.fused(st, env[st.args[0].name], env[st.args[1].name], env)
         else:
             env[st.out] = ex.call(st, val)
     return [o[1] if isinstance(o, tuple) else env[o] for o in ex.plan.outputs]

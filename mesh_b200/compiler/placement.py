@@ -259,6 +259,7 @@ class Propagator:
         self.transfers: list[Transfer] = []
         self.tmp = 0
         self.channel = 0
+        self.moved: dict = {}                     # (value, placement) -> the value that carries it there
         self.extended: dict = {}                  # (value, left, right) -> its halo-extended copy (forward -> backward)
         self.sites = 0                             # random draws so far: each gets its own stream of the generator
         self.renamed: dict[str, str] = {}         # node name -> value that carries it after a stated reshard
@@ -288,7 +289,15 @@ class Propagator:
         return out
 
     def reshard(self, name: str, want: tuple) -> str:
-        """Bring value ``name`` to placement ``want`` (per axis); returns the (possibly new) value name."""
+        """Bring value ``name`` to placement ``want`` (per axis); returns the (possibly new) value name.  A value that
+        was already brought to this placement is reused: values never change, so one transfer serves every reader."""
+        key = (name, tuple(want))
+        if key in self.moved:
+            return self.moved[key]
+        self.moved[key] = out = self._reshard(name, want)
+        return out
+
+    def _reshard(self, name: str, want: tuple) -> str:
         have = self.spec[name]
         cur = name
         for ax in range(self.na):
@@ -436,7 +445,12 @@ class Propagator:
             return [a, R], Spec("S", m_dim, a.counts, a.striped)
         if sb == n_dim and a.kind == "R":
             return [R, b], Spec("S", n_dim, b.counts, b.striped)
-        if sa == m_dim and sb == n_dim:                          # same axis on both: gather the weight-like operand
+        if sa == m_dim and sb == n_dim:
+            # rows of A and columns of B cut over the same axis: one operand has to be whole.  Gather the smaller one
+            # (activations of a few tokens against a large weight: gather the activations and keep the weight's cut,
+            # which is Megatron's sequence-parallel layer; a small weight against many rows: gather the weight)
+            if math.prod(self.shape[targs[0]]) <= math.prod(self.shape[targs[1]]):
+                return [R, b], Spec("S", n_dim, b.counts, b.striped)
             return [a, R], Spec("S", m_dim, a.counts, a.striped)
         if sa == m_dim and b.kind == "P":
             return [a, R], Spec("S", m_dim, a.counts, a.striped)

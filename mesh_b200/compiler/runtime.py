@@ -362,7 +362,7 @@ class Executor:
             elif st.op == "collective":
                 env[st.out] = self.collective(st, env[st.args[0].name])
             elif st.op == "fused":
-                env[st.out] = self.fused(st, env[st.args[0].name], env[st.args[1].name])
+                env[st.out] = self.fused(st, env[st.args[0].name], env[st.args[1].name], env)
             else:
                 env[st.out] = self.call(st, val)
             if self.times is not None:
@@ -396,7 +396,7 @@ class Executor:
                           else FusedRowLinear(ctx.heap, rows_total, w.shape[1], w.shape[0]))
         return cache[key]
 
-    def fused(self, st: Step, a, w_t):
+    def fused(self, st: Step, a, w_t, env=None):
         m = st.meta
         if a is None or w_t is None:
             return None
@@ -405,10 +405,17 @@ class Executor:
             if op is not None:
                 if self.trace is not None:
                     self.trace.append(("all_gather", m.get("kind"), m["axis"], m["channel"]))
-                y, _ = op.forward(a.reshape(-1, m["k"]).contiguous(), w_t.t())
+                y, xbuf = op.forward(a.reshape(-1, m["k"]).contiguous(), w_t.t())
+                if "keep" in m and env is not None:
+                    # other products of the same gathered rows read the kernel's landing zone; it is overwritten two
+                    # uses of this shape later, by which time those products have run (stream order)
+                    env[m["keep"]] = xbuf.local.view(m["rows"], m["k"])
                 return y
             gathered = self.collective(Step("collective", st.out, "all_gather", (), {}, {**m, "full_shape": m["gather_shape"]}), a)
-            return aten.mm.default(gathered.reshape(m["rows"], m["k"]), w_t)
+            gathered = gathered.reshape(m["rows"], m["k"])
+            if "keep" in m and env is not None:
+                env[m["keep"]] = gathered
+            return aten.mm.default(gathered, w_t)
         if st.target == "mm_rs":
             shape = list(m["out_shape"])
             op = self._fused_kernels("mm_rs", a, w_t, a.shape[0])

@@ -508,3 +508,20 @@ def test_group_norm_under_a_batch_cut_takes_the_local_batch_size(n):
     res = Program(sch)(x)
     loss, grads = _eager(m, x)
     _check(res, loss, grads)
+
+
+def test_sequence_parallel_megatron_layer_has_the_textbook_collectives():
+    """Tokens and weights cut over the same processors: per layer one all-gather serves the query, key and value
+    projections, one the two FFN input projections, and each row-parallel projection ends in a reduce-scatter; the
+    activations (smaller than the weights here) are what is gathered.  All four become fused steps."""
+    torch.manual_seed(22)
+    m = Decoder(dim=512, heads=4, ffn=1024, layers=1).eval()
+    x = torch.randn(1, 256, 512)
+    procs = _procs(2)
+    names = tuple(procs)
+    tp = megatron(procs)
+    sch = compile_module(m, (x,), procs, lambda nd: (1, names, None) if nd.op == "placeholder" and nd.name == "x" else tp(nd))
+    assert sch.structure["by_verb"] == {"all_gather": 2, "reduce_scatter": 2, "all_reduce": 1}, sch.structure["by_verb"]
+    prog = Program(sch)
+    assert prog.fusion == {"ag_mm": 2, "mm_rs": 2}
+    assert torch.allclose(prog(x), m(x), atol=1e-4)
