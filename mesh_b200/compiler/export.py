@@ -52,7 +52,7 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
             # the executor can hand it to a fused kernel); the joint forward+backward export needs it decomposed
             decompositions = _inference_table()
         ep = ep.run_decompositions(decompositions if decompositions is not None else _default_table())
-        if expand_loops(ep.graph_module) + merge_repeats(ep.graph_module):
+        if expand_loops(ep.graph_module) + merge_repeats(ep.graph_module) + (unflatten_products(ep.graph_module) if loss is None else 0):
             # results that were items of a loop operator, or repeats of another node, are other nodes now: the
             # signature names them
             out_node = next(n for n in ep.graph_module.graph.nodes if n.op == "output")
@@ -65,6 +65,8 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
             users = [i for i, spec in enumerate(ep.graph_signature.output_specs) if spec.kind == OutputKind.USER_OUTPUT]
             _detach_mutations(ep, keep=users[loss])
             ep = _export_forward_backward(ep, joint_loss_index=users[loss])
+            merge_repeats(ep.graph_module)                    # the backward half repeats views and transposes of the forward
+            unflatten_products(ep.graph_module)
     return read(ep, training=loss is not None)
 
 
@@ -113,6 +115,68 @@ def _made(graph, before, target, args, val):
         node = graph.call_function(target, args)
     node.meta["val"] = val
     return node
+
+
+def unflatten_products(gm: torch.fx.GraphModule) -> int:
+    """``view([B, H, m, k] -> [B*H, m, k])``, the same for the other operand, ``bmm``, ``view`` back to ``[B, H, m, n]``
+    is how attention's two products reach the graph.  Merging batch and heads hides the heads from the placement (a cut
+    along an inner merged dimension has no description), so the values would be gathered; the pattern is rewritten to
+    one product over the four-dimensional operands, whose leading dimensions are both batch dimensions to the rules."""
+    aten = torch.ops.aten
+    views = (aten.view.default, aten._unsafe_view.default, aten.reshape.default)
+
+    def opened(node):
+        """``(the 4-D value a flattened operand came from, whether its last two dimensions are swapped)`` or None."""
+        if not (isinstance(node, torch.fx.Node) and node.op == "call_function"):
+            return None
+        if node.target is aten.permute.default and list(node.args[1]) == [0, 2, 1]:      # the backward's transposed operands
+            inner = opened(node.args[0])
+            return None if inner is None else (inner[0], not inner[1])
+        if node.target not in views:
+            return None
+        src = node.args[0]
+        a, v = src.meta.get("val"), node.meta.get("val")
+        if not (isinstance(a, torch.Tensor) and isinstance(v, torch.Tensor)) or a.ndim != 4 or v.ndim != 3:
+            return None
+        return (src, False) if (a.shape[0] * a.shape[1] == v.shape[0] and tuple(a.shape[2:]) == tuple(v.shape[1:])) else None
+
+    def four(found, before):
+        src, swapped = found
+        if not swapped:
+            return src
+        with gm.graph.inserting_before(before):
+            t = gm.graph.call_function(aten.permute.default, (src, [0, 1, 3, 2]))
+        t.meta["val"] = src.meta["val"].permute(0, 1, 3, 2)
+        return t
+
+    done = 0
+    for node in list(gm.graph.nodes):
+        if node.op != "call_function" or node.target is not aten.bmm.default:
+            continue
+        fa, fb = opened(node.args[0]), opened(node.args[1])
+        if fa is None or fb is None or tuple(fa[0].meta["val"].shape[:2]) != tuple(fb[0].meta["val"].shape[:2]):
+            continue
+        lead = tuple(fa[0].meta["val"].shape[:2])
+        out = node.meta["val"]
+        want = lead + tuple(out.shape[1:])
+        users = list(node.users)
+        if not users or not all(u.op == "call_function" and u.target in views and tuple(u.meta["val"].shape) == want for u in users):
+            continue
+        a4, b4 = four(fa, node), four(fb, node)
+        with gm.graph.inserting_before(node):
+            prod = gm.graph.call_function(aten.matmul.default, (a4, b4))
+        prod.meta.update({k: v for k, v in node.meta.items() if k != "val"})
+        prod.meta["val"] = users[0].meta["val"]
+        for u in users:
+            u.replace_all_uses_with(prod)
+            gm.graph.erase_node(u)
+        gm.graph.erase_node(node)
+        done += 1
+    if done:
+        gm.graph.eliminate_dead_code()                        # the flattened views and their transposes
+        gm.graph.lint()
+        gm.recompile()
+    return done
 
 
 def merge_repeats(gm: torch.fx.GraphModule) -> int:

@@ -433,10 +433,10 @@ class Propagator:
         k_b, n_dim = batch, batch + 1
         sa = a.dim if a.kind == "S" else None
         sb = b.dim if b.kind == "S" else None
-        if batch and sa == 0 and (sb == 0 or b.kind == "R"):
-            return [a, Spec("S", 0, a.counts, a.striped)], Spec("S", 0, a.counts, a.striped)
-        if batch and sb == 0 and a.kind == "R":
-            return [Spec("S", 0, b.counts, b.striped), b], Spec("S", 0, b.counts, b.striped)
+        if batch and sa is not None and sa < batch and (sb == sa or b.kind == "R"):      # a batch dimension: independent products
+            return [a, Spec("S", sa, a.counts, a.striped)], Spec("S", sa, a.counts, a.striped)
+        if batch and sb is not None and sb < batch and a.kind == "R":
+            return [Spec("S", sb, b.counts, b.striped), b], Spec("S", sb, b.counts, b.striped)
         if sa == k_a and (sb == k_b or b.kind == "R"):           # contraction sharded -> partial sums
             return [a, Spec("S", k_b, a.counts, a.striped)], P()
         if sb == k_b and a.kind == "R":
@@ -607,6 +607,9 @@ class Propagator:
             return self.rule_pointwise(node, tnames, specs, ax)
         if tgt in (aten.mm.default, aten.bmm.default):
             return self.rule_mm(node, tnames, specs, ax, 0 if tgt is aten.mm.default else 1)
+        if tgt is aten.matmul.default and len(self.shape[tnames[0]]) == len(self.shape[tnames[1]]) >= 3:
+            # products batched over several leading dimensions (batch and heads kept apart, see export.unflatten_products)
+            return self.rule_mm(node, tnames, specs, ax, len(self.shape[tnames[0]]) - 2)
         if tgt is aten.addmm.default:                                   # bias + a @ b
             w, o = self.rule_mm(node, tnames[1:], specs[1:], ax, 0)
             if o.kind == "S" and o.dim == 1:

@@ -525,3 +525,20 @@ def test_sequence_parallel_megatron_layer_has_the_textbook_collectives():
     prog = Program(sch)
     assert prog.fusion == {"ag_mm": 2, "mm_rs": 2}
     assert torch.allclose(prog(x), m(x), atol=1e-4)
+
+
+def test_tensor_parallel_training_layer_needs_only_its_four_all_reduces():
+    """Megatron tensor parallelism, forward and backward, batch of 2: the attention products keep batch and heads apart
+    (so the cut along the heads survives them) and a layer costs two all-reduces forward and two backward; the only
+    other transfers reduce the gradients of the replicated norm weights."""
+    torch.manual_seed(23)
+    m = Decoder(dim=48, heads=4, ffn=96, layers=1)
+    x = torch.randn(2, 12, 48)
+    procs = _procs(2)
+    sch = compile_module(m, (x,), procs, megatron(procs), loss=0)
+    assert sch.structure["fallbacks"] == 0 and set(sch.structure["by_verb"]) == {"all_reduce"}
+    big = [t for t in sch.plan.transfers if t.nbytes >= 2 * 12 * 48 * 4]
+    assert len(big) == 4, [(t.verb, t.nbytes) for t in sch.plan.transfers]
+    res = Program(sch)(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
