@@ -203,8 +203,8 @@ def merge_repeats(gm: torch.fx.GraphModule) -> int:
         if node.op != "call_function":
             continue
         name = str(node.target)
-        if any(w in name for w in ("rand", "dropout", "bernoulli", "normal", "multinomial", "higher_order")) or "_scatter" in name and False:
-            continue
+        if any(w in name for w in ("rand", "dropout", "bernoulli", "normal", "multinomial", "higher_order")):
+            continue                                          # two draws are two values
         if node.target is not operator.getitem and not isinstance(node.meta.get("val"), torch.Tensor):
             continue                                          # operators with several results keep their own node
         try:
