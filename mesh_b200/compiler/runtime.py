@@ -399,6 +399,8 @@ class Executor:
     def fused(self, st: Step, a, w_t, env=None):
         m = st.meta
         if a is None or w_t is None:
+            if "keep" in m and env is not None:
+                env[m["keep"]] = None                        # absent here: so are the gathered rows for the other readers
             return None
         if st.target == "ag_mm":
             op = self._fused_kernels("ag_mm", a, w_t, m["rows"])
