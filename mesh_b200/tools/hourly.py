@@ -27,6 +27,7 @@ def programs(gpus: int) -> list[dict]:
         {"name": "tp_ffn_period", "cmd": run + ["bench.py", "--gpus", str(gpus)], "deadline_s": 600},
         {"name": "example_parallel", "cmd": [py, "examples/parallel.py", "--small"], "deadline_s": 300},
         {"name": "planner_workload", "cmd": [py, "examples/planner_workload.py", "--ticks", "100"], "deadline_s": 300},
+        {"name": "micro_workloads", "cmd": [py, "benchmarks/micro.py", "all", "--small"], "deadline_s": 300},
     ]
 
 
