@@ -129,3 +129,25 @@ def fuse_plan(plan: Plan) -> tuple[Plan, dict]:
             report["mm_rs"] += 1
     plan.steps = [replace.get(i, st) for i, st in enumerate(steps) if i not in drop]
     return plan, report
+
+
+def bucket_reductions(plan: Plan) -> tuple[Plan, int]:
+    """Gradient all-reduces whose results nothing in the plan reads (they are outputs: the gradients of replicated
+    parameters under a batch cut) are marked as members of one bucket per (axis, dtype); the executor holds them back
+    and reduces each bucket as one flat message at the end of the step - one launch and one latency instead of one per
+    parameter (the reference's planner groups transfers into demands the same way, rdma/mesh-collective.c:1791).
+    Returns the rewritten copy and the number of bucketed transfers."""
+    plan = copy.copy(plan)
+    uses = _uses(plan)
+    end = len(plan.steps)
+    steps, count = [], 0
+    for st in plan.steps:
+        if (st.op == "collective" and st.target == "all_reduce" and st.meta["from"].op == "sum"
+                and all(u == end for u in uses.get(st.out, []))):
+            meta = dict(st.meta)
+            meta["bucket"] = (st.meta["axis"], str(plan.dtypes.get(st.out, plan.dtypes.get(st.args[0].name, "float32"))))
+            st = Step(st.op, st.out, st.target, st.args, st.kwargs, meta)
+            count += 1
+        steps.append(st)
+    plan.steps = steps
+    return plan, count

@@ -336,6 +336,7 @@ class Executor:
     # ---- one program execution
     def run(self, inputs: dict, consts) -> list:
         env: dict[str, Any] = {}
+        pending: dict = {}
         for name, full in inputs.items():
             env[name] = self._here(self.shard(full, self.plan.input_specs[name])) if isinstance(full, torch.Tensor) else full
 
@@ -359,6 +360,9 @@ class Executor:
                 src = env[st.args[0].name]
                 s, ax = st.meta["to"], st.meta["axis"]
                 env[st.out] = None if src is None else self._index(src, s.dim, local_indices(s, self.coords[ax], src.shape[s.dim]))
+            elif st.op == "collective" and "bucket" in st.meta and env[st.args[0].name] is not None:
+                pending.setdefault(st.meta["bucket"], []).append((st, env[st.args[0].name]))     # reduced with its bucket below
+                env[st.out] = None
             elif st.op == "collective":
                 env[st.out] = self.collective(st, env[st.args[0].name])
             elif st.op == "fused":
@@ -369,6 +373,15 @@ class Executor:
                 if self.device.type == "cuda":
                     torch.cuda.synchronize(self.device)
                 self.times.append((index, time.perf_counter() - t0))
+        for members in pending.values():
+            # one flat all-reduce per bucket, then every member gets its piece back
+            first = members[0][0]
+            flat = torch.cat([t.reshape(-1) for _, t in members])
+            flat = self.collective(Step("collective", first.out, "all_reduce", first.args, {}, first.meta), flat)
+            at = 0
+            for st, t in members:
+                env[st.out] = flat[at:at + t.numel()].view(t.shape)
+                at += t.numel()
         out = []
         for o in self.plan.outputs:
             out.append(o[1] if isinstance(o, tuple) else env[o])
@@ -555,6 +568,10 @@ class Program(Arguments):
         if os.environ.get("MESH_FUSE", "1") != "0":
             from .fuse import fuse_plan
             self.plan, self.fusion = fuse_plan(self.plan)
+        self.bucketed = 0
+        if os.environ.get("MESH_BUCKET", "0") == "1":
+            from .fuse import bucket_reductions
+            self.plan, self.bucketed = bucket_reductions(self.plan)
         self.mesh = scheduled.plan.mesh
         distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size() == self.mesh.size
         self.threads = (not distributed) if threads is None else threads

@@ -542,3 +542,35 @@ def test_tensor_parallel_training_layer_needs_only_its_four_all_reduces():
     res = Program(sch)(x)
     loss, grads = _eager(m, x)
     _check(res, loss, grads)
+
+
+def _bucket_rank(rank, world, rdv):
+    torch.manual_seed(24)
+    m = Decoder(dim=48, heads=4, ffn=96, layers=2)
+    x = torch.randn(4, 12, 48)
+    procs = _procs(world)
+    prog = Program(compile_module(m, (x,), procs, data_parallel(procs), loss=0))
+    assert prog.bucketed >= 18
+    res = prog(x)
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
+
+
+def test_gradient_all_reduces_go_out_as_one_bucket(monkeypatch):
+    """``MESH_BUCKET=1``: the all-reduces of gradients that nothing else reads are held back and reduced as one flat
+    message per step, in the threaded interpreter and with one process per processor alike."""
+    monkeypatch.setenv("MESH_BUCKET", "1")
+    monkeypatch.setenv("MESH_SYNC_TRACE", "1")
+    torch.manual_seed(24)
+    m = Decoder(dim=48, heads=4, ffn=96, layers=2)
+    x = torch.randn(4, 12, 48)
+    procs = _procs(2)
+    sch = compile_module(m, (x,), procs, data_parallel(procs), loss=0)
+    prog = Program(sch)
+    res = prog(x)
+    assert prog.bucketed == sch.structure["by_verb"]["all_reduce"] - 1          # all but the loss
+    assert len(prog.per_rank[0][0].trace) == 2                                    # the loss, then one bucket
+    loss, grads = _eager(m, x)
+    _check(res, loss, grads)
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_bucket_rank, 2, init_pg="gloo")
