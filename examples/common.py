@@ -94,6 +94,10 @@ def execute(model, inputs, placement, args, *, loss=None, functions=None, mesh=N
     report = {"processors": len(procs), "channels": s.get("channels"), "by_kind": s.get("by_kind"), "by_verb": s.get("by_verb"),
               "signature": getattr(sch.signature, "digest", None) or str(sch.signature)[:40], "signature_ok": sch.signature.ok(),
               "error": err, "ok": bool(err < tol), "compile_s": round(t_compile, 3), "run_s": round(t_run, 4)}
+    from mesh_b200.compiler.devices import crossings
+    cross = crossings(sch.plan, procs)
+    report["bytes_between_processors"] = s.get("bytes_between_processors")
+    report["between_machines"] = {"transfers": cross["between_machines"], "bytes": cross["bytes_between_machines"]}
     if "function_calls" in s:
         report["function_calls"] = s["function_calls"]
     print(json.dumps(report, default=str), flush=True)
