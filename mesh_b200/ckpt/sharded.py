@@ -55,6 +55,7 @@ def save_sharded(directory, step: int, local: dict, layout: dict, rank: int, wor
         tensors[name] = t
     tmp = d / f"rank{rank}.safetensors.tmp"
     save_file(tensors, str(tmp))
+    _fsync_file(tmp)                           # the shard's bytes are durable before its name (and the commit line) is
     os.replace(tmp, d / f"rank{rank}.safetensors")
     if rank == 0:
         index = {"step": step, "world": world, "extra": extra or {},
@@ -62,6 +63,7 @@ def save_sharded(directory, step: int, local: dict, layout: dict, rank: int, wor
                                  "dtype": str(local[n].dtype), "shape": list(local[n].shape)} for n in local}}
         tmpi = d / "index.json.tmp"
         tmpi.write_text(json.dumps(index, indent=1))
+        _fsync_file(tmpi)
         os.replace(tmpi, d / "index.json")
     _fsync_dir(d)
     if barrier is not None:
@@ -74,6 +76,14 @@ def save_sharded(directory, step: int, local: dict, layout: dict, rank: int, wor
     if barrier is not None:
         barrier()
     return d
+
+
+def _fsync_file(path) -> None:
+    fd = os.open(str(path), os.O_RDONLY)
+    try:
+        os.fsync(fd)
+    finally:
+        os.close(fd)
 
 
 def latest_step(directory) -> int | None:
@@ -114,7 +124,11 @@ def load_sharded(directory, step: int | None, rank: int, world: int, new_layout:
     for name, meta in index["tensors"].items():
         dim, old_counts = meta["dim"], meta["counts"]
         if dim is None:
-            out[name] = shard_of(0)[name].to(device)
+            whole = shard_of(0)[name]
+            if new_layout and name in new_layout and new_layout[name][0] is not None:
+                ndim, ncounts = new_layout[name]            # stored replicated, wanted cut
+                whole = whole.narrow(ndim, sum(ncounts[:rank]), ncounts[rank]).contiguous()
+            out[name] = whole.to(device)
             continue
         total = sum(old_counts)
         dtype = getattr(torch, str(meta.get("dtype", "torch.float32")).split(".")[-1])

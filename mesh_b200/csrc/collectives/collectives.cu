@@ -261,11 +261,14 @@ __global__ void __launch_bounds__(THREADS) alltoallv_kernel(Comm c, const uint8_
   }
 }
 
+// Staging buffers alternate call by call, so call k+2 overwrites what call k published.  That is safe only if every
+// rank's call k+1 saw every peer's arrival for call k+1 (a peer arrives after its call k has finished, by stream
+// order).  Hence every rank of a broadcast or a reduce waits for all arrivals, also the ranks that read nothing.
 __global__ void __launch_bounds__(THREADS) broadcast_kernel(Comm c, uint8_t* buf, uint64_t bytes, int root) {
   if (c.rank == root) copy_bytes(c.staging[c.rank] + HDR, buf, bytes);
   signal_all(c, 0);
+  if (!wait_ranks(c, 0, c.expect_a, (1u << c.world) - 1u)) return;
   if (c.rank == root) return;
-  if (!wait_ranks(c, 0, c.expect_a, 1u << root)) return;
   copy_bytes(buf, c.staging[root] + HDR, bytes);
 }
 
@@ -273,8 +276,8 @@ template <typename T>
 __global__ void __launch_bounds__(THREADS) reduce_kernel(Comm c, const T* in, T* out, uint64_t count, int op, int root) {
   copy_bytes(c.staging[c.rank] + HDR, reinterpret_cast<const uint8_t*>(in), count * sizeof(T));
   signal_all(c, 0);
-  if (c.rank != root) return;
   if (!wait_ranks(c, 0, c.expect_a, (1u << c.world) - 1u)) return;
+  if (c.rank != root) return;
   reduce_pull<T>(c, HDR, out, count, op);
 }
 

@@ -53,6 +53,14 @@ typedef struct MeshGemmArgs {
   const void* tiles;
   const void* n_tiles_dev;
   int max_tiles;               // upper bound of *n_tiles_dev (grid sizing only)
+  // kernel-to-kernel dataflow between consecutive launches of one stream (see Params in gemm_sm100.cuh)
+  void* d_done;                // counters per 128 output rows, raised by the epilogue (4 per tile); NULL: none
+  const void* k_ready;         // counters per `k_ready_rows` K rows that a K block waits for; NULL: none
+  uint32_t k_ready_value;
+  int k_ready_rows;
+  int pdl;                     // bit 0: may start before the previous launch of the stream has finished (every input
+                               // that launch writes is guarded by a_ready / k_ready); bit 1: let the next launch
+                               // start during this kernel's last wave
 } MeshGemmArgs;
 
 // Returns 0 or a negative error (bad shape/alignment) or a positive cudaError_t.

@@ -34,7 +34,7 @@ static bool make_map_mn(CUtensorMap* tm, const void* base, uint64_t mn_cols, uin
 }
 
 template <int A_MN, int B_MN, int EPI, bool AG, int BNV, bool PAIR>
-static int launch(const Params& p, int ctas, cudaStream_t stream) {
+static int launch(const Params& p, int ctas, cudaStream_t stream, bool dependent) {
   auto kern = gemm_kernel<A_MN, B_MN, EPI, AG, BNV, PAIR>;
   static bool configured = false;   // per instantiation
   if (!configured) {
@@ -49,13 +49,15 @@ static int launch(const Params& p, int ctas, cudaStream_t stream) {
   cfg.blockDim = dim3((unsigned)threads);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = PAIR ? 2 : 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = dependent ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_error((int)e, "gemm launch: %s", cudaGetErrorString(e));
@@ -119,6 +121,13 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   p.aux = (const __nv_bfloat16*)a->aux;
   p.ld_aux = a->ld_aux;
   p.status = (Status*)a->status;
+  p.d_done = (uint32_t*)a->d_done;
+  p.k_ready = (const uint32_t*)a->k_ready;
+  p.k_ready_value = a->k_ready_value;
+  p.k_ready_rows = a->k_ready_rows > 0 ? a->k_ready_rows : BM;
+  if (a->k_ready != nullptr && (p.k_ready_rows % BK)) return set_error(-5, "gemm: k_ready_rows must be a multiple of 64");
+  p.pdl_trigger = (a->pdl & 2) ? 1 : 0;
+  const bool dependent = (a->pdl & 1) != 0;
   p.tiles = (const TileDesc*)a->tiles;
   p.n_tiles_dev = (const int*)a->n_tiles_dev;
   p.a_ready = (const uint32_t*)a->a_ready;
@@ -193,11 +202,11 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   do {                                                                      \
     constexpr int E128 = ((E) == EPI_GLU_FWD ? EPI_STORE : (E));            \
     if (bn == 128 && (E) != EPI_GLU_FWD) {                                  \
-      if (pair) return launch<AM, BMJ, E128, G, 128, true>(p, ctas, stream); \
-      return launch<AM, BMJ, E128, G, 128, false>(p, ctas, stream);         \
+      if (pair) return launch<AM, BMJ, E128, G, 128, true>(p, ctas, stream, dependent); \
+      return launch<AM, BMJ, E128, G, 128, false>(p, ctas, stream, dependent);         \
     }                                                                       \
-    if (pair) return launch<AM, BMJ, E, G, 256, true>(p, ctas, stream);     \
-    return launch<AM, BMJ, E, G, 256, false>(p, ctas, stream);              \
+    if (pair) return launch<AM, BMJ, E, G, 256, true>(p, ctas, stream, dependent);     \
+    return launch<AM, BMJ, E, G, 256, false>(p, ctas, stream, dependent);              \
   } while (0)
   switch (a->epi) {
     case EPI_STORE:

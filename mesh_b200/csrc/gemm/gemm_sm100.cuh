@@ -111,6 +111,16 @@ struct Params {
   uint32_t rs_expect;                  // counter value that means "all world partials of this tile arrived"
   __nv_bfloat16* rs_out;               // this rank's reduced output [rows_per_rank][N]
   int rs_rows_per_rank;
+  // ---- kernel-to-kernel dataflow (consecutive launches of one stream that overlap) -----------
+  // A consumer launched as a programmatic dependent starts while its producer's last wave of tiles still runs and
+  // reads the producer's output row block by row block: the producer's epilogue warps raise `d_done[row / 128]`
+  // once per (tile, warp) after their stores have completed, the consumer's TMA warp waits on `a_ready` (rows of a
+  // K-major A, as in the all-gather) or on `k_ready` (K rows of an MN-major operand) before it loads.
+  uint32_t* d_done;
+  const uint32_t* k_ready;  // one counter per `k_ready_rows` K rows; a K block waits for >= k_ready_value
+  uint32_t k_ready_value;
+  int k_ready_rows;
+  int pdl_trigger;          // let the next launch of the stream start during this kernel's last wave
 };
 
 // ------------------------------------------------------------------------------------------
@@ -306,9 +316,13 @@ gemm_kernel(const __grid_constant__ Params p) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int k_checked = 0;       // K row blocks already seen complete (counters only grow)
+      if (p.pdl_trigger && tile_first + tile_step >= total_tiles) griddep_launch_dependents();
       for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
         const Work wk = get_work(p, tile, (int)cta_rank, CTAS, TILE_N);
         const int m0 = wk.m0, n0 = wk.bn0;
+        // this CTA's last tile: the next launch may take the SMs that other CTAs are about to leave
+        if (p.pdl_trigger && tile + tile_step >= total_tiles && tile != tile_first) griddep_launch_dependents();
         // all-gather: this rank's own rows are read straight from the source shard (no wait);
         // rows that arrive from other GPUs wait for their arrival counter.
         const int own_lo = AG ? p.rank * p.ag_rows_per_rank : 0;
@@ -320,6 +334,15 @@ gemm_kernel(const __grid_constant__ Params p) {
         }
         for (int kb = 0; kb < wk.k_blocks; ++kb) {
           const int ka = wk.ka0 + kb * BK, kbb = wk.kb0 + kb * BK;      // K coordinates in A and in B
+          if (p.k_ready != nullptr) {
+            const int need = (ka + BK - 1) / p.k_ready_rows + 1;
+            while (ok && k_checked < need) {
+              ok = wait_flag_ge(p.k_ready + k_checked, p.k_ready_value, p.status, SITE_LOCAL_FLAG);
+              ++k_checked;
+              if (ok && k_checked == need) fence_proxy_async_all();
+            }
+            if (!ok) { *abort_smem = 1; break; }
+          }
           ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, p.status, SITE_SMEM_EMPTY);
           if (!ok) break;
           const uint32_t sA = sA0 + stage * A_STAGE_BYTES;
@@ -601,6 +624,15 @@ gemm_kernel(const __grid_constant__ Params p) {
         if (PAIR && cta_rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
         else mbar_arrive(tempty_bar(acc));
       }
+      if (EPI != EPI_SCATTER && p.d_done != nullptr) {
+        // this warp's 32 rows of the tile are in global memory: one arrival on the row block's counter
+        if (lane == 0) {
+          tma_store_wait_all<0>();
+          fence_proxy_async_all();
+          red_release_gpu_add(p.d_done + m0 / BM, 1u);
+        }
+        __syncwarp();
+      }
     }
     if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
@@ -646,6 +678,7 @@ gemm_kernel(const __grid_constant__ Params p) {
   }
 
   // ------------------------------------------------------------------------- teardown
+  if (p.pdl_trigger) griddep_launch_dependents();
   tc_fence_before();
   __syncthreads();
   if constexpr (PAIR) cluster_sync_all();   // neither CTA frees TMEM or exits while its peer still uses the pair
@@ -708,6 +741,9 @@ gemm_kernel(const __grid_constant__ Params p) {
       }
     }
   }
+  // A kernel that started before its predecessor had finished does not finish before it: whoever is ordered after
+  // this kernel in the stream is then ordered after the whole chain.
+  griddep_wait();
 }
 
 }  // namespace gemm

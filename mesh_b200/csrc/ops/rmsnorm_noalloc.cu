@@ -3,6 +3,8 @@
 // rmsnorm.cu, only the arithmetic.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cstdint>
+#include <mutex>
 #include "noalloc_api.h"
 #include "../runtime/host_common.h"
 
@@ -126,8 +128,10 @@ __global__ void na_dw_reduce_kernel(const float* __restrict__ partials, float* _
 // Device address of the partials array, looked up once per device with that device current.
 constexpr int NA_MAX_DEVICES = 64;
 float* g_partials_addr[NA_MAX_DEVICES] = {nullptr};
+std::mutex g_partials_lock;
 
 int partials_for_current_device(float** out) {
+  std::lock_guard<std::mutex> hold(g_partials_lock);
   int dev = -1;
   MESH_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= NA_MAX_DEVICES) return set_error(-8, "rmsnorm_bwd_noalloc: device index %d out of range", dev);
@@ -155,6 +159,12 @@ extern "C" int mesh_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   if (cols > MESH_NOALLOC_MAX_COLS)
     return set_error(-3, "rmsnorm_bwd_noalloc: cols (%d) exceeds the built-in scratch (%d columns); use "
                          "mesh_rmsnorm_bwd with your own scratch instead", cols, MESH_NOALLOC_MAX_COLS);
+  // A caller with raw pointers gets an error code for a bad one, not a device fault: the kernels read dy, x, w and
+  // write dx as 16-byte vectors and always write dw.
+  if (!dy || !x || !w || !rstd || !dx || !dw)
+    return set_error(-2, "rmsnorm_bwd_noalloc: a null pointer was passed (dy, x, w, rstd, dx and dw are all required)");
+  if ((((uintptr_t)dy | (uintptr_t)x | (uintptr_t)w | (uintptr_t)dx) & 15) || ((uintptr_t)rstd & 3) || ((uintptr_t)dw & 3))
+    return set_error(-2, "rmsnorm_bwd_noalloc: dy, x, w and dx must be 16-byte aligned, rstd and dw 4-byte aligned");
   float* partials = nullptr;
   if (int rc = partials_for_current_device(&partials)) return rc;
   const int blocks = rows < MESH_NOALLOC_MAX_BLOCKS ? rows : MESH_NOALLOC_MAX_BLOCKS;

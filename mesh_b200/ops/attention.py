@@ -129,6 +129,128 @@ def _ring_stream(device):
     return _RING_STREAMS[key]
 
 
+class _FlashBwd(ctypes.Structure):
+    _fields_ = [("fwd", _Flash), ("dout", c_void_p), ("delta", c_void_p), ("ld_do", c_longlong), ("do_cols", c_int),
+                ("do_col0", c_int), ("dq", c_void_p), ("dk", c_void_p), ("dv", c_void_p), ("dk_acc", c_void_p),
+                ("dv_acc", c_void_p), ("ld_dq", c_longlong), ("ld_dkv", c_longlong)]
+
+
+def flash_attention_backward(q, k, v, out, lse, dout, *, causal=True, window=0, scale=None, q_off=0, q_stride=1,
+                             k_off=0, k_stride=1, delta=None, dq=None, dkv_acc=None):
+    """Gradients of :func:`flash_attention`.  Returns ``(dq fp32 [B,Tq,H,hd], dk, dv)``.
+
+    ``dq`` (fp32) is added to when given.  With ``dkv_acc`` (fp32 ``[2, B, Tk, Hkv, hd]``) the key/value gradients
+    are added to it and ``dk, dv`` are returned as its two halves; otherwise they are fresh bf16 tensors.
+    ``lse`` must be the log-sum-exp over ALL keys the queries attended to (for ring attention: the merged one),
+    and ``delta = rowsum(dout * out)`` of the final output."""
+    B, Tq, H, hd = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    scale = hd ** -0.5 if scale is None else scale
+    dout = dout.contiguous()
+    if delta is None:
+        delta = (dout.float() * out.float()).sum(-1).transpose(1, 2).contiguous()       # [B, H, Tq]
+    if dq is None:
+        dq = torch.zeros((B, Tq, H, hd), dtype=torch.float32, device=q.device)
+    a = _FlashBwd()
+    f = a.fwd
+    f.q, f.ldq, f.q_cols = _view2d(q)
+    f.k, f.ldk, f.k_cols = _view2d(k)
+    f.v, f.ldv, f.v_cols = _view2d(v)
+    f.lse = lse.data_ptr()
+    f.B, f.H, f.Hkv, f.Tq, f.Tk, f.head_dim = B, H, Hkv, Tq, Tk, hd
+    f.causal, f.window = int(causal), int(window)
+    f.q_off, f.q_stride, f.k_off, f.k_stride = q_off, q_stride, k_off, k_stride
+    f.scale = scale
+    f.status = status_block(q.device).data_ptr()
+    a.dout, a.ld_do, a.do_cols = _view2d(dout)
+    a.delta = delta.data_ptr()
+    a.dq, a.ld_dq = dq.data_ptr(), dq.stride(1)
+    if dkv_acc is None:
+        dk = torch.empty((B, Tk, Hkv, hd), dtype=torch.bfloat16, device=q.device)
+        dv = torch.empty_like(dk)
+        a.dk, a.dv, a.ld_dkv = dk.data_ptr(), dv.data_ptr(), dk.stride(1)
+    else:
+        assert dkv_acc.dtype == torch.float32 and dkv_acc.is_contiguous()
+        dk, dv = dkv_acc[0], dkv_acc[1]
+        a.dk_acc, a.dv_acc, a.ld_dkv = dk.data_ptr(), dv.data_ptr(), dk.stride(1)
+    rc = _native.lib().mesh_flash_attention_bwd(ctypes.byref(a), c_void_p(torch.cuda.current_stream().cuda_stream))
+    _native.check(rc, "mesh_flash_attention_bwd")
+    _native.count_launch()
+    return dq, dk, dv
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, window, scale):
+        out, lse = flash_attention(q, k, v, causal=causal, window=window, scale=scale, need_lse=True)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.cfg = (causal, window, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        causal, window, scale = ctx.cfg
+        dq, dk, dv = flash_attention_backward(q, k, v, out, lse, dout, causal=causal, window=window, scale=scale)
+        return dq.to(q.dtype), dk, dv, None, None, None
+
+
+def attention(q, k, v, *, causal=True, window=0, scale=None):
+    """Differentiable attention on the flash kernels (``q [B, T, H, hd]``, ``k, v [B, T, Hkv, hd]``, bf16)."""
+    return _Attention.apply(q, k, v, causal, window, scale)
+
+
+def _ring_positions(r, src, P, T, striped):
+    return (r, P, src, P) if striped else (r * T, 1, src * T, 1)
+
+
+class _RingAttention(torch.autograd.Function):
+    """Ring attention with its backward: the KV chunks make a second trip around the ring together with fp32
+    accumulators of their gradients, each rank adding the part its own queries contribute; one more hop brings
+    every accumulator home."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, comm, causal, striped, scale, overlap=None):
+        out, lse = ring_attention(q, k, v, comm, causal=causal, striped=striped, scale=scale, overlap=overlap)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.cfg = (comm, causal, striped, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        comm, causal, striped, scale = ctx.cfg
+        P, r = comm.world, comm.rank
+        B, T, H, hd = q.shape
+        dout = dout.contiguous()
+        delta = (dout.float() * out.float()).sum(-1).transpose(1, 2).contiguous()
+        dq = torch.zeros((B, T, H, hd), dtype=torch.float32, device=q.device)
+        kv = torch.stack([k, v]).contiguous()
+        dkv = torch.zeros(kv.shape, dtype=torch.float32, device=q.device)
+        ring = [(j, (j + 1) % P) for j in range(P)]
+        for step in range(P):
+            src = (r - step) % P
+            q_off, q_stride, k_off, k_stride = _ring_positions(r, src, P, T, striped)
+            nxt = None
+            if step + 1 < P:
+                nxt = torch.empty_like(kv)
+                comm.permute(nxt, kv, ring)
+            if (not causal) or striped or src <= r:
+                flash_attention_backward(q, kv[0], kv[1], out, lse, dout, causal=causal, scale=scale, q_off=q_off,
+                                         q_stride=q_stride, k_off=k_off, k_stride=k_stride, delta=delta, dq=dq, dkv_acc=dkv)
+            moved = torch.empty_like(dkv)
+            comm.permute(moved, dkv, ring)                    # after the last step this hop brings it home
+            dkv = moved
+            if nxt is not None:
+                kv = nxt
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None, None, None
+
+
+def ring_attention_autograd(q, k, v, comm, *, causal=True, striped=False, scale=None, overlap: bool | None = None):
+    """Differentiable :func:`ring_attention` (returns the output only)."""
+    return _RingAttention.apply(q, k, v, comm, causal, striped, scale, overlap)
+
+
 def attention_ref(q, k, v, causal=True, window=0, scale=None, q_off=0, q_stride=1, k_off=0, k_stride=1):
     """fp32 PyTorch statement (oracle)."""
     B, Tq, H, hd = q.shape

@@ -257,8 +257,20 @@ class SymmetricHeap:
         return self._bump, self._sig_bump
 
     def release(self, mark: tuple[int, int]) -> None:
-        """Give back everything allocated since ``mark`` (stack discipline, same on every rank)."""
-        self._bump, self._sig_bump = mark
+        """Give back everything allocated since ``mark`` (stack discipline, same on every rank; collective).
+
+        Signal words are counters that only grow, and their next owner starts expecting from zero: so the returned
+        signal range is cleared here, after every rank's work on it has drained and before any rank can hand it out
+        again (barrier on both sides).  Without that, a communicator built on released words would find the old
+        totals and pass its first waits before its peers had published anything."""
+        bump, sig = mark
+        if sig < self._sig_bump:
+            torch.cuda.synchronize(self.device)
+            self.rdv.barrier("heap-release-drained")            # nobody still signals into the range
+            self._bytes[sig:self._sig_bump].zero_()
+            torch.cuda.synchronize(self.device)
+            self.rdv.barrier("heap-release-cleared")            # cleared everywhere before anyone reuses it
+        self._bump, self._sig_bump = bump, sig
 
     # ------------------------------------------------------------------ teardown
     def close(self) -> None:

@@ -17,7 +17,39 @@ def free_port() -> int:
         return s.getsockname()[1]
 
 
-def _child(rank: int, world: int, port: int, fn, args, use_cuda: bool, init_pg: str | None):
+def free_ports(n: int) -> list[int]:
+    """``n`` distinct free ports, found by holding ``n`` bound sockets at once (a port number derived by
+    arithmetic from another one is not reserved and may be in use)."""
+    socks = []
+    try:
+        for _ in range(n):
+            s = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+            s.bind(("127.0.0.1", 0))
+            socks.append(s)
+        return [s.getsockname()[1] for s in socks]
+    finally:
+        for s in socks:
+            s.close()
+
+
+def _exit_barrier(store, rank: int, world: int, timeout_s: float = 120.0) -> None:
+    """Every rank says that it is through; a rank that failed publishes ``spawn-poison`` instead, and the ranks that
+    wait here leave at once with an error rather than after the full timeout."""
+    import time
+    store.set(f"spawn-exit/{rank}", b"1")
+    keys = [f"spawn-exit/{r}" for r in range(world)]
+    deadline = time.monotonic() + timeout_s
+    while True:
+        if store.check(keys):
+            return
+        if store.check(["spawn-poison"]):
+            raise RuntimeError(f"rank {rank}: another rank failed ({store.get('spawn-poison').decode(errors='replace')})")
+        if time.monotonic() > deadline:
+            raise TimeoutError(f"rank {rank}: not every rank reached the end within {timeout_s}s")
+        time.sleep(0.005)
+
+
+def _child(rank: int, world: int, port: int, aux_port: int, fn, args, use_cuda: bool, init_pg: str | None):
     import torch
     import torch.distributed as dist
     from ..runtime.rendezvous import Rendezvous
@@ -27,7 +59,7 @@ def _child(rank: int, world: int, port: int, fn, args, use_cuda: bool, init_pg: 
         import faulthandler
         faulthandler.dump_traceback_later(watchdog, exit=False)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank))
+                      LOCAL_RANK=str(rank), MESH_AUX_PORT=str(aux_port))
     if use_cuda:
         torch.cuda.set_device(rank)
     store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=120),
@@ -38,7 +70,7 @@ def _child(rank: int, world: int, port: int, fn, args, use_cuda: bool, init_pg: 
     rdv = Rendezvous(dist.PrefixStore("rdv", store), rank, world, timeout_s=120.0)
     try:
         fn(rank, world, rdv, *args)
-        rdv.barrier("spawn-exit")
+        _exit_barrier(store, rank, world)
         # Rank 0's process hosts the store.  It may leave the barrier first, and a store that goes away while another
         # rank is still reading the barrier's keys looks to that rank like a peer that never arrived: so the host
         # stays until every other rank has said that it is through.
@@ -46,8 +78,12 @@ def _child(rank: int, world: int, port: int, fn, args, use_cuda: bool, init_pg: 
             store.set(f"spawn-bye/{rank}", b"1")
         elif world > 1:
             store.wait([f"spawn-bye/{r}" for r in range(1, world)], timedelta(seconds=120))
-    except BaseException:
+    except BaseException as e:
         traceback.print_exc()
+        try:
+            store.set("spawn-poison", f"rank {rank}: {type(e).__name__}".encode())
+        except Exception:
+            pass
         raise
     finally:
         if init_pg and dist.is_initialized():
@@ -57,8 +93,8 @@ def _child(rank: int, world: int, port: int, fn, args, use_cuda: bool, init_pg: 
 def spawn_ranks(fn, world: int, *args, use_cuda: bool = False, init_pg: str | None = None, timeout: float = 600.0):
     """Run ``fn`` on ``world`` ranks and raise if any child fails.  ``fn`` must be importable."""
     import torch.multiprocessing as mp
-    port = free_port()
-    ctx = mp.start_processes(_child, args=(world, port, fn, args, use_cuda, init_pg), nprocs=world, join=False,
+    port, aux_port = free_ports(2)
+    ctx = mp.start_processes(_child, args=(world, port, aux_port, fn, args, use_cuda, init_pg), nprocs=world, join=False,
                              start_method="spawn")
     import time
     deadline = time.monotonic() + timeout

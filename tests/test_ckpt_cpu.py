@@ -22,6 +22,10 @@ def test_reshard_on_load(tmp_path):
     unequal = {"w": (0, [7, 3])}
     a = load_sharded(tmp_path, 3, 0, 2, unequal)[0]["w"]
     assert a.shape[0] == 7 and torch.equal(a, full["w"][:7])
+    # stored replicated, wanted cut: every rank gets its slice, not the whole tensor
+    cut = {"b": (0, [1, 3])}
+    assert torch.equal(load_sharded(tmp_path, 3, 0, 2, cut)[0]["b"], full["b"][:1])
+    assert torch.equal(load_sharded(tmp_path, 3, 1, 2, cut)[0]["b"], full["b"][1:])
     # a step that began but never committed is ignored
     with open(tmp_path / "journal.jsonl", "a") as j:
         j.write(json.dumps({"event": "begin", "step": 9, "world": 4}) + "\n" + '{"event": "comm')

@@ -22,7 +22,7 @@ def _run(rank, world, rdv):
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("mesh", rank=rank, world_size=world,
-                            init_method=f"tcp://127.0.0.1:{int(os.environ['MASTER_PORT']) + 1}")
+                            init_method=f"tcp://127.0.0.1:{os.environ['MESH_AUX_PORT']}")
     try:
         for dtype, n in [(torch.float32, 1000), (torch.bfloat16, 4099), (torch.float16, 64), (torch.int32, 33),
                          (torch.float32, 1 << 20), (torch.bfloat16, (3 << 20) + 8), (torch.int64, 7)]:
@@ -71,12 +71,12 @@ def _run(rank, world, rdv):
         dist.reduce(r, dst=0)
         if rank == 0:
             torch.testing.assert_close(r.cpu(), torch.stack(ins).sum(0), atol=1e-4, rtol=1e-5)
+        comm = dist.group.WORLD._gpu() if hasattr(dist.group.WORLD, "_gpu") else None
         if world > 1:
             nxt, prv = (rank + 1) % world, (rank - 1) % world
             big = ins[rank].repeat(3000)[: (5 << 20)].to(dev)            # 20 MB: several slot-sized pieces
             got = torch.empty_like(big)
             from mesh_b200.distributed import process_group as pgm
-            comm = dist.group.WORLD._gpu() if hasattr(dist.group.WORLD, "_gpu") else None
             if comm is not None:
                 comm.permute(got, big, [(r_, (r_ + 1) % world) for r_ in range(world)])
                 assert torch.equal(got.cpu(), ins[prv].repeat(3000)[: (5 << 20)])
@@ -86,6 +86,43 @@ def _run(rank, world, rdv):
                 x = torch.empty(77, device=dev)
                 dist.recv(x, src=0)
                 assert torch.equal(x.cpu(), ins[0][:77])
+        if world > 1 and comm is not None:
+            # Staging alternates call by call: a run of broadcasts from one root must not overwrite a piece that a
+            # slow reader has not pulled yet.  Small staging so that one tensor takes many pieces; the last rank
+            # starts late (host sleep before its launches) and every broadcast carries different data.
+            import time
+            from mesh_b200.distributed.comm import Communicator
+            mark = comm.heap.mark()
+            small = Communicator(comm.heap, staging_bytes=1 << 20, p2p_slot_bytes=1 << 20)
+            torch.cuda.synchronize()
+            for rep in range(3):
+                if rank == world - 1:
+                    time.sleep(0.2)
+                for j in range(5):
+                    want = (torch.arange(3 << 18, dtype=torch.float32) * (j + 1) + rep).to(dev)     # 3 MiB: 3 pieces
+                    t = want.clone() if rank == 0 else torch.zeros_like(want)
+                    small.broadcast(t, 0)
+                    assert torch.equal(t, want), (rep, j)
+                x = ins[rank][:4096].to(dev)
+                small.reduce(x, 0)
+                y = ins[rank][:4096].to(dev) * 2
+                small.reduce(y, 0)
+                z = ins[rank][:4096].to(dev) * 3
+                small.reduce(z, 0)
+                if rank == 0:
+                    tot = torch.stack(ins).sum(0)[:4096]
+                    for got, f in ((x, 1), (y, 2), (z, 3)):
+                        torch.testing.assert_close(got.cpu(), tot * f, atol=1e-3, rtol=1e-5)
+            # released signal words are handed out again: their new owner must find them at zero, or its first waits
+            # pass before the peers have published (the late rank makes that visible as a wrong sum)
+            comm.heap.release(mark)
+            again = Communicator(comm.heap, staging_bytes=1 << 20, p2p_slot_bytes=1 << 20)
+            for rep in range(3):
+                if rank == world - 1:
+                    time.sleep(0.1)
+                v = ins[rank][:2048].to(dev) + rep
+                again.all_reduce(v)
+                torch.testing.assert_close(v.cpu(), torch.stack(ins).sum(0)[:2048] + rep * world, atol=1e-3, rtol=1e-5)
         dist.barrier()
         check_status()
     finally:

@@ -11,7 +11,7 @@ def _pg_rank(rank, world, rdv):
     import mesh_b200.distributed.process_group  # noqa: F401  (registers "mesh")
     import os
     dist.init_process_group("mesh", rank=rank, world_size=world,
-                            init_method=f"tcp://127.0.0.1:{int(os.environ['MASTER_PORT']) + 1}")
+                            init_method=f"tcp://127.0.0.1:{os.environ['MESH_AUX_PORT']}")
     try:
         t = torch.full((5,), float(rank + 1))
         dist.all_reduce(t)

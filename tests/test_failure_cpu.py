@@ -5,6 +5,7 @@ import subprocess
 import sys
 import textwrap
 
+import pytest
 import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -94,3 +95,19 @@ def test_supervisor_restarts_once_and_resumes(tmp_path):
     events = [json.loads(l)["event"] for l in r.stderr.splitlines() if l.startswith("{")]
     assert events.count("launched") == 2 and "rank_failed" in events and events[-1] == "finished"
     assert (tmp_path / "done-0-1").exists() and int((tmp_path / "done-1-1").read_text()) >= 3   # resumed, not restarted from 0
+
+
+def _one_rank_raises(rank, world, rdv):
+    if rank == 1:
+        raise ValueError("injected failure on rank 1")
+
+
+def test_a_failed_rank_releases_its_peers_from_the_exit_barrier_at_once():
+    """A rank that raises publishes a poison key; the ranks waiting at the end leave with an error in seconds
+    rather than after the barrier's full timeout."""
+    import time
+    from mesh_b200.utils.launch import spawn_ranks
+    t0 = time.monotonic()
+    with pytest.raises(Exception):
+        spawn_ranks(_one_rank_raises, 3, timeout=100.0)
+    assert time.monotonic() - t0 < 60.0
