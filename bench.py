@@ -7,8 +7,9 @@ E2B-class decode tokens/s as a secondary record.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
 
-``--impl mesh`` (default) runs this package's fused kernels; ``--impl baseline`` runs the stock
-NCCL + cuBLAS restatement in ``baseline/``; ``--impl reference`` reports why the reference itself
+``--impl mesh`` (default) runs this package's fused kernels and, in the same process and interleaved
+with them, the stock NCCL + cuBLAS restatement in ``baseline/`` (``vs_baseline`` carries the ratio);
+``--impl baseline`` runs only the stock arm; ``--impl reference`` reports why the reference itself
 cannot run on this hardware.  Rank 0 prints one JSON line.
 """
 from __future__ import annotations
@@ -59,6 +60,17 @@ class ClockSampler:
     def count(self) -> int:
         return len(self.lines)
 
+    def sm_since(self, mark: int) -> list[float]:
+        """SM clocks (MHz) of the samples delivered since ``count()`` returned ``mark``."""
+        out = []
+        for ln in self.lines[mark:]:
+            f = [t.strip() for t in ln.split(",")]
+            try:
+                out.append(float(f[1]))
+            except (IndexError, ValueError):
+                pass
+        return out
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -100,6 +112,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="mesh", choices=["mesh", "baseline", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the secondary E2B-class decode record")
+    ap.add_argument("--no-stock", action="store_true", help="with --impl mesh: skip the in-process stock arm (no vs_baseline)")
+    ap.add_argument("--blocks", type=int, default=4, help="comparison blocks per arm (each about 0.25 s of steps)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -128,91 +142,144 @@ def main() -> int:
     dy = torch.randn(TOKENS, D_MODEL, generator=g).bfloat16()[rank * rows:(rank + 1) * rows].to(dev)
     x_dev = x_host.to(dev).requires_grad_(True)
 
+    # ---- the two arms.  "mesh": this package's fused kernels through its public layer.  "stock": the same layer
+    # restated with torch.distributed (NCCL) collectives and cuBLAS GEMMs (baseline/tp_ffn.py).  With --impl mesh both
+    # are built and the stock arm is timed in the same process, interleaved with the mesh arm, for the ratio.
+    arms: dict[str, dict] = {}
     if args.impl == "mesh":
+        from mesh_b200.ops.loss import dot_sum
         from mesh_b200.parallel.layers import TPGatedFFN
         layer = TPGatedFFN(D_MODEL, D_FF, ctx, act="silu", sequence_parallel=True, seed=7)
-        params = list(layer.parameters())
-
-        def step(x):
-            return layer(x)
-    else:
-        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__))))
+        arms["mesh"] = {"step": layer, "params": list(layer.parameters()), "loss": lambda y: dot_sum(y, dy)}
+    if args.impl == "baseline" or not args.no_stock:
         from baseline.tp_ffn import tp_ffn
         gw = torch.Generator(device="cpu").manual_seed(7)
         sl = slice(rank * Fl, (rank + 1) * Fl)
         wg = torch.empty(D_FF, D_MODEL).normal_(0, 0.02, generator=gw)[sl].to(dev, torch.bfloat16).requires_grad_(True)
         wu = torch.empty(D_FF, D_MODEL).normal_(0, 0.02, generator=gw)[sl].to(dev, torch.bfloat16).requires_grad_(True)
         wd = torch.empty(D_MODEL, D_FF).normal_(0, 0.02, generator=gw)[:, sl].contiguous().to(dev, torch.bfloat16).requires_grad_(True)
-        params = [wg, wu, wd]
         grp = ctx.group if world > 1 else None
-
-        def step(x):
-            return tp_ffn(x, wg, wu, wd, grp)
+        arms["stock"] = {"step": lambda x: tp_ffn(x, wg, wu, wd, grp), "params": [wg, wu, wd],
+                         "loss": lambda y: (y.float() * dy.float()).sum()}
+    main_arm = "mesh" if args.impl == "mesh" else "stock"
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
-
-    def zero_grads():
-        for p in params:
-            p.grad = None
-        x_dev.grad = None
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def run_device_step():
-        y = step(x_dev)
-        y.backward(dy)
+    def device_step(arm):
+        for p in arm["params"]:
+            p.grad = None
+        x_dev.grad = None
+        arm["step"](x_dev).backward(dy)
 
-    # End to end, the input of every step comes from pinned host memory.  The package's input pipeline
-    # (mesh_b200.utils.data.DevicePrefetcher, used by both arms) copies the input of step i+1 on a side stream while
-    # step i computes: every step still pays one host-to-device copy and waits for its own input.
+    def timed_steps(arm, k):
+        """k steps, each between its own pair of CUDA events, L2 flushed (untimed) before each; per-step ms."""
+        evs = []
+        for _ in range(k):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); device_step(arm); e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in evs]
+
+    # End to end, the input of every step comes from pinned host memory and the step's loss is read on the host.
+    # The package's input pipeline (mesh_b200.utils.data.DevicePrefetcher, used by both arms) copies the input of step
+    # i+1 on a side stream while step i computes; the loss goes to pinned memory with an asynchronous copy at the end of
+    # the step and is read one step later (the usual lagged logging of a training loop), the last one before the
+    # region ends: every step pays one host-to-device copy of its input and one device-to-host read of its loss.
     from mesh_b200.utils.data import DevicePrefetcher
     import itertools
     prefetch = DevicePrefetcher(itertools.repeat(x_host), dev, depth=2)
+    loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
 
-    def run_e2e_step():
-        x = prefetch.next().detach().requires_grad_(True)                 # this step's input, copied from pinned memory
-        y = step(x)
-        loss = (y.float() * dy.float()).sum()
-        loss.backward()
-        return float(loss.item())                                         # D2H read of the step's result
+    def e2e_steps(arm, k):
+        evs, losses, pending = [], [], None
+        for i in range(k):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for p in arm["params"]:
+                p.grad = None
+            x = prefetch.next().detach().requires_grad_(True)             # this step's input, copied from pinned memory
+            y = arm["step"](x)
+            loss = arm["loss"](y.detach())                                # sum(y * dy): its gradient is dy
+            y.backward(dy)
+            loss_host[i & 1].copy_(loss, non_blocking=True)               # D2H of the step's result
+            e1.record()
+            if pending is not None:
+                pending[0].synchronize()
+                losses.append(float(loss_host[pending[1]]))
+            pending = (e1, i & 1)
+            evs.append((e0, e1))
+        pending[0].synchronize()
+        losses.append(float(loss_host[pending[1]]))
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in evs], losses
 
-    # ---- device-timed region: K steps, L2 flushed (untimed) between them
-    for _ in range(args.warmup):
-        zero_grads(); run_device_step()
+    def max_over_ranks(vals):
+        t = torch.tensor(vals, device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t]
+
+    # ---- warm-up of every arm, then the headline: exactly K device-timed steps of the main arm
+    for arm in arms.values():
+        for _ in range(args.warmup):
+            device_step(arm)
     barrier()
     sampler = ClockSampler(physical_gpu_index(dev.index))
     sampler.start()
     launches0 = _native.launch_count
-    evs = []
     barrier()
     t_wall0 = time.perf_counter()
-    for _ in range(args.steps):
-        zero_grads()
-        flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(); run_device_step(); e1.record()
-        evs.append((e0, e1))
+    head = timed_steps(arms[main_arm], args.steps)
     barrier()
     t_wall1 = time.perf_counter()
     launches = _native.launch_count - launches0
-    dev_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    dev_ms = sum(head) / args.steps
 
-    # ---- end-to-end through the public API: H2D of the step's input + D2H of its result, every step
-    for _ in range(args.warmup):
-        zero_grads(); run_e2e_step()
+    # ---- end to end, K steps of the main arm
+    e2e_steps(arms[main_arm], args.warmup)
     barrier()
-    e2e_evs = []
-    for _ in range(args.steps):
-        zero_grads()
-        flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(); loss_val = run_e2e_step(); e1.record()
-        e2e_evs.append((e0, e1))
+    e2e, losses = e2e_steps(arms[main_arm], args.steps)
     barrier()
-    e2e_ms = sum(a.elapsed_time(b) for a, b in e2e_evs) / args.steps
+    e2e_ms = sum(e2e) / args.steps
+    dev_ms, e2e_ms = max_over_ranks([dev_ms, e2e_ms])
+
+    # ---- sustained comparison: blocks of steps of each arm in turn (A B A B ...), every block long enough for the
+    # clock sampler to see it; medians per arm, with the SM clock that each arm ran at
+    compare = None
+    if len(arms) == 2:
+        block_steps = max(args.steps, int(0.25 / max(dev_ms * 1e-3, 1e-5)))
+        per = {name: {"dev": [], "e2e": [], "mhz": []} for name in arms}
+        for name in arms:
+            e2e_steps(arms[name], args.warmup)
+        for _ in range(args.blocks):
+            for name in ("mesh", "stock"):
+                barrier()
+                mark = sampler.count()
+                per[name]["dev"] += timed_steps(arms[name], block_steps)
+                per[name]["e2e"] += e2e_steps(arms[name], block_steps)[0]
+                per[name]["mhz"] += sampler.sm_since(mark)
+        med = {}
+        for name in arms:
+            d, e = max_over_ranks([statistics.median(per[name]["dev"]), statistics.median(per[name]["e2e"])])
+            mhz = statistics.median(per[name]["mhz"]) if per[name]["mhz"] else None
+            med[name] = {"us": round(d * 1e3, 2), "e2e_us": round(e * 1e3, 2), "sm_mhz_median": mhz,
+                         "us_x_ghz": round(d * mhz, 1) if mhz else None, "steps": len(per[name]["dev"])}
+        compare = {"ratio": round(med["stock"]["us"] / med["mesh"]["us"], 4),
+                   "e2e_ratio": round(med["stock"]["e2e_us"] / med["mesh"]["e2e_us"], 4),
+                   "baseline_value": med["stock"]["us"], "baseline_e2e": med["stock"]["e2e_us"],
+                   "mesh_value": med["mesh"]["us"], "mesh_e2e": med["mesh"]["e2e_us"],
+                   "direction": "stock PyTorch+NCCL+cuBLAS arm / this package, same process, interleaved blocks; > 1 = this package is faster",
+                   "published_baseline": None, "arms": med,
+                   "method": f"{args.blocks} blocks x {block_steps} steps per arm, alternating; median per-step CUDA-event time, max over ranks"}
+
     # nvidia-smi needs a few hundred milliseconds to deliver its first samples, and K steps can be over sooner:
     # the same load keeps running (untimed) until rank 0 has three samples taken under it, at most 3 seconds
     t_limit = time.perf_counter() + 3.0
@@ -225,19 +292,14 @@ def main() -> int:
         if not int(need):
             break
         for _ in range(10):
-            zero_grads(); run_device_step()
+            device_step(arms[main_arm])
         torch.cuda.synchronize()
         appended += 10
     clocks = sampler.stop()
-    clocks["sampling"] = f"nvidia-smi every 50 ms from the start of the timed region; {appended} untimed steps of the same load appended"
+    clocks["sampling"] = (f"nvidia-smi every 50 ms from the start of the timed region through the comparison blocks; "
+                          f"{appended} untimed steps of the same load appended")
 
-    # ---- max over ranks
-    t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = float(t[0]), float(t[1])
-
-    if args.impl == "mesh":
+    if "mesh" in arms:
         from mesh_b200.utils.status import check_status
         check_status()
 
@@ -258,7 +320,7 @@ def main() -> int:
         line = {
             "metric": "tp_ffn_period_us", "value": round(dev_ms * 1e3, 2), "unit": "us per layer (fwd+bwd)",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms, 5),
-            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": compare, "dtype": "bf16",
             "data": "synthetic (N(0,1) activations, N(0,0.02) random-init weights)", "impl": args.impl,
             "config": {"model": "sequence-parallel SwiGLU FFN, x[4096,4096], d_ff 14336", "global_batch": TOKENS,
                        "seq_len": TOKENS, "parallelism": f"tp{world}+sp", "l2": "256 MiB flush write between steps (untimed)",
@@ -268,8 +330,8 @@ def main() -> int:
             "wall_ms_per_step_incl_flush": round((t_wall1 - t_wall0) * 1e3 / args.steps, 4),
             "clocks": clocks,
             "e2e": {"value": round(e2e_ms * 1e3, 2), "unit": "us per layer (fwd+bwd) incl. H2D input + D2H loss",
-                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4,
-                    "input_pipeline": "pinned host input copied by a double-buffered prefetcher on a side stream (one copy per step, overlapping the previous step)"},
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4, "last_loss": losses[-1],
+                    "input_pipeline": "pinned host input copied by a double-buffered prefetcher on a side stream (one copy per step, overlapping the previous step); loss copied to pinned memory at the end of its step and read one step later"},
             "gpu_launches": launches if args.impl == "mesh" else 0,
         }
         if decode is not None:

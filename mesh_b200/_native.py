@@ -15,9 +15,14 @@ _lib = None
 launch_count = 0   # kernels of this library launched by this process (bench accounting)
 
 
+on_launch = None   # set by the runtime service: mirrors the count into the process's stats block
+
+
 def count_launch(n: int = 1) -> None:
     global launch_count
     launch_count += n
+    if on_launch is not None:
+        on_launch(n)
 
 MAX_RANKS = 8
 

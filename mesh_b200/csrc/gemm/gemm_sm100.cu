@@ -127,7 +127,7 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   p.k_ready_rows = a->k_ready_rows > 0 ? a->k_ready_rows : BM;
   if (a->k_ready != nullptr && (p.k_ready_rows % BK)) return set_error(-5, "gemm: k_ready_rows must be a multiple of 64");
   p.pdl_trigger = (a->pdl & 2) ? 1 : 0;
-  const bool dependent = (a->pdl & 1) != 0;
+  const bool dependent = (a->pdl & 1) != 0 && pdl_enabled();
   p.tiles = (const TileDesc*)a->tiles;
   p.n_tiles_dev = (const int*)a->n_tiles_dev;
   p.a_ready = (const uint32_t*)a->a_ready;

@@ -327,7 +327,7 @@ gemm_kernel(const __grid_constant__ Params p) {
         // rows that arrive from other GPUs wait for their arrival counter.
         const int own_lo = AG ? p.rank * p.ag_rows_per_rank : 0;
         const bool own = AG && m0 >= own_lo && m0 < own_lo + p.ag_rows_per_rank;
-        if (p.a_ready != nullptr && !own) {
+        if (p.a_ready != nullptr && !own && (p.tiles != nullptr || m0 < p.M)) {
           ok = wait_flag_ge(p.a_ready + m0 / p.a_ready_rows, p.a_ready_value, p.status, SITE_LOCAL_FLAG);
           if (!ok) { *abort_smem = 1; break; }
           fence_proxy_async_all();   // data was written through the generic proxy, TMA reads it
@@ -624,7 +624,7 @@ gemm_kernel(const __grid_constant__ Params p) {
         if (PAIR && cta_rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
         else mbar_arrive(tempty_bar(acc));
       }
-      if (EPI != EPI_SCATTER && p.d_done != nullptr) {
+      if (EPI != EPI_SCATTER && p.d_done != nullptr && m0 < p.M) {
         // this warp's 32 rows of the tile are in global memory: one arrival on the row block's counter
         if (lane == 0) {
           tma_store_wait_all<0>();

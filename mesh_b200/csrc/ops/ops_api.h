@@ -21,6 +21,13 @@ int mesh_rmsnorm_bwd_blocks(int rows);
 int mesh_rope(void* x, const int* positions, const float* cos_t, const float* sin_t, int tokens, int heads,
               int head_dim, long long ld, int inverse, void* stream);
 
+// out[0] = sum(a[i] * b[i]) for bf16 a, b of n elements (fp32 accumulation, one launch, result independent of block
+// timing).  Scratch: `partials` fp32[mesh_dot_sum_blocks()] and a zero-initialised `ticket` word, left at zero; calls
+// that share scratch must be ordered on one stream.
+int mesh_dot_sum_bf16(const void* a, const void* b, long long n, float* out, float* partials, unsigned int* ticket,
+                      void* stream);
+int mesh_dot_sum_blocks(void);
+
 // softmax over experts then top-k (k <= 8, experts <= 256).  bias (fp32[experts], may be NULL) is added
 // to the logits before the softmax.  weights fp32[tokens,k] (renormalised over the k when renorm),
 // indices int32[tokens,k]; ties go to the lower expert index.

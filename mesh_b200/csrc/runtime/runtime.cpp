@@ -6,6 +6,7 @@
 // children as a state machine (rdma/mesh-children.c:73-242), health turns (rdma/mesh-records.c:1433),
 // `mesh-stat` (rdma/mesh-stat.c:65-118), and the engine bridge builtins (xonotic/darkplaces-work/mesh_ipc.c:674-704).
 // On NVLink there is no NIC daemon: kernels move the data; this thread only keeps liveness and counters.
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <cstdint>
@@ -85,7 +86,9 @@ int mesh_runtime_start(const char* group, int rank, int world, double heartbeat_
       g_stats->heartbeat_ns.store(now_ns());
       const uint64_t dl = g_stats->deadline_ns.load();
       if (dl && now_ns() > dl) g_stats->abort_flag.store(1);
-      std::this_thread::sleep_for(period);
+      // sleep in short slices so that a stop request is honoured within milliseconds, not a heartbeat period
+      for (auto left = period; left.count() > 0 && g_run.load(); left -= std::chrono::milliseconds(20))
+        std::this_thread::sleep_for(std::min<std::chrono::milliseconds>(left, std::chrono::milliseconds(20)));
     }
   });
   return adopt ? 1 : 0;

@@ -85,11 +85,45 @@ class Communicator:
         self._rcvd = [0] * self.world          # ... and on the channel from each source
         self.L = _native.lib()
         self.max_blocks = self.L.mesh_coll_max_blocks()
-        self.one_shot_max = config().one_shot_max_bytes
+        self.one_shot_max = self._one_shot_threshold()
+        self._svc = None
+        try:
+            from .context import current_or_none
+            from ..runtime import service
+            ctx = current_or_none()
+            if ctx is not None and ctx.service:
+                self._svc = service
+        except Exception:
+            self._svc = None
         self.use_nvls = bool(config().nvls and getattr(heap, "mc_ptr", 0))
         self.calls = 0
 
     # ------------------------------------------------------------------ plumbing
+    def _one_shot_threshold(self) -> int:
+        """Largest message that goes one-shot.  ``MESH_ONE_SHOT_MAX`` when set; otherwise the planner's latency +
+        bytes / bandwidth model decides (one-shot moves ``(world - 1) x n`` bytes into every rank in one round,
+        two-shot ``2 (world - 1) / world x n`` in two): the threshold is where its choice changes."""
+        import os
+        if os.environ.get("MESH_ONE_SHOT_MAX") or self.world == 1:
+            return config().one_shot_max_bytes
+        try:
+            from ..config import capacity
+            from ..runtime.plan import choose_allreduce as _choose
+            alpha = float(capacity().get("collective_alpha_us", 5.0))      # measured launch-to-first-byte latency
+            choose_allreduce = lambda n, w: _choose(n, w, False, alpha)
+            lo, hi = 1 << 10, 64 << 20
+            if choose_allreduce(lo, self.world)[0] != "one_shot":
+                return lo
+            while hi - lo > (4 << 10):
+                mid = (lo + hi) // 2
+                if choose_allreduce(mid, self.world)[0] == "one_shot":
+                    lo = mid
+                else:
+                    hi = mid
+            return min(lo, self.staging_bytes)
+        except Exception:
+            return config().one_shot_max_bytes
+
     def _blocks(self, nbytes: int) -> int:
         # one 16-byte vector per thread (512 threads) until every SM has a block
         return max(1, min(self.max_blocks, (nbytes + (8 << 10) - 1) // (8 << 10)))
@@ -111,7 +145,16 @@ class Communicator:
         a.staging_bytes = self.staging_bytes
         a.status = status_block(self.heap.device).data_ptr()
         a.nblocks = nblocks
+        if self._svc is not None:
+            self._svc.count("collectives", 1)
         return a
+
+    def _bytes_out(self, per_peer: int) -> None:
+        """Stats block of the runtime service: bytes this rank's links carry to each peer for one collective."""
+        if self._svc is not None and per_peer:
+            for peer in range(self.world):
+                if peer != self.rank:
+                    self._svc.count("bytes", per_peer, peer)
 
     @staticmethod
     def _check(t: torch.Tensor, name: str) -> None:
@@ -150,6 +193,7 @@ class Communicator:
                 _native.count_launch()
                 pos += cnt
                 continue
+            self._bytes_out(nbytes if not two else 2 * nbytes // self.world)
             a = self._args(nb, two_step=two)
             rc = self.L.mesh_coll_allreduce(ctypes.byref(a), c_void_p(flat_in[pos:].data_ptr() if n else 0),
                                             c_void_p(flat_out[pos:].data_ptr() if n else 0), c_uint64(cnt), c_int(dt),
@@ -172,6 +216,7 @@ class Communicator:
         if inp.numel() * inp.element_size() > self.staging_bytes:
             return self._reduce_scatter_pieces(out, inp, op, counts)
         arr = (c_uint64 * self.world)(*counts)
+        self._bytes_out(inp.numel() * inp.element_size() // self.world)
         a = self._args(self._blocks(inp.numel() * inp.element_size()))
         rc = self.L.mesh_coll_reduce_scatter(ctypes.byref(a), c_void_p(inp.data_ptr()), c_void_p(out.data_ptr()), arr,
                                              c_int(self._dtype(inp)), c_int(_op_code(op)), _stream())
@@ -228,6 +273,7 @@ class Communicator:
         cap = self.staging_bytes // es
         pieces = max(1, (max(counts) + cap - 1) // cap)
         flat_in, flat_out = inp.view(-1), out.view(-1)
+        self._bytes_out(inp.numel() * es)
         for p in range(pieces):
             lo = [c * p // pieces for c in counts]
             hi = [c * (p + 1) // pieces for c in counts]
@@ -261,6 +307,7 @@ class Communicator:
         if soff[-1] > self.staging_bytes:
             raise ValueError(f"all_to_all: {soff[-1]} bytes exceed the staging buffer ({self.staging_bytes}); "
                              "raise staging_bytes or split the call")
+        self._bytes_out(soff[-1] // max(1, W))
         a = self._args(32)
         rc = self.L.mesh_coll_alltoallv(ctypes.byref(a), c_void_p(inp.data_ptr()), c_void_p(out.data_ptr()),
                                         (c_uint64 * (W + 1))(*soff), (c_uint64 * (W + 1))(*roff), _stream())

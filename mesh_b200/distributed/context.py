@@ -23,6 +23,8 @@ class MeshContext:
         self.rank, self.world, self.device, self.rdv, self.group = rank, world, device, rdv, group
         self._heap = None
         self.launches = 0          # kernels of this library launched (bench accounting)
+        self.monitor = None        # ErrorMonitor of this process's device (CUDA only)
+        self.service = False       # runtime service (stats block + heartbeat thread) running
 
     @property
     def heap(self):
@@ -32,6 +34,10 @@ class MeshContext:
             cfg = config()
             self._heap = SymmetricHeap(self.rdv, cfg.heap_bytes, self.device.index, signal_bytes=cfg.signal_bytes,
                                        multicast=cfg.nvls and self.world > 1 and os.environ.get("MESH_NVLS", "0") == "1")
+            if self.service:
+                from ..runtime import service
+                for peer in range(min(self.world, 8)):                   # every peer's segment is mapped: the channel is up
+                    service.channel(peer, "CONNECTED")
         return self._heap
 
     @property
@@ -80,7 +86,35 @@ def init(backend: str | None = None, device: str | torch.device | None = None, t
         store = dist.HashStore()
     rdv = Rendezvous(store, rank, world, timeout_s=timeout_s)
     _ctx = MeshContext(rank, world, device, rdv, group)
+    _start_runtime(_ctx)
     return _ctx
+
+
+def _start_runtime(ctx: "MeshContext") -> None:
+    """The per-process runtime that every job gets: the stats block with its heartbeat thread (what ``meshctl status``
+    and ``meshctl top`` read, and what a supervisor watches) and, on a GPU, the error monitor that spreads the abort
+    flag after the first device-side failure.  ``MESH_RUNTIME=0`` leaves both out (a process that must not start
+    threads).  A missing native library on a CPU-only machine leaves them out too."""
+    if os.environ.get("MESH_RUNTIME", "1") == "0":
+        return
+    from .. import _native
+    cfg = config()
+    try:
+        from ..runtime import service
+        service.start(cfg.group, ctx.rank, ctx.world, cfg.heartbeat_s)
+        service.count("epoch", ctx.rdv.epoch)
+        if cfg.deadline_s > 0:
+            service.deadline(cfg.deadline_s)
+        ctx.service = True
+        _native.on_launch = lambda n: service.count("launches", n)
+    except Exception:
+        ctx.service = False
+    if ctx.is_cuda:
+        try:
+            from ..runtime.monitor import ErrorMonitor
+            ctx.monitor = ErrorMonitor(ctx.device)
+        except Exception:
+            ctx.monitor = None
 
 
 def current_or_none() -> "MeshContext | None":
@@ -97,8 +131,18 @@ def shutdown() -> None:
     global _ctx
     if _ctx is None:
         return
+    # in order: the monitor stops reading status blocks, the heap drains and unmaps, the service says goodbye last
+    if _ctx.monitor is not None:
+        _ctx.monitor.stop()
+        _ctx.monitor = None
     if _ctx._heap is not None:
         _ctx._heap.close()
+    if _ctx.service:
+        from .. import _native
+        from ..runtime import service
+        _native.on_launch = None
+        service.stop(unlink=True)
+        _ctx.service = False
     if dist.is_initialized():
         try:
             dist.barrier()

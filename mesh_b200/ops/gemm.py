@@ -30,10 +30,45 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_trace: list | None = None
+
+
+class trace:
+    """``with trace() as t:`` records a CUDA-event pair around every GEMM launch of the block;
+    ``t.report()`` gives ``[(label, microseconds)]`` (after a synchronize).  For per-kernel breakdowns: meaningful only
+    with launches that do not overlap (``MESH_GEMM_CHAIN=0``)."""
+
+    def __enter__(self):
+        global _trace
+        self.items = []
+        _trace = self.items
+        return self
+
+    def __exit__(self, *exc):
+        global _trace
+        _trace = None
+
+    def report(self):
+        torch.cuda.synchronize()
+        return [(label, e0.elapsed_time(e1) * 1e3) for label, e0, e1 in self.items]
+
+
+def _label(a: _native.GemmArgs) -> str:
+    epi = {EPI_STORE: "store", EPI_GLU_FWD: "glu_fwd", EPI_GLU_BWD: "glu_bwd", EPI_SCATTER: "reduce_scatter"}[a.epi]
+    pre = "all_gather+" if a.ag_src else ""
+    return f"{pre}gemm[{a.M}x{a.N}x{a.K}{' A^T' if a.a_mn else ''}{' B^T' if a.b_mn else ''}]->{epi}"
+
+
 def _launch(args: _native.GemmArgs) -> None:
+    if _trace is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     rc = _native.lib().mesh_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_stream()))
     _native.check(rc, "mesh_gemm_bf16")
     _native.count_launch()
+    if _trace is not None:
+        e1.record()
+        _trace.append((_label(args), e0, e1))
 
 
 def _base_args(a: torch.Tensor, b: torch.Tensor, a_mn: bool, b_mn: bool) -> tuple[_native.GemmArgs, int, int, int]:
@@ -55,11 +90,65 @@ def _base_args(a: torch.Tensor, b: torch.Tensor, a_mn: bool, b_mn: bool) -> tupl
     return g, M, N, K
 
 
+PDL_DEPENDENT, PDL_TRIGGER = 1, 2
+BM = 128
+EPI_WARPS = 4
+
+
+class Done:
+    """Completion counters of a chain of launches: one per 128 rows of a matrix that one kernel writes and the next
+    launches of the stream read while the writer's last tiles are still running (see ``Params`` in
+    csrc/gemm/gemm_sm100.cuh).  Counters only grow; every use of the chain expects ``tiles x 4`` more arrivals."""
+
+    _cache: dict = {}
+
+    def __init__(self, device, row_blocks: int):
+        self.flags = torch.zeros(row_blocks, dtype=torch.int32, device=device)
+        self.total = 0
+
+    @classmethod
+    def get(cls, device, row_blocks: int, tag: str) -> "Done":
+        key = (torch.device(device).index, row_blocks, tag)
+        if key not in cls._cache:
+            cls._cache[key] = cls(device, row_blocks)
+        return cls._cache[key]
+
+    def produce(self, n_tiles: int) -> int:
+        """The writer's launch: returns the counter value that means "this launch has written the row block"."""
+        self.total = (self.total + n_tiles * EPI_WARPS) & 0x7FFFFFFF
+        return self.total
+
+    def ptr(self) -> int:
+        return self.flags.data_ptr()
+
+
+def chain(g: _native.GemmArgs, *, d_done: Done | None = None, a_ready=None, k_ready=None, dependent: bool = False,
+          trigger: bool = False) -> None:
+    """Dataflow attributes of one launch.  ``a_ready`` / ``k_ready``: ``(pointer, value, rows)``."""
+    if d_done is not None:
+        g.d_done = d_done.ptr()
+    if a_ready is not None:
+        g.a_ready, g.a_ready_value, g.a_ready_rows = a_ready
+    if k_ready is not None:
+        g.k_ready, g.k_ready_value, g.k_ready_rows = k_ready
+    g.pdl = (PDL_DEPENDENT if dependent else 0) | (PDL_TRIGGER if trigger else 0)
+
+
+def chaining() -> bool:
+    """Consecutive GEMMs of a layer overlap (dependent launches + row-block counters) unless ``MESH_GEMM_CHAIN=0``."""
+    import os
+    return os.environ.get("MESH_GEMM_CHAIN", "1") != "0"
+
+
+def tile_n_for(M: int, N: int) -> int:
+    return _native.lib().mesh_gemm_choose_tile_n(M, N, 0)
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
-         out: torch.Tensor | None = None, num_ctas: int = 0, tile_n: int = 0, pair: int = 0) -> torch.Tensor:
+         out: torch.Tensor | None = None, num_ctas: int = 0, tile_n: int = 0, pair: int = 0, **flow) -> torch.Tensor:
     """``out[M,N] = A[M,K] @ B[N,K]^T`` with fp32 accumulation.
 
-    ``a_mn``: ``a`` is stored ``[K, M]``;  ``b_mn``: ``b`` is stored ``[K, N]``.
+    ``a_mn``: ``a`` is stored ``[K, M]``;  ``b_mn``: ``b`` is stored ``[K, N]``.  ``flow``: see :func:`chain`.
     """
     g, M, N, K = _base_args(a, b, a_mn, b_mn)
     if out is None:
@@ -68,12 +157,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.D, g.ldd, g.d_cols = out.data_ptr(), out.stride(0), out.shape[1]
     g.epi = EPI_STORE
     g.num_ctas, g.tile_n, g.pair = num_ctas, tile_n, pair
+    if flow:
+        chain(g, **flow)
     _launch(g)
     return out
 
 
 def glu_fwd(x: torch.Tensor, w_gate_up: torch.Tensor, *, act: str = "silu", save_gu: bool = True,
-            out: torch.Tensor | None = None, gu: torch.Tensor | None = None):
+            out: torch.Tensor | None = None, gu: torch.Tensor | None = None, **flow):
     """``act(x @ Wg^T) * (x @ Wu^T)`` where ``w_gate_up = [Wg; Wu]`` is ``[2F, K]``.
 
     Returns ``(h[M,F], gu[M,2F] or None)``; ``gu = [g | u]`` is what the backward pass needs.
@@ -101,12 +192,14 @@ def glu_fwd(x: torch.Tensor, w_gate_up: torch.Tensor, *, act: str = "silu", save
         gu = None
     g.status = status_block(x.device).data_ptr()
     g.world = 1
+    if flow:
+        chain(g, **flow)
     _launch(g)
     return out, gu
 
 
 def glu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor, *, act: str = "silu",
-            out: torch.Tensor | None = None) -> torch.Tensor:
+            out: torch.Tensor | None = None, tile_n: int = 0, **flow) -> torch.Tensor:
     """Backward of the GLU through the down projection in one kernel.
 
     ``dH = dy @ w_down`` (``w_down`` is ``[D, F]``, used MN-major) and the epilogue turns it into
@@ -133,6 +226,9 @@ def glu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor, *, act: st
     g.D, g.ldd, g.d_cols = out.data_ptr(), out.stride(0), 2 * F
     g.status = status_block(dy.device).data_ptr()
     g.world = 1
+    g.tile_n = tile_n
+    if flow:
+        chain(g, **flow)
     _launch(g)
     return out
 
@@ -170,8 +266,15 @@ class _GluFFN(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_gate_up, w_down, act):
         x2 = x.reshape(-1, x.shape[-1])
-        h, gu = glu_fwd(x2, w_gate_up, act=act, save_gu=True)
-        y = gemm(h, w_down)
+        M, F = x2.shape[0], w_gate_up.shape[0] // 2
+        if chaining():
+            # the down projection starts during the last wave of the gate/up GEMM and reads h row block by row block
+            done = Done.get(x2.device, (M + BM - 1) // BM, "glu.h")
+            h, gu = glu_fwd(x2, w_gate_up, act=act, save_gu=True, d_done=done, trigger=True)
+            y = gemm(h, w_down, a_ready=(done.ptr(), done.produce((F + 127) // 128), BM), dependent=True)
+        else:
+            h, gu = glu_fwd(x2, w_gate_up, act=act, save_gu=True)
+            y = gemm(h, w_down)
         ctx.save_for_backward(x2, w_gate_up, w_down, h, gu)
         ctx.act = act
         ctx.xshape = x.shape
@@ -181,6 +284,16 @@ class _GluFFN(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w_gate_up, w_down, h, gu = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        if chaining():
+            M, F = dy2.shape[0], w_down.shape[1]
+            done = Done.get(dy2.device, (M + BM - 1) // BM, "glu.dgu")
+            bn = tile_n_for(M, F)
+            dgu = glu_bwd(dy2, w_down, gu, act=ctx.act, tile_n=bn, d_done=done, trigger=True)       # [M, 2F]
+            ready = (done.ptr(), done.produce((F + bn - 1) // bn), BM)
+            dx = gemm(dgu, w_gate_up, b_mn=True, a_ready=ready, dependent=True, trigger=True).reshape(ctx.xshape)
+            dw_down = gemm(dy2, h, a_mn=True, b_mn=True, dependent=True, trigger=True)          # reads nothing of the chain
+            dw_gate_up = gemm(dgu, x2, a_mn=True, b_mn=True, k_ready=ready, dependent=True)      # [2F, D]
+            return dx, dw_gate_up, dw_down, None
         dgu = glu_bwd(dy2, w_down, gu, act=ctx.act)                 # [M, 2F]
         dw_down = gemm(dy2, h, a_mn=True, b_mn=True)                # [D, F]
         dx = gemm(dgu, w_gate_up, b_mn=True).reshape(ctx.xshape)    # [M, D]

@@ -111,6 +111,12 @@ class FusedTPFFN:
         self.y_recv = shared_zone(heap, _Scattered, P, self.rows, d_model)
         self.dx_recv = self.y_recv          # forward and backward never overlap within a rank's stream
         self._saved = None
+        # Row-block completion counters of the two matrices that one launch of a pass writes and the next launches
+        # read while the writer's last tiles are still running (h in the forward pass, [dg|du] in the backward pass).
+        self.chain = G.chaining()
+        self.done_h = G.Done(heap.device, tokens // BM)
+        self.done_dgu = G.Done(heap.device, tokens // BM)
+        self.bwd_tile_n = G.tile_n_for(tokens, self.Fl)
 
     # ---------------------------------------------------------------- kernels
     def _args(self, dev) -> _native.GemmArgs:
@@ -128,6 +134,7 @@ class FusedTPFFN:
         for r in range(self.world):
             g.ag_dst[r] = buf.ptr(r)
             g.ag_flags[r] = flags.ptr(r)
+        self._gathered_ready = (flags.ptr(), expect, BM)
         return buf
 
     def _scatter_args(self, g, zone: _Scattered, out: torch.Tensor):
@@ -155,14 +162,18 @@ class FusedTPFFN:
         g.D, g.ldd, g.d_cols = h.data_ptr(), Fl, Fl
         if save:
             g.D2, g.ldd2, g.d2_cols, g.d_up_cols = gu.data_ptr(), 2 * Fl, 2 * Fl, Fl
+        if self.chain:
+            G.chain(g, d_done=self.done_h, trigger=True)
         G._launch(g)
-        # (2) down GEMM -> reduce-scatter
+        # (2) down GEMM -> reduce-scatter; starts during the last wave of (1) and reads h row block by row block
         y = torch.empty((self.rows, D), dtype=torch.bfloat16, device=dev)
         g = self._args(dev)
         g.A, g.lda, g.a_rows = h.data_ptr(), Fl, M
         g.B, g.ldb, g.b_rows = w_down.data_ptr(), w_down.stride(0), D
         g.M, g.N, g.K = M, D, Fl
         self._scatter_args(g, self.y_recv, y)
+        if self.chain:
+            G.chain(g, a_ready=(self.done_h.ptr(), self.done_h.produce((Fl + 127) // 128), BM), dependent=True)
         G._launch(g)
         if save:
             self._saved = (xbuf, h, gu, w_gate_up, w_down)
@@ -183,9 +194,25 @@ class FusedTPFFN:
         g.epi, g.act = G.EPI_GLU_BWD, G.ACT[self.act]
         g.aux, g.ld_aux, g.d_up_cols = gu.data_ptr(), 2 * Fl, Fl
         g.D, g.ldd, g.d_cols = dgu.data_ptr(), 2 * Fl, 2 * Fl
+        g.tile_n = self.bwd_tile_n
+        dy_ready = self._gathered_ready          # dY row blocks in this rank's gathered buffer (arrival counters)
+        if not self.chain:
+            G._launch(g)
+            dw_down = G.gemm(dybuf.local, h, a_mn=True, b_mn=True)
+            dx = torch.empty((self.rows, D), dtype=torch.bfloat16, device=dev)
+            g = self._args(dev)
+            g.A, g.lda, g.a_rows = dgu.data_ptr(), 2 * Fl, M
+            g.B, g.ldb, g.b_mn = w_gate_up.data_ptr(), w_gate_up.stride(0), 1
+            g.M, g.N, g.K = M, D, 2 * Fl
+            self._scatter_args(g, self.dx_recv, dx)
+            G._launch(g)
+            dw_gate_up = G.gemm(dgu, xbuf.local, a_mn=True, b_mn=True)
+            return dx, dw_gate_up, dw_down
+        # The four launches overlap: each starts during the last wave of the one before it and waits, row block by row
+        # block, for what it reads of (3)'s outputs.  dx goes first: the layer below waits for it.
+        G.chain(g, d_done=self.done_dgu, trigger=True)
         G._launch(g)
-        # (4) dWd = dY^T h   (dY is complete in this rank's gathered buffer once (3) has finished)
-        dw_down = G.gemm(dybuf.local, h, a_mn=True, b_mn=True)
+        dgu_ready = (self.done_dgu.ptr(), self.done_dgu.produce((Fl + self.bwd_tile_n - 1) // self.bwd_tile_n), BM)
         # (5) dx partial = [dg|du] Wgu -> reduce-scatter
         dx = torch.empty((self.rows, D), dtype=torch.bfloat16, device=dev)
         g = self._args(dev)
@@ -193,9 +220,12 @@ class FusedTPFFN:
         g.B, g.ldb, g.b_mn = w_gate_up.data_ptr(), w_gate_up.stride(0), 1
         g.M, g.N, g.K = M, D, 2 * Fl
         self._scatter_args(g, self.dx_recv, dx)
+        G.chain(g, a_ready=dgu_ready, dependent=True, trigger=True)
         G._launch(g)
-        # (6) dWgu = [dg|du]^T X
-        dw_gate_up = G.gemm(dgu, xbuf.local, a_mn=True, b_mn=True)
+        # (4) dWd = dY^T h: K runs over the tokens, every K block waits for its rows of the gathered dY
+        dw_down = G.gemm(dybuf.local, h, a_mn=True, b_mn=True, k_ready=dy_ready, dependent=True, trigger=True)
+        # (6) dWgu = [dg|du]^T X: K blocks wait for their rows of [dg|du]
+        dw_gate_up = G.gemm(dgu, xbuf.local, a_mn=True, b_mn=True, k_ready=dgu_ready, dependent=True)
         return dx, dw_gate_up, dw_down
 
 

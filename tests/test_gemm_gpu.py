@@ -10,12 +10,9 @@ def _rand(shape, scale=1.0, seed=0):
     return (torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * scale).to(torch.bfloat16)
 
 
-def _close(got, want, tol=2e-2):
-    got = got.float()
-    want = want.float()
-    err = (got - want).abs().max().item()
-    ref = want.abs().max().item() + 1e-6
-    assert err / ref < tol, f"max err {err} vs max ref {ref}"
+def _close(got, want, tol=4e-3):
+    from _oracle import assert_close_rms
+    assert_close_rms(got, want, tol=tol)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 512), (200, 264, 328), (4096, 1024, 1024)])
@@ -55,7 +52,7 @@ def test_glu_fwd(act, M, F, K):
     a = torch.nn.functional.silu(g) if act == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
     _close(gu[:, :F], g)
     _close(gu[:, F:], u)
-    _close(h, a * u)
+    _close(h, a * u, 6e-3)
 
 
 @pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
@@ -71,14 +68,16 @@ def test_glu_bwd(act, M, F, D):
     a = torch.nn.functional.silu(g) if act == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
     dh = dy.float() @ wd.float()
     (a * u).backward(dh)
-    _close(out[:, :F], g.grad)
-    _close(out[:, F:], u.grad)
+    _close(out[:, :F], g.grad, 6e-3)
+    _close(out[:, F:], u.grad, 6e-3)
 
 
-def test_glu_ffn_autograd():
+@pytest.mark.parametrize("M,D,F", [(512, 256, 640), (2048, 1024, 4096), (384, 512, 1152)])
+def test_glu_ffn_autograd(M, D, F):
+    """The second shape has several waves of tiles per launch, so the chained launches of a pass (dependent launches
+    gated by row-block counters) really overlap; the third has an odd number of row blocks."""
     from mesh_b200.ops.gemm import glu_ffn
     from mesh_b200.utils.status import check_status
-    M, D, F = 512, 256, 640
     x = _rand((M, D), seed=10).requires_grad_(True)
     wgu = _rand((2 * F, D), 0.05, seed=11).requires_grad_(True)
     wd = _rand((D, F), 0.05, seed=12).requires_grad_(True)
@@ -91,7 +90,29 @@ def test_glu_ffn_autograd():
     u = xr @ wgur[F:].T
     yr = (torch.nn.functional.silu(g) * u) @ wdr.T
     yr.backward(dy.float())
-    _close(y, yr)
-    _close(x.grad, xr.grad, 3e-2)
-    _close(wgu.grad, wgur.grad, 3e-2)
-    _close(wd.grad, wdr.grad, 3e-2)
+    _close(y, yr, 8e-3)
+    _close(x.grad, xr.grad, 8e-3)
+    _close(wgu.grad, wgur.grad, 8e-3)
+    _close(wd.grad, wdr.grad, 8e-3)
+
+
+def test_chained_launches_give_the_same_bits_as_serial_ones(monkeypatch):
+    from mesh_b200.ops.gemm import glu_ffn
+    from mesh_b200.utils.status import check_status
+    M, D, F = 2048, 1024, 4096
+    outs = []
+    for mode in ("1", "0", "1"):
+        monkeypatch.setenv("MESH_GEMM_CHAIN", mode)
+        x = _rand((M, D), seed=10).requires_grad_(True)
+        wgu = _rand((2 * F, D), 0.05, seed=11).requires_grad_(True)
+        wd = _rand((D, F), 0.05, seed=12).requires_grad_(True)
+        for _ in range(3):
+            x.grad = wgu.grad = wd.grad = None
+            y = glu_ffn(x, wgu, wd)
+            y.backward(_rand((M, D), seed=13))
+        check_status()
+        outs.append((y.detach(), x.grad, wgu.grad, wd.grad))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    for a, b in zip(outs[0], outs[2]):
+        assert torch.equal(a, b)

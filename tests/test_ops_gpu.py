@@ -56,3 +56,14 @@ def test_router_topk(E, k):
     wr, ir = router_topk_ref(logits, k, bias)
     assert torch.equal(i, ir)
     torch.testing.assert_close(w, wr, atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("n", [8, 1000, 4096 * 512, 4096 * 4096 + 3])
+def test_dot_sum(n):
+    from mesh_b200.ops.loss import dot_sum
+    a = torch.randn(n, device="cuda").bfloat16()
+    b = torch.randn(n, device="cuda").bfloat16()
+    for _ in range(2):                     # the second call finds the scratch as the first left it
+        got = dot_sum(a, b)
+    want = (a.double() * b.double()).sum()
+    assert abs(float(got) - float(want)) <= 1e-3 * float((a.double() * b.double()).abs().sum().sqrt()) + 1e-3

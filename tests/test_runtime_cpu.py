@@ -95,3 +95,36 @@ def test_engine_bridge_abi():
     assert list(dst) == [2, 4, 6, 8]
     assert L.mesh_gather(h, src, ctypes.c_uint64(6), ctypes.c_uint64(4)) == -1
     L.mesh_close(h)
+
+
+def _job_with_runtime(rank, world, rdv, group):
+    import os
+    import torch
+    import torch.distributed as dist
+    os.environ["MESH_GROUP"] = group
+    os.environ["MASTER_PORT"] = os.environ["MESH_AUX_PORT"]      # the launcher's own store holds MASTER_PORT
+    import importlib
+    cfg = importlib.import_module("mesh_b200.config")
+    cfg.set_config(cfg.MeshConfig.from_env())
+    from mesh_b200.distributed import init, shutdown
+    from mesh_b200.runtime import service
+    ctx = init(backend="gloo", device="cpu")
+    assert ctx.service, "init() starts the runtime service"
+    t = torch.ones(4) * (rank + 1)
+    dist.all_reduce(t)
+    service.count("step", 7)
+    rdv.barrier("running")
+    # every rank's block is visible to every other process of the node while the job runs
+    for r in range(world):
+        s = service.read(group, r)
+        assert s is not None and s["alive"] and s["rank"] == r and s["world"] == world and not s["abort"]
+        assert s["step"] == 7
+    rdv.barrier("read")
+    shutdown()
+    assert service.read(group, rank) is None, "shutdown() removes this rank's block"
+
+
+def test_init_starts_the_runtime_service_and_shutdown_stops_it():
+    import os
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_job_with_runtime, 2, f"t{os.getpid()}", timeout=120.0)

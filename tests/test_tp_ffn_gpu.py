@@ -22,10 +22,10 @@ def _reference(x, wg, wu, wd, dy):
     return y.detach(), xr.grad, wgr.grad, wur.grad, wdr.grad
 
 
-def _close(got, want, tol=3e-2):
-    err = (got.float() - want.float()).abs().max().item()
-    ref = want.float().abs().max().item() + 1e-6
-    assert err / ref < tol, f"max err {err} vs {ref}"
+def _close(got, want, tol=8e-3):
+    # intermediates (h, [g|u], [dg|du]) are rounded to bf16 on the way, the reference keeps fp32 throughout
+    from _oracle import assert_close_rms
+    assert_close_rms(got, want, tol=tol)
 
 
 def _run_rank(rank, world, rdv, M, D, F, steps):
@@ -64,9 +64,18 @@ def test_fused_tp_ffn_world1():
     _run_rank(0, 1, rdv, 512, 256, 512, 3)
 
 
+def test_fused_tp_ffn_world1_many_waves():
+    """Enough tiles for several waves per launch, so that the chained launches of a pass really overlap."""
+    import torch.distributed as dist
+    from mesh_b200.runtime.rendezvous import Rendezvous
+    rdv = Rendezvous(dist.HashStore(), 0, 1)
+    _run_rank(0, 1, rdv, 2048, 1024, 4096, 2)
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_fused_tp_ffn_multi(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_run_rank, world, 128 * world * 2, 256, 64 * world * 2, 3, use_cuda=True, timeout=300.0)
+    spawn_ranks(_run_rank, world, 4096, 1024, 1792 * world, 2, use_cuda=True, timeout=300.0)
