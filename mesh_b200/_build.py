@@ -21,6 +21,7 @@ CSRC = ROOT / "csrc"
 LIBDIR = ROOT / "_lib"
 OBJDIR = ROOT.parent / "build" / "obj"
 LIBNAME = "libmesh_b200.so"
+CHECK_LIBNAME = "libmesh_b200_check.so"      # same sources with -DMESH_CHECK=1 (index / alignment checks in the kernels)
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -38,21 +39,25 @@ def sources() -> list[Path]:
     return [p for p in out if "/standalone/" not in str(p)]
 
 
-def _headers_digest() -> str:
+def _flags(check: bool) -> list[str]:
+    return NVCC_FLAGS + (["-DMESH_CHECK=1"] if check else [])
+
+
+def _headers_digest(check: bool = False) -> str:
     h = hashlib.sha256()
     for p in sorted(list(CSRC.rglob("*.cuh")) + list(CSRC.rglob("*.h"))):
         h.update(p.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags(check)).encode())
     return h.hexdigest()
 
 
-def _compile_one(nvcc: str, src: Path, hdr: str, verbose: bool) -> Path:
+def _compile_one(nvcc: str, src: Path, hdr: str, verbose: bool, check: bool = False) -> Path:
     h = hashlib.sha256(src.read_bytes())
     h.update(hdr.encode())
     obj = OBJDIR / f"{src.stem}-{h.hexdigest()[:16]}.o"
     if obj.exists():
         return obj
-    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc, *_flags(check), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if src.suffix == ".cpp":
         cmd.insert(1, "-x"); cmd.insert(2, "cu")
     r = subprocess.run(cmd, capture_output=True, text=True)
@@ -63,52 +68,68 @@ def _compile_one(nvcc: str, src: Path, hdr: str, verbose: bool) -> Path:
     return obj
 
 
-def lib_path() -> Path:
-    return LIBDIR / LIBNAME
+def lib_path(check: bool = False) -> Path:
+    return LIBDIR / (CHECK_LIBNAME if check else LIBNAME)
 
 
-def is_current() -> bool:
-    meta = LIBDIR / "build.json"
-    if not (lib_path().exists() and meta.exists()):
+def _meta_path(check: bool) -> Path:
+    return LIBDIR / ("build_check.json" if check else "build.json")
+
+
+def is_current(check: bool = False) -> bool:
+    meta = _meta_path(check)
+    if not (lib_path(check).exists() and meta.exists()):
         return False
     try:
-        return json.loads(meta.read_text()).get("digest") == _tree_digest()
+        return json.loads(meta.read_text()).get("digest") == _tree_digest(check)
     except Exception:
         return False
 
 
-def _tree_digest() -> str:
-    h = hashlib.sha256(_headers_digest().encode())
+def _tree_digest(check: bool = False) -> str:
+    h = hashlib.sha256(_headers_digest(check).encode())
     for s in sources():
         h.update(str(s.relative_to(CSRC)).encode())
         h.update(s.read_bytes())
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every source for sm_100a and link the shared library.  Returns its path."""
-    if not force and is_current():
-        return lib_path()
+def build(force: bool = False, verbose: bool = False, check: bool = False) -> Path:
+    """Compile every source for sm_100a and link the shared library.  Returns its path.
+    ``check=True`` builds the checked variant (``-DMESH_CHECK=1``) beside the regular one."""
+    if not force and is_current(check):
+        return lib_path(check)
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build mesh_b200's native library")
     OBJDIR.mkdir(parents=True, exist_ok=True)
     LIBDIR.mkdir(parents=True, exist_ok=True)
-    hdr = _headers_digest()
+    # one builder at a time: the ranks of a job that all find the library stale take turns, and all but the first
+    # find it current when their turn comes
+    import fcntl
+    with open(LIBDIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and is_current(check):
+            return lib_path(check)
+        return _build_locked(nvcc, verbose, check)
+
+
+def _build_locked(nvcc: str, verbose: bool, check: bool) -> Path:
+    hdr = _headers_digest(check)
     srcs = sources()
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
-        objs = list(ex.map(lambda s: _compile_one(nvcc, s, hdr, verbose), srcs))
-    tmp = LIBDIR / (LIBNAME + ".tmp")
+        objs = list(ex.map(lambda s: _compile_one(nvcc, s, hdr, verbose, check), srcs))
+    tmp = LIBDIR / (lib_path(check).name + ".tmp")
     cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(tmp),
            *map(str, objs), "-lpthread", "-ldl", "-lrt"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    os.replace(tmp, lib_path())
-    (LIBDIR / "build.json").write_text(json.dumps({"digest": _tree_digest(), "sources": [str(s.relative_to(CSRC)) for s in srcs]}))
-    return lib_path()
+    os.replace(tmp, lib_path(check))
+    _meta_path(check).write_text(json.dumps({"digest": _tree_digest(check), "sources": [str(s.relative_to(CSRC)) for s in srcs]}))
+    return lib_path(check)
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv, check="--check" in sys.argv)
     print(p)

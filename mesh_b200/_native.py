@@ -56,6 +56,12 @@ def available() -> bool:
     return _build.lib_path().exists()
 
 
+def checked() -> bool:
+    """True when the loaded library is the checked build."""
+    L = lib()
+    return bool(L.mesh_checked_build())
+
+
 def lib() -> ctypes.CDLL:
     """Load (building first if sources changed and nvcc is present) and return the library."""
     global _lib
@@ -65,10 +71,12 @@ def lib() -> ctypes.CDLL:
         if _lib is not None:
             return _lib
         from . import _build
-        path = _build.lib_path()
-        if not path.exists() or (not _build.is_current() and _build.nvcc_path() is not None):
+        from .config import config
+        check = bool(config().check)          # MESH_CHECK=1: the library with index / alignment checks in its kernels
+        path = _build.lib_path(check)
+        if not path.exists() or (not _build.is_current(check) and _build.nvcc_path() is not None):
             try:
-                path = _build.build()
+                path = _build.build(check=check)
             except Exception as e:  # keep a stale but loadable library usable
                 if not path.exists():
                     raise RuntimeError(f"mesh_b200 native library is missing and could not be built: {e}") from e

@@ -151,3 +151,66 @@ def bucket_reductions(plan: Plan) -> tuple[Plan, int]:
         steps.append(st)
     plan.steps = steps
     return plan, count
+
+
+def fuse_norms(plan: Plan) -> tuple[Plan, int]:
+    """An RMS norm is captured as the chain ``pow(x, 2) -> mean(last dim, keepdim) -> add(eps) -> rsqrt -> mul(x, .)
+    [-> mul(., w)]``.  Where every link has that one reader (an inference graph: a training graph keeps the
+    intermediates for the backward pass) the chain becomes one ``rms_norm`` step, which the executor runs as the RMSNorm
+    kernel on bf16 CUDA operands and as the same PyTorch expression elsewhere.  The reference lowers a norm as one
+    normalisation record, not as its pointwise pieces (compiler/mesh_compiler/operations.py:6671-6682).
+    Returns the rewritten copy and the number of norms found."""
+    plan = copy.copy(plan)
+    steps = list(plan.steps)
+    uses = _uses(plan)
+    at = {st.out: i for i, st in enumerate(steps)}
+    drop: set[int] = set()
+    replace: dict[int, Step] = {}
+
+    def only_reader(name, target):
+        u = uses.get(name, [])
+        if len(u) != 1 or u[0] >= len(steps):
+            return None
+        st = steps[u[0]]
+        return u[0] if st.op == "call" and st.target in target else None
+
+    for i, st in enumerate(steps):
+        if not (st.op == "call" and st.target is aten.pow.Tensor_Scalar and st.args[1] == 2 and isinstance(st.args[0], Ref)):
+            continue
+        x = st.args[0]
+        shape = plan.full_shapes.get(x.name)
+        j = only_reader(st.out, (aten.mean.dim,))
+        if j is None:
+            continue
+        mean = steps[j]
+        dims = list(mean.args[1]) if len(mean.args) > 1 else []
+        keep = (mean.args[2] if len(mean.args) > 2 else mean.kwargs.get("keepdim", False))
+        if len(dims) != 1 or not keep or (dims[0] != -1 and (shape is None or dims[0] != len(shape) - 1)):
+            continue
+        k = only_reader(mean.out, (aten.add.Tensor, aten.add.Scalar))
+        if k is None or isinstance(steps[k].args[1], Ref):
+            continue
+        eps = float(steps[k].args[1])
+        r = only_reader(steps[k].out, (aten.rsqrt.default,))
+        if r is None:
+            continue
+        m1 = only_reader(steps[r].out, (aten.mul.Tensor,))
+        if m1 is None:
+            continue
+        ops = [a.name for a in steps[m1].args if isinstance(a, Ref)]
+        if sorted(ops) != sorted([x.name, steps[r].out]):
+            continue
+        chain, last, w = [i, j, k, r], m1, None
+        m2 = only_reader(steps[m1].out, (aten.mul.Tensor,))
+        if m2 is not None:
+            other = [a for a in steps[m2].args if isinstance(a, Ref) and a.name != steps[m1].out]
+            wshape = plan.full_shapes.get(other[0].name) if other else None
+            if len(other) == 1 and wshape is not None and len(wshape) == 1:
+                chain.append(m1)
+                last, w = m2, other[0]
+        meta = dict(steps[last].meta)
+        meta.update({"fused": "rms_norm", "eps": eps})
+        replace[last] = Step("fused", steps[last].out, "rms_norm", (x,) if w is None else (x, w), {}, meta)
+        drop.update(chain)
+    plan.steps = [replace.get(i, st) for i, st in enumerate(steps) if i not in drop]
+    return plan, len(replace)

@@ -107,6 +107,8 @@ def _run_with_env(ex: Executor, inputs: dict, consts, env) -> list:
             env[st.out] = None if src is None else ex._index(src, s.dim, local_indices(s, ex.coords[ax], src.shape[s.dim]))
         elif st.op == "collective":
             env[st.out] = ex.collective(st, env[st.args[0].name])
+        elif st.op == "fused" and st.target == "rms_norm":
+            env[st.out] = ex.rms_norm(st, env[st.args[0].name], env[st.args[1].name] if len(st.args) > 1 else None)
         elif st.op == "fused":
             env[st.out] = ex.fused(st, env[st.args[0].name], env[st.args[1].name], env)
         else:
@@ -136,6 +138,8 @@ def _line(st: Step) -> str:
         m = st.meta
         extra = f", left={m['left']}, right={m['right']}" if st.target in ("halo", "halo_back") else ""
         return f"{st.out} = {st.target}({_fmt(st.args[0])}, axis={m['axis']}, channel={m.get('channel')}{extra})   # {m['from']!r} -> {m['to']!r}"
+    if st.op == "fused" and st.target == "rms_norm":
+        return f"{st.out} = rms_norm({', '.join(_fmt(a) for a in st.args)}, eps={st.meta['eps']})"
     if st.op == "fused":
         return f"{st.out} = fused_{st.target}({', '.join(_fmt(a) for a in st.args)}, axis={st.meta['axis']}, channel={st.meta.get('channel')})"
     name = getattr(st.target, "__name__", None) or str(st.target)

@@ -50,7 +50,7 @@ def stage_costs(report: dict, plan) -> list[dict]:
     """Observed seconds per communication-delimited stage: ``[{"stage", "compute_s", "collective_s", "steps"}]``."""
     out, cur = [], {"stage": 0, "compute_s": 0.0, "collective_s": 0.0, "steps": 0}
     for rec, st in zip(report["steps"], plan.steps):
-        if st.op in ("collective", "fused"):
+        if st.op == "collective" or (st.op == "fused" and "channel" in st.meta):      # a fused norm is compute
             cur["collective_s"] += rec["seconds"]
             cur["steps"] += 1
             out.append(cur)

@@ -122,6 +122,8 @@ class Executor:
         # costs, and what a person reads to see where a processor's time goes (compiler/observe.py)
         self.times = [] if os.environ.get("MESH_OBSERVE", "0") == "1" else None
         self.seed, self.execution = int(os.environ.get("MESH_SEED", "0")), 0        # random draws: see draw()
+        from .kernels import Counter
+        self.kernels = Counter()     # products / attention / norms run on this package's kernels vs on PyTorch operators
 
     # ---- shards of full tensors
     def shard(self, full: torch.Tensor, specs: tuple) -> torch.Tensor | None:
@@ -365,6 +367,8 @@ class Executor:
                 env[st.out] = None
             elif st.op == "collective":
                 env[st.out] = self.collective(st, env[st.args[0].name])
+            elif st.op == "fused" and st.target == "rms_norm":
+                env[st.out] = self.rms_norm(st, env[st.args[0].name], env[st.args[1].name] if len(st.args) > 1 else None)
             elif st.op == "fused":
                 env[st.out] = self.fused(st, env[st.args[0].name], env[st.args[1].name], env)
             else:
@@ -445,6 +449,20 @@ class Executor:
             return self.collective(Step("collective", st.out, "reduce_scatter", (), {}, m), partial)
         raise NotImplementedError(st.target)
 
+    def rms_norm(self, st: Step, x, w):
+        """One step for the operator chain of an RMS norm (``fuse.fuse_norms``)."""
+        if x is None or (len(st.args) > 1 and w is None):
+            return None
+        from . import kernels
+        if kernels.enabled():
+            y = kernels.rms_norm(x, w, st.meta["eps"])
+            if y is not None:
+                self.kernels.own += 1
+                return y
+        self.kernels.eager += 1
+        y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + st.meta["eps"])
+        return y if w is None else y * w
+
     def draw(self, m: dict, args):
         """Random numbers for the elements this processor holds, as a function of their positions in the whole tensor
         (Philox4x32-10 keyed by seed, execution and draw site; ``mesh_b200/ops/philox.py``)."""
@@ -489,6 +507,15 @@ class Executor:
             spec = m["out_specs"][ax]
             q, k = args[0], args[1]
             rows = local_indices(spec, self.coords[ax], m["full_shape"][2])
+            from . import kernels
+            if kernels.enabled() and isinstance(rows, slice) and len(args) == 3:
+                y = kernels.attention(q, k, args[2], causal=True, scale=kwargs.get("scale"),
+                                      row_positions=(rows.start or 0, rows.step or 1),
+                                      dropout_p=kwargs.get("dropout_p", 0.0), mask=kwargs.get("attn_mask"))
+                if y is not None:
+                    self.kernels.own += 1
+                    return y
+            self.kernels.eager += 1
             pos = torch.arange(m["full_shape"][2], device=q.device)[rows] if isinstance(rows, slice) else torch.tensor(rows, device=q.device)
             mask = pos[:, None] >= torch.arange(k.shape[2], device=q.device)[None, :]
             kw = {key: v for key, v in kwargs.items() if key not in ("is_causal", "attn_mask")}
@@ -531,7 +558,27 @@ class Executor:
             return e * ok.unsqueeze(-1).to(e.dtype)
         if tgt in (aten.view.default, aten._unsafe_view.default):
             return args[0].reshape(args[1])        # shards and gathered values are not always dense
+        # products and whole attention run on this package's kernels where the operands allow it (compiler/kernels.py)
+        from . import kernels
+        if kernels.enabled():
+            y = None
+            if tgt is aten.mm.default:
+                y = kernels.mm(args[0], args[1])
+            elif tgt is aten.scaled_dot_product_attention.default and len(args) == 3:
+                y = kernels.attention(args[0], args[1], args[2], causal=bool(kwargs.get("is_causal", False)),
+                                      scale=kwargs.get("scale"), dropout_p=kwargs.get("dropout_p", 0.0),
+                                      mask=kwargs.get("attn_mask"))
+            if y is not None:
+                self.kernels.own += 1
+                return y
+        if tgt in _COMPUTE:
+            self.kernels.eager += 1
         return tgt(*args, **kwargs)
+
+
+# operators with a kernel of this package behind them when the operands allow it: the ones counted as "eager" when
+# they run on the PyTorch operator instead
+_COMPUTE = (aten.mm.default, aten.bmm.default, aten.addmm.default, aten.scaled_dot_product_attention.default)
 
 
 # ----------------------------------------------------------------------------- Program
@@ -566,8 +613,9 @@ class Program(Arguments):
         # the execution number advances with every call, so that successive steps draw fresh numbers
         self.seed, self.execution = int(os.environ.get("MESH_SEED", "0")), 0
         if os.environ.get("MESH_FUSE", "1") != "0":
-            from .fuse import fuse_plan
+            from .fuse import fuse_norms, fuse_plan
             self.plan, self.fusion = fuse_plan(self.plan)
+            self.plan, self.fusion["rms_norm"] = fuse_norms(self.plan)
         self.bucketed = 0
         if os.environ.get("MESH_BUCKET", "0") == "1":
             from .fuse import bucket_reductions
@@ -632,6 +680,15 @@ class Program(Arguments):
         owner = 0 if self.entry is None else self.mesh.names.index(self.entry)
         ex, flat = results[owner]
         return self._result(flat, ex, bound, results)
+
+    def structure(self) -> dict:
+        """What the plan was lowered to: fused (collective, product) pairs and norms found, and, after a call, how many
+        products / attention / norm steps ran on this package's kernels and how many on PyTorch operators (summed over
+        the processors this process ran)."""
+        execs = [self.exec] if not self.threads else [r[0] for r in (getattr(self, "per_rank", None) or []) if r is not None]
+        own = sum(e.kernels.own for e in execs)
+        eager = sum(e.kernels.eager for e in execs)
+        return {"fused": dict(self.fusion), "kernels": {"own": own, "eager": eager}, "steps": len(self.plan.steps)}
 
     def _result(self, flat, ex, bound, all_results=None):
         exp = self.exported

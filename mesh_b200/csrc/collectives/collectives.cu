@@ -3,6 +3,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include "coll_api.h"
+#include "../device/check.cuh"
 #include "../device/ptx.cuh"
 #include "../runtime/host_common.h"
 
@@ -256,6 +257,8 @@ __global__ void __launch_bounds__(THREADS) alltoallv_kernel(Comm c, const uint8_
     const int r = (c.rank + s) % c.world;
     const volatile uint64_t* hdr = reinterpret_cast<const volatile uint64_t*>(c.staging[r]);
     const uint64_t lo = hdr[c.rank], hi = hdr[c.rank + 1];
+    // the block's bounds come from the sender's header: in a checked build they must lie inside its staging buffer
+    if (!MESH_CHECK_INDEX(hi, c.staging_bytes + 1, c.status) || !MESH_CHECK_INDEX(lo, hi + 1, c.status)) continue;
     const uint64_t room = t.b[r + 1] - t.b[r];
     copy_bytes(out + t.b[r], c.staging[r] + HDR + lo, min(hi - lo, room));
   }

@@ -20,6 +20,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include "moe_api.h"
+#include "../device/check.cuh"
 #include "../device/ptx.cuh"
 #include "../gemm/gemm_api.h"
 #include "../runtime/host_common.h"
@@ -214,8 +215,10 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchArgs a)
   const int vec = a.d_model / 8;
   for (int i = blockIdx.x * warps + warp; i < n_entries; i += gridDim.x * warps) {
     const int e = a.idx[i];
+    if (!MESH_CHECK_INDEX(e, a.local_experts * a.world, a.status)) continue;      // an expert id from the router
     const int dest = e / a.local_experts;
     const int row = a.send_base[e] + a.slot[i];
+    if (!MESH_CHECK_INDEX(row, 1ll << 30, a.status)) continue;                    // negative: a broken plan
     if (row >= a.cap_rows) {
       if (lane == 0) a.meta[i] = -1;
       continue;
@@ -256,6 +259,7 @@ struct CombineArgs {
   int tokens, k, d_model, local_experts, world;
   const int* idx; const int* meta; const float* weight;        // weight nullptr: plain sum (backward of dispatch)
   const __nv_bfloat16* src[R];                 // every rank's expert-output buffer [cap_rows, d_model]
+  int cap_rows;                                // rows of every expert-output buffer (checked build)
   const uint32_t* ready; uint32_t ready_expect;               // this rank's counter: all peers finished their experts
   __nv_bfloat16* out;                          // [tokens, d_model]
   const __nv_bfloat16* dot_with; float* dots;  // optional: dots[t, j] = <row, dot_with[t]>
@@ -276,6 +280,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const CombineArgs a) {
         const int row = a.meta[t * a.k + j];
         if (row < 0) continue;
         const int dest = a.idx[t * a.k + j] / a.local_experts;
+        if (!MESH_CHECK_INDEX(dest, a.world, a.status) || !MESH_CHECK_INDEX(row, a.cap_rows, a.status)) continue;
         const float w = a.weight ? a.weight[t * a.k + j] : 1.f;
         const uint4 q = __ldcg(reinterpret_cast<const uint4*>(a.src[dest] + (long long)row * a.d_model) + v);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
@@ -387,6 +392,7 @@ extern "C" int mesh_moe_combine(const MeshMoeCombine* m, void* stream) {
   a.ready = (const uint32_t*)m->ready; a.ready_expect = m->ready_expect;
   a.out = (__nv_bfloat16*)m->out; a.dot_with = (const __nv_bfloat16*)m->dot_with; a.dots = m->dots;
   a.status = (Status*)m->status;
+  a.cap_rows = m->cap_rows > 0 ? m->cap_rows : (1 << 30);
   int grid = (m->tokens + 7) / 8;
   if (grid > 148 * 8) grid = 148 * 8;
   moe_combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);

@@ -45,6 +45,7 @@ typedef struct MeshMoeCombine {
   const void* ready; uint32_t ready_expect;
   void* out; const void* dot_with; float* dots;
   void* status;
+  int cap_rows;                 // rows of every source buffer (bounds of the rows named by `meta`)
 } MeshMoeCombine;
 int mesh_moe_combine(const MeshMoeCombine* m, void* stream);
 

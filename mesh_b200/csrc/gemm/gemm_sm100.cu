@@ -128,6 +128,8 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   if (a->k_ready != nullptr && (p.k_ready_rows % BK)) return set_error(-5, "gemm: k_ready_rows must be a multiple of 64");
   p.pdl_trigger = (a->pdl & 2) ? 1 : 0;
   const bool dependent = (a->pdl & 1) != 0 && pdl_enabled();
+  p.a_extent = a->a_mn ? a->M : (a->a_rows ? a->a_rows : a->M);
+  p.b_extent = a->b_mn ? a->N : (a->b_rows ? a->b_rows : a->N);
   p.tiles = (const TileDesc*)a->tiles;
   p.n_tiles_dev = (const int*)a->n_tiles_dev;
   p.a_ready = (const uint32_t*)a->a_ready;

@@ -25,6 +25,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cstdint>
+#include "../device/check.cuh"
 #include "../device/ptx.cuh"
 
 namespace mesh {
@@ -121,6 +122,7 @@ struct Params {
   uint32_t k_ready_value;
   int k_ready_rows;
   int pdl_trigger;          // let the next launch of the stream start during this kernel's last wave
+  int a_extent, b_extent;   // rows (MN extent) of the stored A and B matrices: bounds for descriptor tiles (checked build)
 };
 
 // ------------------------------------------------------------------------------------------
@@ -321,6 +323,15 @@ gemm_kernel(const __grid_constant__ Params p) {
       for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
         const Work wk = get_work(p, tile, (int)cta_rank, CTAS, TILE_N);
         const int m0 = wk.m0, n0 = wk.bn0;
+        // checked build: a tile descriptor built on the device names coordinates inside its matrices, on the 16-byte
+        // grid that a TMA copy needs (an unaligned innermost coordinate is an illegal instruction); a bad tile is
+        // recorded and the kernel unwinds
+        if (p.tiles != nullptr &&
+            !(MESH_CHECK_INDEX(m0 - (int)cta_rank * BM, p.a_extent, p.status) && MESH_CHECK_INDEX(n0, p.b_extent, p.status) &&
+              MESH_CHECK_ALIGNED(wk.ka0, 8, p.status) && MESH_CHECK_ALIGNED(wk.kb0, 8, p.status) &&
+              MESH_CHECK_ALIGNED(A_MN ? m0 : 0, 64, p.status) && MESH_CHECK_ALIGNED(B_MN ? n0 : 0, 64, p.status))) {
+          ok = false; *abort_smem = 1; break;
+        }
         // this CTA's last tile: the next launch may take the SMs that other CTAs are about to leave
         if (p.pdl_trigger && tile + tile_step >= total_tiles && tile != tile_first) griddep_launch_dependents();
         // all-gather: this rank's own rows are read straight from the source shard (no wait);

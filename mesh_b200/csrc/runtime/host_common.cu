@@ -95,3 +95,11 @@ bool pdl_enabled() {
 
 extern "C" const char* mesh_last_error(void) { return mesh::last_error_text(); }
 extern "C" int mesh_sm_count(void) { return mesh::sm_count(); }
+// 1 when this library was compiled with -DMESH_CHECK=1 (index / alignment checks inside the kernels).
+extern "C" int mesh_checked_build(void) {
+#if defined(MESH_CHECK) && MESH_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}

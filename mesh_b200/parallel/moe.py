@@ -43,7 +43,7 @@ class _Combine(ctypes.Structure):
     _fields_ = [("tokens", c_int), ("k", c_int), ("d_model", c_int), ("local_experts", c_int), ("world", c_int),
                 ("idx", c_void_p), ("meta", c_void_p), ("weight", c_void_p), ("src", c_void_p * MAX_RANKS),
                 ("ready", c_void_p), ("ready_expect", c_uint32), ("out", c_void_p), ("dot_with", c_void_p),
-                ("dots", c_void_p), ("status", c_void_p)]
+                ("dots", c_void_p), ("status", c_void_p), ("cap_rows", c_int)]
 
 
 def _s():
@@ -144,6 +144,7 @@ class EPMoE:
         c.dot_with = 0 if dot_with is None else dot_with.data_ptr()
         c.dots = 0 if dots is None else dots.data_ptr()
         c.status = status_block(self.dev).data_ptr()
+        c.cap_rows = self.cap
         _native.check(self.L.mesh_moe_combine(ctypes.byref(c), _s()), "mesh_moe_combine")
         _native.count_launch()
 

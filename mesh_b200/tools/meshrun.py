@@ -5,7 +5,7 @@ torchrun environment (RANK, LOCAL_RANK, WORLD_SIZE, MASTER_ADDR=127.0.0.1, MASTE
 (pid, start time) identity, and when a rank exits without being asked: tells the survivors to stop (SIGTERM,
 then a bounded wait — never SIGKILL while they may hold device state unless the wait runs out), and relaunches
 the whole job, at most once per back-off interval, with ``MESH_RESTART=<n>`` so the script resumes from its last
-checkpoint.  Signals to the supervisor: SIGHUP = restart the job, SIGUSR1 = release (stop the job, keep
+checkpoint; with ``--shrink`` the job is re-formed at a smaller world, without the ranks that failed.  Signals to the supervisor: SIGHUP = restart the job, SIGUSR1 = release (stop the job, keep
 supervising), SIGTERM = stop and exit — the reference's heartbeat supervisor (rdma/mesh-heartbeat.c:5-30, :135-325).
 """
 from __future__ import annotations
@@ -21,11 +21,18 @@ import time
 from ..runtime.failure import alive, process_identity
 from ..utils.launch import free_port
 
+# A rank that ends because a PEER went away (a collective failed under it) exits with this code: the supervisor does
+# not count it among the ranks that were lost when it re-forms the job at a smaller size.
+PEER_LOST_EXIT = 75
+
 
 class Supervisor:
     def __init__(self, cmd: list[str], nproc: int, max_restarts: int = 1, backoff_s: float = 60.0, grace_s: float = 20.0,
-                 env: dict | None = None, log=None):
+                 env: dict | None = None, log=None, shrink: bool = False, min_nproc: int = 1):
         self.cmd, self.nproc, self.max_restarts, self.backoff_s, self.grace_s = cmd, nproc, max_restarts, backoff_s, grace_s
+        # shrink: the job is re-formed without the ranks that failed (their GPUs may be gone) instead of at the same
+        # size; the script reads the new WORLD_SIZE and loads its sharded checkpoint re-cut for it
+        self.shrink, self.min_nproc = shrink, max(1, min_nproc)
         self.env = dict(os.environ if env is None else env)
         self.procs: list[subprocess.Popen] = []
         self.ids: list[tuple] = []
@@ -101,6 +108,13 @@ class Supervisor:
                 if wait > 0:
                     time.sleep(wait)            # at most one reopen per back-off interval
                 self.restarts += 1
+                if self.shrink:
+                    lost = [r for r in set(failed + gone) if codes[r] != PEER_LOST_EXIT]
+                    smaller = self.nproc - max(1, len(lost))
+                    if smaller < self.min_nproc:
+                        self.log(event="giving_up", restarts=self.restarts, reason="fewer ranks left than --min-nproc")
+                        return 1
+                    self.nproc = smaller
                 self.launch()
 
 
@@ -110,6 +124,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-restarts", type=int, default=1)
     ap.add_argument("--backoff", type=float, default=60.0)
     ap.add_argument("--grace", type=float, default=20.0)
+    ap.add_argument("--shrink", action="store_true", help="relaunch without the ranks that failed (a smaller world)")
+    ap.add_argument("--min-nproc", type=int, default=1)
     ap.add_argument("cmd", nargs=argparse.REMAINDER)
     a = ap.parse_args(argv)
     cmd = a.cmd[1:] if a.cmd and a.cmd[0] == "--" else a.cmd
@@ -117,7 +133,7 @@ def main(argv=None) -> int:
         ap.error("no command given")
     if cmd[0].endswith(".py"):
         cmd = [sys.executable, *cmd]
-    return Supervisor(cmd, a.nproc, a.max_restarts, a.backoff, a.grace).run()
+    return Supervisor(cmd, a.nproc, a.max_restarts, a.backoff, a.grace, shrink=a.shrink, min_nproc=a.min_nproc).run()
 
 
 if __name__ == "__main__":

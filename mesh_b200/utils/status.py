@@ -11,7 +11,7 @@ import torch
 
 CODES = {0: "OK", 1: "TIMEOUT", 2: "CANCELED", 3: "STALE", 4: "BOUNDS", 5: "ALIGN", 6: "BAD_ARGUMENT"}
 SITES = {0: "none", 1: "smem_full", 2: "smem_empty", 3: "tmem_full", 4: "tmem_empty", 5: "peer_flag",
-         6: "local_flag", 7: "barrier", 8: "store_drain", 9: "host_flag"}
+         6: "local_flag", 7: "barrier", 8: "store_drain", 9: "host_flag", 10: "check"}
 
 
 class MeshDeviceError(RuntimeError):

@@ -523,7 +523,7 @@ def test_sequence_parallel_megatron_layer_has_the_textbook_collectives():
     sch = compile_module(m, (x,), procs, lambda nd: (1, names, None) if nd.op == "placeholder" and nd.name == "x" else tp(nd))
     assert sch.structure["by_verb"] == {"all_gather": 2, "reduce_scatter": 2, "all_reduce": 1}, sch.structure["by_verb"]
     prog = Program(sch)
-    assert prog.fusion == {"ag_mm": 2, "mm_rs": 2}
+    assert prog.fusion == {"ag_mm": 2, "mm_rs": 2, "rms_norm": 2}
     assert torch.allclose(prog(x), m(x), atol=1e-4)
 
 
