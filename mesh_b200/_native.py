@@ -47,7 +47,8 @@ class GemmArgs(ctypes.Structure):
         ("rs_expect", c_uint32), ("rs_out", c_void_p), ("rs_rows_per_rank", c_int),
         ("num_ctas", c_int), ("tile_n", c_int), ("pair", c_int),
         ("tiles", c_void_p), ("n_tiles_dev", c_void_p), ("max_tiles", c_int),
-        ("d_done", c_void_p), ("k_ready", c_void_p), ("k_ready_value", c_uint32), ("k_ready_rows", c_int), ("pdl", c_int),
+        ("d_done", c_void_p), ("k_ready", c_void_p), ("k_ready_value", c_uint32), ("k_ready_rows", c_int),
+        ("b_scales", c_void_p), ("b_bits", c_int), ("pdl", c_int),
     ]
 
 

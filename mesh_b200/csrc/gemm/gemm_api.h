@@ -58,6 +58,10 @@ typedef struct MeshGemmArgs {
   const void* k_ready;         // counters per `k_ready_rows` K rows that a K block waits for; NULL: none
   uint32_t k_ready_value;
   int k_ready_rows;
+  // group-quantised weights: B = codes ([N, K/2] 4-bit in nibble order 0,4,1,5,2,6,3,7 per 32-bit word, or [N, K] 8-bit),
+  // b_scales = fp16 [N, K/64]; value = (code - 8 or 128) * scale.  Dequantised in registers on the way to the tensor cores.
+  const void* b_scales;
+  int b_bits;                  // 0: bf16 B; 4 or 8
   int pdl;                     // bit 0: may start before the previous launch of the stream has finished (every input
                                // that launch writes is guarded by a_ready / k_ready); bit 1: let the next launch
                                // start during this kernel's last wave

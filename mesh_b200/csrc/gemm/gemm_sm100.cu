@@ -33,16 +33,16 @@ static bool make_map_mn(CUtensorMap* tm, const void* base, uint64_t mn_cols, uin
                       CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int A_MN, int B_MN, int EPI, bool AG, int BNV, bool PAIR>
+template <int A_MN, int B_MN, int EPI, bool AG, int BNV, bool PAIR, int BQ = 0>
 static int launch(const Params& p, int ctas, cudaStream_t stream, bool dependent) {
-  auto kern = gemm_kernel<A_MN, B_MN, EPI, AG, BNV, PAIR>;
+  auto kern = gemm_kernel<A_MN, B_MN, EPI, AG, BNV, PAIR, BQ>;
   static bool configured = false;   // per instantiation
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return set_error((int)e, "cudaFuncSetAttribute(gemm smem): %s", cudaGetErrorString(e));
     configured = true;
   }
-  const int threads = NUM_THREADS + (AG ? 32 * COMM_WARPS : 0);
+  const int threads = NUM_THREADS + ((AG || BQ != 0) ? 32 * COMM_WARPS : 0);
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)ctas);
@@ -128,6 +128,20 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   if (a->k_ready != nullptr && (p.k_ready_rows % BK)) return set_error(-5, "gemm: k_ready_rows must be a multiple of 64");
   p.pdl_trigger = (a->pdl & 2) ? 1 : 0;
   const bool dependent = (a->pdl & 1) != 0 && pdl_enabled();
+  const int bq = a->b_bits;
+  if (bq != 0) {
+    if (bq != 4 && bq != 8) return set_error(-3, "gemm: quantised weights are 4-bit or 8-bit (b_bits %d)", bq);
+    if (a->b_mn || a->a_mn || a->epi != EPI_STORE || a->tiles != nullptr || a->ag_src != nullptr)
+      return set_error(-3, "gemm: quantised weights need K-major operands, a plain store epilogue and a dense grid");
+    if (a->K % 64) return set_error(-3, "gemm: quantised weights need K %% 64 == 0 (one scale per 64 k)");
+    if (a->b_scales == nullptr || (uintptr_t)a->B % 16 || ((bq == 4 ? a->K / 2 : a->K) % 16))
+      return set_error(-2, "gemm: quantised weights need scales and 16-byte aligned code rows");
+    p.bq_codes = (const uint8_t*)a->B;
+    p.bq_scales = (const __half*)a->b_scales;
+    p.bq_row_bytes = bq == 4 ? a->K / 2 : a->K;
+    p.bq_scale_ld = a->K / 64;
+    p.bq_rows = a->b_rows ? a->b_rows : a->N;
+  }
   p.a_extent = a->a_mn ? a->M : (a->a_rows ? a->a_rows : a->M);
   p.b_extent = a->b_mn ? a->N : (a->b_rows ? a->b_rows : a->N);
   p.tiles = (const TileDesc*)a->tiles;
@@ -176,7 +190,8 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
                                       (uint64_t)a->lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
   const uint64_t b_rows = (uint64_t)(a->b_rows ? a->b_rows : a->N);
   // MN-major B: b_rows (when given) is the number of stored K rows (stacked per-expert weights are taller than K)
-  if (a->b_mn) ok = ok && make_map_mn(&p.tmB, a->B, (uint64_t)a->N, (uint64_t)(a->b_rows ? a->b_rows : a->K), (uint64_t)a->ldb, bn_cta / 64);
+  if (bq != 0) { /* no tensor map: the dequantising warps read B */ }
+  else if (a->b_mn) ok = ok && make_map_mn(&p.tmB, a->B, (uint64_t)a->N, (uint64_t)(a->b_rows ? a->b_rows : a->K), (uint64_t)a->ldb, bn_cta / 64);
   else         ok = ok && make_map_2d(&p.tmB, a->B, (uint64_t)a->K, b_rows, (uint64_t)a->ldb, BK,
                                       a->epi == EPI_GLU_FWD ? BN / 2 : bn_cta, CU_TENSOR_MAP_SWIZZLE_128B);
   if (a->epi != EPI_SCATTER) {
@@ -210,6 +225,20 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
     if (pair) return launch<AM, BMJ, E, G, 256, true>(p, ctas, stream, dependent);     \
     return launch<AM, BMJ, E, G, 256, false>(p, ctas, stream, dependent);              \
   } while (0)
+  if (bq != 0) {
+#define MESH_LAUNCH_Q(Q)                                                               \
+    do {                                                                               \
+      if (bn == 128) {                                                                 \
+        if (pair) return launch<0, 0, EPI_STORE, false, 128, true, Q>(p, ctas, stream, dependent);  \
+        return launch<0, 0, EPI_STORE, false, 128, false, Q>(p, ctas, stream, dependent);           \
+      }                                                                                \
+      if (pair) return launch<0, 0, EPI_STORE, false, 256, true, Q>(p, ctas, stream, dependent);    \
+      return launch<0, 0, EPI_STORE, false, 256, false, Q>(p, ctas, stream, dependent);             \
+    } while (0)
+    if (bq == 4) MESH_LAUNCH_Q(4);
+    MESH_LAUNCH_Q(8);
+#undef MESH_LAUNCH_Q
+  }
   switch (a->epi) {
     case EPI_STORE:
       if (ag) {

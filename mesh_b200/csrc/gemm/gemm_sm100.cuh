@@ -123,6 +123,14 @@ struct Params {
   int k_ready_rows;
   int pdl_trigger;          // let the next launch of the stream start during this kernel's last wave
   int a_extent, b_extent;   // rows (MN extent) of the stored A and B matrices: bounds for descriptor tiles (checked build)
+  // ---- group-quantised B (weights): codes + one fp16 scale per 64 k of a row ------------------
+  // The B stages of the shared-memory ring are then not filled by TMA: four extra warps read the codes with plain
+  // loads, dequantise them in registers ((code - 8) * scale for 4-bit, (code - 128) * scale for 8-bit) and store bf16
+  // into the stage in the layout a 128-byte-swizzled TMA load would have produced, so the MMA side is unchanged.
+  const uint8_t* bq_codes;  // [rows, K/2] (4-bit, eight codes per 32-bit word in nibble order 0,4,1,5,2,6,3,7) or [rows, K]
+  const __half* bq_scales;  // [rows, K/64]
+  long long bq_row_bytes, bq_scale_ld;
+  int bq_rows;
 };
 
 // ------------------------------------------------------------------------------------------
@@ -252,9 +260,35 @@ __device__ __forceinline__ Work get_work(const Params& p, int tile, int cta_rank
   return w;
 }
 
-template <int A_MN, int B_MN, int EPI, bool AG, int BN_T, bool PAIR>
-__global__ void __launch_bounds__(NUM_THREADS + (AG ? 32 * COMM_WARPS : 0), 1)
+// four 8-bit codes -> two bf16x2 words (c - 128) * s, exact until the final rounding to bf16
+__device__ __forceinline__ void dequant_bytes(uint32_t w, float s, uint32_t& lo, uint32_t& hi) {
+  const float k = 8388736.f;                                      // 2^23 + 128
+  const float f0 = (__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)) - k) * s;
+  const float f1 = (__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)) - k) * s;
+  const float f2 = (__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7542)) - k) * s;
+  const float f3 = (__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7543)) - k) * s;
+  lo = pack_bf16(f0, f1);
+  hi = pack_bf16(f2, f3);
+}
+// eight 4-bit codes of one word (nibble order 0,4,1,5,2,6,3,7 = k 0..7) -> eight bf16 (c - 8) * s, in k order
+__device__ __forceinline__ uint4 dequant_nibbles(uint32_t p, __nv_bfloat162 s2) {
+  const __nv_bfloat162 bias2 = __floats2bfloat162_rn(136.f, 136.f);
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t t = ((p >> (4 * i)) & 0x000F000Fu) | 0x43004300u;          // bf16(128 + code) in both halves
+    __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&t), bias2), s2);
+    o[i] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// BQ: 0 = B comes by TMA (bf16); 4 / 8 = B is group-quantised and is dequantised into the stages by extra warps.
+template <int A_MN, int B_MN, int EPI, bool AG, int BN_T, bool PAIR, int BQ = 0>
+__global__ void __launch_bounds__(NUM_THREADS + ((AG || BQ != 0) ? 32 * COMM_WARPS : 0), 1)
 gemm_kernel(const __grid_constant__ Params p) {
+  static_assert(!(AG && BQ != 0), "the extra warps push the all-gather or dequantise weights, not both");
+  static_assert(BQ == 0 || (!B_MN && (EPI == EPI_STORE)), "quantised weights: K-major B, plain store epilogue");
   // tile width is a template parameter: 256 or 128; a CTA stages BN (single) or BN/2 (pair) rows of B
   constexpr int BN = BN_T;
   constexpr int CTAS = PAIR ? 2 : 1;
@@ -289,7 +323,7 @@ gemm_kernel(const __grid_constant__ Params p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), 1 + (BQ != 0 ? COMM_WARPS * CTAS : 0));   // + one arrival per dequantising warp
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -299,7 +333,7 @@ gemm_kernel(const __grid_constant__ Params p) {
     *abort_smem = 0;
     fence_mbar_init();
     prefetch_tmap(&p.tmA);
-    prefetch_tmap(&p.tmB);
+    if (BQ == 0) prefetch_tmap(&p.tmB);
     if (EPI != EPI_SCATTER) prefetch_tmap(&p.tmD);
   }
   if (warp == 0) {
@@ -360,11 +394,13 @@ gemm_kernel(const __grid_constant__ Params p) {
           const uint32_t sB = sB0 + stage * B_STAGE_BYTES;
           if constexpr (!PAIR) {
             const uint32_t fb = full_bar(stage);
-            mbar_expect_tx(fb, STAGE_BYTES);
+            mbar_expect_tx(fb, BQ != 0 ? A_STAGE_BYTES : STAGE_BYTES);
             if (A_MN) tma_load_3d(sA, &p.tmA, fb, 0, ka, m0 / 64);
             else if (own) tma_load_2d(sA, &p.tmA2, fb, ka, m0 - own_lo);
             else      tma_load_2d(sA, &p.tmA, fb, ka, m0);
-            if (EPI == EPI_GLU_FWD) {
+            if (BQ != 0) {
+              // B is written by the dequantising warps
+            } else if (EPI == EPI_GLU_FWD) {
               tma_load_2d(sB, &p.tmB, fb, kbb, n0);
               tma_load_2d(sB + B_STAGE_BYTES / 2, &p.tmB, fb, kbb, p.b_up_rows + n0);
             } else if (B_MN) {
@@ -374,12 +410,14 @@ gemm_kernel(const __grid_constant__ Params p) {
             }
           } else {
             // Both CTAs' bytes are counted on the leader's barrier; only the leader arms it.
-            if (cta_rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+            if (cta_rank == 0) mbar_expect_tx(full_bar(stage), 2 * (BQ != 0 ? A_STAGE_BYTES : STAGE_BYTES));
             const uint32_t fb = mapa_u32(full_bar(stage), 0);
             if (A_MN) tma_load_3d_pair(sA, &p.tmA, fb, 0, ka, m0 / 64);
             else if (own) tma_load_2d_pair(sA, &p.tmA2, fb, ka, m0 - own_lo);
             else      tma_load_2d_pair(sA, &p.tmA, fb, ka, m0);
-            if (EPI == EPI_GLU_FWD) {
+            if (BQ != 0) {
+              // B is written by the dequantising warps
+            } else if (EPI == EPI_GLU_FWD) {
               // leader stages the gate rows, its peer the up rows: accumulator columns [0,128) | [128,256)
               tma_load_2d_pair(sB, &p.tmB, fb, kbb, (cta_rank ? p.b_up_rows : 0) + n0);
             } else if (B_MN) {
@@ -647,6 +685,87 @@ gemm_kernel(const __grid_constant__ Params p) {
     }
     if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
+  } else if (BQ != 0) {
+    // ===================================================================== weight dequantisation
+    // 128 threads fill this CTA's B stage for every k block: a thread takes half rows (32 k = 64 bytes of bf16 = four
+    // 16-byte chunks), reads their codes one k block ahead, and stores chunk c of row r at r*128 + ((c ^ (r & 7)) << 4)
+    // inside 1 KiB groups of 8 rows: the image of a 128-byte-swizzled TMA load.
+    const int tid = (warp - (2 + EPI_WARPS)) * 32 + lane;
+    constexpr int NT = COMM_WARPS * 32;
+    constexpr int UNITS = BN_CTA * 2 / NT;                 // half rows per thread and k block (1, 2 or 4)
+    static_assert(BN_CTA * 2 % NT == 0, "half rows must divide among the dequantising threads");
+    constexpr int WORDS = BQ == 4 ? 4 : 8;                 // 32-bit code words per half row
+    const int my_tiles = tile_first < total_tiles ? (total_tiles - tile_first + tile_step - 1) / tile_step : 0;
+    const int steps = my_tiles * p.k_blocks;
+    uint32_t cur[UNITS][WORDS], nxt[UNITS][WORDS];
+    float cur_s[UNITS], nxt_s[UNITS];
+    auto fetch = [&](int step, uint32_t (&w)[UNITS][WORDS], float (&sc)[UNITS]) {
+      const int ti = step / p.k_blocks, kb = step - ti * p.k_blocks;
+      const Work wk = get_work(p, tile_first + ti * tile_step, (int)cta_rank, CTAS, TILE_N);
+      const int n_base = wk.bn0 + (int)cta_rank * BN_CTA;
+      const int k0 = wk.kb0 + kb * BK;
+#pragma unroll
+      for (int u = 0; u < UNITS; ++u) {
+        const int unit = tid + u * NT, row = unit >> 1, half = unit & 1;
+        const int n = n_base + row;
+        if (n < p.bq_rows) {
+          const uint8_t* src = p.bq_codes + (long long)n * p.bq_row_bytes + (BQ == 4 ? (k0 >> 1) + half * 16 : k0 + half * 32);
+          const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(src));
+          w[u][0] = q0.x; w[u][1] = q0.y; w[u][2] = q0.z; w[u][3] = q0.w;
+          if constexpr (BQ == 8) {
+            const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+            w[u][4] = q1.x; w[u][5] = q1.y; w[u][6] = q1.z; w[u][7] = q1.w;
+          }
+          sc[u] = __half2float(p.bq_scales[(long long)n * p.bq_scale_ld + (k0 >> 6)]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < WORDS; ++j) w[u][j] = BQ == 4 ? 0x88888888u : 0x80808080u;    // codes of zero
+          sc[u] = 0.f;
+        }
+      }
+    };
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    if (steps > 0) fetch(0, cur, cur_s);
+    for (int step = 0; ok && step < steps; ++step) {
+      if (step + 1 < steps) fetch(step + 1, nxt, nxt_s);
+      ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, p.status, SITE_SMEM_EMPTY);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const uint32_t sB = sB0 + stage * B_STAGE_BYTES;
+#pragma unroll
+      for (int u = 0; u < UNITS; ++u) {
+        const int unit = tid + u * NT, row = unit >> 1, half = unit & 1;
+        const uint32_t row_addr = sB + (row >> 3) * 1024 + (row & 7) * 128;
+        const __nv_bfloat162 s2 = __floats2bfloat162_rn(cur_s[u], cur_s[u]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          if constexpr (BQ == 4) {
+            v = dequant_nibbles(cur[u][j], s2);
+          } else {
+            dequant_bytes(cur[u][2 * j], cur_s[u], v.x, v.y);
+            dequant_bytes(cur[u][2 * j + 1], cur_s[u], v.z, v.w);
+          }
+          const uint32_t addr = row_addr + ((((uint32_t)(half * 4 + j)) ^ ((uint32_t)row & 7u)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+        }
+      }
+      fence_proxy_async_smem();               // the tensor core reads these bytes through the async proxy
+      __syncwarp();
+      if (lane == 0) {
+        if (PAIR && cta_rank != 0) mbar_arrive_cluster(mapa_u32(full_bar(stage), 0));
+        else mbar_arrive(full_bar(stage));
+      }
+#pragma unroll
+      for (int u = 0; u < UNITS; ++u) {
+        cur_s[u] = nxt_s[u];
+#pragma unroll
+        for (int j = 0; j < WORDS; ++j) cur[u][j] = nxt[u][j];
+      }
+      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    }
   } else if (AG) {
     // ===================================================================== all-gather push
     // The comm warps of all CTAs together store this rank's rows into every rank's gathered

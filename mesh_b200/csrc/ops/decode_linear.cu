@@ -21,6 +21,7 @@
 #include "decode_api.h"
 #include "../device/ptx.cuh"
 #include "../runtime/host_common.h"
+#include <cstdlib>
 #include <cstring>
 
 namespace mesh {
@@ -51,6 +52,8 @@ struct LinArgs {
   const uint32_t* step_ptr; uint32_t calls_per_step, call_index;   // sequence number = step * calls + index + 1
   const __nv_bfloat16* residual; long long ldr;       // [B, N]
   Status* status;
+  int l2_prefetch;
+  int xpad;                                           // bytes of padding per x row in shared memory (bank spread)
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -99,12 +102,32 @@ __device__ __forceinline__ void group_rows(const LinArgs& a, int g, int& rA, int
 
 // One pipeline step = one chunk of CH k-values of one 16-row group for this warp's K slice.
 // bf16: CH = 32*U (U 16-byte loads per row); 4-bit: CH = 64*U (U pairs of 32-bit words per row).
+// Weight formats (template parameter W4): 0 = bf16; 1 = 4-bit codes read as 4-byte words (any K % 512 == 0);
+// 2 = 4-bit codes read 16 bytes at a time (a lane takes 32 consecutive k of a 128-wide block: four times the bytes in
+// flight per load instruction, which is what a latency-bound stream of quarter-size weights needs); 3 = 8-bit codes,
+// 16 bytes = 16 consecutive k per lane.  A dot product does not notice the order of k as long as W and x agree.
 template <int W4, int U>
 struct Chunk {
-  uint4 a[W4 ? (U + 1) / 2 : U];      // bf16: U x 16 B of row A;  4-bit: U x {word0, word1} packed two per uint4
-  uint4 b[W4 ? (U + 1) / 2 : U];
+  uint4 a[W4 == 1 ? (U + 1) / 2 : U];  // bf16 / wide formats: U x 16 B of row A;  format 1: U x {word0, word1}
+  uint4 b[W4 == 1 ? (U + 1) / 2 : U];
   float sa[W4 ? U : 1], sb[W4 ? U : 1];
 };
+
+template <int W4, int U> struct ChunkK { static constexpr int value = (W4 == 0 ? 32 : W4 == 1 ? 64 : W4 == 2 ? 128 : 64) * U; };
+// byte offset inside an x row of the first k this lane multiplies in a chunk
+template <int W4> __device__ __forceinline__ int lane_k(int t4) { return W4 == 2 ? t4 * 32 : (W4 == 3 ? t4 * 16 : t4 * 8); }
+
+// four 8-bit codes -> two bf16x2 words (c - 128) * s, exact until the final rounding to bf16
+__device__ __forceinline__ void dequant_b4(uint32_t w, float s, uint32_t& lo, uint32_t& hi) {
+  const float k = 8388736.f;                                      // 2^23 + 128
+  const float f0 = (__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)) - k) * s;
+  const float f1 = (__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)) - k) * s;
+  const float f2 = (__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7542)) - k) * s;
+  const float f3 = (__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7543)) - k) * s;
+  __nv_bfloat162 a = __floats2bfloat162_rn(f0, f1), b = __floats2bfloat162_rn(f2, f3);
+  lo = *reinterpret_cast<uint32_t*>(&a);
+  hi = *reinterpret_cast<uint32_t*>(&b);
+}
 
 template <int W4, int U>
 __device__ __forceinline__ void load_chunk(const LinArgs& a, int grp, int kb, int k_lo, int g8, int t4, Chunk<W4, U>& c) {
@@ -118,6 +141,22 @@ __device__ __forceinline__ void load_chunk(const LinArgs& a, int grp, int kb, in
     for (int u = 0; u < U; ++u) {
       c.a[u] = __ldcs(reinterpret_cast<const uint4*>(wA + 32 * u));
       c.b[u] = __ldcs(reinterpret_cast<const uint4*>(wB + 32 * u));
+    }
+  } else if constexpr (W4 == 2 || W4 == 3) {
+    constexpr int KPB = W4 == 2 ? 2 : 1;                  // k values per byte
+    constexpr int BLK = W4 == 2 ? 128 : 64;               // k per 16-byte load of a quad of lanes
+    const long long row_bytes = K / KPB;
+    const uint8_t* wA = reinterpret_cast<const uint8_t*>(a.w) + (long long)(rA + g8) * row_bytes + (k_lo + kb) / KPB + t4 * 16;
+    const uint8_t* wB = reinterpret_cast<const uint8_t*>(a.w) + (long long)(rB + g8) * row_bytes + (k_lo + kb) / KPB + t4 * 16;
+    const int k_lane = k_lo + kb + lane_k<W4>(t4);
+    const __half* sA = a.scales + (long long)(rA + g8) * (K / 64);
+    const __half* sB = a.scales + (long long)(rB + g8) * (K / 64);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      c.a[u] = __ldcs(reinterpret_cast<const uint4*>(wA + u * (BLK / KPB)));
+      c.b[u] = __ldcs(reinterpret_cast<const uint4*>(wB + u * (BLK / KPB)));
+      c.sa[u] = __half2float(sA[(k_lane + u * BLK) >> 6]);
+      c.sb[u] = __half2float(sB[(k_lane + u * BLK) >> 6]);
     }
   } else {
     const uint32_t* wA = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.w) + (long long)(rA + g8) * (K / 2)) + ((k_lo + kb) >> 3) + t4;
@@ -147,6 +186,39 @@ __device__ __forceinline__ void mma_chunk(const Chunk<W4, U>& c, const uint8_t* 
       mma_bf16(acc, c.a[u].x, c.b[u].x, c.a[u].y, c.b[u].y, xv.x, xv.y);
       mma_bf16(acc, c.a[u].z, c.b[u].z, c.a[u].w, c.b[u].w, xv.z, xv.w);
     }
+  } else if constexpr (W4 == 2) {
+    const __nv_bfloat162 off = __floats2bfloat162_rn(136.f, 136.f);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const __nv_bfloat162 sa2 = __floats2bfloat162_rn(c.sa[u], c.sa[u]), sb2 = __floats2bfloat162_rn(c.sb[u], c.sb[u]);
+      const uint32_t pa[4] = {c.a[u].x, c.a[u].y, c.a[u].z, c.a[u].w};
+      const uint32_t pb[4] = {c.b[u].x, c.b[u].y, c.b[u].z, c.b[u].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {                       // word j: 8 consecutive k = two MMAs
+        uint32_t wa[4], wb[4];
+        dequant8(pa[j], sa2, off, wa);
+        dequant8(pb[j], sb2, off, wb);
+        const uint4 xv = *reinterpret_cast<const uint4*>(xp + 256 * u + 16 * j);
+        mma_bf16(acc, wa[0], wb[0], wa[1], wb[1], xv.x, xv.y);
+        mma_bf16(acc, wa[2], wb[2], wa[3], wb[3], xv.z, xv.w);
+      }
+    }
+  } else if constexpr (W4 == 3) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t pa[4] = {c.a[u].x, c.a[u].y, c.a[u].z, c.a[u].w};
+      const uint32_t pb[4] = {c.b[u].x, c.b[u].y, c.b[u].z, c.b[u].w};
+      const uint4 x0 = *reinterpret_cast<const uint4*>(xp + 128 * u);
+      const uint4 x1 = *reinterpret_cast<const uint4*>(xp + 128 * u + 16);
+      const uint32_t xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {                       // word j: 4 consecutive k = one MMA
+        uint32_t al, ah, bl, bh;
+        dequant_b4(pa[j], c.sa[u], al, ah);
+        dequant_b4(pb[j], c.sb[u], bl, bh);
+        mma_bf16(acc, al, bl, ah, bh, xw[2 * j], xw[2 * j + 1]);
+      }
+    }
   } else {
     const uint32_t* pa = reinterpret_cast<const uint32_t*>(c.a);
     const uint32_t* pb = reinterpret_cast<const uint32_t*>(c.b);
@@ -173,14 +245,14 @@ template <int W4, int U>
 __global__ void __launch_bounds__(THREADS) decode_linear_kernel(const LinArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int K = a.K;
-  const int xstride = K * 2 + XPAD;                               // bytes per x row
+  const int xstride = K * 2 + a.xpad;                             // bytes per x row
   uint8_t* xs = smem;                                             // [NB][xstride]
   float* red = reinterpret_cast<float*>(smem + NB * xstride);     // [WARPS][16][NB]
   float* fin = red + WARPS * 16 * NB;                             // [16][NB]
   __shared__ float rstd_s[NB];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g8 = lane >> 2, t4 = lane & 3;
-  constexpr int CH = (W4 ? 64 : 32) * U;
+  constexpr int CH = ChunkK<W4, U>::value;
   const int kslice = K / WARPS;
   const int k_lo = warp * kslice;
   const int chunks = kslice / CH;
@@ -192,6 +264,19 @@ __global__ void __launch_bounds__(THREADS) decode_linear_kernel(const LinArgs a)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   Chunk<W4, U> c0, c1;
   if (steps > 0) load_chunk<W4, U>(a, blockIdx.x, 0, k_lo, g8, t4, c0);
+  if (a.l2_prefetch) {
+    // Every row this CTA will read is requested into L2 now, while the kernel before this one in the stream is
+    // still running (this kernel's CTAs are resident beside it): HBM keeps streaming across the kernel boundary and
+    // the loads below find their bytes in L2.  One bulk prefetch per row (16 rows per group).
+    const long long row_bytes = W4 == 0 ? (long long)K * 2 : (W4 == 3 ? (long long)K : (long long)K / 2);
+    for (int i = threadIdx.x; i < my_groups * 16; i += THREADS) {
+      int rA, rB;
+      group_rows(a, blockIdx.x + (i >> 4) * gridDim.x, rA, rB);
+      const int row = ((i & 15) < 8) ? rA + (i & 15) : rB + (i & 15) - 8;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(a.w) + (long long)row * row_bytes;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)row_bytes) : "memory");
+    }
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // ---- prologue: x (zero rows past the batch) -> shared memory, optionally RMS-normalised
@@ -241,7 +326,7 @@ __global__ void __launch_bounds__(THREADS) decode_linear_kernel(const LinArgs a)
     }
   }
 
-  const uint8_t* xbase = xs + g8 * xstride + (k_lo + t4 * 8) * 2;
+  const uint8_t* xbase = xs + g8 * xstride + (k_lo + lane_k<W4>(t4)) * 2;
   float c[4] = {0.f, 0.f, 0.f, 0.f};
 
   // Two register sets alternate: while one chunk feeds the tensor cores the next one is in flight,
@@ -367,7 +452,8 @@ using namespace mesh::decode;
 extern "C" int mesh_decode_linear(const MeshDecodeLinear* d, void* stream) {
   if (d->B < 1 || d->B > NB) return set_error(-2, "decode_linear: batch must be 1..8");
   if (d->K % 256) return set_error(-2, "decode_linear: K must be a multiple of 256");
-  if (d->w4 && d->K % 512) return set_error(-2, "decode_linear: 4-bit weights need K %% 512 == 0");
+  if (d->w4 != 0 && d->w4 != 1 && d->w4 != 8) return set_error(-2, "decode_linear: weight format must be 0 (bf16), 1 (4-bit) or 8 (8-bit)");
+  if (d->w4 && d->K % 512) return set_error(-2, "decode_linear: quantised weights need K %% 512 == 0");
   if (d->N % 16) return set_error(-2, "decode_linear: N must be a multiple of 16");
   if (d->world > MESH_DEC_MAX_RANKS) return set_error(-4, "decode_linear: world too large");
   LinArgs a;
@@ -396,20 +482,44 @@ extern "C" int mesh_decode_linear(const MeshDecodeLinear* d, void* stream) {
   if (smem > 220 * 1024) return set_error(-2, "decode_linear: K too large for shared memory");
   const int kslice = d->K / WARPS;
   // chunk width: 128 k per step when the slice allows it (4 x 16 B per row in flight, twice), else one block
-  const bool wide = d->w4 ? (kslice % 128 == 0) : (kslice % 128 == 0);
+  const bool wide = kslice % 128 == 0;
   void (*kern)(const LinArgs) = nullptr;
   int slot = 0;
-  if (d->w4) { kern = wide ? decode_linear_kernel<1, 2> : decode_linear_kernel<1, 1>; slot = wide ? 0 : 1; }
+  a.xpad = XPAD;
+  static int narrow4 = -1;
+  if (narrow4 < 0) { const char* e = getenv("MESH_DECODE_W4_NARROW"); narrow4 = (e && e[0] == '1') ? 1 : 0; }
+  if (d->w4 == 8) {
+    // 8-bit codes, 16 bytes (16 k) per lane and load: chunks of 64 k per quad of lanes
+    if (kslice % 256 == 0) { kern = decode_linear_kernel<3, 4>; slot = 4; }
+    else if (kslice % 128 == 0) { kern = decode_linear_kernel<3, 2>; slot = 5; }
+    else { kern = decode_linear_kernel<3, 1>; slot = 6; }
+    a.xpad = 16;
+  } else if (d->w4 && kslice % 128 == 0 && !narrow4) {
+    // 4-bit codes, 16 bytes (32 k) per lane and load: chunks of 128 k per quad of lanes
+    if (kslice % 256 == 0) { kern = decode_linear_kernel<2, 2>; slot = 7; }
+    else { kern = decode_linear_kernel<2, 1>; slot = 8; }
+    a.xpad = 16;
+  } else if (d->w4) { kern = wide ? decode_linear_kernel<1, 2> : decode_linear_kernel<1, 1>; slot = wide ? 0 : 1; }
   else       { kern = wide ? decode_linear_kernel<0, 4> : decode_linear_kernel<0, 1>; slot = wide ? 2 : 3; }
-  static bool configured[4] = {false, false, false, false};
+  static bool configured[9] = {false, false, false, false, false, false, false, false, false};
   if (!configured[slot]) {
     MESH_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     configured[slot] = true;
   }
   int grid = a.n_groups;
-  // at most two CTAs per SM: fewer, longer-lived CTAs amortise the x prologue and keep the weight
-  // pipeline full across group boundaries
-  const int cap = sm_count() * (smem > 100 * 1024 ? 1 : 2);
+  // CTAs per SM.  One (the default) leaves room on every SM for a CTA of the NEXT kernel of the stream, which starts
+  // as a programmatic dependent, asks for its weights (L2 prefetch, first chunk) and only then waits for this kernel:
+  // the weight stream does not stop at kernel boundaries.  MESH_DECODE_CTAS_PER_SM=2 gives the older behaviour (a
+  // kernel fills the SMs by itself and the next one starts when it ends).
+  static int per_sm = -1, prefetch = -1;
+  if (per_sm < 0) {
+    const char* e = getenv("MESH_DECODE_CTAS_PER_SM");
+    per_sm = (e && e[0] == '2') ? 2 : 1;
+    const char* f = getenv("MESH_DECODE_L2_PREFETCH");
+    prefetch = (f && f[0] == '0') ? 0 : 1;
+  }
+  a.l2_prefetch = prefetch;       // rows are multiples of 16 bytes in every format (K % 256 == 0)
+  const int cap = sm_count() * (smem > 100 * 1024 ? 1 : per_sm);
   if (grid > cap) grid = cap;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));

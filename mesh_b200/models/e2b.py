@@ -85,13 +85,14 @@ class E2BDecoder:
             wd = _rand((d, c.d_ff), c.init_std, s + 7, dev)[:, r * self.Fl:(r + 1) * self.Fl].contiguous()
             L = dict(n1=torch.ones(d, dtype=torch.bfloat16, device=dev), n2=torch.ones(d, dtype=torch.bfloat16, device=dev),
                      wqkv=wqkv, wo=wo, wgu=wgu, wd=wd)
-            if quant == "w4":
+            if quant in ("w4", "w8"):
+                quantize, dequantize = (D.quantize_w4, D.dequantize_w4) if quant == "w4" else (D.quantize_w8, D.dequantize_w8)
                 for k in ("wqkv", "wo", "wgu", "wd"):
-                    if L[k].shape[1] % 512:                   # the 4-bit kernel walks K in steps of 512: a shard this
+                    if L[k].shape[1] % 512:                   # the quantised kernels walk K in steps of 512: a shard this
                         continue                              # narrow (wo at TP=8) stays bf16
-                    codes, scales = D.quantize_w4(L[k])
+                    codes, scales = quantize(L[k])
                     L[k + "_q"], L[k + "_s"] = codes, scales
-                    L[k] = D.dequantize_w4(codes, scales)     # prefill GEMMs use the dequantised values (same numbers)
+                    L[k] = dequantize(codes, scales)          # prefill GEMMs use the dequantised values (same numbers)
             L["kc"] = torch.zeros((batch, self.kvh, c.max_seq, hd), dtype=torch.bfloat16, device=dev)
             L["vc"] = torch.zeros_like(L["kc"])
             self.layers.append(L)
@@ -102,8 +103,8 @@ class E2BDecoder:
         self.emb = torch.cat(chunks)
         del chunks
         self.lm_head = self.emb[r * self.Vl:(r + 1) * self.Vl]
-        if quant == "w4":
-            self.lm_q, self.lm_s = D.quantize_w4(self.lm_head)
+        if quant in ("w4", "w8"):
+            self.lm_q, self.lm_s = (D.quantize_w4 if quant == "w4" else D.quantize_w8)(self.lm_head)
         self.nf = torch.ones(d, dtype=torch.bfloat16, device=dev)
         self.cos, self.sin = rope_tables(c.max_seq, hd, c.theta, device=dev)
         # decode workspaces
@@ -132,7 +133,7 @@ class E2BDecoder:
 
     # ------------------------------------------------------------------ pieces
     def _w(self, L, name):
-        if self.quant == "w4" and (name + "_q") in L:
+        if self.quant in ("w4", "w8") and (name + "_q") in L:
             return L[name + "_q"], L[name + "_s"]
         return L[name], None
 
@@ -163,12 +164,19 @@ class E2BDecoder:
                 D.decode_linear(self.h, w, scales=s, mode=D.ALLREDUCE, out=x, residual=x1, ar=self._ar(2 * l + 1))
             else:
                 D.decode_linear(self.h, w, scales=s, out=x, residual=x1)
-        if self.quant == "w4":
+        if self.quant in ("w4", "w8"):
             D.decode_linear(x, self.lm_q, scales=self.lm_s, norm_w=self.nf, eps=c.eps, out=self.logits)
         else:
             D.decode_linear(x, self.lm_head, norm_w=self.nf, eps=c.eps, out=self.logits)
         D.decode_argmax(self.logits, self.tok, self.pos, vocab_offset=self.rank * self.Vl, rank=self.rank, world=self.world,
                         xchg_ptrs=self.xchg.ptrs() if self.world > 1 else None, step=self.step)
+
+    def _mm(self, x, L, name):
+        """Prefill projection: quantised weights go through the GEMM that dequantises them in registers."""
+        if self.quant in ("w4", "w8") and (name + "_q") in L and x.shape[1] % 64 == 0:
+            from ..ops.gemm import gemm_q
+            return gemm_q(x, L[name + "_q"], L[name + "_s"])
+        return gemm(x, L[name])
 
     # ------------------------------------------------------------------ prefill
     def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
@@ -183,7 +191,7 @@ class E2BDecoder:
         att_out = torch.empty((B * T, self.qh * hd), dtype=torch.bfloat16, device=self.dev)
         for l, L in enumerate(self.layers):
             h, _, _ = rmsnorm_fwd(x, L["n1"], c.eps)
-            qkv = gemm(h, L["wqkv"])
+            qkv = self._mm(h, L, "wqkv")
             qv = qkv[:, :self.qh * hd].view(B * T, self.qh, hd)
             kv = qkv[:, self.qh * hd:(self.qh + self.kvh) * hd].view(B * T, self.kvh, hd)
             rope_(qv, positions, self.cos, self.sin)
@@ -194,18 +202,18 @@ class E2BDecoder:
             # prefill attention straight from the fused qkv matrix (tcgen05 flash attention; no copies of q, k, v)
             flash_attention(qv.view(B, T, self.qh, hd), kv.view(B, T, self.kvh, hd), vv.view(B, T, self.kvh, hd), causal=True,
                             window=c.window if c.is_local(l) else 0, out=att_out.view(B, T, self.qh, hd))
-            o = gemm(att_out, L["wo"])
+            o = self._mm(att_out, L, "wo")
             if comm is not None:
                 comm.all_reduce(o)
             x = x + o
             h, _, _ = rmsnorm_fwd(x, L["n2"], c.eps)
             a, _ = glu_fwd(h, L["wgu"], act="gelu_tanh", save_gu=False)
-            o = gemm(a, L["wd"])
+            o = self._mm(a, L, "wd")
             if comm is not None:
                 comm.all_reduce(o)
             x = x + o
         last = x.view(B, T, d)[:, -1].contiguous()
-        if self.quant == "w4":
+        if self.quant in ("w4", "w8"):
             D.decode_linear(last, self.lm_q, scales=self.lm_s, norm_w=self.nf, eps=c.eps, out=self.logits)
         else:
             D.decode_linear(last, self.lm_head, norm_w=self.nf, eps=c.eps, out=self.logits)
@@ -243,7 +251,7 @@ class E2BDecoder:
         return self.out_tokens[:steps]
 
 
-def bench_decode(ctx, steps: int = 256, prompt_len: int = 512, configs=(("bf16", 1), ("bf16", 8), ("w4", 1), ("w4", 8)),
+def bench_decode(ctx, steps: int = 256, prompt_len: int = 512, configs=(("bf16", 1), ("bf16", 8), ("w4", 1), ("w4", 8), ("w8", 1), ("w8", 8)),
                  cfg: E2BConfig | None = None) -> dict:
     """Decode tokens/s (whole job: batch * steps / time), device-timed, max over ranks."""
     import torch.distributed as dist

@@ -63,6 +63,22 @@ def dequantize_w4(codes: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     return (vals.view(N, K // 64, 64) * scales.float()[..., None]).view(N, K).to(torch.bfloat16)
 
 
+def quantize_w8(w: torch.Tensor, group: int = 64):
+    """``w [N, K]`` -> ``(codes uint8 [N, K], scales fp16 [N, K/group])``: ``w ~ (code - 128) * scale[row, k // 64]``,
+    codes in the natural order of k (the north star's 8-bit group-quantised variant)."""
+    assert group == 64 and w.dim() == 2 and w.shape[1] % 64 == 0
+    N, K = w.shape
+    wf = w.float().view(N, K // group, group)
+    scale = (wf.abs().amax(-1) / 127.0).clamp_min(1e-8).to(torch.float16)
+    codes = torch.clamp(torch.round(wf / scale.float()[..., None]) + 128, 1, 255).to(torch.uint8)
+    return codes.view(N, K).contiguous(), scale.contiguous()
+
+
+def dequantize_w8(codes: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    N, K = codes.shape
+    return ((codes.float() - 128.0).view(N, K // 64, 64) * scales.float()[..., None]).view(N, K).to(torch.bfloat16)
+
+
 def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -76,7 +92,8 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, *, scales: torch.Tensor | No
                   mode: int = STORE, act: str = "gelu_tanh", up_off: int = 0,
                   out: torch.Tensor | None = None, out_f32: bool = False, residual: torch.Tensor | None = None,
                   qkv: dict | None = None, ar: dict | None = None) -> torch.Tensor | None:
-    """One fused skinny linear layer.  ``x [B<=8, K]`` bf16; ``w`` bf16 ``[rows, K]`` or uint8 codes with ``scales``.
+    """One fused skinny linear layer.  ``x [B<=8, K]`` bf16; ``w`` bf16 ``[rows, K]``, or uint8 codes with
+    ``scales`` (``[rows, K/2]``: 4-bit, :func:`quantize_w4`; ``[rows, K]``: 8-bit, :func:`quantize_w8`).
 
     ``mode``: STORE (``out[b, n]``, optional ``residual`` added) | GLU (``w = [gate; up]``, ``up_off`` = gate rows) |
     QKV (``qkv`` = dict(q_heads, kv_heads, head_dim, pos, cos, sin, q_out, k_cache, v_cache, max_seq)) |
@@ -84,7 +101,11 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, *, scales: torch.Tensor | No
     outputs, adds ``residual``).
     """
     B, K = x.shape
-    w4 = scales is not None
+    w4 = 0                                   # weight format: 0 bf16, 1 4-bit codes, 8 8-bit codes
+    if scales is not None:
+        w4 = 8 if w.shape[1] == K else 1
+        if w4 == 1 and w.shape[1] * 2 != K:
+            raise ValueError(f"decode_linear: codes of width {w.shape[1]} do not fit K = {K} in 4 or 8 bits")
     rows = w.shape[0]
     d = _Lin()
     d.x, d.ldx, d.B, d.K = x.data_ptr(), x.stride(0), B, K

@@ -130,29 +130,38 @@ def to_group64(fields: dict, dtype=torch.bfloat16, device=None):
 
 
 class CodedLinear(torch.nn.Module):
-    """``y = x W^T`` with ``W`` stored as 4-bit codes and one fp16 scale per group of 64 inputs.
+    """``y = x W^T`` with ``W`` stored as 4-bit or 8-bit codes and one fp16 scale per group of 64 inputs.
 
-    Up to 8 rows of ``x`` on CUDA go through the fused decode kernel (dequantised in registers); anything else
-    dequantises the matrix and multiplies."""
+    On bf16 CUDA inputs the codes are dequantised in registers on the way to the tensor cores, never to memory: up to
+    8 rows of ``x`` go through the fused decode kernel (weight streaming), more rows through the tcgen05 GEMM with
+    dequantising producer warps (``gemm_q``).  Elsewhere (CPU, other dtypes, widths the kernels do not tile) the
+    matrix is dequantised and multiplied with PyTorch."""
 
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, bits: int = 4):
         super().__init__()
-        from .decode import quantize_w4
-        codes, scales = quantize_w4(weight)
+        from .decode import quantize_w4, quantize_w8
+        if bits not in (4, 8):
+            raise ValueError("CodedLinear: 4 or 8 bits")
+        codes, scales = (quantize_w4 if bits == 4 else quantize_w8)(weight)
+        self.bits = bits
         self.register_buffer("codes", codes)
         self.register_buffer("scales", scales)
         self.out_features, self.in_features = weight.shape
 
     def dense(self) -> torch.Tensor:
-        from .decode import dequantize_w4
-        return dequantize_w4(self.codes, self.scales)
+        from .decode import dequantize_w4, dequantize_w8
+        return (dequantize_w4 if self.bits == 4 else dequantize_w8)(self.codes, self.scales)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
-        if x2.is_cuda and x2.dtype == torch.bfloat16 and x2.shape[0] <= 8 and self.in_features % 512 == 0:
-            from .decode import decode_linear
-            return decode_linear(x2.contiguous(), self.codes, scales=self.scales).reshape(*lead, self.out_features)
+        if x2.is_cuda and x2.dtype == torch.bfloat16 and x2.shape[0] > 0:
+            if x2.shape[0] <= 8 and self.in_features % 512 == 0 and self.out_features % 16 == 0:
+                from .decode import decode_linear
+                return decode_linear(x2.contiguous(), self.codes, scales=self.scales).reshape(*lead, self.out_features)
+            if self.in_features % 64 == 0 and self.out_features % 8 == 0:
+                from .gemm import gemm_q
+                return gemm_q(x2.contiguous(), self.codes, self.scales).reshape(*lead, self.out_features)
         return torch.nn.functional.linear(x2, self.dense().to(x2.dtype)).reshape(*lead, self.out_features)
 
 
@@ -219,7 +228,16 @@ class CodedMatrix(torch.nn.Module):
                         self.stored_cols, dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return torch.nn.functional.linear(self.transform(x), self.weight(x.dtype))
+        return _linear(self.transform(x), self.weight(x.dtype))
+
+
+def _linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x w^T``: this package's GEMM for bf16 CUDA operands it tiles, PyTorch elsewhere."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 \
+            and x.numel() > 0:
+        from .gemm import gemm
+        return gemm(x.reshape(-1, x.shape[-1]).contiguous(), w.contiguous()).reshape(*x.shape[:-1], w.shape[0])
+    return torch.nn.functional.linear(x, w)
 
 
 class CodedFFN(torch.nn.Module):
@@ -237,8 +255,8 @@ class CodedFFN(torch.nn.Module):
 
     def forward(self, x):
         t = self.gate.transform(x)
-        g = torch.nn.functional.linear(t, self.gate.weight(x.dtype))
-        u = torch.nn.functional.linear(t if self.shared else self.up.transform(x), self.up.weight(x.dtype))
+        g = _linear(t, self.gate.weight(x.dtype))
+        u = _linear(t if self.shared else self.up.transform(x), self.up.weight(x.dtype))
         return self.down(torch.nn.functional.gelu(g, approximate="tanh") * u)
 
 

@@ -163,6 +163,41 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def gemm_q(a: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, *, out: torch.Tensor | None = None,
+           num_ctas: int = 0, tile_n: int = 0, pair: int = 0) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ W[N, K]^T`` with ``W`` group-quantised: ``codes`` uint8 ``[N, K/2]`` (4-bit,
+    :func:`mesh_b200.ops.decode.quantize_w4`) or ``[N, K]`` (8-bit, ``quantize_w8``) and ``scales`` fp16 ``[N, K/64]``.
+
+    The codes are dequantised in registers by four extra warps of the GEMM kernel and written straight into the
+    tensor cores' shared-memory stages: the bf16 matrix never exists in global memory (K13 of the reference's operation
+    table; its coded weights are decoded the same way, compiler/mesh_compiler/operations.py:6996-7040)."""
+    _check2d(a, "a")
+    if codes.dtype != torch.uint8 or scales.dtype != torch.float16 or not codes.is_contiguous() or not scales.is_contiguous():
+        raise ValueError("gemm_q: codes must be contiguous uint8 and scales contiguous fp16")
+    M, K = a.shape
+    N = codes.shape[0]
+    bits = 8 if codes.shape[1] == K else 4
+    if bits == 4 and codes.shape[1] * 2 != K:
+        raise ValueError(f"gemm_q: codes of width {codes.shape[1]} do not fit K = {K} in 4 or 8 bits")
+    if K % 64 or tuple(scales.shape) != (N, K // 64):
+        raise ValueError("gemm_q: K must be a multiple of 64 with one scale per 64 inputs")
+    g = _native.GemmArgs()
+    g.A, g.B, g.b_scales, g.b_bits = a.data_ptr(), codes.data_ptr(), scales.data_ptr(), bits
+    g.M, g.N, g.K = M, N, K
+    g.lda, g.ldb = a.stride(0), K
+    g.a_rows, g.b_rows = M, N
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    _check2d(out, "out")
+    g.D, g.ldd, g.d_cols = out.data_ptr(), out.stride(0), out.shape[1]
+    g.epi = EPI_STORE
+    g.status = status_block(a.device).data_ptr()
+    g.world = 1
+    g.num_ctas, g.tile_n, g.pair = num_ctas, tile_n, pair
+    _launch(g)
+    return out
+
+
 def glu_fwd(x: torch.Tensor, w_gate_up: torch.Tensor, *, act: str = "silu", save_gu: bool = True,
             out: torch.Tensor | None = None, gu: torch.Tensor | None = None, **flow):
     """``act(x @ Wg^T) * (x @ Wu^T)`` where ``w_gate_up = [Wg; Wu]`` is ``[2F, K]``.

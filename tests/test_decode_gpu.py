@@ -40,16 +40,45 @@ def test_decode_linear_glu(act):
     _close(y, a * u)
 
 
-def test_decode_linear_w4():
+@pytest.mark.parametrize("B,K,N", [(5, 2048, 1024), (1, 8192, 2048), (8, 512, 64), (3, 1024, 256), (2, 4096, 48)])
+def test_decode_linear_w4(B, K, N, monkeypatch):
+    """4-bit group-64 weights: the 16-byte-per-lane reader (K slices of 128 and more per warp) and the 4-byte reader
+    (narrower slices, or MESH_DECODE_W4_NARROW=1) against the dequantised weights in fp32."""
     from mesh_b200.ops.decode import decode_linear, dequantize_w4, quantize_w4
-    B, K, N = 5, 2048, 1024
     x = torch.randn(B, K, device="cuda").bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
     codes, scales = quantize_w4(w)
     wd = dequantize_w4(codes, scales)
-    assert (wd.float() - w.float()).abs().max() < 0.02 * 4 / 7 + 1e-3       # half a quantisation step at 4 sigma
+    assert (wd.float() - w.float()).abs().max() < 0.02 * 5 / 7 + 1e-3       # half a quantisation step at 5 sigma
     y = decode_linear(x, codes, scales=scales)
     _close(y, x.float() @ wd.float().T)
+
+
+@pytest.mark.parametrize("B,K,N", [(5, 2048, 1024), (1, 8192, 2048), (8, 512, 64), (3, 1024, 256)])
+def test_decode_linear_w8(B, K, N):
+    from mesh_b200.ops.decode import decode_linear, dequantize_w8, quantize_w8
+    x = torch.randn(B, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+    codes, scales = quantize_w8(w)
+    wd = dequantize_w8(codes, scales)
+    assert (wd.float() - w.float()).abs().max() < 0.02 * 5 / 127 + 5e-4
+    y = decode_linear(x, codes, scales=scales)
+    _close(y, x.float() @ wd.float().T)
+
+
+def test_decode_glu_and_norm_with_quantised_weights():
+    from mesh_b200.ops.decode import GLU, decode_linear, dequantize_w4, dequantize_w8, quantize_w4, quantize_w8
+    B, K, F = 4, 2048, 512
+    x = torch.randn(B, K, device="cuda").bfloat16()
+    nw = (torch.randn(K, device="cuda") * 0.1 + 1).bfloat16()
+    w = (torch.randn(2 * F, K, device="cuda") * 0.02).bfloat16()
+    xn = (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()).bfloat16().float()
+    for quantize, dequantize in ((quantize_w4, dequantize_w4), (quantize_w8, dequantize_w8)):
+        codes, scales = quantize(w)
+        wd = dequantize(codes, scales).float()
+        y = decode_linear(x, codes, scales=scales, norm_w=nw, eps=1e-6, mode=GLU, act="gelu_tanh")
+        g, u = xn @ wd[:F].T, xn @ wd[F:].T
+        _close(y, torch.nn.functional.gelu(g, approximate="tanh") * u)
 
 
 def test_decode_qkv_rope_cache():

@@ -52,9 +52,9 @@ def _ref_logits(m, tokens):
         x = x + a @ L["wd"].float().T
     xf = x[:, -1]
     xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + c.eps) * m.nf.float()
-    if m.quant == "w4":          # the LM head reads the 4-bit codes of the tied table
-        from mesh_b200.ops.decode import dequantize_w4
-        return xf @ dequantize_w4(m.lm_q, m.lm_s).float().T
+    if m.quant in ("w4", "w8"):          # the LM head reads the codes of the tied table
+        from mesh_b200.ops.decode import dequantize_w4, dequantize_w8
+        return xf @ (dequantize_w4 if m.quant == "w4" else dequantize_w8)(m.lm_q, m.lm_s).float().T
     return xf @ m.emb.float().T
 
 
@@ -69,7 +69,7 @@ def _rel(a, b):
     return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
 
 
-@pytest.mark.parametrize("quant", ["bf16", "w4"])
+@pytest.mark.parametrize("quant", ["bf16", "w4", "w8"])
 def test_e2b_solo_matches_reference(quant):
     from mesh_b200.models.e2b import E2BDecoder
     from mesh_b200.utils.status import check_status

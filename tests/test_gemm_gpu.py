@@ -116,3 +116,30 @@ def test_chained_launches_give_the_same_bits_as_serial_ones(monkeypatch):
         assert torch.equal(a, b)
     for a, b in zip(outs[0], outs[2]):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (384, 1000, 2048), (4096, 2048, 2048), (200, 264, 320)])
+def test_gemm_with_group_quantised_weights(bits, M, N, K):
+    """Codes dequantised in registers by the GEMM's producer warps, against the dequantised matrix in fp32."""
+    from mesh_b200.ops.decode import dequantize_w4, dequantize_w8, quantize_w4, quantize_w8
+    from mesh_b200.ops.gemm import gemm_q
+    from mesh_b200.utils.status import check_status
+    a = _rand((M, K), seed=21)
+    w = _rand((N, K), 0.05, seed=22)
+    codes, scales = (quantize_w4 if bits == 4 else quantize_w8)(w)
+    wd = (dequantize_w4 if bits == 4 else dequantize_w8)(codes, scales)
+    for pair, tile_n in ((0, 0), (-1, 256), (0, 128), (-1, 128)):
+        out = gemm_q(a, codes, scales, pair=pair, tile_n=tile_n)
+        check_status()
+        _close(out, a.float() @ wd.float().T)
+
+
+def test_coded_linear_uses_the_kernels_for_any_batch():
+    from mesh_b200.ops.fragment import CodedLinear
+    w = _rand((1024, 2048), 0.05, seed=23)
+    for bits in (4, 8):
+        lin = CodedLinear(w, bits=bits).cuda()
+        for rows in (3, 8, 9, 700):
+            x = _rand((rows, 2048), seed=24 + rows)
+            _close(lin(x), x.float() @ lin.dense().float().T)
