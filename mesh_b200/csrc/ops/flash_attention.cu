@@ -263,6 +263,21 @@ __global__ void __launch_bounds__(THREADS, 1) flash_fwd_kernel(const __grid_cons
         m_ref = mx;
       }
       const float neg_ms = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref * p.scale_log2;
+      // The exponentials are computed into registers first: they need nothing from the previous block's P V
+      // product, which the tensor core is still running.
+      float sum = 0.f;
+      uint32_t w[NCH][16];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), p.scale_log2, neg_ms));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), p.scale_log2, neg_ms));
+          sum += p0 + p1;
+          __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
+          w[c][i / 2] = *reinterpret_cast<uint32_t*>(&hb);
+        }
+      }
       // P of the previous block must have been consumed before it is overwritten, and O must be final
       if (it > 0) {
         ok = mbar_wait(bar(O_DONE), (it - 1) & 1, abort_smem, p.status, SITE_TMEM_EMPTY);
@@ -270,26 +285,16 @@ __global__ void __launch_bounds__(THREADS, 1) flash_fwd_kernel(const __grid_cons
         if (!ok) continue;
         tc_fence_after();
       }
-      float sum = 0.f;
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), p.scale_log2, neg_ms));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), p.scale_log2, neg_ms));
-          sum += p0 + p1;
-          __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
-          w[i / 2] = *reinterpret_cast<uint32_t*>(&hb);
-        }
         // 32 columns = 64 bytes = 4 pieces of 16 B inside the 128-byte swizzled row of their 64-column chunk
         const int col = half * HALF + c * 32;
         const uint32_t row_base = sP + (col / 64) * (BQ * 128) + row * 128;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const uint32_t chunk = (((col % 64) / 32) * 4 + j) ^ (row & 7);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (chunk << 4)), "r"(w[4 * j]),
-                       "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3]) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (chunk << 4)), "r"(w[c][4 * j]),
+                       "r"(w[c][4 * j + 1]), "r"(w[c][4 * j + 2]), "r"(w[c][4 * j + 3]) : "memory");
         }
       }
       l = l * alpha + sum;

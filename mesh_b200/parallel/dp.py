@@ -36,8 +36,12 @@ class DataParallel:
     """Wraps a module: ``loss.backward()`` then ``dp.finish()``; gradients are averaged over the group."""
 
     def __init__(self, module: torch.nn.Module, world: int, rank: int, group=None, bucket_bytes: int = 64 << 20,
-                 all_reduce: bool = True):
+                 all_reduce: bool = True, axis=None):
+        """``axis``: the data-parallel :class:`~mesh_b200.parallel.topology.AxisContext` of a grid job; on CUDA its
+        communicator (this package's collective kernels over the axis' ranks) moves the buckets.  Without it the verbs
+        pick the job-wide communicator (``group is None``) or the ``torch.distributed`` group."""
         self.module, self.world, self.rank, self.group, self.all_reduce = module, world, rank, group, all_reduce
+        self.axis = axis
         params = [p for p in module.parameters() if p.requires_grad]
         self.buckets: list[_Bucket] = []
         cur, size = [], 0
@@ -68,6 +72,26 @@ class DataParallel:
             self._reduce(self.buckets[self.next_bucket])
             self.next_bucket += 1
 
+    def _own_comm(self, t):
+        ax = self.axis
+        if ax is not None and t.is_cuda and getattr(ax, "_heap", None) is not None:
+            return ax.comm
+        return None
+
+    def reduce_scatter(self, flat: torch.Tensor) -> torch.Tensor:
+        c = self._own_comm(flat)
+        if c is not None:
+            out = torch.empty(flat.numel() // self.world, dtype=flat.dtype, device=flat.device)
+            return c.reduce_scatter(out, flat, "sum")
+        return verbs.reduce_scatter(flat, 0, "sum", group=self.group)
+
+    def all_gather(self, shard: torch.Tensor) -> torch.Tensor:
+        c = self._own_comm(shard)
+        if c is not None:
+            out = torch.empty(shard.numel() * self.world, dtype=shard.dtype, device=shard.device)
+            return c.all_gather(out, shard.contiguous())
+        return verbs.all_gather(shard, 0, group=self.group)
+
     def _reduce(self, b: _Bucket):
         if self.world == 1:
             b.shard.copy_(b.flat[: b.per])
@@ -75,10 +99,10 @@ class DataParallel:
         if self.side is not None:
             self.side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.side):
-                b.shard = verbs.reduce_scatter(b.flat, 0, "sum", group=self.group)
+                b.shard = self.reduce_scatter(b.flat)
                 b.flat.record_stream(self.side)
         else:
-            b.shard = verbs.reduce_scatter(b.flat, 0, "sum", group=self.group)
+            b.shard = self.reduce_scatter(b.flat)
         self.launched.append(b)
 
     def finish(self):
@@ -89,7 +113,7 @@ class DataParallel:
         for b in self.buckets:
             b.shard = b.shard / self.world
             if self.all_reduce and self.world > 1:
-                full = verbs.all_gather(b.shard, 0, group=self.group)
+                full = self.all_gather(b.shard)
                 for p, off in zip(b.params, b.offsets):
                     p.grad.copy_(full[off: off + p.numel()].view_as(p))
             out.append((b.params, b.shard))

@@ -91,3 +91,59 @@ class ShardedAdamW:
         self.step_no = int(sd["step"])
         for i, st in enumerate(self.state):
             st["master"].copy_(sd[f"master.{i}"]); st["m"].copy_(sd[f"m.{i}"]); st["v"].copy_(sd[f"v.{i}"])
+
+
+class BucketedAdamW:
+    """ZeRO-1 AdamW over the buckets of a :class:`~mesh_b200.parallel.dp.DataParallel`.
+
+    The gradient traffic is the data-parallel wrapper's: one reduce-scatter per bucket, started from the autograd hooks
+    while the backward pass is still running, on this package's collective kernels when the ranks share a symmetric
+    heap.  This optimizer holds fp32 master weights and moments for this rank's slice of every bucket only, updates
+    the slice with the fused kernel (which also writes the new bf16 values) and all-gathers the updated slices, one
+    all-gather per bucket - no per-parameter collectives.  ``dp`` must be built with ``all_reduce=False``."""
+
+    def __init__(self, dp, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0):
+        if dp.all_reduce:
+            raise ValueError("BucketedAdamW reduces and gathers the buckets itself: build DataParallel(all_reduce=False)")
+        self.dp = dp
+        self._inner = ShardedAdamW([], lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        self.state = []
+        for b in dp.buckets:
+            flat = torch.cat([p.detach().reshape(-1) for p in b.params])
+            if b.padded > flat.numel():
+                flat = torch.cat([flat, flat.new_zeros(b.padded - flat.numel())])
+            lo = dp.rank * b.per
+            master = flat[lo:lo + b.per].float().clone()
+            self.state.append({"master": master, "m": torch.zeros_like(master), "v": torch.zeros_like(master),
+                               "new": torch.empty(b.per, dtype=b.params[0].dtype, device=master.device)})
+
+    @property
+    def step_no(self) -> int:
+        return self._inner.step_no
+
+    @torch.no_grad()
+    def step(self) -> None:
+        """After ``loss.backward()``: joins the bucket reductions, updates, gathers."""
+        shards = self.dp.finish()
+        self._inner.step_no += 1
+        for b, st, (_, g) in zip(self.dp.buckets, self.state, shards):
+            new = st["new"]
+            if st["master"].is_cuda and new.dtype == torch.bfloat16:
+                self._inner._update(st, g.contiguous(), new)
+            else:
+                self._inner._update(st, g.contiguous(), None)
+                new.copy_(st["master"])
+            full = self.dp.all_gather(new) if self.dp.world > 1 else new
+            for p, off in zip(b.params, b.offsets):
+                p.copy_(full[off: off + p.numel()].view_as(p))
+
+    def state_dict(self) -> dict:
+        out = {"step": self._inner.step_no}
+        for i, st in enumerate(self.state):
+            out[f"master.{i}"], out[f"m.{i}"], out[f"v.{i}"] = st["master"], st["m"], st["v"]
+        return out
+
+    def load_state_dict(self, sd: dict) -> None:
+        self._inner.step_no = int(sd["step"])
+        for i, st in enumerate(self.state):
+            st["master"].copy_(sd[f"master.{i}"]); st["m"].copy_(sd[f"m.{i}"]); st["v"].copy_(sd[f"v.{i}"])

@@ -7,6 +7,12 @@ rdma/mesh-flow.c:7-12); it names no training schedule.  This module adds the usu
 ``P - s`` microbatches of activations are alive on a stage.  A send toward a neighbour and the receive of the
 opposite direction from the same neighbour are issued as one batch, which is what keeps two stages that both want
 to send first from waiting on each other.
+
+On GPUs the transfers overlap the compute (``_AsyncWire``): activations and gradients travel on two communicators of
+their own, every send is issued as soon as its tensor has been computed and is not waited for, and every receive is
+posted one phase ahead, so that the next microbatch's input arrives during the current backward pass and the next
+gradient during the current forward pass; the compute stream waits (on the device, not the host) only where it first
+reads a received tensor.  ``MESH_PP_OVERLAP=0`` goes back to the batched, waited exchanges.
 """
 from __future__ import annotations
 
@@ -37,6 +43,67 @@ class _Wire:
         if ops:
             for w in dist.batch_isend_irecv(ops):
                 w.wait()
+
+
+class _AsyncWire:
+    """Point-to-point along the pipeline axis without waits on the critical path (NCCL ranks).
+
+    Two communicators: ``axis.group`` carries activations toward later stages, ``axis.group_back`` gradients toward
+    earlier ones.  On each of them this rank's operations are queued in the order of the data flow (receive input i,
+    send output i, receive input i + 1, ...), which is the order the neighbours use too, so no operation waits behind
+    one that depends on it."""
+
+    def __init__(self, axis):
+        self.axis = axis
+        self.prev = None if axis.first else axis.peer(-1)
+        self.next = None if axis.last else axis.peer(+1)
+        self.sent_bytes = 0
+        self.sends: list = []          # (work, tensor): kept until the end of the step
+        self.side = torch.cuda.Stream(axis.device)
+
+    def _post(self, fn, t, peer, group):
+        main = torch.cuda.current_stream(self.axis.device)
+        self.side.wait_stream(main)                  # the tensor (a send's payload, a receive's buffer) exists
+        with torch.cuda.stream(self.side):
+            w = fn(t, peer, group=group)
+        t.record_stream(self.side)
+        return w
+
+    def send_next(self, t):
+        if self.next is not None:
+            self.sent_bytes += t.numel() * t.element_size()
+            self.sends.append((self._post(dist.isend, t, self.next, self.axis.group), t))
+
+    def send_prev(self, t):
+        if self.prev is not None and t is not None:
+            self.sent_bytes += t.numel() * t.element_size()
+            self.sends.append((self._post(dist.isend, t, self.prev, self.axis.group_back), t))
+
+    def recv_prev(self, buf):
+        return None if self.prev is None else (self._post(dist.irecv, buf, self.prev, self.axis.group), buf)
+
+    def recv_next(self, buf):
+        return None if self.next is None else (self._post(dist.irecv, buf, self.next, self.axis.group_back), buf)
+
+    @staticmethod
+    def take(posted):
+        """The received tensor; the current stream waits for its arrival."""
+        if posted is None:
+            return None
+        w, buf = posted
+        w.wait()
+        return buf
+
+    def drain(self):
+        for w, _ in self.sends:
+            w.wait()
+        self.sends.clear()
+
+
+def _overlapped(axis) -> bool:
+    import os
+    return (os.environ.get("MESH_PP_OVERLAP", "1") != "0" and axis.device.type == "cuda"
+            and getattr(axis, "group_back", None) is not None and axis.world > 1)
 
 
 def run_1f1b(stage: Callable[[torch.Tensor], torch.Tensor], axis, microbatches: Sequence, *,
@@ -93,6 +160,37 @@ def run_1f1b(stage: Callable[[torch.Tensor], torch.Tensor], axis, microbatches: 
         x.grad = None
         return g
 
+    if _overlapped(axis):
+        # Same schedule, transfers off the critical path: see _AsyncWire.
+        aw = _AsyncWire(axis)
+        n_fwd = n_bwd = 0
+        x_posted = aw.recv_prev(new_act()) if (not axis.first and M > 0) else None
+        g_posted = aw.recv_next(new_act()) if (not axis.last and M > 0) else None
+
+        def do_forward():
+            nonlocal n_fwd, x_posted
+            y = forward(n_fwd, aw.take(x_posted))
+            n_fwd += 1
+            if not axis.last:
+                aw.send_next(y.detach())
+            x_posted = aw.recv_prev(new_act()) if (not axis.first and n_fwd < M) else None
+
+        def do_backward():
+            nonlocal n_bwd, g_posted
+            gx = backward(aw.take(g_posted))
+            n_bwd += 1
+            aw.send_prev(gx)
+            g_posted = aw.recv_next(new_act()) if (not axis.last and n_bwd < M) else None
+
+        for _ in range(warm):
+            do_forward()
+        for _ in range(rem):
+            do_forward()
+            do_backward()
+        for _ in range(warm):
+            do_backward()
+        aw.drain()
+        return losses, {"peak_alive": peak_alive, "sent_bytes": aw.sent_bytes, "microbatches": M, "overlapped": True}
     # ---- warm-up forwards
     for i in range(warm):
         x_in = None

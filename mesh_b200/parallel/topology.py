@@ -84,6 +84,7 @@ class AxisContext:
         self.name, self.ranks = name, ranks
         self.rank, self.world = ranks.index(rank), len(ranks)
         self.device, self.group = device, group
+        self.group_back = None       # pipeline axis: a second group for the traffic that flows toward earlier stages
         self._heap, self._comm = heap, None
 
     @property
@@ -143,10 +144,20 @@ class ParallelContext:
                         h = dist.new_group(g)
                         if g == mine:
                             group = h
+            back = None
+            if ax == "pp" and dims.size(ax) > 1 and world > 1 and dist.is_initialized():
+                # Activations flow toward later stages and gradients toward earlier ones.  Each direction gets a group
+                # (a communicator) of its own, so that its sends and receives are queued in the order in which the data
+                # comes into being and neither direction ever waits behind the other (parallel/pp.py).
+                for g in dims.groups(ax):
+                    h = dist.new_group(g)
+                    if g == mine:
+                        back = h
             heap = None
             if use_heap and dims.size(ax) > 1:
                 heap = ctx.heap if dims.size(ax) == world else ctx.heap.group(mine)
             self.axes[ax] = AxisContext(ax, rank, mine, self.device, group, heap)
+            self.axes[ax].group_back = back
 
     def __getattr__(self, name):
         axes = self.__dict__.get("axes", {})
