@@ -6,3 +6,4 @@ from .runtime import Program  # noqa: F401
 from .lower import lower  # noqa: F401,E402
 from .fuse import fuse_plan  # noqa: F401,E402
 from . import syncmon, check  # noqa: F401,E402
+from .bridge import Prepared, prepare, workspace  # noqa: F401,E402

@@ -66,13 +66,16 @@ class Function(torch.nn.Module):
 
 
 class _Runner:
+    """The runner of the older interface over :class:`~mesh_b200.compiler.bridge.Prepared`: ``copies`` input sets,
+    at most ``horizon`` executions in flight, executions started on the device's stream (one CUDA-graph launch each
+    where the program allows it) and their ends observed through events."""
+
     def __init__(self, scheduled, examples, copies: int, horizon: int):
-        self.scheduled, self.copies, self.horizon = scheduled, max(1, copies), max(0, horizon)
-        self._program = Program(scheduled)
-        self._inputs = [[e.clone() if torch.is_tensor(e) else e for e in examples] for _ in range(self.copies)]
-        self._started = 0
-        self._ended = 0
-        self.results: dict[int, Any] = {}
+        from .bridge import Prepared
+        self.scheduled, self.copies = scheduled, max(1, copies)
+        self._prepared = Prepared(scheduled, examples, copies=self.copies, horizon=max(1, horizon))
+        self.horizon = self._prepared.horizon
+        self._program = self._prepared.program
 
     # -- attributes of the reference's runner
     @property
@@ -83,35 +86,28 @@ class _Runner:
     def structure(self):
         return self.scheduled.structure
 
+    @property
+    def results(self) -> dict:
+        return self._prepared._results
+
+    @property
+    def _inputs(self):
+        return self._prepared._inputs
+
     def ended(self, execution: int | None = None) -> bool:
         """Whether ``execution`` (default: the latest started) has finished."""
-        b = self._started - 1 if execution is None else execution
-        return b < self._ended
+        return self._prepared.ended(execution)
 
     def inputs(self):
         """The writable input set of the next execution; waits until the execution that last used it is over."""
-        b = self._started
-        if b - self.horizon >= 0 and not self.ended(b - self.horizon):
-            self.synchronize()
-        return self._inputs[b % self.copies]
+        return self._prepared.inputs()
 
     def __call__(self, *args):
-        b = self._started
-        if args:
-            for dst, src in zip(self._inputs[b % self.copies], args):
-                if torch.is_tensor(dst):
-                    dst.copy_(src)
-        self._started += 1
-        out = self._program(*self._inputs[b % self.copies])
-        self.results[b] = out
-        self.results.pop(b - self.copies, None)
-        self._ended = self._started            # the executors of this package return when the execution is over
-        return out
+        b = self._prepared.start(*args)
+        return self._prepared._results[b]
 
     def synchronize(self) -> None:
-        if torch.cuda.is_available():
-            torch.cuda.synchronize()
-        self._ended = self._started
+        self._prepared.synchronize()
 
     def save(self, directory: str) -> None:
         archive.save(directory, self.scheduled)

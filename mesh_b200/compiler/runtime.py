@@ -659,6 +659,14 @@ class Program(Arguments):
         world = ThreadWorld(self.mesh.size)
         results: list = [None] * self.mesh.size
         errors: list = []
+        if self.mesh.size == 1:
+            # one processor: run in the calling thread (its current stream, and a CUDA-graph capture if one is open)
+            dev = self.devices[0] if self.devices else self.device
+            ex = Executor(self.plan, 0, ThreadCollectives(world, self.mesh, 0, dev if self.devices else None), dev)
+            ex.seed, ex.execution = self.seed, execution
+            results[0] = (ex, ex.run(bound, self._consts))
+            self.per_rank = results
+            return self._result(results[0][1], ex, bound, results)
 
         def work(r):
             try:

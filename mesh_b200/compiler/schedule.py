@@ -114,3 +114,115 @@ def stages(plan: Plan) -> list[list[Step]]:
         else:
             out[-1].append(st)
     return [s for s in out if s]
+
+
+# ----------------------------------------------------------------------------- declared transfers, lifetimes, carried edges
+@dataclass
+class Declared:
+    """One transfer of the plan with the steps that bound it in time (the reference's produced / read / consumed
+    events of a declared transfer, compiler/mesh_compiler/schedule.py:198-284): the value it sends exists after step
+    ``produced``, the transfer itself is step ``at``, its result is first read at ``read`` and last at ``consumed``
+    (``len(steps)`` = a program output).  ``slack`` = steps between the producer and the transfer plus steps between
+    the transfer and its first reader: what an overlapping executor can hide the transfer behind."""
+    channel: int
+    verb: str
+    axis: int
+    value: str
+    result: str
+    produced: int
+    at: int
+    read: int
+    consumed: int
+    nbytes: int
+    weight: float = 1.0
+
+    @property
+    def slack(self) -> int:
+        return max(0, self.at - self.produced - 1) + max(0, self.read - self.at - 1)
+
+
+def _first_last_use(plan: Plan) -> tuple[dict, dict]:
+    first: dict[str, int] = {}
+    last: dict[str, int] = {}
+    for i, st in enumerate(plan.steps):
+        refs: list[str] = []
+        _refs(st.args, refs)
+        _refs(st.kwargs, refs)
+        for r in refs:
+            first.setdefault(r, i)
+            last[r] = i
+    end = len(plan.steps)
+    for o in plan.outputs:
+        if isinstance(o, str):
+            first.setdefault(o, end)
+            last[o] = end
+    return first, last
+
+
+def declarations(plan: Plan, cost=unit_cost) -> list[Declared]:
+    """Every collective (plain or fused with its product) of the plan as a :class:`Declared` transfer."""
+    produced = {name: -1 for name in plan.inputs}
+    for i, st in enumerate(plan.steps):
+        produced[st.out] = i
+    first, last = _first_last_use(plan)
+    by_channel = {t.channel: t for t in plan.transfers}
+    out = []
+    for i, st in enumerate(plan.steps):
+        if not (st.op == "collective" or (st.op == "fused" and "channel" in st.meta)):
+            continue
+        m = st.meta
+        src = st.args[0].name if st.args and isinstance(st.args[0], Ref) else st.out
+        t = by_channel.get(m.get("channel"))
+        out.append(Declared(m.get("channel", -1), st.target, m.get("axis", 0), src, st.out, produced.get(src, -1), i,
+                            first.get(st.out, len(plan.steps)), last.get(st.out, len(plan.steps)),
+                            t.nbytes if t is not None else 0, float(cost(st))))
+    return out
+
+
+def lifetimes(plan: Plan, itemsize=None) -> list[tuple[str, int, int, int]]:
+    """``(value, first step, last step, bytes on one processor)`` for every value a step produces: what the
+    workspace planner colours (values whose lifetimes do not overlap share bytes).  Sizes are those of the largest
+    shard; ``itemsize(name)`` defaults to the plan's dtype table."""
+    import math
+
+    import torch
+    _, last = _first_last_use(plan)
+    out = []
+    for i, st in enumerate(plan.steps):
+        shape = plan.full_shapes.get(st.out)
+        if shape is None:
+            continue
+        n = int(math.prod(shape)) if len(shape) else 1
+        specs = plan.output_specs.get(st.out) if hasattr(plan, "output_specs") else None
+        for s in (specs or ()):
+            if getattr(s, "kind", "R") == "S" and s.counts and shape[s.dim]:
+                n = n // shape[s.dim] * max(s.counts)
+        dt = plan.dtypes.get(st.out, torch.float32)
+        size = itemsize(st.out) if itemsize is not None else torch.empty((), dtype=dt).element_size() if isinstance(dt, torch.dtype) else 4
+        out.append((st.out, i, max(i, last.get(st.out, i)), n * size))
+    return out
+
+
+def carried(plan: Plan, copies: int = 1) -> list[tuple[str, str, int]]:
+    """Loop-carried dependences between successive executions of a standing plan: ``(earlier, later, lag)`` means the
+    step ``later`` of execution ``t + lag`` must follow the step ``earlier`` of execution ``t``.  With ``copies`` sets
+    of buffers, execution ``t + copies`` rewrites what execution ``t`` used: its first write of every input waits for
+    the last read of that input ``copies`` executions earlier (write after read), and a collective's staging is
+    reused by the same collective one execution later (lag 1: the sequence of collectives is the same in every
+    execution, which is what lets their counters only grow).  The reference derives the same edges for its
+    ``copies`` buffers (compiler/mesh_compiler/schedule.py:112-140, rdma/mesh-collective.c:390)."""
+    first, last = _first_last_use(plan)
+    edges = []
+    for name in plan.inputs:
+        if name in last:
+            edges.append((f"read:{name}@{last[name]}", f"write:{name}", max(1, copies)))
+    for d in declarations(plan):
+        edges.append((f"{d.verb}:{d.result}@{d.at}", f"{d.verb}:{d.result}@{d.at}", 1))
+    return edges
+
+
+def horizon(plan: Plan, copies: int) -> int:
+    """How many executions may be in flight at once: with ``copies`` input sets, execution ``t + copies`` may not
+    start writing its inputs before execution ``t`` has read them, so at most ``copies`` executions overlap; a plan
+    with no input at all (constants only) is bounded by its collectives' lag-1 edges, which stream order satisfies."""
+    return max(1, copies)

@@ -1,0 +1,74 @@
+"""Declared transfers, lifetimes and workspace layout of a plan; a prepared program with several input sets."""
+import pytest
+import torch
+
+from mesh_b200.compiler import compile_module, prepare, workspace
+from mesh_b200.compiler import schedule as S
+from mesh_b200.models.llama import Block, megatron
+from mesh_b200.runtime.rendezvous import MeshStale
+
+
+def _compiled():
+    torch.manual_seed(0)
+    m = torch.nn.Sequential(Block(64, 4, 128)).eval()
+    x = torch.randn(2, 16, 64)
+    procs = {"a": (0, "cpu"), "b": (0, "cpu")}
+    return m, x, compile_module(m, (x,), procs, megatron(procs))
+
+
+def test_declared_transfers_carry_their_events_in_step_order():
+    _, _, sch = _compiled()
+    ds = S.declarations(sch.plan)
+    assert len(ds) == 2 and all(d.verb == "all_reduce" for d in ds)          # the two all-reduces of a Megatron block
+    for d in ds:
+        assert d.produced < d.at < d.read <= d.consumed
+        assert sch.plan.steps[d.at].out == d.result and d.nbytes > 0
+    assert S.horizon(sch.plan, 3) == 3
+    edges = S.carried(sch.plan, copies=2)
+    assert any(e[2] == 2 and e[1].startswith("write:") for e in edges)        # inputs: write after read, lag = copies
+    assert sum(1 for e in edges if e[2] == 1) == len(ds)                      # collectives: lag 1
+
+
+def test_workspace_shares_bytes_between_values_that_do_not_overlap():
+    _, _, sch = _compiled()
+    w = workspace(sch, copies=2)
+    assert 0 < w["bytes_per_copy"] < w["bytes_unshared"]
+    lt = {name: (a, b, n) for name, a, b, n in S.lifetimes(sch.plan)}
+    names = list(w["offsets"])
+    # no two values that are alive at the same step overlap in a copy; the copies are disjoint
+    for i, p in enumerate(names):
+        for q in names[i + 1:]:
+            (a0, a1, an), (b0, b1, bn) = lt[p], lt[q]
+            if a0 <= b1 and b0 <= a1 and an and bn:
+                po, qo = w["offsets"][p][0], w["offsets"][q][0]
+                assert po + an <= qo or qo + bn <= po, (p, q)
+    assert all(o[1] >= w["bytes_per_copy"] for o in w["offsets"].values())
+
+
+def test_prepared_program_rotates_input_sets_and_refuses_a_stale_view():
+    m, x, sch = _compiled()
+    pr = prepare(sch, (x,), copies=2)
+    outs = []
+    for step in range(4):
+        ins = pr.inputs()
+        ins[0].copy_(x * (step + 1))
+        b = pr.start()
+        assert b == step and pr.ended(b)
+        outs.append(pr.result(b))
+    for step, o in enumerate(outs):
+        assert torch.allclose(o, m(x * (step + 1)), atol=1e-5)
+    with pytest.raises(KeyError):
+        pr.result(0)                                         # held for `copies` executions only
+
+    class _Rdv:                                              # a membership view that moves
+        epoch = 0
+
+        def check_epoch(self, e):
+            if e != self.epoch:
+                raise MeshStale("view moved")
+    rdv = _Rdv()
+    pr2 = prepare(sch, (x,), copies=1, rdv=rdv)
+    pr2.start()
+    rdv.epoch = 1
+    with pytest.raises(MeshStale):
+        pr2.start()

@@ -243,7 +243,7 @@ def test_observed_step_times():
     assert len(rep["steps"]) == len(prog.plan.steps) and rep["total"] > 0
     assert any(k.startswith("blocks.1") for k in rep["by_module"]) and rep["by_kind"].get("collective", 0) > 0
     stages = stage_costs(rep, prog.plan)
-    n_coll = sum(1 for st in prog.plan.steps if st.op in ("collective", "fused"))
+    n_coll = sum(1 for st in prog.plan.steps if st.op == "collective" or (st.op == "fused" and "channel" in st.meta))
     assert len(stages) in (n_coll, n_coll + 1)
     assert abs(sum(s["compute_s"] + s["collective_s"] for s in stages) - rep["total"]) < 1e-9
     # observation is off again afterwards
