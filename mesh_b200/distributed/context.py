@@ -49,6 +49,28 @@ class MeshContext:
         return self._comm
 
     @property
+    def channels(self):
+        """Peer channels of this process (``runtime/channels.py``): created with the heap, one per peer, CONNECTED
+        once the peers' segments are mapped.  They carry the transfers that are left to the copy engines."""
+        if getattr(self, "_channels", None) is None:
+            from ..runtime.channels import PeerChannels
+            _ = self.heap                                   # peers are mapped first
+            self._channels = PeerChannels(self.rank, self.world, self.device.index if self.is_cuda else -1)
+            self._channels.connect_all()
+        return self._channels
+
+    def bulk_put(self, dst, peer: int, src: torch.Tensor) -> int:
+        """Store ``src`` into rank ``peer``'s copy of the symmetric buffer ``dst`` with the copy engines (no SM is
+        used), ordered after the work now on the current stream.  Returns a ticket for ``channels.done`` /
+        ``channels.wait_on_stream``.  For bulk moves (re-sharding, weight distribution at start-up); the collectives and
+        the fused layers move their data from inside kernels."""
+        n = src.numel() * src.element_size()
+        if n > dst.nbytes:
+            raise ValueError("bulk_put: source larger than the destination buffer")
+        stream = torch.cuda.current_stream(self.device).cuda_stream if self.is_cuda else 0
+        return self.channels.copy(peer, dst.ptr(peer), src.data_ptr(), n, stream)
+
+    @property
     def is_cuda(self) -> bool:
         return self.device.type == "cuda"
 
@@ -135,6 +157,9 @@ def shutdown() -> None:
     if _ctx.monitor is not None:
         _ctx.monitor.stop()
         _ctx.monitor = None
+    if getattr(_ctx, "_channels", None) is not None:
+        _ctx._channels.close()                              # bounded flush, proxy thread joined, channels CLOSED
+        _ctx._channels = None
     if _ctx._heap is not None:
         _ctx._heap.close()
     if _ctx.service:

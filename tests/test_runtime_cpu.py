@@ -128,3 +128,31 @@ def test_init_starts_the_runtime_service_and_shutdown_stops_it():
     import os
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_job_with_runtime, 2, f"t{os.getpid()}", timeout=120.0)
+
+
+def test_peer_channels_state_machine_queue_and_bounded_flush():
+    """Host-memory channels (no CUDA call): transitions in order only, copies served by the proxy thread, a channel
+    that is not connected takes no work, flush waits only for channels with outstanding work."""
+    import ctypes
+    import pytest
+    from mesh_b200.runtime.channels import ChannelError, PeerChannels
+    ch = PeerChannels(rank=0, world=3, device=-1)
+    assert [ch.state(p) for p in range(3)] == ["OPEN"] * 3
+    with pytest.raises(ChannelError):
+        ch.advance(1, "CONNECTED")                       # OPEN -> CONNECTED skips MAPPED
+    src = (ctypes.c_ubyte * 4096)(*([7] * 4096))
+    dst = (ctypes.c_ubyte * 4096)()
+    with pytest.raises(ChannelError):
+        ch.copy(1, ctypes.addressof(dst), ctypes.addressof(src), 4096)   # not connected yet
+    ch.connect_all()
+    assert ch.state(2) == "CONNECTED"
+    tickets = [ch.copy(1, ctypes.addressof(dst) + 1024 * i, ctypes.addressof(src) + 1024 * i, 1024) for i in range(4)]
+    assert tickets == sorted(tickets)
+    assert ch.flush(2000) == 0
+    assert all(ch.done(1, t) for t in tickets) and bytes(dst) == bytes(src)
+    assert ch.bytes(1) == 4096 and ch.bytes(2) == 0
+    ch.wait_on_stream(1, tickets[-1], 0, 100)            # issued long ago: returns at once
+    ch.advance(2, "HALTED")
+    with pytest.raises(ChannelError):
+        ch.copy(2, ctypes.addressof(dst), ctypes.addressof(src), 16)
+    assert ch.close(1000) == 0
