@@ -187,6 +187,7 @@ class Plan:
     transfers: list
     full_shapes: dict                # name -> global shape
     dtypes: dict
+    duplicated: int = 0              # invariant values recomputed where they are read instead of transferred
 
 
 @dataclasses.dataclass

@@ -297,8 +297,66 @@ class Propagator:
         self.moved[key] = out = self._reshard(name, want)
         return out
 
+    # ---- replicated cheap compute
+    DUPLICATE_LIMIT = 1 << 22       # elements: beyond this a transfer is cheaper than every reader recomputing
+
+    def _producers(self) -> dict:
+        return {st.out: st for st in self.steps}
+
+    def invariant(self, name: str, producers: dict | None = None, seen: set | None = None) -> bool:
+        """Does ``name`` depend on no input of the program at all (an index table, a mask, a constant folded from
+        literals)?  Such a value can be computed wherever it is read."""
+        producers = self._producers() if producers is None else producers
+        seen = set() if seen is None else seen
+        if name in seen:
+            return True
+        seen.add(name)
+        st = producers.get(name)
+        if st is None or st.op not in ("call", "const", "alias"):
+            return False                                    # a placeholder, or the result of a transfer
+        if st.op == "const":
+            return True                                     # every processor builds the whole module: its constants are everywhere
+        if "draw" in st.meta:
+            return False
+        refs: list = []
+        _walk_refs(st.args, refs)
+        _walk_refs(st.kwargs, refs)
+        return all(self.invariant(r, producers, seen) for r in refs)
+
+    def duplicate(self, name: str) -> str:
+        """Re-emit the steps that compute the invariant value ``name`` with replicated placement: every processor
+        computes its own copy and no transfer is needed (the reference duplicates invariant nodes onto every reader,
+        compiler/mesh_compiler/placement.py:884-903: duplicated cheap compute is free, a crossing is not)."""
+        producers = self._producers()
+        done: dict[str, str] = {}
+
+        def emit(n: str) -> str:
+            if n in done:
+                return done[n]
+            st = producers[n]
+            if all(s.kind == "R" for s in self.spec.get(n, ())) and st.op != "alias":
+                done[n] = n                                 # already everywhere
+                return n
+            args = _map_refs(st.args, emit)
+            kwargs = _map_refs(st.kwargs, emit)
+            out = self.fresh(n)
+            self.steps.append(Step(st.op, out, st.target, args, kwargs, {k: v for k, v in st.meta.items() if k != "out_specs"}))
+            self.shape[out] = self.shape[n]
+            if n in self.dtype:
+                self.dtype[out] = self.dtype[n]
+            self.spec[out] = self.all_r()
+            done[n] = out
+            return out
+        out = emit(name)
+        self.duplicated = getattr(self, "duplicated", 0) + 1
+        return out
+
     def _reshard(self, name: str, want: tuple) -> str:
         have = self.spec[name]
+        if any(h.kind == "O" and w != h for h, w in zip(have, want)) and math.prod(self.shape.get(name, (1,)) or (1,)) <= self.DUPLICATE_LIMIT \
+                and self.invariant(name):
+            # a value that depends on no input, held by one processor and wanted elsewhere: recompute, do not transfer
+            return self.reshard(self.duplicate(name), want)
         cur = name
         for ax in range(self.na):
             h, w = have[ax], want[ax]
@@ -1286,6 +1344,27 @@ def normalise(stated, node, mesh: Mesh, names_to_axis) -> tuple | None:
     return tuple(specs)
 
 
+def _walk_refs(obj, out: list) -> None:
+    if isinstance(obj, Ref):
+        out.append(obj.name)
+    elif isinstance(obj, (list, tuple)):
+        for o in obj:
+            _walk_refs(o, out)
+    elif isinstance(obj, dict):
+        for o in obj.values():
+            _walk_refs(o, out)
+
+
+def _map_refs(obj, fn):
+    if isinstance(obj, Ref):
+        return Ref(fn(obj.name))
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_map_refs(o, fn) for o in obj)
+    if isinstance(obj, dict):
+        return {k: _map_refs(v, fn) for k, v in obj.items()}
+    return obj
+
+
 def place(exported, processors: dict, placement: Callable, mesh_shape: tuple | None = None) -> Plan:
     """Propagate the stated placements through the exported graph and insert collectives."""
     names = tuple(processors)
@@ -1327,5 +1406,6 @@ def place(exported, processors: dict, placement: Callable, mesh_shape: tuple | N
     order = [n.name for n in gm.graph.nodes if n.op == "placeholder"]
     prop = Propagator(gm, mesh, stated)
     plan = prop.run(order)
+    plan.duplicated = getattr(prop, "duplicated", 0)
     # stated placements on intermediate nodes are constraints: applied by resharding right after the node
     return plan

@@ -100,6 +100,7 @@ def schedule(plan: Plan, cost=unit_cost) -> tuple[Signature, dict]:
         "local_slices": sum(1 for s in plan.steps if s.op == "slice"),
         "levels": level,
         "uncovered": uncovered, "unwaited": unwaited, "redundant": redundant,
+        "duplicated": getattr(plan, "duplicated", 0),
         "signature": sig.digest,
     }
     return sig, structure

@@ -574,3 +574,33 @@ def test_gradient_all_reduces_go_out_as_one_bucket(monkeypatch):
     _check(res, loss, grads)
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_bucket_rank, 2, init_pg="gloo")
+
+
+def test_invariant_values_are_recomputed_where_they_are_read():
+    """A table that depends on no input, stated on one processor and read on another, is computed on both: no
+    transfer carries it (duplicated cheap compute is free, a crossing is not)."""
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = torch.nn.Linear(16, 16), torch.nn.Linear(16, 16)
+
+        def forward(self, x):
+            table = torch.sin(torch.arange(16, dtype=torch.float32) / 16.0) * 2.0
+            return self.b(self.a(x) + table) * table
+    torch.manual_seed(0)
+    m = M().eval()
+    x = torch.randn(4, 16)
+    procs = {"p0": (0, "cpu"), "p1": (0, "cpu")}
+
+    def placement(node):
+        if node.name in ("arange", "div", "sin", "mul", "addmm", "add"):
+            return "p0"
+        if node.name in ("addmm_1", "mul_1"):
+            return "p1"
+        return None
+    sch = compile_module(m, (x,), procs, placement)
+    assert sch.structure["duplicated"] == 1
+    moved = {t.value for t in sch.plan.transfers}
+    assert not any(v.startswith(("mul", "sin", "arange", "div")) and not v.startswith("mul_1") for v in moved), moved
+    out = Program(sch, threads=True)(x)
+    assert torch.allclose(out, m(x), atol=1e-6)
