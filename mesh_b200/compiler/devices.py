@@ -18,9 +18,25 @@ import torch
 from .ir import Plan
 
 
-def device_of(description, available_only: bool = False) -> torch.device:
-    """The torch device of one processor description ``(machine, device)`` (or a bare device)."""
+ENGINES = ("host",)       # device names that are engines of this package rather than torch devices
+
+
+def is_engine(description) -> bool:
+    """Is the processor an engine that is not a torch device?  ``"host"``: the host engine
+    (``mesh_b200.runtime.host_engine``), the counterpart of the reference's processors that are neither CPU nor GPU
+    code paths of torch (its ``'ane'`` device, compiler/mesh_compiler/devices.py:50-69, lower_coreml.py:101-321): the
+    products, norms and sums placed there run as batches on the engine's own threads over host memory, and the
+    engine reports which device ran each of them."""
     name = description[1] if isinstance(description, (tuple, list)) else description
+    return str(name) in ENGINES
+
+
+def device_of(description, available_only: bool = False) -> torch.device:
+    """The torch device of one processor description ``(machine, device)`` (or a bare device); an engine's values
+    live in host memory."""
+    name = description[1] if isinstance(description, (tuple, list)) else description
+    if str(name) in ENGINES:
+        return torch.device("cpu")
     dev = torch.device(name)
     if dev.type == "cuda" and available_only and not torch.cuda.is_available():
         return torch.device("cpu")

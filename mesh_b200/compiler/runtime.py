@@ -124,6 +124,8 @@ class Executor:
         self.seed, self.execution = int(os.environ.get("MESH_SEED", "0")), 0        # random draws: see draw()
         from .kernels import Counter
         self.kernels = Counter()     # products / attention / norms run on this package's kernels vs on PyTorch operators
+        self.engine = None           # a HostEngine when this processor is one (compiler/devices.py::is_engine)
+        self.engine_report: list = []
 
     # ---- shards of full tensors
     def shard(self, full: torch.Tensor, specs: tuple) -> torch.Tensor | None:
@@ -449,10 +451,38 @@ class Executor:
             return self.collective(Step("collective", st.out, "reduce_scatter", (), {}, m), partial)
         raise NotImplementedError(st.target)
 
+    def _on_engine(self, st: Step, tgt, args):
+        """A product or a sum placed on an engine processor runs as a batch of the host engine; ``None``: not an
+        operation the engine has (it then runs on the PyTorch operator, on the host)."""
+        ok = lambda t: isinstance(t, torch.Tensor) and not t.is_cuda and t.dtype in (torch.float32, torch.bfloat16) and t.dim() == 2
+        ops = None
+        if tgt is aten.mm.default and ok(args[0]) and ok(args[1]) and args[0].dtype == args[1].dtype:
+            a = args[0] if args[0].stride(1) == 1 else args[0].contiguous()
+            b = args[1].t() if args[1].t().stride(1) == 1 else args[1].t().contiguous()      # the engine takes B as [n, k]
+            out = torch.empty((a.shape[0], b.shape[0]), dtype=a.dtype)
+            ops = [("gemm_nt", a, b, out)]
+        elif tgt is aten.add.Tensor and len(args) == 2 and ok(args[0]) and ok(args[1]) and args[0].shape == args[1].shape \
+                and args[0].dtype == args[1].dtype:
+            a, b = (t if t.stride(1) == 1 else t.contiguous() for t in args)
+            out = torch.empty_like(a, memory_format=torch.contiguous_format)
+            ops = [("add", a, b, out)]
+        if ops is None:
+            return None
+        rep = self.engine.wait(self.engine.submit(ops))
+        self.engine_report += [{"step": st.out, **r} for r in rep]
+        return ops[0][-1]
+
     def rms_norm(self, st: Step, x, w):
         """One step for the operator chain of an RMS norm (``fuse.fuse_norms``)."""
         if x is None or (len(st.args) > 1 and w is None):
             return None
+        if self.engine is not None and w is not None and not x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) \
+                and w.dtype == x.dtype:
+            x2 = x.reshape(-1, x.shape[-1]).contiguous()
+            out = torch.empty_like(x2)
+            rep = self.engine.wait(self.engine.submit([("rmsnorm", x2, w.contiguous(), out, float(st.meta["eps"]))]))
+            self.engine_report += [{"step": st.out, **r} for r in rep]
+            return out.view(x.shape)
         from . import kernels
         if kernels.enabled():
             y = kernels.rms_norm(x, w, st.meta["eps"])
@@ -558,6 +588,10 @@ class Executor:
             return e * ok.unsqueeze(-1).to(e.dtype)
         if tgt in (aten.view.default, aten._unsafe_view.default):
             return args[0].reshape(args[1])        # shards and gathered values are not always dense
+        if self.engine is not None:
+            y = self._on_engine(st, tgt, args)
+            if y is not None:
+                return y
         # products and whole attention run on this package's kernels where the operands allow it (compiler/kernels.py)
         from . import kernels
         if kernels.enabled():
@@ -632,13 +666,18 @@ class Program(Arguments):
         elif device == "processors":
             # every processor on the device its description names (the reference's on_devices stage); values that
             # cross are copied where they arrive
-            from .devices import on_devices
+            from .devices import is_engine, on_devices
             self.devices = on_devices(scheduled.processors)
+            if any(is_engine(d) for d in scheduled.processors.values()):
+                from ..runtime.host_engine import HostEngine
+                shared = HostEngine()
+                self.engines = [shared if is_engine(d) else None for d in scheduled.processors.values()]
             self.device = self.devices[0 if entry is None else self.mesh.names.index(entry)]
         else:
             self.device = torch.device(device or "cpu")
         self.entry = entry
         self.last_structure = None
+        self.engines = getattr(self, "engines", None)
 
     def _consts(self, target):
         gm = self.exported.graph_module
@@ -673,6 +712,7 @@ class Program(Arguments):
                 dev = self.devices[r] if self.devices else self.device
                 ex = Executor(self.plan, r, ThreadCollectives(world, self.mesh, r, dev if self.devices else None), dev)
                 ex.seed, ex.execution = self.seed, execution
+                ex.engine = self.engines[r] if self.engines else None
                 results[r] = (ex, ex.run(bound, self._consts))
             except BaseException as e:  # surfaced to the caller below
                 errors.append(e)
@@ -688,6 +728,14 @@ class Program(Arguments):
         owner = 0 if self.entry is None else self.mesh.names.index(self.entry)
         ex, flat = results[owner]
         return self._result(flat, ex, bound, results)
+
+    def engine_report(self) -> list:
+        """After a call: ``[{processor, step, op, device, seconds}]`` for every operation an engine processor ran."""
+        out = []
+        for r, res in enumerate(getattr(self, "per_rank", None) or []):
+            if res is not None:
+                out += [{"processor": self.mesh.names[r], **rec} for rec in res[0].engine_report]
+        return out
 
     def structure(self) -> dict:
         """What the plan was lowered to: fused (collective, product) pairs and norms found, and, after a call, how many

@@ -44,3 +44,38 @@ def test_gpu_and_host_processors_in_one_program():
     assert [d.type for d in prog.devices] == ["cuda", "cpu"]
     out = prog(x)
     assert out.device.type == "cuda" and torch.allclose(out.cpu(), m(x), atol=1e-4)
+
+
+def test_a_processor_that_is_an_engine_runs_its_products_on_the_host_engine():
+    """Two processors: a torch device and the host engine.  The layers placed on the engine run as batches of the
+    engine (products, the RMS norm, the residual sum), which reports the device that ran each; the result is the
+    eager one."""
+    import torch
+    from mesh_b200.compiler import Program, compile_module
+    from mesh_b200.models.llama import RMSNorm
+
+    class Two(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = torch.nn.Linear(32, 64, bias=False), torch.nn.Linear(64, 32, bias=False)
+            self.n = RMSNorm(32)
+
+        def forward(self, x):
+            h = torch.tanh(self.a(x))
+            return x + self.b(h) + self.n(x)
+    torch.manual_seed(0)
+    m = Two().eval()
+    x = torch.randn(8, 32)
+    procs = {"dev": (0, "cpu"), "eng": (0, "host")}
+
+    def placement(node):
+        if node.op == "placeholder":
+            return None
+        return "dev" if node.name in ("mm", "tanh", "permute") else "eng"
+    sch = compile_module(m, (x,), procs, placement)
+    prog = Program(sch, device="processors", entry="eng")
+    out = prog(x)
+    assert torch.allclose(out, m(x), atol=1e-5)
+    rep = prog.engine_report()
+    kinds = {r["op"] for r in rep}
+    assert "gemm_nt" in kinds and all(r["processor"] == "eng" and r["device"].startswith("cpu") for r in rep), rep
