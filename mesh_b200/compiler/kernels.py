@@ -56,11 +56,14 @@ def mm(a: torch.Tensor, b: torch.Tensor):
     return gemm(a, b, a_mn=a_mn, b_mn=True)
 
 
-def attention(q, k, v, *, causal: bool, scale=None, row_positions=None, dropout_p: float = 0.0, mask=None):
+def attention(q, k, v, *, causal: bool, scale=None, row_positions=None, dropout_p: float = 0.0, mask=None, dropout=None):
     """Whole attention, ``q [B, H, Tq, hd]``, ``k, v [B, Hkv, Tk, hd]`` as the captured operator has them, on the flash
     kernel; ``row_positions``: ``(first, stride)`` of the query rows in the whole sequence when they are a shard.
-    ``None`` when the kernel does not take the case (a mask tensor, dropout, a head size it has no tiles for)."""
-    if mask is not None or dropout_p or not _bf16_cuda(q, k, v) or q.dim() != 4:
+    ``dropout``: the kernel's dropout description (``ops/attention.py::_set_dropout``) when the operator drops
+    probabilities; its mask is a function of logical coordinates, so a cut of the heads or of the sequence changes
+    nothing.  ``None`` when the kernel does not take the case (a mask tensor, dropout without a description, a head
+    size it has no tiles for)."""
+    if mask is not None or (dropout_p and not dropout) or not _bf16_cuda(q, k, v) or q.dim() != 4:
         return None
     B, H, Tq, hd = q.shape
     Hkv, Tk = k.shape[1], k.shape[2]
@@ -71,7 +74,8 @@ def attention(q, k, v, *, causal: bool, scale=None, row_positions=None, dropout_
     off, stride = (0, 1) if row_positions is None else row_positions
     if causal and row_positions is None and Tq != Tk:
         return None
-    out = flash_attention(qt, kt, vt, causal=causal, scale=scale, q_off=off, q_stride=stride)
+    out = flash_attention(qt, kt, vt, causal=causal, scale=scale, q_off=off, q_stride=stride,
+                          dropout=dropout if dropout_p else None)
     return out.transpose(1, 2)
 
 

@@ -451,6 +451,25 @@ class Executor:
             return self.collective(Step("collective", st.out, "reduce_scatter", (), {}, m), partial)
         raise NotImplementedError(st.target)
 
+    def _attention_dropout(self, st: Step, opt: dict, q):
+        """The kernel's dropout description for an attention step that drops probabilities, or ``None``: the draw is
+        keyed by this program's seed and execution, the step's position in the plan (its site) and the logical head
+        (heads cut over processors are offset); a batch cut is left to the PyTorch operator."""
+        p = opt.get("dropout_p", 0.0) or 0.0
+        if not p:
+            return None
+        m = st.meta
+        head_off, heads_total = 0, q.shape[1]
+        for ax, s in enumerate(m.get("out_specs", ())):
+            if getattr(s, "kind", "R") == "S":
+                if s.dim == 0:
+                    return None
+                if s.dim == 1:
+                    head_off, heads_total = sum(s.counts[:self.coords[ax]]), m["full_shape"][1]
+        site = m.get("site", self.plan.steps.index(st) if st in self.plan.steps else 0)
+        return {"p": float(p), "seed": self.seed, "execution": self.execution, "site": int(site) & 0xFFFFFFFF,
+                "head_off": head_off, "heads_total": heads_total}
+
     def _on_engine(self, st: Step, tgt, args):
         """A product or a sum placed on an engine processor runs as a batch of the host engine; ``None``: not an
         operation the engine has (it then runs on the PyTorch operator, on the host)."""
@@ -538,10 +557,13 @@ class Executor:
             q, k = args[0], args[1]
             rows = local_indices(spec, self.coords[ax], m["full_shape"][2])
             from . import kernels
-            if kernels.enabled() and isinstance(rows, slice) and len(args) == 3:
-                y = kernels.attention(q, k, args[2], causal=True, scale=kwargs.get("scale"),
+            if kernels.enabled() and isinstance(rows, slice):
+                opt = dict(zip(("attn_mask", "dropout_p", "is_causal"), args[3:6]))
+                opt.update(kwargs)
+                y = kernels.attention(q, k, args[2], causal=True, scale=opt.get("scale"),
                                       row_positions=(rows.start or 0, rows.step or 1),
-                                      dropout_p=kwargs.get("dropout_p", 0.0), mask=kwargs.get("attn_mask"))
+                                      dropout_p=opt.get("dropout_p", 0.0) or 0.0, mask=opt.get("attn_mask"),
+                                      dropout=self._attention_dropout(st, opt, q))
                 if y is not None:
                     self.kernels.own += 1
                     return y
@@ -598,10 +620,13 @@ class Executor:
             y = None
             if tgt is aten.mm.default:
                 y = kernels.mm(args[0], args[1])
-            elif tgt is aten.scaled_dot_product_attention.default and len(args) == 3:
-                y = kernels.attention(args[0], args[1], args[2], causal=bool(kwargs.get("is_causal", False)),
-                                      scale=kwargs.get("scale"), dropout_p=kwargs.get("dropout_p", 0.0),
-                                      mask=kwargs.get("attn_mask"))
+            elif tgt is aten.scaled_dot_product_attention.default:
+                # (query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None, enable_gqa=False)
+                opt = dict(zip(("attn_mask", "dropout_p", "is_causal"), args[3:6]))
+                opt.update(kwargs)
+                y = kernels.attention(args[0], args[1], args[2], causal=bool(opt.get("is_causal", False)),
+                                      scale=opt.get("scale"), dropout_p=opt.get("dropout_p", 0.0) or 0.0,
+                                      mask=opt.get("attn_mask"), dropout=self._attention_dropout(st, opt, args[0]))
             if y is not None:
                 self.kernels.own += 1
                 return y
@@ -679,17 +704,31 @@ class Program(Arguments):
         self.last_structure = None
         self.engines = getattr(self, "engines", None)
 
+    def _on_device(self, key, t: torch.Tensor) -> torch.Tensor:
+        """``t`` on this program's device.  A parameter or constant that lives elsewhere is copied once and again
+        only after it has been written (live parameters are re-read on every call, but not re-copied when unchanged)."""
+        if t.device == self.device:
+            return t
+        cache = self.__dict__.setdefault("_device_copies", {})
+        stamp = (t._version, t.data_ptr(), tuple(t.shape))
+        hit = cache.get(key)
+        if hit is None or hit[0] != stamp:
+            cache[key] = hit = (stamp, t.detach().to(self.device))
+        return hit[1]
+
     def _consts(self, target):
         gm = self.exported.graph_module
         obj = gm
         for part in str(target).split("."):
             obj = getattr(obj, part)
-        return obj.to(self.device) if isinstance(obj, torch.Tensor) and not self.devices else obj
+        return self._on_device(("const", str(target)), obj) if isinstance(obj, torch.Tensor) and not self.devices else obj
 
     def __call__(self, *args, **kwargs):
         bound = self.prepare(args, kwargs)
         if not self.devices:
-            bound = {k: (v.to(self.device) if isinstance(v, torch.Tensor) and v.device != self.device else v) for k, v in bound.items()}
+            state = self.exported.state
+            bound = {k: ((self._on_device(("state", k), v) if k in state else v.to(self.device))
+                         if isinstance(v, torch.Tensor) and v.device != self.device else v) for k, v in bound.items()}
         execution, self.execution = self.execution, self.execution + 1
         if not self.threads:
             self.exec.seed, self.exec.execution = self.seed, execution

@@ -23,6 +23,7 @@ typedef struct MeshDecodeLinear {
   const uint32_t* step_ptr; uint32_t calls_per_step, call_index;   // all-reduce sequence = *step_ptr * calls + index + 1
   const void* residual; long long ldr;
   void* status;
+  const void* next_w; unsigned long long next_bytes;   // optional: bytes to prefetch into L2 for the layer that follows
 } MeshDecodeLinear;
 
 int mesh_decode_linear(const MeshDecodeLinear* d, void* stream);

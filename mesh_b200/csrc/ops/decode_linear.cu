@@ -53,6 +53,7 @@ struct LinArgs {
   const __nv_bfloat16* residual; long long ldr;       // [B, N]
   Status* status;
   int l2_prefetch;
+  const uint8_t* next_w; unsigned long long next_bytes;   // weights of the linear layer that follows in the stream
   int xpad;                                           // bytes of padding per x row in shared memory (bank spread)
 };
 
@@ -329,6 +330,20 @@ __global__ void __launch_bounds__(THREADS) decode_linear_kernel(const LinArgs a)
   const uint8_t* xbase = xs + g8 * xstride + (k_lo + lane_k<W4>(t4)) * 2;
   float c[4] = {0.f, 0.f, 0.f, 0.f};
 
+  // The layer that follows streams weights that depend on nothing computed here: ask for them to be brought into L2
+  // now, behind this kernel's own loads, so that HBM keeps streaming through this kernel's reduction and epilogue,
+  // the kernel boundary and the next kernel's prologue.  Every CTA requests its slice in 16 KiB pieces.
+  if (a.next_w != nullptr) {
+    constexpr unsigned long long PIECE = 16384;
+    const unsigned long long pieces = (a.next_bytes + PIECE - 1) / PIECE;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * THREADS + threadIdx.x; i < pieces;
+         i += (unsigned long long)gridDim.x * THREADS) {
+      const unsigned long long off = i * PIECE;
+      const uint32_t n = (uint32_t)((a.next_bytes - off < PIECE ? a.next_bytes - off : PIECE) & ~15ull);
+      if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.next_w + off), "r"(n) : "memory");
+    }
+  }
+
   // Two register sets alternate: while one chunk feeds the tensor cores the next one is in flight,
   // across group boundaries too, so the stream of weight loads never drains.
   for (int step = 0; step < steps; ++step) {
@@ -473,6 +488,8 @@ extern "C" int mesh_decode_linear(const MeshDecodeLinear* d, void* stream) {
   a.step_ptr = d->step_ptr; a.calls_per_step = d->calls_per_step; a.call_index = d->call_index;
   a.residual = (const __nv_bfloat16*)d->residual; a.ldr = d->ldr;
   a.status = (Status*)d->status;
+  a.next_w = (const uint8_t*)d->next_w; a.next_bytes = d->next_bytes;
+  if (((uintptr_t)a.next_w & 15) != 0) { a.next_w = nullptr; a.next_bytes = 0; }
   if (d->mode == MESH_DEC_QKV) {
     if (d->head_dim % 16 || (d->q_heads + 2 * d->kv_heads) * d->head_dim != d->N)
       return set_error(-2, "decode_linear: qkv rows must equal (q_heads + 2 kv_heads) * head_dim");
@@ -507,16 +524,17 @@ extern "C" int mesh_decode_linear(const MeshDecodeLinear* d, void* stream) {
     configured[slot] = true;
   }
   int grid = a.n_groups;
-  // CTAs per SM.  One (the default) leaves room on every SM for a CTA of the NEXT kernel of the stream, which starts
-  // as a programmatic dependent, asks for its weights (L2 prefetch, first chunk) and only then waits for this kernel:
-  // the weight stream does not stop at kernel boundaries.  MESH_DECODE_CTAS_PER_SM=2 gives the older behaviour (a
-  // kernel fills the SMs by itself and the next one starts when it ends).
+  // CTAs per SM: two fill the machine with loads in flight (measured: one CTA per SM, which would leave room for a
+  // CTA of the next kernel to start early, loses a fifth of the decode rate).  MESH_DECODE_CTAS_PER_SM=1 and
+  // MESH_DECODE_L2_PREFETCH=1 (each CTA asks for its own rows before waiting for the previous kernel) remain as
+  // switches for experiments; what keeps HBM busy across kernel boundaries is the prefetch of the NEXT layer's
+  // weights (`next_w`).
   static int per_sm = -1, prefetch = -1;
   if (per_sm < 0) {
     const char* e = getenv("MESH_DECODE_CTAS_PER_SM");
-    per_sm = (e && e[0] == '2') ? 2 : 1;
+    per_sm = (e && e[0] == '1') ? 1 : 2;
     const char* f = getenv("MESH_DECODE_L2_PREFETCH");
-    prefetch = (f && f[0] == '0') ? 0 : 1;
+    prefetch = (f && f[0] == '1') ? 1 : 0;
   }
   a.l2_prefetch = prefetch;       // rows are multiples of 16 bytes in every format (K % 256 == 0)
   const int cap = sm_count() * (smem > 100 * 1024 ? 1 : per_sm);

@@ -24,6 +24,7 @@
 #include <math_constants.h>
 #include <cstring>
 #include "ops_api.h"
+#include "../device/philox.cuh"
 #include "../device/ptx.cuh"
 #include "../runtime/host_common.h"
 
@@ -44,6 +45,8 @@ struct Params {
   int q_off, q_stride, k_off, k_stride;
   float scale_log2;                   // softmax scale * log2(e)
   Status* status;
+  DropoutKey drop;
+  int head_off, heads_total;                    // drop.p == 0: no dropout
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -267,13 +270,20 @@ __global__ void __launch_bounds__(THREADS, 1) flash_fwd_kernel(const __grid_cons
       // product, which the tensor core is still running.
       float sum = 0.f;
       uint32_t w[NCH][16];
+      DropoutRow dr;
+      if (p.drop.p > 0.f) dr.begin((uint32_t)(b * p.heads_total + p.head_off + h), (uint32_t)qpos);
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), p.scale_log2, neg_ms));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), p.scale_log2, neg_ms));
-          sum += p0 + p1;
+          float p0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), p.scale_log2, neg_ms));
+          float p1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), p.scale_log2, neg_ms));
+          sum += p0 + p1;                         // the row sum is that of the undropped probabilities
+          if (p.drop.p > 0.f) {
+            const uint32_t kpos = (uint32_t)(p.k_off + (kbase + half * HALF + c * 32 + i) * p.k_stride);
+            p0 = dr.keep(p.drop, kpos) ? p0 * p.drop.inv_keep : 0.f;
+            p1 = dr.keep(p.drop, kpos + (uint32_t)p.k_stride) ? p1 * p.drop.inv_keep : 0.f;
+          }
           __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
           w[c][i / 2] = *reinterpret_cast<uint32_t*>(&hb);
         }
@@ -396,6 +406,12 @@ static int launch(const MeshFlashArgs* a, cudaStream_t stream) {
   p.k_off = a->k_off; p.k_stride = a->k_stride > 0 ? a->k_stride : 1;
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.status = (Status*)a->status;
+  p.drop.p = a->dropout_p > 0.f ? a->dropout_p : 0.f;
+  p.drop.inv_keep = p.drop.p > 0.f ? 1.f / (1.f - p.drop.p) : 1.f;
+  p.drop.k0 = (uint32_t)(a->seed & 0xffffffffull) ^ (a->execution * 0x9E3779B9u);
+  p.drop.k1 = (uint32_t)(a->seed >> 32);
+  p.drop.site = a->site;
+  p.head_off = a->head_off; p.heads_total = a->heads_total > 0 ? a->heads_total : a->H;
   static bool configured = false;
   if (!configured) {
     MESH_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
@@ -416,6 +432,7 @@ extern "C" int mesh_flash_attention_fwd(const MeshFlashArgs* a, void* stream) {
   if (a->ldq % 8 || a->ldk % 8 || a->ldv % 8 || a->ldo % 8 || a->q_col0 % 8 || a->k_col0 % 8 || a->v_col0 % 8)
     return set_error(-2, "flash_attention: leading dimensions and head offsets must be multiples of 8 elements");
   if (a->Tq % 1 || a->B < 1) return set_error(-2, "flash_attention: empty problem");
+  if (!(a->dropout_p >= 0.f && a->dropout_p < 1.f)) return set_error(-2, "flash_attention: dropout_p must be in [0, 1)");
   switch (a->head_dim) {
     case 64: return fa::launch<64>(a, (cudaStream_t)stream);
     case 128: return fa::launch<128>(a, (cudaStream_t)stream);

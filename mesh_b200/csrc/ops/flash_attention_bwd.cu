@@ -18,6 +18,7 @@
 #include <math_constants.h>
 #include <cstring>
 #include "ops_api.h"
+#include "../device/philox.cuh"
 #include "../device/ptx.cuh"
 #include "../runtime/host_common.h"
 
@@ -40,6 +41,8 @@ struct Params {
   int causal, window, q_off, q_stride, k_off, k_stride;
   float scale, scale_log2;
   Status* status;
+  DropoutKey drop;
+  int head_off, heads_total;
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -214,6 +217,8 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
       tc_fence_after();
       // P and dS may be overwritten: SDP_FULL of this iteration was issued after the MMA warp had waited for the
       // previous iteration's second group of products, which read them
+      DropoutRow dr;
+      if (p.drop.p > 0.f) dr.begin((uint32_t)(b * p.heads_total + p.head_off + h), (uint32_t)qpos);
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t rs[32], rp[32];
@@ -233,8 +238,14 @@ __global__ void __launch_bounds__(THREADS, 1) flash_bwd_kernel(const __grid_cons
               const bool vis = kj < p.Tk && (!p.causal || kpos <= qpos) && (p.window <= 0 || kpos > qpos - p.window);
               pr = vis ? pr : 0.f;
             }
-            pv[u] = pr;
-            dv[u] = pr * (__uint_as_float(rp[e + u]) - dl) * p.scale;
+            // dropout: dV sees the dropped, rescaled probabilities; dP comes back through the same mask
+            float m = 1.f;
+            if (p.drop.p > 0.f) {
+              const uint32_t kpos = (uint32_t)(p.k_off + (k0 + half * 64 + c * 32 + e + u) * p.k_stride);
+              m = dr.keep(p.drop, kpos) ? p.drop.inv_keep : 0.f;
+            }
+            pv[u] = pr * m;
+            dv[u] = pr * (__uint_as_float(rp[e + u]) * m - dl) * p.scale;
           }
           __nv_bfloat162 hp = __floats2bfloat162_rn(pv[0], pv[1]);
           __nv_bfloat162 hd2 = __floats2bfloat162_rn(dv[0], dv[1]);
@@ -350,6 +361,12 @@ static int launch(const MeshFlashBwdArgs* a, cudaStream_t stream) {
   p.q_off = f.q_off; p.q_stride = f.q_stride > 0 ? f.q_stride : 1; p.k_off = f.k_off; p.k_stride = f.k_stride > 0 ? f.k_stride : 1;
   p.scale = f.scale; p.scale_log2 = f.scale * 1.4426950408889634f;
   p.status = (Status*)f.status;
+  p.drop.p = f.dropout_p > 0.f ? f.dropout_p : 0.f;
+  p.drop.inv_keep = p.drop.p > 0.f ? 1.f / (1.f - p.drop.p) : 1.f;
+  p.drop.k0 = (uint32_t)(f.seed & 0xffffffffull) ^ (f.execution * 0x9E3779B9u);
+  p.drop.k1 = (uint32_t)(f.seed >> 32);
+  p.drop.site = f.site;
+  p.head_off = f.head_off; p.heads_total = f.heads_total > 0 ? f.heads_total : f.H;
   static bool configured = false;
   if (!configured) {
     MESH_CUDA_OK(cudaFuncSetAttribute(flash_bwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));

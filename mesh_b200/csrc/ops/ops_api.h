@@ -46,6 +46,12 @@ typedef struct MeshFlashArgs {
   int q_off, q_stride, k_off, k_stride;
   float scale;
   void* status;
+  // dropout of the attention probabilities (0: none), drawn as csrc/device/philox.cuh describes: a function of the
+  // logical coordinates, so every shard of a sequence drops what one device would
+  float dropout_p;
+  unsigned long long seed;
+  unsigned int site, execution;
+  int head_off, heads_total;     // logical head of local head h is head_off + h of heads_total (0: H); head-sharded layers
 } MeshFlashArgs;
 int mesh_flash_attention_fwd(const MeshFlashArgs* a, void* stream);
 

@@ -146,24 +146,39 @@ class E2BDecoder:
         c = self.cfg
         x, x1 = self.x
         torch.index_select(self.emb, 0, self.tok, out=x)
+        import os
+        ahead = os.environ.get("MESH_DECODE_PREFETCH_NEXT", "1") != "0"
+        head = self.lm_q if self.quant in ("w4", "w8") else self.lm_head
+
+        def nxt(l, name):
+            """Weights of the linear layer that follows (its codes when quantised): prefetched into L2 by this one."""
+            if not ahead:
+                return None
+            if name == "head":
+                return head
+            return self._w(self.layers[l], name)[0]
         for l, L in enumerate(self.layers):
             w, s = self._w(L, "wqkv")
-            D.decode_linear(x, w, scales=s, norm_w=L["n1"], eps=c.eps, mode=D.QKV,
+            D.decode_linear(x, w, scales=s, norm_w=L["n1"], eps=c.eps, mode=D.QKV, next_weights=nxt(l, "wo"),
                             qkv=dict(q_heads=self.qh, kv_heads=self.kvh, head_dim=c.head_dim, pos=self.pos, cos=self.cos,
                                      sin=self.sin, q_out=self.q, k_cache=L["kc"], v_cache=L["vc"], max_seq=c.max_seq))
             self.att(self.q, L["kc"], L["vc"], self.pos, self.att_out, window=c.window if c.is_local(l) else 0)
             w, s = self._w(L, "wo")
             if self.world > 1:
-                D.decode_linear(self.att_out, w, scales=s, mode=D.ALLREDUCE, out=x1, residual=x, ar=self._ar(2 * l))
+                D.decode_linear(self.att_out, w, scales=s, mode=D.ALLREDUCE, out=x1, residual=x, ar=self._ar(2 * l),
+                                next_weights=nxt(l, "wgu"))
             else:
-                D.decode_linear(self.att_out, w, scales=s, out=x1, residual=x)
+                D.decode_linear(self.att_out, w, scales=s, out=x1, residual=x, next_weights=nxt(l, "wgu"))
             w, s = self._w(L, "wgu")
-            D.decode_linear(x1, w, scales=s, norm_w=L["n2"], eps=c.eps, mode=D.GLU, act="gelu_tanh", out=self.h)
+            D.decode_linear(x1, w, scales=s, norm_w=L["n2"], eps=c.eps, mode=D.GLU, act="gelu_tanh", out=self.h,
+                            next_weights=nxt(l, "wd"))
+            after = nxt(l + 1, "wqkv") if l + 1 < len(self.layers) else nxt(l, "head")
             w, s = self._w(L, "wd")
             if self.world > 1:
-                D.decode_linear(self.h, w, scales=s, mode=D.ALLREDUCE, out=x, residual=x1, ar=self._ar(2 * l + 1))
+                D.decode_linear(self.h, w, scales=s, mode=D.ALLREDUCE, out=x, residual=x1, ar=self._ar(2 * l + 1),
+                                next_weights=after)
             else:
-                D.decode_linear(self.h, w, scales=s, out=x, residual=x1)
+                D.decode_linear(self.h, w, scales=s, out=x, residual=x1, next_weights=after)
         if self.quant in ("w4", "w8"):
             D.decode_linear(x, self.lm_q, scales=self.lm_s, norm_w=self.nf, eps=c.eps, out=self.logits)
         else:

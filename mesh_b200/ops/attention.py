@@ -7,7 +7,7 @@ placement.py:57-69).
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_uint32, c_uint64, c_void_p
 
 import torch
 
@@ -21,7 +21,9 @@ class _Flash(ctypes.Structure):
                 ("q_cols", c_int), ("k_cols", c_int), ("v_cols", c_int), ("q_col0", c_int), ("k_col0", c_int), ("v_col0", c_int),
                 ("B", c_int), ("H", c_int), ("Hkv", c_int), ("Tq", c_int), ("Tk", c_int), ("head_dim", c_int),
                 ("causal", c_int), ("window", c_int), ("q_off", c_int), ("q_stride", c_int), ("k_off", c_int),
-                ("k_stride", c_int), ("scale", c_float), ("status", c_void_p)]
+                ("k_stride", c_int), ("scale", c_float), ("status", c_void_p),
+                ("dropout_p", c_float), ("seed", c_uint64), ("site", c_uint32), ("execution", c_uint32),
+                ("head_off", c_int), ("heads_total", c_int)]
 
 
 def _view2d(t: torch.Tensor):
@@ -32,9 +34,23 @@ def _view2d(t: torch.Tensor):
     return t.data_ptr(), t.stride(1), H * hd
 
 
+def _set_dropout(a, dropout) -> None:
+    """``dropout``: ``None`` or a dict ``p, seed, site=0, execution=0, head_off=0, heads_total=None``.  The keep mask
+    is a function of the logical coordinates (batch, head_off + head of heads_total, query position, key position):
+    every shard of the heads or of the sequence drops what one device would (``ops/philox.py::attention_keep_mask``)."""
+    if not dropout or not dropout.get("p"):
+        return
+    a.dropout_p = float(dropout["p"])
+    a.seed = int(dropout.get("seed", 0)) & 0xFFFFFFFFFFFFFFFF
+    a.site, a.execution = int(dropout.get("site", 0)) & 0xFFFFFFFF, int(dropout.get("execution", 0)) & 0xFFFFFFFF
+    a.head_off = int(dropout.get("head_off", 0))
+    a.heads_total = int(dropout.get("heads_total") or 0)
+
+
 def flash_attention(q, k, v, *, causal=True, window=0, scale=None, q_off=0, q_stride=1, k_off=0, k_stride=1,
-                    need_lse=False, out=None):
-    """``q [B, Tq, H, hd]``, ``k, v [B, Tk, Hkv, hd]`` bf16 -> ``out [B, Tq, H, hd]`` (and ``lse [B, H, Tq]``)."""
+                    need_lse=False, out=None, dropout=None):
+    """``q [B, Tq, H, hd]``, ``k, v [B, Tk, Hkv, hd]`` bf16 -> ``out [B, Tq, H, hd]`` (and ``lse [B, H, Tq]``).
+    ``dropout``: see :func:`_set_dropout` (dropout of the attention probabilities, inside the kernel)."""
     B, Tq, H, hd = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     scale = hd ** -0.5 if scale is None else scale
@@ -52,6 +68,7 @@ def flash_attention(q, k, v, *, causal=True, window=0, scale=None, q_off=0, q_st
     a.q_off, a.q_stride, a.k_off, a.k_stride = q_off, q_stride, k_off, k_stride
     a.scale = scale
     a.status = status_block(q.device).data_ptr()
+    _set_dropout(a, dropout)
     rc = _native.lib().mesh_flash_attention_fwd(ctypes.byref(a), c_void_p(torch.cuda.current_stream().cuda_stream))
     _native.check(rc, "mesh_flash_attention_fwd")
     _native.count_launch()
@@ -136,7 +153,7 @@ class _FlashBwd(ctypes.Structure):
 
 
 def flash_attention_backward(q, k, v, out, lse, dout, *, causal=True, window=0, scale=None, q_off=0, q_stride=1,
-                             k_off=0, k_stride=1, delta=None, dq=None, dkv_acc=None):
+                             k_off=0, k_stride=1, delta=None, dq=None, dkv_acc=None, dropout=None):
     """Gradients of :func:`flash_attention`.  Returns ``(dq fp32 [B,Tq,H,hd], dk, dv)``.
 
     ``dq`` (fp32) is added to when given.  With ``dkv_acc`` (fp32 ``[2, B, Tk, Hkv, hd]``) the key/value gradients
@@ -162,6 +179,7 @@ def flash_attention_backward(q, k, v, out, lse, dout, *, causal=True, window=0, 
     f.q_off, f.q_stride, f.k_off, f.k_stride = q_off, q_stride, k_off, k_stride
     f.scale = scale
     f.status = status_block(q.device).data_ptr()
+    _set_dropout(f, dropout)
     a.dout, a.ld_do, a.do_cols = _view2d(dout)
     a.delta = delta.data_ptr()
     a.dq, a.ld_dq = dq.data_ptr(), dq.stride(1)
@@ -181,23 +199,25 @@ def flash_attention_backward(q, k, v, out, lse, dout, *, causal=True, window=0, 
 
 class _Attention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, window, scale):
-        out, lse = flash_attention(q, k, v, causal=causal, window=window, scale=scale, need_lse=True)
+    def forward(ctx, q, k, v, causal, window, scale, dropout=None):
+        out, lse = flash_attention(q, k, v, causal=causal, window=window, scale=scale, need_lse=True, dropout=dropout)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.cfg = (causal, window, scale)
+        ctx.cfg = (causal, window, scale, dropout)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse = ctx.saved_tensors
-        causal, window, scale = ctx.cfg
-        dq, dk, dv = flash_attention_backward(q, k, v, out, lse, dout, causal=causal, window=window, scale=scale)
-        return dq.to(q.dtype), dk, dv, None, None, None
+        causal, window, scale, dropout = ctx.cfg
+        dq, dk, dv = flash_attention_backward(q, k, v, out, lse, dout, causal=causal, window=window, scale=scale,
+                                              dropout=dropout)
+        return dq.to(q.dtype), dk, dv, None, None, None, None
 
 
-def attention(q, k, v, *, causal=True, window=0, scale=None):
-    """Differentiable attention on the flash kernels (``q [B, T, H, hd]``, ``k, v [B, T, Hkv, hd]``, bf16)."""
-    return _Attention.apply(q, k, v, causal, window, scale)
+def attention(q, k, v, *, causal=True, window=0, scale=None, dropout=None):
+    """Differentiable attention on the flash kernels (``q [B, T, H, hd]``, ``k, v [B, T, Hkv, hd]``, bf16).
+    ``dropout``: ``dict(p=..., seed=..., site=0, execution=0)``; the backward pass redraws the same mask."""
+    return _Attention.apply(q, k, v, causal, window, scale, dropout)
 
 
 def _ring_positions(r, src, P, T, striped):
@@ -251,7 +271,7 @@ def ring_attention_autograd(q, k, v, comm, *, causal=True, striped=False, scale=
     return _RingAttention.apply(q, k, v, comm, causal, striped, scale, overlap)
 
 
-def attention_ref(q, k, v, causal=True, window=0, scale=None, q_off=0, q_stride=1, k_off=0, k_stride=1):
+def attention_ref(q, k, v, causal=True, window=0, scale=None, q_off=0, q_stride=1, k_off=0, k_stride=1, dropout=None):
     """fp32 PyTorch statement (oracle)."""
     B, Tq, H, hd = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
@@ -270,6 +290,13 @@ def attention_ref(q, k, v, causal=True, window=0, scale=None, q_off=0, q_stride=
     lse = torch.logsumexp(s, -1)
     p = torch.softmax(s, -1)
     p = torch.where(torch.isnan(p), torch.zeros_like(p), p)
+    if dropout and dropout.get("p"):
+        from .philox import attention_keep_mask
+        Ht = dropout.get("heads_total") or H
+        bh = (torch.arange(B, device=q.device)[:, None] * Ht + dropout.get("head_off", 0) + torch.arange(H, device=q.device)[None, :])
+        keep = attention_keep_mask(bh[:, :, None, None], qp[None, None, :, None], kp[None, None, None, :], float(dropout["p"]),
+                                   int(dropout.get("seed", 0)), int(dropout.get("site", 0)), int(dropout.get("execution", 0)))
+        p = torch.where(keep, p / (1.0 - float(dropout["p"])), torch.zeros_like(p))
     return torch.einsum("bhts,bshd->bthd", p, vf), lse
 
 

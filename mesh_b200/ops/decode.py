@@ -36,6 +36,7 @@ class _Lin(ctypes.Structure):
         ("step_ptr", c_void_p), ("calls_per_step", c_uint32), ("call_index", c_uint32),
         ("residual", c_void_p), ("ldr", c_longlong),
         ("status", c_void_p),
+        ("next_w", c_void_p), ("next_bytes", ctypes.c_uint64),
     ]
 
 
@@ -91,14 +92,16 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, *, scales: torch.Tensor | No
                   norm_w: torch.Tensor | None = None, eps: float = 1e-6, norm_off: float = 0.0,
                   mode: int = STORE, act: str = "gelu_tanh", up_off: int = 0,
                   out: torch.Tensor | None = None, out_f32: bool = False, residual: torch.Tensor | None = None,
-                  qkv: dict | None = None, ar: dict | None = None) -> torch.Tensor | None:
+                  qkv: dict | None = None, ar: dict | None = None, next_weights: torch.Tensor | None = None) -> torch.Tensor | None:
     """One fused skinny linear layer.  ``x [B<=8, K]`` bf16; ``w`` bf16 ``[rows, K]``, or uint8 codes with
     ``scales`` (``[rows, K/2]``: 4-bit, :func:`quantize_w4`; ``[rows, K]``: 8-bit, :func:`quantize_w8`).
 
     ``mode``: STORE (``out[b, n]``, optional ``residual`` added) | GLU (``w = [gate; up]``, ``up_off`` = gate rows) |
     QKV (``qkv`` = dict(q_heads, kv_heads, head_dim, pos, cos, sin, q_out, k_cache, v_cache, max_seq)) |
     ALLREDUCE (``ar`` = dict(rank, world, recv_ptrs, step, calls_per_step, call_index); sums the ranks' partial
-    outputs, adds ``residual``).
+    outputs, adds ``residual``).  ``next_weights``: the weight matrix of the linear layer that follows in the step; this
+    kernel asks for (up to 96 MB of) it to be brought into L2 while it streams its own, so that HBM does not sit idle
+    across the kernel boundary.
     """
     B, K = x.shape
     w4 = 0                                   # weight format: 0 bf16, 1 4-bit codes, 8 8-bit codes
@@ -130,6 +133,9 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, *, scales: torch.Tensor | No
             d.ar_recv[r] = ar["recv_ptrs"][r]
         d.step_ptr, d.calls_per_step, d.call_index = _p(ar.get("step")), ar.get("calls_per_step", 1), ar.get("call_index", 0)
     d.status = status_block(x.device).data_ptr()
+    if next_weights is not None:
+        d.next_w = next_weights.data_ptr()
+        d.next_bytes = min(next_weights.numel() * next_weights.element_size(), 96 << 20)
     rc = _native.lib().mesh_decode_linear(ctypes.byref(d), _stream())
     _native.check(rc, "mesh_decode_linear")
     _native.count_launch()

@@ -81,3 +81,18 @@ def dropout(x: torch.Tensor, p: float, seed: int, execution: int = 0, site: int 
     idx = logical_index(shape, slices, x.device)
     keep = uniform(idx, seed, execution, site) >= p
     return torch.where(keep, x / (1 - p), torch.zeros((), dtype=x.dtype, device=x.device))
+
+
+def attention_keep_mask(bh: torch.Tensor, qpos: torch.Tensor, kpos: torch.Tensor, p: float, seed: int, site: int = 0,
+                        execution: int = 0) -> torch.Tensor:
+    """Keep mask of attention dropout as the flash kernels draw it (``csrc/device/philox.cuh``): one Philox call per
+    four consecutive key positions, counter ``(kpos >> 2, qpos, batch * heads + head, site)``, key
+    ``(seed_lo ^ execution * 0x9E3779B9, seed_hi)``, ``u = (word[kpos & 3] >> 8) * 2^-24``, keep iff ``u >= p``.
+    ``bh``, ``qpos``, ``kpos``: broadcastable int64 tensors of logical coordinates.  Returns a bool tensor."""
+    bh, qpos, kpos = torch.broadcast_tensors(bh.to(torch.int64), qpos.to(torch.int64), kpos.to(torch.int64))
+    k0 = ((seed & MASK) ^ ((execution * 0x9E3779B9) & MASK)) & MASK
+    k1 = (seed >> 32) & MASK
+    words = philox4x32((kpos >> 2, qpos, bh, torch.full_like(kpos, site & MASK)), (k0, k1))
+    sel = kpos & 3
+    w = torch.where(sel == 0, words[0], torch.where(sel == 1, words[1], torch.where(sel == 2, words[2], words[3])))
+    return (w >> 8).to(torch.float32) * (1.0 / (1 << 24)) >= p

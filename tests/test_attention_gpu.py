@@ -174,3 +174,64 @@ def test_head_exchange_attention_two_ranks():
         pytest.skip("needs 2 GPUs")
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_ulysses_rank, 2, use_cuda=True, timeout=300.0)
+
+
+@pytest.mark.parametrize("hd,H,Hkv,T,causal", [(128, 4, 2, 256, True), (64, 2, 2, 200, False), (256, 2, 1, 256, True)])
+def test_flash_forward_with_dropout_matches_the_logical_mask(hd, H, Hkv, T, causal):
+    """Dropout inside the kernel: Philox keyed by (head, query position, key position), against the fp32 statement
+    that applies the same mask; the kept fraction is 1 - p."""
+    from mesh_b200.ops.attention import attention_ref, flash_attention
+    from mesh_b200.ops.philox import attention_keep_mask
+    from mesh_b200.utils.status import check_status
+    torch.manual_seed(3)
+    B = 2
+    q = torch.randn(B, T, H, hd, device="cuda").bfloat16()
+    k = torch.randn(B, T, Hkv, hd, device="cuda").bfloat16()
+    v = torch.randn(B, T, Hkv, hd, device="cuda").bfloat16()
+    drop = dict(p=0.25, seed=0x1234_5678_9ABC, site=3, execution=7)
+    out = flash_attention(q, k, v, causal=causal, dropout=drop)
+    check_status()
+    ref, _ = attention_ref(q, k, v, causal, dropout=drop)
+    _close(out, ref, 3e-2)
+    plain, _ = attention_ref(q, k, v, causal)
+    assert (out.float() - plain).abs().max() > 0.05                  # the mask did something
+    keep = attention_keep_mask(torch.zeros(1, 1, dtype=torch.int64), torch.arange(512)[:, None], torch.arange(512)[None, :],
+                               0.25, drop["seed"], drop["site"], drop["execution"])
+    assert abs(float(keep.float().mean()) - 0.75) < 0.01
+
+
+def test_dropout_is_the_same_for_a_shard_of_the_queries_and_of_the_heads():
+    from mesh_b200.ops.attention import flash_attention
+    torch.manual_seed(4)
+    B, T, H, hd = 1, 512, 4, 128
+    q, k, v = (torch.randn(B, T, H, hd, device="cuda").bfloat16() for _ in range(3))
+    drop = dict(p=0.3, seed=99)
+    whole = flash_attention(q, k, v, causal=True, dropout=drop)
+    # the second half of the queries, as a sequence shard would hold them (logical positions through q_off)
+    part = flash_attention(q[:, 256:].contiguous(), k, v, causal=True, q_off=256, dropout=drop)
+    _close(part, whole[:, 256:], 1e-2)                                 # another mask would differ by O(1)
+    # heads 2..3 only, as a tensor-parallel rank would hold them
+    heads = flash_attention(q[:, :, 2:].contiguous(), k[:, :, 2:].contiguous(), v[:, :, 2:].contiguous(), causal=True,
+                            dropout=dict(drop, head_off=2, heads_total=4))
+    _close(heads, whole[:, :, 2:], 1e-2)
+
+
+@pytest.mark.parametrize("hd,H,Hkv", [(128, 4, 2), (64, 2, 2)])
+def test_flash_backward_with_dropout(hd, H, Hkv):
+    from mesh_b200.ops.attention import attention, attention_ref
+    from mesh_b200.utils.status import check_status
+    torch.manual_seed(5)
+    B, T = 2, 256
+    q = torch.randn(B, T, H, hd, device="cuda").bfloat16().requires_grad_(True)
+    k = torch.randn(B, T, Hkv, hd, device="cuda").bfloat16().requires_grad_(True)
+    v = torch.randn(B, T, Hkv, hd, device="cuda").bfloat16().requires_grad_(True)
+    dout = torch.randn(B, T, H, hd, device="cuda").bfloat16()
+    drop = dict(p=0.2, seed=77, site=1)
+    attention(q, k, v, causal=True, dropout=drop).backward(dout)
+    check_status()
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    o, _ = attention_ref(qf, kf, vf, True, dropout=drop)
+    o.backward(dout.float())
+    _close(q.grad, qf.grad, 3e-2)
+    _close(k.grad, kf.grad, 3e-2)
+    _close(v.grad, vf.grad, 3e-2)
