@@ -46,6 +46,11 @@ def test_stats_block_and_meshctl():
         out = subprocess.run([sys.executable, "-m", "mesh_b200.tools.meshctl", "status", "--group", group, "--world", "1", "--ready"],
                              capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
         assert out.returncode == 0 and json.loads(out.stdout)["ranks"][0]["pid"] == os.getpid()
+        top = subprocess.run([sys.executable, "-m", "mesh_b200.tools.meshctl", "top", "--group", group, "--world", "4",
+                              "--count", "2", "--interval", "0.1"], capture_output=True, text=True,
+                             cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        assert top.returncode == 0 and "links (MB/s" in top.stdout and "CONN" in top.stdout and "(no stats block)" in top.stdout
+        assert "ranks 1/4 alive" in top.stdout
         service.deadline(0.05)                            # the service thread raises abort once the deadline passes
         time.sleep(0.2)
         assert service.aborted()
