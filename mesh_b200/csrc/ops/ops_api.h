@@ -28,6 +28,17 @@ int mesh_dot_sum_bf16(const void* a, const void* b, long long n, float* out, flo
                       void* stream);
 int mesh_dot_sum_blocks(void);
 
+// Cross-entropy over a vocabulary shard logits[rows, cols] (bf16, row stride ld): per-row maximum, sum of exponentials
+// relative to that maximum, and the target's logit when the target (int64 global class id) lies in
+// [vocab_start, vocab_start + cols) and is not ignore_index (else 0).
+int mesh_ce_stats_bf16(const void* logits, long long ld, int rows, int cols, const long long* targets, long long vocab_start,
+                       long long ignore_index, float* row_max, float* row_sum, float* target_logit, void* stream);
+// d = (exp(logits - gmax) / gsum - onehot(target)) * gscale, bf16 (may be the logits buffer itself); gmax, gsum: the
+// whole-vocabulary statistics; gscale[rows]: upstream gradient, 0 for ignored rows.
+int mesh_ce_grad_bf16(const void* logits, long long ld, void* dlogits, long long ldd, int rows, int cols,
+                      const long long* targets, long long vocab_start, const float* gmax, const float* gsum,
+                      const float* gscale, void* stream);
+
 // softmax over experts then top-k (k <= 8, experts <= 256).  bias (fp32[experts], may be NULL) is added
 // to the logits before the softmax.  weights fp32[tokens,k] (renormalised over the k when renorm),
 // indices int32[tokens,k]; ties go to the lower expert index.

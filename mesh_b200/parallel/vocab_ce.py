@@ -25,6 +25,56 @@ def _all_reduce(x: torch.Tensor, group, op: str) -> None:
         dist.all_reduce(x, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM, group=g)
 
 
+def _s():
+    from ctypes import c_void_p
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class _VocabParallelCEKernel(torch.autograd.Function):
+    """bf16 CUDA logits: statistics in one pass (``csrc/ops/cross_entropy.cu``), two tiny all-reduces, gradient in one
+    pass from the logits themselves - no fp32 copy of the logits or of their exponentials is kept for the backward."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, start, group, ignore_index):
+        from ctypes import c_int, c_longlong, c_void_p
+        from .. import _native
+        n, v = logits.shape
+        dev = logits.device
+        t64 = targets.to(torch.int64).contiguous()
+        stats = torch.empty((3, n), dtype=torch.float32, device=dev)            # local max, local sum, target logit
+        rc = _native.lib().mesh_ce_stats_bf16(c_void_p(logits.data_ptr()), c_longlong(logits.stride(0)), c_int(n), c_int(v),
+                                              c_void_p(t64.data_ptr()), c_longlong(start), c_longlong(ignore_index),
+                                              c_void_p(stats[0].data_ptr()), c_void_p(stats[1].data_ptr()),
+                                              c_void_p(stats[2].data_ptr()), _s())
+        _native.check(rc, "mesh_ce_stats_bf16")
+        _native.count_launch()
+        gmax = stats[0].clone()
+        _all_reduce(gmax, group, "max")
+        sums = torch.stack([stats[1] * torch.exp(stats[0] - gmax), stats[2]])
+        _all_reduce(sums, group, "sum")
+        live = t64 != ignore_index
+        loss = torch.where(live, torch.log(sums[0]) + gmax - sums[1], torch.zeros_like(gmax))
+        ctx.save_for_backward(logits, t64, gmax, sums[0].contiguous(), live)
+        ctx.start = start
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        from ctypes import c_int, c_longlong, c_void_p
+        from .. import _native
+        logits, t64, gmax, gsum, live = ctx.saved_tensors
+        n, v = logits.shape
+        gscale = (g.float() * live.float()).contiguous()
+        d = torch.empty((n, v), dtype=torch.bfloat16, device=logits.device)
+        rc = _native.lib().mesh_ce_grad_bf16(c_void_p(logits.data_ptr()), c_longlong(logits.stride(0)), c_void_p(d.data_ptr()),
+                                             c_longlong(d.stride(0)), c_int(n), c_int(v), c_void_p(t64.data_ptr()),
+                                             c_longlong(ctx.start), c_void_p(gmax.data_ptr()), c_void_p(gsum.data_ptr()),
+                                             c_void_p(gscale.data_ptr()), _s())
+        _native.check(rc, "mesh_ce_grad_bf16")
+        _native.count_launch()
+        return d, None, None, None, None
+
+
 class _VocabParallelCE(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, targets, start, group, ignore_index):
@@ -60,7 +110,10 @@ def vocab_parallel_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, vo
     ``targets [N]``: global class ids (the same on every rank of ``group``, a torch.distributed group or an axis
     context).  Returns the per-token losses (``reduction="none"``), their sum, or their mean over the tokens that are
     not ``ignore_index``."""
-    loss = _VocabParallelCE.apply(logits, targets, int(vocab_start), group, int(ignore_index))
+    if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.dim() == 2 and logits.stride(1) == 1:
+        loss = _VocabParallelCEKernel.apply(logits, targets, int(vocab_start), group, int(ignore_index))
+    else:
+        loss = _VocabParallelCE.apply(logits, targets, int(vocab_start), group, int(ignore_index))
     if reduction == "none":
         return loss
     if reduction == "sum":

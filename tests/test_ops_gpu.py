@@ -67,3 +67,22 @@ def test_dot_sum(n):
         got = dot_sum(a, b)
     want = (a.double() * b.double()).sum()
     assert abs(float(got) - float(want)) <= 1e-3 * float((a.double() * b.double()).abs().sum().sqrt()) + 1e-3
+
+
+@pytest.mark.parametrize("n,v,start", [(64, 1000, 0), (300, 25152, 25152), (7, 4099, 100)])
+def test_cross_entropy_kernels_match_fp32(n, v, start):
+    """One vocabulary shard alone (group of one): loss and gradient against torch's fp32 cross-entropy over the shard,
+    with targets outside the shard and ignored rows."""
+    from mesh_b200.parallel.vocab_ce import vocab_parallel_cross_entropy
+    torch.manual_seed(0)
+    logits = (torch.randn(n, v, device="cuda") * 3).bfloat16().requires_grad_(True)
+    targets = torch.randint(start, start + v, (n,), device="cuda")
+    targets[::5] = -100
+    loss = vocab_parallel_cross_entropy(logits, targets, start, None, reduction="sum")
+    loss.backward()
+    ref = logits.detach().float().requires_grad_(True)
+    local = torch.where(targets == -100, targets, targets - start)
+    want = torch.nn.functional.cross_entropy(ref, local, ignore_index=-100, reduction="sum")
+    want.backward()
+    assert abs(float(loss) - float(want)) <= 2e-3 * abs(float(want)) + 1e-3
+    assert float((logits.grad.float() - ref.grad).abs().max()) < 8e-3
