@@ -126,8 +126,27 @@ def _build_locked(nvcc: str, verbose: bool, check: bool) -> Path:
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, lib_path(check))
-    _meta_path(check).write_text(json.dumps({"digest": _tree_digest(check), "sources": [str(s.relative_to(CSRC)) for s in srcs]}))
+    _meta_path(check).write_text(json.dumps({"digest": _tree_digest(check), "sources": [str(s.relative_to(CSRC)) for s in srcs],
+                                             "objects": [o.name for o in objs]}))
+    _prune_objects()
     return lib_path(check)
+
+
+def _prune_objects() -> None:
+    """Objects are cached by content hash; those that neither library variant was last linked from are deleted, so the
+    cache does not grow with every edit."""
+    keep: set[str] = set()
+    for check in (False, True):
+        try:
+            keep.update(json.loads(_meta_path(check).read_text()).get("objects", []))
+        except Exception:
+            return                                  # an older metadata file: keep everything
+    for f in OBJDIR.glob("*.o"):
+        if f.name not in keep:
+            try:
+                f.unlink()
+            except OSError:
+                pass
 
 
 if __name__ == "__main__":
