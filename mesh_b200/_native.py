@@ -49,6 +49,7 @@ class GemmArgs(ctypes.Structure):
         ("tiles", c_void_p), ("n_tiles_dev", c_void_p), ("max_tiles", c_int),
         ("d_done", c_void_p), ("k_ready", c_void_p), ("k_ready_value", c_uint32), ("k_ready_rows", c_int),
         ("b_scales", c_void_p), ("b_bits", c_int), ("pdl", c_int),
+        ("ar_out", c_void_p * MAX_RANKS), ("ar_flag", c_void_p * MAX_RANKS), ("ar_expect", c_uint32),
     ]
 
 

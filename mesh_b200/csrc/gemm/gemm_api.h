@@ -65,6 +65,12 @@ typedef struct MeshGemmArgs {
   int pdl;                     // bit 0: may start before the previous launch of the stream has finished (every input
                                // that launch writes is guarded by a_ready / k_ready); bit 1: let the next launch
                                // start during this kernel's last wave
+  // GEMM -> all-reduce (with epi = scatter): after a rank has summed a tile of its rows it stores the tile into every
+  // rank's full output `ar_out[r]` ([M, N] bf16 in the symmetric heap) and raises `ar_flag[r]`; the kernel ends once
+  // this rank's counter shows every other rank's tiles (`ar_expect`, cumulative over uses).  NULL ar_out[0]: reduce-scatter only.
+  void* ar_out[MESH_MAX_RANKS];
+  void* ar_flag[MESH_MAX_RANKS];
+  uint32_t ar_expect;
 } MeshGemmArgs;
 
 // Returns 0 or a negative error (bad shape/alignment) or a positive cudaError_t.

@@ -177,6 +177,12 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
       if (!make_map_2d(&p.tmRS[r], a->rs_recv[r], 64, view_rows, 64, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
         return last_error_code();
     }
+    for (int r = 0; r < p.world; ++r) {
+      p.ar_out[r] = (__nv_bfloat16*)a->ar_out[r];
+      p.ar_flag[r] = (uint32_t*)a->ar_flag[r];
+    }
+    p.ar_expect = a->ar_expect;
+    if (p.ar_out[0] != nullptr && (a->N % 8)) return set_error(-5, "gemm: all-reduce output needs N %% 8 == 0");
     p.rs_recv = (const __nv_bfloat16*)a->rs_recv[p.rank];
     p.rs_expect = a->rs_expect;
     p.rs_out = (__nv_bfloat16*)a->rs_out;

@@ -123,6 +123,10 @@ struct Params {
   int k_ready_rows;
   int pdl_trigger;          // let the next launch of the stream start during this kernel's last wave
   int a_extent, b_extent;   // rows (MN extent) of the stored A and B matrices: bounds for descriptor tiles (checked build)
+  // ---- GEMM -> all-reduce: the reduce tail also broadcasts every summed tile -------------------
+  __nv_bfloat16* ar_out[MAX_RANKS];    // every rank's full output [M, N]; nullptr: reduce-scatter only
+  uint32_t* ar_flag[MAX_RANKS];        // ar_flag[r]: rank r's arrival counter, one arrival per (tile, source rank)
+  uint32_t ar_expect;
   // ---- group-quantised B (weights): codes + one fp16 scale per 64 k of a row ------------------
   // The B stages of the shared-memory ring are then not filled by TMA: four extra warps read the codes with plain
   // loads, dequantise them in registers ((code - 8) * scale for 4-bit, (code - 128) * scale for 8-bit) and store bf16
@@ -867,8 +871,27 @@ gemm_kernel(const __grid_constant__ Params p) {
         o.y = pack_bf16(acc[2], acc[3]);
         o.z = pack_bf16(acc[4], acc[5]);
         o.w = pack_bf16(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(p.rs_out + (long long)(mt * BM + r) * p.N + nt * BN + c * 64 + v * 8) = o;
+        const long long at = (long long)(mt * BM + r) * p.N + nt * BN + c * 64 + v * 8;
+        if (p.rs_out != nullptr) *reinterpret_cast<uint4*>(p.rs_out + at) = o;
+        if (p.ar_out[0] != nullptr) {
+          // all-reduce: the summed tile goes into every rank's full output, at this rank's rows
+          const long long full = (long long)p.rank * p.rs_rows_per_rank * p.N + at;
+#pragma unroll
+          for (int d = 0; d < MAX_RANKS; ++d)
+            if (d < p.world) *reinterpret_cast<uint4*>(p.ar_out[d] + full) = o;
+        }
       }
+      if (p.ar_out[0] != nullptr) {
+        // one arrival per tile on every other rank's counter; the barrier orders the block's stores before the
+        // signalling threads, whose system-scope release is cumulative over them
+        __syncthreads();
+        if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) red_release_sys_add(p.ar_flag[threadIdx.x], 1u);
+      }
+    }
+    if (p.ar_out[0] != nullptr) {
+      // the full output is complete here once every other rank's tiles have arrived
+      if (threadIdx.x == 0) item_ok = wait_flag_ge(p.ar_flag[p.rank], p.ar_expect, p.status, SITE_PEER_FLAG) ? 1 : 0;
+      __syncthreads();
     }
   }
   // A kernel that started before its predecessor had finished does not finish before it: whoever is ordered after

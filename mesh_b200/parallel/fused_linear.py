@@ -57,8 +57,9 @@ class _FusedBase:
         for r in range(self.world):
             g.rs_recv[r] = buf.ptr(r)
             g.rs_count[r] = count.ptr(r)
-        g.rs_expect, g.rs_out, g.rs_rows_per_rank = expect, out.data_ptr(), self.rows
+        g.rs_expect, g.rs_out, g.rs_rows_per_rank = expect, (0 if out is None else out.data_ptr()), self.rows
         g.m_rotate = ((self.rank + 1) % self.world) * (self.rows // BM)
+        return zone
 
 
 class FusedColumnLinear(_FusedBase):
@@ -176,21 +177,51 @@ class FusedRowLinearAllReduce(_FusedBase):
     parallelism, the row-parallel half: examples/parallel.py:84-89 of the reference, whose compiler emits a reduce
     there, compiler/mesh_compiler/placement.py:812-834).
 
-    A two-shot all-reduce whose first shot is the GEMM's own epilogue: the tiles are scattered to the owners of their
-    token rows and summed there (:class:`FusedRowLinear`), then the summed rows are all-gathered with the
-    communicator's kernel, so the partial products never make a round trip through HBM before they cross NVLink.
-    Backward: ``dy`` is whole on every rank, so ``dh = dy W`` and ``dW = dy^T h`` are local products."""
+    ONE kernel: the GEMM's epilogue scatters the partial tiles to the owners of their token rows; as soon as an owner
+    has summed a tile of its rows it stores the sum into every rank's full output (peer stores) and raises that rank's
+    counter; the kernel ends on every rank when all other ranks' tiles have arrived.  The partial products never make
+    a round trip through HBM before they cross NVLink, and the gathering half starts while later tiles are still being
+    multiplied.  ``MESH_FUSED_AR=0`` runs the older composition (the same scattering GEMM, then the communicator's
+    all-gather kernel).  Backward: ``dy`` is whole on every rank, so ``dh = dy W`` and ``dW = dy^T h`` are local."""
 
     def __init__(self, heap, comm, tokens: int, k_local: int, d_out: int):
+        import os
         super().__init__(heap, tokens, k_local, d_out)
         self.row = FusedRowLinear(heap, tokens, k_local, d_out)
-        self.comm, self.D = comm, d_out
+        self.comm, self.D, self.K = comm, d_out, k_local
+        self.one_kernel = os.environ.get("MESH_FUSED_AR", "1") != "0"
+        if self.one_kernel:
+            # full outputs [tokens, D], two of them used in turn (a rank can be one use ahead of a peer), and one
+            # arrival counter each; counters only grow
+            self.full = [heap.alloc((tokens, d_out), torch.bfloat16) for _ in range(2)]
+            self.flag = [heap.alloc_signals(1) for _ in range(2)]
+            self.uses = [0, 0]
+            self.turn = 0
 
-    def forward(self, h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        mine = self.row.forward(h, w)                                     # [tokens / world, D]: summed over the ranks
-        full = torch.empty((self.M, self.D), dtype=mine.dtype, device=mine.device)
-        self.comm.all_gather(full, mine)
-        return full
+    def forward(self, h: torch.Tensor, w: torch.Tensor, copy: bool = True) -> torch.Tensor:
+        """``copy=False`` returns the landing buffer itself, which is overwritten two calls later."""
+        if not self.one_kernel:
+            mine = self.row.forward(h, w)                                 # [tokens / world, D]: summed over the ranks
+            full = torch.empty((self.M, self.D), dtype=mine.dtype, device=mine.device)
+            self.comm.all_gather(full, mine)
+            return full
+        dev = h.device
+        par = self.turn & 1
+        self.turn += 1
+        self.uses[par] += 1
+        g = self._args(dev)
+        g.A, g.lda, g.a_rows = h.data_ptr(), h.stride(0), self.M
+        g.B, g.ldb, g.b_rows = w.data_ptr(), w.stride(0), self.D
+        g.M, g.N, g.K = self.M, self.D, self.K
+        zone = self._scatter_args(g, self.row.y_recv, None)
+        n_tiles = (self.D + zone.tile_n - 1) // zone.tile_n
+        for r in range(self.world):
+            g.ar_out[r] = self.full[par].ptr(r)
+            g.ar_flag[r] = self.flag[par].ptr(r)
+        g.ar_expect = ((self.world - 1) * (self.rows // BM) * n_tiles * self.uses[par]) & 0xFFFFFFFF
+        G._launch(g)
+        out = self.full[par].local.view(self.M, self.D)
+        return out.clone() if copy else out
 
     def backward(self, dy: torch.Tensor, h: torch.Tensor, w: torch.Tensor):
         dy = dy.contiguous()
