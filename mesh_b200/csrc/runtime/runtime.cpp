@@ -11,6 +11,7 @@
 #include <chrono>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <fcntl.h>
 #include <mutex>
@@ -63,6 +64,7 @@ static MeshStats* map_block(const char* name, int create) {
 }
 
 // Create (or re-adopt after a restart) this rank's stats block and start the service thread.
+int mesh_runtime_stop(int unlink_block);
 int mesh_runtime_start(const char* group, int rank, int world, double heartbeat_s) {
   std::lock_guard<std::mutex> lk(g_mu);
   if (g_stats) return 0;
@@ -80,6 +82,13 @@ int mesh_runtime_start(const char* group, int rank, int world, double heartbeat_
   s->abort_flag.store(0);
   g_stats = s;
   g_run.store(true);
+  static bool at_exit_installed = false;
+  if (!at_exit_installed) {
+    // a process that ends without calling stop (an exception on its way out) still joins the service thread before the
+    // thread object is destroyed; the block stays for a supervisor to read
+    at_exit_installed = true;
+    atexit([] { mesh_runtime_stop(0); });
+  }
   const auto period = std::chrono::milliseconds((int)(heartbeat_s > 0.01 ? heartbeat_s * 1000 : 10));
   g_thread = std::thread([period] {
     while (g_run.load()) {

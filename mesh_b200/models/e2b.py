@@ -147,7 +147,10 @@ class E2BDecoder:
         x, x1 = self.x
         torch.index_select(self.emb, 0, self.tok, out=x)
         import os
-        ahead = os.environ.get("MESH_DECODE_PREFETCH_NEXT", "1") != "0"
+        # measured on a B200: asking for whole next matrices (tens of MB) while the current one streams halves the
+        # decode rate (the lines are evicted again before they are used and cross HBM twice); off unless switched on,
+        # and then capped (MESH_DECODE_PREFETCH_MB, default 8 MB: enough to bridge a kernel boundary)
+        ahead = os.environ.get("MESH_DECODE_PREFETCH_NEXT", "0") == "1"
         head = self.lm_q if self.quant in ("w4", "w8") else self.lm_head
 
         def nxt(l, name):

@@ -100,8 +100,8 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, *, scales: torch.Tensor | No
     QKV (``qkv`` = dict(q_heads, kv_heads, head_dim, pos, cos, sin, q_out, k_cache, v_cache, max_seq)) |
     ALLREDUCE (``ar`` = dict(rank, world, recv_ptrs, step, calls_per_step, call_index); sums the ranks' partial
     outputs, adds ``residual``).  ``next_weights``: the weight matrix of the linear layer that follows in the step; this
-    kernel asks for (up to 96 MB of) it to be brought into L2 while it streams its own, so that HBM does not sit idle
-    across the kernel boundary.
+    kernel asks for its first ``MESH_DECODE_PREFETCH_MB`` (default 8) megabytes to be brought into L2 while it streams its
+    own, so that HBM does not sit idle across the kernel boundary.
     """
     B, K = x.shape
     w4 = 0                                   # weight format: 0 bf16, 1 4-bit codes, 8 8-bit codes
@@ -135,7 +135,9 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, *, scales: torch.Tensor | No
     d.status = status_block(x.device).data_ptr()
     if next_weights is not None:
         d.next_w = next_weights.data_ptr()
-        d.next_bytes = min(next_weights.numel() * next_weights.element_size(), 96 << 20)
+        import os
+        cap = int(float(os.environ.get("MESH_DECODE_PREFETCH_MB", "8")) * (1 << 20))
+        d.next_bytes = min(next_weights.numel() * next_weights.element_size(), cap)
     rc = _native.lib().mesh_decode_linear(ctypes.byref(d), _stream())
     _native.check(rc, "mesh_decode_linear")
     _native.count_launch()

@@ -23,6 +23,8 @@ def _comm_of(group, t):
 def _world(group) -> int:
     if hasattr(group, "ranks") and hasattr(group, "world"):
         return group.world
+    if not (dist.is_available() and dist.is_initialized()):
+        return 1                                   # a single process: every collective is the identity
     return dist.get_world_size(group)
 
 

@@ -129,6 +129,44 @@ class HostWord:
         """Has everything up to ``value`` left this rank (``mesh_host_sent``): its source buffers may be rewritten."""
         return int(self.t[2]) >= value
 
+    # ---- the same word seen from a CUDA stream (no kernel involved: stream memory operations)
+    def _stream_words(self) -> torch.Tensor:
+        """32-bit mirrors for the stream operations: [0] raised by the host for streams to wait on, [1] written by
+        streams for the host to read.  Pinned, so both sides see them."""
+        w = getattr(self, "_w32", None)
+        if w is None:
+            w = self._w32 = torch.zeros(2, dtype=torch.int32).pin_memory()
+        return w
+
+    def publish_to_streams(self, value: int) -> None:
+        """``publish`` that streams blocked in :meth:`stream_wait` also see (monotonic)."""
+        self.publish(value)
+        w = self._stream_words()
+        if value > int(w[0]):
+            w[0] = value
+
+    def stream_wait(self, value: int, stream=None) -> None:
+        """Everything queued on ``stream`` (default: the current one) after this call starts only once the word has
+        been published to at least ``value`` - the device-side counterpart of :meth:`wait`, without a polling kernel
+        (``cuStreamWaitValue32``).  The host must publish in finite time: a stream wait has no timeout of its own."""
+        from ctypes import c_uint32, c_void_p
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        w = self._stream_words()
+        rc = _native.lib().mesh_stream_wait_value(c_void_p(s), c_void_p(w.data_ptr()), c_uint32(value & 0xFFFFFFFF))
+        _native.check(rc, "mesh_stream_wait_value")
+
+    def stream_mark_sent(self, value: int, stream=None) -> None:
+        """The stream records ``value`` once everything queued before this call has finished; :meth:`stream_sent`
+        reads it (``cuStreamWriteValue32``): the host learns that a buffer has left without synchronising."""
+        from ctypes import c_uint32, c_void_p
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        w = self._stream_words()
+        rc = _native.lib().mesh_stream_write_value(c_void_p(s), c_void_p(w.data_ptr() + 4), c_uint32(value & 0xFFFFFFFF))
+        _native.check(rc, "mesh_stream_write_value")
+
+    def stream_sent(self, value: int) -> bool:
+        return int(self._stream_words()[1]) >= value
+
     def wait(self, value: int, timeout_s: float = 5.0) -> int:
         """0 when reached, ``ECANCELED`` when cancelled, ``ETIMEDOUT`` after ``timeout_s`` without progress."""
         last, t_last = int(self.t[0]), time.monotonic()
