@@ -74,6 +74,7 @@ def main():
     ap.add_argument("--d-model", type=int, default=2048)
     ap.add_argument("--d-ff", type=int, default=1408)
     ap.add_argument("--top-k", type=int, default=6)
+    ap.add_argument("--phases", action="store_true", help="mesh arm: also report the time of every phase of a step")
     a = ap.parse_args()
     from mesh_b200.config import MeshConfig, set_config
     set_config(MeshConfig.from_env(heap_bytes=8 << 30))
@@ -114,12 +115,25 @@ def main():
                 t.grad = None
             baseline_layer(xp, wr, w1p, w2p, bias, k, E, world, grp).backward(dy)
     ms = time_steps(step, a.steps, a.warmup, world, dev)
+    phases = None
     if a.impl == "mesh":
         check_status()
+        if a.phases:
+            import statistics
+            per: dict = {}
+            for _ in range(5):
+                moe.timeline = []
+                step()
+                torch.cuda.synchronize()
+                for name, us in moe.phases(moe.timeline):
+                    per.setdefault(name, []).append(us)
+            moe.timeline = None
+            phases = {name: round(statistics.median(v), 1) for name, v in per.items()}
     flops = 3 * T * k * (2 * D * 2 * Fh + 2 * Fh * D) * world
     emit(rank, {"metric": "moe_ep_train_tokens_per_s", "value": round(T * world / (ms * 1e-3), 1), "unit": "tokens/s (fwd+bwd)",
                 "impl": a.impl, "n_gpus": world, "ms_per_step": round(ms, 4), "steps": a.steps,
                 "tflops_total": round(flops / (ms * 1e-3) / 1e12, 1), "gpu_launches_per_step": launches,
+                **({"phase_us_rank0": phases} if phases else {}),
                 "config": {"tokens_per_rank": T, "d_model": D, "experts": E, "d_ff": Fh, "top_k": k, "ep": world,
                            "skew": "per-rank N(0,1) expert bias", "l2": "256 MiB flush write between steps (untimed)"}})
     from mesh_b200.distributed import shutdown

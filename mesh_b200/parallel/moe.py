@@ -148,13 +148,30 @@ class EPMoE:
         _native.check(self.L.mesh_moe_combine(ctypes.byref(c), _s()), "mesh_moe_combine")
         _native.count_launch()
 
+    # ------------------------------------------------------------------ phase timeline (benchmarks)
+    timeline: list | None = None      # set to [] to record a CUDA event after every phase of forward / backward
+
+    def _mark(self, name: str) -> None:
+        if self.timeline is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.timeline.append((name, e))
+
+    @staticmethod
+    def phases(timeline: list) -> list:
+        """``[(phase, microseconds)]`` from a recorded timeline (after a synchronize): the time between consecutive
+        marks, i.e. the kernels of that phase as the stream ran them."""
+        return [(b[0], a[1].elapsed_time(b[1]) * 1e3) for a, b in zip(timeline, timeline[1:])]
+
     # ------------------------------------------------------------------ forward / backward
     def forward(self, x, w_router, w1, w2, bias=None):
         """x [T, D] bf16; w_router [E, D]; w1 [El*2F, D] (per expert: gate rows then up rows); w2 [El*D, F]."""
         T, D, F, k = self.T, self.D, self.F, self.k
         self.steps += 1
+        self._mark("start")
         logits = G.gemm(x, w_router)                                            # [T, E]
         weights, idx = router_topk(logits, k, bias, renorm=True)
+        self._mark("router")
         self.idx = idx.reshape(-1).contiguous()
         arr = (c_void_p * MAX_RANKS)(*[c_void_p(self.counts.ptr(r)) if r < self.world else c_void_p(0) for r in range(MAX_RANKS)])
         _native.check(self.L.mesh_moe_count(c_void_p(self.idx.data_ptr()), c_int(T * k), c_void_p(self.slot.data_ptr()),
@@ -171,15 +188,20 @@ class EPMoE:
         _native.check(self.L.mesh_moe_zero_pad(c_void_p(self.recv_x.ptr()), c_void_p(self.layout.data_ptr()), c_int(self.El),
                                                c_int(D), _s()), "mesh_moe_zero_pad")
         _native.count_launch(3)
+        self._mark("count+plan+pad")
         self._dispatch(x, None, self.recv_x, 0)
+        self._mark("dispatch")
         expect = self.world * DISPATCH_BLOCKS * self.steps
         rx = self.recv_x.local
         self._grouped(0, rx, w1, self.h, M=self.cap, N=F, K=D, epi=G.EPI_GLU_FWD, D2=self.gu, b_up_rows=F, d_up_cols=F,
                       a_ready=self.sig.ptr() + 0, a_ready_value=expect)
+        self._mark("experts glu")
         self._grouped(1, self.h, w2, self.y.local, M=self.cap, N=D, K=F)
+        self._mark("experts down")
         self._signal(2)
         out = torch.empty((T, D), dtype=torch.bfloat16, device=self.dev)
         self._combine(self.y, 2, weights.reshape(-1), out)
+        self._mark("combine")
         self._saved = (x, w_router, w1, w2, logits, weights, bias)
         return out
 
@@ -189,22 +211,30 @@ class EPMoE:
         dout = dout.contiguous()
         # gradients of the routing weights: <expert output row, dOut[t]> (reads the forward's y on the peers)
         dots = torch.empty((T, k), dtype=torch.float32, device=self.dev)
+        self._mark("bwd start")
         self._combine(self.y, 2, None, None, dot_with=dout, dots=dots.view(-1))
+        self._mark("bwd weight dots")
         _native.check(self.L.mesh_moe_zero_pad(c_void_p(self.recv_dy.ptr()), c_void_p(self.layout.data_ptr()), c_int(self.El),
                                                c_int(D), _s()), "mesh_moe_zero_pad")
         self._dispatch(dout, weights.reshape(-1).contiguous(), self.recv_dy, 1)
+        self._mark("bwd dispatch")
         expect = self.world * DISPATCH_BLOCKS * self.steps
         rdy, rx = self.recv_dy.local, self.recv_x.local
         self._grouped(2, rdy, w2, self.dgu, M=self.cap, N=F, K=D, b_mn=True, epi=G.EPI_GLU_BWD, aux=self.gu, d_up_cols=F,
                       a_ready=self.sig.ptr() + 4, a_ready_value=expect, d_cols=2 * F)
+        self._mark("bwd dH glu")
         dw2 = torch.zeros_like(w2)
         self._grouped(4, rdy, self.h, dw2, M=D, N=F, K=self.cap, a_mn=True, b_mn=True)
+        self._mark("bwd dW2")
         self._grouped(3, self.dgu, w1, self.dx.local, M=self.cap, N=D, K=2 * F, b_mn=True)
+        self._mark("bwd dX")
         dw1 = torch.zeros_like(w1)
         self._grouped(5, self.dgu, rx, dw1, M=2 * F, N=D, K=self.cap, a_mn=True, b_mn=True)
+        self._mark("bwd dW1")
         self._signal(3)
         dx = torch.empty((T, D), dtype=torch.bfloat16, device=self.dev)
         self._combine(self.dx, 3, None, dx)
+        self._mark("bwd combine")
         # router: weights = renormalised top-k of softmax(logits + bias)
         lg = logits.float().detach().requires_grad_(True)
         p = torch.softmax(lg + (bias.float() if bias is not None else 0.0), dim=-1)
@@ -216,6 +246,7 @@ class EPMoE:
         dx = dx + G.gemm(dlogits, w_router, b_mn=True)
         dw_router = G.gemm(dlogits, x, a_mn=True, b_mn=True) if (dlogits.shape[1] % 64 == 0 and x.shape[1] % 64 == 0) else \
             (dlogits.float().T @ x.float()).to(torch.bfloat16)
+        self._mark("bwd router")
         return dx, dw_router, dw1, dw2
 
 
