@@ -9,6 +9,9 @@ serialised, ``MESH_GEMM_CHAIN=0`` semantics), the same six GEMMs run locally wit
 launches chained (the default), the stock PyTorch + NCCL + cuBLAS arm, and the bytes each fused kernel sends over
 NVLink with the time those bytes need at the measured peer bandwidth.  Every number is the median over the timed
 steps and the maximum over ranks.
+
+``--shard-of N`` on one GPU times the local GEMMs at the shard shapes of an N-GPU job (d_ff / N columns): what the
+tensor cores of one rank need at that N, tile waves included, with no GPU but this one.
 """
 from __future__ import annotations
 
@@ -32,9 +35,14 @@ def main() -> int:
     from mesh_b200.ops import gemm as G
     from mesh_b200.parallel.tp_ffn import FusedTPFFN
     from mesh_b200.utils.status import check_status
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shard-of", type=int, default=0)
+    a = ap.parse_args()
     ctx = init(backend="nccl")
     rank, world, dev = ctx.rank, ctx.world, ctx.device
-    rows, Fl = TOKENS // world, D_FF // world
+    shard_of = a.shard_of if (a.shard_of and world == 1) else world
+    rows, Fl = TOKENS // world, D_FF // shard_of
     g = torch.Generator(device="cpu").manual_seed(1)
     x = torch.randn(rows, D_MODEL, generator=g).bfloat16().to(dev)
     dy = torch.randn(rows, D_MODEL, generator=g).bfloat16().to(dev)
@@ -62,7 +70,7 @@ def main() -> int:
             ts.append(e0.elapsed_time(e1) * 1e3)
         return statistics.median(ts)
 
-    out = {"n_gpus": world, "tokens": TOKENS, "d_model": D_MODEL, "d_ff": D_FF}
+    out = {"n_gpus": world, "shard_of": shard_of, "tokens": TOKENS, "d_model": D_MODEL, "d_ff": D_FF}
     if world > 1:
         op = FusedTPFFN(ctx.heap, TOKENS, D_MODEL, D_FF)
 
@@ -129,7 +137,7 @@ def main() -> int:
     remote = (world - 1) / world
     ag_bytes = rows * D_MODEL * 2 * (world - 1)                 # this rank's shard stored into every peer
     rs_bytes = TOKENS * D_MODEL * 2 * remote                    # partial tiles stored to their owners
-    flops = 3 * (2 * TOKENS * D_MODEL * 2 * D_FF + 2 * TOKENS * D_FF * D_MODEL) / world
+    flops = 3 * (2 * TOKENS * D_MODEL * 2 * D_FF + 2 * TOKENS * D_FF * D_MODEL) / shard_of
     from mesh_b200.config import capacity
     peak = capacity().get("bf16_tflops_sustained", 1382.0)
     out["link"] = {"all_gather_bytes_per_launch": int(ag_bytes), "reduce_scatter_bytes_per_launch": int(rs_bytes),

@@ -1,6 +1,7 @@
 // C ABI of the decode-time kernels: skinny fused linear layers, split-KV attention for one query
 // token per sequence, and vocabulary-parallel greedy selection.
 #pragma once
+#include <stddef.h>
 #include <stdint.h>
 #ifdef __cplusplus
 extern "C" {
@@ -46,6 +47,39 @@ int mesh_decode_attention_scratch_floats(int B, int q_heads, int head_dim, int s
 // step (device word, may be NULL): the exchange's sequence number is *step + 1 and the kernel increments *step.
 int mesh_decode_argmax(const float* logits, long long ldl, int B, int vocab_local, int vocab_offset, int* tokens_out,
                        int* pos, int rank, int world, void* const* xchg, uint32_t* step, void* status, void* stream);
+
+// A whole decode step as ONE cooperative kernel: the operations run in order, every CTA of the grid takes its share of
+// each, and a grid barrier separates them (the first weights of a layer are requested before its barrier is waited
+// on, so HBM keeps streaming across layers).  The results are those of the stand-alone launches, bit for bit.
+enum MeshDecodeOpKind { MESH_DEC_OP_EMBED = 0, MESH_DEC_OP_LINEAR = 1, MESH_DEC_OP_ATTENTION = 2, MESH_DEC_OP_ARGMAX = 3 };
+
+typedef struct MeshDecodeOp {
+  int kind;
+  MeshDecodeLinear lin;                                  // LINEAR
+  // ATTENTION: arguments of mesh_decode_attention with one query token per sequence
+  const void* q; const void* k_cache; const void* v_cache; const int* pos; void* att_out; float* scratch; int* counters;
+  int B, q_heads, kv_heads, head_dim, max_seq, window; float scale; int splits;
+  // EMBED: x[b, :] = table[tok[b], :]  (bf16 rows of d_model, a multiple of 8)
+  const void* table; const int* tok; void* x; int d_model;
+  // ARGMAX: arguments of mesh_decode_argmax; part_v / part_i: scratch for batch * mesh_decode_step_max_grid() pairs
+  const float* logits; long long ldl; int vocab_local, vocab_offset; int* tokens_out; int* pos_inc; int rank, world;
+  void* xchg[MESH_DEC_MAX_RANKS]; uint32_t* step; float* part_v; int* part_i;
+  void* status;
+} MeshDecodeOp;
+
+// Bytes of device memory that hold the translated operations of a step of n_ops operations.
+size_t mesh_decode_step_bytes(int n_ops);
+// Largest grid a step kernel is launched with on this device.
+int mesh_decode_step_max_grid(void);
+// Checks and translates the operations into dev_ops (a synchronous copy); returns the device operation count, the grid
+// and the dynamic shared memory the step needs.
+int mesh_decode_step_prepare(const MeshDecodeOp* ops, int n_ops, void* dev_ops, size_t dev_bytes, int* n_dev, int* grid,
+                             int* smem);
+// One step.  barrier: two zeroed 32-bit words that belong to this step program (left consistent by every run that
+// did not time out inside the barrier itself).  trace (may be NULL): 2 * 3 * n_dev 64-bit words; the first and the last
+// CTA write {start, end of own share, nanoseconds spent waiting} (globaltimer) for every operation.
+int mesh_decode_step_run(const void* dev_ops, int n_dev, uint32_t* barrier, void* status, int grid, int smem,
+                         unsigned long long* trace, void* stream);
 
 #ifdef __cplusplus
 }

@@ -145,7 +145,7 @@ class E2BDecoder:
         """Enqueue one token for every sequence (reads self.tok / self.pos, writes them back)."""
         c = self.cfg
         x, x1 = self.x
-        torch.index_select(self.emb, 0, self.tok, out=x)
+        D.decode_embed(self.emb, self.tok, x)
         import os
         # measured on a B200: asking for whole next matrices (tens of MB) while the current one streams halves the
         # decode rate (the lines are evicted again before they are used and cross HBM twice); off unless switched on,
@@ -241,8 +241,41 @@ class E2BDecoder:
         return self.tok.clone()
 
     # ------------------------------------------------------------------ decode
-    def capture(self):
-        """Record one decode step in a CUDA graph (after a warm-up step on a side stream)."""
+    def weight_bytes(self) -> int:
+        """Bytes of weights (codes and scales when quantised) one decode step reads on this rank."""
+        n = 0
+        for L in self.layers:
+            for k in ("wqkv", "wo", "wgu", "wd"):
+                if (k + "_q") in L and self.quant in ("w4", "w8"):
+                    n += L[k + "_q"].numel() + L[k + "_s"].numel() * 2
+                else:
+                    n += L[k].numel() * 2
+        if self.quant in ("w4", "w8"):
+            n += self.lm_q.numel() + self.lm_s.numel() * 2
+        else:
+            n += self.lm_head.numel() * 2
+        return n
+
+    def step_kernel_fits(self) -> bool:
+        """Whether the whole step can run as one cooperative kernel (``ops/decode.py::DecodeStep``)."""
+        return self.qh // self.kvh <= 4
+
+    def capture(self, mode: str | None = None):
+        """Prepare the decode step for replay.  ``mode``: ``"step"``: the whole step as one cooperative kernel;
+        ``"graph"``: the step's launches recorded in a CUDA graph (after a warm-up step on a side stream).
+        Default: ``MESH_DECODE_MODE``, else ``"step"`` where the model fits it."""
+        import os
+        mode = mode or os.environ.get("MESH_DECODE_MODE") or ("step" if self.step_kernel_fits() else "graph")
+        if mode not in ("step", "graph"):
+            raise ValueError(f"decode mode {mode!r}: 'step' or 'graph'")
+        self.mode = mode
+        if mode == "step":
+            saved = (self.pos.clone(), self.tok.clone(), self.step.clone())
+            with D.record_step(self.dev) as st:
+                self._decode_step()
+            self.stepk, self.graph = st, None
+            return saved
+        self.stepk = None
         s = torch.cuda.Stream(device=self.dev)
         s.wait_stream(torch.cuda.current_stream())
         saved = (self.pos.clone(), self.tok.clone(), self.step.clone())
@@ -260,24 +293,29 @@ class E2BDecoder:
 
     def decode(self, steps: int, record: bool = True) -> torch.Tensor:
         """Greedy-decode ``steps`` tokens per sequence by replaying the captured step."""
-        if self.graph is None:
+        if self.graph is None and getattr(self, "stepk", None) is None:
             raise RuntimeError("call capture() first")
         for i in range(steps):
-            self.graph.replay()
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self.stepk.run()
             if record:
                 self.out_tokens[i].copy_(self.tok)
         return self.out_tokens[:steps]
 
 
 def bench_decode(ctx, steps: int = 256, prompt_len: int = 512, configs=(("bf16", 1), ("bf16", 8), ("w4", 1), ("w4", 8), ("w8", 1), ("w8", 8)),
-                 cfg: E2BConfig | None = None) -> dict:
-    """Decode tokens/s (whole job: batch * steps / time), device-timed, max over ranks."""
+                 cfg: E2BConfig | None = None, mode: str | None = None) -> dict:
+    """Decode tokens/s (whole job: batch * steps / time), device-timed, max over ranks.  ``mode``: how the step is
+    replayed (``E2BDecoder.capture``)."""
     import torch.distributed as dist
     cfg = cfg or E2BConfig()
     res = {"model": "E2B-class decoder (30L, d2048, 8q/2kv x256, GeGLU 8192, SWA 512 4:1, vocab 262144 tied)",
            "prompt": prompt_len, "decode_steps": steps, "tp": ctx.world, "runs": []}
     if ctx.world > 1:
         _ = ctx.comm                      # allocated before the mark below, so it outlives the per-run release
+    from ..config import capacity
     from ..runtime.monitor import ErrorMonitor
     from ..utils.status import check_status, clear_abort
     for quant, B in configs:
@@ -293,7 +331,7 @@ def bench_decode(ctx, steps: int = 256, prompt_len: int = 512, configs=(("bf16",
         prompt = torch.randint(0, cfg.vocab, (B, prompt_len), generator=g, dtype=torch.int32).to(ctx.device)
         m.prefill(prompt)
         torch.cuda.synchronize()
-        saved = m.capture()
+        saved = m.capture(mode)
         # the warm-up and capture advanced nothing visible except pos/tok/step of the warm-up step: restore
         m.pos.copy_(saved[0]); m.tok.copy_(saved[1])
         if ctx.world > 1:
@@ -332,8 +370,10 @@ def bench_decode(ctx, steps: int = 256, prompt_len: int = 512, configs=(("bf16",
             clear_abort(ctx.device)
             check_status(ctx.device)
             raise RuntimeError("decode: another rank reported a device-side failure")
-        res["runs"].append({"weights": quant, "batch": B, "ms_per_token": round(ms / steps, 4),
-                            "tokens_per_s": round(B * steps / (ms * 1e-3), 1)})
+        res["runs"].append({"weights": quant, "batch": B, "mode": m.mode, "ms_per_token": round(ms / steps, 4),
+                            "tokens_per_s": round(B * steps / (ms * 1e-3), 1), "weight_bytes": m.weight_bytes(),
+                            "frac_of_weight_streaming_bound": round(m.weight_bytes() / (capacity().get("hbm_gbs", 6650.0) * 1e9)
+                                                                    / (ms / steps * 1e-3), 3)})
         del m
         torch.cuda.empty_cache()
         if mark is not None:

@@ -40,6 +40,139 @@ class _Lin(ctypes.Structure):
     ]
 
 
+class _Op(ctypes.Structure):
+    """``MeshDecodeOp``: one operation of a step program (``csrc/ops/decode_api.h``)."""
+    _fields_ = [
+        ("kind", c_int), ("lin", _Lin),
+        ("q", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("pos", c_void_p), ("att_out", c_void_p),
+        ("scratch", c_void_p), ("counters", c_void_p),
+        ("B", c_int), ("q_heads", c_int), ("kv_heads", c_int), ("head_dim", c_int), ("max_seq", c_int), ("window", c_int),
+        ("scale", c_float), ("splits", c_int),
+        ("table", c_void_p), ("tok", c_void_p), ("x", c_void_p), ("d_model", c_int),
+        ("logits", c_void_p), ("ldl", c_longlong), ("vocab_local", c_int), ("vocab_offset", c_int),
+        ("tokens_out", c_void_p), ("pos_inc", c_void_p), ("rank", c_int), ("world", c_int),
+        ("xchg", c_void_p * MAX_RANKS), ("step", c_void_p), ("part_v", c_void_p), ("part_i", c_void_p),
+        ("status", c_void_p),
+    ]
+
+
+OP_EMBED, OP_LINEAR, OP_ATTENTION, OP_ARGMAX = 0, 1, 2, 3
+_recording: list | None = None           # operations of the step being recorded (``record_step``)
+
+
+class DecodeStep:
+    """A decode step as one cooperative kernel.  Record the step's calls once::
+
+        with record_step(device) as step:
+            model._decode_step()          # decode_embed / decode_linear / DecodeAttention / decode_argmax calls
+        step.run()                        # every later token: one launch
+
+    Inside the block the calls launch nothing; they describe the operations, which ``run`` executes in that order with a
+    grid barrier between them.  The tensors the calls named are kept alive by the step and must keep their addresses."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.ops: list = []
+        self.keep: list = []
+        self.dev_ops = None
+        self.n_dev = self.grid = self.smem = 0
+
+    def __enter__(self):
+        global _recording
+        if _recording is not None:
+            raise RuntimeError("a decode step is already being recorded")
+        _recording = self.ops
+        return self
+
+    def __exit__(self, et, ev, tb):
+        global _recording
+        _recording = None
+        if et is None:
+            self._prepare()
+        return False
+
+    def _prepare(self):
+        L = _native.lib()
+        n = len(self.ops)
+        if n == 0:
+            raise RuntimeError("record_step: the block made no decode call")
+        arr = (_Op * n)()
+        max_grid = int(L.mesh_decode_step_max_grid())
+        for i, (op, keep) in enumerate(self.ops):
+            if op.kind == OP_ARGMAX:
+                pv = torch.empty(op.B * max_grid, dtype=torch.float32, device=self.device)
+                pi = torch.empty(op.B * max_grid, dtype=torch.int32, device=self.device)
+                op.part_v, op.part_i = pv.data_ptr(), pi.data_ptr()
+                self.keep += [pv, pi]
+            ctypes.memmove(ctypes.byref(arr, i * ctypes.sizeof(_Op)), ctypes.byref(op), ctypes.sizeof(_Op))
+            self.keep.append(keep)
+        L.mesh_decode_step_bytes.restype = ctypes.c_size_t
+        nbytes = int(L.mesh_decode_step_bytes(c_int(n)))
+        self.dev_ops = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.barrier = torch.zeros(2, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        n_dev, grid, smem = c_int(0), c_int(0), c_int(0)
+        rc = L.mesh_decode_step_prepare(arr, c_int(n), c_void_p(self.dev_ops.data_ptr()), ctypes.c_size_t(nbytes),
+                                        ctypes.byref(n_dev), ctypes.byref(grid), ctypes.byref(smem))
+        _native.check(rc, "mesh_decode_step_prepare")
+        self.n_dev, self.grid, self.smem = n_dev.value, grid.value, smem.value
+        self.status = status_block(self.device)
+
+    def run(self, trace: torch.Tensor | None = None):
+        """One step.  ``trace``: an int64 tensor of ``2 * 3 * n_dev`` words on the device; the first and the last CTA
+        write {start, end of own share, nanoseconds waited} per operation (see :meth:`timeline`)."""
+        rc = _native.lib().mesh_decode_step_run(c_void_p(self.dev_ops.data_ptr()), c_int(self.n_dev),
+                                                c_void_p(self.barrier.data_ptr()), c_void_p(self.status.data_ptr()),
+                                                c_int(self.grid), c_int(self.smem), c_void_p(_p(trace)), _stream())
+        _native.check(rc, "mesh_decode_step_run")
+        _native.count_launch()
+
+    def kinds(self) -> list[str]:
+        """Name of every device operation of the step, in order."""
+        names = []
+        for op, _ in self.ops:
+            if op.kind == OP_LINEAR:
+                names.append(("linear", "glu", "qkv", "linear+allreduce")[op.lin.mode] + f" {op.lin.N}x{op.lin.K}")
+            elif op.kind == OP_ATTENTION:
+                names.append("attention")
+            elif op.kind == OP_EMBED:
+                names.append("embed")
+            else:
+                names += ["argmax slices", "argmax merge"]
+        return names
+
+    def timeline(self) -> list[dict]:
+        """Runs one step with the trace on and returns, per operation, microseconds from the step's start to the
+        operation's start and end on the first CTA, and the microseconds the first and the last CTA waited at the
+        barrier before it."""
+        t = torch.zeros(2 * 3 * self.n_dev, dtype=torch.int64, device=self.device)
+        self.run(trace=t)
+        torch.cuda.synchronize(self.device)
+        v = t.cpu().view(2, self.n_dev, 3)
+        t0 = int(v[0, 0, 0])
+        return [{"op": name, "start_us": (int(v[0, i, 0]) - t0) / 1e3, "end_us": (int(v[0, i, 1]) - t0) / 1e3,
+                 "waited_us": int(v[0, i, 2]) / 1e3, "last_cta_end_us": (int(v[1, i, 1]) - t0) / 1e3,
+                 "last_cta_waited_us": int(v[1, i, 2]) / 1e3}
+                for i, name in enumerate(self.kinds())]
+
+
+def record_step(device="cuda") -> DecodeStep:
+    return DecodeStep(device)
+
+
+def decode_embed(table: torch.Tensor, tok: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[b, :] = table[tok[b], :]`` (bf16 rows): the step's first operation."""
+    if _recording is not None:
+        op = _Op()
+        op.kind = OP_EMBED
+        op.table, op.tok, op.x, op.B, op.d_model = table.data_ptr(), tok.data_ptr(), out.data_ptr(), tok.shape[0], table.shape[1]
+        if not (out.is_contiguous() and table.is_contiguous() and table.dtype == torch.bfloat16):
+            raise ValueError("decode_embed: contiguous bf16 table and output")
+        _recording.append((op, (table, tok, out)))
+        return out
+    return torch.index_select(table, 0, tok, out=out)
+
+
 def quantize_w4(w: torch.Tensor, group: int = 64):
     """``w [N, K]`` -> ``(codes uint8 [N, K/2] in the kernel's packing, scales fp16 [N, K/group])``."""
     assert group == 64 and w.dim() == 2 and w.shape[1] % 64 == 0
@@ -138,6 +271,12 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, *, scales: torch.Tensor | No
         import os
         cap = int(float(os.environ.get("MESH_DECODE_PREFETCH_MB", "8")) * (1 << 20))
         d.next_bytes = min(next_weights.numel() * next_weights.element_size(), cap)
+    if _recording is not None:
+        op = _Op()
+        op.kind = OP_LINEAR
+        op.lin = d
+        _recording.append((op, (x, w, scales, norm_w, out, residual, qkv, ar)))
+        return out
     rc = _native.lib().mesh_decode_linear(ctypes.byref(d), _stream())
     _native.check(rc, "mesh_decode_linear")
     _native.count_launch()
@@ -157,6 +296,18 @@ class DecodeAttention:
 
     def __call__(self, q, k_cache, v_cache, pos, out, window: int = 0, scale: float | None = None):
         scale = self.hd ** -0.5 if scale is None else scale
+        if _recording is not None:
+            if self.T != 1:
+                raise ValueError("a recorded step decodes one token per sequence")
+            op = _Op()
+            op.kind = OP_ATTENTION
+            op.q, op.k_cache, op.v_cache, op.pos, op.att_out = (q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                                pos.data_ptr(), out.data_ptr())
+            op.scratch, op.counters = self.scratch.data_ptr(), self.counters.data_ptr()
+            op.B, op.q_heads, op.kv_heads, op.head_dim, op.max_seq = self.B, self.qh, self.kvh, self.hd, k_cache.shape[-2]
+            op.window, op.scale, op.splits = window, scale, self.splits
+            _recording.append((op, (q, k_cache, v_cache, pos, out, self)))
+            return out
         rc = _native.lib().mesh_decode_attention(
             c_void_p(q.data_ptr()), c_void_p(k_cache.data_ptr()), c_void_p(v_cache.data_ptr()), c_void_p(pos.data_ptr()),
             c_void_p(out.data_ptr()), c_void_p(self.scratch.data_ptr()), c_void_p(self.counters.data_ptr()),
@@ -170,6 +321,16 @@ class DecodeAttention:
 def decode_argmax(logits: torch.Tensor, tokens_out: torch.Tensor, pos: torch.Tensor | None, vocab_offset: int = 0,
                   rank: int = 0, world: int = 1, xchg_ptrs: list[int] | None = None, step: torch.Tensor | None = None):
     B, V = logits.shape
+    if _recording is not None:
+        op = _Op()
+        op.kind = OP_ARGMAX
+        op.logits, op.ldl, op.B, op.vocab_local, op.vocab_offset = logits.data_ptr(), logits.stride(0), B, V, vocab_offset
+        op.tokens_out, op.pos_inc, op.rank, op.world = tokens_out.data_ptr(), _p(pos), rank, world
+        for r, ptr in enumerate(xchg_ptrs or []):
+            op.xchg[r] = ptr
+        op.step, op.status = _p(step), status_block(logits.device).data_ptr()
+        _recording.append((op, (logits, tokens_out, pos, step)))
+        return tokens_out
     arr = (c_void_p * MAX_RANKS)(*([c_void_p(p) for p in (xchg_ptrs or [])] + [c_void_p(0)] * (MAX_RANKS - len(xchg_ptrs or []))))
     rc = _native.lib().mesh_decode_argmax(c_void_p(logits.data_ptr()), c_longlong(logits.stride(0)), c_int(B), c_int(V),
                                           c_int(vocab_offset), c_void_p(tokens_out.data_ptr()), c_void_p(_p(pos)),

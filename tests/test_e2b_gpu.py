@@ -69,8 +69,9 @@ def _rel(a, b):
     return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
 
 
+@pytest.mark.parametrize("mode", ["step", "graph"])
 @pytest.mark.parametrize("quant", ["bf16", "w4", "w8"])
-def test_e2b_solo_matches_reference(quant):
+def test_e2b_solo_matches_reference(quant, mode):
     from mesh_b200.models.e2b import E2BDecoder
     from mesh_b200.utils.status import check_status
     cfg = _small_cfg()
@@ -80,7 +81,7 @@ def test_e2b_solo_matches_reference(quant):
     m.prefill(prompt)
     assert _rel(m.logits, _ref_logits(m, prompt)) < 0.05
     seq = torch.cat([prompt, m.tok[:, None]], 1)
-    m.capture()
+    m.capture(mode)
     m.pos.fill_(T); m.tok.copy_(seq[:, -1])
     for _ in range(steps):
         m.decode(1)
@@ -89,6 +90,33 @@ def test_e2b_solo_matches_reference(quant):
         seq = torch.cat([seq, m.tok[:, None]], 1)        # follow the kernel's own greedy choice
     check_status()
     assert m.pos.tolist() == [T + steps] * B
+
+
+@pytest.mark.parametrize("quant,B", [("bf16", 1), ("bf16", 8), ("w4", 3), ("w8", 8)])
+def test_step_kernel_equals_separate_launches(quant, B):
+    """The whole step as one cooperative kernel runs the same layer bodies as the separate launches: same logits and
+    tokens, bit for bit, token after token."""
+    from mesh_b200.models.e2b import E2BDecoder
+    from mesh_b200.utils.status import check_status
+    cfg = _small_cfg()
+    T, steps = 20, 8
+    prompt = torch.randint(0, cfg.vocab, (B, T), dtype=torch.int32, device="cuda")
+    runs = []
+    for mode in ("graph", "step"):
+        m = E2BDecoder(cfg, _solo_ctx(), B, quant)
+        first = m.prefill(prompt)
+        m.capture(mode)                      # the graph form runs a warm-up step: put the state back
+        m.pos.fill_(T - 1); m.tok.copy_(first)
+        step0 = int(m.step[0])
+        logits = []
+        for _ in range(steps):
+            m.decode(1)
+            logits.append(m.logits.clone())
+        toks = m.decode(4).clone()
+        check_status()
+        runs.append((torch.stack(logits), toks, m.pos.clone(), torch.tensor(int(m.step[0]) - step0)))
+    for a, b in zip(runs[0], runs[1]):
+        assert torch.equal(a, b)
 
 
 def _tp_rank(rank, world, rdv):
