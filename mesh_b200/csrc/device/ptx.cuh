@@ -130,6 +130,14 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// ----------------------------------------------------------------------------- bulk copies (no tensor map)
+// Global -> this CTA's shared memory, completion counted in bytes on an mbarrier.  Both addresses 16-byte aligned,
+// the size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
 // ----------------------------------------------------------------------------- TMA
 // Plain tiled loads/stores.  The innermost coordinate times the element size must
 // be a multiple of 16 bytes (callers only pass tile-aligned coordinates).

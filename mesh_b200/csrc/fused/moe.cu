@@ -52,38 +52,74 @@ __device__ __forceinline__ bool ll_load(const uint2* p, uint32_t seq, uint32_t& 
 }
 
 // ------------------------------------------------------------------------------------------- count
-// One block per expert: slot[i] = number of earlier entries (token order) routed to the same expert.
-__global__ void __launch_bounds__(1024)
+// slot[i] = number of earlier entries (token order) routed to the same expert.  A block ranks a chunk of 1024 entries
+// (lanes that chose the same expert find each other with a match, warps are ordered through a small table in shared
+// memory) and leaves the chunk's histogram in `work`; the block that finishes last turns the histograms into each
+// chunk's starting slot per expert, adds them to the slots, and pushes the totals to every rank.
+constexpr int COUNT_CHUNK = 1024;
+
+__global__ void __launch_bounds__(COUNT_CHUNK)
 moe_count_kernel(const int* __restrict__ idx, int n_entries, int* __restrict__ slot, int experts, int rank, int world,
-                 uint2* c0, uint2* c1, uint2* c2, uint2* c3, uint2* c4, uint2* c5, uint2* c6, uint2* c7, uint32_t seq) {
-  const int e = blockIdx.x;
-  __shared__ int warp_tot[32];
-  __shared__ int running;
-  if (threadIdx.x == 0) running = 0;
-  __syncthreads();
+                 int* __restrict__ work, uint2* c0, uint2* c1, uint2* c2, uint2* c3, uint2* c4, uint2* c5, uint2* c6,
+                 uint2* c7, uint32_t seq) {
+  __shared__ int cnt[32][MAX_E];            // [warp][expert]: entries of the warp, then entries of the warps before it
+  __shared__ int last_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int base = 0; base < n_entries; base += 1024) {
-    const int i = base + threadIdx.x;
-    const bool hit = i < n_entries && idx[i] == e;
-    const unsigned b = __ballot_sync(0xffffffffu, hit);
-    if (lane == 0) warp_tot[warp] = __popc(b);
-    __syncthreads();
-    int before = 0;
-    for (int w = 0; w < warp; ++w) before += warp_tot[w];
-    if (hit) slot[i] = running + before + __popc(b & ((1u << lane) - 1u));
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int tot = 0;
-      for (int w = 0; w < 32; ++w) tot += warp_tot[w];
-      running += tot;
+  const int chunks = gridDim.x;
+  int* hist = work;                         // [chunks][experts]
+  int* done = work + (long long)chunks * experts;
+  for (int j = threadIdx.x; j < 32 * MAX_E; j += blockDim.x) (&cnt[0][0])[j] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * COUNT_CHUNK + threadIdx.x;
+  const bool valid = i < n_entries;
+  const int e = valid ? idx[i] : -1 - lane;                                  // invalid lanes match nobody
+  const bool good = valid && e >= 0 && e < experts;
+  const unsigned same = __match_any_sync(0xffffffffu, e);
+  const int in_warp = __popc(same & ((1u << lane) - 1u));
+  if (good && in_warp == 0) cnt[warp][e] = __popc(same);
+  __syncthreads();
+  if ((int)threadIdx.x < experts) {                                          // exclusive scan over the warps
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = cnt[w][threadIdx.x];
+      cnt[w][threadIdx.x] = run;
+      run += c;
     }
-    __syncthreads();
+    hist[(long long)blockIdx.x * experts + threadIdx.x] = run;
   }
-  if (threadIdx.x < world) {
-    uint2* peers[8] = {c0, c1, c2, c3, c4, c5, c6, c7};
-    // count matrix on every rank: [parity][src rank][expert]
-    uint2* p = peers[threadIdx.x] + ((long long)(seq & 1u) * world + rank) * experts + e;
-    ll_store(p, (uint32_t)running, seq);
+  __syncthreads();
+  if (good) slot[i] = cnt[warp][e] + in_warp;
+  else if (valid) slot[i] = 0;
+  // ---- the last block to finish completes the slots
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int d = atomicAdd(done, 1);
+    last_s = (d == chunks - 1);
+    if (last_s) *done = 0;                                                   // ready for the next launch
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  if ((int)threadIdx.x < experts) {
+    int run = 0;
+    for (int c = 0; c < chunks; ++c) {
+      int* h = hist + (long long)c * experts + threadIdx.x;
+      const int n = __ldcg(h);
+      *h = run;
+      run += n;
+    }
+    if (world > 0) {
+      uint2* peers[8] = {c0, c1, c2, c3, c4, c5, c6, c7};
+      // count matrix on every rank: [parity][src rank][expert]
+      for (int r = 0; r < world; ++r)
+        ll_store(peers[r] + ((long long)(seq & 1u) * world + rank) * experts + threadIdx.x, (uint32_t)run, seq);
+    }
+  }
+  __syncthreads();
+  for (int j = COUNT_CHUNK + (int)threadIdx.x; j < n_entries; j += COUNT_CHUNK) {   // chunk 0 starts at slot 0
+    const int ej = idx[j];
+    if (ej >= 0 && ej < experts) slot[j] = __ldcg(slot + j) + hist[(long long)(j / COUNT_CHUNK) * experts + ej];
   }
 }
 
@@ -156,33 +192,49 @@ __global__ void __launch_bounds__(512) moe_plan_kernel(const PlanArgs a) {
     }
     a.layout[3 * El] = total;
     a.layout[3 * El + 1] = dropped;
-    // ---- tile tables (pair tiles: 256 output rows each)
-    const int D = a.d_model, F = a.d_ff;
-    int n0 = 0, n1 = 0, n2 = 0, n3 = 0, n4 = 0, n5 = 0;
+  }
+  __syncthreads();
+  // ---- tile tables (pair tiles: 256 output rows each).  Table t of expert el holds cnt[t][el] descriptors starting at
+  // off[t][el]; thread 0 lays the offsets out (6 x local experts additions), then every warp writes the descriptors of
+  // its experts, a lane per tile: the tables are thousands of 32-byte records, far too many for one thread.
+  __shared__ int off[6][MAX_E + 1];
+  const int D = a.d_model, F = a.d_ff;
+  const int ntn[6] = {(F + 127) / 128, (D + 255) / 256, (F + 255) / 256, (D + 255) / 256, (F + 255) / 256, (D + 255) / 256};
+  const int dw_mt[2] = {(D + 255) / 256, (2 * F + 255) / 256};
+  if (threadIdx.x < 6) {
+    const int t = threadIdx.x;
+    int n = 0;
     for (int el = 0; el < El; ++el) {
-      const int mt_n = pad_loc[el] / 256;
-      for (int mt = 0; mt < mt_n; ++mt) {
-        const int row = base_loc[el] + mt * 256;
-        for (int nt = 0; nt < (F + 127) / 128 && n0 < a.max_tiles; ++nt)       // h = act(x W1g^T) * (x W1u^T)
-          a.t_glu[n0++] = MeshTileDesc{row, 0, D / 64, el * 2 * F + nt * 128, 0, row, nt * 128, 0};
-        for (int nt = 0; nt < (D + 255) / 256 && n1 < a.max_tiles; ++nt)       // y = h W2^T
-          a.t_down[n1++] = MeshTileDesc{row, 0, F / 64, el * D + nt * 256, 0, row, nt * 256, 0};
-        for (int nt = 0; nt < (F + 255) / 256 && n2 < a.max_tiles; ++nt)       // dH = dY W2   (W2 stacked [El*D, F], MN-major)
-          a.t_dh[n2++] = MeshTileDesc{row, 0, D / 64, nt * 256, el * D, row, nt * 256, 0};
-        for (int nt = 0; nt < (D + 255) / 256 && n3 < a.max_tiles; ++nt)       // dX = dGU W1  (W1 stacked [El*2F, D], MN-major)
-          a.t_dx[n3++] = MeshTileDesc{row, 0, (2 * F) / 64, nt * 256, el * 2 * F, row, nt * 256, 0};
-      }
-      const int kb = pad_loc[el] / 64;
-      if (kb > 0) {
-        for (int mt = 0; mt < (D + 255) / 256; ++mt)                            // dW2[el] = dY^T h      [D, F]
-          for (int nt = 0; nt < (F + 255) / 256 && n4 < a.max_tiles; ++nt)
-            a.t_dw2[n4++] = MeshTileDesc{mt * 256, base_loc[el], kb, nt * 256, 0, el * D + mt * 256, nt * 256, 0};
-        for (int mt = 0; mt < (2 * F + 255) / 256; ++mt)                        // dW1[el] = dGU^T x     [2F, D]
-          for (int nt = 0; nt < (D + 255) / 256 && n5 < a.max_tiles; ++nt)
-            a.t_dw1[n5++] = MeshTileDesc{mt * 256, base_loc[el], kb, nt * 256, 0, el * 2 * F + mt * 256, nt * 256, 0};
+      off[t][el] = n;
+      const int rows = pad_loc[el];
+      n += t < 4 ? (rows / 256) * ntn[t] : (rows >= 64 ? dw_mt[t - 4] * ntn[t] : 0);
+    }
+    off[t][El] = n;
+    a.n_tiles[t] = min(n, a.max_tiles);
+  }
+  __syncthreads();
+  MeshTileDesc* const tab[6] = {a.t_glu, a.t_down, a.t_dh, a.t_dx, a.t_dw2, a.t_dw1};
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int el = warp; el < El; el += nwarps) {
+    const int base = base_loc[el], kb = pad_loc[el] / 64;
+#pragma unroll
+    for (int t = 0; t < 6; ++t) {
+      const int cnt = off[t][el + 1] - off[t][el];
+      for (int j = lane; j < cnt; j += 32) {
+        const int at = off[t][el] + j;
+        if (at >= a.max_tiles) break;
+        const int mt = j / ntn[t], nt = j - mt * ntn[t];
+        const int row = base + mt * 256;
+        MeshTileDesc d;
+        if (t == 0) d = MeshTileDesc{row, 0, D / 64, el * 2 * F + nt * 128, 0, row, nt * 128, 0};            // h = act(x W1g^T) * (x W1u^T)
+        else if (t == 1) d = MeshTileDesc{row, 0, F / 64, el * D + nt * 256, 0, row, nt * 256, 0};           // y = h W2^T
+        else if (t == 2) d = MeshTileDesc{row, 0, D / 64, nt * 256, el * D, row, nt * 256, 0};               // dH = dY W2   (W2 stacked [El*D, F], MN-major)
+        else if (t == 3) d = MeshTileDesc{row, 0, (2 * F) / 64, nt * 256, el * 2 * F, row, nt * 256, 0};     // dX = dGU W1  (W1 stacked [El*2F, D], MN-major)
+        else if (t == 4) d = MeshTileDesc{mt * 256, base, kb, nt * 256, 0, el * D + mt * 256, nt * 256, 0};  // dW2[el] = dY^T h   [D, F]
+        else d = MeshTileDesc{mt * 256, base, kb, nt * 256, 0, el * 2 * F + mt * 256, nt * 256, 0};          // dW1[el] = dGU^T x  [2F, D]
+        tab[t][at] = d;
       }
     }
-    a.n_tiles[0] = n0; a.n_tiles[1] = n1; a.n_tiles[2] = n2; a.n_tiles[3] = n3; a.n_tiles[4] = n4; a.n_tiles[5] = n5;
   }
 }
 
@@ -331,13 +383,19 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const CombineArgs a) {
 using namespace mesh;
 using namespace mesh::moe;
 
+extern "C" int mesh_moe_count_work_ints(int n_entries, int experts) {
+  return (n_entries + COUNT_CHUNK - 1) / COUNT_CHUNK * experts + 1;
+}
+
 extern "C" int mesh_moe_count(const int* idx, int n_entries, int* slot, int experts, int rank, int world,
-                              void* const* count_ptrs, uint32_t seq, void* stream) {
+                              void* const* count_ptrs, uint32_t seq, int* work, void* stream) {
   if (experts > MAX_E || world > R || experts % world) return set_error(-2, "moe_count: experts <= %d, divisible by world <= %d", MAX_E, R);
+  if (n_entries < 1 || work == nullptr) return set_error(-2, "moe_count: no entries or no work buffer");
   uint2* c[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   for (int r = 0; r < world; ++r) c[r] = (uint2*)count_ptrs[r];
-  moe_count_kernel<<<experts, 1024, 0, (cudaStream_t)stream>>>(idx, n_entries, slot, experts, rank, world, c[0], c[1], c[2],
-                                                               c[3], c[4], c[5], c[6], c[7], seq);
+  const int chunks = (n_entries + COUNT_CHUNK - 1) / COUNT_CHUNK;
+  moe_count_kernel<<<chunks, COUNT_CHUNK, 0, (cudaStream_t)stream>>>(idx, n_entries, slot, experts, rank, world, work, c[0],
+                                                                     c[1], c[2], c[3], c[4], c[5], c[6], c[7], seq);
   MESH_CUDA_OK(cudaGetLastError());
   return 0;
 }

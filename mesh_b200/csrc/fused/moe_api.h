@@ -11,8 +11,11 @@ extern "C" {
 
 // idx int32 [n_entries] (token-major, k choices per token) -> slot[n_entries]; this rank's histogram is pushed to
 // every rank's count matrix (count_ptrs[d]: uint2 [2][world][experts]).
+// work: int32 [mesh_moe_count_work_ints(n_entries, experts)], zero before the first call (the kernel leaves its
+// counter zero).
+int mesh_moe_count_work_ints(int n_entries, int experts);
 int mesh_moe_count(const int* idx, int n_entries, int* slot, int experts, int rank, int world, void* const* count_ptrs,
-                   uint32_t seq, void* stream);
+                   uint32_t seq, int* work, void* stream);
 
 typedef struct MeshMoePlan {
   const void* counts; uint32_t seq;

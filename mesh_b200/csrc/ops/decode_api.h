@@ -48,9 +48,10 @@ int mesh_decode_attention_scratch_floats(int B, int q_heads, int head_dim, int s
 int mesh_decode_argmax(const float* logits, long long ldl, int B, int vocab_local, int vocab_offset, int* tokens_out,
                        int* pos, int rank, int world, void* const* xchg, uint32_t* step, void* status, void* stream);
 
-// A whole decode step as ONE cooperative kernel: the operations run in order, every CTA of the grid takes its share of
-// each, and a grid barrier separates them (the first weights of a layer are requested before its barrier is waited
-// on, so HBM keeps streaming across layers).  The results are those of the stand-alone launches, bit for bit.
+// A whole decode step as ONE cooperative kernel: the operations run in order, every CTA of the grid (one per SM) takes
+// its share of each, and a grid barrier separates them.  In every CTA one warp streams the weights of all the layers,
+// in order, through a ring of stages in shared memory; it never waits at a barrier, so HBM keeps streaming while the
+// computing warps wait for the layer before, stage x, reduce and store.
 enum MeshDecodeOpKind { MESH_DEC_OP_EMBED = 0, MESH_DEC_OP_LINEAR = 1, MESH_DEC_OP_ATTENTION = 2, MESH_DEC_OP_ARGMAX = 3 };
 
 typedef struct MeshDecodeOp {
@@ -67,18 +68,26 @@ typedef struct MeshDecodeOp {
   void* status;
 } MeshDecodeOp;
 
+// How a prepared step is launched: filled by mesh_decode_step_prepare, passed back to mesh_decode_step_run.
+typedef struct MeshDecodeStepPlan {
+  int n_dev;          // device operations (a selection is two)
+  int grid;           // CTAs: one per SM
+  int smem;           // dynamic shared memory per CTA
+  int ring_off;       // bytes of per-layer work area in front of the weight ring
+  int slot_bytes;     // bytes of one weight stage
+  int n_stages;       // stages of the ring
+} MeshDecodeStepPlan;
+
 // Bytes of device memory that hold the translated operations of a step of n_ops operations.
 size_t mesh_decode_step_bytes(int n_ops);
 // Largest grid a step kernel is launched with on this device.
 int mesh_decode_step_max_grid(void);
-// Checks and translates the operations into dev_ops (a synchronous copy); returns the device operation count, the grid
-// and the dynamic shared memory the step needs.
-int mesh_decode_step_prepare(const MeshDecodeOp* ops, int n_ops, void* dev_ops, size_t dev_bytes, int* n_dev, int* grid,
-                             int* smem);
+// Checks and translates the operations into dev_ops (a synchronous copy) and fills the launch plan.
+int mesh_decode_step_prepare(const MeshDecodeOp* ops, int n_ops, void* dev_ops, size_t dev_bytes, MeshDecodeStepPlan* plan);
 // One step.  barrier: two zeroed 32-bit words that belong to this step program (left consistent by every run that
 // did not time out inside the barrier itself).  trace (may be NULL): 2 * 3 * n_dev 64-bit words; the first and the last
 // CTA write {start, end of own share, nanoseconds spent waiting} (globaltimer) for every operation.
-int mesh_decode_step_run(const void* dev_ops, int n_dev, uint32_t* barrier, void* status, int grid, int smem,
+int mesh_decode_step_run(const void* dev_ops, const MeshDecodeStepPlan* plan, uint32_t* barrier, void* status,
                          unsigned long long* trace, void* stream);
 
 #ifdef __cplusplus

@@ -31,9 +31,12 @@ struct AttArgs {
 };
 
 // One work item (split, kv head, sequence-token b) of the attention; `sm_acc_raw`: ATT_WARPS * group * HD floats of
-// shared memory.  All threads of the CTA call it together; it ends with the CTA's threads in step.
-template <int HD, int MAXG>
-__device__ __forceinline__ void attention_item(const AttArgs& A, int split, int kvh, int b, float* sm_acc_raw) {
+// shared memory.  The ATT_THREADS computing threads call it together (`sync` is their barrier).
+struct AttBlockSync { __device__ __forceinline__ void operator()() const { __syncthreads(); } };
+
+template <int HD, int MAXG, class Sync = AttBlockSync>
+__device__ __forceinline__ void attention_item(const AttArgs& A, int split, int kvh, int b, float* sm_acc_raw,
+                                               Sync sync = Sync{}) {
   constexpr int PER = HD / 32;                       // dims per lane
   constexpr int MAX_GROUP = MAXG;
   // no __restrict__ here: inside a step kernel q and the newest cache row were written by an earlier phase of the
@@ -125,7 +128,7 @@ __device__ __forceinline__ void attention_item(const AttArgs& A, int split, int 
       for (int i = 0; i < PER; ++i) sm_acc(warp, g, lane * PER + i) = acc[g][i];
     }
   }
-  __syncthreads();
+  sync();
   // thread -> (head g, dims d, d + 256/..): 256 threads cover HD dims for one head at a time
   float* part = scratch + (((long long)b * q_heads + kvh * group) * splits + split) * (HD + 2);
   for (int g = 0; g < group; ++g) {
@@ -148,13 +151,13 @@ __device__ __forceinline__ void attention_item(const AttArgs& A, int split, int 
   // ---- the last CTA of this (sequence, kv head) merges the splits
   __shared__ int is_last;
   __threadfence();
-  __syncthreads();
+  sync();
   if (threadIdx.x == 0) {
     const int done = atomicAdd(&counters[b * kv_heads + kvh], 1);
     is_last = (done == splits - 1);
     if (is_last) counters[b * kv_heads + kvh] = 0;      // ready for the next launch
   }
-  __syncthreads();
+  sync();
   if (!is_last) return;
   __threadfence();
   // weights of every (head, split) first — 64 independent loads at most — then the value sums
@@ -166,7 +169,7 @@ __device__ __forceinline__ void attention_item(const AttArgs& A, int split, int 
     const int g = idx / splits, s = idx % splits;
     w_s[g][s] = __ldcg(pbase + ((long long)g * splits + s) * (HD + 2) + HD);          // m of the split
   }
-  __syncthreads();
+  sync();
   if ((int)threadIdx.x < group) {
     const int g = threadIdx.x;
     float mm = -CUDART_INF_F;
@@ -180,7 +183,7 @@ __device__ __forceinline__ void attention_item(const AttArgs& A, int split, int 
     }
     inv_s[g] = ll > 0.f ? 1.f / ll : 0.f;
   }
-  __syncthreads();
+  sync();
   for (int idx = threadIdx.x; idx < group * HD; idx += ATT_THREADS) {
     const int g = idx / HD, d = idx % HD;
     const float* pg = pbase + (long long)g * splits * (HD + 2) + d;

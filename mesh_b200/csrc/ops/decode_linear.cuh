@@ -86,8 +86,15 @@ __device__ __forceinline__ float dec_act(float g, int act) {
   }
 }
 
+// What the weight loads of the main loop read of a layer's arguments, held in registers: the arguments themselves may
+// sit in shared memory (a step kernel), where every barrier would force them to be read again.
+struct LinHot {
+  const void* w; const __half* scales; int K, mode, up_off, head_dim;
+};
+
 // first row of the two 8-row groups a CTA works on
-__device__ __forceinline__ void group_rows(const LinArgs& a, int g, int& rA, int& rB) {
+template <class Args>
+__device__ __forceinline__ void group_rows(const Args& a, int g, int& rA, int& rB) {
   if (a.mode == MESH_DEC_GLU) {
     rA = g * 8;
     rB = a.up_off + g * 8;
@@ -132,7 +139,7 @@ __device__ __forceinline__ void dequant_b4(uint32_t w, float s, uint32_t& lo, ui
 }
 
 template <int W4, int U>
-__device__ __forceinline__ void load_chunk(const LinArgs& a, int grp, int kb, int k_lo, int g8, int t4, Chunk<W4, U>& c) {
+__device__ __forceinline__ void load_chunk(const LinHot& a, int grp, int kb, int k_lo, int g8, int t4, Chunk<W4, U>& c) {
   int rA, rB;
   group_rows(a, grp, rA, rB);
   const int K = a.K;
@@ -243,51 +250,15 @@ __device__ __forceinline__ void mma_chunk(const Chunk<W4, U>& c, const uint8_t* 
   }
 }
 
-// Shared memory a launch needs for a layer of width K and batch B: the staged rows of x plus the K-split partials.
-__host__ __device__ inline size_t lin_smem_bytes(int K, int B) {
-  return (size_t)B * ((size_t)K * 2 + XPAD) + (size_t)(WARPS + 1) * 16 * NB * sizeof(float);
-}
+// Barrier among the threads that compute a layer: the whole CTA of a stand-alone launch.
+struct BlockSync { __device__ __forceinline__ void operator()() const { __syncthreads(); } };
 
-// The whole layer for one CTA of a grid of `gridDim.x` (groups blockIdx.x, blockIdx.x + gridDim.x, ...).
-// `wait_inputs()` is called once, after the first weights have been requested and before x is read: a stand-alone
-// launch waits there for the kernel before it in the stream, a step kernel for the grid barrier of the previous layer.
-// Only the B rows of x that exist are staged; the MMA's batch columns past B repeat row B - 1 and are never stored.
-template <int W4, int U, class Wait>
-__device__ __forceinline__ void linear_body(const LinArgs& a, uint8_t* smem, Wait wait_inputs) {
-  const int K = a.K;
-  const int xstride = K * 2 + a.xpad;                             // bytes per x row
-  uint8_t* xs = smem;                                             // [B][xstride]
-  float* red = reinterpret_cast<float*>(smem + (size_t)a.B * (K * 2 + XPAD));   // [WARPS][16][NB]
-  float* fin = red + WARPS * 16 * NB;                             // [16][NB]
+// The B rows of x -> shared memory, optionally RMS-normalised.  Called by the THREADS computing threads together.
+template <class Sync>
+__device__ __forceinline__ void stage_x(const LinArgs& a, uint8_t* xs, int xstride, Sync sync) {
   __shared__ float rstd_s[NB];
+  const int K = a.K;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g8 = lane >> 2, t4 = lane & 3;
-  constexpr int CH = ChunkK<W4, U>::value;
-  const int kslice = K / WARPS;
-  const int k_lo = warp * kslice;
-  const int chunks = kslice / CH;
-  const int my_groups = (a.n_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int steps = my_groups * chunks;
-
-  // The weights of this layer do not depend on the layer before it, so the first chunk is requested before waiting.
-  Chunk<W4, U> c0, c1;
-  if (steps > 0) load_chunk<W4, U>(a, blockIdx.x, 0, k_lo, g8, t4, c0);
-  if (a.l2_prefetch) {
-    // Every row this CTA will read is requested into L2 now, while the kernel before this one in the stream is
-    // still running (this kernel's CTAs are resident beside it): HBM keeps streaming across the kernel boundary and
-    // the loads below find their bytes in L2.  One bulk prefetch per row (16 rows per group).
-    const long long row_bytes = W4 == 0 ? (long long)K * 2 : (W4 == 3 ? (long long)K : (long long)K / 2);
-    for (int i = threadIdx.x; i < my_groups * 16; i += THREADS) {
-      int rA, rB;
-      group_rows(a, blockIdx.x + (i >> 4) * gridDim.x, rA, rB);
-      const int row = ((i & 15) < 8) ? rA + (i & 15) : rB + (i & 15) - 8;
-      const uint8_t* src = reinterpret_cast<const uint8_t*>(a.w) + (long long)row * row_bytes;
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)row_bytes) : "memory");
-    }
-  }
-  wait_inputs();
-
-  // ---- prologue: the B rows of x -> shared memory, optionally RMS-normalised
   {
     const int nvec = K >> 3;
     for (int b = warp; b < a.B; b += WARPS) {
@@ -310,7 +281,7 @@ __device__ __forceinline__ void linear_body(const LinArgs& a, uint8_t* smem, Wai
         if (lane == 0) rstd_s[b] = rsqrtf(ss / (float)K + a.eps);
       }
     }
-    __syncthreads();
+    sync();
     if (a.norm_w) {
       for (int idx = threadIdx.x; idx < a.B * nvec; idx += THREADS) {
         const int b = idx / nvec, v = idx % nvec;
@@ -328,40 +299,18 @@ __device__ __forceinline__ void linear_body(const LinArgs& a, uint8_t* smem, Wai
         }
         *p = q;
       }
-      __syncthreads();
+      sync();
     }
   }
 
-  const uint8_t* xbase = xs + (g8 < a.B ? g8 : a.B - 1) * xstride + (k_lo + lane_k<W4>(t4)) * 2;
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
+}
 
-  // The layer that follows streams weights that depend on nothing computed here: ask for them to be brought into L2
-  // now, behind this kernel's own loads, so that HBM keeps streaming through this kernel's reduction and epilogue,
-  // the kernel boundary and the next kernel's prologue.  Every CTA requests its slice in 16 KiB pieces.
-  if (a.next_w != nullptr) {
-    constexpr unsigned long long PIECE = 16384;
-    const unsigned long long pieces = (a.next_bytes + PIECE - 1) / PIECE;
-    for (unsigned long long i = (unsigned long long)blockIdx.x * THREADS + threadIdx.x; i < pieces;
-         i += (unsigned long long)gridDim.x * THREADS) {
-      const unsigned long long off = i * PIECE;
-      const uint32_t n = (uint32_t)((a.next_bytes - off < PIECE ? a.next_bytes - off : PIECE) & ~15ull);
-      if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.next_w + off), "r"(n) : "memory");
-    }
-  }
-
-  // Two register sets alternate: while one chunk feeds the tensor cores the next one is in flight,
-  // across group boundaries too, so the stream of weight loads never drains.
-  for (int step = 0; step < steps; ++step) {
-    const int gi = step / chunks, ci = step - gi * chunks;
-    const int grp = blockIdx.x + gi * gridDim.x;
-    if (step + 1 < steps) {
-      const int gn = (step + 1) / chunks, cn = (step + 1) - gn * chunks;
-      if (step & 1) load_chunk<W4, U>(a, blockIdx.x + gn * gridDim.x, cn * CH, k_lo, g8, t4, c0);
-      else          load_chunk<W4, U>(a, blockIdx.x + gn * gridDim.x, cn * CH, k_lo, g8, t4, c1);
-    }
-    if (step & 1) mma_chunk<W4, U>(c1, xbase + ci * CH * 2, c);
-    else          mma_chunk<W4, U>(c0, xbase + ci * CH * 2, c);
-    if (ci != chunks - 1) continue;
+// K-split reduction of one 16-row group through shared memory, then the layer's epilogue.  c: this thread's partial
+// sums (c0,c1 = row g8, batch 2t,2t+1; c2,c3 = row g8+8).  Ends with the computing threads in step.
+template <class Sync>
+__device__ __forceinline__ void finish_group(const LinArgs& a, int grp, float (&c)[4], float* red, float* fin, Sync sync) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g8 = lane >> 2, t4 = lane & 3;
     int rA, rB;
     group_rows(a, grp, rA, rB);
     // ---- K-split reduction through shared memory: c0,c1 = (row g8, batch 2t,2t+1); c2,c3 = row g8+8
@@ -370,14 +319,14 @@ __device__ __forceinline__ void linear_body(const LinArgs& a, uint8_t* smem, Wai
     my[g8 * NB + 2 * t4 + 1] = c[1];
     my[(g8 + 8) * NB + 2 * t4] = c[2];
     my[(g8 + 8) * NB + 2 * t4 + 1] = c[3];
-    __syncthreads();
+    sync();
     if (threadIdx.x < 16 * NB) {
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) s += red[w * 16 * NB + threadIdx.x];
       fin[threadIdx.x] = s;
     }
-    __syncthreads();
+    sync();
     // ---- epilogue: thread e = (row r of 16, batch n)
     if (threadIdx.x < 16 * NB) {
       const int r = threadIdx.x / NB, n = threadIdx.x % NB;
@@ -458,7 +407,86 @@ __device__ __forceinline__ void linear_body(const LinArgs& a, uint8_t* smem, Wai
         }
       }
     }
-    __syncthreads();
+  sync();
+}
+
+// Shared memory a launch needs for a layer of width K and batch B: the staged rows of x plus the K-split partials.
+__host__ __device__ inline size_t lin_smem_bytes(int K, int B) {
+  return (size_t)B * ((size_t)K * 2 + XPAD) + (size_t)(WARPS + 1) * 16 * NB * sizeof(float);
+}
+
+// The whole layer for one CTA of a grid of `gridDim.x` (groups blockIdx.x, blockIdx.x + gridDim.x, ...).
+// `wait_inputs()` is called once, after the first weights have been requested and before x is read: a stand-alone
+// launch waits there for the kernel before it in the stream, a step kernel for the grid barrier of the previous layer.
+// Only the B rows of x that exist are staged; the MMA's batch columns past B repeat row B - 1 and are never stored.
+template <int W4, int U, class Wait>
+__device__ __forceinline__ void linear_body(const LinArgs& a, uint8_t* smem, Wait wait_inputs) {
+  const int K = a.K;
+  const int xstride = K * 2 + a.xpad;                             // bytes per x row
+  uint8_t* xs = smem;                                             // [B][xstride]
+  float* red = reinterpret_cast<float*>(smem + (size_t)a.B * (K * 2 + XPAD));   // [WARPS][16][NB]
+  float* fin = red + WARPS * 16 * NB;                             // [16][NB]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  constexpr int CH = ChunkK<W4, U>::value;
+  const int kslice = K / WARPS;
+  const int k_lo = warp * kslice;
+  const int chunks = kslice / CH;
+  const int my_groups = (a.n_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int steps = my_groups * chunks;
+
+  // The weights of this layer do not depend on the layer before it, so the first chunk is requested before waiting.
+  const LinHot hot{a.w, a.scales, a.K, a.mode, a.up_off, a.head_dim};
+  Chunk<W4, U> c0, c1;
+  if (steps > 0) load_chunk<W4, U>(hot, blockIdx.x, 0, k_lo, g8, t4, c0);
+  if (a.l2_prefetch) {
+    // Every row this CTA will read is requested into L2 now, while the kernel before this one in the stream is
+    // still running (this kernel's CTAs are resident beside it): HBM keeps streaming across the kernel boundary and
+    // the loads below find their bytes in L2.  One bulk prefetch per row (16 rows per group).
+    const long long row_bytes = W4 == 0 ? (long long)K * 2 : (W4 == 3 ? (long long)K : (long long)K / 2);
+    for (int i = threadIdx.x; i < my_groups * 16; i += THREADS) {
+      int rA, rB;
+      group_rows(a, blockIdx.x + (i >> 4) * gridDim.x, rA, rB);
+      const int row = ((i & 15) < 8) ? rA + (i & 15) : rB + (i & 15) - 8;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(a.w) + (long long)row * row_bytes;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)row_bytes) : "memory");
+    }
+  }
+  wait_inputs();
+
+  stage_x(a, xs, xstride, BlockSync{});
+
+  const uint8_t* xbase = xs + (g8 < a.B ? g8 : a.B - 1) * xstride + (k_lo + lane_k<W4>(t4)) * 2;
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+
+  // The layer that follows streams weights that depend on nothing computed here: ask for them to be brought into L2
+  // now, behind this kernel's own loads, so that HBM keeps streaming through this kernel's reduction and epilogue,
+  // the kernel boundary and the next kernel's prologue.  Every CTA requests its slice in 16 KiB pieces.
+  if (a.next_w != nullptr) {
+    constexpr unsigned long long PIECE = 16384;
+    const unsigned long long pieces = (a.next_bytes + PIECE - 1) / PIECE;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * THREADS + threadIdx.x; i < pieces;
+         i += (unsigned long long)gridDim.x * THREADS) {
+      const unsigned long long off = i * PIECE;
+      const uint32_t n = (uint32_t)((a.next_bytes - off < PIECE ? a.next_bytes - off : PIECE) & ~15ull);
+      if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.next_w + off), "r"(n) : "memory");
+    }
+  }
+
+  // Two register sets alternate: while one chunk feeds the tensor cores the next one is in flight,
+  // across group boundaries too, so the stream of weight loads never drains.
+  for (int step = 0; step < steps; ++step) {
+    const int gi = step / chunks, ci = step - gi * chunks;
+    const int grp = blockIdx.x + gi * gridDim.x;
+    if (step + 1 < steps) {
+      const int gn = (step + 1) / chunks, cn = (step + 1) - gn * chunks;
+      if (step & 1) load_chunk<W4, U>(hot, blockIdx.x + gn * gridDim.x, cn * CH, k_lo, g8, t4, c0);
+      else          load_chunk<W4, U>(hot, blockIdx.x + gn * gridDim.x, cn * CH, k_lo, g8, t4, c1);
+    }
+    if (step & 1) mma_chunk<W4, U>(c1, xbase + ci * CH * 2, c);
+    else          mma_chunk<W4, U>(c0, xbase + ci * CH * 2, c);
+    if (ci != chunks - 1) continue;
+    finish_group(a, grp, c, red, fin, BlockSync{});
     c[0] = c[1] = c[2] = c[3] = 0.f;
   }
 }

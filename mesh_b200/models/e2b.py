@@ -263,9 +263,11 @@ class E2BDecoder:
     def capture(self, mode: str | None = None):
         """Prepare the decode step for replay.  ``mode``: ``"step"``: the whole step as one cooperative kernel;
         ``"graph"``: the step's launches recorded in a CUDA graph (after a warm-up step on a side stream).
-        Default: ``MESH_DECODE_MODE``, else ``"step"`` where the model fits it."""
+        Default: ``MESH_DECODE_MODE``, else ``"graph"``."""
         import os
-        mode = mode or os.environ.get("MESH_DECODE_MODE") or ("step" if self.step_kernel_fits() else "graph")
+        mode = mode or os.environ.get("MESH_DECODE_MODE") or "graph"
+        if mode == "step" and not self.step_kernel_fits():
+            raise ValueError("the step kernel takes groups of at most 4 query heads per KV head")
         if mode not in ("step", "graph"):
             raise ValueError(f"decode mode {mode!r}: 'step' or 'graph'")
         self.mode = mode

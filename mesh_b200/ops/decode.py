@@ -56,6 +56,11 @@ class _Op(ctypes.Structure):
     ]
 
 
+class _StepPlan(ctypes.Structure):
+    _fields_ = [("n_dev", c_int), ("grid", c_int), ("smem", c_int), ("ring_off", c_int), ("slot_bytes", c_int),
+                ("n_stages", c_int)]
+
+
 OP_EMBED, OP_LINEAR, OP_ATTENTION, OP_ARGMAX = 0, 1, 2, 3
 _recording: list | None = None           # operations of the step being recorded (``record_step``)
 
@@ -68,7 +73,8 @@ class DecodeStep:
         step.run()                        # every later token: one launch
 
     Inside the block the calls launch nothing; they describe the operations, which ``run`` executes in that order with a
-    grid barrier between them.  The tensors the calls named are kept alive by the step and must keep their addresses."""
+    grid barrier between them, one CTA per SM, the weights of all layers streamed through shared memory by a warp that
+    does not wait at the barriers.  The tensors the calls named are kept alive by the step and must keep their addresses."""
 
     def __init__(self, device):
         self.device = torch.device(device)
@@ -111,19 +117,19 @@ class DecodeStep:
         self.dev_ops = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.barrier = torch.zeros(2, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
-        n_dev, grid, smem = c_int(0), c_int(0), c_int(0)
+        self.plan = _StepPlan()
         rc = L.mesh_decode_step_prepare(arr, c_int(n), c_void_p(self.dev_ops.data_ptr()), ctypes.c_size_t(nbytes),
-                                        ctypes.byref(n_dev), ctypes.byref(grid), ctypes.byref(smem))
+                                        ctypes.byref(self.plan))
         _native.check(rc, "mesh_decode_step_prepare")
-        self.n_dev, self.grid, self.smem = n_dev.value, grid.value, smem.value
+        self.n_dev, self.grid, self.smem = self.plan.n_dev, self.plan.grid, self.plan.smem
         self.status = status_block(self.device)
 
     def run(self, trace: torch.Tensor | None = None):
         """One step.  ``trace``: an int64 tensor of ``2 * 3 * n_dev`` words on the device; the first and the last CTA
         write {start, end of own share, nanoseconds waited} per operation (see :meth:`timeline`)."""
-        rc = _native.lib().mesh_decode_step_run(c_void_p(self.dev_ops.data_ptr()), c_int(self.n_dev),
+        rc = _native.lib().mesh_decode_step_run(c_void_p(self.dev_ops.data_ptr()), ctypes.byref(self.plan),
                                                 c_void_p(self.barrier.data_ptr()), c_void_p(self.status.data_ptr()),
-                                                c_int(self.grid), c_int(self.smem), c_void_p(_p(trace)), _stream())
+                                                c_void_p(_p(trace)), _stream())
         _native.check(rc, "mesh_decode_step_run")
         _native.count_launch()
 

@@ -77,7 +77,9 @@ class EPMoE:
         mt = self.cap // 256 + self.El
         self.max_tiles = mt * max(-(-d_ff // 128), d_model // 256 + 1, -(-2 * d_ff // 256) * (d_model // 256)) + 64
         i32 = dict(dtype=torch.int32, device=dev)
+        self.side = torch.cuda.Stream(dev)          # the router's backward runs beside the experts' (see backward)
         self.slot = torch.zeros(tokens * k, **i32)
+        self.count_work = torch.zeros(int(_native.lib().mesh_moe_count_work_ints(c_int(tokens * k), c_int(experts))), **i32)
         self.meta = torch.zeros(tokens * k, **i32)
         self.send_base = torch.zeros(experts, **i32)
         self.layout = torch.zeros(3 * self.El + 2, **i32)
@@ -175,7 +177,8 @@ class EPMoE:
         self.idx = idx.reshape(-1).contiguous()
         arr = (c_void_p * MAX_RANKS)(*[c_void_p(self.counts.ptr(r)) if r < self.world else c_void_p(0) for r in range(MAX_RANKS)])
         _native.check(self.L.mesh_moe_count(c_void_p(self.idx.data_ptr()), c_int(T * k), c_void_p(self.slot.data_ptr()),
-                                            c_int(self.E), c_int(self.rank), c_int(self.world), arr, c_uint32(self.steps), _s()),
+                                            c_int(self.E), c_int(self.rank), c_int(self.world), arr, c_uint32(self.steps),
+                                            c_void_p(self.count_work.data_ptr()), _s()),
                       "mesh_moe_count")
         p = _Plan()
         p.counts, p.seq, p.rank, p.world, p.experts = self.counts.ptr(), self.steps, self.rank, self.world, self.E
@@ -209,11 +212,39 @@ class EPMoE:
         x, w_router, w1, w2, logits, weights, bias = self._saved
         T, D, F, k = self.T, self.D, self.F, self.k
         dout = dout.contiguous()
-        # gradients of the routing weights: <expert output row, dOut[t]> (reads the forward's y on the peers)
+        # Gradients of the routing weights, <expert output row, dOut[t]> (reads the forward's y on the peers), and
+        # the router's own backward need nothing of the expert backward: they run on a second stream beside it (the
+        # pull of y is inbound NVLink traffic while the dispatch of dOut is outbound) and join at the end.
+        import os
+        overlap = os.environ.get("MESH_MOE_OVERLAP", "1") != "0" and self.timeline is None
+        main = torch.cuda.current_stream(self.dev)
+        side = self.side if overlap else main
         dots = torch.empty((T, k), dtype=torch.float32, device=self.dev)
         self._mark("bwd start")
-        self._combine(self.y, 2, None, None, dot_with=dout, dots=dots.view(-1))
-        self._mark("bwd weight dots")
+
+        def router_backward():
+            self._combine(self.y, 2, None, None, dot_with=dout, dots=dots.view(-1))
+            self._mark("bwd weight dots")
+            # router: weights = renormalised top-k of softmax(logits + bias)
+            lg = logits.float().detach().requires_grad_(True)
+            p = torch.softmax(lg + (bias.float() if bias is not None else 0.0), dim=-1)
+            sel = torch.gather(p, 1, self.idx.view(T, k).long())
+            wn = sel / sel.sum(-1, keepdim=True)
+            kept = (self.meta.view(T, k) >= 0).float()
+            (wn * dots * kept).sum().backward()
+            dlogits = lg.grad.to(torch.bfloat16)
+            dxr = G.gemm(dlogits, w_router, b_mn=True)
+            dwr = G.gemm(dlogits, x, a_mn=True, b_mn=True) if (dlogits.shape[1] % 64 == 0 and x.shape[1] % 64 == 0) else \
+                (dlogits.float().T @ x.float()).to(torch.bfloat16)
+            self._mark("bwd router")
+            return dxr, dwr
+
+        if overlap:
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                dx_router, dw_router = router_backward()
+        else:
+            dx_router, dw_router = router_backward()
         _native.check(self.L.mesh_moe_zero_pad(c_void_p(self.recv_dy.ptr()), c_void_p(self.layout.data_ptr()), c_int(self.El),
                                                c_int(D), _s()), "mesh_moe_zero_pad")
         self._dispatch(dout, weights.reshape(-1).contiguous(), self.recv_dy, 1)
@@ -235,18 +266,11 @@ class EPMoE:
         dx = torch.empty((T, D), dtype=torch.bfloat16, device=self.dev)
         self._combine(self.dx, 3, None, dx)
         self._mark("bwd combine")
-        # router: weights = renormalised top-k of softmax(logits + bias)
-        lg = logits.float().detach().requires_grad_(True)
-        p = torch.softmax(lg + (bias.float() if bias is not None else 0.0), dim=-1)
-        sel = torch.gather(p, 1, self.idx.view(T, k).long())
-        wn = sel / sel.sum(-1, keepdim=True)
-        kept = (self.meta.view(T, k) >= 0).float()
-        (wn * dots * kept).sum().backward()
-        dlogits = lg.grad.to(torch.bfloat16)
-        dx = dx + G.gemm(dlogits, w_router, b_mn=True)
-        dw_router = G.gemm(dlogits, x, a_mn=True, b_mn=True) if (dlogits.shape[1] % 64 == 0 and x.shape[1] % 64 == 0) else \
-            (dlogits.float().T @ x.float()).to(torch.bfloat16)
-        self._mark("bwd router")
+        if overlap:
+            main.wait_stream(side)
+            for t in (dx_router, dw_router, dots):
+                t.record_stream(main)
+        dx = dx + dx_router
         return dx, dw_router, dw1, dw2
 
 

@@ -49,9 +49,9 @@ class _AsyncWire:
     """Point-to-point along the pipeline axis without waits on the critical path (NCCL ranks).
 
     Two communicators: ``axis.group`` carries activations toward later stages, ``axis.group_back`` gradients toward
-    earlier ones.  On each of them this rank's operations are queued in the order of the data flow (receive input i,
-    send output i, receive input i + 1, ...), which is the order the neighbours use too, so no operation waits behind
-    one that depends on it."""
+    earlier ones.  Sends are queued on a side stream and never waited for on the compute stream (the sender goes on
+    while the next stage is still busy); on each communicator this rank's operations are queued in the order of the
+    data flow, which is the order the neighbours use too."""
 
     def __init__(self, axis):
         self.axis = axis
@@ -60,6 +60,27 @@ class _AsyncWire:
         self.sent_bytes = 0
         self.sends: list = []          # (work, tensor): kept until the end of the step
         self.side = torch.cuda.Stream(axis.device)
+        self._connect()
+
+    def _connect(self):
+        """First use of the axis: one blocking word along every link in both directions, pair by pair from the first
+        stage on.  NCCL creates the communicator of a pair of ranks at their first transfer, and that creation blocks
+        the host until both ranks are in it; the schedule below posts a stage's receive of gradients before the later
+        stage can send any, so without this step the first stage would wait for the creation on the gradient
+        communicator while the second waits for it on the activation communicator."""
+        axis = self.axis
+        if getattr(axis, "_pp_connected", False):
+            return
+        t = torch.zeros(1, device=axis.device)
+        for r in range(axis.world - 1):
+            if axis.rank == r:
+                dist.send(t, self.next, group=axis.group)
+                dist.recv(t, self.next, group=axis.group_back)
+            elif axis.rank == r + 1:
+                dist.recv(t, self.prev, group=axis.group)
+                dist.send(t, self.prev, group=axis.group_back)
+        torch.cuda.synchronize(axis.device)
+        axis._pp_connected = True
 
     def _post(self, fn, t, peer, group):
         main = torch.cuda.current_stream(self.axis.device)
@@ -101,9 +122,12 @@ class _AsyncWire:
 
 
 def _overlapped(axis) -> bool:
+    """Asynchronous sends from the second step of an axis on: the first step runs with matched, waited transfers, so
+    that every kernel of the step has been launched once (loading a module can make the host wait for the device, which
+    must not happen while a send that the next stage has not asked for yet is running)."""
     import os
     return (os.environ.get("MESH_PP_OVERLAP", "1") != "0" and axis.device.type == "cuda"
-            and getattr(axis, "group_back", None) is not None and axis.world > 1)
+            and getattr(axis, "group_back", None) is not None and axis.world > 1 and getattr(axis, "_pp_warm", False))
 
 
 def run_1f1b(stage: Callable[[torch.Tensor], torch.Tensor], axis, microbatches: Sequence, *,
@@ -161,26 +185,27 @@ def run_1f1b(stage: Callable[[torch.Tensor], torch.Tensor], axis, microbatches: 
         return g
 
     if _overlapped(axis):
-        # Same schedule, transfers off the critical path: see _AsyncWire.
+        # Same schedule, sends off the critical path: see _AsyncWire.  A receive is posted where its data is needed, not
+        # earlier: an NCCL receive is a kernel that runs until its sender arrives, and whatever makes the host wait for
+        # the whole device meanwhile (a module loaded at a kernel's first launch, a freed block) would then wait for a
+        # peer that may be waiting for this rank.
         aw = _AsyncWire(axis)
         n_fwd = n_bwd = 0
-        x_posted = aw.recv_prev(new_act()) if (not axis.first and M > 0) else None
-        g_posted = aw.recv_next(new_act()) if (not axis.last and M > 0) else None
 
         def do_forward():
-            nonlocal n_fwd, x_posted
-            y = forward(n_fwd, aw.take(x_posted))
+            nonlocal n_fwd
+            x_in = None if axis.first else aw.take(aw.recv_prev(new_act()))
+            y = forward(n_fwd, x_in)
             n_fwd += 1
             if not axis.last:
                 aw.send_next(y.detach())
-            x_posted = aw.recv_prev(new_act()) if (not axis.first and n_fwd < M) else None
 
         def do_backward():
-            nonlocal n_bwd, g_posted
-            gx = backward(aw.take(g_posted))
+            nonlocal n_bwd
+            gy = None if axis.last else aw.take(aw.recv_next(new_act()))
+            gx = backward(gy)
             n_bwd += 1
             aw.send_prev(gx)
-            g_posted = aw.recv_next(new_act()) if (not axis.last and n_bwd < M) else None
 
         for _ in range(warm):
             do_forward()
@@ -224,6 +249,10 @@ def run_1f1b(stage: Callable[[torch.Tensor], torch.Tensor], axis, microbatches: 
             wire.exchange(recv_next=gy)
         gx = backward(gy)
         wire.exchange(send_prev=gx)
+    try:
+        axis._pp_warm = True
+    except AttributeError:
+        pass
     return losses, {"peak_alive": peak_alive, "sent_bytes": wire.sent_bytes, "microbatches": M}
 
 

@@ -8,9 +8,10 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _small_cfg():
+def _small_cfg(q_heads=4):
+    """``q_heads=8`` makes every layer 1024 wide or more: what the one-kernel step needs of 4-bit weights."""
     from mesh_b200.models.e2b import E2BConfig
-    return E2BConfig(layers=5, d_model=1024, q_heads=4, kv_heads=2, head_dim=128, d_ff=2048, vocab=4096, window=16,
+    return E2BConfig(layers=5, d_model=1024, q_heads=q_heads, kv_heads=2, head_dim=128, d_ff=2048, vocab=4096, window=16,
                      local_per_global=4, max_seq=96, init_std=0.05)
 
 
@@ -74,7 +75,7 @@ def _rel(a, b):
 def test_e2b_solo_matches_reference(quant, mode):
     from mesh_b200.models.e2b import E2BDecoder
     from mesh_b200.utils.status import check_status
-    cfg = _small_cfg()
+    cfg = _small_cfg(8 if mode == "step" else 4)
     B, T, steps = 2, 24, 6
     m = E2BDecoder(cfg, _solo_ctx(), B, quant)
     prompt = torch.randint(0, cfg.vocab, (B, T), dtype=torch.int32, device="cuda")
@@ -93,30 +94,38 @@ def test_e2b_solo_matches_reference(quant, mode):
 
 
 @pytest.mark.parametrize("quant,B", [("bf16", 1), ("bf16", 8), ("w4", 3), ("w8", 8)])
-def test_step_kernel_equals_separate_launches(quant, B):
-    """The whole step as one cooperative kernel runs the same layer bodies as the separate launches: same logits and
-    tokens, bit for bit, token after token."""
+def test_step_kernel_follows_separate_launches(quant, B):
+    """The whole step as one cooperative kernel against the step's separate launches, token after token from the same
+    inputs: the layers are the same arithmetic with the sums over k taken in another order, so the logits agree to
+    rounding, the chosen tokens wherever the best logit leads by more than that, and the counters exactly."""
     from mesh_b200.models.e2b import E2BDecoder
     from mesh_b200.utils.status import check_status
-    cfg = _small_cfg()
-    T, steps = 20, 8
+    cfg = _small_cfg(8)
+    T, steps = 20, 10
     prompt = torch.randint(0, cfg.vocab, (B, T), dtype=torch.int32, device="cuda")
-    runs = []
+    models = []
     for mode in ("graph", "step"):
         m = E2BDecoder(cfg, _solo_ctx(), B, quant)
         first = m.prefill(prompt)
         m.capture(mode)                      # the graph form runs a warm-up step: put the state back
         m.pos.fill_(T - 1); m.tok.copy_(first)
-        step0 = int(m.step[0])
-        logits = []
-        for _ in range(steps):
-            m.decode(1)
-            logits.append(m.logits.clone())
-        toks = m.decode(4).clone()
-        check_status()
-        runs.append((torch.stack(logits), toks, m.pos.clone(), torch.tensor(int(m.step[0]) - step0)))
-    for a, b in zip(runs[0], runs[1]):
-        assert torch.equal(a, b)
+        models.append(m)
+    g, s = models
+    g0, s0 = int(g.step[0]), int(s.step[0])
+    for _ in range(steps):
+        s.tok.copy_(g.tok); s.pos.copy_(g.pos)
+        g.decode(1); s.decode(1)
+        a, b = g.logits.float(), s.logits.float()
+        assert float((a - b).square().mean().sqrt() / a.square().mean().sqrt()) < 2e-2
+        top = a.topk(2, dim=-1).values
+        clear = (top[:, 0] - top[:, 1]) > 0.1 * a.abs().amax(-1)
+        assert torch.equal(g.tok[clear], s.tok[clear])
+        assert torch.equal(g.pos, s.pos)
+    check_status()
+    assert int(g.step[0]) - g0 == int(s.step[0]) - s0 == steps
+    s.decode(3)                                # several steps back to back: the barrier words carry over
+    check_status()
+    assert s.pos.tolist() == [T - 1 + steps + 3] * B
 
 
 def _tp_rank(rank, world, rdv):
@@ -155,9 +164,11 @@ def _tp_rank(rank, world, rdv):
     ctx.heap.close()
 
 
+@pytest.mark.parametrize("mode", ["graph", "step"])
 @pytest.mark.parametrize("world", [2, 4])
-def test_e2b_tensor_parallel(world):
+def test_e2b_tensor_parallel(world, mode, monkeypatch):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from mesh_b200.utils.launch import spawn_ranks
+    monkeypatch.setenv("MESH_DECODE_MODE", mode)          # the ranks inherit it
     spawn_ranks(_tp_rank, world, use_cuda=True, timeout=300.0)
