@@ -825,13 +825,20 @@ gemm_kernel(const __grid_constant__ Params p) {
     // =================================================================== reduce tail
     // Sum the `world` partial copies of every (m-tile, n-tile) of this rank's rows once
     // its arrival counter shows that all of them landed.
+    // A tile is cut into `split` row slices when there are fewer tiles than CTAs (few rows per rank at large world
+    // sizes), so that every SM takes part in the sum.
     const int my_m_tiles = (p.rs_rows_per_rank + BM - 1) / BM;
-    const int items = my_m_tiles * p.n_tiles;
+    const int tiles_mine = my_m_tiles * p.n_tiles;
+    int split = 1;                       // all-reduce counts one arrival per tile on the other ranks: tiles stay whole
+    while (p.ar_out[0] == nullptr && split < 8 && tiles_mine * split * 2 <= (int)gridDim.x) split *= 2;
+    const int items = tiles_mine * split;
+    const int slice_rows = BM / split;
     __shared__ int item_ok;
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
-      const int mt = item / p.n_tiles, nt = item % p.n_tiles;
+      const int tile_i = item / split, slice = item - tile_i * split;
+      const int mt = tile_i / p.n_tiles, nt = tile_i % p.n_tiles;
       if (threadIdx.x == 0) {
-        item_ok = wait_flag_ge(p.rs_count[p.rank] + item, p.rs_expect, p.status, SITE_PEER_FLAG) ? 1 : 0;
+        item_ok = wait_flag_ge(p.rs_count[p.rank] + tile_i, p.rs_expect, p.status, SITE_PEER_FLAG) ? 1 : 0;
       }
       __syncthreads();
       const bool good = item_ok != 0;
@@ -841,8 +848,10 @@ gemm_kernel(const __grid_constant__ Params p) {
       const int m_tiles_local = p.rs_rows_per_rank / BM;
       constexpr int TILE_ELEMS = BM * BN;
       // one 16-byte vector per thread and step: (chunk c, row r, vector v) with v fastest
-      for (int idx = threadIdx.x; idx < (BN / 64) * BM * 8; idx += blockDim.x) {
-        const int v = idx & 7, r = (idx >> 3) & (BM - 1), c = idx >> 10;
+      const int per_chunk = slice_rows * 8;
+      for (int idx = threadIdx.x; idx < (BN / 64) * per_chunk; idx += blockDim.x) {
+        const int c = idx / per_chunk, in_chunk = idx - c * per_chunk;
+        const int v = in_chunk & 7, r = slice * slice_rows + (in_chunk >> 3);
         if (c * 64 + v * 8 >= cols) continue;
         const long long in_tile = (long long)c * (BM * 64) + r * 64 + v * 8;
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
