@@ -135,11 +135,30 @@ def run_baseline(ctx, cfg, B, prompt_len, steps):
     return float(ms[0])
 
 
+def explain_baseline(ctx, cfg, B: int = 1) -> dict:
+    """Kernels of one eager step of the stock decoder: how many, their summed device time, and the largest groups."""
+    from torch.profiler import ProfilerActivity, profile
+    m = BaselineDecoder(cfg, ctx.rank, ctx.world, ctx.group if ctx.world > 1 else None, B, ctx.device)
+    with torch.no_grad():
+        for _ in range(3):
+            m.step()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            m.step()
+            torch.cuda.synchronize()
+    rows = [(e.key, e.count, e.device_time_total) for e in prof.key_averages() if e.device_time_total > 0]
+    rows.sort(key=lambda r: -r[2])
+    return {"kernels": int(sum(r[1] for r in rows)), "device_us": round(sum(r[2] for r in rows), 1),
+            "top": [{"kernel": k[:60], "launches": int(n), "us": round(t, 1)} for k, n, t in rows[:8]]}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--impl", default="mesh", choices=["mesh", "baseline"])
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--explain", action="store_true",
+                    help="baseline arm: where a decode step's time goes (kernels of one eager step by device time)")
     a = ap.parse_args()
     ctx = init()
     from mesh_b200.models.e2b import E2BConfig, bench_decode
@@ -156,6 +175,8 @@ def main():
             rec["runs"].append({"weights": "bf16", "batch": B, "ms_per_token": round(ms / a.steps, 4),
                                 "tokens_per_s": round(B * a.steps / (ms * 1e-3), 1)})
             torch.cuda.empty_cache()
+        if a.explain:
+            rec["baseline_step_kernels"] = explain_baseline(ctx, cfg)
     rec.update({"metric": "e2b_decode_tokens_per_s", "impl": a.impl, "n_gpus": ctx.world})
     emit(ctx.rank, rec)
     from mesh_b200.distributed import shutdown

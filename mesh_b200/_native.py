@@ -50,6 +50,7 @@ class GemmArgs(ctypes.Structure):
         ("d_done", c_void_p), ("k_ready", c_void_p), ("k_ready_value", c_uint32), ("k_ready_rows", c_int),
         ("b_scales", c_void_p), ("b_bits", c_int), ("pdl", c_int),
         ("ar_out", c_void_p * MAX_RANKS), ("ar_flag", c_void_p * MAX_RANKS), ("ar_expect", c_uint32),
+        ("ag_split", c_int),
     ]
 
 
@@ -76,7 +77,9 @@ def lib() -> ctypes.CDLL:
         from .config import config
         check = bool(config().check)          # MESH_CHECK=1: the library with index / alignment checks in its kernels
         path = _build.lib_path(check)
-        if not path.exists() or (not _build.is_current(check) and _build.nvcc_path() is not None):
+        import os
+        rebuild = os.environ.get("MESH_BUILD", "1") != "0"     # MESH_BUILD=0: load the library as it is, stale or not
+        if not path.exists() or (rebuild and not _build.is_current(check) and _build.nvcc_path() is not None):
             try:
                 path = _build.build(check=check)
             except Exception as e:  # keep a stale but loadable library usable

@@ -71,6 +71,10 @@ typedef struct MeshGemmArgs {
   void* ar_out[MESH_MAX_RANKS];
   void* ar_flag[MESH_MAX_RANKS];
   uint32_t ar_expect;
+  // all-gather: parts a 128-row block is pushed in (each part raises the block's counter once, so a block is there
+  // when its counter has grown by ag_split); 0: 8.  With blocks_per_rank * ag_split >= CTAs, all CTAs push to one
+  // destination at a time, in the order the destinations need the rows.
+  int ag_split;
 } MeshGemmArgs;
 
 // Returns 0 or a negative error (bad shape/alignment) or a positive cudaError_t.

@@ -150,6 +150,7 @@ extern "C" int mesh_gemm_bf16(const MeshGemmArgs* a, void* stream_v) {
   p.a_ready_value = a->a_ready_value;
   p.a_ready_rows = a->a_ready_rows > 0 ? a->a_ready_rows : BM;
   p.m_rotate = a->m_rotate;   // converted to scheduling units below
+  p.ag_split = a->ag_split > 0 ? a->ag_split : 8;
   p.rank = a->rank; p.world = a->world > 0 ? a->world : 1;
   const bool ag = a->ag_src != nullptr;
   if (ag) {

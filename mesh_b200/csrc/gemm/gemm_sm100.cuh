@@ -95,6 +95,7 @@ struct Params {
   uint32_t a_ready_value;
   int a_ready_rows;
   int m_rotate;             // first m-tile visited (own shard first)
+  int ag_split;             // parts per 128-row block pushed by the comm warps
   // push side (run by the comm warps): this rank's rows `ag_src` [ag_rows_per_rank, ag_ld] are
   // stored into every rank's gathered buffer `ag_dst[d]` at row rank*ag_rows_per_rank, and the
   // destination's arrival counter `ag_flags[d][block]` is raised once per part.
@@ -772,21 +773,24 @@ gemm_kernel(const __grid_constant__ Params p) {
     }
   } else if (AG) {
     // ===================================================================== all-gather push
-    // The comm warps of all CTAs together store this rank's rows into every rank's gathered
-    // buffer (own copy first, then the rank before this one, and so on, because each
-    // consumer walks its tiles starting from its own rows and continuing with the next
-    // rank's), 128-row blocks split in AG_SPLIT parts, and raise the destination's counter.
+    // The comm warps of all CTAs together store this rank's rows into every rank's gathered buffer: first to the rank
+    // before this one, then the one before that, and so on, the own copy last, because each consumer walks its tiles
+    // starting from its own rows (read from the source, no wait) and continuing with the next rank's.  128-row blocks
+    // go in `ag_split` parts, each raising the destination's counter once; with enough parts that one destination
+    // occupies every CTA, the ranks send along one permutation at a time and each block arrives at the full rate of a
+    // port, in the order it is needed, instead of all blocks arriving together at the end.
     const int cw = warp - (2 + EPI_WARPS);
     const int tid = cw * 32 + lane;
     constexpr int NT = COMM_WARPS * 32;
+    const int split = p.ag_split;
     const int blocks_per_rank = p.ag_rows_per_rank / p.a_ready_rows;
     const long long vec_per_block = (p.ag_ld / 8) * p.a_ready_rows;   // 16-byte vectors
-    const long long per_part = (vec_per_block + AG_SPLIT - 1) / AG_SPLIT;
-    const int units = blocks_per_rank * p.world * AG_SPLIT;
+    const long long per_part = (vec_per_block + split - 1) / split;
+    const int units = blocks_per_rank * p.world * split;
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
-      const int part = unit % AG_SPLIT;
-      const int blk = (unit / AG_SPLIT) % blocks_per_rank;
-      const int step = unit / (AG_SPLIT * blocks_per_rank);           // 0 .. world-1
+      const int part = unit % split;
+      const int blk = (unit / split) % blocks_per_rank;
+      const int step = (unit / (split * blocks_per_rank) + 1) % p.world;   // 1 .. world-1, then 0 (the own copy)
       const int dest = (p.rank - step + p.world) % p.world;
       const long long row0 = (long long)blk * p.a_ready_rows;
       const uint4* src = reinterpret_cast<const uint4*>(p.ag_src + row0 * p.ag_ld);

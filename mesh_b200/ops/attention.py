@@ -168,6 +168,10 @@ def flash_attention_backward(q, k, v, out, lse, dout, *, causal=True, window=0, 
         delta = (dout.float() * out.float()).sum(-1).transpose(1, 2).contiguous()       # [B, H, Tq]
     if dq is None:
         dq = torch.zeros((B, Tq, H, hd), dtype=torch.float32, device=q.device)
+    if hd not in (64, 128):
+        # the backward kernel keeps dK and dV of a key block in tensor memory, which holds them up to 128 columns wide
+        return _backward_by_blocks(q, k, v, lse, dout, delta, dq, dkv_acc, causal, window, scale, q_off, q_stride, k_off,
+                                   k_stride, dropout)
     a = _FlashBwd()
     f = a.fwd
     f.q, f.ldq, f.q_cols = _view2d(q)
@@ -194,6 +198,43 @@ def flash_attention_backward(q, k, v, out, lse, dout, *, causal=True, window=0, 
     rc = _native.lib().mesh_flash_attention_bwd(ctypes.byref(a), c_void_p(torch.cuda.current_stream().cuda_stream))
     _native.check(rc, "mesh_flash_attention_bwd")
     _native.count_launch()
+    return dq, dk, dv
+
+
+def _backward_by_blocks(q, k, v, lse, dout, delta, dq, dkv_acc, causal, window, scale, q_off, q_stride, k_off, k_stride,
+                        dropout, block: int = 512):
+    """The attention backward for head sizes the backward kernel does not take (256): the same five products per block
+    of queries as the kernel, as fp32 tensor operations (``P = exp(S * scale - L)`` from the forward pass's log-sum-exp,
+    ``dS = P (dP - delta) scale``), masks on logical positions.  Memory: one ``[B, H, block, Tk]`` fp32 tile at a time."""
+    if dropout is not None and dropout.get("p", 0.0) > 0:
+        raise NotImplementedError("attention backward with dropout needs head_dim 64 or 128")
+    B, Tq, H, hd = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    g = H // Hkv
+    kf, vf = k.float(), v.float()
+    dk = torch.zeros((B, Tk, Hkv, hd), dtype=torch.float32, device=q.device) if dkv_acc is None else dkv_acc[0]
+    dv = torch.zeros_like(dk) if dkv_acc is None else dkv_acc[1]
+    kpos = k_off + torch.arange(Tk, device=q.device) * k_stride
+    for q0 in range(0, Tq, block):
+        q1 = min(Tq, q0 + block)
+        qs = q[:, q0:q1].float().view(B, q1 - q0, Hkv, g, hd)
+        do = dout[:, q0:q1].float().view(B, q1 - q0, Hkv, g, hd)
+        s = torch.einsum("bqhgd,bkhd->bhgqk", qs, kf) * scale
+        p = torch.exp(s - lse[:, :, q0:q1].view(B, Hkv, g, q1 - q0, 1).float())
+        qpos = q_off + torch.arange(q0, q1, device=q.device) * q_stride
+        keep = torch.ones((q1 - q0, Tk), dtype=torch.bool, device=q.device)
+        if causal:
+            keep &= kpos[None, :] <= qpos[:, None]
+        if window and window > 0:
+            keep &= kpos[None, :] > qpos[:, None] - window
+        p = torch.where(keep, p, torch.zeros((), device=q.device))
+        dv += torch.einsum("bhgqk,bqhgd->bkhd", p, do)
+        dp = torch.einsum("bqhgd,bkhd->bhgqk", do, vf)
+        ds = p * (dp - delta[:, :, q0:q1].view(B, Hkv, g, q1 - q0, 1)) * scale
+        dq[:, q0:q1] += torch.einsum("bhgqk,bkhd->bqhgd", ds, kf).reshape(B, q1 - q0, H, hd)
+        dk += torch.einsum("bhgqk,bqhgd->bkhd", ds, qs)
+    if dkv_acc is None:
+        return dq, dk.to(torch.bfloat16), dv.to(torch.bfloat16)
     return dq, dk, dv
 
 

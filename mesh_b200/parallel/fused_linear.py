@@ -45,6 +45,7 @@ class _FusedBase:
         g.a_ready, g.a_ready_value, g.a_ready_rows = flags.ptr(), expect, BM
         g.m_rotate = self.rank * (self.rows // BM)
         g.ag_src, g.ag_rows_per_rank, g.ag_ld = src.data_ptr(), self.rows, width
+        g.ag_split = zone.split
         for r in range(self.world):
             g.ag_dst[r] = buf.ptr(r)
             g.ag_flags[r] = flags.ptr(r)

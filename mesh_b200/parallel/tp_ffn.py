@@ -43,6 +43,13 @@ class _Gathered:
     def __init__(self, heap: SymmetricHeap, M: int, D: int, copies: int = 2):
         copies = max(2, copies)
         self.copies = copies
+        # parts a 128-row block is pushed in: enough that the blocks for ONE destination occupy every CTA, so the
+        # ranks send along one permutation at a time and blocks arrive in the order they are needed
+        from ..config import capacity
+        blocks = max(1, M // heap.world // BM)
+        self.split = AG_SPLIT
+        while self.split < 64 and blocks * self.split < capacity().get("sm_count", 148):
+            self.split *= 2
         self.buf = [heap.alloc((M, D), torch.bfloat16) for _ in range(copies)]
         self.flags = [heap.alloc_signals(M // BM) for _ in range(copies)]
         self.uses = [0] * copies
@@ -52,7 +59,7 @@ class _Gathered:
         par = self.turn % self.copies
         self.turn += 1
         self.uses[par] += 1
-        return self.buf[par], self.flags[par], AG_SPLIT * self.uses[par]
+        return self.buf[par], self.flags[par], self.split * self.uses[par]
 
 
 class _Scattered:
@@ -131,6 +138,7 @@ class FusedTPFFN:
         g.a_ready, g.a_ready_value, g.a_ready_rows = flags.ptr(), expect, BM
         g.m_rotate = self.rank * (self.rows // BM)
         g.ag_src, g.ag_rows_per_rank, g.ag_ld = src.data_ptr(), self.rows, self.D
+        g.ag_split = zone.split
         for r in range(self.world):
             g.ag_dst[r] = buf.ptr(r)
             g.ag_flags[r] = flags.ptr(r)

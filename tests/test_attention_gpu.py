@@ -81,9 +81,10 @@ def _ref_grads(q, k, v, dout, causal, window):
     return qf.grad, kf.grad, vf.grad
 
 
-@pytest.mark.parametrize("hd,H,Hkv", [(128, 4, 4), (128, 4, 2), (64, 2, 1)])
+@pytest.mark.parametrize("hd,H,Hkv", [(128, 4, 4), (128, 4, 2), (64, 2, 1), (256, 4, 2)])
 @pytest.mark.parametrize("T,causal,window", [(256, True, 0), (384, True, 100), (200, False, 0)])
 def test_flash_backward(hd, H, Hkv, T, causal, window):
+    """Head size 256 has the forward kernel and a backward in blocks of tensor operations; 64 and 128 both kernels."""
     from mesh_b200.ops.attention import attention
     from mesh_b200.utils.status import check_status
     torch.manual_seed(1)
