@@ -114,7 +114,7 @@ def run_baseline(ctx, cfg, B, prompt_len, steps):
         torch.cuda.current_stream().wait_stream(side)
         m.pos.zero_()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):   # the runtime's monitor thread is running
             m.step()
         m.pos.zero_()
         for t in range(prompt_len):

@@ -288,7 +288,10 @@ class E2BDecoder:
         if self.world > 1:
             self.ctx.rdv.barrier("e2b-warm")
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        # thread_local: the runtime's service threads (status monitor, channel proxy) make CUDA calls on their own
+        # streams; with the default, process-wide mode such a call during the capture invalidates it (seen with the
+        # longer captures of batch 8)
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
             self._decode_step()
         self.graph = g
         return saved

@@ -66,7 +66,9 @@ class Plan:
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        # thread_local: the runtime's own service threads (status monitor, channel proxy) make CUDA calls on their own
+        # streams; with the default, process-wide mode any such call during the capture invalidates it
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
             fn()
         self.graphs[copy] = g
 
