@@ -149,6 +149,42 @@ def _prune_objects() -> None:
                 pass
 
 
+RACE_CHECK_SOURCES = ["runtime/runtime.cpp", "runtime/host_engine.cpp", "standalone/race_check.cpp"]
+
+
+def build_race_check(out: Path | None = None) -> Path | None:
+    """The host runtime's thread-facing sources and their driver (``csrc/standalone/race_check.cpp``) compiled with
+    ThreadSanitizer into one executable.  ``None`` when the compiler has no ThreadSanitizer runtime."""
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        return None
+    out = out or (ROOT.parent / "build" / "race_check")
+    out.parent.mkdir(parents=True, exist_ok=True)
+    cmd = [cxx, "-std=c++17", "-fsanitize=thread", "-O1", "-g", "-pthread", *[str(CSRC / f) for f in RACE_CHECK_SOURCES],
+           "-o", str(out), "-lrt"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        if "tsan" in r.stderr.lower() or "sanitize" in r.stderr.lower():
+            return None
+        raise RuntimeError(f"race check did not compile:\n{r.stderr[-2000:]}")
+    return out
+
+
+def run_race_check(timeout: float = 300.0) -> tuple[int, str]:
+    """Build and run the race check: ``(exit code, output)``; 0 = the driver's expectations held and ThreadSanitizer
+    reported nothing, 66 = ThreadSanitizer reported a race, -1 = no ThreadSanitizer here."""
+    exe = build_race_check()
+    if exe is None:
+        return -1, "no ThreadSanitizer runtime"
+    env = dict(os.environ, TSAN_OPTIONS="exitcode=66 halt_on_error=0")
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=timeout, env=env)
+    return r.returncode, (r.stdout + r.stderr)[-6000:]
+
+
 if __name__ == "__main__":
+    if "--race-check" in sys.argv:
+        rc, text = run_race_check()
+        print(text)
+        sys.exit(0 if rc in (0, -1) else rc)
     p = build(force="--force" in sys.argv, verbose="-v" in sys.argv, check="--check" in sys.argv)
     print(p)

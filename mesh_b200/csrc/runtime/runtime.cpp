@@ -44,7 +44,10 @@ typedef struct MeshStats {
   char group[64];
 } MeshStats;
 
-static MeshStats* g_stats = nullptr;
+// Counters are bumped from any thread (launch wrappers, the channel proxy, the status monitor) without a lock, also
+// while another thread stops the service: the pointer is atomic and a stopped block is never unmapped (4 KB per
+// start/stop cycle stay mapped), so a reader that loaded the pointer just before a stop still writes to valid memory.
+static std::atomic<MeshStats*> g_stats{nullptr};
 static char g_name[128];
 static std::thread g_thread;
 static std::atomic<bool> g_run{false};
@@ -67,7 +70,7 @@ static MeshStats* map_block(const char* name, int create) {
 int mesh_runtime_stop(int unlink_block);
 int mesh_runtime_start(const char* group, int rank, int world, double heartbeat_s) {
   std::lock_guard<std::mutex> lk(g_mu);
-  if (g_stats) return 0;
+  if (g_stats.load()) return 0;
   snprintf(g_name, sizeof(g_name), "/mesh_b200_%s_%d", group, rank);
   MeshStats* s = map_block(g_name, 1);
   if (!s) return -1;
@@ -80,7 +83,7 @@ int mesh_runtime_start(const char* group, int rank, int world, double heartbeat_
   snprintf(s->group, sizeof(s->group), "%s", group);
   s->heartbeat_ns.store(now_ns());
   s->abort_flag.store(0);
-  g_stats = s;
+  g_stats.store(s);
   g_run.store(true);
   static bool at_exit_installed = false;
   if (!at_exit_installed) {
@@ -90,11 +93,11 @@ int mesh_runtime_start(const char* group, int rank, int world, double heartbeat_
     atexit([] { mesh_runtime_stop(0); });
   }
   const auto period = std::chrono::milliseconds((int)(heartbeat_s > 0.01 ? heartbeat_s * 1000 : 10));
-  g_thread = std::thread([period] {
+  g_thread = std::thread([period, s] {
     while (g_run.load()) {
-      g_stats->heartbeat_ns.store(now_ns());
-      const uint64_t dl = g_stats->deadline_ns.load();
-      if (dl && now_ns() > dl) g_stats->abort_flag.store(1);
+      s->heartbeat_ns.store(now_ns());
+      const uint64_t dl = s->deadline_ns.load();
+      if (dl && now_ns() > dl) s->abort_flag.store(1);
       // sleep in short slices so that a stop request is honoured within milliseconds, not a heartbeat period
       for (auto left = period; left.count() > 0 && g_run.load(); left -= std::chrono::milliseconds(20))
         std::this_thread::sleep_for(std::min<std::chrono::milliseconds>(left, std::chrono::milliseconds(20)));
@@ -107,36 +110,39 @@ int mesh_runtime_start(const char* group, int rank, int world, double heartbeat_
 // unless `unlink` is set.
 int mesh_runtime_stop(int unlink_block) {
   std::lock_guard<std::mutex> lk(g_mu);
-  if (!g_stats) return 0;
+  MeshStats* s = g_stats.load();
+  if (!s) return 0;
   g_run.store(false);
   if (g_thread.joinable()) g_thread.join();
-  for (int i = 0; i < MESH_MAX_PEERS; ++i) g_stats->channel_state[i].store(MESH_CH_CLOSED);
-  g_stats->heartbeat_ns.store(0);
-  munmap((void*)g_stats, sizeof(MeshStats));
-  g_stats = nullptr;
+  g_stats.store(nullptr);
+  for (int i = 0; i < MESH_MAX_PEERS; ++i) s->channel_state[i].store(MESH_CH_CLOSED);
+  s->heartbeat_ns.store(0);
   if (unlink_block) shm_unlink(g_name);
   return 0;
 }
 
 void mesh_runtime_count(int what, uint64_t n, int peer) {
-  if (!g_stats) return;
+  MeshStats* s = g_stats.load();
+  if (!s) return;
   switch (what) {
-    case 0: g_stats->launches.fetch_add(n); break;
-    case 1: g_stats->collectives.fetch_add(n); break;
-    case 2: g_stats->timeouts.fetch_add(n); break;
-    case 3: if (peer >= 0 && peer < MESH_MAX_PEERS) g_stats->bytes_to_peer[peer].fetch_add(n); break;
-    case 4: g_stats->step.store(n); break;
-    case 5: g_stats->epoch.store(n); break;
+    case 0: s->launches.fetch_add(n); break;
+    case 1: s->collectives.fetch_add(n); break;
+    case 2: s->timeouts.fetch_add(n); break;
+    case 3: if (peer >= 0 && peer < MESH_MAX_PEERS) s->bytes_to_peer[peer].fetch_add(n); break;
+    case 4: s->step.store(n); break;
+    case 5: s->epoch.store(n); break;
   }
 }
 void mesh_runtime_channel(int peer, int state) {
-  if (g_stats && peer >= 0 && peer < MESH_MAX_PEERS) g_stats->channel_state[peer].store(state);
+  MeshStats* s = g_stats.load();
+  if (s && peer >= 0 && peer < MESH_MAX_PEERS) s->channel_state[peer].store(state);
 }
 void mesh_runtime_deadline(double seconds_from_now) {
-  if (g_stats) g_stats->deadline_ns.store(seconds_from_now > 0 ? now_ns() + (uint64_t)(seconds_from_now * 1e9) : 0);
+  MeshStats* s = g_stats.load();
+  if (s) s->deadline_ns.store(seconds_from_now > 0 ? now_ns() + (uint64_t)(seconds_from_now * 1e9) : 0);
 }
-int mesh_runtime_aborted(void) { return g_stats ? (int)g_stats->abort_flag.load() : 0; }
-void mesh_runtime_abort(int v) { if (g_stats) g_stats->abort_flag.store((uint64_t)v); }
+int mesh_runtime_aborted(void) { MeshStats* s = g_stats.load(); return s ? (int)s->abort_flag.load() : 0; }
+void mesh_runtime_abort(int v) { MeshStats* s = g_stats.load(); if (s) s->abort_flag.store((uint64_t)v); }
 
 // Read-only view of any rank's block (what `meshctl status` prints).  Returns 0, or -1 when absent.
 int mesh_runtime_read(const char* group, int rank, uint64_t* out /*[16 + 2*MESH_MAX_PEERS]*/) {
