@@ -24,6 +24,29 @@ def count_launch(n: int = 1) -> None:
     if on_launch is not None:
         on_launch(n)
 
+
+class nvtx:
+    """``with nvtx("name"):`` opens an NVTX range around the block when ``MESH_NVTX=1`` (ranges show up in any tool
+    that reads NVTX; off, the block costs one environment lookup at import).  The reference brackets its phases for its
+    own ledger (``MESH_LEDGER``); these are the same phases named for external profilers."""
+    enabled = __import__("os").environ.get("MESH_NVTX", "0") == "1"
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if nvtx.enabled:
+            import torch
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if nvtx.enabled:
+            import torch
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 MAX_RANKS = 8
 
 

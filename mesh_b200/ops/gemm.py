@@ -63,7 +63,11 @@ def _launch(args: _native.GemmArgs) -> None:
     if _trace is not None:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-    rc = _native.lib().mesh_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_stream()))
+    if _native.nvtx.enabled:
+        with _native.nvtx(_label(args)):
+            rc = _native.lib().mesh_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_stream()))
+    else:
+        rc = _native.lib().mesh_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_stream()))
     _native.check(rc, "mesh_gemm_bf16")
     _native.count_launch()
     if _trace is not None:

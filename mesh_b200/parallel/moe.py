@@ -154,6 +154,8 @@ class EPMoE:
     timeline: list | None = None      # set to [] to record a CUDA event after every phase of forward / backward
 
     def _mark(self, name: str) -> None:
+        if _native.nvtx.enabled:                  # an NVTX marker at the end of every phase
+            torch.cuda.nvtx.mark("moe: " + name)
         if self.timeline is not None:
             e = torch.cuda.Event(enable_timing=True)
             e.record()

@@ -68,3 +68,22 @@ def test_imported_name_exists(key, where):
         importlib.import_module(f"{mod}.{name}")          # ``from package import submodule``
     except ImportError:
         pytest.fail(f"{where} imports {name!r} from {mod}, which does not define it")
+
+
+def test_nvtx_ranges_are_balanced_and_off_by_default(monkeypatch):
+    """``MESH_NVTX=1`` brackets launches with NVTX ranges; off, nothing touches the NVTX calls."""
+    import torch
+
+    from mesh_b200 import _native
+    calls = []
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: calls.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: calls.append(("pop", None)))
+    monkeypatch.setattr(_native.nvtx, "enabled", False)
+    with _native.nvtx("quiet"):
+        pass
+    assert calls == []
+    monkeypatch.setattr(_native.nvtx, "enabled", True)
+    with _native.nvtx("outer"):
+        with _native.nvtx("inner"):
+            pass
+    assert calls == [("push", "outer"), ("push", "inner"), ("pop", None), ("pop", None)]
