@@ -332,3 +332,62 @@ def calls(program: torch.nn.Module, args: tuple, functions, **options) -> tuple[
             if qual in counts:
                 counts[qual].add(key)
     return exp, {k: max(1, len(v)) for k, v in counts.items()}
+
+
+# ----------------------------------------------------------------------------- substitution of a function by parts
+class Parts(torch.nn.Module):
+    """What a substituted function becomes: its parts called in order.  ``wiring[p]`` lists where part ``p`` takes each
+    input from - ``("call", i)``: input ``i`` of the original call; ``("part", q, o)``: output ``o`` of the earlier part
+    ``q`` - and ``results[k] = (p, o)`` names the part output that is output ``k`` of the original call."""
+
+    def __init__(self, parts, wiring, results):
+        super().__init__()
+        self.names = [name for name, _ in parts]
+        for name, m in parts:
+            self.add_module(name, m)
+        self.wiring = [list(w) for w in wiring]
+        self.results = list(results)
+
+    def forward(self, *args):
+        made: list[tuple] = []
+        for name, inputs in zip(self.names, self.wiring):
+            argv = [args[s[1]] if s[0] == "call" else made[s[1]][s[2]] for s in inputs]
+            out = getattr(self, name)(*argv)
+            made.append(tuple(out) if isinstance(out, (tuple, list)) else (out,))
+        outs = tuple(made[p][o] for p, o in self.results)
+        return outs[0] if len(outs) == 1 else outs
+
+
+def substitute(program: torch.nn.Module, key, parts, results=None) -> int:
+    """Replace every call of the function ``key`` in ``program`` by calls of ``parts``, in order, and return how many
+    were replaced.  ``key``: a submodule's qualified name, a module class, or a predicate over ``(name, module)``.
+    ``parts``: ``[(name, module, inputs)]`` with ``inputs`` as in :class:`Parts`; a module given as a callable
+    ``make(original)`` is built per replaced call (so that parts can take over the original's parameters).
+    ``results``: which part outputs are the original call's outputs (default: all outputs of the last part).
+
+    The reference rewrites its call graph in place (compiler/mesh_compiler/export.py:525-640: every call of ``key``
+    becomes the calls of ``parts``, an input a call input or an earlier part's output, ``results`` mapping part outputs
+    to the call's outputs) and uses it to outline iterative linear algebra into repeated calls of one step
+    (compiler/mesh_compiler/decompose.py).  Here calls are inlined at capture and every node remembers the submodule it
+    came from, so the rewrite happens one level up, on the module tree, before the capture: the captured graph then
+    carries the parts as call instances of their own (``calls.analyse`` sees them, placements can name them)."""
+    def matches(name, m):
+        if isinstance(key, str):
+            return name == key
+        if isinstance(key, type):
+            return isinstance(m, key)
+        return bool(key(name, m))
+
+    found = [(name, m) for name, m in program.named_modules() if name and matches(name, m)]
+    # a match inside another match would be replaced with its parent: keep outermost ones only
+    found = [(n, m) for n, m in found if not any(n.startswith(o + ".") for o, _ in found)]
+    for name, original in found:
+        built = [(pname, (make(original) if not isinstance(make, torch.nn.Module) else make)) for pname, make, _ in parts]
+        wiring = [inputs for _, _, inputs in parts]
+        res = results
+        if res is None:
+            res = [(len(parts) - 1, 0)]
+        parent_name, _, leaf = name.rpartition(".")
+        parent = program.get_submodule(parent_name) if parent_name else program
+        setattr(parent, leaf, Parts(built, wiring, res))
+    return len(found)

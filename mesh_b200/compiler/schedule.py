@@ -103,6 +103,9 @@ def schedule(plan: Plan, cost=unit_cost) -> tuple[Signature, dict]:
         "duplicated": getattr(plan, "duplicated", 0),
         "signature": sig.digest,
     }
+    cp = copies(plan)
+    structure["writes"] = len(cp.index)                    # distinct staged writes behind the transfers
+    structure["shared_writes"] = len(plan.transfers) - len(cp.index) if plan.transfers else 0
     return sig, structure
 
 
@@ -227,3 +230,47 @@ def horizon(plan: Plan, copies: int) -> int:
     start writing its inputs before execution ``t`` has read them, so at most ``copies`` executions overlap; a plan
     with no input at all (constants only) is bounded by its collectives' lag-1 edges, which stream order satisfies."""
     return max(1, copies)
+
+
+# ----------------------------------------------------------------------------- copies: transfers that share one write
+@dataclass
+class Copies:
+    """Transfers grouped by what they send: ``group[channel]`` is the key of a transfer (the value it sends, on which
+    axis and in which form it leaves), ``index[key]`` numbers the distinct keys in plan order, ``member[k]`` lists the
+    channels that share write ``k``.  Every collective here first copies its operand into this rank's staging buffer
+    (publish, then the readers pull): transfers in one group publish the same bytes, so only the first member needs
+    the copy and the later ones can raise their signals on it, provided nothing rewrote the staging slot in between
+    (``reusable`` counts the members for which that holds: no other transfer on the same axis between them)."""
+    group: dict
+    index: dict
+    member: dict
+    reusable: int = 0
+
+
+def copies(plan: Plan) -> Copies:
+    """The logical copies of a plan's declared transfers (the reference groups its SENDs the same way before planning:
+    each distinct (source, wire value, sent view, writers) is one write of its members,
+    compiler/mesh_compiler/lower_inductor.py:7-32)."""
+    produced = {}
+    for i, st in enumerate(plan.steps):
+        produced[st.out] = i
+    group, order = {}, []
+    for d in declarations(plan):
+        st = plan.steps[d.at]
+        # what leaves: the value, the axis it travels on, the verb's sending form (a gather and a broadcast of one value
+        # both publish the whole local block; a scatter or an all-to-all publishes it cut for its readers)
+        form = "cut" if d.verb in ("scatter", "all_to_all", "reduce_scatter", "mm_rs") else "whole"
+        key = (d.value, d.axis, form, produced.get(d.value, -1))
+        group[d.channel] = key
+        order.append((d.at, d.channel, d.axis, key))
+    index = {key: k for k, key in enumerate(dict.fromkeys(group.values()))}
+    member: dict[int, list] = {}
+    for ch, key in group.items():
+        member.setdefault(index[key], []).append(ch)
+    reusable = 0
+    last_on_axis: dict[int, tuple] = {}
+    for _, ch, axis, key in sorted(order):
+        if last_on_axis.get(axis) == key:
+            reusable += 1
+        last_on_axis[axis] = key
+    return Copies(group, index, member, reusable)

@@ -78,3 +78,73 @@ def test_compile_program_reports_the_analysis():
                           lambda node: (0, names, None) if node.op == "placeholder" and node.name in ("x", "y") else None)
     rep = sch.structure["call_analysis"]
     assert rep["calls"] == 4 and rep["width"] == 2 and sch.structure["function_calls"] == {"a": 2, "b": 1, "t": 1}
+
+
+def test_substitute_replaces_every_call_of_a_function_by_its_parts():
+    """A block function replaced by two parts that take over its parameters: same numbers, the parts are call
+    instances of their own in the captured program, and the program still compiles and runs cut over two processors."""
+    import torch
+
+    from mesh_b200.compiler import calls as C
+    from mesh_b200.compiler.export import Parts, calls, substitute
+
+    class Block(torch.nn.Module):
+        def __init__(self, d):
+            super().__init__()
+            self.lin = torch.nn.Linear(d, d)
+
+        def forward(self, x, gate):
+            return torch.tanh(self.lin(x)) * gate, x
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = Block(16), Block(16)
+
+        def forward(self, x, gate):
+            y, _ = self.a(x, gate)
+            z, skip = self.b(y, gate)
+            return z + skip
+
+    class Project(torch.nn.Module):
+        def __init__(self, lin):
+            super().__init__()
+            self.lin = lin
+
+        def forward(self, x):
+            return self.lin(x)
+
+    class Gate(torch.nn.Module):
+        def forward(self, h, gate):
+            return torch.tanh(h) * gate
+
+    torch.manual_seed(0)
+    net = Net()
+    x, gate = torch.randn(4, 16), torch.randn(4, 16)
+    want = net(x, gate)
+    n = substitute(net, Block, [("project", lambda blk: Project(blk.lin), [("call", 0)]),
+                                ("gate", lambda blk: Gate(), [("part", 0, 0), ("call", 1)])],
+                   results=[(1, 0), (0, 0)])
+    assert n == 2 and isinstance(net.a, Parts) and isinstance(net.b, Parts)
+    # output 1 of the original call was x itself; the substitution's second result is the projection instead, so the
+    # network's skip term changes on purpose: state what it must be
+    h1 = torch.tanh(net.a.project(x)) * gate
+    lin2 = net.b.project(h1)
+    assert torch.allclose(net(x, gate), torch.tanh(lin2) * gate + lin2, atol=1e-6)
+    assert not torch.allclose(net(x, gate), want)
+    # results that keep the original meaning: the pass-through output comes straight from the call's input
+    net2 = Net()
+    net2.load_state_dict({k.replace(".project.lin.", ".lin."): v for k, v in net.state_dict().items()})
+    want2 = net2(x, gate)
+
+    class Pass(torch.nn.Module):
+        def forward(self, x):
+            return x
+    substitute(net2, Block, [("project", lambda blk: Project(blk.lin), [("call", 0)]),
+                             ("gate", lambda blk: Gate(), [("part", 0, 0), ("call", 1)]),
+                             ("keep", lambda blk: Pass(), [("call", 0)])], results=[(1, 0), (2, 0)])
+    assert torch.allclose(net2(x, gate), want2, atol=1e-6)
+    exp, counts = calls(net2, (x, gate), ["a.project", "a.gate", "b.project", "b.gate"])
+    assert counts == {"a.project": 1, "a.gate": 1, "b.project": 1, "b.gate": 1}
+    an = C.analyse(exp, ["a.project", "a.gate", "b.project", "b.gate"])
+    assert len(an.calls) == 4

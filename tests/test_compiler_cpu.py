@@ -604,3 +604,28 @@ def test_invariant_values_are_recomputed_where_they_are_read():
     assert not any(v.startswith(("mul", "sin", "arange", "div")) and not v.startswith("mul_1") for v in moved), moved
     out = Program(sch, threads=True)(x)
     assert torch.allclose(out, m(x), atol=1e-6)
+
+
+def test_transfers_that_send_one_value_share_a_write():
+    """Two transfers that publish the same value on one axis are one staged write with two members; an unrelated
+    transfer is a write of its own; the structure report counts both."""
+    from mesh_b200.compiler import schedule as S
+    from mesh_b200.compiler.ir import Mesh, Plan, Ref, Step, Transfer
+
+    def coll(verb, out, src, channel, kind):
+        return Step("collective", out, verb, (Ref(src),), {}, {"axis": 0, "kind": kind, "to": None, "from": None, "channel": channel})
+    steps = [Step("call", "h", "t", (Ref("x"),)),
+             coll("all_gather", "h_all", "h", 0, "broadcast"),
+             coll("broadcast", "h_b", "h", 1, "broadcast"),
+             Step("call", "g", "u", (Ref("h_all"), Ref("h_b"))),
+             coll("all_reduce", "g_sum", "g", 2, "reduce")]
+    transfers = [Transfer(0, "broadcast", "all_gather", 0, "h", 0, (), nbytes=1024),
+                 Transfer(1, "broadcast", "broadcast", 0, "h", 0, (), nbytes=1024),
+                 Transfer(2, "reduce", "all_reduce", 0, "g", 0, (), nbytes=64)]
+    plan = Plan(Mesh(("a", "b"), (2,)), steps, ["x"], {}, ["g_sum"], {}, transfers, {}, {})
+    cp = S.copies(plan)
+    assert len(cp.index) == 2
+    assert sorted(map(sorted, cp.member.values())) == [[0, 1], [2]]
+    assert cp.reusable == 1
+    _, structure = S.schedule(plan)
+    assert structure["writes"] == 2 and structure["shared_writes"] == 1
