@@ -351,12 +351,29 @@ class Executor:
                 return type(a)(val(x) for x in a)
             return a
 
+        # values with a destination are computed straight into the storage of the concatenation that reads them
+        from . import destine
+        dest = self.__dict__.get("_destinations")
+        if dest is None:
+            dest = self._destinations = destine.analyse(self.plan) if destine.enabled() else {}
+        parents: dict[str, dict] = {}                    # concatenation -> {"buf", "slots", "filled"} for this execution
+        self.destined = 0
         for index, st in enumerate(self.plan.steps):
             if self.times is not None:
                 if self.device.type == "cuda":
                     torch.cuda.synchronize(self.device)
                 t0 = time.perf_counter()
-            if st.op == "const":
+            if st.out in dest and st.op == "call":
+                env[st.out] = self._call_into(st, val, dest[st.out], parents)
+            elif st.op == "call" and st.out in parents:
+                # a concatenation all of whose pieces were written in place: its storage is the result
+                rec = parents.pop(st.out)
+                if rec["buf"] is not None and rec["filled"] == len(rec["slots"]):
+                    env[st.out] = rec["buf"]
+                    self.destined += 1
+                else:
+                    env[st.out] = self.call(st, val)
+            elif st.op == "const":
                 env[st.out] = self._here(consts(st.target))
             elif st.op == "alias":
                 env[st.out] = env[st.args[0].name]
@@ -538,6 +555,51 @@ class Executor:
             return x, torch.ones_like(x, dtype=torch.bool)
         keep = u >= p
         return torch.where(keep, x / (1 - p), torch.zeros((), dtype=x.dtype, device=x.device)), keep
+
+    def _call_into(self, st: Step, val, d, parents: dict):
+        """Run a pointwise step whose result is piece ``d.position`` of the concatenation ``d.parent``: the parent's
+        storage is laid out when its first piece arrives (every piece's local shape follows from the cut recorded for
+        it), and the step writes into its slice through the operator's ``out=`` form.  Whatever does not fit (an operand
+        on another processor, a shape that differs from the recorded one) falls back to the plain call, and the
+        concatenation then runs as usual."""
+        from . import destine
+        rec = parents.get(d.parent)
+        if rec is None:
+            rec = parents[d.parent] = {"buf": None, "slots": None, "filled": 0}
+            try:
+                metas = [next(s for s in self.plan.steps if s.out == name).meta for name in d.pieces]
+                shapes = [destine.local_shape(m, self.coords) for m in metas]
+                base = list(shapes[0])
+                if all(len(sh) == len(base) and all(a == b for k, (a, b) in enumerate(zip(sh, base)) if k != d.dim) for sh in shapes):
+                    base[d.dim] = sum(sh[d.dim] for sh in shapes)
+                    rec["buf"] = torch.empty(base, dtype=self.plan.dtypes[d.parent], device=self.device)
+                    at, slots = 0, []
+                    for sh in shapes:
+                        slots.append(rec["buf"].narrow(d.dim, at, sh[d.dim]))
+                        at += sh[d.dim]
+                    rec["slots"] = slots
+            except (StopIteration, KeyError):
+                rec["buf"] = None
+        if rec["buf"] is None:
+            return self.call(st, val)
+        args = [val(a) for a in st.args]
+        kwargs = {k: val(v) for k, v in st.kwargs.items()}
+        if any(a is None for a, r in zip(args, st.args) if isinstance(r, Ref)):
+            rec["buf"] = None
+            return None
+        if "device" in kwargs and kwargs["device"] is not None:
+            kwargs["device"] = self.device
+        view = rec["slots"][d.position]
+        try:
+            shape = torch.broadcast_shapes(*[tuple(a.shape) for a in args if isinstance(a, torch.Tensor)])
+        except RuntimeError:
+            shape = None
+        if shape != tuple(view.shape):
+            rec["buf"] = None                              # not the recorded shape: no destination for this parent
+            return st.target(*args, **kwargs)
+        st.target.overloadpacket.out(*args, **kwargs, out=view)
+        rec["filled"] += 1
+        return view
 
     def call(self, st: Step, val):
         args = list(val(a) for a in st.args)

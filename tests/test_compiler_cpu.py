@@ -629,3 +629,40 @@ def test_transfers_that_send_one_value_share_a_write():
     assert cp.reusable == 1
     _, structure = S.schedule(plan)
     assert structure["writes"] == 2 and structure["shared_writes"] == 1
+
+
+def test_pieces_of_a_concatenation_are_computed_in_place():
+    """A rotary-style rotation (two pointwise halves, concatenated) under a batch cut: both halves have a destination,
+    the concatenation runs without a copy (its result is the storage the halves were written into), and the numbers
+    are those of eager execution; with the switch off nothing has a destination."""
+    from mesh_b200.compiler import destine
+
+    class Rotate(torch.nn.Module):
+        def forward(self, x, c, s):
+            a, b = x[..., :8], x[..., 8:]
+            return torch.cat([a * c - b * s, b * c + a * s], -1) * 2.0
+
+    torch.manual_seed(0)
+    x, c, s = torch.randn(6, 4, 16), torch.randn(4, 8), torch.randn(4, 8)
+    want = Rotate()(x, c, s)
+    procs = _procs(2)
+
+    def run(expect):
+        sch = compile_module(Rotate(), (x, c, s), procs, data_parallel(procs))
+        prog = Program(sch)
+        got = prog(x, c, s)
+        got = got[0] if isinstance(got, (tuple, list)) else got
+        assert torch.allclose(got, want, atol=1e-6)
+        execs = [r[0] for r in prog.per_rank if r is not None] if getattr(prog, "per_rank", None) else [prog.exec]
+        assert all(e.destined == expect for e in execs)
+        return sch
+
+    sch = run(1)
+    found = destine.analyse(sch.plan)
+    assert len(found) == 2 and len({d.parent for d in found.values()}) == 1
+    import os
+    os.environ["MESH_DESTINED"] = "0"
+    try:
+        run(0)
+    finally:
+        del os.environ["MESH_DESTINED"]
