@@ -3,11 +3,13 @@
 // A decoder step is ~150 small dependent operations (per layer: QKV projection, attention, output projection, GLU,
 // down projection; then the vocabulary projection and the selection).  Launched one by one, every boundary costs a
 // launch, a ramp of CTAs, the staging of x and a drained memory pipeline: at batch 1 that, not HBM, bounds the step.
-// Here a persistent grid (as many CTAs as are resident at once) walks a list of operations; every CTA takes its share
-// of each, and a grid barrier with split arrive / wait separates them: a CTA arrives when its share is written,
-// requests the first weights of the next layer (they depend on nothing computed here) and only then waits, so HBM
-// keeps streaming across the boundaries.  The layers are the bodies the stand-alone kernels run (decode_linear.cuh,
-// decode_attention.cuh), so the results are theirs bit for bit.
+// Here a persistent grid (one CTA per SM, launched cooperatively) walks a list of operations; every CTA takes its share
+// of each, and a grid barrier with split arrive / wait separates them.  Eight warps of a CTA compute; a ninth streams
+// the weights of ALL layers, in order, through a ring of stages in shared memory (cp.async.bulk, one copy per weight
+// row and stage, completion counted on an mbarrier) and is held back only by the ring's capacity, never by a barrier,
+// so HBM keeps streaming while the computing warps wait for the layer before, stage x and reduce.  The layers are the
+// arithmetic of the stand-alone kernels (decode_linear.cuh, decode_attention.cuh) with the sums over k taken stage by
+// stage, so the results agree with theirs to rounding.
 //
 // Reference counterpart: the prepared machine that runs a whole decoder step without returning to the host between
 // layers (design/prepared-machine.md; rdma/mesh-dataflow.c:287-317 starts it once and lets signals order the parts).

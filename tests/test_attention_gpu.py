@@ -45,7 +45,7 @@ def test_flash_fused_qkv_view_and_striped_positions():
     _close(o, o_full)
 
 
-def _ring_rank(rank, world, rdv, striped):
+def _ring_rank(rank, world, rdv, striped, overlap=False):
     from mesh_b200.config import MeshConfig, set_config
     from mesh_b200.distributed.context import MeshContext
     from mesh_b200.ops.attention import attention_ref, ring_attention
@@ -57,7 +57,9 @@ def _ring_rank(rank, world, rdv, striped):
     g = torch.Generator(device="cpu").manual_seed(0)
     q, k, v = (torch.randn(B, T, H, hd, generator=g).bfloat16().cuda() for _ in range(3))
     sl = slice(rank, T, world) if striped else slice(rank * (T // world), (rank + 1) * (T // world))
-    o, _ = ring_attention(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous(), ctx.comm, causal=True, striped=striped)
+    o, _ = ring_attention(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous(), ctx.comm, causal=True,
+                          striped=striped, overlap=overlap)
+    torch.cuda.synchronize()
     check_status()
     ref, _ = attention_ref(q, k, v, True)
     _close(o, ref[:, sl])
@@ -65,12 +67,14 @@ def _ring_rank(rank, world, rdv, striped):
     ctx.heap.close()
 
 
+@pytest.mark.parametrize("overlap", [False, True])
 @pytest.mark.parametrize("striped", [False, True])
-def test_ring_attention_two_ranks(striped):
+def test_ring_attention_two_ranks(striped, overlap):
+    """``overlap``: the next KV chunk travels on a side stream under the attention of the current one."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from mesh_b200.utils.launch import spawn_ranks
-    spawn_ranks(_ring_rank, 2, striped, use_cuda=True, timeout=300.0)
+    spawn_ranks(_ring_rank, 2, striped, overlap, use_cuda=True, timeout=300.0)
 
 
 def _ref_grads(q, k, v, dout, causal, window):
