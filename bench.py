@@ -233,7 +233,23 @@ def main() -> int:
             device_step(arm)
     barrier()
     sampler = ClockSampler(physical_gpu_index(dev.index))
-    sampler.start()
+    if rank == 0:
+        sampler.start()
+    # nvidia-smi needs up to a second to come up and holds driver locks while it does (launches issued meanwhile were
+    # seen to stall: a 20-step region of 8 ms steps next to 3.3 ms steps in the blocks after it): the same load keeps
+    # running, untimed, until the sampler has delivered its first line; its 50 ms queries then run through the timed
+    # region as required
+    t_up = time.perf_counter() + 5.0
+    while True:
+        need = torch.tensor([int(rank == 0 and sampler.proc is not None and sampler.count() < 1 and time.perf_counter() < t_up)],
+                            device=dev)
+        if world > 1:
+            dist.broadcast(need, 0)
+        if not int(need):
+            break
+        for _ in range(5):
+            device_step(arms[main_arm])
+        torch.cuda.synchronize()
     launches0 = _native.launch_count
     barrier()
     t_wall0 = time.perf_counter()
