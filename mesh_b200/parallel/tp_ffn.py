@@ -96,10 +96,15 @@ def shared_zone(heap, cls, *shape):
 class FusedTPFFN:
     """Holds the symmetric workspaces of one (M, D, F) FFN shape and runs its six fused kernels.
 
-    ``w_gate_up``: this rank's ``[2*F/world, D]`` (gate rows, then up rows); ``w_down``: ``[D, F/world]``.
+    ``w_gate_up``: this rank's ``[2*Fl, D]`` (gate rows, then up rows); ``w_down``: ``[D, Fl]``, with ``Fl = F / world``
+    or, for unequal shares of the hidden units (heterogeneous ranks, ``runtime/allocate.py``), ``ff_local``: any
+    multiple of 64; the ranks' shares add up to ``F``.  The hidden width is a local dimension of every kernel here (the
+    gathered and scattered dimension is the tokens'), so ranks with different shares run the same six launches and only
+    differ in how long they compute.
     """
 
-    def __init__(self, heap: SymmetricHeap, tokens: int, d_model: int, d_ff: int, act: str = "silu", in_flight: int = 1):
+    def __init__(self, heap: SymmetricHeap, tokens: int, d_model: int, d_ff: int, act: str = "silu", in_flight: int = 1,
+                 ff_local: int | None = None):
         self.heap = heap
         self.rank, self.world = heap.rank, heap.world
         self.M, self.D, self.F = tokens, d_model, d_ff
@@ -107,10 +112,14 @@ class FusedTPFFN:
         P = self.world
         if tokens % (P * BM):
             raise ValueError(f"tokens ({tokens}) must be a multiple of world*128")
-        if d_ff % P or (d_ff // P) % 64 or d_model % 64:
-            raise ValueError("d_ff/world and d_model must be multiples of 64")
+        if ff_local is None:
+            if d_ff % P:
+                raise ValueError("d_ff must be a multiple of the world size (or pass ff_local)")
+            ff_local = d_ff // P
+        if ff_local % 64 or ff_local <= 0 or d_model % 64:
+            raise ValueError("this rank's share of d_ff and d_model must be multiples of 64")
         self.rows = tokens // P
-        self.Fl = d_ff // P
+        self.Fl = ff_local
         self.x_full = _Gathered(heap, tokens, d_model, copies=in_flight + 1)
         self.dy_full = shared_zone(heap, _Gathered, tokens, d_model)
         self.y_recv = shared_zone(heap, _Scattered, P, self.rows, d_model)

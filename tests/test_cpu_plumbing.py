@@ -74,6 +74,14 @@ def _ffn_rank(rank, world, rdv):
     assert (ysp - ys[rank * rows:(rank + 1) * rows]).abs().max() / ys.abs().max() < 1e-5
 
 
+    # unequal shares of the hidden units (a rank three times the other): the same layer
+    shares = [3072, 1024]
+    un = TPGatedFFN(1024, 4096, ctx, dtype=torch.float32, seed=3, sequence_parallel=True, ff_shares=shares)
+    assert un.w_down.shape == (1024, shares[rank])
+    yun = un(x[rank * rows:(rank + 1) * rows])
+    assert (yun - ys[rank * rows:(rank + 1) * rows]).abs().max() / ys.abs().max() < 1e-5
+
+
 def test_tp2_swiglu_ffn_matches_single_device():
     spawn_ranks(_ffn_rank, 2, init_pg="gloo")
 

@@ -28,7 +28,7 @@ def _close(got, want, tol=8e-3):
     assert_close_rms(got, want, tol=tol)
 
 
-def _run_rank(rank, world, rdv, M, D, F, steps):
+def _run_rank(rank, world, rdv, M, D, F, steps, shares=None):
     from mesh_b200.parallel.tp_ffn import FusedTPFFN
     from mesh_b200.runtime.heap import SymmetricHeap
     from mesh_b200.utils.status import check_status
@@ -37,13 +37,15 @@ def _run_rank(rank, world, rdv, M, D, F, steps):
     heap = SymmetricHeap(rdv, 256 << 20, rank)
     x, wg, wu, wd, dy = _full_problem(M, D, F)
     y_ref, dx_ref, dwg_ref, dwu_ref, dwd_ref = _reference(x, wg, wu, wd, dy)
-    rows, Fl = M // world, F // world
+    rows = M // world
+    shares = list(shares) if shares else [F // world] * world          # hidden units per rank
+    Fl = shares[rank]
     sl = slice(rank * rows, (rank + 1) * rows)
-    fs = slice(rank * Fl, (rank + 1) * Fl)
+    fs = slice(sum(shares[:rank]), sum(shares[:rank + 1]))
     wgu_l = torch.cat([wg[fs], wu[fs]], 0).to(dev)
     wd_l = wd[:, fs].contiguous().to(dev)
     x_l, dy_l = x[sl].to(dev), dy[sl].to(dev)
-    op = FusedTPFFN(heap, M, D, F)
+    op = FusedTPFFN(heap, M, D, F, ff_local=Fl)
     for _ in range(steps):   # repeated steps exercise the parity buffers and monotonic counters
         y = op.forward(x_l, wgu_l, wd_l)
         dx, dwgu, dwd = op.backward(dy_l)
@@ -79,3 +81,11 @@ def test_fused_tp_ffn_multi(world):
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_run_rank, world, 128 * world * 2, 256, 64 * world * 2, 3, use_cuda=True, timeout=300.0)
     spawn_ranks(_run_rank, world, 4096, 1024, 1792 * world, 2, use_cuda=True, timeout=300.0)
+
+
+def test_fused_tp_ffn_unequal_hidden_shares():
+    """Two ranks with different shares of the hidden units (1024 and 512 of 1536): the same kernels, the same numbers."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_run_rank, 2, 1024, 512, 1536, 2, (1024, 512), use_cuda=True, timeout=300.0)
