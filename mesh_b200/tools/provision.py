@@ -65,7 +65,7 @@ def desired(gpus: int, keys: str | None, python: str = sys.executable, prefix: s
         text = Path(keys).read_text()
         if not text.endswith("\n"):
             text += "\n"
-        items.append(Item("/root/.ssh/authorized_keys.d/mesh_fleet", text, 0o600, "keys the fleet commands log in with"))
+        items.append(Item("/etc/ssh/authorized_keys.d/mesh_fleet", text, 0o600, "keys the fleet commands log in with"))
     return items
 
 

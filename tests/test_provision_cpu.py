@@ -47,13 +47,13 @@ def test_provision_reports_then_converges_and_is_idempotent(tmp_path):
     root = tmp_path / "root"
     items = P.desired(2, str(keys))
     assert {i.path for i in items} >= {"/etc/mesh_b200/env", "/etc/systemd/system/mesh-telemetry.service",
-                                       "/etc/systemd/system/mesh-hourly.timer", "/root/.ssh/authorized_keys.d/mesh_fleet"}
+                                       "/etc/systemd/system/mesh-hourly.timer", "/etc/ssh/authorized_keys.d/mesh_fleet"}
     first = P.diff(items, root)
     assert len(first) == len(items) and all(c["change"] == "create" for c in first)
     assert not root.exists()                                   # a report writes nothing
     done = P.apply(items, root)
     assert len(done) == len(items)
-    assert (root / "root/.ssh/authorized_keys.d/mesh_fleet").stat().st_mode & 0o777 == 0o600
+    assert (root / "etc/ssh/authorized_keys.d/mesh_fleet").stat().st_mode & 0o777 == 0o600
     assert "mesh_b200.tools.telemetry" in (root / "etc/systemd/system/mesh-telemetry.service").read_text()
     assert P.diff(items, root) == [] and P.apply(items, root) == []          # converged: nothing left to do
     (root / "etc/mesh_b200/env").write_text("MESH_GPUS=1\n")                   # drift is found and repaired
