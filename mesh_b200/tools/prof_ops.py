@@ -4,6 +4,9 @@
     python -m mesh_b200.tools.prof_ops glu_fwd | glu_bwd | rmsnorm | rope | router
     python -m mesh_b200.tools.prof_ops flash_fwd | flash_bwd --m <seq> --n <heads> --k <head_dim> [--time]
     python -m mesh_b200.tools.prof_ops decode_linear --m <batch> --n <out rows> --k <in cols> [--time]
+    python -m mesh_b200.tools.prof_ops e2b_decode --m <batch> [--n 4] [--k <position>]    (the last step is bracketed
+                                       with cudaProfilerStart/Stop for `ncu --profile-from-start off`)
+    python -m mesh_b200.tools.prof_ops e2b_step_timeline --m <batch> [--n 4|8]             (step kernel, per-operation times)
 
 Sizes are chosen larger than L2 (126 MB) in total footprint where DRAM figures matter but a few
 hundred MB at most, so a full-metric capture of one or two launches ends by itself in about a minute.
@@ -124,10 +127,44 @@ def main() -> None:
         m = E2BDecoder(E2BConfig(), ctx, a.m if a.m <= 8 else 1, "w4" if a.n == 4 else "bf16")
         prompt = torch.randint(0, 262144, (m.B, 64), dtype=torch.int32, device=dev)
         m.prefill(prompt)
-        m.pos.fill_(600)
+        if a.k != 4096:
+            m.pos.fill_(a.k)                              # --k <position>: how many keys the attention sees
         torch.cuda.synchronize()
         for _ in range(a.iters):
             m._decode_step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()                       # with `ncu --profile-from-start off`: only this step is listed
+        m._decode_step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    elif a.op == "e2b_step_timeline":
+        # the decode step as one cooperative kernel: per kind of operation, microseconds on the first CTA (device clock)
+        import collections
+        import json
+        import torch.distributed as dist
+        from mesh_b200.distributed.context import MeshContext
+        from mesh_b200.models.e2b import E2BConfig, E2BDecoder
+        from mesh_b200.runtime.rendezvous import Rendezvous
+        ctx = MeshContext(0, 1, torch.device("cuda", 0), Rendezvous(dist.HashStore(), 0, 1), None)
+        m = E2BDecoder(E2BConfig(), ctx, a.m if a.m <= 8 else 1, {4: "w4", 8: "w8"}.get(a.n, "bf16"))
+        prompt = torch.randint(0, 262144, (m.B, 512), dtype=torch.int32, device=dev)
+        m.prefill(prompt)
+        m.capture("step")
+        m.decode(5, record=False)
+        torch.cuda.synchronize()
+        tl = m.stepk.timeline()
+        agg: dict = collections.OrderedDict()
+        prev_end = 0.0
+        for r in tl:
+            d = agg.setdefault(r["op"], {"n": 0, "body_us": 0.0, "waited_us": 0.0, "gap_us": 0.0})
+            d["n"] += 1
+            d["body_us"] += r["end_us"] - r["start_us"]
+            d["waited_us"] += r["waited_us"]
+            d["gap_us"] += r["start_us"] - prev_end
+            prev_end = r["end_us"]
+        print(json.dumps({"weights": m.quant, "batch": m.B, "grid": m.stepk.grid, "smem": m.stepk.smem,
+                          "step_us": round(tl[-1]["end_us"], 1),
+                          "per_kind": {k: {x: round(y, 1) for x, y in v.items()} for k, v in agg.items()}}))
     else:
         raise SystemExit(f"unknown op {a.op}")
     check_status()
