@@ -10,6 +10,8 @@ the same inputs, so nothing needs to be exchanged.
 """
 from __future__ import annotations
 
+import math
+
 from . import export as _export
 from .ir import Scheduled
 from .placement import place
@@ -31,7 +33,37 @@ def compile_module(module, args, processors, placement, cost=unit_cost, planning
                    kwargs=None, **export_options) -> Scheduled:
     """Ahead-of-time compile of one module call.  ``loss=<flat output index>`` compiles forward+backward."""
     exported = _export.export(module, args, kwargs, **export_options)
+    if not exported.training and "inner_cuts" not in export_options and _cuts_inner_dimension(exported, placement):
+        # an input cut along an inner leading dimension (the batch of a sequence-first layout): capture again with the
+        # linear layers' leading dimensions kept apart, or the cut would be lost at the first flattening view
+        exported = _export.export(module, args, kwargs, inner_cuts=True, **export_options)
     return compile_captured(exported, processors, placement, cost, mesh)
+
+
+def _cuts_inner_dimension(exported, placement) -> bool:
+    """Does the stated placement cut a user input of three or more dimensions along a dimension that is neither its
+    last nor, once dimensions of size one are set aside, its first?  (A cut behind leading dimensions of size one is
+    still the outermost factor of the merged rows, which the view rule describes.)"""
+    if not callable(placement):
+        return False
+    for node in exported.graph_module.graph.nodes:
+        if node.op != "placeholder":
+            continue
+        val = node.meta.get("val")
+        nd = getattr(val, "ndim", 0)
+        if nd < 3:
+            continue
+        try:
+            stated = placement(node)
+        except Exception:
+            continue
+        if stated is None:
+            continue
+        for item in (stated if isinstance(stated, list) else [stated]):
+            dim = item[0] if isinstance(item, tuple) and item and isinstance(item[0], int) else None
+            if dim is not None and 0 < dim % nd < nd - 1 and math.prod(val.shape[:dim % nd]) > 1:
+                return True
+    return False
 
 
 def compile_program(program, args, functions, processors, placement, cost=unit_cost, planning=None, machine=None,

@@ -10,6 +10,7 @@ outputs where the exporter provides them.
 """
 from __future__ import annotations
 
+import math
 import warnings
 
 import torch
@@ -42,8 +43,10 @@ def _inference_table() -> dict:
 
 
 def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, loss: int | None = None,
-           strict: bool = True, decompositions=None) -> Exported:
-    """Export ``module(*args, **kwargs)``; with ``loss`` (index of the loss among flat outputs) the joint graph."""
+           strict: bool = True, decompositions=None, inner_cuts: bool = False) -> Exported:
+    """Export ``module(*args, **kwargs)``; with ``loss`` (index of the loss among flat outputs) the joint graph.
+    ``inner_cuts``: an input is cut along an inner leading dimension (see :func:`unflatten_linears`): linear layers keep
+    their operands' leading dimensions apart (inference graphs)."""
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
         ep = torch.export.export(module, tuple(args), kwargs or {}, strict=strict)
@@ -52,7 +55,9 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
             # the executor can hand it to a fused kernel); the joint forward+backward export needs it decomposed
             decompositions = _inference_table()
         ep = ep.run_decompositions(decompositions if decompositions is not None else _default_table())
-        if expand_loops(ep.graph_module) + merge_repeats(ep.graph_module) + (unflatten_products(ep.graph_module) if loss is None else 0):
+        if expand_loops(ep.graph_module) + merge_repeats(ep.graph_module) + \
+                ((unflatten_products(ep.graph_module) + (unflatten_linears(ep.graph_module) if inner_cuts else 0))
+                 if loss is None else 0):
             # results that were items of a loop operator, or repeats of another node, are other nodes now: the
             # signature names them
             out_node = next(n for n in ep.graph_module.graph.nodes if n.op == "output")
@@ -174,6 +179,75 @@ def unflatten_products(gm: torch.fx.GraphModule) -> int:
         done += 1
     if done:
         gm.graph.eliminate_dead_code()                        # the flattened views and their transposes
+        gm.graph.lint()
+        gm.recompile()
+    return done
+
+
+def unflatten_linears(gm: torch.fx.GraphModule) -> int:
+    """A linear layer on an input with several leading dimensions reaches the graph as ``view([..., K] -> [M, K])``,
+    ``mm`` / ``addmm`` with the weight, ``view`` back to ``[..., N]``.  Merging the leading dimensions hides all but the
+    outermost of them from the placement: a cut along an inner one (the batch of a sequence-first ``[T, B, E]`` layout,
+    as inside ``nn.MultiheadAttention``) has no description on the merged dimension, so the value would be gathered.
+    The pattern is rewritten to one product of the un-merged operand with the weight (``matmul`` of ``[..., K]`` and
+    ``[K, N]``, plus the bias), whose leading dimensions are all row dimensions to the rules.  When the flattened view
+    also merges trailing dimensions into ``K`` (``[T, B, H, hd] -> [T*B, H*hd]``), a view that merges only those is
+    put in front."""
+    aten = torch.ops.aten
+    views = (aten.view.default, aten._unsafe_view.default, aten.reshape.default)
+
+    def leading(shape, K):
+        """Leading dimensions of ``shape`` once its trailing dimensions are merged to ``K`` (or None)."""
+        acc, i = 1, len(shape)
+        while i > 0 and acc < K:
+            i -= 1
+            acc *= shape[i]
+        if acc != K or i < 2:                               # nothing to keep apart unless two leading dimensions remain
+            return None
+        return tuple(shape[:i])
+
+    done = 0
+    for node in list(gm.graph.nodes):
+        if node.op != "call_function" or node.target not in (aten.mm.default, aten.addmm.default):
+            continue
+        off = 1 if node.target is aten.addmm.default else 0
+        if len(node.kwargs) or len(node.args) != 2 + off:
+            continue
+        flat, w = node.args[off], node.args[off + 1]
+        if not (isinstance(flat, torch.fx.Node) and flat.op == "call_function" and flat.target in views and isinstance(w, torch.fx.Node)):
+            continue
+        src = flat.args[0]
+        a, f, wv, out = (n.meta.get("val") for n in (src, flat, w, node))
+        if not all(isinstance(t, torch.Tensor) for t in (a, f, wv, out)) or f.ndim != 2 or wv.ndim != 2 or a.ndim < 3:
+            continue
+        M, K = f.shape
+        lead = leading(tuple(a.shape), K)
+        if lead is None or math.prod(lead) != M:
+            continue
+        want = lead + (out.shape[1],)
+        users = list(node.users)
+        if not users or not all(u.op == "call_function" and u.target in views and tuple(u.meta["val"].shape) == want for u in users):
+            continue
+        with gm.graph.inserting_before(node):
+            x = src
+            if tuple(a.shape) != lead + (K,):
+                x = gm.graph.call_function(aten.view.default, (src, list(lead + (K,))))
+                x.meta["val"] = a.reshape(lead + (K,))
+            prod = gm.graph.call_function(aten.matmul.default, (x, w))
+            prod.meta.update({k: v for k, v in node.meta.items() if k != "val"})
+            prod.meta["val"] = users[0].meta["val"]
+            res = prod
+            if off:
+                res = gm.graph.call_function(aten.add.Tensor, (prod, node.args[0]))
+                res.meta.update({k: v for k, v in node.meta.items() if k != "val"})
+                res.meta["val"] = users[0].meta["val"]
+        for u in users:
+            u.replace_all_uses_with(res)
+            gm.graph.erase_node(u)
+        gm.graph.erase_node(node)
+        done += 1
+    if done:
+        gm.graph.eliminate_dead_code()
         gm.graph.lint()
         gm.recompile()
     return done

@@ -219,8 +219,19 @@ def _convolution_backward(node, shapes):
             "outs": ["S", "P", "P"]}
 
 
+def _embedding_bag(node, shapes):
+    # (weight [V, E], indices, offsets, scale_grad_by_freq, mode, ...) -> (output [bags, E], offset2bag, bag_size,
+    # max_indices): the embedding columns are independent, so a table cut along E gives bags cut along E; the rows
+    # (vocabulary) are protected.  Mode 2 (max) also returns per-column indices and is left to the generic path.
+    mode = node.args[4] if len(node.args) > 4 else node.kwargs.get("mode", 0)
+    if mode == 2 or len(shapes[0]) != 2:
+        return None
+    return {"batched": [True] + [False] * (len(shapes) - 1), "protect": {0}, "outs": ["S", "R", "R", "R"]}
+
+
 # operators whose leading (or all but one) dimensions are independent problems: a cut there stays where it is
 BATCHED = {
+    aten._embedding_bag.default: _embedding_bag, aten._embedding_bag_forward_only.default: _embedding_bag,
     aten.linalg_cholesky_ex.default: _trailing(2, 2), aten.linalg_qr.default: _trailing(2, 2),
     aten._linalg_solve_ex.default: _trailing(2, 4), aten.linalg_solve_triangular.default: _trailing(2, 1),
     aten.cholesky_solve.default: _trailing(2, 1), aten.triu.default: _trailing(2, 1), aten.tril.default: _trailing(2, 1),
@@ -521,6 +532,31 @@ class Propagator:
             return [o if a.kind != "R" else R, o if b.kind != "R" else R], o
         return [R, R], R
 
+    def rule_rows_mm(self, node, targs, specs, ax):
+        """``A[..., K] x B[K, N]``: rows of A are independent; the contraction and the columns behave as in ``mm``."""
+        a, b = specs
+        nd = len(self.shape[targs[0]])
+        k_a, n_out = nd - 1, nd - 1
+        if a.kind == "S" and a.dim < k_a and b.kind == "R":                     # any leading dimension cut: local
+            return [a, R], Spec("S", a.dim, a.counts, a.striped)
+        if a.kind == "S" and a.dim == k_a and (b.kind == "R" or (b.kind == "S" and b.dim == 0)):
+            return [a, Spec("S", 0, a.counts, a.striped)], P()                  # contraction cut: partial sums
+        if b.kind == "S" and b.dim == 0 and a.kind == "R":
+            return [Spec("S", k_a, b.counts, b.striped), b], P()
+        if b.kind == "S" and b.dim == 1 and a.kind == "R":                      # columns cut (column-parallel weight)
+            return [R, b], Spec("S", n_out, b.counts, b.striped)
+        if a.kind == "S" and a.dim < k_a and b.kind == "S" and b.dim == 1:
+            # rows and columns cut over the same axis: one operand has to be whole; gather the smaller one
+            if math.prod(self.shape[targs[0]]) <= math.prod(self.shape[targs[1]]):
+                return [R, b], Spec("S", n_out, b.counts, b.striped)
+            return [a, R], Spec("S", a.dim, a.counts, a.striped)
+        if a.kind == "P" and b.kind == "R":
+            return [a, b], a
+        if a.kind == "O" or b.kind == "O":
+            o = a if a.kind == "O" else b
+            return [o if a.kind != "R" else R, o if b.kind != "R" else R], o
+        return [R, R], R
+
     def rule_view(self, node, targs, specs, ax):
         s = specs[0]
         if s.kind != "S":
@@ -668,6 +704,10 @@ class Propagator:
         if tgt is aten.matmul.default and len(self.shape[tnames[0]]) == len(self.shape[tnames[1]]) >= 3:
             # products batched over several leading dimensions (batch and heads kept apart, see export.unflatten_products)
             return self.rule_mm(node, tnames, specs, ax, len(self.shape[tnames[0]]) - 2)
+        if tgt is aten.matmul.default and len(self.shape[tnames[0]]) >= 3 and len(self.shape[tnames[1]]) == 2:
+            # [..., K] x [K, N] (a linear layer whose operand keeps its leading dimensions, export.unflatten_linears):
+            # every leading dimension is a row dimension
+            return self.rule_rows_mm(node, tnames, specs, ax)
         if tgt is aten.addmm.default:                                   # bias + a @ b
             w, o = self.rule_mm(node, tnames[1:], specs[1:], ax, 0)
             if o.kind == "S" and o.dim == 1:

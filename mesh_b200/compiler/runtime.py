@@ -682,6 +682,11 @@ class Executor:
             y = None
             if tgt is aten.mm.default:
                 y = kernels.mm(args[0], args[1])
+            elif tgt is aten.matmul.default and args[0].dim() >= 3 and args[1].dim() == 2:
+                # a linear layer whose operand keeps its leading dimensions: one product over the merged rows
+                y = kernels.mm(args[0].reshape(-1, args[0].shape[-1]), args[1])
+                if y is not None:
+                    y = y.view(*args[0].shape[:-1], y.shape[-1])
             elif tgt is aten.scaled_dot_product_attention.default:
                 # (query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None, enable_gqa=False)
                 opt = dict(zip(("attn_mask", "dropout_p", "is_causal"), args[3:6]))
@@ -699,7 +704,8 @@ class Executor:
 
 # operators with a kernel of this package behind them when the operands allow it: the ones counted as "eager" when
 # they run on the PyTorch operator instead
-_COMPUTE = (aten.mm.default, aten.bmm.default, aten.addmm.default, aten.scaled_dot_product_attention.default)
+_COMPUTE = (aten.mm.default, aten.bmm.default, aten.addmm.default, aten.matmul.default,
+            aten.scaled_dot_product_attention.default)
 
 
 # ----------------------------------------------------------------------------- Program

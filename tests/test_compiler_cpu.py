@@ -666,3 +666,60 @@ def test_pieces_of_a_concatenation_are_computed_in_place():
         run(0)
     finally:
         del os.environ["MESH_DESTINED"]
+
+
+def test_sequence_first_attention_keeps_a_batch_cut():
+    """``nn.MultiheadAttention`` in its sequence-first layout ``[T, B, E]`` with the batch (the inner leading dimension)
+    cut: the linear layers keep their leading dimensions apart, so the projections, the head split and the attention all
+    run on the shard, and the only transfer is the gather of the result (the input itself is never gathered)."""
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.att = torch.nn.MultiheadAttention(32, 4, batch_first=False)
+
+        def forward(self, x):
+            return self.att(x, x, x, need_weights=False)[0]
+
+    torch.manual_seed(0)
+    m = Net().eval()
+    x = torch.randn(6, 4, 32)
+    procs = _procs(2)
+    sch = compile_module(m, (x,), procs, lambda node: (1, tuple(procs), None) if node.op == "placeholder" and node.name == "x" else None)
+    moved = [t.value for t in sch.plan.transfers]
+    assert "x" not in moved and len(moved) == 1 and sch.structure["by_verb"] == {"all_gather": 1}
+    assert any(st.target is torch.ops.aten.matmul.default for st in sch.plan.steps if st.op == "call")
+    got = Program(sch)(x)
+    got = got[0] if isinstance(got, (tuple, list)) else got
+    assert torch.allclose(got, m(x), atol=1e-5)
+    # a cut along the first dimension needs none of this and is captured as before
+    sch0 = compile_module(m, (x,), procs, lambda node: (0, tuple(procs), None) if node.op == "placeholder" and node.name == "x" else None)
+    assert not any(st.target is torch.ops.aten.matmul.default and len(sch0.plan.full_shapes[st.out]) == 3
+                   for st in sch0.plan.steps if st.op == "call")
+    got0 = Program(sch0)(x)
+    got0 = got0[0] if isinstance(got0, (tuple, list)) else got0
+    assert torch.allclose(got0, m(x), atol=1e-5)
+
+
+def test_embedding_bag_keeps_a_column_cut_table():
+    """A bag-of-embeddings table cut along the embedding dimension: the bags come out cut the same way and only they
+    (not the table) are gathered for the replicated layer that follows."""
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.bag = torch.nn.EmbeddingBag(50, 32, mode="sum")
+            self.lin = torch.nn.Linear(32, 8)
+
+        def forward(self, idx, off):
+            return self.lin(self.bag(idx, off))
+
+    torch.manual_seed(0)
+    m = Net().eval()
+    idx, off = torch.randint(0, 50, (20,)), torch.tensor([0, 3, 9, 15])
+    procs = _procs(2)
+    sch = compile_module(m, (idx, off), procs,
+                         lambda node: (1, tuple(procs), None) if node.op == "placeholder" and node.name == "p_bag_weight" else None)
+    assert sch.structure["fallbacks"] == 0
+    assert [t.value for t in sch.plan.transfers] != ["p_bag_weight"] and sch.structure["bytes_between_processors"] == 4 * 32 * 4
+    got = Program(sch)(idx, off)
+    got = got[0] if isinstance(got, (tuple, list)) else got
+    assert torch.allclose(got, m(idx, off), atol=1e-6)
