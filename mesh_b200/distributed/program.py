@@ -54,9 +54,24 @@ class Invocation:
         return self.program.storage(part, self.index)
 
 
+@dataclasses.dataclass(frozen=True)
+class Placement:
+    """Where transfers travel: ``routes[(source rank, destination rank)] = (relay, relay, ...)`` forces a delivery
+    through the named ranks, in order, instead of the direct link (the reference lets the caller force relay paths the
+    same way, ``Placement(routes:)``, examples/indexed-gather.swift:20-23; on a switch every pair has a direct link, so
+    the default is no relay; a route is for shaping traffic or for machines that are not fully connected)."""
+    routes: dict = dataclasses.field(default_factory=dict)
+
+    def hops(self, src: int, dst: int) -> list[int]:
+        via = [r for r in self.routes.get((src, dst), ()) if r not in (src, dst)]
+        return via + [dst]
+
+
 class Mesh:
-    def __init__(self, rank: int | None = None, size: int | None = None, group=None, device="cpu", copies: int = 2):
+    def __init__(self, rank: int | None = None, size: int | None = None, group=None, device="cpu", copies: int = 2,
+                 placement: Placement | None = None):
         self.group = group
+        self.placement = placement or Placement()
         self.rank = dist.get_rank(group) if rank is None else rank
         self.size = dist.get_world_size(group) if size is None else size
         self.device, self.copies = torch.device(device), copies
@@ -93,25 +108,37 @@ class Mesh:
         return p
 
     # ------------------------------------------------------------------ verbs
-    def _deliver(self, part: Part, to: int) -> tuple[Part, tuple | None]:
-        """The copy of ``part`` on rank ``to`` and the transfer that makes it (None when it is there already)."""
+    def _deliver(self, part: Part, to: int) -> tuple[Part, list]:
+        """The copy of ``part`` on rank ``to`` and the transfers that make it, hop by hop (none when it is there
+        already).  A routed delivery lands on every relay first; a relay's copy is shared like any other."""
         if part.rank == to:
-            return part, None
-        key = (part.ident, to)
-        if key in self.delivered:
-            return self.delivered[key], None                # the same immutable part: one receive is shared
-        copy = self._new(to, part.shape, part.dtype)
-        self.delivered[key] = copy
-        return copy, (part, copy)
+            return part, []
+        origin = part.ident
+        moves, here = [], part
+        for hop in self.placement.hops(part.rank, to):
+            if not 0 <= hop < self.size:
+                raise ValueError(f"route through rank {hop}: not in a job of {self.size}")
+            key = (origin, hop)
+            if key in self.delivered:
+                here = self.delivered[key]                  # the same immutable part: one receive is shared
+                continue
+            copy = self._new(hop, part.shape, part.dtype)
+            self.delivered[key] = copy
+            moves.append((here, copy))
+            here = copy
+        return here, moves
 
     def _transfers(self, pairs) -> list[Part]:
-        outs, moves = [], []
+        """One verb: its direct transfers go out as one batch; relayed ones add a batch per further hop."""
+        outs, by_depth = [], []
         for part, to in pairs:
-            copy, move = self._deliver(part, to)
+            copy, moves = self._deliver(part, to)
             outs.append(copy)
-            if move is not None:
-                moves.append(move)
-        if moves:
+            for depth, move in enumerate(moves):
+                while len(by_depth) <= depth:
+                    by_depth.append([])
+                by_depth[depth].append(move)
+        for moves in by_depth:
             self.steps.append(("move", moves))
         return outs
 

@@ -67,3 +67,33 @@ def test_call_refuses_parts_on_other_ranks():
         m.call(lambda u, v: u + v, [a, b], [a], on=0)
     with pytest.raises(ValueError):
         m.reduce([a, b], to=0, op="mean")
+
+
+def _routed_rank(rank, world, rdv):
+    """A delivery forced through a relay: 0 -> 2 goes by way of 1; the relay's copy is an ordinary part (a later
+    delivery of the same part to the relay shares it), and the numbers arrive unchanged."""
+    from mesh_b200.distributed.program import Mesh, Placement
+    m = Mesh(device="cpu", copies=2, placement=Placement(routes={(0, 2): (1,)}))
+    x = m.tensor(on=0, sections=[(5,)])[0]
+    far = m.send(x, to=2)
+    near = m.send(x, to=1)                      # the relay already holds it
+    assert far.rank == 2 and near.rank == 1
+    moves = [s for s in m.steps if s[0] == "move"]
+    assert [[(a.rank, b.rank) for a, b in mv] for _, mv in moves] == [[(0, 1)], [(1, 2)]]
+    direct = m.send(m.tensor(on=2, sections=[(5,)])[0], to=0)        # no route stated for (2, 0): the direct link
+    assert [(a.rank, b.rank) for a, b in m.steps[-1][1]] == [(2, 0)]
+    m.start(wait_s=20.0)
+    for i in range(2):
+        inv = m.invocation(i)
+        if rank == 0:
+            inv.part(x).copy_(torch.arange(5.0) + i)
+        inv.submit()
+        assert m.result(i) == 0
+        if rank in (1, 2):
+            assert torch.equal(inv.part(near if rank == 1 else far), torch.arange(5.0) + i)
+    assert direct.rank == 0
+
+
+def test_forced_relay_routes():
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_routed_rank, 3, init_pg="gloo")
