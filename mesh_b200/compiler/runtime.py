@@ -410,6 +410,19 @@ class Executor:
             out.append(o[1] if isinstance(o, tuple) else env[o])
         return out
 
+    def run_step(self, st: Step, env: dict, val):
+        """One step that is neither a constant, an alias nor a collective, on the values in ``env`` (generated host
+        programs call this for the steps they do not spell out, ``compiler/hostgen.py``)."""
+        if st.op == "slice":
+            src = env.get(st.args[0].name)
+            s, ax = st.meta["to"], st.meta["axis"]
+            return None if src is None else self._index(src, s.dim, local_indices(s, self.coords[ax], src.shape[s.dim]))
+        if st.op == "fused" and st.target == "rms_norm":
+            return self.rms_norm(st, env.get(st.args[0].name), env.get(st.args[1].name) if len(st.args) > 1 else None)
+        if st.op == "fused":
+            return self.fused(st, env.get(st.args[0].name), env.get(st.args[1].name), env)
+        return self.call(st, val)
+
     # ---- fused (collective, matmul) pairs, see compiler/fuse.py
     def _fused_kernels(self, kind: str, a, w_t, rows_total: int):
         """The fused-kernel object for this shape, or None when the pair has to run unfused (CPU ranks, dtypes other
