@@ -24,13 +24,15 @@ from .runtime import Program
 
 
 def workspace(scheduled, copies: int = 1, align: int = 256) -> dict:
-    """``{"bytes_per_copy", "bytes_unshared", "copies", "offsets": {value: [offset per copy]}, "transfers": [...]}``."""
+    """``{"bytes_per_copy", "bytes_unshared", "copies", "offsets": {value: [offset per copy]}, "transfers": [...],
+    "planned": the native planner's demands, order and exposed time for those transfers}``."""
     from ..runtime.plan import layout
     lt = _schedule.lifetimes(scheduled.plan)
     offs, one = layout([(a, b, c) for _, a, b, c in lt], copies=copies, align=align) if lt else ([[]] * copies, 0)
     return {"bytes_per_copy": one, "bytes_unshared": sum(c for *_, c in lt), "copies": copies,
             "offsets": {name: [offs[c][i] for c in range(copies)] for i, (name, *_rest) in enumerate(lt)},
-            "transfers": _schedule.declarations(scheduled.plan), "horizon": _schedule.horizon(scheduled.plan, copies)}
+            "transfers": _schedule.declarations(scheduled.plan), "horizon": _schedule.horizon(scheduled.plan, copies),
+            "planned": _schedule.planned(scheduled.plan)}
 
 
 class Prepared:

@@ -140,12 +140,21 @@ def bucket_reductions(plan: Plan) -> tuple[Plan, int]:
     plan = copy.copy(plan)
     uses = _uses(plan)
     end = len(plan.steps)
+    # which reductions travel together is the planner's decision: its demands (flat messages up to the bucket size,
+    # members that exist before the group's earliest reader)
+    demand_of: dict = {}
+    try:
+        from .schedule import planned
+        demand_of = {t["channel"]: t["demand"] for t in planned(plan)["transfers"]}
+    except Exception:
+        demand_of = {}
     steps, count = [], 0
     for st in plan.steps:
         if (st.op == "collective" and st.target == "all_reduce" and st.meta["from"].op == "sum"
                 and all(u == end for u in uses.get(st.out, []))):
             meta = dict(st.meta)
-            meta["bucket"] = (st.meta["axis"], str(plan.dtypes.get(st.out, plan.dtypes.get(st.args[0].name, "float32"))))
+            meta["bucket"] = (st.meta["axis"], str(plan.dtypes.get(st.out, plan.dtypes.get(st.args[0].name, "float32"))),
+                              demand_of.get(st.meta.get("channel"), 0))
             st = Step(st.op, st.out, st.target, st.args, st.kwargs, meta)
             count += 1
         steps.append(st)

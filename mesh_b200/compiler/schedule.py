@@ -274,3 +274,23 @@ def copies(plan: Plan) -> Copies:
             reusable += 1
         last_on_axis[axis] = key
     return Copies(group, index, member, reusable)
+
+
+def planned(plan: Plan, step_us: float = 10.0, bucket_bytes: int = 32 << 20, staging_bytes: int = 64 << 20) -> dict:
+    """The plan's declared transfers through the native planner (``runtime/plan.py::plan_transfers``): which transfers
+    travel together as one demand, with which algorithm and in how many pieces, in which order on each axis, and how
+    much of the link time the step cannot hide.  ``{"transfers": [declared + planned fields], "summary": {...}}``."""
+    from ..runtime.plan import plan_transfers
+    end = len(plan.steps)
+    decl = declarations(plan)
+    uses = {}
+    for d in decl:
+        uses[d.result] = d.read
+    rows = [{"bytes": d.nbytes, "axis": d.axis, "verb": d.verb if d.verb in ("all_reduce", "all_gather", "reduce_scatter", "all_to_all")
+             else {"ag_mm": "all_gather", "mm_rs": "reduce_scatter"}.get(d.verb, "point"),
+             "at": d.at, "read": max(d.read, d.at), "groupable": d.verb == "all_reduce" and d.read >= end} for d in decl]
+    out, summary = plan_transfers(rows, list(plan.mesh.shape), step_us=step_us, bucket_bytes=bucket_bytes,
+                                  staging_bytes=staging_bytes) if rows else ([], {"link_us": 0.0, "exposed_us": 0.0,
+                                                                                 "makespan_us": 0.0, "demands": 0})
+    return {"transfers": [dict(channel=d.channel, verb=d.verb, value=d.value, result=d.result, **o) for d, o in zip(decl, out)],
+            "summary": summary}

@@ -44,6 +44,46 @@ def layout(buffers: list[tuple[int, int, int]], copies: int = 1, align: int = 25
     return [[out[c * n + i] for i in range(n)] for c in range(copies)], int(one)
 
 
+VERBS = {"all_reduce": 0, "all_gather": 1, "reduce_scatter": 2, "all_to_all": 3}
+
+
+class _TransferIn(ctypes.Structure):
+    _fields_ = [("bytes", c_int64), ("axis", ctypes.c_int32), ("verb", ctypes.c_int32), ("at", ctypes.c_int32),
+                ("read", ctypes.c_int32), ("groupable", ctypes.c_int32), ("pad", ctypes.c_int32)]
+
+
+class _TransferOut(ctypes.Structure):
+    _fields_ = [("demand", ctypes.c_int32), ("algo", ctypes.c_int32), ("pieces", ctypes.c_int32), ("order", ctypes.c_int32),
+                ("start_us", c_double), ("end_us", c_double), ("exposed_us", c_double)]
+
+
+def plan_transfers(transfers: list[dict], worlds: list[int], *, step_us: float = 10.0, alpha_us: float | None = None,
+                   nvls: bool = False, bucket_bytes: int = 32 << 20, staging_bytes: int = 64 << 20) -> tuple[list[dict], dict]:
+    """The native planner on a step's declared transfers.  ``transfers``: dicts with ``bytes, axis, verb, at, read`` and
+    optionally ``groupable`` (a reduction that may travel with others: nothing reads it before ``read``); ``worlds``:
+    ranks per axis; ``step_us``: time of one plan step in the cost model.  Returns per transfer ``{demand, algo, pieces,
+    order, start_us, end_us, exposed_us}`` and the summary ``{link_us, exposed_us, makespan_us, demands}``: transfers of
+    one axis grouped into demands (flat messages up to ``bucket_bytes``), an algorithm and a piece count per demand, the
+    demands ordered earliest deadline first on the axis's links, and how long each reader waits."""
+    n = len(transfers)
+    cin = (_TransferIn * max(1, n))()
+    for i, t in enumerate(transfers):
+        cin[i].bytes, cin[i].axis, cin[i].verb = int(t["bytes"]), int(t.get("axis", 0)), VERBS.get(t.get("verb", "point"), 4)
+        cin[i].at, cin[i].read, cin[i].groupable = int(t["at"]), int(t["read"]), int(bool(t.get("groupable", False)))
+    cout = (_TransferOut * max(1, n))()
+    summary = (c_double * 4)()
+    cap = capacity()
+    alpha = float(cap.get("collective_alpha_us", 5.0)) if alpha_us is None else alpha_us
+    rc = _native.lib().mesh_plan_transfers(c_int(n), cin, c_int(len(worlds)), (c_int * max(1, len(worlds)))(*worlds),
+                                           c_double(step_us), c_double(alpha), c_double(cap["nvlink_gbs_per_dir"]),
+                                           c_int(int(nvls)), c_int64(bucket_bytes), c_int64(staging_bytes), cout, summary)
+    if rc != 0:
+        raise ValueError("plan_transfers: a transfer names an axis that does not exist, a reader before its transfer or a negative size")
+    out = [{"demand": cout[i].demand, "algo": ALGOS[cout[i].algo], "pieces": cout[i].pieces, "order": cout[i].order,
+            "start_us": cout[i].start_us, "end_us": cout[i].end_us, "exposed_us": cout[i].exposed_us} for i in range(n)]
+    return out, {"link_us": summary[0], "exposed_us": summary[1], "makespan_us": summary[2], "demands": int(summary[3])}
+
+
 class Plan:
     """A captured step with ``copies`` workspaces; ``start()`` launches execution ``t`` on copy ``t % copies``."""
 

@@ -72,3 +72,28 @@ def test_prepared_program_rotates_input_sets_and_refuses_a_stale_view():
     rdv.epoch = 1
     with pytest.raises(MeshStale):
         pr2.start()
+
+
+def test_workspace_carries_the_planned_transfers():
+    """The prepared program's plan information includes the native planner's view of its transfers: the gradient
+    reductions of a data-parallel step travel as few demands (buckets), every transfer has an algorithm, a place in the
+    order of its axis and the time its reader waits; a small bucket size gives more demands."""
+    import torch
+
+    from mesh_b200.compiler import compile_module
+    from mesh_b200.compiler import schedule as S
+    from mesh_b200.compiler.bridge import workspace
+    from mesh_b200.models.llama import Decoder, data_parallel
+    torch.manual_seed(1)
+    m = Decoder(dim=32, heads=2, ffn=64, layers=2)
+    x = torch.randn(4, 6, 32)
+    procs = {f"p{i}": (0, "cpu") for i in range(2)}
+    sch = compile_module(m, (x,), procs, data_parallel(procs), loss=0)
+    ws = workspace(sch)
+    planned = ws["planned"]
+    n = len(sch.plan.transfers)
+    assert len(planned["transfers"]) == n and planned["summary"]["demands"] < n
+    assert all(t["algo"] in ("one_shot", "two_shot", "nvls", "copy_engine") and t["pieces"] >= 1 for t in planned["transfers"])
+    small = S.planned(sch.plan, bucket_bytes=8 << 10)
+    assert small["summary"]["demands"] > planned["summary"]["demands"]
+    assert abs(small["summary"]["exposed_us"] - sum({t["demand"]: t["exposed_us"] for t in small["transfers"]}.values())) < 1e-6

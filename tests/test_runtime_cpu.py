@@ -161,3 +161,62 @@ def test_peer_channels_state_machine_queue_and_bounded_flush():
     with pytest.raises(ChannelError):
         ch.copy(2, ctypes.addressof(dst), ctypes.addressof(src), 16)
     assert ch.close(1000) == 0
+
+
+def test_transfer_planner_groups_orders_and_accounts():
+    """Declared transfers through the native planner: gradient reductions that nobody reads before the end travel as
+    one demand up to the bucket size; a transfer somebody waits for is a demand of its own and goes first when both are
+    ready (earliest deadline); demands of one axis never overlap and never start before their value exists; the
+    summary adds up; every rank computes the same plan (two calls agree)."""
+    import random
+
+    from mesh_b200.runtime.plan import plan_transfers
+    end = 100
+    grads = [{"bytes": 4 << 20, "axis": 0, "verb": "all_reduce", "at": 60 + 5 * i, "read": end, "groupable": True} for i in range(6)]
+    act = {"bytes": 8 << 20, "axis": 0, "verb": "all_gather", "at": 62, "read": 64}
+    big = {"bytes": 200 << 20, "axis": 1, "verb": "all_reduce", "at": 10, "read": 20}
+    rows = grads + [act, big]
+    out, summary = plan_transfers(rows, [8, 2], step_us=10.0, alpha_us=5.0, bucket_bytes=16 << 20, staging_bytes=64 << 20)
+    again, summary2 = plan_transfers(rows, [8, 2], step_us=10.0, alpha_us=5.0, bucket_bytes=16 << 20, staging_bytes=64 << 20)
+    assert out == again and summary == summary2
+    # 6 x 4 MiB into 16 MiB buckets: 4 + 2; the activation gather and the other axis' reduction stand alone
+    g = [o["demand"] for o in out[:6]]
+    assert g[0] == g[1] == g[2] == g[3] != g[4] == g[5]
+    assert out[6]["demand"] not in g and out[7]["demand"] not in g and summary["demands"] == 4
+    assert out[7]["pieces"] == 4 and out[7]["algo"] in ("two_shot", "one_shot")
+    # the activation is needed at step 64 and is there in time; the gradients are exposed only past the end
+    assert out[6]["start_us"] >= 63 * 10.0 and out[6]["exposed_us"] == max(0.0, out[6]["end_us"] - 64 * 10.0)
+    # no overlap on an axis, release respected
+    for ax in (0, 1):
+        spans = sorted({(o["start_us"], o["end_us"], o["demand"]) for o, r in zip(out, rows) if r["axis"] == ax})
+        for (s0, e0, _), (s1, e1, _) in zip(spans, spans[1:]):
+            assert s1 >= e0 - 1e-9
+    for o, r in zip(out, rows):
+        last = max(rr["at"] for oo, rr in zip(out, rows) if oo["demand"] == o["demand"])
+        assert o["start_us"] >= (last + 1) * 10.0 - 1e-9
+    spans = {o["demand"]: (o["start_us"], o["end_us"], o["exposed_us"]) for o in out}
+    assert abs(summary["link_us"] - sum(e - s for s, e, _ in spans.values())) < 1e-6
+    assert abs(summary["exposed_us"] - sum(x for _, _, x in spans.values())) < 1e-6
+    assert abs(summary["makespan_us"] - max(e for _, e, _ in spans.values())) < 1e-6
+    # random programs: the same invariants
+    rng = random.Random(1)
+    for _ in range(20):
+        rows = []
+        for _ in range(rng.randint(1, 12)):
+            at = rng.randint(0, 50)
+            rows.append({"bytes": rng.randint(1, 40) << 20, "axis": rng.randint(0, 1), "verb": rng.choice(["all_reduce", "all_gather", "reduce_scatter"]),
+                         "at": at, "read": at + rng.randint(0, 30), "groupable": rng.random() < 0.5})
+        out, summary = plan_transfers(rows, [4, 2], step_us=7.0, bucket_bytes=64 << 20)
+        for ax in (0, 1):
+            spans = sorted({(o["start_us"], o["end_us"]) for o, r in zip(out, rows) if r["axis"] == ax})
+            assert all(b[0] >= a[1] - 1e-9 for a, b in zip(spans, spans[1:]))
+        for o, r in zip(out, rows):
+            assert o["start_us"] >= (r["at"] + 1) * 7.0 - 1e-9 and o["exposed_us"] >= 0
+            members = [rr for oo, rr in zip(out, rows) if oo["demand"] == o["demand"]]
+            if len(members) > 1:
+                assert all(m["groupable"] and m["verb"] == "all_reduce" and m["axis"] == r["axis"] for m in members)
+                assert sum(m["bytes"] for m in members) <= 64 << 20
+                assert max(m["at"] for m in members) < min(m["read"] for m in members)
+    import pytest
+    with pytest.raises(ValueError):
+        plan_transfers([{"bytes": 1, "axis": 3, "verb": "all_reduce", "at": 0, "read": 1}], [2])
