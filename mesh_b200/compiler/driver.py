@@ -37,7 +37,23 @@ def compile_module(module, args, processors, placement, cost=unit_cost, planning
         # an input cut along an inner leading dimension (the batch of a sequence-first layout): capture again with the
         # linear layers' leading dimensions kept apart, or the cut would be lost at the first flattening view
         exported = _export.export(module, args, kwargs, inner_cuts=True, **export_options)
-    return compile_captured(exported, processors, placement, cost, mesh)
+    sch = compile_captured(exported, processors, placement, cost, mesh)
+    if exported.training and "decompositions" not in export_options and _gathers_for_batch_statistics(sch):
+        # a training-mode batch norm whose input is cut along the batch (or a spatial dimension) would gather it to get
+        # the statistics of the whole batch: capture again with the norm stated as means and sums, which become partial
+        # sums and two small all-reduces
+        from .decompose import norms
+        exported = _export.export(module, args, kwargs, decompositions=norms(), **export_options)
+        sch = compile_captured(exported, processors, placement, cost, mesh)
+    return sch
+
+
+def _gathers_for_batch_statistics(sch) -> bool:
+    import torch
+    aten = torch.ops.aten
+    batch_norms = (aten._native_batch_norm_legit_functional.default, aten._native_batch_norm_legit.default,
+                   aten._native_batch_norm_legit.no_stats, aten.native_batch_norm.default)
+    return any(st.target in batch_norms and st.meta.get("fallback") and st.meta.get("gathered") for st in sch.plan.steps)
 
 
 def _cuts_inner_dimension(exported, placement) -> bool:

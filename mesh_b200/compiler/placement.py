@@ -109,6 +109,35 @@ POINTWISE = {
     aten.remainder.Scalar, aten.fmod.Scalar, aten.isnan.default, aten.isinf.default, aten.nan_to_num.default,
     aten.lift_fresh_copy.default, aten.contiguous.default if hasattr(aten, "contiguous") else aten.clone.default,
 }
+
+
+def _overloads(*names) -> set:
+    """The operator overloads named ``packet.overload`` that this build of PyTorch has (older and newer builds differ in
+    which activations are primitive and which are decomposed before the compiler sees them)."""
+    found = set()
+    for name in names:
+        packet, _, overload = name.partition(".")
+        op = getattr(getattr(aten, packet, None), overload or "default", None)
+        if op is not None:
+            found.add(op)
+    return found
+
+
+# the rest of the element-by-element family: activations and their derivatives, transcendental functions, comparisons,
+# integer arithmetic, three-operand blends
+POINTWISE |= _overloads(
+    "elu", "elu_backward", "celu", "selu", "log1p", "expm1", "log10", "log_sigmoid_forward", "log_sigmoid_backward",
+    "hardswish", "hardswish_backward", "hardsigmoid", "hardsigmoid_backward", "hardtanh_backward", "leaky_relu_backward",
+    "softplus_backward", "mish", "mish_backward", "relu6", "threshold", "logit", "logit_backward", "tan", "atan", "asin",
+    "acos", "sinh", "cosh", "asinh", "acosh", "atanh", "atan2", "trunc", "frac", "erfc", "erfinv", "lgamma", "digamma",
+    "sgn", "signbit", "positive", "hypot", "copysign.Tensor", "copysign.Scalar", "xlogy.Tensor", "logaddexp", "logaddexp2",
+    "logical_xor", "bitwise_xor.Tensor", "bitwise_and.Scalar", "bitwise_or.Scalar", "bitwise_xor.Scalar",
+    "bitwise_left_shift.Tensor", "bitwise_right_shift.Tensor", "ne.Tensor", "fmod.Tensor", "remainder.Tensor",
+    "floor_divide", "div.Tensor_mode", "div.Scalar_mode", "pow.Scalar", "lerp.Scalar", "lerp.Tensor", "addcmul", "addcdiv",
+    "clamp.Tensor", "clamp_min.Tensor", "clamp_max.Tensor", "where.ScalarOther", "where.ScalarSelf", "heaviside",
+    "isfinite", "isposinf", "isneginf", "rad2deg", "deg2rad", "sinc", "i0", "special_erfcx", "special_ndtri",
+    "empty_like",
+)
 # ops that stay "partial" when exactly the listed argument positions are partial and the rest replicated/scalars
 LINEAR_IN = {
     aten.add.Tensor: "all", aten.sub.Tensor: "all", aten.neg.default: "all", aten.clone.default: "all",
@@ -159,6 +188,59 @@ def _split(position: int, removes: bool = False):
     return describe
 
 
+def _along_reduce(position: int, outs: int, keep_position: int):
+    """Reductions along one dimension that return values and indices (``max.dim``, ``kthvalue``, ...): the other
+    dimensions are independent; without ``keepdim`` the dimensions behind the reduced one move up."""
+    def describe(node, shapes):
+        nd = max(len(shapes[0]), 1)
+        dim = (node.args[position] if len(node.args) > position else node.kwargs.get("dim", -1)) % nd
+        keep = node.args[keep_position] if len(node.args) > keep_position else node.kwargs.get("keepdim", False)
+        info = {"batched": [True] + [False] * (len(shapes) - 1), "protect": {dim}, "outs": ["S"] * outs}
+        if not keep:
+            info["out_dim"] = lambda d: d - (1 if d > dim else 0)
+        return info
+    return describe
+
+
+def _over_dims(outs: int):
+    """Statistics over a list of dimensions given as the second argument (``var``, ``std``, ``var_mean``, norms): a cut
+    along a dimension that stays is local (the sums of squares have no partial form here)."""
+    def describe(node, shapes):
+        nd = max(len(shapes[0]), 1)
+        dims = node.args[1] if len(node.args) > 1 else node.kwargs.get("dim")
+        if isinstance(dims, (int, float)) and node.target in _NORMS:          # (self, ord, dims, keepdim)
+            dims = node.args[2] if len(node.args) > 2 else node.kwargs.get("dim")
+            keep = node.args[3] if len(node.args) > 3 else node.kwargs.get("keepdim", False)
+        else:
+            keep = node.kwargs.get("keepdim", node.args[3] if len(node.args) > 3 else False)
+        if dims is None or dims == []:
+            return None
+        dims = {d % nd for d in (dims if isinstance(dims, (list, tuple)) else [dims])}
+        info = {"batched": [True] + [False] * (len(shapes) - 1), "protect": dims, "outs": ["S"] * outs}
+        if not keep:
+            info["out_dim"] = lambda d: d - sum(1 for r in dims if r < d)
+        return info
+    return describe
+
+
+def _padded(node, shapes):
+    # (input, pad, value): ``pad`` lists (before, after) pairs from the last dimension backwards; a dimension that gets no
+    # padding is a batch dimension
+    nd = len(shapes[0])
+    pad = list(node.args[1])
+    touched = {nd - 1 - i // 2 for i, p in enumerate(pad) if p != 0}
+    return {"batched": [True], "protect": touched, "outs": ["S"]}
+
+
+def _rolled(node, shapes):
+    # (input, shifts, dims): without dims the whole tensor is rolled as one line
+    nd = len(shapes[0])
+    dims = node.args[2] if len(node.args) > 2 else node.kwargs.get("dims", [])
+    if not dims:
+        return None
+    return {"batched": [True], "protect": {d % nd for d in dims}, "outs": ["S"]}
+
+
 def _layer_norm(node, shapes):
     core = len(node.args[1])
     nd = len(shapes[0])
@@ -181,6 +263,10 @@ POOLS = {
     aten.max_pool2d_with_indices.default: {"kernel": 1, "stride": 2, "padding": 3, "dilation": 4, "inputs": (0,), "outputs": (), "outs": 2, "backward": False},
     aten.avg_pool2d_backward.default: {"kernel": 2, "stride": 3, "padding": 4, "dilation": None, "inputs": (1,), "outputs": (0,), "outs": 1, "backward": True},
     aten.max_pool2d_with_indices_backward.default: {"kernel": 2, "stride": 3, "padding": 4, "dilation": 5, "inputs": (1,), "outputs": (0, 2), "outs": 1, "backward": True},
+    aten.avg_pool3d.default: {"kernel": 1, "stride": 2, "padding": 3, "dilation": None, "inputs": (0,), "outputs": (), "outs": 1, "backward": False, "spatial": 3},
+    aten.max_pool3d_with_indices.default: {"kernel": 1, "stride": 2, "padding": 3, "dilation": 4, "inputs": (0,), "outputs": (), "outs": 2, "backward": False, "spatial": 3},
+    aten.avg_pool3d_backward.default: {"kernel": 2, "stride": 3, "padding": 4, "dilation": None, "inputs": (1,), "outputs": (0,), "outs": 1, "backward": True, "spatial": 3},
+    aten.max_pool3d_with_indices_backward.default: {"kernel": 2, "stride": 3, "padding": 4, "dilation": 5, "inputs": (1,), "outputs": (0, 2), "outs": 1, "backward": True, "spatial": 3},
 }
 
 
@@ -244,7 +330,46 @@ BATCHED = {
     aten.native_group_norm.default: _group_norm, aten.native_group_norm_backward.default: _group_norm_backward,
     aten.convolution.default: _convolution, aten.convolution_backward.default: _convolution_backward,
     aten.native_layer_norm.default: _layer_norm, aten.native_layer_norm_backward.default: _layer_norm_backward,
+    aten.max.dim: _along_reduce(1, 2, 2), aten.min.dim: _along_reduce(1, 2, 2), aten.kthvalue.default: _along_reduce(2, 2, 3),
+    aten.median.dim: _along_reduce(1, 2, 2), aten.mode.default: _along_reduce(1, 2, 2),
+    aten.prod.dim_int: _along_reduce(1, 1, 2), aten.cumprod.default: _along(1, 1), aten.logcumsumexp.default: _along(1, 1),
+    aten.var.correction: _over_dims(1), aten.std.correction: _over_dims(1), aten.var_mean.correction: _over_dims(2),
+    aten.std_mean.correction: _over_dims(2), aten.linalg_vector_norm.default: _over_dims(1),
+    aten.constant_pad_nd.default: _padded, aten.roll.default: _rolled, aten.index_select.default: _along(1, 1),
+    aten.glu.default: _along(1, 1),
+    # windows over the trailing dimensions: samples and channels are independent (a cut along a window dimension is the
+    # halo rule's business where there is one)
+    aten.avg_pool2d.default: _trailing(2, 1, (0,)), aten.max_pool2d_with_indices.default: _trailing(2, 2, (0,)),
+    aten.avg_pool2d_backward.default: _trailing(2, 1, (0, 1)),
+    aten.max_pool2d_with_indices_backward.default: _trailing(2, 1, (0, 1, 2)),
+    aten.avg_pool3d.default: _trailing(3, 1, (0,)), aten.max_pool3d_with_indices.default: _trailing(3, 2, (0,)),
+    aten.avg_pool3d_backward.default: _trailing(3, 1, (0, 1)),
+    aten.max_pool3d_with_indices_backward.default: _trailing(3, 1, (0, 1, 2)),
+    aten._adaptive_avg_pool2d.default: _trailing(2, 1, (0,)), aten._adaptive_avg_pool2d_backward.default: _trailing(2, 1, (0, 1)),
+    aten._adaptive_avg_pool3d.default: _trailing(3, 1, (0,)), aten._adaptive_avg_pool3d_backward.default: _trailing(3, 1, (0, 1)),
+    aten.adaptive_max_pool2d.default: _trailing(2, 2, (0,)), aten.adaptive_max_pool2d_backward.default: _trailing(2, 1, (0, 1, 2)),
+    aten.upsample_nearest1d.default: _trailing(1, 1, (0,)), aten.upsample_nearest2d.default: _trailing(2, 1, (0,)),
+    aten.upsample_nearest3d.default: _trailing(3, 1, (0,)), aten.upsample_linear1d.default: _trailing(1, 1, (0,)),
+    aten.upsample_bilinear2d.default: _trailing(2, 1, (0,)), aten.upsample_bicubic2d.default: _trailing(2, 1, (0,)),
+    aten.upsample_trilinear3d.default: _trailing(3, 1, (0,)),
+    aten.upsample_nearest1d.vec: _trailing(1, 1, (0,)), aten.upsample_nearest2d.vec: _trailing(2, 1, (0,)),
+    aten.upsample_nearest3d.vec: _trailing(3, 1, (0,)), aten.upsample_linear1d.vec: _trailing(1, 1, (0,)),
+    aten.upsample_bilinear2d.vec: _trailing(2, 1, (0,)), aten.upsample_bicubic2d.vec: _trailing(2, 1, (0,)),
+    aten.upsample_trilinear3d.vec: _trailing(3, 1, (0,)),
+    aten.pixel_shuffle.default: _trailing(3, 1, (0,)), aten.pixel_unshuffle.default: _trailing(3, 1, (0,)),
 }
+_NORMS = {aten.linalg_vector_norm.default}
+# batch norm variants: how many leading arguments are tensors (some optional), which of them have the input's shape,
+# and what each output is (the input's shape, a per-channel vector, or something no cut applies to)
+_CHANNEL_NORMS = {
+    aten._native_batch_norm_legit_no_training.default: {"tensors": 5, "full": (0,), "outs": ("full", "vector", "vector")},
+    aten._native_batch_norm_legit_functional.default: {"tensors": 5, "full": (0,), "outs": ("full", "vector", "vector", "vector", "vector")},
+    aten._native_batch_norm_legit.no_stats: {"tensors": 3, "full": (0,), "outs": ("full", "vector", "vector")},
+    aten.native_batch_norm.default: {"tensors": 5, "full": (0,), "outs": ("full", "vector", "vector")},
+    aten.native_batch_norm_backward.default: {"tensors": 7, "full": (0, 1), "outs": ("full", "vector", "vector")},
+}
+_INDEX_GETS = _overloads("index.Tensor", "_unsafe_index.Tensor")
+_INDEX_PUTS = _overloads("index_put.default", "_unsafe_index_put.default")
 
 
 def _shape(node) -> tuple:
@@ -642,11 +767,25 @@ class Propagator:
             return
         if tgt is aten.convolution_backward.default and self.halo_convolution_backward(node, tnames):
             return
+        if tgt is aten.convolution.default and self.patch_transposed_convolution(node, tnames):
+            return
+        if tgt is aten.convolution_backward.default and self.patch_transposed_convolution(node, tnames, backward=True):
+            return
+        if tgt is aten.convolution.default and (self.channel_convolution(node, tnames) or self.depthwise_convolution(node, tnames)):
+            return
+        if tgt is aten.convolution_backward.default and self.depthwise_convolution(node, tnames, backward=True):
+            return
+        if tgt in _CHANNEL_NORMS and self.channel_norm(node, tnames):
+            return
+        if tgt is aten.convolution_backward.default and self.channel_convolution_backward(node, tnames):
+            return
         if tgt is aten._assert_tensor_metadata.default:
             return                                       # a trace-time check of dtype/shape: nothing to run, no reason to gather
         if tgt is aten.index_put.default and self.accumulating_index_put(node):
             return
         if tgt in (aten.cat.default, aten.stack.default) and self.joined(node):
+            return
+        if (tgt in _INDEX_GETS or tgt in _INDEX_PUTS) and self.indexed(node):
             return
         if tgt in POOLS and self.pooled(node, tnames):
             return
@@ -972,7 +1111,7 @@ class Propagator:
         return True
 
     def pooled(self, node, tnames) -> bool:
-        """2-D pooling (and its backward) over an input cut along a spatial dimension where no window straddles a cut:
+        """2-D and 3-D pooling (and its backward) over an input cut along a spatial dimension where no window straddles a cut:
         stride = kernel, no padding or dilation there, every processor's extent a multiple of the kernel.  Each
         processor pools its own block; the output is cut at the same places, divided by the kernel.  (The indices of a
         max pooling are positions within the local block, which is what its backward, run on the same block, expects.)
@@ -983,11 +1122,12 @@ class Propagator:
         def arg(key, default):
             pos = info[key]
             v = args[pos] if pos is not None and len(args) > pos else default
-            return list(v) if isinstance(v, (list, tuple)) else [v, v]
+            return list(v) if isinstance(v, (list, tuple)) else [v] * k
+        k = info.get("spatial", 2)                                     # window dimensions: the trailing ones
         kernel = arg("kernel", None)
         stride = arg("stride", []) or kernel
         padding, dilation = arg("padding", 0), arg("dilation", 1)
-        kernel, stride, padding, dilation = (v * 2 if len(v) == 1 else v for v in (kernel, stride, padding, dilation))
+        kernel, stride, padding, dilation = (v * k if len(v) == 1 else v for v in (kernel, stride, padding, dilation))
         x = tnames[list(info["inputs"])[0]] if not info["backward"] else tnames[1]
         nd = len(self.shape[x])
         ins = [tnames[i] for i in info["inputs"]]
@@ -1009,10 +1149,10 @@ class Propagator:
                 continue
             if sp.kind != "S" or sp.striped:
                 return False
-            if sp.dim < nd - 2:                                        # batch or channel: nothing to check
+            if sp.dim < nd - k:                                        # batch or channel: nothing to check
                 small = sp
             else:
-                i = sp.dim - (nd - 2)
+                i = sp.dim - (nd - k)
                 if stride[i] != kernel[i] or padding[i] or dilation[i] != 1 or any(c % kernel[i] for c in sp.counts):
                     return False
                 small = Spec("S", sp.dim, tuple(c // kernel[i] for c in sp.counts))
@@ -1180,6 +1320,89 @@ class Propagator:
                                self.ref_kwargs(node.kwargs, new_names), {"out_specs": out_spec, "full_shape": _shape(node)}))
         return True
 
+    def indexed(self, node) -> bool:
+        """``x[..., i, j, ...]`` (``index.Tensor``) and ``x.index_put((..., i, j, ...), values)`` where ``x`` is cut along
+        a dimension that the index tensors leave alone (a ``None`` entry before them, or behind them when they sit
+        together): every processor indexes its own block with the whole index tensors."""
+        put = node.target in _INDEX_PUTS
+        base, indices = node.args[0], list(node.args[1])
+        values = node.args[2] if put else None
+        if not _is_tensor_node(base) or (put and not _is_tensor_node(values)):
+            return False
+        bname = self.renamed.get(base.name, base.name)
+        bshape = self.shape[bname]
+        at = [i for i, ix in enumerate(indices) if ix is not None]
+        if not at or not all(_is_tensor_node(indices[i]) for i in at):
+            return False
+        first, last, together = at[0], at[-1], at[-1] - at[0] + 1 == len(at)
+        out_nd = len(_shape(node))
+        spread = out_nd - (len(bshape) - len(at))            # dimensions the broadcast index tensors contribute
+        vname = self.renamed.get(values.name, values.name) if put else None
+        specs = self.spec[bname]
+        base_want, out_spec, val_want = [], [], []
+        found = False
+        if put:
+            vshape = self.shape[vname]
+            res_nd = len(bshape) - len(at) + max(len(self.shape[self.renamed.get(indices[i].name, indices[i].name)]) for i in at)
+        for ax, sp in enumerate(specs):
+            if sp.kind == "R" and put and self.spec[vname][ax].kind == "S":
+                # a whole base (the zeros a backward accumulates into) under cut values: the base gives up all but the
+                # rows of the values' cut when that dimension is one the index tensors leave alone
+                vs = self.spec[vname][ax]
+                rdim = vs.dim + (res_nd - len(vshape))               # its dimension in the indexed result
+                if rdim < first:
+                    bdim = rdim
+                elif together and rdim >= first + (res_nd - (len(bshape) - len(at))):
+                    bdim = rdim - (res_nd - (len(bshape) - len(at))) + len(at)
+                else:
+                    return False
+                if vshape[vs.dim] != bshape[bdim]:
+                    return False
+                sp = Spec("S", bdim, vs.counts, vs.striped)
+            if sp.kind == "R":
+                if put and self.spec[vname][ax].kind not in ("R", "P"):
+                    return False
+                base_want.append(R); out_spec.append(R); val_want.append(R)
+                continue
+            if sp.kind != "S" or sp.dim in at:
+                return False
+            if sp.dim < first:
+                moved = sp.dim
+            elif together and sp.dim > last:
+                moved = sp.dim - len(at) + spread
+            else:
+                return False
+            found = True
+            base_want.append(sp)
+            if put:
+                # the values line up with the indexed result (trailing-aligned broadcast): cut them where they span the
+                # dimension, keep them whole where they broadcast over it
+                res_dim = sp.dim if sp.dim < first else sp.dim - len(at) + (res_nd - (len(bshape) - len(at)))
+                vdim = res_dim - (res_nd - len(vshape))
+                if vdim >= 0 and vshape[vdim] == bshape[sp.dim]:
+                    val_want.append(Spec("S", vdim, sp.counts, sp.striped))
+                elif vdim < 0 or vshape[vdim] == 1:
+                    val_want.append(R)
+                else:
+                    return False
+                out_spec.append(sp)
+            else:
+                out_spec.append(Spec("S", moved, sp.counts, sp.striped))
+        if not found:
+            return False
+        new_names = {base.name: self.reshard(bname, tuple(base_want))}
+        for i in at:
+            iname = self.renamed.get(indices[i].name, indices[i].name)
+            new_names[indices[i].name] = self.reshard(iname, self.all_r())
+        if put:
+            if any(s.kind == "P" for s in self.spec[vname]) and not all(w.kind == "R" for w in val_want):
+                pass                                         # reshard below sums partial values first
+            new_names[values.name] = self.reshard(vname, tuple(val_want))
+        self.spec[node.name] = tuple(out_spec)
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
+                               self.ref_kwargs(node.kwargs, new_names), {"out_specs": tuple(out_spec), "full_shape": _shape(node)}))
+        return True
+
     def _spatial_cut(self, x: str):
         """``((axis, spec), {axis: batch spec})`` when ``x`` is cut along exactly one spatial dimension (contiguous) and,
         on other grid axes, at most along the batch dimension; ``(None, None)`` otherwise."""
@@ -1213,13 +1436,15 @@ class Propagator:
         i = sp.dim - 2
         k = self.shape[w][sp.dim]
         reach = dilation[i] * (k - 1)
-        if stride[i] != 1 or 2 * padding[i] != reach or min(sp.counts) < max(padding[i], reach - padding[i]):
+        halo = self._halo_extent(self.shape[x][sp.dim], _shape(node)[sp.dim], sp.counts, stride[i], padding[i], reach)
+        if halo is None:
             return False
-        left, right = padding[i], reach - padding[i]
+        left, right = halo
+        small = tuple(c // stride[i] for c in sp.counts)
         src = x
-        if reach and (x, left, right) in self.extended:
+        if left + right and (x, left, right) in self.extended:
             src = self.extended[(x, left, right)]
-        elif reach:
+        elif left + right:
             src = self.fresh(x)
             self.extended[(x, left, right)] = src
             self.channel += 1
@@ -1236,7 +1461,7 @@ class Propagator:
         padding[i] = 0
         new_args = list(self.ref_args(node.args, {node.args[0].name: src}))
         new_args[4] = padding
-        out_spec = tuple(Spec("S", sp.dim, sp.counts) if a == ax else batch.get(a, R) for a in range(self.na))
+        out_spec = tuple(Spec("S", sp.dim, small) if a == ax else batch.get(a, R) for a in range(self.na))
         self.spec[node.name] = out_spec
         self.steps.append(Step("call", node.name, node.target, tuple(new_args), self.ref_kwargs(node.kwargs),
                                {"out_specs": out_spec, "full_shape": _shape(node), "halo": (left, right)}))
@@ -1244,6 +1469,22 @@ class Propagator:
         if want is not None and want != out_spec:
             self.renamed[node.name] = self.reshard(node.name, want)
         return True
+
+    @staticmethod
+    def _halo_extent(n_in: int, n_out: int, counts, stride: int, padding: int, reach: int):
+        """``(left, right)`` rows a processor needs from its neighbours so that it can compute, from its own block of a
+        cut dimension, the outputs whose windows start in that block; ``None`` when the outputs do not divide that way.
+        They do when every block is a multiple of the stride and the operator makes one output per ``stride`` inputs
+        ('same' windows at stride 1, the usual halving convolutions, patch embeddings): output ``o`` reads inputs
+        ``o * stride - padding .. + reach``, so a block starting at a multiple of the stride needs ``padding`` rows on
+        its left and ``reach - padding - (stride - 1)`` on its right (none when that is negative: its last rows are
+        then read by nobody)."""
+        if n_in % stride or n_out * stride != n_in or any(c % stride for c in counts):
+            return None
+        left, right = padding, max(reach - padding - (stride - 1), 0)
+        if left + right and min(counts) < max(left, right):
+            return None
+        return left, right
 
     def _halo_step(self, x: str, ax: int, sp: Spec, left: int, right: int, verb: str = "halo") -> str:
         """Emit the neighbour exchange of ``x``'s edge rows (or, for ``halo_back``, its adjoint); returns the new value."""
@@ -1262,6 +1503,307 @@ class Propagator:
         self.spec[out] = self.spec[x]
         return out
 
+    def _channel_axes(self, x: str, w: str, transposed: bool, out_of_grad: bool = False):
+        """Per grid axis, how a convolution's channels are cut: ``"out"`` (the weight along its output channels, the
+        column-parallel form), ``"in"`` (the input along its channels and the weight, if cut, the same way: the
+        row-parallel form, partial sums), ``"batch"``, ``None`` (whole), or ``False`` when the rule does not apply."""
+        o_dim, i_dim = (1, 0) if transposed else (0, 1)
+        kinds = []
+        for a in range(self.na):
+            xs, ws = self.spec[x][a], self.spec[w][a]
+            if xs.kind not in ("R", "S") or ws.kind not in ("R", "S"):
+                return False
+            if ws.kind == "S" and ws.dim == o_dim and xs.kind == "R":
+                kinds.append(("out", ws))
+            elif xs.kind == "S" and xs.dim == 1 and (ws.kind == "R" or (ws.dim == i_dim and ws.counts == xs.counts and ws.striped == xs.striped)):
+                kinds.append(("in", xs))
+            elif xs.kind == "S" and xs.dim == 0 and ws.kind == "R":
+                kinds.append(("batch", xs))
+            elif xs.kind == "R" and ws.kind == "R":
+                kinds.append((None, None))
+            else:
+                return False
+        if not any(k in ("out", "in") for k, _ in kinds):
+            return False                                   # nothing of this rule's: batch cuts have their own
+        return kinds
+
+    def channel_norm(self, node, tnames) -> bool:
+        """Batch norm (every variant, forward and backward) over an input cut along its channels: channels are normalised
+        independently, so every processor works on its own with the matching slices of the per-channel vectors, and
+        the per-channel results come out cut the same way.  Instance norm reaches this rule as a batch norm over
+        ``[1, samples * channels, ...]`` when the samples are cut."""
+        layout = _CHANNEL_NORMS[node.target]
+        names = [self.renamed.get(a.name, a.name) if _is_tensor_node(a) else None for a in node.args[: layout["tensors"]]]
+        full = [names[i] for i in layout["full"]]
+        x = full[0]
+        if len(self.shape[x]) < 2:
+            return False
+        wants = {n: [] for n in names if n is not None}
+        big, small = [], []
+        found = False
+        for a in range(self.na):
+            sp = self.spec[x][a]
+            others = [self.spec[n][a] for n in names if n is not None and n != x]
+            if sp.kind == "S" and sp.dim == 1 and all(o.kind in ("R", "S") for o in others):
+                found = True
+                big.append(Spec("S", 1, sp.counts, sp.striped)); small.append(Spec("S", 0, sp.counts, sp.striped))
+            elif sp.kind == "R" and all(o.kind == "R" for o in others):
+                big.append(R); small.append(R)
+            else:
+                return False
+            for i, n in enumerate(names):
+                if n is not None and len(wants[n]) <= a:
+                    wants[n].append(big[-1] if i in layout["full"] else small[-1])
+        if not found:
+            return False
+        new_names = {}
+        for arg, n in zip(node.args[: layout["tensors"]], names):
+            if n is not None:
+                new_names[arg.name] = self.reshard(n, tuple(wants[n]))
+        val = node.meta["val"]
+        for j, v in enumerate(val):
+            if v is None:
+                continue
+            kind = layout["outs"][j]
+            sp = tuple(big) if kind == "full" else tuple(small) if (kind == "vector" and v.numel()) else self.all_r()
+            self.spec[(node.name, j)] = sp
+        self.spec[node.name] = self.all_r()
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
+                               self.ref_kwargs(node.kwargs, new_names), {"out_specs": tuple(big), "full_shape": tuple(self.shape[x])}))
+        return True
+
+    def depthwise_convolution(self, node, tnames, backward: bool = False) -> bool:
+        """A convolution with one group per input channel, cut along the channels: the groups are independent, so every
+        processor convolves its channels with its rows of the weight; the number of groups it passes is the number of
+        channels it holds."""
+        args = list(node.args)
+        off = 1 if backward else 0
+        transposed, groups = args[6 + off], args[8 + off]
+        x, w = tnames[off], tnames[1 + off]
+        cin = self.shape[x][1]
+        if transposed or groups != cin or groups == 1 or self.shape[w][1] != 1 or self.shape[w][0] % cin:
+            return False
+        mult = self.shape[w][0] // cin
+        others = tnames[:off] + tnames[2 + off:]
+        xs_, ws_, found = [], [], None
+        for a in range(self.na):
+            sp, wsp = self.spec[x][a], self.spec[w][a]
+            if sp.kind == "S" and sp.dim == 1 and not sp.striped and wsp.kind in ("R", "S"):
+                if found is not None:
+                    return False
+                found = (a, tuple(sp.counts))
+                xs_.append(sp); ws_.append(Spec("S", 0, tuple(c * mult for c in sp.counts)))
+            elif sp.kind == "S" and sp.dim == 0 and wsp.kind == "R":
+                xs_.append(sp); ws_.append(R)
+            elif sp.kind == "R" and wsp.kind == "R":
+                xs_.append(R); ws_.append(R)
+            else:
+                return False
+        if found is None or any(self.spec[n][a].kind not in ("R", "S", "P") for n in others for a in range(self.na)):
+            return False
+        outs_ = tuple(Spec("S", 1, s.counts) if (s.kind == "S" and s.dim == 0 and a == found[0]) else x_ for a, (s, x_) in enumerate(zip(ws_, xs_)))
+        new_names = {node.args[off].name: self.reshard(x, tuple(xs_)), node.args[1 + off].name: self.reshard(w, tuple(ws_))}
+        meta = {"groups_local": (8 + off, found[0], found[1]), "full_shape": _shape(node) if not backward else ()}
+        if not backward:
+            if len(tnames) > 2:
+                new_names[node.args[2].name] = self.reshard(tnames[2], tuple(s if s.kind == "S" and s.dim == 0 and a == found[0] else R for a, s in enumerate(ws_)))
+            self.spec[node.name] = outs_
+            meta["out_specs"] = outs_
+            self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names), self.ref_kwargs(node.kwargs), meta))
+            want = self.stated.get(node.name)
+            if want is not None and want != outs_:
+                self.renamed[node.name] = self.reshard(node.name, want)
+            return True
+        mask = list(args[10])
+        new_names[node.args[0].name] = self.reshard(tnames[0], outs_)
+        if args[3] is not None:
+            meta["bias_sizes"] = (found[0], tuple(c * mult for c in found[1]))
+        raw = self.fresh(node.name)
+        self.steps.append(Step("call", raw, node.target, self.ref_args(node.args, new_names), self.ref_kwargs(node.kwargs), meta))
+        vec = tuple(s if (s.kind == "S" and a == found[0]) else (P() if xs_[a].kind == "S" else R) for a, s in enumerate(ws_))
+        items = []
+        for j, sp in enumerate((tuple(xs_), vec, vec)):
+            if not mask[j]:
+                items.append(None)
+                continue
+            item = self.fresh(f"{node.name}_{j}")
+            self.steps.append(Step("call", item, operator.getitem, (Ref(raw), j)))
+            v = node.meta["val"][j]
+            self.shape[item], self.dtype[item] = tuple(v.shape), v.dtype
+            self.spec[item] = sp
+            self.spec[(node.name, j)] = sp
+            items.append(item)
+        self.spec[node.name] = self.all_r()
+        self.shape[node.name] = ()
+        self.steps.append(Step("call", node.name, pack, tuple(Ref(it) if it is not None else None for it in items)))
+        return True
+
+    def channel_convolution(self, node, tnames) -> bool:
+        """A convolution (or transposed convolution) without groups whose channels are cut.  Output channels cut on the
+        weight: every processor computes its own output channels from the whole input (the bias is cut the same way).
+        Input channels cut: every processor convolves its channels with the matching slice of the weight and the
+        results are partial sums; the bias joins after the sum.  The convolution analogue of column- and row-parallel
+        linear layers (the reference derives both from the contraction labels of its rules,
+        compiler/mesh_compiler/placement.py:503-517)."""
+        args = list(node.args)
+        transposed, groups = args[6], args[8]
+        if groups != 1:
+            return False
+        x, w = tnames[0], tnames[1]
+        b = tnames[2] if len(tnames) > 2 else None
+        kinds = self._channel_axes(x, w, transposed)
+        if not kinds:
+            return False
+        if b is not None and any(sp.kind not in ("R", "S") for sp in self.spec[b]):
+            return False
+        o_dim, i_dim = (1, 0) if transposed else (0, 1)
+        xw, ww, bw, out = [], [], [], []
+        for k, sp in kinds:
+            if k == "out":
+                xw.append(R); ww.append(Spec("S", o_dim, sp.counts, sp.striped)); bw.append(Spec("S", 0, sp.counts, sp.striped))
+                out.append(Spec("S", 1, sp.counts, sp.striped))
+            elif k == "in":
+                xw.append(sp); ww.append(Spec("S", i_dim, sp.counts, sp.striped)); bw.append(R); out.append(P())
+            elif k == "batch":
+                xw.append(sp); ww.append(R); bw.append(R); out.append(sp)
+            else:
+                xw.append(R); ww.append(R); bw.append(R); out.append(R)
+        partial = any(o.kind == "P" for o in out)
+        new_names = {node.args[0].name: self.reshard(x, tuple(xw)), node.args[1].name: self.reshard(w, tuple(ww))}
+        full = _shape(node)
+        if b is not None and not partial:
+            new_names[node.args[2].name] = self.reshard(b, tuple(bw))
+        call_args = list(self.ref_args(node.args, new_names))
+        target = node.name
+        if b is not None and partial:
+            call_args[2] = None                            # the bias is added once, after the sum
+            target = self.fresh(node.name)
+            self.shape[target] = full
+            self.dtype[target] = self.dtype[node.name]
+        self.spec[target] = tuple(out)
+        self.steps.append(Step("call", target, node.target, tuple(call_args), self.ref_kwargs(node.kwargs),
+                               {"out_specs": tuple(out), "full_shape": full}))
+        if b is not None and partial:
+            summed = tuple(R if o.kind == "P" else o for o in out)
+            whole = self.reshard(target, summed)
+            # channel cuts of other axes also cut the bias: state its placement, then line it up with the channels
+            bias = self.reshard(b, tuple(bw))
+            lined = self.fresh(b)
+            shape = [1, full[1]] + [1] * (len(full) - 2)
+            lined_spec = tuple(Spec("S", 1, s.counts, s.striped) if s.kind == "S" else R for s in bw)
+            self.shape[lined], self.dtype[lined], self.spec[lined] = tuple(shape), self.dtype.get(b, self.dtype[node.name]), lined_spec
+            self.steps.append(Step("call", lined, aten.view.default, (Ref(bias), shape), {},
+                                   {"out_specs": lined_spec, "full_shape": tuple(shape), "localize": ("shape", 1)}))
+            self.spec[node.name] = summed
+            self.steps.append(Step("call", node.name, aten.add.Tensor, (Ref(whole), Ref(lined)), {},
+                                   {"out_specs": summed, "full_shape": full}))
+        want = self.stated.get(node.name)
+        if want is not None and want != self.spec[node.name]:
+            self.renamed[node.name] = self.reshard(node.name, want)
+        return True
+
+    def channel_convolution_backward(self, node, tnames) -> bool:
+        """The backward of :meth:`channel_convolution`.  Output channels cut: the incoming gradient is cut along its
+        channels, the weight and bias gradients come out cut the same way, and the input gradient is a partial sum
+        over the output channels.  Input channels cut: the incoming gradient is whole, the input and weight gradients
+        are cut along the input channels, and every processor computes the same bias gradient."""
+        args = list(node.args)
+        transposed, groups, mask = args[7], args[9], list(args[10])
+        if groups != 1:
+            return False
+        g, x, w = tnames[0], tnames[1], tnames[2]
+        kinds = self._channel_axes(x, w, transposed)
+        if not kinds or any(sp.kind not in ("R", "S", "P") for sp in self.spec[g]):
+            return False
+        o_dim, i_dim = (1, 0) if transposed else (0, 1)
+        gw, xw, ww, dx, dw, db = [], [], [], [], [], []
+        local_bias = None
+        for a, (k, sp) in enumerate(kinds):
+            if k == "out":
+                gw.append(Spec("S", 1, sp.counts, sp.striped)); xw.append(R); ww.append(Spec("S", o_dim, sp.counts, sp.striped))
+                dx.append(P()); dw.append(Spec("S", o_dim, sp.counts, sp.striped)); db.append(Spec("S", 0, sp.counts, sp.striped))
+                local_bias = (a, tuple(sp.counts))
+            elif k == "in":
+                gw.append(R); xw.append(sp); ww.append(Spec("S", i_dim, sp.counts, sp.striped))
+                dx.append(sp); dw.append(Spec("S", i_dim, sp.counts, sp.striped)); db.append(R)
+            elif k == "batch":
+                gw.append(sp); xw.append(sp); ww.append(R); dx.append(sp); dw.append(P()); db.append(P())
+            else:
+                gw.append(R); xw.append(R); ww.append(R); dx.append(R); dw.append(R); db.append(R)
+        new_names = {node.args[0].name: self.reshard(g, tuple(gw)), node.args[1].name: self.reshard(x, tuple(xw)),
+                     node.args[2].name: self.reshard(w, tuple(ww))}
+        raw = self.fresh(node.name)
+        meta = {"full_shape": ()}
+        if local_bias is not None and args[3] is not None:
+            meta["bias_sizes"] = local_bias                # the bias extent argument: this processor's channels
+        self.steps.append(Step("call", raw, node.target, self.ref_args(node.args, new_names), self.ref_kwargs(node.kwargs), meta))
+        items = []
+        for j, sp in enumerate((dx, dw, db)):
+            if not mask[j]:
+                items.append(None)
+                continue
+            item = self.fresh(f"{node.name}_{j}")
+            self.steps.append(Step("call", item, operator.getitem, (Ref(raw), j)))
+            val = node.meta["val"][j]
+            self.shape[item], self.dtype[item] = tuple(val.shape), val.dtype
+            self.spec[item] = tuple(sp)
+            self.spec[(node.name, j)] = tuple(sp)
+            items.append(item)
+        self.spec[node.name] = self.all_r()
+        self.shape[node.name] = ()
+        self.steps.append(Step("call", node.name, pack, tuple(Ref(it) if it is not None else None for it in items)))
+        return True
+
+    def patch_transposed_convolution(self, node, tnames, backward: bool = False) -> bool:
+        """A transposed convolution whose windows do not overlap along a cut spatial dimension (stride = kernel there, no
+        padding, dilation or output padding: the usual learned upsampling): every input row makes ``stride`` output rows
+        of its own, so each processor works on its block alone and the output is cut at the same places times the
+        stride.  In the backward the weight and bias gradients are partial sums."""
+        off = 1 if backward else 0
+        args = list(node.args)
+        stride, padding, dilation, transposed, out_pad = args[3 + off], args[4 + off], args[5 + off], args[6 + off], args[7 + off]
+        x, w = tnames[off], tnames[1 + off]
+        if not transposed or any(self.spec[n][a].kind != "R" for n in tnames[1 + off:] for a in range(self.na)):
+            return False
+        cut, batch = self._spatial_cut(x)
+        if cut is None:
+            return False
+        ax, sp = cut
+        i = sp.dim - 2
+        if self.shape[w][sp.dim] != stride[i] or padding[i] or dilation[i] != 1 or out_pad[i]:
+            return False
+        big = tuple(Spec("S", sp.dim, tuple(c * stride[i] for c in sp.counts)) if a == ax else batch.get(a, R) for a in range(self.na))
+        like_input = tuple(Spec("S", sp.dim, sp.counts) if a == ax else batch.get(a, R) for a in range(self.na))
+        if not backward:
+            self.spec[node.name] = big
+            self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args), self.ref_kwargs(node.kwargs),
+                                   {"out_specs": big, "full_shape": _shape(node)}))
+            want = self.stated.get(node.name)
+            if want is not None and want != big:
+                self.renamed[node.name] = self.reshard(node.name, want)
+            return True
+        g = tnames[0]
+        mask = list(args[10])
+        new_names = {node.args[0].name: self.reshard(g, big)}
+        raw = self.fresh(node.name)
+        self.steps.append(Step("call", raw, node.target, self.ref_args(node.args, new_names), self.ref_kwargs(node.kwargs), {"full_shape": ()}))
+        partial = tuple(P() if (a == ax or a in batch) else R for a in range(self.na))
+        items = []
+        for j in range(3):
+            if not mask[j]:
+                items.append(None)
+                continue
+            item = self.fresh(f"{node.name}_{j}")
+            self.steps.append(Step("call", item, operator.getitem, (Ref(raw), j)))
+            val = node.meta["val"][j]
+            self.shape[item], self.dtype[item] = tuple(val.shape), val.dtype
+            self.spec[item] = self.spec[(node.name, j)] = like_input if j == 0 else partial
+            items.append(item)
+        self.spec[node.name] = self.all_r()
+        self.shape[node.name] = ()
+        self.steps.append(Step("call", node.name, pack, tuple(Ref(it) if it is not None else None for it in items)))
+        return True
+
     def halo_convolution_backward(self, node, tnames) -> bool:
         """The backward of :meth:`halo_convolution`.  Every processor differentiates the convolution of its own extended
         block: the weight and bias gradients are partial sums; the gradient with respect to the extended block has
@@ -1278,15 +1820,15 @@ class Propagator:
         i = sp.dim - 2
         k = self.shape[w][sp.dim]
         reach = dilation[i] * (k - 1)
-        if stride[i] != 1 or 2 * padding[i] != reach or min(sp.counts) < max(padding[i], reach - padding[i]):
+        halo = self._halo_extent(self.shape[x][sp.dim], self.shape[g][sp.dim], sp.counts, stride[i], padding[i], reach)
+        if halo is None:
             return False
-        if self.shape[g][sp.dim] != self.shape[x][sp.dim]:
-            return False
-        left, right = padding[i], reach - padding[i]
-        same = tuple(Spec("S", sp.dim, sp.counts) if a == ax else batch.get(a, R) for a in range(self.na))
+        left, right = halo
+        small = tuple(c // stride[i] for c in sp.counts)
+        same = tuple(Spec("S", sp.dim, small) if a == ax else batch.get(a, R) for a in range(self.na))
         g_local = self.reshard(g, same)
         x_ext = x
-        if reach:
+        if left + right:
             x_ext = self.extended.get((x, left, right)) or self._halo_step(x, ax, sp, left, right)
             self.extended[(x, left, right)] = x_ext
         padding[i] = 0
@@ -1296,6 +1838,7 @@ class Propagator:
         self.steps.append(Step("call", raw, node.target, tuple(new_args), self.ref_kwargs(node.kwargs),
                                {"halo": (left, right), "full_shape": ()}))
         partial = tuple(P() if (a == ax or a in batch) else R for a in range(self.na))     # sums over rows and samples
+        like_input = tuple(Spec("S", sp.dim, sp.counts) if a == ax else batch.get(a, R) for a in range(self.na))
         items = []
         for j in range(3):
             if not mask[j]:
@@ -1305,14 +1848,14 @@ class Propagator:
             self.steps.append(Step("call", item, operator.getitem, (Ref(raw), j)))
             val = node.meta["val"][j]
             self.shape[item], self.dtype[item] = tuple(val.shape), val.dtype
-            self.spec[item] = same if j == 0 else partial
-            if j == 0 and reach:
+            self.spec[item] = like_input if j == 0 else partial
+            if j == 0 and left + right:
                 self.shape[item] = self.shape[x]
                 if x in self.dtype:
                     self.dtype[item] = self.dtype[x]
                 item = self._halo_step(item, ax, sp, left, right, "halo_back")
             items.append(item)
-            self.spec[(node.name, j)] = same if j == 0 else partial
+            self.spec[(node.name, j)] = like_input if j == 0 else partial
         self.spec[node.name] = self.all_r()
         self.shape[node.name] = ()
         self.steps.append(Step("call", node.name, pack, tuple(Ref(it) if it is not None else None for it in items)))
@@ -1321,18 +1864,25 @@ class Propagator:
     def fallback(self, node, tnames, list_args):
         """Rule miss: gather every tensor input and run the op replicated."""
         new_names = {}
+        gathered = 0                               # operands that were not whole everywhere: each costs a transfer
+
+        def whole(x):
+            nonlocal gathered
+            src = self.renamed.get(x.name, x.name)
+            gathered += any(s.kind != "R" for s in self.spec.get(src, ()))
+            new_names[x.name] = self.reshard(src, self.all_r())
         for a in node.args:
             if _is_tensor_node(a):
-                new_names[a.name] = self.reshard(self.renamed.get(a.name, a.name), self.all_r())
+                whole(a)
         for la in list_args:
             for x in la:
                 if _is_tensor_node(x):
-                    new_names[x.name] = self.reshard(self.renamed.get(x.name, x.name), self.all_r())
+                    whole(x)
         for v in node.kwargs.values():
             if _is_tensor_node(v):
-                new_names[v.name] = self.reshard(self.renamed.get(v.name, v.name), self.all_r())
+                whole(v)
         self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
-                               self.ref_kwargs(node.kwargs, new_names), {"fallback": True}))
+                               self.ref_kwargs(node.kwargs, new_names), {"fallback": True, "gathered": gathered}))
         self.spec[node.name] = self.all_r()
 
     def ref_args(self, args, rename=None):

@@ -653,6 +653,12 @@ class Executor:
                 extra[0] = mask
                 return tgt(q, k, args[2], *extra, **kw)
             return tgt(q, k, args[2], attn_mask=mask, is_causal=False, **kw)
+        if "groups_local" in m:                            # (argument, grid axis, channels per processor): one group per channel held
+            pos, ax, counts = m["groups_local"]
+            args[pos] = counts[self.coords[ax]]
+        if "bias_sizes" in m:                              # (grid axis, channels per processor): this processor's extent
+            ax, counts = m["bias_sizes"]
+            args[3] = [counts[self.coords[ax]]]
         if "batch_arg" in m:
             args[m["batch_arg"]] = args[0].shape[0]        # the operator takes the batch size as a number: this shard's
         loc = m.get("localize")

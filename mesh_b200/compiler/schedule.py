@@ -97,6 +97,8 @@ def schedule(plan: Plan, cost=unit_cost) -> tuple[Signature, dict]:
         "bytes_between_processors": int(sum(t.nbytes for t in plan.transfers)),
         "calls": sum(1 for s in plan.steps if s.op == "call"),
         "fallbacks": sum(1 for s in plan.steps if s.meta.get("fallback")),
+        # rule misses that cost something: an operand that was cut or partial had to be made whole first
+        "gathering_fallbacks": sum(1 for s in plan.steps if s.meta.get("fallback") and s.meta.get("gathered")),
         "local_slices": sum(1 for s in plan.steps if s.op == "slice"),
         "levels": level,
         "uncovered": uncovered, "unwaited": unwaited, "redundant": redundant,
