@@ -82,6 +82,9 @@ def _direct(st, coords=()) -> str | None:
         return _view(st, coords)
     if not isinstance(t, torch._ops.OpOverload) or t.namespace != "aten" or t in _DISPATCHED or any(k in st.meta for k in _SPECIAL):
         return None
+    stated = list(st.meta.get("out_specs", ())) + [sp for item in st.meta.get("items", {}).values() for sp in item[0]]
+    if any(getattr(sp, "kind", "R") == "S" and 0 in sp.counts for sp in stated):
+        return None                               # some processor's share is empty: the executor states that result itself
     args = [_lit(a) for a in st.args]
     kwargs = {k: _lit(v) for k, v in st.kwargs.items()}
     if any(a is None for a in args) or any(v is None for v in kwargs.values()):

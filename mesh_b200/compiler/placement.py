@@ -736,8 +736,24 @@ class Propagator:
                         output_specs[name] = want
                     else:
                         outputs.append(("const", o))
+        self._describe_items()
         return Plan(self.mesh, self.steps, inputs_order, input_specs, outputs, output_specs, self.transfers,
                     dict(self.shape), dict(self.dtype))
+
+    def _describe_items(self) -> None:
+        """Operators with several results: note on the step what each item is (placement, whole shape, dtype), read off
+        the ``getitem`` steps that take them apart.  The executor needs it when a processor's share of a cut operand is
+        empty and it states the results itself instead of calling an operator that refuses empty operands."""
+        makers = {st.out: st for st in self.steps if st.op == "call" and not st.meta.get("fallback")}
+        for st in self.steps:
+            if st.op != "call" or st.target is not operator.getitem or not isinstance(st.args[0], Ref):
+                continue
+            maker = makers.get(st.args[0].name)
+            j = st.args[1]
+            if maker is None or maker.target is operator.getitem or not isinstance(j, int):
+                continue
+            if st.out in self.spec and st.out in self.dtype and st.out in self.shape:
+                maker.meta.setdefault("items", {})[j] = (self.spec[st.out], tuple(self.shape[st.out]), self.dtype[st.out])
 
     def call(self, node):
         tgt = node.target

@@ -625,6 +625,37 @@ class Executor:
         m = st.meta
         if "draw" in m:
             return self.draw(m, args)
+        if "out_specs" in m and st.out in self.plan.dtypes and m.get("full_shape") and \
+                any(isinstance(a, torch.Tensor) and a.numel() == 0 for a in args):
+            # this processor's share of a cut operand is empty (more processors than rows, or a share that rounds to
+            # nothing).  Operators disagree about empty operands (some refuse them, a convolution over no channels
+            # returns the wrong shape), and the result is known anyway: nothing where the cut dimension stays, the
+            # reduction's identity where it is summed over.
+            shape = list(m["full_shape"])
+            pending = None
+            for ax, sp in enumerate(m["out_specs"]):
+                if sp.kind == "S" and sp.dim < len(shape):
+                    shape[sp.dim] = sp.counts[self.coords[ax]]
+                elif sp.kind == "P":
+                    pending = sp.op
+            if pending is not None or 0 in shape:
+                dtype = self.plan.dtypes[st.out]
+                fill = 0 if pending in (None, "sum") else _identity(pending, dtype)
+                return torch.full(shape, fill, dtype=dtype, device=self.device)
+        if "items" in m and any(isinstance(a, torch.Tensor) and a.numel() == 0 for a in args):
+            # the same for an operator with several results (a convolution's backward, a norm with its statistics, a
+            # pooling with its indices): each item by its own placement
+            items = [None] * (max(m["items"]) + 1)
+            for j, (specs, full, dtype) in m["items"].items():
+                shape, pending = list(full), None
+                for ax, sp in enumerate(specs):
+                    if sp.kind == "S" and sp.dim < len(shape):
+                        shape[sp.dim] = sp.counts[self.coords[ax]]
+                    elif sp.kind == "P":
+                        pending = sp.op
+                fill = 0 if pending in (None, "sum") else _identity(pending, dtype)
+                items[j] = torch.full(shape, fill, dtype=dtype, device=self.device)
+            return tuple(items)
         if "causal_rows" in m:
             # whole attention over this processor's query rows: row i of the whole sequence sees keys 0..i
             ax = m["causal_rows"]
@@ -719,6 +750,15 @@ class Executor:
         if tgt in _COMPUTE:
             self.kernels.eager += 1
         return tgt(*args, **kwargs)
+
+
+def _identity(op: str, dtype):
+    """The value a reduction starts from: what an empty share contributes."""
+    if op == "max":
+        return -float("inf") if dtype.is_floating_point else (False if dtype == torch.bool else torch.iinfo(dtype).min)
+    if op == "min":
+        return float("inf") if dtype.is_floating_point else (True if dtype == torch.bool else torch.iinfo(dtype).max)
+    return 0
 
 
 # operators with a kernel of this package behind them when the operands allow it: the ones counted as "eager" when

@@ -112,17 +112,37 @@ CASES = [
 
 @pytest.mark.parametrize("name,dim,train,kept", CASES)
 def test_module_under_a_cut_matches_eager(name, dim, train, kept):
+    _run(name, dim, train, kept, 2, None)
+
+
+# shares that are unequal, and shares that come out empty (more processors than channels or rows): operators that refuse
+# empty operands are not called there; the executor states the empty or zero result itself
+UNEVEN = [
+    ("strided_convolutions", 1, True, 3, (3, 1, 2)), ("pooled_classifier", 1, True, 3, (3, 1, 2)),
+    ("volumes", 1, True, 3, (3, 1, 2)), ("resized", 1, False, 3, (3, 1, 2)), ("residual_batch_norm", 1, True, 3, (1, 2, 1)),
+    ("learned_upsampling", 2, True, 5, None), ("learned_upsampling", 1, True, 5, None), ("depthwise_separable", 1, True, 5, (4, 0, 1, 2, 1)),
+    ("instance_norm", 0, True, 5, None), ("instance_norm", 2, True, 5, (5, 0, 3, 2, 2)), ("patch_embedding", 2, True, 5, None),
+    ("extremes", 0, True, 5, None),
+]
+
+
+@pytest.mark.parametrize("name,dim,train,n,units", UNEVEN)
+def test_module_under_uneven_and_empty_shares_matches_eager(name, dim, train, n, units):
+    _run(name, dim, train, False, n, units)
+
+
+def _run(name, dim, train, kept, n, units):
     make, shape = ZOO[name]
     torch.manual_seed(0)
     model = make()
     x = torch.randn(*shape)
-    procs = _procs(2)
+    procs = _procs(n)
     names = tuple(procs)
 
     def place(node):
         val = node.meta.get("val")
         mine = node.op == "placeholder" and not node.name.startswith(("p_", "b_")) and getattr(val, "shape", None) == x.shape
-        return (dim, names, None) if mine else None
+        return (dim, names, units) if mine else None
 
     if not train:
         model.eval()
