@@ -50,6 +50,7 @@ def save(directory, scheduled: Scheduled, exported_program=None) -> None:
         "structure": scheduled.structure,
         "output_processor": scheduled.output_processor,
         "training": ex.training,
+        "tied": dict(ex.tied),
     }
     tmp = d / "scheduled.json.tmp"
     tmp.write_text(json.dumps(meta, indent=1, default=str))
@@ -66,6 +67,11 @@ def load(directory) -> Scheduled:
     for name, t in state.items():                 # the archive's own copy of the state tensors
         if name in exported.state:
             exported.state[name] = (exported.state[name][0], t)
+    exported.tied = dict(meta.get("tied") or {})
+    by_name = {qual: t for qual, t in exported.state.values()}
+    for name, (qual, _t) in list(exported.state.items()):     # names that share a tensor read one tensor again
+        if qual in exported.tied and exported.tied[qual] in by_name:
+            exported.state[name] = (qual, by_name[exported.tied[qual]])
     input_specs = {k: tuple(_spec_from(s) for s in v) for k, v in meta["input_specs"].items()}
     out_specs = {int(i): tuple(_spec_from(s) for s in v) for i, v in meta["output_specs"].items()}
     processors = {k: tuple(v) for k, v in meta["processors"].items()}

@@ -35,6 +35,22 @@ def _default_table() -> dict:
     return dict(_TABLE)
 
 
+def _views_may_copy(gm: torch.fx.GraphModule) -> int:
+    """Every ``view`` of the traced module becomes a ``reshape`` before the graph is traced again with composite
+    operators expanded.  The first trace runs fused operators (attention above all) whose results have the memory
+    layout of their kernels; module code after them (``transpose(1, 2)`` then ``view``) relies on that layout.  Expanded
+    into products and a softmax, the same value comes out dense in another order, and a ``view`` that was legal on the
+    first layout is not on the second: a ``reshape`` copies there and stays a view everywhere else."""
+    n = 0
+    for node in gm.graph.nodes:
+        if node.op == "call_function" and node.target in (torch.ops.aten.view.default, torch.ops.aten._unsafe_view.default):
+            node.target = torch.ops.aten.reshape.default
+            n += 1
+    if n:
+        gm.recompile()
+    return n
+
+
 def _inference_table() -> dict:
     """The default table without attention, which inference graphs keep whole."""
     table = _default_table()
@@ -47,6 +63,58 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
     """Export ``module(*args, **kwargs)``; with ``loss`` (index of the loss among flat outputs) the joint graph.
     ``inner_cuts``: an input is cut along an inner leading dimension (see :func:`unflatten_linears`): linear layers keep
     their operands' leading dimensions apart (inference graphs)."""
+    tied = _untie(module) if loss is not None else {}
+    try:
+        exported = _export(module, args, kwargs, loss, strict, decompositions, inner_cuts)
+    finally:
+        _retie(module, tied)
+    for name, (qual, _tensor) in list(exported.state.items()):
+        if qual in tied:                                    # the placeholder reads the shared tensor, not the stand-in
+            exported.state[name] = (qual, tied[qual][1])
+    exported.tied = {alias: first for alias, (first, _p) in tied.items()}
+    return exported
+
+
+def _untie(module: torch.nn.Module) -> dict:
+    """Parameters that are one tensor under several names (an output projection tied to the embedding): the joint
+    forward+backward capture wants a gradient per parameter name and refuses a name that gets none, so every later
+    name gets a stand-in of its own for the capture.  Returns ``{later name: (first name, the shared parameter)}``;
+    the program then returns, under both names, the sum of the two gradients (:func:`tied_gradients`)."""
+    seen, tied = {}, {}
+    for name, p in module.named_parameters(remove_duplicate=False):
+        if id(p) in seen:
+            tied[name] = (seen[id(p)], p)
+        else:
+            seen[id(p)] = name
+    for name, (_first, p) in tied.items():
+        owner, _, leaf = name.rpartition(".")
+        holder = module.get_submodule(owner) if owner else module
+        holder._parameters[leaf] = torch.nn.Parameter(p.detach().clone(), requires_grad=p.requires_grad)
+    return tied
+
+
+def _retie(module: torch.nn.Module, tied: dict) -> None:
+    for name, (_first, p) in tied.items():
+        owner, _, leaf = name.rpartition(".")
+        holder = module.get_submodule(owner) if owner else module
+        holder._parameters[leaf] = p
+
+
+def tied_gradients(grads: dict, tied: dict) -> dict:
+    """Gradients by parameter name, with the names that share a tensor carrying the sum of their gradients."""
+    if not tied:
+        return grads
+    total: dict = {}
+    for name, g in grads.items():
+        first = tied.get(name, name)
+        if g is not None:
+            total[first] = g if total.get(first) is None else total[first] + g
+        else:
+            total.setdefault(first, None)
+    return {name: total.get(tied.get(name, name)) for name in grads}
+
+
+def _export(module, args, kwargs, loss, strict, decompositions, inner_cuts) -> Exported:
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
         ep = torch.export.export(module, tuple(args), kwargs or {}, strict=strict)
@@ -54,6 +122,8 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
             # inference keeps attention as one operation (the placement has a rule for heads cut over processors and
             # the executor can hand it to a fused kernel); the joint forward+backward export needs it decomposed
             decompositions = _inference_table()
+        if loss is not None:
+            _views_may_copy(ep.graph_module)
         ep = ep.run_decompositions(decompositions if decompositions is not None else _default_table())
         if expand_loops(ep.graph_module) + merge_repeats(ep.graph_module) + \
                 ((unflatten_products(ep.graph_module) + (unflatten_linears(ep.graph_module) if inner_cuts else 0))
@@ -69,10 +139,77 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
             # ``loss`` counts the module's own outputs; new values of mutated buffers come before them in the graph
             users = [i for i, spec in enumerate(ep.graph_signature.output_specs) if spec.kind == OutputKind.USER_OUTPUT]
             _detach_mutations(ep, keep=users[loss])
+            paths = [(n.target, n.meta.get("nn_module_stack")) for n in ep.graph_module.graph.nodes if n.op == "call_function"]
             ep = _export_forward_backward(ep, joint_loss_index=users[loss])
+            restore_module_paths(ep, paths)
             merge_repeats(ep.graph_module)                    # the backward half repeats views and transposes of the forward
             unflatten_products(ep.graph_module)
     return read(ep, training=loss is not None)
+
+
+def restore_module_paths(ep, forward: list, window: int = 16) -> int:
+    """Give the nodes of a joint forward+backward graph the submodule paths (``nn_module_stack``) that the joint trace
+    drops, so that placements and share solvers can go by model part in training graphs too (the reference's ``segment``,
+    examples/parallel.py:92-95).  ``forward``: ``(target, stack)`` of the forward graph's operator nodes, in order.  The
+    joint graph starts with the same operators in the same order (with a few inserted or dropped): they are matched
+    in order within a small window.  A backward node gets the path of the latest forward value or parameter it reads
+    (the activations and weights its layer saved), else that of the gradient it continues."""
+    gm = ep.graph_module
+    owners = {}
+    for spec in ep.graph_signature.input_specs:
+        target = getattr(spec, "target", None)
+        if isinstance(target, str) and "." in target:
+            parts = target.split(".")[:-1]
+            owners[spec.arg.name] = {".".join(parts[: i + 1]): (".".join(parts[: i + 1]), "torch.nn.modules.module.Module") for i in range(len(parts))}
+    nodes = [n for n in gm.graph.nodes if n.op == "call_function"]
+    j, at, given = 0, {}, 0                                # at: node name -> position of its forward anchor
+    for i, n in enumerate(nodes):
+        if j >= len(forward):
+            break
+        hit = next((k for k in range(j, min(j + window, len(forward))) if forward[k][0] is n.target), None)
+        if hit is None:
+            continue
+        if forward[hit][1]:
+            n.meta["nn_module_stack"] = forward[hit][1]
+            given += 1
+        at[n.name] = i
+        j = hit + 1
+    matched = set(at)
+    stack_at = {i: nodes[i].meta.get("nn_module_stack") for i in at.values()}
+    for n in nodes:
+        if n.name in matched:
+            continue
+        saved, grads, owner, kept = -1, [], None, []
+        for a in n.all_input_nodes:
+            if a.name in owners:
+                owner = owners[a.name]                       # a parameter: its layer, whatever the order
+            elif a.name in matched:
+                kept.append(a)                               # an activation the forward pass saved
+            elif a.name in at:
+                grads.append(at[a.name])                     # a gradient on its way back
+        limit = min(grads) if grads else len(nodes)
+        for a in kept:
+            # the operator being differentiated read this activation (or made it): of the forward readers that come no
+            # later than the gradient's own anchor, the latest - an activation saved as a layer's input was made by
+            # the layer before, and the node belongs to the layer that read it
+            readers = [at[u.name] for u in a.users if u.name in matched and at[u.name] <= limit]
+            saved = max(saved, max(readers) if readers else at[a.name])
+        if saved >= 0:
+            here = saved
+        elif grads:
+            here = min(grads)                                # gradients flow towards earlier layers
+        else:
+            here = None
+        stack = owner or (stack_at.get(here) if here is not None else None)
+        if here is not None:
+            at[n.name] = here
+        elif owner is not None and grads == []:
+            pass
+        if stack:
+            n.meta["nn_module_stack"] = stack
+            stack_at.setdefault(here, stack) if here is not None else None
+            given += 1
+    return given
 
 
 def _detach_mutations(ep, keep: int | None = None) -> int:

@@ -202,6 +202,7 @@ class Exported:
     mutations: dict                  # output index -> placeholder name written in place
     training: bool = False
     program: Any = None              # the torch.export.ExportedProgram (what archives store)
+    tied: dict = dataclasses.field(default_factory=dict)    # parameter name -> the name it shares its tensor with
 
 
 class TrainingResult(NamedTuple):

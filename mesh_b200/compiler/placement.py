@@ -602,6 +602,18 @@ class Propagator:
                 keep = True
             elif lin == "first" and partial[0] and sum(partial) == 1 and others_ok:
                 keep = True
+            if keep and lin in ("one", "first"):
+                # scaling a partial sum can wait for the sum - unless the partial value has other readers too: then each
+                # of them would reduce its own product of it.  Sum it once, here, and let them share the result (the
+                # single all-reduce in the backward of a column-parallel layer, whose input gradient feeds both the
+                # norm's input gradient and its weight gradient).
+                tensor_args = [a for a in node.args if _is_tensor_node(a)]
+                if len(tensor_args) == len(specs):
+                    src = tensor_args[partial.index(True)]
+                    if len(src.users) > 1 and any(u.target not in LINEAR_IN for u in src.users):
+                        keep = False
+                    elif len(src.users) > 1 and sum(1 for u in src.users if LINEAR_IN.get(u.target) in ("one", "first")) > 1:
+                        keep = False
             if keep:
                 return list(specs), specs[partial.index(True)]
             return [R if s.kind == "P" else s for s in specs], (owner or R) if not any(s.kind == "S" for s in specs) else R
@@ -756,9 +768,41 @@ class Propagator:
                 maker.meta.setdefault("items", {})[j] = (self.spec[st.out], tuple(self.shape[st.out]), self.dtype[st.out])
 
     def call(self, node):
+        before = dict(self.renamed)
+        try:
+            self._call(node)
+        finally:
+            # operands moved to this node's stated processor were renamed for this node only
+            for name in getattr(self, "_moved_for_node", ()):
+                if name in before:
+                    self.renamed[name] = before[name]
+                else:
+                    self.renamed.pop(name, None)
+            self._moved_for_node = []
+
+    def _call(self, node):
         tgt = node.target
         flat_args = list(node.args)
         tnames = [self.renamed.get(a.name, a.name) for a in flat_args if _is_tensor_node(a)]
+        stated = self.stated.get(node.name)
+        self._moved_for_node = []
+        if stated is not None and tgt is not operator.getitem and any(s.kind == "O" for s in stated):
+            # "this node runs on that processor": operands that live whole on another processor go there first, so
+            # that the operator runs where it was placed (otherwise it would run where its operands are and only its
+            # result would move - and every later reader on the stated processor would pull its own copy)
+            for a in flat_args:
+                if not _is_tensor_node(a):
+                    continue
+                src = self.renamed.get(a.name, a.name)
+                have = self.spec.get(src)
+                if have is None or len(have) != len(stated):
+                    continue
+                if any(h.kind == "O" and w.kind == "O" and h.owner != w.owner for h, w in zip(have, stated)) and all(
+                        h.kind in ("R", "O") for h in have):
+                    want = tuple(w if (h.kind == "O" and w.kind == "O") else h for h, w in zip(have, stated))
+                    self.renamed[a.name] = self.reshard(src, want)
+                    self._moved_for_node.append(a.name)
+            tnames = [self.renamed.get(a.name, a.name) for a in flat_args if _is_tensor_node(a)]
         if tgt is operator.getitem:
             src = self.renamed.get(node.args[0].name, node.args[0].name)
             self.steps.append(Step("call", node.name, tgt, (Ref(src), node.args[1])))
@@ -985,8 +1029,15 @@ class Propagator:
             return [R, R], R
         if tgt is aten.scaled_dot_product_attention.default:
             # q, k, v [batch, heads, tokens, head_dim]: heads (or the batch) cut the same way on all three -> local
+            if len(tnames) == 4 and _is_tensor_node(node.args[3] if len(node.args) > 3 else node.kwargs.get("attn_mask")):
+                # with a mask tensor [batch | 1, heads | 1, queries, keys]: the mask follows the cut where it spans the
+                # cut dimension and stays whole where it broadcasts over it
+                res = self._attention_with_mask(node, tnames, specs)
+                if res is not None:
+                    return res
+                return None
             if len(tnames) != 3:
-                return None                                   # a mask tensor: leave it to the generic path
+                return None
             q = specs[0]
             same_heads = self.shape[tnames[0]][1] == self.shape[tnames[1]][1] == self.shape[tnames[2]][1]
             if q.kind == "S" and q.dim in (0, 1) and not q.striped and (q.dim == 0 or same_heads):
@@ -1044,6 +1095,28 @@ class Propagator:
         if tgt in (aten.native_layer_norm.default,):
             return None
         return None
+
+    def _attention_with_mask(self, node, tnames, specs):
+        q, k, v, mask = specs
+        qs, ks, ms = self.shape[tnames[0]], self.shape[tnames[1]], self.shape[tnames[3]]
+        if len(ms) != 4 or len(qs) != 4:
+            return None
+        same_heads = qs[1] == ks[1] == self.shape[tnames[2]][1]
+        cut = next((s for s in (q, k, v) if s.kind == "S"), None)
+        if any(s.kind not in ("R", "S") for s in specs):
+            return [R, R, R, R], R
+        if cut is None:
+            if mask.kind == "S" and mask.dim in (0, 1, 2) and not mask.striped and ms[mask.dim] == qs[mask.dim] and (mask.dim != 1 or same_heads):
+                want = Spec("S", mask.dim, mask.counts)            # only the mask is cut: the others give up all but its rows
+                return ([want, want if mask.dim < 2 else R, want if mask.dim < 2 else R, want]), want
+            return [R, R, R, R], R
+        if cut.dim in (0, 1) and not cut.striped and (cut.dim == 0 or same_heads):
+            want = Spec("S", cut.dim, cut.counts)
+            return [want, want, want, want if ms[cut.dim] == qs[cut.dim] else R], want
+        if q.kind == "S" and q.dim == 2:
+            want = Spec("S", 2, q.counts, q.striped)               # queries are independent: their mask rows go with them
+            return [want, R, R, want if ms[2] == qs[2] else R], want
+        return [R, R, R, R], R
 
     def rule_reduce(self, node, tnames, specs, ax, meta):
         s = specs[0]

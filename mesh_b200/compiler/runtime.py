@@ -931,6 +931,9 @@ class Program(Arguments):
         if exp.training:
             outs = [v for k, v in returned if k in ("user", "loss")]
             grads_p = {t: v for (k, t), v in zip(exp.outputs, flat) if k == "grad_param"}
+            if exp.tied:
+                from .export import tied_gradients
+                grads_p = tied_gradients(grads_p, exp.tied)
             grads_i = {t: v for (k, t), v in zip(exp.outputs, flat) if k == "grad_input"}
             try:
                 outs_tree = pytree.tree_unflatten(outs, exp.out_spec)

@@ -529,16 +529,20 @@ def test_sequence_parallel_megatron_layer_has_the_textbook_collectives():
 
 def test_tensor_parallel_training_layer_needs_only_its_four_all_reduces():
     """Megatron tensor parallelism, forward and backward, batch of 2: the attention products keep batch and heads apart
-    (so the cut along the heads survives them) and a layer costs two all-reduces forward and two backward; the only
-    other transfers reduce the gradients of the replicated norm weights."""
+    (so the cut along the heads survives them) and a layer costs two all-reduces forward and two backward.  The first
+    layer's second backward all-reduce would only serve the gradient of its norm weight (the input needs none): that
+    partial sum is scaled and summed over the rows first and goes out as one small all-reduce of the weight gradient.
+    A partial sum with several readers is summed once and shared."""
     torch.manual_seed(23)
-    m = Decoder(dim=48, heads=4, ffn=96, layers=1)
-    x = torch.randn(2, 12, 48)
     procs = _procs(2)
-    sch = compile_module(m, (x,), procs, megatron(procs), loss=0)
-    assert sch.structure["fallbacks"] == 0 and set(sch.structure["by_verb"]) == {"all_reduce"}
-    big = [t for t in sch.plan.transfers if t.nbytes >= 2 * 12 * 48 * 4]
-    assert len(big) == 4, [(t.verb, t.nbytes) for t in sch.plan.transfers]
+    x = torch.randn(2, 12, 48)
+    for layers in (1, 2):
+        m = Decoder(dim=48, heads=4, ffn=96, layers=layers)
+        sch = compile_module(m, (x,), procs, megatron(procs), loss=0)
+        assert sch.structure["fallbacks"] == 0 and set(sch.structure["by_verb"]) == {"all_reduce"}
+        big = [t for t in sch.plan.transfers if t.nbytes >= 2 * 12 * 48 * 4]
+        assert len(big) == 4 * layers - 1, [(t.verb, t.nbytes) for t in sch.plan.transfers]
+        assert len(sch.plan.transfers) == 4 * layers, [(t.verb, t.nbytes) for t in sch.plan.transfers]
     res = Program(sch)(x)
     loss, grads = _eager(m, x)
     _check(res, loss, grads)

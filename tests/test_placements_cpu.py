@@ -1,0 +1,90 @@
+"""The placement library (``compiler/placements.py``): placements stated by name patterns, on the package's decoder."""
+import torch
+import torch.nn as nn
+
+from mesh_b200.compiler import Program, compile_module, placements
+from mesh_b200.models.llama import Decoder
+
+
+def _procs(n):
+    return {f"p{i}": (0, "cpu") for i in range(n)}
+
+
+def _eager(m, *a):
+    for p in m.parameters():
+        p.grad = None
+    loss = m(*a)
+    loss.backward()
+    return loss.detach(), {k: p.grad.clone() for k, p in m.named_parameters()}
+
+
+def _close(res, loss, grads, tol=2e-5):
+    assert abs(float(res.outputs.detach()) - float(loss)) <= tol * max(1.0, abs(float(loss)))
+    scale = max(float(g.abs().max()) for g in grads.values())
+    for k, g in res.parameters.items():
+        r = grads[k]
+        if g.shape != r.shape:
+            r = r[tuple(slice(0, n) for n in g.shape)]
+        assert (g - r).abs().max() <= tol * scale, k
+
+
+def test_tensor_parallel_by_names_matches_the_models_own_placement():
+    torch.manual_seed(0)
+    m = Decoder(dim=48, heads=4, ffn=96, layers=2)
+    x = torch.randn(2, 12, 48)
+    procs = _procs(2)
+    place = placements.tensor_parallel(tuple(procs), column=("wq", "wk", "wv", "w1", "w3"), row=("wo", "w2"))
+    sch = compile_module(m, (x,), procs, place, loss=0)
+    assert set(sch.structure["by_verb"]) == {"all_reduce"} and sch.structure["fallbacks"] == 0
+    cut = [k for k, v in sch.plan.input_specs.items() if any(s.kind == "S" for s in v)]
+    assert len(cut) == 2 * 7                                   # seven projections per layer, nothing else
+    _close(Program(sch)(x), *_eager(m, x))
+
+
+def test_patterns_match_whole_path_components_only():
+    match = placements._matcher(("q_proj", r"layers_[0-3]"))
+    assert match("p_model_layers_0_self_attn_q_proj_weight") and match("p_model_layers_3_mlp_up_weight")
+    assert not match("p_model_xq_proj_weight") and not match("p_model_layers_12_mlp_up_weight")
+
+
+def test_pipeline_by_module_paths_and_data_parallel_combined():
+    """Layers 0 and 1 on the first processor, 2 and 3 on the second: activations cross once forward and once backward;
+    every parameter's gradient is produced where the parameter lives."""
+    torch.manual_seed(1)
+    m = Decoder(dim=32, heads=2, ffn=64, layers=4)
+    x = torch.randn(2, 8, 32)
+    procs = _procs(2)
+    place = placements.pipeline({r"blocks\.[01]\.": "p0", r"blocks\.[23]\.": "p1"})
+    sch = compile_module(m, (x,), procs, place, loss=0)
+    sends = sch.structure["by_verb"].get("send_recv", 0)
+    assert 2 <= sends <= 4 and set(sch.structure["by_verb"]) <= {"send_recv", "broadcast"}, sch.structure["by_verb"]
+    _close(Program(sch)(x), *_eager(m, x))
+
+
+class _Tagger(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.embed = nn.Embedding(64, 16)
+        self.proj = nn.Linear(16, 32)
+        self.out = nn.Linear(32, 8)
+
+    def forward(self, ids, labels):
+        h = torch.relu(self.proj(self.embed(ids)))
+        return nn.functional.cross_entropy(self.out(h).flatten(0, 1), labels.flatten())
+
+
+def test_vocabulary_parallel_embedding_with_column_and_row_layers_and_cut_inputs():
+    torch.manual_seed(2)
+    m = _Tagger()
+    ids, labels = torch.randint(0, 64, (4, 6)), torch.randint(0, 8, (4, 6))
+    procs = _procs(2)
+    names = tuple(procs)
+    tp = placements.tensor_parallel(names, column=("proj",), row=("out",), vocabulary=("embed",))
+    sch = compile_module(m, (ids, labels), procs, tp, loss=0)
+    assert sch.plan.input_specs["p_embed_weight"][0].dim == 0 and sch.plan.input_specs["p_proj_bias"][0].kind == "S"
+    _close(Program(sch)(ids, labels), *_eager(m, ids, labels))
+    # the same model with every input cut along the batch instead: parameters whole, gradients all-reduced
+    dp = placements.combine(placements.data_parallel(names, inputs=("ids", "labels")), lambda node: None)
+    sch = compile_module(m, (ids, labels), procs, dp, loss=0)
+    assert sch.structure["by_verb"].get("all_reduce", 0) >= len(list(m.parameters()))
+    _close(Program(sch)(ids, labels), *_eager(m, ids, labels))
