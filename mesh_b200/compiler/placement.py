@@ -172,6 +172,8 @@ def _along(position: int, outs: int, default=-1):
     def describe(node, shapes):
         nd = len(shapes[0])
         dim = node.args[position] if len(node.args) > position else node.kwargs.get("dim", default)
+        if dim is None:
+            return None                                     # the operator works on the flattened tensor
         return {"batched": [True] + [False] * (len(shapes) - 1), "protect": {dim % max(nd, 1)}, "outs": ["S"] * outs}
     return describe
 
@@ -239,6 +241,36 @@ def _rolled(node, shapes):
     if not dims:
         return None
     return {"batched": [True], "protect": {d % nd for d in dims}, "outs": ["S"]}
+
+
+def _transformed(node, shapes):
+    # (input, dims, normalization, ...): a Fourier transform along ``dims``; the other dimensions are a batch
+    nd = max(len(shapes[0]), 1)
+    dims = node.args[1]
+    return {"batched": [True], "protect": {d % nd for d in dims}, "outs": ["S"]}
+
+
+def _as_complex(node, shapes):
+    # [..., 2] -> complex [...]: the last dimension is consumed
+    return {"batched": [True], "protect": {len(shapes[0]) - 1}, "outs": ["S"]}
+
+
+def _as_real(node, shapes):
+    # complex [...] -> [..., 2]: every dimension stays where it is
+    return {"batched": [True], "protect": set(), "outs": ["S"]}
+
+
+def _repeated(node, shapes):
+    # (input, repeats): ``repeats`` lines up with the trailing dimensions; a dimension repeated once is a batch dimension
+    nd = len(shapes[0])
+    reps = list(node.args[1])
+    off = len(reps) - nd
+    if off < 0:
+        return None
+    info = {"batched": [True], "protect": {d for d in range(nd) if reps[d + off] != 1}, "outs": ["S"]}
+    if off:
+        info["out_dim"] = lambda d: d + off
+    return info
 
 
 def _layer_norm(node, shapes):
@@ -357,6 +389,15 @@ BATCHED = {
     aten.upsample_bilinear2d.vec: _trailing(2, 1, (0,)), aten.upsample_bicubic2d.vec: _trailing(2, 1, (0,)),
     aten.upsample_trilinear3d.vec: _trailing(3, 1, (0,)),
     aten.pixel_shuffle.default: _trailing(3, 1, (0,)), aten.pixel_unshuffle.default: _trailing(3, 1, (0,)),
+    aten._fft_c2c.default: _transformed, aten._fft_r2c.default: _transformed, aten._fft_c2r.default: _transformed,
+    aten.view_as_complex.default: _as_complex, aten.view_as_real.default: _as_real,
+    aten._cdist_forward.default: _trailing(2, 1), aten.grid_sampler_2d.default: _trailing(3, 1),
+    aten._linalg_eigh.default: _trailing(2, 2), aten._linalg_svd.default: _trailing(2, 3),
+    aten.linalg_matrix_exp.default: _trailing(2, 1), aten.linalg_eig.default: _trailing(2, 2),
+    aten.linalg_ldl_factor_ex.default: _trailing(2, 3), aten.linalg_lu.default: _trailing(2, 3),
+    aten.linalg_householder_product.default: _trailing(2, 1), aten.geqrf.default: _trailing(2, 2),
+    aten.triangular_solve.default: _trailing(2, 2),
+    aten.repeat.default: _repeated, aten.repeat_interleave.self_int: _along(2, 1, default=None),
 }
 _NORMS = {aten.linalg_vector_norm.default}
 # batch norm variants: how many leading arguments are tensors (some optional), which of them have the input's shape,
@@ -1092,6 +1133,14 @@ class Propagator:
             if s.kind == "S":
                 return [R], R
             return [s], s
+        if tgt is aten.histc.default:
+            # counts of a fixed range of bins: every processor counts its own elements, the counts are partial sums
+            lo = node.args[2] if len(node.args) > 2 else node.kwargs.get("min", 0)
+            hi = node.args[3] if len(node.args) > 3 else node.kwargs.get("max", 0)
+            s = specs[0]
+            if s.kind == "S" and lo != hi:                   # (min = max = 0 means the data's own range: a global fact)
+                return [s], P()
+            return [R], R
         if tgt in (aten.native_layer_norm.default,):
             return None
         return None

@@ -215,3 +215,70 @@ def test_column_then_row_parallel_convolutions_need_one_all_reduce(transposed, n
         if g.shape != r.shape:
             r = r[tuple(slice(0, m) for m in g.shape)]
         assert (g - r).abs().max() <= 2e-5 * scale, k
+
+
+def _spd(x):
+    return x @ x.mT + 4 * torch.eye(x.shape[-1])
+
+
+# operators of the numerics table (transforms, complex numbers, distances, histograms, factorisations, scans, ranks,
+# scatters, windows, samplers, norms, losses, contractions, repeats): a cut along the samples stays through all of them
+NUMERICS = {
+    "fourier": (lambda x: torch.fft.rfft(x, dim=-1).abs().sum(-1, keepdim=True) + torch.fft.fft(x, dim=-1).real
+                + torch.fft.irfft(torch.fft.rfft(x, dim=-1), n=x.shape[-1], dim=-1), (4, 6, 16)),
+    "fourier_2d": (lambda x: torch.fft.fft2(x).abs() + torch.fft.ifft2(torch.fft.fft2(x)).real, (4, 8, 8)),
+    "complex": (lambda x: torch.view_as_real(torch.view_as_complex(x.reshape(4, 6, 8, 2))
+                                             * torch.polar(torch.ones(8), torch.arange(8.) * 0.1)).flatten(-2), (4, 6, 16)),
+    "distances": (lambda x: torch.cdist(x, x.flip(1)), (4, 6, 16)),
+    "histogram": (lambda x: torch.histc(x, bins=8, min=-3, max=3), (4, 6, 16)),
+    "determinant_inverse": (lambda x: torch.linalg.det(_spd(x))[..., None, None] * torch.linalg.inv(_spd(x)), (4, 6, 6)),
+    "solves": (lambda x: torch.linalg.solve(_spd(x), x) + torch.cholesky_solve(x, torch.linalg.cholesky(_spd(x))), (4, 6, 6)),
+    "spectra": (lambda x: torch.linalg.eigvalsh(_spd(x)) + torch.linalg.svdvals(x), (4, 6, 6)),
+    "matrix_exponential": (lambda x: torch.linalg.matrix_exp(x * 0.1), (4, 6, 6)),
+    "lu": (lambda x: torch.linalg.lu_factor(_spd(x))[0], (4, 6, 6)),
+    "scans": (lambda x: x.cumsum(-1) + x.cumprod(-1) + x.cummax(-1).values + x.cummin(-1)[0] + torch.logcumsumexp(x, -1), (4, 6, 16)),
+    "ranks": (lambda x: x.kthvalue(3, -1).values + x.median(-1).values + x.mode(-1).values + x.sort(-1).values[..., 0]
+              + x.argsort(-1)[..., 0].float(), (4, 6, 16)),
+    "scatters": (lambda x: torch.zeros(4, 6, 20).scatter_add(-1, (x.abs() * 5).long().clamp(0, 19), x)
+                 + torch.zeros(4, 6, 20).index_add(-1, torch.arange(16), x), (4, 6, 16)),
+    "windows": (lambda x: F.fold(F.unfold(x, 3, padding=1), (8, 8), 3, padding=1), (4, 2, 8, 8)),
+    "sampler": (lambda x: F.grid_sample(x, torch.stack(torch.meshgrid(torch.linspace(-1, 1, 5), torch.linspace(-1, 1, 5),
+                                                                      indexing="ij"), -1).expand(4, 5, 5, 2), align_corners=False), (4, 2, 8, 8)),
+    "norms": (lambda x: F.layer_norm(x, (16,)) + F.normalize(x, dim=-1) + x.norm(dim=-1, keepdim=True)
+              + torch.linalg.vector_norm(x, ord=1, dim=-1, keepdim=True) + F.rms_norm(x, (16,)), (4, 6, 16)),
+    "losses": (lambda x: F.cross_entropy(x.flatten(0, 1), x.flatten(0, 1).argmax(-1), reduction="none").view(4, 6)
+               + F.mse_loss(x, x.flip(-1), reduction="none").mean(-1)
+               + F.kl_div(x.log_softmax(-1), x.flip(-1).softmax(-1), reduction="none").sum(-1)
+               + F.binary_cross_entropy_with_logits(x, (x.flip(-1) > 0).float(), reduction="none").sum(-1), (4, 6, 16)),
+    "contractions": (lambda x: torch.einsum("bij,bkj->bik", x, x).sum(-1) + torch.einsum("bij->bj", x)[:, :6]
+                     + torch.einsum("bii->bi", x[..., :6]), (4, 6, 16)),
+    "repeats": (lambda x: x.repeat(1, 2, 1)[:, :6] + x.repeat_interleave(2, dim=1)[:, :6] + x.tile((1, 1, 2))[..., :16], (4, 6, 16)),
+    "blends": (lambda x: torch.lerp(x, x.flip(-1), 0.3) + torch.addcmul(x, x, x, value=0.5) + torch.addcdiv(x, x, x.abs() + 1)
+               + torch.hypot(x, x.flip(-1)) + torch.atan2(x, x.flip(-1)) + x.frac() + torch.fmod(x, 2.0) + torch.remainder(x, 2.0), (4, 6, 16)),
+    "pools_1d": (lambda x: F.avg_pool1d(x, 2).repeat(1, 1, 2) + F.max_pool1d(x, 2).repeat(1, 1, 2) + F.adaptive_avg_pool1d(x, 16), (4, 6, 16)),
+}
+
+
+class _Function(nn.Module):
+    def __init__(self, f):
+        super().__init__()
+        self.f = f
+
+    def forward(self, x):
+        return self.f(x)
+
+
+@pytest.mark.parametrize("name", sorted(NUMERICS))
+def test_numerics_keep_a_cut_along_the_samples(name):
+    f, shape = NUMERICS[name]
+    torch.manual_seed(0)
+    x = torch.randn(*shape)
+    model = _Function(f).eval()
+    procs = _procs(2)
+    names = tuple(procs)
+    sch = compile_module(model, (x,), procs, lambda node: (0, names, None) if node.op == "placeholder" and node.name == "x" else None)
+    got, ref = Program(sch)(x), model(x)
+    assert (got - ref).abs().max() <= 1e-5 * (ref.abs().max() + 1e-6)
+    assert sch.structure["gathering_fallbacks"] == 0, [str(s.target) for s in sch.plan.steps if s.meta.get("gathered")]
+    if name == "histogram":                                    # every processor counts its own elements: one small sum
+        assert sch.structure["by_verb"] == {"all_reduce": 1}
