@@ -25,24 +25,28 @@ from .runtime import Program
 
 def workspace(scheduled, copies: int = 1, align: int = 256) -> dict:
     """``{"bytes_per_copy", "bytes_unshared", "copies", "offsets": {value: [offset per copy]}, "transfers": [...],
-    "planned": the native planner's demands, order and exposed time for those transfers}``."""
+    "planned": the native planner's demands, order and exposed time for those transfers, "pipeline": its steady state
+    for repeated starts (period, latency, copies)}``."""
     from ..runtime.plan import layout
     lt = _schedule.lifetimes(scheduled.plan)
     offs, one = layout([(a, b, c) for _, a, b, c in lt], copies=copies, align=align) if lt else ([[]] * copies, 0)
     return {"bytes_per_copy": one, "bytes_unshared": sum(c for *_, c in lt), "copies": copies,
             "offsets": {name: [offs[c][i] for c in range(copies)] for i, (name, *_rest) in enumerate(lt)},
             "transfers": _schedule.declarations(scheduled.plan), "horizon": _schedule.horizon(scheduled.plan, copies),
-            "planned": _schedule.planned(scheduled.plan)}
+            "planned": _schedule.planned(scheduled.plan), "pipeline": _schedule.pipelined(scheduled.plan)}
 
 
 class Prepared:
     """``prepared = prepare(scheduled, examples)``; ``prepared.inputs()`` -> writable input set of the next execution,
     ``prepared.start()`` -> execution number, ``prepared.result(b)``, ``prepared.ended(b)``, ``prepared.synchronize()``."""
 
-    def __init__(self, scheduled, examples, copies: int = 2, horizon: int | None = None, program: Program | None = None,
+    def __init__(self, scheduled, examples, copies: int | None = 2, horizon: int | None = None, program: Program | None = None,
                  graphs: bool | None = None, rdv=None):
         self.scheduled = scheduled
         self.program = program or Program(scheduled)
+        if copies is None:
+            # as many sets of buffers as executions are alive at once in the planner's steady state (within reason)
+            copies = min(4, max(1, _schedule.pipelined(scheduled.plan)["copies"]))
         self.copies = max(1, copies)
         self.horizon = max(1, min(horizon or self.copies, self.copies))
         dev = self.program.device if isinstance(self.program.device, torch.device) else torch.device("cpu")
@@ -135,5 +139,5 @@ class Prepared:
         self._results.clear()
 
 
-def prepare(scheduled, examples, copies: int = 2, horizon: int | None = None, **kw) -> Prepared:
+def prepare(scheduled, examples, copies: int | None = 2, horizon: int | None = None, **kw) -> Prepared:
     return Prepared(scheduled, examples, copies, horizon, **kw)

@@ -296,3 +296,57 @@ def planned(plan: Plan, step_us: float = 10.0, bucket_bytes: int = 32 << 20, sta
                                                                                  "makespan_us": 0.0, "demands": 0})
     return {"transfers": [dict(channel=d.channel, verb=d.verb, value=d.value, result=d.result, **o) for d, o in zip(decl, out)],
             "summary": summary}
+
+
+def pipelined(plan: Plan, cost=unit_cost, step_us: float = 10.0) -> dict:
+    """The steady state of the plan when it is started again and again by an executor that overlaps transfers with
+    compute (``runtime/plan.py::plan_pipeline``, the native planner's modulo scheduler): every step is a task - compute
+    steps on the processor's stream in program order, every transfer on the links of its axis in program order, a
+    transfer's duration from the planner's latency + bytes model, a compute step's from ``cost(step) * step_us`` - with
+    the plan's data flow as dependences and the lag-1 edge of every collective (its staging is reused by the same
+    collective of the next execution).  ``{"period_us", "latency_us", "copies", "resource_bound_us",
+    "recurrence_bound_us", "bound_by"}``: how often an execution can start, how long one takes, how many sets of buffers
+    that needs (what ``Prepared`` takes as its default ``copies``), and which resource sets the period."""
+    from ..runtime.plan import plan_pipeline
+    steps = plan.steps
+    n = len(steps)
+    if n == 0:
+        return {"period_us": 0.0, "latency_us": 0.0, "copies": 1, "resource_bound_us": 0.0, "recurrence_bound_us": 0.0,
+                "bound_by": "nothing"}
+    link_us = {}
+    for t in planned(plan, step_us=step_us, bucket_bytes=0)["transfers"]:
+        link_us[t["result"]] = max(0.0, t["end_us"] - t["start_us"])
+    free = ("alias", "const", "slice")
+    dur, res = [], []
+    for st in steps:
+        transfer = st.op == "collective" or (st.op == "fused" and "channel" in st.meta)
+        if transfer:
+            dur.append(link_us.get(st.out, step_us))
+            res.append(1 + int(st.meta.get("axis", 0)))
+        else:
+            import operator
+            nothing = st.op in free or st.target is operator.getitem
+            dur.append(0.0 if nothing else float(cost(st)) * step_us)
+            res.append(0)
+    produced = {st.out: i for i, st in enumerate(steps)}
+    edges, last_on = [], {}
+    for i, st in enumerate(steps):
+        refs: list[str] = []
+        _refs(st.args, refs)
+        _refs(st.kwargs, refs)
+        for r in set(refs):
+            if r in produced and produced[r] != i:
+                edges.append((produced[r], i, 0))
+        if res[i] in last_on:                              # a stream runs its tasks in program order
+            edges.append((last_on[res[i]], i, 0))
+        last_on[res[i]] = i
+        if res[i] > 0:
+            edges.append((i, i, 1))
+    r = plan_pipeline(dur, res, edges)
+    busy = {}
+    for d, k in zip(dur, res):
+        busy[k] = busy.get(k, 0.0) + d
+    top = max(busy, key=busy.get)
+    bound_by = "dependences" if r["recurrence_bound"] > r["resource_bound"] else ("compute" if top == 0 else f"links of axis {top - 1}")
+    return {"period_us": r["period"], "latency_us": r["latency"], "copies": r["copies"], "resource_bound_us": r["resource_bound"],
+            "recurrence_bound_us": r["recurrence_bound"], "bound_by": bound_by}

@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <cmath>
 #include <vector>
 
 extern "C" int64_t mesh_graph_colour(int n, const int* start, const int* end, const int64_t* size, int64_t align, int64_t* offset);
@@ -190,6 +191,143 @@ int mesh_plan_transfers(int n, const MeshTransferIn* in, int n_axes, const int* 
     summary_out[0] = link_sum; summary_out[1] = exposed_sum; summary_out[2] = makespan; summary_out[3] = (double)demands.size();
   }
   return 0;
+}
+
+// ---- executions in flight: the steady state of a plan that is started again and again
+//
+// One execution of a standing plan is a set of tasks (its steps) with durations, each on one resource (this processor's
+// compute stream, the links of one grid axis), and dependences between them; a dependence may also reach into a later
+// execution (`lag` executions later: a collective's staging is reused by the same collective of the next execution, an
+// accumulator is read by the next step).  Started every `period`, executions overlap, and the questions of the
+// reference's template / unroll stage (rdma/mesh-collective.c:244, :390: copies and lags) are: how short can the period
+// be, when does every task start within its execution, and how many executions are alive at once - that many sets of
+// buffers (`copies`) are needed for the period to hold.  This is modulo scheduling:
+//   * the period is bounded below by the busiest resource (the sum of its tasks' durations) and by every dependence
+//     cycle (its durations divided by its lags: found by bisection on the period with a longest-path test);
+//   * tasks are placed in dependence order at the earliest time that respects their predecessors and finds their
+//     resource free modulo the period; when a task finds no room within one period the period grows a little and the
+//     placement starts over (bounded);
+//   * latency = the span of one execution under those starts; copies = ceil(latency / period).
+// Returns 0, -1 on bad input (a dependence cycle without lag, an unknown task or resource), -2 when no period was found
+// within the attempts.  summary_out[0..4] = {period, latency, copies, resource bound, recurrence bound}.
+static bool has_positive_cycle(int n, int m, const int* eu, const int* ev, const int* lag, const double* dur, double period) {
+  std::vector<double> dist(n, 0.0);
+  for (int it = 0; it <= n; ++it) {
+    bool moved = false;
+    for (int e = 0; e < m; ++e) {
+      const double w = dur[eu[e]] - period * (double)lag[e];
+      if (dist[eu[e]] + w > dist[ev[e]] + 1e-9) { dist[ev[e]] = dist[eu[e]] + w; moved = true; }
+    }
+    if (!moved) return false;
+  }
+  return true;
+}
+
+int mesh_plan_pipeline(int n, const double* dur, const int* resource, int n_resources, int m, const int* eu, const int* ev,
+                       const int* lag, double* start_out, double* summary_out) {
+  if (n < 0 || m < 0 || n_resources < 1) return -1;
+  for (int i = 0; i < n; ++i)
+    if (dur[i] < 0 || resource[i] < 0 || resource[i] >= n_resources) return -1;
+  for (int e = 0; e < m; ++e)
+    if (eu[e] < 0 || eu[e] >= n || ev[e] < 0 || ev[e] >= n || lag[e] < 0) return -1;
+  if (n == 0) {
+    if (summary_out) { summary_out[0] = summary_out[1] = summary_out[3] = summary_out[4] = 0.0; summary_out[2] = 1.0; }
+    return 0;
+  }
+  // order within one execution (edges without lag must be acyclic)
+  std::vector<int> indeg(n, 0), order;
+  for (int e = 0; e < m; ++e) if (lag[e] == 0) indeg[ev[e]]++;
+  for (int i = 0; i < n; ++i) if (!indeg[i]) order.push_back(i);
+  for (size_t k = 0; k < order.size(); ++k)
+    for (int e = 0; e < m; ++e)
+      if (lag[e] == 0 && eu[e] == order[k] && --indeg[ev[e]] == 0) order.push_back(ev[e]);
+  if ((int)order.size() != n) return -1;
+  // bounds on the period
+  std::vector<double> busy(n_resources, 0.0);
+  double total = 0.0, longest = 0.0;
+  for (int i = 0; i < n; ++i) { busy[resource[i]] += dur[i]; total += dur[i]; if (dur[i] > longest) longest = dur[i]; }
+  double res_bound = 0.0;
+  for (double b : busy) if (b > res_bound) res_bound = b;
+  double rec_bound = 0.0;
+  bool any_lag = false;
+  for (int e = 0; e < m; ++e) any_lag |= lag[e] > 0;
+  if (any_lag && total > 0) {
+    double lo = 0.0, hi = total;                           // a cycle holds at most every task once per unit of lag
+    if (has_positive_cycle(n, m, eu, ev, lag, dur, hi)) return -1;
+    for (int it = 0; it < 60; ++it) {
+      const double mid = 0.5 * (lo + hi);
+      if (has_positive_cycle(n, m, eu, ev, lag, dur, mid)) lo = mid; else hi = mid;
+    }
+    rec_bound = hi;
+  }
+  double period = res_bound > rec_bound ? res_bound : rec_bound;
+  if (period <= 0) period = longest > 0 ? longest : 1.0;
+  struct Busy { double from, to; };                       // within [0, period), from <= to (a wrapped task makes two)
+  std::vector<double> start(n, 0.0);
+  for (int attempt = 0; attempt < 160; ++attempt) {
+    std::vector<std::vector<Busy>> table(n_resources);
+    std::vector<char> placed(n, 0);
+    bool ok = true;
+    for (int k = 0; k < n && ok; ++k) {
+      const int v = order[k];
+      double est = 0.0;
+      for (int e = 0; e < m; ++e)
+        if (ev[e] == v && placed[eu[e]]) {
+          const double t = start[eu[e]] + dur[eu[e]] - period * (double)lag[e];
+          if (t > est) est = t;
+        }
+      // earliest t in [est, est + period) whose window [t, t + dur) is free modulo the period
+      double t = est;
+      bool found = dur[v] <= 0;
+      for (int guard = 0; guard < 4 * n + 8 && !found; ++guard) {
+        const double a = std::fmod(t, period), b = a + dur[v];
+        double bump = -1.0;
+        for (const Busy& z : table[resource[v]]) {
+          const bool hit = (a < z.to - 1e-9 && z.from < b - 1e-9) || (b > period && z.from < b - period - 1e-9);
+          if (hit) {
+            // move to the end of the interval we ran into (in unwrapped time)
+            double to = z.to;
+            if (!(a < z.to - 1e-9 && z.from < b - 1e-9)) to += period;      // hit through the wrapped part
+            const double cand = t + (to - a);
+            if (cand > bump) bump = cand;
+          }
+        }
+        if (bump < 0) found = true;
+        else { t = bump; if (t - est >= period - 1e-9) break; }
+      }
+      if (!found || dur[v] > period + 1e-9) { ok = false; break; }
+      start[v] = t;
+      placed[v] = 1;
+      if (dur[v] > 0) {
+        const double a = std::fmod(t, period), b = a + dur[v];
+        if (b <= period + 1e-9) table[resource[v]].push_back(Busy{a, b < period ? b : period});
+        else { table[resource[v]].push_back(Busy{a, period}); table[resource[v]].push_back(Busy{0.0, b - period}); }
+      }
+    }
+    // dependences that reach back from a later task of the order to an earlier one (lag > 0) were not seen when the
+    // earlier one was placed: check them now
+    for (int e = 0; e < m && ok; ++e)
+      if (start[ev[e]] + period * (double)lag[e] + 1e-9 < start[eu[e]] + dur[eu[e]]) ok = false;
+    if (ok) {
+      double first = 1e300, last = 0.0;
+      for (int i = 0; i < n; ++i) {
+        if (start[i] < first) first = start[i];
+        if (start[i] + dur[i] > last) last = start[i] + dur[i];
+      }
+      const double latency = last - first;
+      for (int i = 0; i < n; ++i) start_out[i] = start[i] - first;
+      if (summary_out) {
+        summary_out[0] = period;
+        summary_out[1] = latency;
+        summary_out[2] = std::ceil(latency / period - 1e-9) < 1.0 ? 1.0 : std::ceil(latency / period - 1e-9);
+        summary_out[3] = res_bound;
+        summary_out[4] = rec_bound;
+      }
+      return 0;
+    }
+    period *= 1.02;
+  }
+  return -2;
 }
 
 // ---- archives: header {magic, version, epoch, words, checksum} + 8-byte words

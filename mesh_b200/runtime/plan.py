@@ -84,6 +84,32 @@ def plan_transfers(transfers: list[dict], worlds: list[int], *, step_us: float =
     return out, {"link_us": summary[0], "exposed_us": summary[1], "makespan_us": summary[2], "demands": int(summary[3])}
 
 
+def plan_pipeline(durations: list[float], resources: list[int], edges: list[tuple[int, int, int]]) -> dict:
+    """The steady state of a plan started again and again (the native planner's modulo scheduler).  ``durations[i]`` and
+    ``resources[i]``: time and resource (compute stream, the links of an axis, ...) of task ``i`` of one execution;
+    ``edges``: ``(earlier, later, lag)`` - ``later`` of execution ``t + lag`` follows ``earlier`` of execution ``t``.
+    Returns ``{period, latency, copies, resource_bound, recurrence_bound, starts}``: how often an execution can start,
+    how long one takes under that schedule, how many are alive at once (the sets of buffers needed), the two lower
+    bounds on the period, and every task's start within its execution."""
+    n, m = len(durations), len(edges)
+    if len(resources) != n:
+        raise ValueError("plan_pipeline: one resource per task")
+    n_res = (max(resources) + 1) if resources else 1
+    starts = (c_double * max(1, n))()
+    summary = (c_double * 5)()
+    arr = lambda t, vals: (t * max(1, len(vals)))(*vals)       # noqa: E731
+    L = _native.lib()
+    rc = L.mesh_plan_pipeline(c_int(n), arr(c_double, [float(d) for d in durations]), arr(c_int, [int(r) for r in resources]),
+                              c_int(n_res), c_int(m), arr(c_int, [e[0] for e in edges]), arr(c_int, [e[1] for e in edges]),
+                              arr(c_int, [e[2] for e in edges]), starts, summary)
+    if rc == -1:
+        raise ValueError("plan_pipeline: bad input (an unknown task, a negative time or lag, or a dependence cycle within one execution)")
+    if rc != 0:
+        raise RuntimeError("plan_pipeline: no period found")
+    return {"period": summary[0], "latency": summary[1], "copies": int(summary[2]), "resource_bound": summary[3],
+            "recurrence_bound": summary[4], "starts": [starts[i] for i in range(n)]}
+
+
 class Plan:
     """A captured step with ``copies`` workspaces; ``start()`` launches execution ``t`` on copy ``t % copies``."""
 

@@ -97,3 +97,28 @@ def test_workspace_carries_the_planned_transfers():
     small = S.planned(sch.plan, bucket_bytes=8 << 10)
     assert small["summary"]["demands"] > planned["summary"]["demands"]
     assert abs(small["summary"]["exposed_us"] - sum({t["demand"]: t["exposed_us"] for t in small["transfers"]}.values())) < 1e-6
+
+
+def test_workspace_states_the_steady_state_of_repeated_starts():
+    """``workspace()["pipeline"]``: period, latency and copies from the native modulo scheduler over the plan's steps;
+    ``prepare(copies=None)`` takes that many sets of buffers."""
+    import torch
+    from mesh_b200.compiler import compile_module, prepare, workspace
+    from mesh_b200.models.llama import Decoder, megatron
+    torch.manual_seed(0)
+    m = Decoder(dim=32, heads=2, ffn=64, layers=1).eval()
+    x = torch.randn(2, 8, 32)
+    procs = {f"p{i}": (0, "cpu") for i in range(2)}
+    sch = compile_module(m, (x,), procs, megatron(procs))
+    pipe = workspace(sch, 2)["pipeline"]
+    assert pipe["period_us"] >= pipe["resource_bound_us"] > 0 and pipe["latency_us"] > 0
+    assert pipe["copies"] == max(1, -(-int(pipe["latency_us"] / pipe["period_us"] * 1e6) // 10 ** 6))
+    assert pipe["bound_by"] in ("compute", "dependences") or pipe["bound_by"].startswith("links of axis")
+    # transfers that cost more than the compute between them: the links set the period and executions overlap
+    from mesh_b200.compiler import schedule
+    slow = schedule.pipelined(sch.plan, step_us=0.01)
+    assert slow["bound_by"].startswith("links") and slow["copies"] >= 1
+    p = prepare(sch, (x,), copies=None)
+    assert p.copies == min(4, max(1, pipe["copies"]))
+    p.start(x)
+    assert torch.allclose(p.result(), m(x), atol=1e-5)

@@ -220,3 +220,40 @@ def test_transfer_planner_groups_orders_and_accounts():
     import pytest
     with pytest.raises(ValueError):
         plan_transfers([{"bytes": 1, "axis": 3, "verb": "all_reduce", "at": 0, "read": 1}], [2])
+
+
+def test_pipeline_planner_period_latency_and_copies():
+    """The native modulo scheduler: the period is the busiest resource or the tightest dependence cycle, whichever is
+    longer; copies = executions alive at once; starts respect dependences and never overlap two tasks of one resource
+    modulo the period."""
+    from mesh_b200.runtime.plan import plan_pipeline
+    chain = [(0, 1, 0), (1, 2, 0)]
+    r = plan_pipeline([2.0, 3.0, 1.0], [0, 1, 2], chain)                 # three stages, three resources
+    assert abs(r["period"] - 3.0) < 1e-6 and abs(r["latency"] - 6.0) < 1e-6 and r["copies"] == 2
+    assert r["starts"] == [0.0, 2.0, 5.0]
+    r = plan_pipeline([2.0, 3.0, 1.0], [0, 0, 0], chain)                 # one resource: no overlap possible
+    assert abs(r["period"] - 6.0) < 1e-6 and r["copies"] == 1
+    r = plan_pipeline([2.0, 3.0, 1.0], [0, 1, 2], chain + [(2, 0, 1)])   # the next execution waits for this one's end
+    assert abs(r["period"] - 6.0) < 1e-6 and abs(r["recurrence_bound"] - 6.0) < 1e-6 and r["copies"] == 1
+    r = plan_pipeline([2.0, 3.0, 1.0], [0, 1, 2], chain + [(2, 0, 2)])   # ... for the one before: two in flight
+    assert abs(r["period"] - 3.0) < 1e-6 and r["copies"] == 2
+    # a random instance: check the schedule itself
+    import random
+    rng = random.Random(5)
+    n = 24
+    dur = [rng.choice([0.5, 1.0, 2.0, 3.5]) for _ in range(n)]
+    res = [rng.randrange(3) for _ in range(n)]
+    edges = [(a, b, 0) for b in range(n) for a in range(b) if rng.random() < 0.12] + [(n - 1, 0, 3), (10, 4, 1)]
+    r = plan_pipeline(dur, res, edges)
+    P, st = r["period"], r["starts"]
+    assert P >= max(r["resource_bound"], r["recurrence_bound"]) - 1e-6
+    for a, b, lag in edges:
+        assert st[b] + lag * P >= st[a] + dur[a] - 1e-6
+    for k in range(3):
+        spans = sorted((st[i] % P, dur[i]) for i in range(n) if res[i] == k)
+        wrapped = [(s, d) for s, d in spans] + [(s + P, d) for s, d in spans]
+        for (s0, d0), (s1, _d1) in zip(wrapped, wrapped[1:]):
+            assert s1 >= s0 + d0 - 1e-6
+    assert r["copies"] == max(1, -(-int(r["latency"] / P * 1e6) // 10 ** 6))
+    with pytest.raises(ValueError):
+        plan_pipeline([1.0, 1.0], [0, 0], [(0, 1, 0), (1, 0, 0)])        # a cycle within one execution
