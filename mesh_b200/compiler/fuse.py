@@ -162,6 +162,68 @@ def bucket_reductions(plan: Plan) -> tuple[Plan, int]:
     return plan, count
 
 
+def fuse_ring_attention(plan: Plan) -> tuple[Plan, int]:
+    """Context parallelism as a ring: attention over queries cut along the sequence whose keys and values were cut the
+    same way and gathered for it,
+
+        K = all_gather(k); V = all_gather(v); y = attention(q, K, V)      ->   y = fused ring_attention(q, k, v)
+
+    becomes one step in which the key / value blocks travel around the processors of the axis while every processor
+    attends its queries to the block it holds and merges the partial results by their running maximum and sum
+    (blockwise attention with ring rotation, the reference's attention operator,
+    compiler/mesh_compiler/operations.py:7081-7166).  No processor ever holds the whole keys and values; the bytes on
+    the links are those of the two gathers.  A causal mask goes by the positions of the tokens in the whole sequence,
+    for contiguous and striped cuts alike.  Applies when the gathered values have no other reader, there is no mask
+    tensor and no dropout."""
+    sdpa = aten.scaled_dot_product_attention.default
+    plan = copy.copy(plan)
+    steps = list(plan.steps)
+    uses = _uses(plan)
+    producer = {st.out: i for i, st in enumerate(steps)}
+    drop: set[int] = set()
+    replace: dict[int, Step] = {}
+    count = 0
+    for i, st in enumerate(steps):
+        if st.op != "call" or st.target is not sdpa or "out_specs" not in st.meta or len(st.args) < 3:
+            continue
+        if not all(isinstance(a, Ref) for a in st.args[:3]):
+            continue
+        opt = dict(zip(("attn_mask", "dropout_p", "is_causal"), st.args[3:6]))
+        opt.update(st.kwargs)
+        if opt.get("attn_mask") is not None or (opt.get("dropout_p") or 0.0) != 0.0:
+            continue
+        cut = [(ax, sp) for ax, sp in enumerate(st.meta["out_specs"]) if sp.kind == "S" and sp.dim == 2]
+        if len(cut) != 1:
+            continue
+        ax, sp = cut[0]
+        gathers = []
+        for ref in st.args[1:3]:
+            j = producer.get(ref.name)
+            g = steps[j] if j is not None else None
+            if g is None or g.op != "collective" or g.target != "all_gather" or g.meta.get("axis") != ax or j in drop:
+                break
+            frm = g.meta["from"]
+            if frm.kind != "S" or frm.dim != 2 or tuple(frm.counts) != tuple(sp.counts) or frm.striped != sp.striped:
+                break
+            if uses.get(ref.name, []) != [i]:
+                break
+            gathers.append(j)
+        if len(gathers) != 2 or gathers[0] == gathers[1]:
+            continue
+        kg, vg = steps[gathers[0]], steps[gathers[1]]
+        meta = dict(st.meta)
+        meta.update({"fused": "ring_attention", "axis": ax, "channel": kg.meta["channel"], "kind": "permute",
+                     "causal": bool(opt.get("is_causal", False)) or "causal_rows" in st.meta, "scale": opt.get("scale"),
+                     "enable_gqa": bool(opt.get("enable_gqa", False)), "keys": tuple(kg.meta["full_shape"]),
+                     "channels": (kg.meta["channel"], vg.meta["channel"])})
+        replace[i] = Step("fused", st.out, "ring_attention", (st.args[0], kg.args[0], vg.args[0]), {}, meta)
+        drop.update(gathers)
+        count += 1
+    if count:
+        plan.steps = [replace.get(i, st) for i, st in enumerate(steps) if i not in drop]
+    return plan, count
+
+
 def fuse_norms(plan: Plan) -> tuple[Plan, int]:
     """An RMS norm is captured as the chain ``pow(x, 2) -> mean(last dim, keepdim) -> add(eps) -> rsqrt -> mul(x, .)
     [-> mul(., w)]``.  Where every link has that one reader (an inference graph: a training graph keeps the

@@ -740,13 +740,17 @@ class Propagator:
         if s.kind != "S":
             return [s], s
         ish, osh = self.shape[targs[0]], _shape(node)
-        if s.striped:
-            return [R], R
         pre = int(math.prod(ish[:s.dim]))
         acc = 1
         for d_out, sz in enumerate(osh):
             if acc == pre and sz != 1 or (acc == pre and d_out == len(osh) - 1):
                 n_in = ish[s.dim]
+                if s.striped:
+                    # round-robin rows survive a view only where their dimension is left alone (same extent, neither
+                    # merged with a neighbour nor split): [B, T, E] -> [B, T, H, D] keeps tokens cut round-robin
+                    if sz == n_in and int(math.prod(osh[d_out + 1:])) == int(math.prod(ish[s.dim + 1:])):
+                        return [s], Spec("S", d_out, s.counts, True)
+                    break
                 if sz % n_in == 0:                     # the sharded dim becomes the outer factor of a merged dim
                     f = sz // n_in
                     return [s], Spec("S", d_out, tuple(c * f for c in s.counts))

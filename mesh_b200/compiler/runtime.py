@@ -445,8 +445,77 @@ class Executor:
                           else FusedRowLinear(ctx.heap, rows_total, w.shape[1], w.shape[0]))
         return cache[key]
 
+    def ring_attention(self, st: Step, q, k, v):
+        """Blockwise attention with the key / value blocks rotating around the axis (``fuse.fuse_ring_attention``).
+        Round ``r`` attends this processor's queries to the block that started on processor ``me - r``; partial results
+        are merged by running maximum and sum (rows that have seen nothing yet carry weight zero); a causal mask
+        compares positions in the whole sequence, whatever the cut.  Accumulates in fp32."""
+        m = st.meta
+        if q is None or k is None or v is None:
+            return None
+        ax = m["axis"]
+        spec = m["out_specs"][ax]
+        P, me = self.mesh.shape[ax], self.coords[ax]
+        total = m["full_shape"][2]
+        if self.trace is not None:
+            self.trace.append(("ring", m.get("kind"), ax, m["channel"]))
+
+        def positions(r):
+            idx = local_indices(spec, r, total)
+            if isinstance(idx, slice):
+                return torch.arange(idx.start or 0, idx.stop, idx.step or 1, device=q.device)
+            return torch.as_tensor(list(idx), device=q.device, dtype=torch.long)
+        scale = m.get("scale")
+        scale = (q.shape[-1] ** -0.5) if scale is None else scale
+        qf = q.float() * scale
+        group = q.shape[1] // k.shape[1] if k.shape[1] and q.shape[1] != k.shape[1] else 1
+        qpos = positions(me)
+        acc = torch.zeros(*q.shape[:-1], v.shape[-1], dtype=torch.float32, device=q.device)
+        top = torch.full((*q.shape[:-1], 1), float("-inf"), dtype=torch.float32, device=q.device)
+        den = torch.zeros_like(top)
+        threads = None
+        if P > 1 and not self.dist:
+            threads = (self.coll.gather_all(k, ax)[0], self.coll.gather_all(v, ax)[0])
+        kb, vb = k, v
+        for r in range(P):
+            src = (me - r) % P
+            if threads is not None:
+                kb, vb = threads[0][src], threads[1][src]
+            if kb.shape[2]:
+                kk, vv = kb.float(), vb.float()
+                if group > 1:
+                    kk, vv = kk.repeat_interleave(group, 1), vv.repeat_interleave(group, 1)
+                s = qf @ kk.transpose(-1, -2)
+                if m.get("causal"):
+                    s = s.masked_fill(positions(src)[None, :] > qpos[:, None], float("-inf"))
+                blk = s.amax(-1, keepdim=True)
+                new = torch.maximum(top, blk)
+                safe = torch.where(torch.isinf(new), torch.zeros_like(new), new)      # rows that still see nothing
+                w = torch.exp(s - safe)
+                keep = torch.exp(torch.where(torch.isinf(top), torch.full_like(top, float("-inf")), top - safe))
+                den = den * keep + w.sum(-1, keepdim=True)
+                acc = acc * keep + w @ vv
+                top = new
+            if r < P - 1 and threads is None and P > 1:
+                kb, vb = self._pass_on((kb, vb), ax, [list(x.shape[:2]) + [spec.counts[(src - 1) % P]] + [x.shape[3]] for x in (k, v)])
+        out = acc / torch.where(den == 0, torch.ones_like(den), den)
+        return out.to(q.dtype)
+
+    def _pass_on(self, blocks, ax, shapes):
+        """Send ``blocks`` to the next processor of the axis and receive, with ``shapes``, what the previous one sends."""
+        grp, g = self.coll.group(ax)
+        P, me = self.mesh.shape[ax], self.coords[ax]
+        got = [torch.empty(sh, dtype=b.dtype, device=b.device) for sh, b in zip(shapes, blocks)]
+        ops = [dist.P2POp(dist.isend, b.contiguous(), g[(me + 1) % P], group=grp) for b in blocks]
+        ops += [dist.P2POp(dist.irecv, t, g[(me - 1) % P], group=grp) for t in got]
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+        return got
+
     def fused(self, st: Step, a, w_t, env=None):
         m = st.meta
+        if st.target == "ring_attention":
+            return self.ring_attention(st, a, w_t, None if env is None else env.get(st.args[2].name))
         if a is None or w_t is None:
             if "keep" in m and env is not None:
                 env[m["keep"]] = None                        # absent here: so are the gathered rows for the other readers
@@ -802,6 +871,9 @@ class Program(Arguments):
             from .fuse import fuse_norms, fuse_plan
             self.plan, self.fusion = fuse_plan(self.plan)
             self.plan, self.fusion["rms_norm"] = fuse_norms(self.plan)
+            if os.environ.get("MESH_RING_ATTENTION", "1") != "0":
+                from .fuse import fuse_ring_attention
+                self.plan, self.fusion["ring_attention"] = fuse_ring_attention(self.plan)
         self.bucketed = 0
         if os.environ.get("MESH_BUCKET", "0") == "1":
             from .fuse import bucket_reductions

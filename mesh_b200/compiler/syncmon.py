@@ -11,7 +11,7 @@ from __future__ import annotations
 import hashlib
 
 
-_FUSED = {"ag_mm": "all_gather", "mm_rs": "reduce_scatter"}
+_FUSED = {"ag_mm": "all_gather", "mm_rs": "reduce_scatter", "ring_attention": "ring"}
 
 
 def expected(plan) -> list[tuple]:

@@ -523,7 +523,7 @@ def test_sequence_parallel_megatron_layer_has_the_textbook_collectives():
     sch = compile_module(m, (x,), procs, lambda nd: (1, names, None) if nd.op == "placeholder" and nd.name == "x" else tp(nd))
     assert sch.structure["by_verb"] == {"all_gather": 2, "reduce_scatter": 2, "all_reduce": 1}, sch.structure["by_verb"]
     prog = Program(sch)
-    assert prog.fusion == {"ag_mm": 2, "mm_rs": 2, "rms_norm": 2}
+    assert prog.fusion == {"ag_mm": 2, "mm_rs": 2, "rms_norm": 2, "ring_attention": 0}
     assert torch.allclose(prog(x), m(x), atol=1e-4)
 
 
@@ -727,3 +727,60 @@ def test_embedding_bag_keeps_a_column_cut_table():
     got = Program(sch)(idx, off)
     got = got[0] if isinstance(got, (tuple, list)) else got
     assert torch.allclose(got, m(idx, off), atol=1e-6)
+
+
+class _Blocks(torch.nn.Module):
+    """The decoder's blocks without its loss: an inference graph, where attention stays one operator."""
+
+    def __init__(self, layers=2):
+        super().__init__()
+        self.d = Decoder(dim=32, heads=4, ffn=64, layers=layers)
+
+    def forward(self, x):
+        for b in self.d.blocks:
+            x = b(x)
+        return x
+
+
+@pytest.mark.parametrize("n,units", [(2, None), (3, (3, 1, 2)), (4, "striped"), (5, None)])
+def test_context_parallel_attention_runs_as_a_ring(n, units, monkeypatch):
+    """Tokens cut over the processors, contiguous, unequal, round-robin or with an empty share: the two gathers of keys
+    and values in front of every attention become one ring step (blocks rotate, partial results merge by running
+    maximum and sum, causal masks by positions in the whole sequence); what remains gathered is the output."""
+    torch.manual_seed(31)
+    m = _Blocks().eval()
+    x = torch.randn(2, 12, 32)
+    procs = _procs(n)
+    sch = compile_module(m, (x,), procs, sequence_parallel(procs, units=units))
+    assert sch.structure["by_verb"] == {"all_gather": 5} and sch.structure["gathering_fallbacks"] == 0
+    prog = Program(sch)
+    assert prog.fusion["ring_attention"] == 2
+    rings = [st for st in prog.plan.steps if st.op == "fused" and st.target == "ring_attention"]
+    assert len(rings) == 2 and all(st.meta["causal"] and st.meta["kind"] == "permute" for st in rings)
+    assert sum(1 for st in prog.plan.steps if st.op == "collective") == 1
+    ref = m(x)
+    assert (prog(x) - ref).abs().max() <= 1e-5 * ref.abs().max()
+    from mesh_b200.compiler import syncmon
+    assert [v for v, *_ in syncmon.expected(prog.plan)].count("ring") == 2
+    monkeypatch.setenv("MESH_RING_ATTENTION", "0")               # the gathered form computes the same numbers
+    plain = Program(sch)
+    assert plain.fusion.get("ring_attention", 0) == 0
+    assert (plain(x) - ref).abs().max() <= 1e-5 * ref.abs().max()
+
+
+def _ring_rank(rank, world, rdv):
+    torch.manual_seed(32)
+    m = _Blocks(layers=1).eval()
+    x = torch.randn(2, 10, 32)
+    procs = _procs(world)
+    prog = Program(compile_module(m, (x,), procs, sequence_parallel(procs, units=(2, 1, 2))))
+    assert prog.fusion["ring_attention"] == 1 and not prog.threads
+    out = prog(x)                                                # blocks pass from process to process (point to point)
+    if out is not None:
+        ref = m(x)
+        assert (out - ref).abs().max() <= 1e-5 * ref.abs().max()
+
+
+def test_ring_attention_between_processes():
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_ring_rank, 3, init_pg="gloo")
