@@ -2125,6 +2125,10 @@ def place(exported, processors: dict, placement: Callable, mesh_shape: tuple | N
                 continue
             sp = normalise(placement(node), node, mesh, names_to_axis)
             if sp is not None:
+                cut = [s.dim for s in sp if s.kind == "S"]
+                if len(cut) != len(set(cut)):
+                    raise ValueError(f"placement of {node.name}: dimension {cut[0]} is cut along more than one axis of "
+                                     f"the processor grid; cut it once, over the processors of both axes as one line")
                 stated[node.name] = sp
     # gradients land where their parameter lives (sharded parameters get reduce-scattered gradients)
     if out_node is not None:

@@ -284,3 +284,13 @@ def test_whole_attention_under_every_cut(causal):
             if dim == 2 and which == ("q", "k", "v"):
                 # queries stay cut (with their rows of the causal mask); keys, values and the result are gathered
                 assert sch.structure["fallbacks"] == 0 and sch.structure["by_verb"] == {"all_gather": 3}
+
+
+def test_one_dimension_cut_along_two_grid_axes_is_refused_with_a_reason():
+    import pytest
+    from mesh_b200.compiler import compile_module
+    m = torch.nn.Linear(8, 8)
+    x = torch.randn(4, 8)
+    procs = {f"p{i}": (0, "cpu") for i in range(4)}
+    with pytest.raises(ValueError, match="more than one axis"):
+        compile_module(m, (x,), procs, lambda n: ((0, 0), None, (None, None)) if n.name == "input" or n.name == "x" else None, mesh=(2, 2))
