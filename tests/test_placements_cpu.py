@@ -88,3 +88,23 @@ def test_vocabulary_parallel_embedding_with_column_and_row_layers_and_cut_inputs
     sch = compile_module(m, (ids, labels), procs, dp, loss=0)
     assert sch.structure["by_verb"].get("all_reduce", 0) >= len(list(m.parameters()))
     _close(Program(sch)(ids, labels), *_eager(m, ids, labels))
+
+
+def test_training_graphs_keep_their_submodule_paths():
+    """The joint forward+backward trace drops the nodes' submodule paths; the capture puts them back: nearly every
+    operator of a training plan knows the model part it belongs to (what share solvers and pipelines go by), and the
+    backward operators of a layer carry that layer's path."""
+    from mesh_b200.compiler import shares
+    torch.manual_seed(3)
+    m = Decoder(dim=32, heads=2, ffn=64, layers=2)
+    x = torch.randn(2, 8, 32)
+    sch = compile_module(m, (x,), _procs(2), placements.data_parallel(("p0", "p1")), loss=0)
+    calls = [n for n in sch.exported.graph_module.graph.nodes if n.op == "call_function"]
+    with_path = [n for n in calls if n.meta.get("nn_module_stack")]
+    assert len(with_path) >= 0.95 * len(calls)
+    backward_of_w2 = [n for n in calls if "blocks.1.w2" in [q for q, _ in (n.meta.get("nn_module_stack") or {}).values()]]
+    assert len(backward_of_w2) >= 4                       # the forward product, its two backward products, their views
+    parts = {st.meta.get("module") for st in sch.plan.steps if st.op == "call"}
+    assert {"blocks.0.w1", "blocks.1.wo", "blocks.1.attention_norm"} <= parts
+    staged = shares.stages(sch)
+    assert staged is not None
