@@ -76,9 +76,11 @@ def _cuts_inner_dimension(exported, placement) -> bool:
         if stated is None:
             continue
         for item in (stated if isinstance(stated, list) else [stated]):
-            dim = item[0] if isinstance(item, tuple) and item and isinstance(item[0], int) else None
-            if dim is not None and 0 < dim % nd < nd - 1 and math.prod(val.shape[:dim % nd]) > 1:
-                return True
+            first = item[0] if isinstance(item, tuple) and item else None
+            dims = [first] if isinstance(first, int) else [d for d in first if isinstance(d, int)] if isinstance(first, (tuple, list)) else []
+            for dim in dims:                                 # (the N-D form states one dimension per grid axis)
+                if 0 < dim % nd < nd - 1 and math.prod(val.shape[:dim % nd]) > 1:
+                    return True
     return False
 
 

@@ -449,6 +449,17 @@ class Propagator:
     def all_r(self) -> tuple:
         return tuple(R for _ in range(self.na))
 
+    def wanted(self, name: str):
+        """The placement stated for the value ``name``, with the axes it leaves open (``...`` in the N-D form) filled
+        in by what propagation found; ``None`` when nothing is stated (or nothing is known of the value yet)."""
+        want = self.stated.get(name)
+        if want is None or all(w is not None for w in want):
+            return want
+        have = self.spec.get(name)
+        if have is None or len(have) != len(want):
+            return None
+        return tuple(h if w is None else w for w, h in zip(want, have))
+
     def emit_collective(self, verb: str, kind: str, axis: int, src: str, spec_from: Spec, spec_to: Spec, consumer=JOIN) -> str:
         out = self.fresh(src)
         self.channel += 1
@@ -610,6 +621,15 @@ class Propagator:
         return out
 
     # ---- per-axis rules.  Each returns (wanted specs of tensor args, out spec) for ONE axis.
+    @staticmethod
+    def _owned(specs):
+        """The owner spec when, along one axis, some operand is whole on one coordinate and the others are whole on the
+        same coordinate or replicated; else ``None``."""
+        owner = next((s for s in specs if s.kind == "O"), None)
+        if owner is None or any(s.kind not in ("R", "O") for s in specs):
+            return None
+        return owner
+
     def rule_pointwise(self, node, targs, specs, ax):
         out_shape = _shape(node)
         nd = len(out_shape)
@@ -774,6 +794,7 @@ class Propagator:
                 if isinstance(v, torch.Tensor):
                     self.dtype[node.name] = v.dtype
                 sp = self.stated.get(node.name) or self.all_r()
+                sp = tuple(R if x is None else x for x in sp)          # an axis left open on an input: whole there
                 self.spec[node.name] = sp
                 input_specs[node.name] = sp
             elif node.op == "get_attr":
@@ -831,7 +852,7 @@ class Propagator:
         tnames = [self.renamed.get(a.name, a.name) for a in flat_args if _is_tensor_node(a)]
         stated = self.stated.get(node.name)
         self._moved_for_node = []
-        if stated is not None and tgt is not operator.getitem and any(s.kind == "O" for s in stated):
+        if stated is not None and tgt is not operator.getitem and any(s is not None and s.kind == "O" for s in stated):
             # "this node runs on that processor": operands that live whole on another processor go there first, so
             # that the operator runs where it was placed (otherwise it would run where its operands are and only its
             # result would move - and every later reader on the stated processor would pull its own copy)
@@ -842,9 +863,8 @@ class Propagator:
                 have = self.spec.get(src)
                 if have is None or len(have) != len(stated):
                     continue
-                if any(h.kind == "O" and w.kind == "O" and h.owner != w.owner for h, w in zip(have, stated)) and all(
-                        h.kind in ("R", "O") for h in have):
-                    want = tuple(w if (h.kind == "O" and w.kind == "O") else h for h, w in zip(have, stated))
+                if any(w is not None and h.kind == "O" and w.kind == "O" and h.owner != w.owner for h, w in zip(have, stated)):
+                    want = tuple(w if (w is not None and h.kind == "O" and w.kind == "O") else h for h, w in zip(have, stated))
                     self.renamed[a.name] = self.reshard(src, want)
                     self._moved_for_node.append(a.name)
             tnames = [self.renamed.get(a.name, a.name) for a in flat_args if _is_tensor_node(a)]
@@ -935,12 +955,17 @@ class Propagator:
         if stack:
             meta["module"] = list(stack.values())[-1][0]          # submodule path the op was traced from
         self.steps.append(Step("call", node.name, tgt, args, kwargs, meta))
-        want = self.stated.get(node.name)
+        want = self.wanted(node.name)
         if want is not None and want != tuple(out_specs):
             self.renamed[node.name] = self.reshard(node.name, want)      # a stated placement is a constraint
 
     def axis_rule(self, node, tnames, specs, ax, meta):
         tgt = node.target
+        owned = self._owned(specs)
+        if owned is not None and tgt not in POINTWISE and tgt not in (aten.mm.default, aten.bmm.default, aten.matmul.default, aten.addmm.default):
+            # along this axis every operand is whole on one coordinate (a pipeline stage) or everywhere: the operator
+            # runs on that coordinate only, whatever it is
+            return [owned if s.kind == "O" else R for s in specs], owned
         if tgt in POINTWISE:
             return self.rule_pointwise(node, tnames, specs, ax)
         if tgt in (aten.mm.default, aten.bmm.default):
@@ -1247,7 +1272,7 @@ class Propagator:
         self.spec[node.name] = out_spec
         self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
                                self.ref_kwargs(node.kwargs, new_names), {"out_specs": out_spec, "full_shape": _shape(node)}))
-        want = self.stated.get(node.name)
+        want = self.wanted(node.name)
         if want is not None and want != out_spec:
             self.renamed[node.name] = self.reshard(node.name, want)
         return True
@@ -1339,6 +1364,14 @@ class Propagator:
         found = False
         for ax in range(self.na):
             specs = [self.spec[n][ax] for n in tnames]
+            owned = self._owned(specs)
+            if owned is not None:                           # a pipeline stage along this axis: run there
+                for n in tnames:
+                    if len(wants[n]) <= ax:
+                        wants[n].append(owned)
+                for o in out_specs:
+                    o.append(owned)
+                continue
             if any(s.kind not in ("R", "S") for s in specs):
                 return False
             cut = next((s for s, f in zip(specs, flags) if f and s.kind == "S"), None)
@@ -1387,7 +1420,7 @@ class Propagator:
             meta["module"] = list(stack.values())[-1][0]
         self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
                                self.ref_kwargs(node.kwargs, new_names), meta))
-        want = self.stated.get(node.name)
+        want = self.wanted(node.name)
         if not several and want is not None and want != self.spec[node.name]:
             self.renamed[node.name] = self.reshard(node.name, want)
         return True
@@ -1607,7 +1640,7 @@ class Propagator:
         self.spec[node.name] = out_spec
         self.steps.append(Step("call", node.name, node.target, tuple(new_args), self.ref_kwargs(node.kwargs),
                                {"out_specs": out_spec, "full_shape": _shape(node), "halo": (left, right)}))
-        want = self.stated.get(node.name)
+        want = self.wanted(node.name)
         if want is not None and want != out_spec:
             self.renamed[node.name] = self.reshard(node.name, want)
         return True
@@ -1752,7 +1785,7 @@ class Propagator:
             self.spec[node.name] = outs_
             meta["out_specs"] = outs_
             self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names), self.ref_kwargs(node.kwargs), meta))
-            want = self.stated.get(node.name)
+            want = self.wanted(node.name)
             if want is not None and want != outs_:
                 self.renamed[node.name] = self.reshard(node.name, want)
             return True
@@ -1839,7 +1872,7 @@ class Propagator:
             self.spec[node.name] = summed
             self.steps.append(Step("call", node.name, aten.add.Tensor, (Ref(whole), Ref(lined)), {},
                                    {"out_specs": summed, "full_shape": full}))
-        want = self.stated.get(node.name)
+        want = self.wanted(node.name)
         if want is not None and want != self.spec[node.name]:
             self.renamed[node.name] = self.reshard(node.name, want)
         return True
@@ -1920,7 +1953,7 @@ class Propagator:
             self.spec[node.name] = big
             self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args), self.ref_kwargs(node.kwargs),
                                    {"out_specs": big, "full_shape": _shape(node)}))
-            want = self.stated.get(node.name)
+            want = self.wanted(node.name)
             if want is not None and want != big:
                 self.renamed[node.name] = self.reshard(node.name, want)
             return True
@@ -2008,11 +2041,19 @@ class Propagator:
         new_names = {}
         gathered = 0                               # operands that were not whole everywhere: each costs a transfer
 
+        # an axis along which every operand is whole on one coordinate (or everywhere) stays that way: the operator
+        # runs on that coordinate; only cut and partial operands are made whole
+        every = [self.spec.get(self.renamed.get(x.name, x.name)) for x in
+                 [a for a in node.args if _is_tensor_node(a)] + [x for la in list_args for x in la if _is_tensor_node(x)] +
+                 [v for v in node.kwargs.values() if _is_tensor_node(v)]]
+        every = [sp for sp in every if sp is not None and len(sp) == self.na]
+        target = tuple((self._owned([sp[a] for sp in every]) or R) if every else R for a in range(self.na))
+
         def whole(x):
             nonlocal gathered
             src = self.renamed.get(x.name, x.name)
-            gathered += any(s.kind != "R" for s in self.spec.get(src, ()))
-            new_names[x.name] = self.reshard(src, self.all_r())
+            gathered += any(s.kind not in ("R", "O") for s in self.spec.get(src, ()))
+            new_names[x.name] = self.reshard(src, target)
         for a in node.args:
             if _is_tensor_node(a):
                 whole(a)
@@ -2025,7 +2066,7 @@ class Propagator:
                 whole(v)
         self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names),
                                self.ref_kwargs(node.kwargs, new_names), {"fallback": True, "gathered": gathered}))
-        self.spec[node.name] = self.all_r()
+        self.spec[node.name] = target
 
     def ref_args(self, args, rename=None):
         rename = rename or {}
@@ -2062,6 +2103,17 @@ def normalise(stated, node, mesh: Mesh, names_to_axis) -> tuple | None:
         specs = [R] * na
         for a, (d, u) in enumerate(zip(dims, units_l)):
             if d is None:
+                continue
+            if d is Ellipsis:                              # this axis is left to propagation
+                specs[a] = None
+                continue
+            if isinstance(d, str):                         # "@k": whole on coordinate k of this axis (a pipeline stage)
+                if not d.startswith("@"):
+                    raise ValueError(f"placement of {node.name}: {d!r} is neither a dimension nor '@coordinate'")
+                k = int(d[1:])
+                if not 0 <= k < mesh.shape[a]:
+                    raise ValueError(f"placement of {node.name}: coordinate {k} is outside axis {a} of the grid")
+                specs[a] = O(k)
                 continue
             d = d % len(shape)
             c = counts(shape[d], u, mesh.shape[a])
@@ -2125,7 +2177,7 @@ def place(exported, processors: dict, placement: Callable, mesh_shape: tuple | N
                 continue
             sp = normalise(placement(node), node, mesh, names_to_axis)
             if sp is not None:
-                cut = [s.dim for s in sp if s.kind == "S"]
+                cut = [s.dim for s in sp if s is not None and s.kind == "S"]
                 if len(cut) != len(set(cut)):
                     raise ValueError(f"placement of {node.name}: dimension {cut[0]} is cut along more than one axis of "
                                      f"the processor grid; cut it once, over the processors of both axes as one line")

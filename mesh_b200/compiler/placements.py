@@ -10,6 +10,7 @@ library is placed without editing it:
   vocabulary-parallel embeddings;
 * :func:`data_parallel`, :func:`sequence_parallel`: cut the user inputs;
 * :func:`pipeline`: whole submodules on one processor each;
+* :func:`grid`: pipeline stages, tensor-parallel layers and cut inputs on a grid of processors whose axes have roles;
 * :func:`combine`: the first builder that states something for a node wins.
 
 Placeholder names are the qualified parameter names with dots replaced by underscores and a ``p_`` (parameter),
@@ -113,6 +114,75 @@ def pipeline(stages: dict) -> Callable:
             proc = of_path(qual + ".")
             if proc is not None:
                 return proc
+        return None
+    return placement
+
+
+def grid(axes: Sequence[str], *, stages: dict | None = None, stage_axis: str | None = None, column: Iterable[str] = (),
+         row: Iterable[str] = (), vocabulary: Iterable[str] = (), tensor_axis: str | None = None,
+         inputs: dict | None = None) -> Callable:
+    """One placement for a grid of processors whose axes have roles - the compiled form of a hybrid job such as
+    ``("pp", "cp", "tp")`` with ``compile_module(..., mesh=(2, 2, 2))``.
+
+    * ``stages`` / ``stage_axis``: ``{module path pattern: coordinate}`` - the submodules that run on each coordinate of
+      the pipeline axis.  Their parameters live there (``"@k"`` along that axis) and their operators run there, forward
+      and backward; the other axes of an operator are left to propagation (``...``).
+    * ``column`` / ``row`` / ``vocabulary`` / ``tensor_axis``: Megatron cuts of the named layers along the tensor axis.
+    * ``inputs``: ``{input name: {axis name: dimension}}`` - cuts of the user inputs (tokens over a context axis, samples
+      over a data axis); inputs enter at coordinate 0 of the pipeline axis.
+    """
+    axes = tuple(axes)
+    na = len(axes)
+    s_ax = axes.index(stage_axis) if stage_axis is not None else None
+    t_ax = axes.index(tensor_axis) if tensor_axis is not None else None
+    compiled = [(re.compile(p), k) for p, k in (stages or {}).items()]
+    is_col, is_row, is_vocab = _matcher(column), _matcher(row), _matcher(vocabulary)
+    inputs = inputs or {}
+
+    def stage_of_path(path: str):
+        for pat, k in compiled:
+            if pat.match(path):
+                return k
+        return None
+
+    def stage_of_parameter(name: str):
+        path = name.split("_", 1)[1]
+        for pat, k in compiled:
+            if re.match(pat.pattern.replace(r"\.", "_").replace(".", "_"), path):
+                return k
+        return None
+
+    def placement(node):
+        if _is_state(node):
+            dims = [None] * na
+            k = stage_of_parameter(node.name) if s_ax is not None else None
+            if k is not None:
+                dims[s_ax] = f"@{k}"
+            nd = getattr(node.meta.get("val"), "ndim", 0)
+            if t_ax is not None:
+                if node.name.endswith("_weight") and nd >= 2:
+                    dims[t_ax] = 0 if (is_col(node.name) or is_vocab(node.name)) else 1 if is_row(node.name) else None
+                elif node.name.endswith("_bias") and nd == 1 and is_col(node.name):
+                    dims[t_ax] = 0
+            return (tuple(dims), None, None) if any(d is not None for d in dims) else None
+        if node.op == "placeholder":
+            dims = [None] * na
+            for axis, dim in inputs.get(node.name, {}).items():
+                dims[axes.index(axis)] = dim
+            if s_ax is not None:
+                dims[s_ax] = "@0"
+            return (tuple(dims), None, None) if any(d is not None for d in dims) else None
+        if s_ax is None:
+            return None
+        stack = node.meta.get("nn_module_stack")
+        if not stack:
+            return None
+        for _key, (qual, _cls) in reversed(list(stack.items())):
+            k = stage_of_path(qual + ".")
+            if k is not None:
+                dims = [...] * na
+                dims[s_ax] = f"@{k}"
+                return (tuple(dims), None, None)
         return None
     return placement
 

@@ -62,12 +62,14 @@ class ThreadWorld:
 class ThreadCollectives:
     def __init__(self, world: ThreadWorld, mesh: Mesh, rank: int, device: torch.device | None = None):
         self.world, self.mesh, self.rank, self.device = world, mesh, rank, device
-        self.seq = 0
+        self.seq: dict = {}
 
     def gather_all(self, t, axis):
-        self.seq += 1
+        # exchanges are numbered per line of processors: a line that sits out a collective (its value lives on another
+        # pipeline stage) must not fall out of step with the lines it shares other axes with
         g = self.mesh.axis_group(self.rank, axis)
-        parts = self.world.exchange(self.seq, g, self.rank, t)
+        self.seq[g] = self.seq.get(g, 0) + 1
+        parts = self.world.exchange(self.seq[g], g, self.rank, t)
         if self.device is not None:               # processors on different devices: what arrives is copied to this one
             parts = [v.to(self.device) if isinstance(v, torch.Tensor) and v.device != self.device else v for v in parts]
         return parts, g
@@ -158,6 +160,10 @@ class Executor:
             self.trace.append((verb, m.get("kind"), ax, m["channel"]))
         if P == 1 and verb not in ("halo", "halo_back"):
             return t
+        if t is None and frm.kind != "O":
+            # the value lives on another coordinate of some other axis (another pipeline stage): so it does for every
+            # processor of this axis's line, and none of them takes part
+            return None
         if verb == "halo":
             return self._halo(t, ax, frm.dim, m["left"], m["right"], me, P)
         if verb == "halo_back":
@@ -961,7 +967,9 @@ class Program(Arguments):
         [t.start() for t in ts]
         [t.join() for t in ts]
         if errors:
-            raise errors[0]
+            # the first failure aborts the barriers of the others: report the cause, not a bystander's broken barrier
+            real = [e for e in errors if not isinstance(e, threading.BrokenBarrierError)]
+            raise (real or errors)[0]
         self.per_rank = results
         owner = 0 if self.entry is None else self.mesh.names.index(self.entry)
         ex, flat = results[owner]

@@ -39,3 +39,13 @@ def test_planner_workload_moves_columns_to_the_fast_rank():
 def test_hybrid_train_example_solo_cpu():
     losses = _load("hybrid_train").main(["--small", "--steps", "4"])
     assert losses[-1] < losses[0]
+
+
+@pytest.mark.parametrize("flags", [[], ["--inference", "--grid", "2,2,1"]])
+def test_hybrid_job_as_one_compiled_program(flags):
+    """Pipeline x context x tensor on a grid of CPU threads: one compiled step, the numbers of eager PyTorch."""
+    rep = _load("hybrid_compiled").main(["--small"] + flags)
+    assert rep["ok"] and rep["signature_ok"] and rep["gathering_fallbacks"] == 0, rep
+    assert rep["by_verb"].get("send_recv", 0) >= 1
+    if flags:
+        assert rep["fused"]["ring_attention"] == 4, rep
