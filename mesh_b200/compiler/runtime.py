@@ -105,8 +105,19 @@ class DistCollectives:
         grp, g = self.group(axis)
         shapes = [None] * len(g)
         dist.all_gather_object(shapes, (tuple(t.shape), t.dtype), group=grp)
-        outs = [torch.empty(s, dtype=d, device=t.device) for s, d in shapes]
-        dist.all_gather(outs, t.contiguous(), group=grp)
+        if len({(s, d) for s, d in shapes}) == 1:
+            outs = [torch.empty(s, dtype=d, device=t.device) for s, d in shapes]
+            dist.all_gather(outs, t.contiguous(), group=grp)
+            return outs, g
+        # parts of different sizes (an absent value is an empty stand-in): as bytes, padded to the longest
+        sizes = [int(math.prod(s)) * torch.empty((), dtype=d).element_size() for s, d in shapes]
+        longest = max(max(sizes), 1)
+        mine = torch.zeros(longest, dtype=torch.uint8, device=t.device)
+        raw = t.contiguous().reshape(-1).view(torch.uint8)
+        mine[: raw.numel()] = raw
+        bufs = [torch.empty(longest, dtype=torch.uint8, device=t.device) for _ in g]
+        dist.all_gather(bufs, mine, group=grp)
+        outs = [b[:n].view(d).reshape(s) if n else torch.empty(s, dtype=d, device=t.device) for b, n, (s, d) in zip(bufs, sizes, shapes)]
         return outs, g
 
 
@@ -169,7 +180,7 @@ class Executor:
         if verb == "halo_back":
             return self._halo_back(t, ax, frm.dim, m["left"], m["right"], me, P)
         if self.dist:
-            return self._collective_dist(verb, ax, frm, to, t, m)
+            return self._collective_dist(verb, ax, frm, to, t, m, step.args[0].name if step.args and isinstance(step.args[0], Ref) else None)
         parts, g = self.coll.gather_all(t, ax)
         if verb == "all_reduce" or verb == "reduce":
             out = self._reduce(parts, frm.op)
@@ -292,7 +303,7 @@ class Executor:
             out[tuple(sl)] = p
         return out
 
-    def _collective_dist(self, verb, ax, frm, to, t, m):
+    def _collective_dist(self, verb, ax, frm, to, t, m, step_name: str | None = None):
         from ..distributed import verbs
         grp, g = self.coll.group(ax)
         me = self.coords[ax]
@@ -314,9 +325,31 @@ class Executor:
             return out.contiguous()
         if verb == "broadcast":
             src = g[frm.owner]
-            buf = t if t is not None else torch.empty(m["full_shape"], dtype=self.plan.dtypes.get(m.get("value", ""), torch.float32), device=self.device)
+            buf = t if t is not None else torch.empty(m["full_shape"], dtype=self.plan.dtypes.get(m.get("value") or step_name or "", torch.float32), device=self.device)
             dist.broadcast(buf, src=src, group=grp)
             return buf
+        if verb == "send_recv":
+            # a value whole on one coordinate moves to another (a pipeline crossing): point to point, its shape first
+            # (the receiver knows the whole shape, not how the other axes cut it on the sender)
+            if frm.owner == to.owner:
+                return t
+            name = m.get("value") or (step_name or "")
+            dtype = self.plan.dtypes.get(name, torch.float32)
+            if me == frm.owner:
+                head = torch.zeros(9, dtype=torch.int64, device=self.device)
+                head[0] = t.dim()
+                head[1:1 + t.dim()] = torch.tensor(list(t.shape), dtype=torch.int64)
+                dist.send(head, g[to.owner], group=grp)
+                dist.send(t.contiguous(), g[to.owner], group=grp)
+                return None
+            if me == to.owner:
+                head = torch.zeros(9, dtype=torch.int64, device=self.device)
+                dist.recv(head, g[frm.owner], group=grp)
+                shape = [int(v) for v in head[1:1 + int(head[0])].tolist()]
+                got = torch.empty(shape, dtype=dtype, device=self.device)
+                dist.recv(got, g[frm.owner], group=grp)
+                return got
+            return None
         # uncommon verbs (striped gathers, owner moves): generic gather of the parts
         stand_in = t if t is not None else torch.empty(0, device=self.device)
         parts, _ = self.coll.gather_all(stand_in, ax)
