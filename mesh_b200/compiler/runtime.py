@@ -325,7 +325,14 @@ class Executor:
             return out.contiguous()
         if verb == "broadcast":
             src = g[frm.owner]
-            buf = t if t is not None else torch.empty(m["full_shape"], dtype=self.plan.dtypes.get(m.get("value") or step_name or "", torch.float32), device=self.device)
+            # the shape first: on a grid the owner may hold a block of the value (cut along other axes), which only it knows
+            head = torch.zeros(9, dtype=torch.int64, device=self.device)
+            if t is not None:
+                head[0] = t.dim()
+                head[1:1 + t.dim()] = torch.tensor(list(t.shape), dtype=torch.int64)
+            dist.broadcast(head, src=src, group=grp)
+            shape = [int(v) for v in head[1:1 + int(head[0])].tolist()]
+            buf = t.contiguous() if t is not None else torch.empty(shape, dtype=self.plan.dtypes.get(m.get("value") or step_name or "", torch.float32), device=self.device)
             dist.broadcast(buf, src=src, group=grp)
             return buf
         if verb == "send_recv":
