@@ -982,7 +982,13 @@ class Propagator:
             if o.kind == "S" and o.dim == 1:
                 bias = Spec("S", len(self.shape[tnames[0]]) - 1, o.counts, o.striped)
             elif o.kind == "P":
-                return [R, R, R], R                                      # keep it simple: bias with partial sums
+                # a row-parallel layer with a bias: every processor adds its partial product, and only the first of the
+                # axis adds the bias, so the sum counts it once - the result stays a partial sum (it can still be
+                # reduce-scattered by its reader instead of all-reduced here)
+                if specs[0].kind != "R" or node.kwargs.get("beta", 1) != 1 or node.kwargs.get("alpha", 1) != 1:
+                    return [R, R, R], R
+                meta.setdefault("once", (0, []))[1].append(ax)
+                bias = R
             else:
                 bias = R
             return [bias] + w, o
@@ -1817,7 +1823,7 @@ class Propagator:
         """A convolution (or transposed convolution) without groups whose channels are cut.  Output channels cut on the
         weight: every processor computes its own output channels from the whole input (the bias is cut the same way).
         Input channels cut: every processor convolves its channels with the matching slice of the weight and the
-        results are partial sums; the bias joins after the sum.  The convolution analogue of column- and row-parallel
+        results are partial sums, the bias entering through the first processor of the axis only.  The convolution analogue of column- and row-parallel
         linear layers (the reference derives both from the contraction labels of its rules,
         compiler/mesh_compiler/placement.py:503-517)."""
         args = list(node.args)
@@ -1843,35 +1849,15 @@ class Propagator:
                 xw.append(sp); ww.append(R); bw.append(R); out.append(sp)
             else:
                 xw.append(R); ww.append(R); bw.append(R); out.append(R)
-        partial = any(o.kind == "P" for o in out)
         new_names = {node.args[0].name: self.reshard(x, tuple(xw)), node.args[1].name: self.reshard(w, tuple(ww))}
-        full = _shape(node)
-        if b is not None and not partial:
+        meta = {"out_specs": tuple(out), "full_shape": _shape(node)}
+        if b is not None:
             new_names[node.args[2].name] = self.reshard(b, tuple(bw))
-        call_args = list(self.ref_args(node.args, new_names))
-        target = node.name
-        if b is not None and partial:
-            call_args[2] = None                            # the bias is added once, after the sum
-            target = self.fresh(node.name)
-            self.shape[target] = full
-            self.dtype[target] = self.dtype[node.name]
-        self.spec[target] = tuple(out)
-        self.steps.append(Step("call", target, node.target, tuple(call_args), self.ref_kwargs(node.kwargs),
-                               {"out_specs": tuple(out), "full_shape": full}))
-        if b is not None and partial:
-            summed = tuple(R if o.kind == "P" else o for o in out)
-            whole = self.reshard(target, summed)
-            # channel cuts of other axes also cut the bias: state its placement, then line it up with the channels
-            bias = self.reshard(b, tuple(bw))
-            lined = self.fresh(b)
-            shape = [1, full[1]] + [1] * (len(full) - 2)
-            lined_spec = tuple(Spec("S", 1, s.counts, s.striped) if s.kind == "S" else R for s in bw)
-            self.shape[lined], self.dtype[lined], self.spec[lined] = tuple(shape), self.dtype.get(b, self.dtype[node.name]), lined_spec
-            self.steps.append(Step("call", lined, aten.view.default, (Ref(bias), shape), {},
-                                   {"out_specs": lined_spec, "full_shape": tuple(shape), "localize": ("shape", 1)}))
-            self.spec[node.name] = summed
-            self.steps.append(Step("call", node.name, aten.add.Tensor, (Ref(whole), Ref(lined)), {},
-                                   {"out_specs": summed, "full_shape": full}))
+            summed = [a for a, o in enumerate(out) if o.kind == "P"]
+            if summed:
+                meta["once"] = (2, summed)                 # the first processor of a summed axis brings the bias
+        self.spec[node.name] = tuple(out)
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names), self.ref_kwargs(node.kwargs), meta))
         want = self.wanted(node.name)
         if want is not None and want != self.spec[node.name]:
             self.renamed[node.name] = self.reshard(node.name, want)
@@ -2052,7 +2038,7 @@ class Propagator:
         def whole(x):
             nonlocal gathered
             src = self.renamed.get(x.name, x.name)
-            gathered += any(s.kind not in ("R", "O") for s in self.spec.get(src, ()))
+            gathered += any(s.kind == "S" for s in self.spec.get(src, ()))       # (summing a partial operand is no loss)
             new_names[x.name] = self.reshard(src, target)
         for a in node.args:
             if _is_tensor_node(a):

@@ -799,6 +799,10 @@ class Executor:
                 extra[0] = mask
                 return tgt(q, k, args[2], *extra, **kw)
             return tgt(q, k, args[2], attn_mask=mask, is_causal=False, **kw)
+        if "once" in m:                                    # (argument, axes): a term every processor of those axes holds but
+            pos, axes = m["once"]                           # that must enter a partial sum once - the first one brings it
+            if any(self.coords[ax] != 0 for ax in axes) and isinstance(args[pos], torch.Tensor):
+                args[pos] = torch.zeros_like(args[pos])
         if "groups_local" in m:                            # (argument, grid axis, channels per processor): one group per channel held
             pos, ax, counts = m["groups_local"]
             args[pos] = counts[self.coords[ax]]

@@ -705,8 +705,9 @@ def test_sequence_first_attention_keeps_a_batch_cut():
 
 
 def test_embedding_bag_keeps_a_column_cut_table():
-    """A bag-of-embeddings table cut along the embedding dimension: the bags come out cut the same way and only they
-    (not the table) are gathered for the replicated layer that follows."""
+    """A bag-of-embeddings table cut along the embedding dimension: the bags come out cut the same way, the layer that
+    follows multiplies each processor's columns with the matching rows of its weight (the bias entering once), and the
+    only transfer is the sum of those small partial products - neither the table nor the bags are gathered."""
     class Net(torch.nn.Module):
         def __init__(self):
             super().__init__()
@@ -723,7 +724,7 @@ def test_embedding_bag_keeps_a_column_cut_table():
     sch = compile_module(m, (idx, off), procs,
                          lambda node: (1, tuple(procs), None) if node.op == "placeholder" and node.name == "p_bag_weight" else None)
     assert sch.structure["fallbacks"] == 0
-    assert [t.value for t in sch.plan.transfers] != ["p_bag_weight"] and sch.structure["bytes_between_processors"] == 4 * 32 * 4
+    assert [t.verb for t in sch.plan.transfers] == ["all_reduce"] and sch.structure["bytes_between_processors"] == 4 * 8 * 4
     got = Program(sch)(idx, off)
     got = got[0] if isinstance(got, (tuple, list)) else got
     assert torch.allclose(got, m(idx, off), atol=1e-6)

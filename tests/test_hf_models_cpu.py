@@ -124,3 +124,34 @@ def test_megatron_placement_by_parameter_names_costs_the_textbook_all_reduces(tr
         if g.shape != r.shape:                               # a cut weight: this processor's block
             r = r[tuple(slice(0, n) for n in g.shape)]
         assert (g - r).abs().max() <= 2e-5 * scale, name
+
+
+def test_row_parallel_layers_with_a_bias_keep_their_partial_sums():
+    """BERT's projections carry biases.  Megatron placement by names: the row-parallel layers add their bias through the
+    first processor only, so their results stay partial sums - two all-reduces per layer and nothing gathered."""
+    from mesh_b200.compiler import placements
+    torch.manual_seed(0)
+    cfg = transformers.BertConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                  num_attention_heads=4, max_position_embeddings=64, hidden_dropout_prob=0.0,
+                                  attention_probs_dropout_prob=0.0)
+    bert = transformers.BertModel(cfg)
+    bert.config._attn_implementation = "sdpa"
+
+    class Hidden(nn.Module):
+        def __init__(self, m):
+            super().__init__()
+            self.m = m
+
+        def forward(self, ids):
+            return self.m(input_ids=ids).last_hidden_state
+    model = Hidden(bert).eval()
+    ids = torch.randint(0, 128, (4, 16))
+    procs = {f"p{i}": (0, "cpu") for i in range(2)}
+    place = placements.tensor_parallel(tuple(procs), column=("query", "key", "value", "intermediate_dense"),
+                                       row=("attention_output_dense", r"layer_\d+_output_dense"))
+    sch = compile_module(model, (ids,), procs, place, strict=False)
+    assert sch.structure["by_verb"] == {"all_reduce": 4} and sch.structure["gathering_fallbacks"] == 0
+    once = [st for st in sch.plan.steps if "once" in st.meta]
+    assert len(once) == 4                                     # the four row-parallel layers
+    got, ref = Program(sch)(ids), model(ids)
+    assert (got - ref).abs().max() <= 1e-5 * ref.abs().max()
