@@ -14,6 +14,7 @@ import math
 import warnings
 
 import torch
+from torch.utils import _pytree as pytree
 from torch.export.graph_signature import InputKind, OutputKind
 
 from .ir import Exported
@@ -64,9 +65,25 @@ def export(module: torch.nn.Module, args: tuple, kwargs: dict | None = None, *, 
     ``inner_cuts``: an input is cut along an inner leading dimension (see :func:`unflatten_linears`): linear layers keep
     their operands' leading dimensions apart (inference graphs)."""
     tied = _untie(module) if loss is not None else {}
+    frozen = []
     try:
-        exported = _export(module, args, kwargs, loss, strict, decompositions, inner_cuts)
+        try:
+            exported = _export(module, args, kwargs, loss, strict, decompositions, inner_cuts)
+        except AssertionError as e:
+            if loss is None or "did not receive a gradient" not in str(e):
+                raise
+            # parameters the loss does not depend on (a shared table reached only through its other names, a head that
+            # this call does not use): the joint capture refuses them.  Find them with one eager backward pass and
+            # capture again with those left out of the gradients
+            frozen = _without_gradient(module, args, kwargs, loss)
+            if not frozen:
+                raise
+            for p in frozen:
+                p.requires_grad_(False)
+            exported = _export(module, args, kwargs, loss, strict, decompositions, inner_cuts)
     finally:
+        for p in frozen:
+            p.requires_grad_(True)
         _retie(module, tied)
     for name, (qual, _tensor) in list(exported.state.items()):
         if qual in tied:                                    # the placeholder reads the shared tensor, not the stand-in
@@ -93,6 +110,22 @@ def _untie(module: torch.nn.Module) -> dict:
     return tied
 
 
+def _without_gradient(module: torch.nn.Module, args, kwargs, loss: int) -> list:
+    """The parameters (requiring gradients) that get none when output ``loss`` of ``module(*args)`` is differentiated."""
+    params = [p for p in module.parameters() if p.requires_grad]
+    saved = [p.grad for p in params]
+    for p in params:
+        p.grad = None
+    try:
+        out = module(*args, **(kwargs or {}))
+        flat = pytree.tree_leaves(out)
+        flat[loss].backward()
+        return [p for p in params if p.grad is None]
+    finally:
+        for p, g in zip(params, saved):
+            p.grad = g
+
+
 def _retie(module: torch.nn.Module, tied: dict) -> None:
     for name, (_first, p) in tied.items():
         owner, _, leaf = name.rpartition(".")
@@ -111,7 +144,11 @@ def tied_gradients(grads: dict, tied: dict) -> dict:
             total[first] = g if total.get(first) is None else total[first] + g
         else:
             total.setdefault(first, None)
-    return {name: total.get(tied.get(name, name)) for name in grads}
+    out = {name: total.get(tied.get(name, name)) for name in grads}
+    for first in set(tied.values()):                       # a first name that is only ever reached through the others
+        if first not in out and first in total:
+            out[first] = total[first]
+    return out
 
 
 def _export(module, args, kwargs, loss, strict, decompositions, inner_cuts) -> Exported:

@@ -785,3 +785,39 @@ def _ring_rank(rank, world, rdv):
 def test_ring_attention_between_processes():
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_ring_rank, 3, init_pg="gloo")
+
+
+def test_shared_tables_and_unused_parameters_in_training_graphs():
+    """One table under three names of which the first is never read directly (encoder / decoder embeddings of a shared
+    table), plus a head that this call does not use: the capture leaves out what gets no gradient, and the shared
+    table's gradient - the sum over the names that are read - comes back under every one of its names."""
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.shared = torch.nn.Embedding(20, 8)
+            self.enc = torch.nn.Embedding(20, 8)
+            self.dec = torch.nn.Embedding(20, 8)
+            self.enc.weight = self.shared.weight
+            self.dec.weight = self.shared.weight
+            self.mix = torch.nn.Linear(8, 8)
+            self.unused = torch.nn.Linear(8, 3)
+
+        def forward(self, a, b):
+            return (self.mix(self.enc(a)) * self.dec(b)).sum(-1).pow(2).mean()
+
+    torch.manual_seed(40)
+    m = Net()
+    a, b = torch.randint(0, 20, (4, 6)), torch.randint(0, 20, (4, 6))
+    procs = _procs(2)
+    names = tuple(procs)
+    sch = compile_module(m, (a, b), procs, lambda n: (0, names, None) if n.op == "placeholder" and n.name in ("a", "b") else None, loss=0)
+    assert sch.exported.tied == {"enc.weight": "shared.weight", "dec.weight": "shared.weight"}
+    assert m.enc.weight is m.shared.weight and m.dec.weight is m.shared.weight and m.unused.weight.requires_grad
+    res = Program(sch)(a, b)
+    loss = m(a, b)
+    loss.backward()
+    assert abs(float(res.outputs.detach()) - float(loss.detach())) < 1e-5
+    assert "unused.weight" not in res.parameters
+    for name in ("shared.weight", "enc.weight", "dec.weight"):
+        assert torch.allclose(res.parameters[name], m.shared.weight.grad, atol=1e-6), name
+    assert torch.allclose(res.parameters["mix.weight"], m.mix.weight.grad, atol=1e-6)
