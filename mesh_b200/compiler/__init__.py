@@ -7,3 +7,4 @@ from .lower import lower  # noqa: F401,E402
 from .fuse import fuse_plan  # noqa: F401,E402
 from . import syncmon, check  # noqa: F401,E402
 from .bridge import Prepared, prepare, workspace  # noqa: F401,E402
+from . import attention_op  # noqa: F401,E402  (registers mesh::attention and its backward)

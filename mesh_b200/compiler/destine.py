@@ -24,7 +24,7 @@ from .placement import POINTWISE, local_indices
 aten = torch.ops.aten
 
 # meta keys that make the executor treat a call specially (its operands or result are rewritten on the way)
-_SPECIAL = ("draw", "causal_rows", "batch_arg", "bias_sizes", "groups_local", "once", "localize", "mean_as_sum", "vocab_parallel", "halo", "fallback")
+_SPECIAL = ("draw", "causal_rows", "batch_arg", "bias_sizes", "groups_local", "once", "query_rows", "localize", "mean_as_sum", "vocab_parallel", "halo", "fallback")
 
 
 def enabled() -> bool:

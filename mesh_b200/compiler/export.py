@@ -52,6 +52,17 @@ def _views_may_copy(gm: torch.fx.GraphModule) -> int:
     return n
 
 
+def _training_table() -> dict:
+    """The default table with attention kept one differentiable operator (``compiler/attention_op.py``) where it has
+    neither a mask tensor nor dropout; ``MESH_ATTENTION_OP=0`` leaves it to the plain expansion."""
+    import os
+    table = _default_table()
+    if os.environ.get("MESH_ATTENTION_OP", "1") != "0":
+        from .attention_op import substitute as attention
+        table[torch.ops.aten.scaled_dot_product_attention.default] = attention
+    return table
+
+
 def _inference_table() -> dict:
     """The default table without attention, which inference graphs keep whole."""
     table = _default_table()
@@ -161,7 +172,8 @@ def _export(module, args, kwargs, loss, strict, decompositions, inner_cuts) -> E
             decompositions = _inference_table()
         if loss is not None:
             _views_may_copy(ep.graph_module)
-        ep = ep.run_decompositions(decompositions if decompositions is not None else _default_table())
+        ep = ep.run_decompositions(decompositions if decompositions is not None else
+                                   (_training_table() if loss is not None else _default_table()))
         if expand_loops(ep.graph_module) + merge_repeats(ep.graph_module) + \
                 ((unflatten_products(ep.graph_module) + (unflatten_linears(ep.graph_module) if inner_cuts else 0))
                  if loss is None else 0):

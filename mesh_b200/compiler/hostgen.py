@@ -21,7 +21,7 @@ from .lower import lower
 aten = torch.ops.aten
 
 # meta keys and targets that need the executor's own handling
-_SPECIAL = ("draw", "causal_rows", "batch_arg", "bias_sizes", "groups_local", "once", "localize", "mean_as_sum", "vocab_parallel", "halo", "fallback")
+_SPECIAL = ("draw", "causal_rows", "batch_arg", "bias_sizes", "groups_local", "once", "query_rows", "localize", "mean_as_sum", "vocab_parallel", "halo", "fallback")
 _DISPATCHED = (aten.mm.default, aten.matmul.default, aten.scaled_dot_product_attention.default, aten.view.default,
                aten._unsafe_view.default)
 

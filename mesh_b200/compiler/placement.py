@@ -902,6 +902,10 @@ class Propagator:
             return
         if tgt in _CHANNEL_NORMS and self.channel_norm(node, tnames):
             return
+        if getattr(tgt, "namespace", None) == "mesh" and str(tgt) in ("mesh.attention.default", "mesh.attention_backward.default"):
+            from . import attention_op  # noqa: F401  (registers the operators)
+            if self.attention_operator(node, tnames, backward=str(tgt) == "mesh.attention_backward.default"):
+                return
         if tgt is aten.convolution_backward.default and self.channel_convolution_backward(node, tnames):
             return
         if tgt is aten._assert_tensor_metadata.default:
@@ -1707,6 +1711,68 @@ class Propagator:
         if not any(k in ("out", "in") for k, _ in kinds):
             return False                                   # nothing of this rule's: batch cuts have their own
         return kinds
+
+    def attention_operator(self, node, tnames, backward: bool = False) -> bool:
+        """``mesh::attention`` and its backward (``compiler/attention_op.py``).  Samples and heads are independent: a
+        cut there (the same on every operand, the key / value heads following the query heads' groups) is local.
+        Queries cut along the sequence stay cut: every processor attends its queries to all keys and values (gathered
+        if they were cut) and states where its queries sit in the whole sequence; in the backward the query gradient is
+        cut the same way and the key / value gradients are partial sums over the processors' queries.  An axis on
+        which everything is whole on one coordinate (a pipeline stage) runs there."""
+        from .attention_op import BACKWARD
+        off = 1 if backward else 0
+        q, k, v = tnames[off], tnames[off + 1], tnames[off + 2]
+        rows = [tnames[0], tnames[4], tnames[5]] if backward else []      # grad, out, lse: laid out like the queries
+        qs, ks = self.shape[q], self.shape[k]
+        group = qs[1] // ks[1] if ks[1] else 1
+        causal = node.args[6 if backward else 3]
+        wants = {n: [] for n in tnames}
+        like_q, like_kv, outs = [], [], []
+        meta = {}
+        for ax in range(self.na):
+            specs = [self.spec[n][ax] for n in tnames]
+            owned = self._owned(specs)
+            sq, sk = self.spec[q][ax], self.spec[k][ax]
+            cut = next((s for s in specs if s.kind == "S"), None)
+            if owned is not None:
+                like_q.append(owned); like_kv.append(owned); outs.append((owned, owned, owned))
+            elif cut is None:
+                like_q.append(R); like_kv.append(R); outs.append((R, R, R))
+            elif sq.kind == "S" and sq.dim == 2 and "rows" not in meta and (
+                    not sq.striped or len(set(sq.counts)) == 1) and (not causal or qs[2] == ks[2]):
+                like_q.append(Spec("S", 2, sq.counts, sq.striped)); like_kv.append(R)
+                outs.append((like_q[-1], P(), P()))
+                meta["rows"] = ax
+            elif cut.kind == "S" and cut.dim == 0 and not cut.striped:
+                like_q.append(Spec("S", 0, cut.counts)); like_kv.append(like_q[-1]); outs.append((like_q[-1],) * 3)
+            elif sq.kind == "S" and sq.dim == 1 and not sq.striped and all(c % group == 0 for c in sq.counts):
+                like_q.append(Spec("S", 1, sq.counts)); like_kv.append(Spec("S", 1, tuple(c // group for c in sq.counts)))
+                outs.append((like_q[-1], like_kv[-1], like_kv[-1]))
+            elif sq.kind == "R" and sk.kind == "S" and sk.dim == 1 and not sk.striped:
+                like_kv.append(Spec("S", 1, sk.counts)); like_q.append(Spec("S", 1, tuple(c * group for c in sk.counts)))
+                outs.append((like_q[-1], like_kv[-1], like_kv[-1]))
+            else:
+                like_q.append(R); like_kv.append(R); outs.append((R, R, R))
+        new_names = {}
+        for arg, n in zip([a for a in node.args if _is_tensor_node(a)], tnames):
+            spec = tuple(like_kv) if n in (k, v) and n not in (q,) else tuple(like_q)
+            if n in rows and n == tnames[5]:
+                spec = tuple(like_q)                         # lse [batch, heads, queries]: the same three leading dimensions
+            new_names[arg.name] = self.reshard(n, spec)
+        meta["full_shape"] = ()
+        if causal and "rows" in meta:
+            meta["query_rows"] = (meta["rows"], like_q[meta["rows"]], 8 if backward else 5, qs[2])
+        meta.pop("rows", None)
+        self.steps.append(Step("call", node.name, node.target, self.ref_args(node.args, new_names), self.ref_kwargs(node.kwargs), meta))
+        self.spec[node.name] = self.all_r()
+        n_out = 3 if backward else 2
+        for j in range(n_out):
+            if backward:
+                sp = tuple(o[j] for o in outs)
+            else:
+                sp = tuple(like_q)                           # out and lse follow the queries
+            self.spec[(node.name, j)] = sp
+        return True
 
     def channel_norm(self, node, tnames) -> bool:
         """Batch norm (every variant, forward and backward) over an input cut along its channels: channels are normalised

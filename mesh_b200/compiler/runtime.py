@@ -799,6 +799,16 @@ class Executor:
                 extra[0] = mask
                 return tgt(q, k, args[2], *extra, **kw)
             return tgt(q, k, args[2], attn_mask=mask, is_causal=False, **kw)
+        if "query_rows" in m:
+            # (grid axis, the queries' cut, position of the row arguments, queries in all): where this processor's
+            # queries sit in the whole sequence - a block starts at its offset, a round-robin share at its coordinate
+            ax, sp, pos, total = m["query_rows"]
+            rows = local_indices(sp, self.coords[ax], total)
+            if isinstance(rows, slice):
+                args[pos], args[pos + 1] = rows.start or 0, rows.step or 1
+            else:
+                rows = list(rows)
+                args[pos], args[pos + 1] = (rows[0] if rows else 0), ((rows[1] - rows[0]) if len(rows) > 1 else 1)
         if "once" in m:                                    # (argument, axes): a term every processor of those axes holds but
             pos, axes = m["once"]                           # that must enter a partial sum once - the first one brings it
             if any(self.coords[ax] != 0 for ax in axes) and isinstance(args[pos], torch.Tensor):

@@ -1,0 +1,80 @@
+"""``mesh::attention`` / ``mesh::attention_backward``: attention as one differentiable operator of training graphs."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from mesh_b200.compiler import Program, attention_op, compile_module
+from mesh_b200.models.llama import Decoder, megatron, sequence_parallel
+
+
+@pytest.mark.parametrize("kv_heads,causal", [(4, True), (2, True), (1, False)])
+def test_operator_and_its_backward_match_scaled_dot_product_attention(kv_heads, causal):
+    torch.manual_seed(0)
+    q = torch.randn(2, 4, 6, 8, requires_grad=True)
+    k = torch.randn(2, kv_heads, 6, 8, requires_grad=True)
+    v = torch.randn(2, kv_heads, 6, 8, requires_grad=True)
+    w = torch.randn(2, 4, 6, 8)
+    y = attention_op.substitute(q, k, v, is_causal=causal, enable_gqa=True)
+    (y * w).sum().backward()
+    mine = [t.grad.clone() for t in (q, k, v)]
+    for t in (q, k, v):
+        t.grad = None
+    ref = F.scaled_dot_product_attention(q, k, v, is_causal=causal, enable_gqa=True)
+    (ref * w).sum().backward()
+    assert torch.allclose(y, ref, atol=2e-6)
+    for a, t in zip(mine, (q, k, v)):
+        assert torch.allclose(a, t.grad, atol=2e-6)
+
+
+def test_queries_state_their_positions_in_the_whole_sequence():
+    torch.manual_seed(1)
+    q, k, v = (torch.randn(1, 2, 8, 4) for _ in range(3))
+    full = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+    block = torch.ops.mesh.attention(q[:, :, 4:], k, v, True, 0.5, 4, 1)[0]            # the second half of the queries
+    assert torch.allclose(block, full[:, :, 4:], atol=1e-6)
+    every_other = torch.ops.mesh.attention(q[:, :, 1::2], k, v, True, 0.5, 1, 2)[0]    # a round-robin share
+    assert torch.allclose(every_other, full[:, :, 1::2], atol=1e-6)
+    # a mask tensor or dropout: the plain formulation, same numbers
+    mask = torch.tril(torch.ones(8, 8, dtype=torch.bool))
+    assert torch.allclose(attention_op.substitute(q, k, v, attn_mask=mask), full, atol=1e-6)
+
+
+def _run(m, x, procs, place):
+    sch = compile_module(m, (x,), procs, place, loss=0)
+    res = Program(sch)(x)
+    for p in m.parameters():
+        p.grad = None
+    loss = m(x)
+    loss.backward()
+    assert abs(float(res.outputs.detach()) - float(loss.detach())) < 1e-5
+    scale = max(float(p.grad.abs().max()) for p in m.parameters())
+    for k, g in res.parameters.items():
+        r = dict(m.named_parameters())[k].grad
+        if g.shape != r.shape:
+            r = r[tuple(slice(0, n) for n in g.shape)]
+        assert (g - r).abs().max() <= 2e-5 * scale, k
+    return sch
+
+
+@pytest.mark.parametrize("n,units", [(2, None), (4, "striped"), (2, (3, 1))])
+def test_training_plans_carry_one_attention_and_one_backward_per_layer(n, units, monkeypatch):
+    torch.manual_seed(2)
+    m = Decoder(dim=32, heads=4, ffn=64, layers=2)
+    x = torch.randn(2, 8, 32)
+    procs = {f"p{i}": (0, "cpu") for i in range(n)}
+    # heads cut (Megatron): attention and its backward are local
+    sch = _run(m, x, procs, megatron(procs))
+    names = [str(st.target) for st in sch.plan.steps]
+    assert names.count("mesh.attention.default") == 2 and names.count("mesh.attention_backward.default") == 2
+    assert set(sch.structure["by_verb"]) == {"all_reduce"} and sch.structure["gathering_fallbacks"] == 0
+    # queries cut along the sequence: they stay cut and state their rows; keys and values are gathered, their
+    # gradients are partial sums
+    x = torch.randn(1, 8, 32)                                  # (one sample: the token cut is the rows' outermost factor)
+    sch = _run(m, x, procs, sequence_parallel(procs, units=units))
+    att = [st for st in sch.plan.steps if str(st.target) == "mesh.attention.default"]
+    assert len(att) == 2 and all("query_rows" in st.meta for st in att)
+    assert sch.structure["gathering_fallbacks"] == 0 and sch.structure["by_verb"].get("all_gather", 0) >= 4
+    fewer = len(sch.plan.steps)
+    monkeypatch.setenv("MESH_ATTENTION_OP", "0")               # the plain expansion: same numbers, many more steps
+    sch = _run(m, x, procs, sequence_parallel(procs, units=units))
+    assert not any("mesh.attention" in str(st.target) for st in sch.plan.steps) and len(sch.plan.steps) > fewer
