@@ -33,10 +33,12 @@ def compile_module(module, args, processors, placement, cost=unit_cost, planning
                    kwargs=None, **export_options) -> Scheduled:
     """Ahead-of-time compile of one module call.  ``loss=<flat output index>`` compiles forward+backward."""
     exported = _export.export(module, args, kwargs, **export_options)
-    if not exported.training and "inner_cuts" not in export_options and _cuts_inner_dimension(exported, placement):
-        # an input cut along an inner leading dimension (the batch of a sequence-first layout): capture again with the
-        # linear layers' leading dimensions kept apart, or the cut would be lost at the first flattening view
-        exported = _export.export(module, args, kwargs, inner_cuts=True, **export_options)
+    inner = _cuts_inner_dimension(exported, placement) if "inner_cuts" not in export_options else 0
+    if inner:
+        # an input cut along an inner leading dimension (the batch of a sequence-first layout, the tokens of several
+        # samples): capture again with the linear layers' leading dimensions kept apart (inference) or merged with the
+        # cut dimension outermost (training), or the cut would be lost at the first flattening view
+        exported = _export.export(module, args, kwargs, inner_cuts=inner, **export_options)
     sch = compile_captured(exported, processors, placement, cost, mesh)
     if exported.training and "decompositions" not in export_options and _gathers_for_batch_statistics(sch):
         # a training-mode batch norm whose input is cut along the batch (or a spatial dimension) would gather it to get
@@ -56,12 +58,12 @@ def _gathers_for_batch_statistics(sch) -> bool:
     return any(st.target in batch_norms and st.meta.get("fallback") and st.meta.get("gathered") for st in sch.plan.steps)
 
 
-def _cuts_inner_dimension(exported, placement) -> bool:
+def _cuts_inner_dimension(exported, placement) -> int:
     """Does the stated placement cut a user input of three or more dimensions along a dimension that is neither its
     last nor, once dimensions of size one are set aside, its first?  (A cut behind leading dimensions of size one is
     still the outermost factor of the merged rows, which the view rule describes.)"""
     if not callable(placement):
-        return False
+        return 0
     for node in exported.graph_module.graph.nodes:
         if node.op != "placeholder":
             continue
@@ -80,8 +82,8 @@ def _cuts_inner_dimension(exported, placement) -> bool:
             dims = [first] if isinstance(first, int) else [d for d in first if isinstance(d, int)] if isinstance(first, (tuple, list)) else []
             for dim in dims:                                 # (the N-D form states one dimension per grid axis)
                 if 0 < dim % nd < nd - 1 and math.prod(val.shape[:dim % nd]) > 1:
-                    return True
-    return False
+                    return dim % nd                          # the cut dimension (truthy: never the first)
+    return 0
 
 
 def compile_program(program, args, functions, processors, placement, cost=unit_cost, planning=None, machine=None,

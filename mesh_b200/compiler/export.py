@@ -183,6 +183,8 @@ def _export(module, args, kwargs, loss, strict, decompositions, inner_cuts) -> E
             for spec, node in zip(ep.graph_signature.output_specs, out_node.args[0]):
                 if isinstance(node, torch.fx.Node) and hasattr(spec.arg, "name"):
                     spec.arg.name = node.name
+        if loss is not None and inner_cuts:
+            outermost_rows(ep.graph_module, int(inner_cuts) if not isinstance(inner_cuts, bool) else 1)
         if loss is not None:
             from torch.export.experimental import _export_forward_backward
             # ``loss`` counts the module's own outputs; new values of mutated buffers come before them in the graph
@@ -431,6 +433,72 @@ def unflatten_linears(gm: torch.fx.GraphModule) -> int:
             u.replace_all_uses_with(res)
             gm.graph.erase_node(u)
         gm.graph.erase_node(node)
+        done += 1
+    if done:
+        gm.graph.eliminate_dead_code()
+        gm.graph.lint()
+        gm.recompile()
+    return done
+
+
+def outermost_rows(gm: torch.fx.GraphModule, dim: int) -> int:
+    """The training-graph counterpart of :func:`unflatten_linears`.  There the weight gradient contracts over the merged
+    rows, so the rows have to stay merged; instead the merge is made in another order: the leading dimension ``dim``
+    (the one that is cut: the tokens of a ``[B, T, E]`` layout) is moved to the front first,
+
+        view([B, T, K] -> [B*T, K]); mm; view([B*T, N] -> [B, T, N])
+            ->  permute -> [T, B, K]; clone; view([T*B, K]); mm; view([T, B, N]); permute -> [B, T, N]
+
+    which makes the cut the outermost factor of the rows - something the view rule describes - in the forward product
+    and, through differentiation of the rewritten graph, in both backward products: activations cut along the tokens
+    stay cut through the linear layers of a training step with several samples (the price is the transposing copy)."""
+    aten = torch.ops.aten
+    views = (aten.view.default, aten._unsafe_view.default, aten.reshape.default)
+    done = 0
+    for node in list(gm.graph.nodes):
+        if node.op != "call_function" or node.target not in (aten.mm.default, aten.addmm.default):
+            continue
+        off = 1 if node.target is aten.addmm.default else 0
+        if len(node.kwargs) or len(node.args) != 2 + off:
+            continue
+        flat, w = node.args[off], node.args[off + 1]
+        if not (isinstance(flat, torch.fx.Node) and flat.op == "call_function" and flat.target in views and isinstance(w, torch.fx.Node)):
+            continue
+        src = flat.args[0]
+        a, f, out = (n.meta.get("val") for n in (src, flat, node))
+        if not all(isinstance(t, torch.Tensor) for t in (a, f, out)) or f.ndim != 2 or a.ndim < 3 or not 0 < dim < a.ndim - 1:
+            continue
+        lead = tuple(a.shape[:-1])
+        if math.prod(lead) != f.shape[0] or a.shape[-1] != f.shape[1] or math.prod(lead[:dim]) == 1:
+            continue
+        want = lead + (out.shape[1],)
+        users = list(node.users)
+        if not users or not all(u.op == "call_function" and u.target in views and tuple(u.meta["val"].shape) == want for u in users):
+            continue
+        nd = a.ndim
+        perm = [dim] + [d for d in range(nd - 1) if d != dim] + [nd - 1]
+        back = [perm.index(d) for d in range(nd)]
+        with gm.graph.inserting_before(node):
+            moved = gm.graph.call_function(aten.permute.default, (src, perm))
+            moved.meta["val"] = a.permute(perm)
+            dense = gm.graph.call_function(aten.clone.default, (moved,), {"memory_format": torch.contiguous_format})
+            dense.meta["val"] = a.permute(perm).contiguous()
+            rows = gm.graph.call_function(aten.view.default, (dense, [f.shape[0], f.shape[1]]))
+            rows.meta["val"] = dense.meta["val"].reshape(f.shape[0], f.shape[1])
+            for n in (moved, dense, rows):
+                n.meta.update({k: v for k, v in flat.meta.items() if k != "val"})
+        node.replace_input_with(flat, rows)
+        with gm.graph.inserting_after(node):
+            shaped = gm.graph.call_function(aten.view.default, (node, [a.shape[d] for d in perm[:-1]] + [out.shape[1]]))
+        with gm.graph.inserting_after(shaped):
+            restored = gm.graph.call_function(aten.permute.default, (shaped, back))
+        shaped.meta.update({k: v for k, v in users[0].meta.items() if k != "val"})
+        restored.meta.update({k: v for k, v in users[0].meta.items() if k != "val"})
+        shaped.meta["val"] = out.reshape([a.shape[d] for d in perm[:-1]] + [out.shape[1]])
+        restored.meta["val"] = shaped.meta["val"].permute(back)
+        for u in users:
+            u.replace_all_uses_with(restored)
+            gm.graph.erase_node(u)
         done += 1
     if done:
         gm.graph.eliminate_dead_code()

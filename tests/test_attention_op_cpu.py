@@ -78,3 +78,22 @@ def test_training_plans_carry_one_attention_and_one_backward_per_layer(n, units,
     monkeypatch.setenv("MESH_ATTENTION_OP", "0")               # the plain expansion: same numbers, many more steps
     sch = _run(m, x, procs, sequence_parallel(procs, units=units))
     assert not any("mesh.attention" in str(st.target) for st in sch.plan.steps) and len(sch.plan.steps) > fewer
+
+
+@pytest.mark.parametrize("n,units", [(2, None), (3, (3, 1, 2))])
+def test_token_cut_survives_a_training_step_with_several_samples(n, units):
+    """``[B, T, E]`` with B > 1 and the tokens cut: the capture merges the rows of every linear layer with the tokens
+    outermost, so the activations stay cut through forward and backward products - queries keep their rows, weight
+    gradients are partial sums over the processors' tokens (all-reduced), key / value gradients are reduce-scattered;
+    nothing gathers an activation for want of a description."""
+    torch.manual_seed(3)
+    m = Decoder(dim=32, heads=4, ffn=64, layers=2)
+    x = torch.randn(2, 8, 32)
+    procs = {f"p{i}": (0, "cpu") for i in range(n)}
+    sch = _run(m, x, procs, sequence_parallel(procs, units=units))
+    att = [st for st in sch.plan.steps if str(st.target) == "mesh.attention.default"]
+    assert len(att) == 2 and all("query_rows" in st.meta for st in att)
+    verbs = sch.structure["by_verb"]
+    assert verbs.get("reduce_scatter", 0) == 2 and verbs["all_reduce"] >= len(list(m.parameters()))
+    gathered = [t.value for t in sch.plan.transfers if t.verb == "all_gather"]
+    assert len(gathered) == 6                              # keys and values of two layers forward, the output, one loss term
