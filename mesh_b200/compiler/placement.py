@@ -1738,7 +1738,7 @@ class Propagator:
                 like_q.append(owned); like_kv.append(owned); outs.append((owned, owned, owned))
             elif cut is None:
                 like_q.append(R); like_kv.append(R); outs.append((R, R, R))
-            elif sq.kind == "S" and sq.dim == 2 and "rows" not in meta and (
+            elif sq.kind == "S" and sq.dim == 2 and "rows" not in meta and len({q, k, v}) == 3 and (
                     not sq.striped or len(set(sq.counts)) == 1) and (not causal or qs[2] == ks[2]):
                 like_q.append(Spec("S", 2, sq.counts, sq.striped)); like_kv.append(R)
                 outs.append((like_q[-1], P(), P()))

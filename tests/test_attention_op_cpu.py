@@ -97,3 +97,25 @@ def test_token_cut_survives_a_training_step_with_several_samples(n, units):
     assert verbs.get("reduce_scatter", 0) == 2 and verbs["all_reduce"] >= len(list(m.parameters()))
     gathered = [t.value for t in sch.plan.transfers if t.verb == "all_gather"]
     assert len(gathered) == 6                              # keys and values of two layers forward, the output, one loss term
+
+
+@pytest.mark.parametrize("dim", [0, 1])
+def test_attention_of_one_tensor_with_itself(dim):
+    """``attention(h, h, h)``: one value is queries, keys and values at once, so it cannot be both cut (as queries) and
+    whole (as keys) along the sequence - that axis gathers; a cut along the samples is local as ever."""
+    import torch.nn as nn
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.l = nn.Linear(8, 8)
+
+        def forward(self, x):
+            h = self.l(x).view(2, 6, 2, 4).transpose(1, 2)
+            return F.scaled_dot_product_attention(h, h, h, is_causal=True).pow(2).mean()
+    torch.manual_seed(4)
+    m, x = Net(), torch.randn(2, 6, 8)
+    procs = {f"p{i}": (0, "cpu") for i in range(2)}
+    names = tuple(procs)
+    sch = _run(m, x, procs, lambda n: (dim, names, None) if n.name == "x" else None)
+    assert ("all_gather" in sch.structure["by_verb"]) == (dim == 1)
