@@ -60,6 +60,10 @@ def check_plan(plan: Plan) -> list[str]:
         if st.out in defined:
             problems.append(f"step {i} defines {st.out!r} a second time")
         defined.add(st.out)
+        if st.op == "fused" and "keep" in st.meta:
+            defined.add(st.meta["keep"])                     # the gathered rows it hands on to the other readers
+        if st.op == "fused" and "channel" in st.meta:
+            n_collective += len(st.meta.get("channels", (st.meta["channel"],)))      # a fused step stands for its transfers
         if st.op == "collective":
             n_collective += 1
             ax = st.meta.get("axis")

@@ -112,3 +112,30 @@ def test_sync_monitor_matches_the_signature_and_names_divergence(monkeypatch):
     t[1], t[2] = t[2], t[1]
     rep = syncmon.compare(sch, t, prog.plan)
     assert not rep["ok"] and rep["first_divergence"]["index"] == 1 and rep["missing"] == []
+
+
+def test_plans_with_fused_steps_pass_the_checker():
+    """Fused (collective, product) pairs hand their gathered rows on under another name, and a ring step stands for the
+    two gathers it replaced: the checker knows both."""
+    import torch
+    from mesh_b200.compiler import Program, check, compile_module
+    from mesh_b200.models.llama import Decoder, megatron, sequence_parallel
+    procs = {f"p{i}": (0, "cpu") for i in range(2)}
+    names = tuple(procs)
+    m = Decoder(dim=512, heads=4, ffn=1024, layers=1).eval()
+    x = torch.randn(1, 256, 512)
+    tp = megatron(procs)
+    prog = Program(compile_module(m, (x,), procs, lambda nd: (1, names, None) if nd.op == "placeholder" and nd.name == "x" else tp(nd)))
+    assert prog.fusion["ag_mm"] == 2 and check.check_plan(prog.plan) == []
+
+    class Blocks(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.d = Decoder(dim=32, heads=4, ffn=64, layers=1)
+
+        def forward(self, x):
+            for b in self.d.blocks:
+                x = b(x)
+            return x
+    prog = Program(compile_module(Blocks().eval(), (torch.randn(2, 12, 32),), procs, sequence_parallel(procs)))
+    assert prog.fusion["ring_attention"] == 1 and check.check_plan(prog.plan) == []
