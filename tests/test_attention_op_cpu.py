@@ -119,3 +119,26 @@ def test_attention_of_one_tensor_with_itself(dim):
     names = tuple(procs)
     sch = _run(m, x, procs, lambda n: (dim, names, None) if n.name == "x" else None)
     assert ("all_gather" in sch.structure["by_verb"]) == (dim == 1)
+
+
+def _sp_rank(rank, world, rdv):
+    torch.manual_seed(6)
+    m = Decoder(dim=32, heads=4, ffn=64, layers=1)
+    x = torch.randn(2, 9, 32)
+    procs = {f"p{i}": (0, "cpu") for i in range(world)}
+    sch = compile_module(m, (x,), procs, sequence_parallel(procs, units=(4, 2, 3)), loss=0)
+    prog = Program(sch)
+    assert not prog.threads
+    res = prog(x)                                          # one process per processor
+    loss = m(x)
+    loss.backward()
+    assert abs(float(res.outputs.detach()) - float(loss.detach())) < 1e-5
+    scale = max(float(p.grad.abs().max()) for p in m.parameters())
+    for k, g in res.parameters.items():
+        r = dict(m.named_parameters())[k].grad
+        assert g.shape == r.shape and (g - r).abs().max() <= 2e-5 * scale, k
+
+
+def test_sequence_parallel_training_between_processes():
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_sp_rank, 3, init_pg="gloo")

@@ -282,3 +282,36 @@ def test_numerics_keep_a_cut_along_the_samples(name):
     assert sch.structure["gathering_fallbacks"] == 0, [str(s.target) for s in sch.plan.steps if s.meta.get("gathered")]
     if name == "histogram":                                    # every processor counts its own elements: one small sum
         assert sch.structure["by_verb"] == {"all_reduce": 1}
+
+
+def _zoo_rank(rank, world, rdv):
+    # channel-parallel, strided-halo and depthwise convolutions with norms, one process per processor
+    for name, dim in (("strided_convolutions", 1), ("strided_convolutions", 2), ("depthwise_separable", 1), ("residual_batch_norm", 0)):
+        make, shape = ZOO[name]
+        torch.manual_seed(0)
+        model = _Loss(make()).train()
+        eager = copy.deepcopy(model)
+        x = torch.randn(*shape)
+        procs = _procs(world)
+        names = tuple(procs)
+
+        def place(node):
+            val = node.meta.get("val")
+            mine = node.op == "placeholder" and not node.name.startswith(("p_", "b_")) and getattr(val, "shape", None) == x.shape
+            return (dim, names, None) if mine else None
+        prog = Program(compile_module(model, (x,), procs, place, loss=0))
+        assert not prog.threads
+        res = prog(x)
+        ref = eager(x)
+        ref.backward()
+        assert abs(float(res.outputs.detach()) - float(ref.detach())) <= 1e-5 * max(1.0, abs(float(ref.detach()))), name
+        scale = max(float(p.grad.abs().max()) for p in eager.parameters())
+        for k, g in res.parameters.items():
+            r = dict(eager.named_parameters())[k].grad
+            if g is not None and g.shape == r.shape:
+                assert (g - r).abs().max() <= 2e-5 * scale, (name, k)
+
+
+def test_zoo_models_between_processes():
+    from mesh_b200.utils.launch import spawn_ranks
+    spawn_ranks(_zoo_rank, 2, init_pg="gloo")
