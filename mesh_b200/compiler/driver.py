@@ -69,7 +69,8 @@ def _cuts_inner_dimension(exported, placement) -> int:
             continue
         val = node.meta.get("val")
         nd = getattr(val, "ndim", 0)
-        if nd < 3:
+        indices = nd == 2 and not (val.dtype.is_floating_point or val.dtype.is_complex)     # token ids: an embedding adds
+        if nd < 3 and not indices:                                                           # the feature dimension later
             continue
         try:
             stated = placement(node)
@@ -81,7 +82,7 @@ def _cuts_inner_dimension(exported, placement) -> int:
             first = item[0] if isinstance(item, tuple) and item else None
             dims = [first] if isinstance(first, int) else [d for d in first if isinstance(d, int)] if isinstance(first, (tuple, list)) else []
             for dim in dims:                                 # (the N-D form states one dimension per grid axis)
-                if 0 < dim % nd < nd - 1 and math.prod(val.shape[:dim % nd]) > 1:
+                if 0 < dim % nd < nd - (0 if indices else 1) and math.prod(val.shape[:dim % nd]) > 1:
                     return dim % nd                          # the cut dimension (truthy: never the first)
     return 0
 

@@ -504,6 +504,7 @@ def outermost_rows(gm: torch.fx.GraphModule, dim: int) -> int:
         gm.graph.eliminate_dead_code()
         gm.graph.lint()
         gm.recompile()
+        _views_may_copy(gm)        # what comes back from a product is a permuted value now: later views of it may have to copy
     return done
 
 

@@ -173,8 +173,9 @@ def fuse_ring_attention(plan: Plan) -> tuple[Plan, int]:
     (blockwise attention with ring rotation, the reference's attention operator,
     compiler/mesh_compiler/operations.py:7081-7166).  No processor ever holds the whole keys and values; the bytes on
     the links are those of the two gathers.  A causal mask goes by the positions of the tokens in the whole sequence,
-    for contiguous and striped cuts alike.  Applies when the gathered values have no other reader, there is no mask
-    tensor and no dropout."""
+    for contiguous and striped cuts alike; a mask tensor ``[.., queries, keys]`` is read by the rows this processor holds
+    and the columns of the block at hand; a block that a causal mask hides entirely is skipped.  Applies when the
+    gathered values have no other reader and there is no dropout."""
     sdpa = aten.scaled_dot_product_attention.default
     plan = copy.copy(plan)
     steps = list(plan.steps)
@@ -190,7 +191,10 @@ def fuse_ring_attention(plan: Plan) -> tuple[Plan, int]:
             continue
         opt = dict(zip(("attn_mask", "dropout_p", "is_causal"), st.args[3:6]))
         opt.update(st.kwargs)
-        if opt.get("attn_mask") is not None or (opt.get("dropout_p") or 0.0) != 0.0:
+        if (opt.get("dropout_p") or 0.0) != 0.0:
+            continue
+        mask = opt.get("attn_mask")
+        if mask is not None and not isinstance(mask, Ref):
             continue
         cut = [(ax, sp) for ax, sp in enumerate(st.meta["out_specs"]) if sp.kind == "S" and sp.dim == 2]
         if len(cut) != 1:
@@ -216,7 +220,9 @@ def fuse_ring_attention(plan: Plan) -> tuple[Plan, int]:
                      "causal": bool(opt.get("is_causal", False)) or "causal_rows" in st.meta, "scale": opt.get("scale"),
                      "enable_gqa": bool(opt.get("enable_gqa", False)), "keys": tuple(kg.meta["full_shape"]),
                      "channels": (kg.meta["channel"], vg.meta["channel"])})
-        replace[i] = Step("fused", st.out, "ring_attention", (st.args[0], kg.args[0], vg.args[0]), {}, meta)
+        operands = (st.args[0], kg.args[0], vg.args[0]) + ((mask,) if mask is not None else ())
+        meta["masked"] = mask is not None
+        replace[i] = Step("fused", st.out, "ring_attention", operands, {}, meta)
         drop.update(gathers)
         count += 1
     if count:

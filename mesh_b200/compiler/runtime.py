@@ -491,7 +491,7 @@ class Executor:
                           else FusedRowLinear(ctx.heap, rows_total, w.shape[1], w.shape[0]))
         return cache[key]
 
-    def ring_attention(self, st: Step, q, k, v):
+    def ring_attention(self, st: Step, q, k, v, mask=None):
         """Blockwise attention with the key / value blocks rotating around the axis (``fuse.fuse_ring_attention``).
         Round ``r`` attends this processor's queries to the block that started on processor ``me - r``; partial results
         are merged by running maximum and sum (rows that have seen nothing yet carry weight zero); a causal mask
@@ -516,6 +516,8 @@ class Executor:
         qf = q.float() * scale
         group = q.shape[1] // k.shape[1] if k.shape[1] and q.shape[1] != k.shape[1] else 1
         qpos = positions(me)
+        if mask is not None and mask.shape[-2] == total and total != q.shape[2]:
+            mask = mask.index_select(-2, qpos)               # a whole mask: the rows of this processor's queries
         acc = torch.zeros(*q.shape[:-1], v.shape[-1], dtype=torch.float32, device=q.device)
         top = torch.full((*q.shape[:-1], 1), float("-inf"), dtype=torch.float32, device=q.device)
         den = torch.zeros_like(top)
@@ -527,13 +529,17 @@ class Executor:
             src = (me - r) % P
             if threads is not None:
                 kb, vb = threads[0][src], threads[1][src]
-            if kb.shape[2]:
+            hidden = bool(m.get("causal")) and kb.shape[2] and qpos.numel() and int(positions(src).min()) > int(qpos.max())
+            if kb.shape[2] and not hidden:                   # (a block wholly in these queries' future adds nothing)
                 kk, vv = kb.float(), vb.float()
                 if group > 1:
                     kk, vv = kk.repeat_interleave(group, 1), vv.repeat_interleave(group, 1)
                 s = qf @ kk.transpose(-1, -2)
                 if m.get("causal"):
                     s = s.masked_fill(positions(src)[None, :] > qpos[:, None], float("-inf"))
+                if mask is not None:
+                    cols = mask.index_select(-1, positions(src))
+                    s = s.masked_fill(cols.logical_not(), float("-inf")) if cols.dtype == torch.bool else s + cols.float()
                 blk = s.amax(-1, keepdim=True)
                 new = torch.maximum(top, blk)
                 safe = torch.where(torch.isinf(new), torch.zeros_like(new), new)      # rows that still see nothing
@@ -561,7 +567,10 @@ class Executor:
     def fused(self, st: Step, a, w_t, env=None):
         m = st.meta
         if st.target == "ring_attention":
-            return self.ring_attention(st, a, w_t, None if env is None else env.get(st.args[2].name))
+            rest = [None if env is None else env.get(r.name) for r in st.args[2:]]
+            if m.get("masked") and rest[1] is None:
+                return None
+            return self.ring_attention(st, a, w_t, *rest)
         if a is None or w_t is None:
             if "keep" in m and env is not None:
                 env[m["keep"]] = None                        # absent here: so are the gathered rows for the other readers

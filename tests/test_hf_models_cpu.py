@@ -60,9 +60,12 @@ def test_inference_logits_under_batch_and_sequence_cuts(make, dim):
     ids = torch.randint(0, 128, (4, 16))
     procs = {f"p{i}": (0, "cpu") for i in range(2)}
     sch = compile_module(model, (ids,), procs, _place(ids, dim, tuple(procs)), strict=False)
-    got, ref = Program(sch)(ids), model(ids)
+    prog = Program(sch)
+    got, ref = prog(ids), model(ids)
     assert (got - ref).abs().max() <= 1e-5 * ref.abs().max()
     assert sch.structure["gathering_fallbacks"] == 0       # attention with its mask tensor keeps the cut
+    # tokens cut: every layer's attention is a ring step that reads its mask by rows held and columns of the block at hand
+    assert prog.fusion["ring_attention"] == (2 if dim == 1 else 0)
 
 
 @pytest.mark.parametrize("make,dim", [(_llama, 0), (_llama, 1), (_gpt2, 0), (_gpt2, 1)])
