@@ -158,3 +158,68 @@ def test_row_parallel_layers_with_a_bias_keep_their_partial_sums():
     assert len(once) == 4                                     # the four row-parallel layers
     got, ref = Program(sch)(ids), model(ids)
     assert (got - ref).abs().max() <= 1e-5 * ref.abs().max()
+
+
+def _vit():
+    cfg = transformers.ViTConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=32,
+                                 patch_size=8, num_labels=5, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    return (transformers.ViTForImageClassification(cfg), (torch.randn(4, 3, 32, 32), torch.randint(0, 5, (4,))),
+            lambda m, x, y: m(pixel_values=x, labels=y).loss)
+
+
+def _resnet():
+    cfg = transformers.ResNetConfig(num_channels=3, embedding_size=8, hidden_sizes=[8, 16], depths=[1, 1], layer_type="basic", num_labels=5)
+    return (transformers.ResNetForImageClassification(cfg), (torch.randn(4, 3, 32, 32), torch.randint(0, 5, (4,))),
+            lambda m, x, y: m(pixel_values=x, labels=y).loss)
+
+
+def _t5():
+    cfg = transformers.T5Config(vocab_size=128, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_heads=4, dropout_rate=0.0,
+                                decoder_start_token_id=0, pad_token_id=0)
+    return (transformers.T5ForConditionalGeneration(cfg), (torch.randint(0, 128, (4, 12)), torch.randint(0, 128, (4, 8))),
+            lambda m, x, y: m(input_ids=x, labels=y).loss)
+
+
+class _Call(nn.Module):
+    def __init__(self, m, f):
+        super().__init__()
+        self.m, self.f = m, f
+
+    def forward(self, *a):
+        return self.f(self.m, *a)
+
+
+@pytest.mark.parametrize("family", [_vit, _resnet, _t5])
+def test_other_families_train_under_a_batch_cut(family):
+    """A vision transformer (patch-embedding convolution), a residual network (training-mode batch norm: captured again
+    with its statistics as sums) and an encoder-decoder with one table under four names, data-parallel on two
+    processors: eager's loss and gradients."""
+    torch.manual_seed(0)
+    base, inputs, call = family()
+    try:
+        base.config._attn_implementation = "sdpa"
+    except Exception:
+        pass
+    model = _Call(base, call).train()
+    procs = {f"p{i}": (0, "cpu") for i in range(2)}
+    names = tuple(procs)
+
+    def place(node):
+        val = node.meta.get("val")
+        user = node.op == "placeholder" and not node.name.startswith(("p_", "b_", "c_"))
+        return (0, names, None) if user and getattr(val, "ndim", 0) >= 1 and val.shape[0] == 4 else None
+    sch = compile_module(model, inputs, procs, place, strict=False, loss=0)
+    res = Program(sch)(*inputs)
+    ref = model(*inputs)
+    ref.backward()
+    assert abs(float(res.outputs.detach()) - float(ref.detach())) <= 1e-5 * max(1.0, abs(float(ref.detach())))
+    scale = max(float(p.grad.abs().max()) for p in model.parameters() if p.grad is not None)
+    shared = dict(model.named_parameters(remove_duplicate=False))
+    checked = 0
+    for name, g in res.parameters.items():
+        r = shared[name].grad
+        if r is None or g is None:
+            continue
+        assert g.shape == r.shape and (g - r).abs().max() <= 3e-5 * scale, name
+        checked += 1
+    assert checked >= 10
