@@ -273,6 +273,17 @@ def _repeated(node, shapes):
     return info
 
 
+def _matrices_with_vectors(outs: int):
+    """Operands that are stacks of matrices together with stacks of vectors over the same leading dimensions (an LU
+    factorisation with its pivots, a matrix with a new diagonal): the leading dimensions are a batch for all of them."""
+    def describe(node, shapes):
+        nd = len(shapes[0])
+        if nd < 3:
+            return None
+        return {"batched": [True] * len(shapes), "protect": {nd - 2, nd - 1}, "outs": ["S"] * outs}
+    return describe
+
+
 def _layer_norm(node, shapes):
     core = len(node.args[1])
     nd = len(shapes[0])
@@ -398,6 +409,9 @@ BATCHED = {
     aten.linalg_householder_product.default: _trailing(2, 1), aten.geqrf.default: _trailing(2, 2),
     aten.triangular_solve.default: _trailing(2, 2),
     aten.repeat.default: _repeated, aten.repeat_interleave.self_int: _along(2, 1, default=None),
+    aten._cdist_backward.default: _trailing(2, 1), aten.grid_sampler_2d_backward.default: _trailing(3, 2),
+    aten.linalg_lu_solve.default: _matrices_with_vectors(1), aten.lu_unpack.default: _matrices_with_vectors(3),
+    aten.diagonal_scatter.default: _matrices_with_vectors(1),
 }
 _NORMS = {aten.linalg_vector_norm.default}
 # batch norm variants: how many leading arguments are tensors (some optional), which of them have the input's shape,

@@ -315,3 +315,27 @@ def _zoo_rank(rank, world, rdv):
 def test_zoo_models_between_processes():
     from mesh_b200.utils.launch import spawn_ranks
     spawn_ranks(_zoo_rank, 2, init_pg="gloo")
+
+
+# the same functions differentiated: the backward operators keep the cut too (input gradients against eager's)
+DIFFERENTIATED = ["fourier_2d", "complex", "distances", "determinant_inverse", "solves", "spectra", "matrix_exponential", "lu",
+                  "scans", "scatters", "windows", "sampler", "norms", "losses", "contractions", "repeats", "blends", "pools_1d"]
+
+
+@pytest.mark.parametrize("name", DIFFERENTIATED)
+def test_numerics_backward_keeps_a_cut_along_the_samples(name):
+    f, shape = NUMERICS[name]
+    torch.manual_seed(0)
+    x = torch.randn(*shape, requires_grad=True)
+    model = _Loss(_Function(f))
+    procs = _procs(2)
+    names = tuple(procs)
+    sch = compile_module(model, (x,), procs, lambda node: (0, names, None) if node.op == "placeholder" and node.name == "x" else None, loss=0)
+    res = Program(sch)(x)
+    ref = model(x)
+    ref.backward()
+    assert abs(float(res.outputs.detach()) - float(ref.detach())) <= 1e-5 * max(1.0, abs(float(ref.detach())))
+    got = next(iter(res.inputs.values()))
+    want = x.grad[: got.shape[0]] if got.shape != x.grad.shape else x.grad
+    assert (got - want).abs().max() <= 2e-4 * (want.abs().max() + 1e-9)
+    assert sch.structure["gathering_fallbacks"] == 0, [str(s.target) for s in sch.plan.steps if s.meta.get("gathered")]
