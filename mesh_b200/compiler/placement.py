@@ -476,6 +476,13 @@ class Propagator:
 
     def emit_collective(self, verb: str, kind: str, axis: int, src: str, spec_from: Spec, spec_to: Spec, consumer=JOIN) -> str:
         out = self.fresh(src)
+        if self.mesh.shape[axis] == 1:
+            # an axis of one processor: the value is already what the transfer would make of it
+            self.steps.append(Step("alias", out, None, (Ref(src),)))
+            self.shape[out] = self.shape[src]
+            if src in self.dtype:
+                self.dtype[out] = self.dtype[src]
+            return out
         self.channel += 1
         shp = self.shape[src]
         nbytes = int(math.prod(shp)) * (torch.empty((), dtype=self.dtype[src]).element_size() if src in self.dtype else 4)
