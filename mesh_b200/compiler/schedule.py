@@ -298,7 +298,7 @@ def planned(plan: Plan, step_us: float = 10.0, bucket_bytes: int = 32 << 20, sta
             "summary": summary}
 
 
-def pipelined(plan: Plan, cost=unit_cost, step_us: float = 10.0) -> dict:
+def pipelined(plan: Plan, cost=unit_cost, step_us: float = 10.0, observed: dict | None = None) -> dict:
     """The steady state of the plan when it is started again and again by an executor that overlaps transfers with
     compute (``runtime/plan.py::plan_pipeline``, the native planner's modulo scheduler): every step is a task - compute
     steps on the processor's stream in program order, every transfer on the links of its axis in program order, a
@@ -306,7 +306,8 @@ def pipelined(plan: Plan, cost=unit_cost, step_us: float = 10.0) -> dict:
     the plan's data flow as dependences and the lag-1 edge of every collective (its staging is reused by the same
     collective of the next execution).  ``{"period_us", "latency_us", "copies", "resource_bound_us",
     "recurrence_bound_us", "bound_by"}``: how often an execution can start, how long one takes, how many sets of buffers
-    that needs (what ``Prepared`` takes as its default ``copies``), and which resource sets the period."""
+    that needs (what ``Prepared`` takes as its default ``copies``), and which resource sets the period.  ``observed``:
+    a report of ``compiler/observe.py::observe`` for this plan - every step's measured time replaces its modelled one."""
     from ..runtime.plan import plan_pipeline
     steps = plan.steps
     n = len(steps)
@@ -328,6 +329,10 @@ def pipelined(plan: Plan, cost=unit_cost, step_us: float = 10.0) -> dict:
             nothing = st.op in free or st.target is operator.getitem
             dur.append(0.0 if nothing else float(cost(st)) * step_us)
             res.append(0)
+    if observed is not None:
+        for rec in observed.get("steps", ()):
+            if 0 <= rec["index"] < n:
+                dur[rec["index"]] = float(rec["seconds"]) * 1e6
     produced = {st.out: i for i, st in enumerate(steps)}
     edges, last_on = [], {}
     for i, st in enumerate(steps):

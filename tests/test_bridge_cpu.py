@@ -122,3 +122,20 @@ def test_workspace_states_the_steady_state_of_repeated_starts():
     assert p.copies == min(4, max(1, pipe["copies"]))
     p.start(x)
     assert torch.allclose(p.result(), m(x), atol=1e-5)
+
+
+def test_steady_state_from_observed_step_times():
+    """Measured step times (``observe``) in place of the modelled ones: the period is at least the measured compute."""
+    import torch
+    from mesh_b200.compiler import Program, compile_module, schedule
+    from mesh_b200.compiler.observe import observe
+    from mesh_b200.models.llama import Decoder, megatron
+    torch.manual_seed(0)
+    m = Decoder(dim=32, heads=2, ffn=64, layers=1).eval()
+    x = torch.randn(2, 8, 32)
+    procs = {f"p{i}": (0, "cpu") for i in range(2)}
+    prog = Program(compile_module(m, (x,), procs, megatron(procs)))
+    report = observe(prog, x)
+    pipe = schedule.pipelined(prog.plan, observed=report)
+    compute_us = sum(r["seconds"] for r in report["steps"] if r["op"] not in ("collective",)) * 1e6
+    assert pipe["period_us"] >= 0.5 * compute_us and pipe["latency_us"] >= pipe["period_us"] * 0.5 and pipe["copies"] >= 1
